@@ -1,0 +1,93 @@
+"""Builds the single native library ``elfa_b200/_native/libelfa_b200.so`` from ``elfa_b200/csrc``.
+
+Every ``.cu`` file is compiled for sm_100a only (``-gencode arch=compute_100a,code=sm_100a``) with
+``nvcc`` (no GPU needed: nvcc cross-compiles) and linked into one shared object that the Python
+side loads with ``ctypes``. Objects are rebuilt only when their source or a header is newer.
+
+    python -m elfa_b200.build [--force] [--verbose]
+
+reference: ``scripts/build_kernels.sh:55-118`` builds one ``libcuda_<stem>.so`` per ``.cu`` with
+``-arch=sm_100``; ``build.zig:42-69`` links them. Here there is one library and one arch.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+OUT_DIR = PKG / "_native"
+OBJ_DIR = OUT_DIR / "obj"
+LIB = OUT_DIR / "libelfa_b200.so"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+]
+
+
+def find_nvcc() -> str:
+    cand = shutil.which("nvcc") or os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
+    if not os.path.exists(cand):
+        raise RuntimeError("nvcc not found (set CUDA_HOME)")
+    return cand
+
+
+def _newest_header_mtime() -> float:
+    return max((p.stat().st_mtime for p in CSRC.glob("*.h*")), default=0.0)
+
+
+def _compile(nvcc: str, src: Path, obj: Path, verbose: bool) -> str:
+    cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    if verbose:
+        cmd.insert(1, "-Xptxas")
+        cmd.insert(2, "-v")
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stdout}\n{r.stderr}")
+    return r.stderr
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    nvcc = find_nvcc()
+    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    sources = sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cpp"))
+    if not sources:
+        raise RuntimeError("no native sources found")
+    hdr_m = _newest_header_mtime()
+    jobs = []
+    for src in sources:
+        obj = OBJ_DIR / (src.stem + ".o")
+        stale = force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_m)
+        if stale:
+            jobs.append((src, obj))
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            for log in ex.map(lambda j: _compile(nvcc, j[0], j[1], verbose), jobs):
+                if verbose and log:
+                    print(log, file=sys.stderr)
+    objs = [OBJ_DIR / (s.stem + ".o") for s in sources]
+    if jobs or not LIB.exists():
+        cmd = [nvcc, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart", "-Xcompiler", "-fPIC"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    return LIB
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--force", action="store_true")
+    ap.add_argument("--verbose", action="store_true")
+    a = ap.parse_args(argv)
+    print(build(force=a.force, verbose=a.verbose))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,72 @@
+// C ABI of the elfa_b200 native library (libelfa_b200.so). Every function returns an ELFA_* code
+// (0 = ok); elfa_last_error() gives the message of the last failure on the calling thread.
+// All device pointers are raw CUDA pointers; `stream` is a cudaStream_t passed as void*.
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// GEMM epilogue flags (bitmask).
+#define ELFA_EPI_BIAS 1u          // + bias[N] (bf16)
+#define ELFA_EPI_GELU 2u          // tanh-GELU after bias
+#define ELFA_EPI_DGELU_AUX 4u     // multiply by GELU'(aux[M,N])
+#define ELFA_EPI_ADD_AUX 8u       // + aux[M,N] (residual)
+#define ELFA_EPI_ACCUM 16u        // C += result
+#define ELFA_EPI_OUT_F32 32u      // C is fp32 (default bf16)
+#define ELFA_EPI_STORE_PREACT 64u // also store the value before GELU to `preact`
+
+const char* elfa_last_error(void);
+int elfa_version(void);
+int elfa_status(unsigned int* out);
+int elfa_device_info(int device, long long* out6);
+int elfa_is_blackwell(int device);
+int elfa_enable_peer_access(int* n_enabled);
+int elfa_pinned_alloc(void** out, size_t bytes);
+int elfa_pinned_free(void* p);
+
+// C[M,N] = epilogue(alpha * op(A) * op(B)); see gemm_bf16.cu for operand conventions.
+int elfa_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                   long long ldc, int a_mn_major, int b_mn_major, const void* bias, const void* aux, long long ldaux,
+                   void* preact, long long ldpre, float alpha, unsigned flags, int force_bn, int max_ctas, void* stream);
+
+// ---- norm.cu -----------------------------------------------------------------------------------
+int elfa_norm_fwd(const void* x, const void* res, const void* w, const void* b, void* y, void* sum_out, float* mean_out,
+                  float* rstd_out, int rows, int D, float eps, int kind, void* stream);
+int elfa_norm_bwd_partials(int rows, int D);
+int elfa_norm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, const void* dres, void* dx,
+                  void* dw, void* db, float* scratch, int rows, int D, int kind, int grads_f32, int accumulate, void* stream);
+
+// ---- elementwise.cu ----------------------------------------------------------------------------
+int elfa_elementwise(int op, const void* a, const void* b, void* out, long long n, float alpha, void* stream);
+int elfa_embedding_fwd(const long long* ids, const void* tok, const void* pos, void* out, int tokens, int D, int seq, int pos0,
+                       int vocab_lo, int vocab_hi, void* stream);
+int elfa_embedding_bwd(const long long* ids, const void* dy, void* dtok, void* dpos, int tokens, int D, int seq, int pos0,
+                       int vocab_lo, int vocab_hi, int grads_f32, void* stream);
+int elfa_cast(const void* src, int src_type, void* dst, int dst_type, long long n, float scale, void* stream);
+
+// ---- xent.cu -----------------------------------------------------------------------------------
+int elfa_xent_stats(const void* logits, long long ld, const long long* targets, float* stats, int rows, int V, int vocab_lo,
+                    int vocab_total, void* stream);
+int elfa_xent_grad(void* logits, long long ld, void* dlogits, long long ldd, const long long* targets, const float* stats,
+                   int nslices, float* loss_out, int rows, int V, int vocab_lo, int vocab_total, float smoothing,
+                   const float* grad_scale_ptr, float grad_scale, void* stream);
+
+// ---- optim.cu ----------------------------------------------------------------------------------
+int elfa_sumsq(const void* grad, int grad_type, long long n, float* part, void* scalars, int accumulate, void* stream);
+int elfa_clip_coef(void* scalars, float max_norm, float inv_loss_scale, void* stream);
+int elfa_adamw(void* param, int param_type, float* master, float* m, float* v, const void* grad, int grad_type, long long n,
+               float lr, float beta1, float beta2, float eps, float wd, int step, const void* scalars, void* stream);
+int elfa_lion(void* param, int param_type, float* master, float* m, const void* grad, int grad_type, long long n, float lr,
+              float beta1, float beta2, float wd, const void* scalars, void* stream);
+int elfa_muon_momentum(float* m, const void* grad, int grad_type, void* y, long long n, float beta, const void* scalars,
+                       float* part, float* norm_out, void* stream);
+int elfa_three_i_minus(void* g, int d, void* stream);
+int elfa_muon_apply(void* param, int param_type, float* master, const void* y, long long n, float lr, const void* scalars,
+                    void* stream);
+
+#ifdef __cplusplus
+}
+#endif

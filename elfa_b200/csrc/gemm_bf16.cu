@@ -1,0 +1,432 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a: TMA -> shared memory ring -> tcgen05.mma with
+// fp32 accumulators in tensor memory (double buffered) -> tcgen05.ld epilogue with fused
+// bias / GELU / dGELU / residual / accumulate.
+//
+// Replaces the reference's cuBLAS wrapper and its one-thread-per-output "sm100" GEMM
+// (reference: kernels/cuda/gemm.cu:212-232,315-327,412-423 forward/backward through cublasGemmEx;
+// kernels/cuda/gemm_sm100.cu:46-72 naive bf16 kernel, :142-171 static tile table;
+// kernels/cuda/gemm.cu:50-72 bias add and column sum).
+//
+// C[M,N] = epilogue(alpha * A * B) where each operand is given either
+//   K-major  : A as [M,K] row-major / B as [N,K] row-major  (contraction index contiguous), or
+//   MN-major : A as [K,M] row-major / B as [K,N] row-major  (output index contiguous).
+// This covers forward (x[M,K] * W[K,N]), input gradient (dy[M,N] * W[K,N]^T) and weight gradient
+// (x[M,K]^T * dy[M,N]) of a Linear layer without materialising any transpose.
+//
+// Roles per CTA (192 threads, one CTA per SM, grid = min(tiles, SMs)):
+//   warp 0   : TMA producer (one lane) - fills a STAGES-deep ring of {A 128x64, B BNx64} bf16 tiles
+//   warp 1   : allocates tensor memory; one lane issues tcgen05.mma (128 x BN x 16 per instruction)
+//   warps 2-5: epilogue - each owns one 32-lane quarter of the accumulator
+// Every wait is bounded; on a timeout the CTA sets the device status word, stops and tears down.
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "elfa_native.h"
+
+namespace elfa {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+
+struct GemmParams {
+  int M, N, K;
+  void* C;
+  long long ldc;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* aux;
+  long long ldaux;
+  __nv_bfloat16* preact;
+  long long ldpre;
+  float alpha;
+  unsigned flags;
+  unsigned int* status;
+  int tiles_m, tiles_n, group_m;
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int BAR_OFF = STAGES * (A_BYTES + B_BYTES);
+  static constexpr int NUM_BARS = 2 * STAGES + 4;
+  static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16;
+  static constexpr int DYN = TOTAL + 1024;  // slack for manual 1024-byte alignment
+};
+
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& mb, int& nb) {
+  int per_group = p.group_m * p.tiles_n;
+  int g = tile / per_group;
+  int first_m = g * p.group_m;
+  int gsz = min(p.group_m, p.tiles_m - first_m);
+  int r = tile - g * per_group;
+  mb = first_m + r % gsz;
+  nb = r / gsz;
+}
+
+template <int BN, bool A_MN, bool B_MN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  using L = SmemLayout<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * L::A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + L::NUM_BARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = 2 * BN;  // 128 / 256 / 512: a power of two >= 32
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int mb, nb;
+        tile_coords(p, tile, mb, nb);
+        const int m0 = mb * BM, n0 = nb * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status)) { ok = false; break; }
+          mbar_expect_tx(full_bar(s), L::A_BYTES + L::B_BYTES);
+          const uint32_t a_dst = smem_u32(sA + s * L::A_BYTES);
+          const uint32_t b_dst = smem_u32(sB + s * L::B_BYTES);
+          if (!A_MN) {
+            tma_load_2d(a_dst, &tmA, kb * BK, m0, full_bar(s));
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tmA, m0 + j * 64, kb * BK, full_bar(s));
+          }
+          if (!B_MN) {
+            tma_load_2d(b_dst, &tmB, kb * BK, n0, full_bar(s));
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, n0 + j * 64, kb * BK, full_bar(s));
+          }
+        }
+      }
+      if (!ok) {
+        // give the copies already issued a bounded chance to land before the CTA exits
+        for (uint32_t j = it > (uint32_t)STAGES ? it - STAGES : 0; j < it; ++j) {
+          const long long t0 = clock64();
+          while (!mbar_try(full_bar(j % STAGES), (j / STAGES) & 1) && clock64() - t0 < 4000000) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      uint32_t it = 0, tile_iter = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
+        const uint32_t buf = tile_iter & 1, bph = (tile_iter >> 1) & 1;
+        if (!mbar_wait(tempty_bar(buf), bph ^ 1, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(full_bar(s), ph, abort_flag, p.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(sA + s * L::A_BYTES);
+          const uint32_t b_base = smem_u32(sB + s * L::B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // K-major: 16 elements = 32 bytes along the swizzled 128-byte row.
+            // MN-major: 16 K-rows of 128 bytes = two 1024-byte swizzle atoms.
+            const uint64_t da = A_MN ? make_smem_desc(a_base + k * 2048, 8192, 1024, 2)
+                                     : make_smem_desc(a_base + k * 32, 16, 1024, 2);
+            const uint64_t db = B_MN ? make_smem_desc(b_base + k * 2048, 8192, 1024, 2)
+                                     : make_smem_desc(b_base + k * 32, 16, 1024, 2);
+            tc_mma_f16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(empty_bar(s));  // frees the smem slot once these MMAs have read it
+        }
+        if (ok) tc_commit(tfull_bar(buf));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+    uint32_t tile_iter = 0;
+    const unsigned fl = p.flags;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_iter) {
+      int mb, nb;
+      tile_coords(p, tile, mb, nb);
+      const int m0 = mb * BM, n0 = nb * BN;
+      const uint32_t buf = tile_iter & 1, bph = (tile_iter >> 1) & 1;
+      bool ok = mbar_wait(tfull_bar(buf), bph, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) continue;  // uniform across the warp
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        if (fl & ELFA_EPI_BIAS) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = col0 + g * 8;
+            if (col + 8 > p.N) continue;
+            float* w = v + g * 8;
+            if (fl & ELFA_EPI_STORE_PREACT) {
+              uint4 o = make_uint4(pack_bf16(w[0], w[1]), pack_bf16(w[2], w[3]), pack_bf16(w[4], w[5]), pack_bf16(w[6], w[7]));
+              *reinterpret_cast<uint4*>(p.preact + (long long)row * p.ldpre + col) = o;
+            }
+            if (fl & ELFA_EPI_GELU) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) w[j] = gelu_tanh(w[j]);
+            }
+            if (fl & (ELFA_EPI_DGELU_AUX | ELFA_EPI_ADD_AUX)) {
+              const uint4 a = *reinterpret_cast<const uint4*>(p.aux + (long long)row * p.ldaux + col);
+              const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float lo = bf16_lo(aw[j]), hi = bf16_hi(aw[j]);
+                if (fl & ELFA_EPI_DGELU_AUX) {
+                  w[2 * j] *= dgelu_tanh(lo);
+                  w[2 * j + 1] *= dgelu_tanh(hi);
+                } else {
+                  w[2 * j] += lo;
+                  w[2 * j + 1] += hi;
+                }
+              }
+            }
+            if (fl & ELFA_EPI_OUT_F32) {
+              float* cp = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col;
+              float4 o0 = make_float4(w[0], w[1], w[2], w[3]), o1 = make_float4(w[4], w[5], w[6], w[7]);
+              if (fl & ELFA_EPI_ACCUM) {
+                const float4 c0 = *reinterpret_cast<const float4*>(cp), c1 = *reinterpret_cast<const float4*>(cp + 4);
+                o0.x += c0.x; o0.y += c0.y; o0.z += c0.z; o0.w += c0.w;
+                o1.x += c1.x; o1.y += c1.y; o1.z += c1.z; o1.w += c1.w;
+              }
+              *reinterpret_cast<float4*>(cp) = o0;
+              *reinterpret_cast<float4*>(cp + 4) = o1;
+            } else {
+              __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col;
+              if (fl & ELFA_EPI_ACCUM) {
+                const uint4 c = *reinterpret_cast<const uint4*>(cp);
+                const uint32_t cw[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  w[2 * j] += bf16_lo(cw[j]);
+                  w[2 * j + 1] += bf16_hi(cw[j]);
+                }
+              }
+              uint4 o = make_uint4(pack_bf16(w[0], w[1]), pack_bf16(w[2], w[3]), pack_bf16(w[4], w[5]), pack_bf16(w[6], w[7]));
+              *reinterpret_cast<uint4*>(cp) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(buf));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+struct TmapKey {
+  const void* base;
+  uint64_t rows, cols, ld;
+  uint32_t br, bc;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && br == o.br && bc == o.bc;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.base);
+    h = h * 1000003u ^ k.rows;
+    h = h * 1000003u ^ k.cols;
+    h = h * 1000003u ^ k.ld;
+    h = h * 1000003u ^ (((uint64_t)k.br << 32) | k.bc);
+    return h;
+  }
+};
+static std::mutex g_tm_mu;
+static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tm_cache;
+
+int cached_tmap_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems, uint32_t box_rows,
+                     uint32_t box_cols) {
+  TmapKey key{base, rows, cols, ld_elems, box_rows, box_cols};
+  {
+    std::lock_guard<std::mutex> lk(g_tm_mu);
+    auto it = g_tm_cache.find(key);
+    if (it != g_tm_cache.end()) {
+      *out = it->second;
+      return ELFA_OK;
+    }
+  }
+  int rc = make_tmap_2d(out, base, 2, rows, cols, ld_elems * 2, box_rows, box_cols, true);
+  if (rc != ELFA_OK) return rc;
+  std::lock_guard<std::mutex> lk(g_tm_mu);
+  if (g_tm_cache.size() > 8192) g_tm_cache.clear();
+  g_tm_cache.emplace(key, *out);
+  return ELFA_OK;
+}
+
+static int g_sm_count = 0;
+int sm_count() {
+  if (!g_sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (g_sm_count <= 0) g_sm_count = 148;
+  }
+  return g_sm_count;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int max_ctas, cudaStream_t stream) {
+  constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  using L = SmemLayout<BN, STAGES>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, STAGES>;
+  static bool configured = false;
+  if (!configured) {
+    ELFA_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
+    configured = true;
+  }
+  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  p.group_m = 8;
+  int tiles = p.tiles_m * p.tiles_n;
+  int grid = tiles < max_ctas ? tiles : max_ctas;
+  kern<<<grid, GEMM_THREADS, L::DYN, stream>>>(tmA, tmB, p);
+  ELFA_CUDA(cudaGetLastError());
+  return ELFA_OK;
+}
+
+template <int BN>
+int dispatch_layout(int a_mn, int b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int max_ctas,
+                    cudaStream_t stream) {
+  if (!a_mn && !b_mn) return launch_gemm<BN, false, false>(tmA, tmB, p, max_ctas, stream);
+  if (!a_mn && b_mn) return launch_gemm<BN, false, true>(tmA, tmB, p, max_ctas, stream);
+  if (a_mn && !b_mn) return launch_gemm<BN, true, false>(tmA, tmB, p, max_ctas, stream);
+  return launch_gemm<BN, true, true>(tmA, tmB, p, max_ctas, stream);
+}
+
+}  // namespace
+
+int pick_bn(int M, int N, int forced) {
+  if (forced == 64 || forced == 128 || forced == 256) return forced;
+  const int sms = sm_count();
+  const long long tm = (M + BM - 1) / BM;
+  if (N >= 256 && tm * ((N + 255) / 256) >= sms) return 256;
+  if (N >= 128 && tm * ((N + 127) / 128) >= sms / 2) return 128;
+  if (N > 64 && tm * ((N + 127) / 128) >= sms / 4) return 128;
+  return N > 128 ? 128 : 64;
+}
+
+}  // namespace elfa
+
+using namespace elfa;
+
+ELFA_API int elfa_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                            long long ldc, int a_mn_major, int b_mn_major, const void* bias, const void* aux,
+                            long long ldaux, void* preact, long long ldpre, float alpha, unsigned flags, int force_bn,
+                            int max_ctas, void* stream) {
+  ELFA_REQUIRE(A && B && C, "gemm: null operand");
+  ELFA_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: empty problem");
+  ELFA_REQUIRE(N % 8 == 0, "gemm: N must be a multiple of 8");
+  ELFA_REQUIRE(lda % 8 == 0 && ldb % 8 == 0, "gemm: operand row pitch must be a multiple of 8 elements");
+  ELFA_REQUIRE(ldc % ((flags & ELFA_EPI_OUT_F32) ? 4 : 8) == 0, "gemm: ldc alignment");
+  ELFA_REQUIRE(!(flags & ELFA_EPI_BIAS) || bias, "gemm: bias flag without pointer");
+  ELFA_REQUIRE(!(flags & (ELFA_EPI_DGELU_AUX | ELFA_EPI_ADD_AUX)) || (aux && ldaux % 8 == 0), "gemm: aux flag without pointer");
+  ELFA_REQUIRE(!(flags & ELFA_EPI_STORE_PREACT) || (preact && ldpre % 8 == 0), "gemm: preact flag without pointer");
+  unsigned int* st = status_word();
+  ELFA_REQUIRE(st != nullptr, "gemm: no status word");
+
+  const int BN = pick_bn(M, N, force_bn);
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a_mn_major) rc = cached_tmap_bf16(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, BK);
+  else rc = cached_tmap_bf16(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, 64);
+  if (rc != ELFA_OK) return rc;
+  if (!b_mn_major) rc = cached_tmap_bf16(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN, BK);
+  else rc = cached_tmap_bf16(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, 64);
+  if (rc != ELFA_OK) return rc;
+
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.aux = static_cast<const __nv_bfloat16*>(aux);
+  p.ldaux = ldaux;
+  p.preact = static_cast<__nv_bfloat16*>(preact);
+  p.ldpre = ldpre;
+  p.alpha = alpha;
+  p.flags = flags;
+  p.status = st;
+  const int ctas = (max_ctas > 0 && max_ctas < sm_count()) ? max_ctas : sm_count();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (BN) {
+    case 256: return dispatch_layout<256>(a_mn_major, b_mn_major, tmA, tmB, p, ctas, s);
+    case 128: return dispatch_layout<128>(a_mn_major, b_mn_major, tmA, tmB, p, ctas, s);
+    default: return dispatch_layout<64>(a_mn_major, b_mn_major, tmA, tmB, p, ctas, s);
+  }
+}

@@ -1,0 +1,146 @@
+// Host runtime of the native library: error reporting, the per-device status word, device
+// queries, TMA tensor-map creation, peer access, pinned host memory.
+// Native counterpart of the reference's CUDA runtime shim (reference: src/runtime/cuda.zig:283-507,
+// src/cuda_bindings.zig:14-135): PyTorch owns contexts and streams, this file adds what the
+// kernels need beyond that.
+#include <mutex>
+#include <string>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace elfa {
+
+static thread_local std::string g_last_error;
+void set_last_error(const char* msg) { g_last_error = msg ? msg : ""; }
+int cuda_fail(cudaError_t e, const char* what) {
+  g_last_error = std::string(what) + ": " + cudaGetErrorString(e);
+  return ELFA_ERR_CUDA;
+}
+
+static std::mutex g_mu;
+static unsigned int* g_status[64] = {nullptr};
+
+unsigned int* status_word() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_status[dev]) {
+    unsigned int* p = nullptr;
+    if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, 256);
+    g_status[dev] = p;
+  }
+  return g_status[dev];
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+static EncodeTiledFn get_encode() {
+  if (g_encode) return g_encode;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return nullptr;
+  g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  return g_encode;
+}
+
+int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld_bytes,
+                 uint32_t box_rows, uint32_t box_cols, bool swizzle128) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) {
+    set_last_error("cuTensorMapEncodeTiled is not available (no driver?)");
+    return ELFA_ERR_CUDA;
+  }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld_bytes & 15)) {
+    set_last_error("tensor map: base address and row pitch must be multiples of 16 bytes");
+    return ELFA_ERR_ARG;
+  }
+  CUtensorMapDataType dt = elem_bytes == 1   ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                           : elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                             : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_error = "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r);
+    return ELFA_ERR_CUDA;
+  }
+  return ELFA_OK;
+}
+
+}  // namespace elfa
+
+using namespace elfa;
+
+ELFA_API const char* elfa_last_error() { return g_last_error.c_str(); }
+
+ELFA_API int elfa_version() { return 100; }
+
+// Reads and clears the status word of the current device (synchronises the device).
+ELFA_API int elfa_status(unsigned int* out) {
+  unsigned int* p = status_word();
+  ELFA_REQUIRE(p != nullptr, "no status word (no device?)");
+  ELFA_CUDA(cudaDeviceSynchronize());
+  ELFA_CUDA(cudaMemcpy(out, p, sizeof(unsigned int), cudaMemcpyDeviceToHost));
+  ELFA_CUDA(cudaMemset(p, 0, sizeof(unsigned int)));
+  return ELFA_OK;
+}
+
+// out[0]=major out[1]=minor out[2]=SM count out[3]=max opt-in shared memory per block out[4]=L2 bytes
+ELFA_API int elfa_device_info(int device, long long* out) {
+  cudaDeviceProp p;
+  ELFA_CUDA(cudaGetDeviceProperties(&p, device));
+  out[0] = p.major;
+  out[1] = p.minor;
+  out[2] = p.multiProcessorCount;
+  out[3] = (long long)p.sharedMemPerBlockOptin;
+  out[4] = p.l2CacheSize;
+  out[5] = (long long)p.totalGlobalMem;
+  return ELFA_OK;
+}
+
+ELFA_API int elfa_is_blackwell(int device) {
+  cudaDeviceProp p;
+  if (cudaGetDeviceProperties(&p, device) != cudaSuccess) return 0;
+  return p.major >= 10 ? 1 : 0;
+}
+
+// Enables peer access from the current device to every other visible device that supports it.
+// Returns the number of peers enabled in *n_enabled.
+ELFA_API int elfa_enable_peer_access(int* n_enabled) {
+  int cur = 0, n = 0, cnt = 0;
+  ELFA_CUDA(cudaGetDevice(&cur));
+  ELFA_CUDA(cudaGetDeviceCount(&n));
+  for (int d = 0; d < n; ++d) {
+    if (d == cur) continue;
+    int can = 0;
+    ELFA_CUDA(cudaDeviceCanAccessPeer(&can, cur, d));
+    if (!can) continue;
+    cudaError_t e = cudaDeviceEnablePeerAccess(d, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+      cudaGetLastError();
+      e = cudaSuccess;
+    }
+    ELFA_CUDA(e);
+    ++cnt;
+  }
+  if (n_enabled) *n_enabled = cnt;
+  return ELFA_OK;
+}
+
+ELFA_API int elfa_pinned_alloc(void** out, size_t bytes) {
+  ELFA_CUDA(cudaHostAlloc(out, bytes, cudaHostAllocPortable));
+  return ELFA_OK;
+}
+ELFA_API int elfa_pinned_free(void* p) {
+  ELFA_CUDA(cudaFreeHost(p));
+  return ELFA_OK;
+}

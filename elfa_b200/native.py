@@ -1,0 +1,137 @@
+"""ctypes binding of the native library.
+
+The C prototypes are read from ``csrc/elfa_native.h`` so that the Python signatures can never
+drift from the header. Pointer arguments accept ``torch.Tensor`` (its ``data_ptr()``), ``int`` or
+``None``. Every call checks the return code and raises :class:`NativeError` with the library's
+message; on a CUDA machine a missing library is an error, never a silent fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import re
+from pathlib import Path
+from typing import Any, Dict, Optional
+
+import torch
+
+_PKG = Path(__file__).resolve().parent
+_LIB_PATH = _PKG / "_native" / "libelfa_b200.so"
+_HEADER = _PKG / "csrc" / "elfa_native.h"
+
+ST_MBAR_TIMEOUT = 1
+ST_FLAG_TIMEOUT = 2
+ST_BAD_TARGET = 4
+ST_NONFINITE = 8
+
+EPI_BIAS, EPI_GELU, EPI_DGELU_AUX, EPI_ADD_AUX, EPI_ACCUM, EPI_OUT_F32, EPI_STORE_PREACT = 1, 2, 4, 8, 16, 32, 64
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+class CommTimeout(NativeError):
+    """A bounded device-side wait ran out (peer flag or pipeline barrier)."""
+
+
+def _ctype(decl: str):
+    d = decl.strip()
+    if "*" in d:
+        return ctypes.c_void_p
+    d = re.sub(r"\bconst\b", "", d).strip()
+    base = " ".join(d.split()[:-1]) if len(d.split()) > 1 else d
+    return {
+        "int": ctypes.c_int, "unsigned": ctypes.c_uint, "unsigned int": ctypes.c_uint, "long long": ctypes.c_longlong,
+        "float": ctypes.c_float, "double": ctypes.c_double, "size_t": ctypes.c_size_t, "uint64_t": ctypes.c_uint64,
+        "uint32_t": ctypes.c_uint32,
+    }[base]
+
+
+def _parse_header(text: str) -> Dict[str, list]:
+    text = re.sub(r"//[^\n]*", "", text)
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    protos = {}
+    for m in re.finditer(r"\b(int|const char\*)\s+(elfa_\w+)\s*\(([^)]*)\)\s*;", text):
+        ret, name, args = m.group(1), m.group(2), m.group(3).strip()
+        argt = [] if args in ("", "void") else [_ctype(a) for a in args.split(",")]
+        protos[name] = (ret, argt)
+    return protos
+
+
+class _Lib:
+    def __init__(self) -> None:
+        self._dll: Optional[ctypes.CDLL] = None
+        self._protos: Dict[str, Any] = {}
+
+    def available(self) -> bool:
+        return _LIB_PATH.exists()
+
+    def load(self) -> ctypes.CDLL:
+        if self._dll is not None:
+            return self._dll
+        if not _LIB_PATH.exists():
+            raise NativeError(f"native library {_LIB_PATH} is missing: run `python -m elfa_b200.build`")
+        dll = ctypes.CDLL(str(_LIB_PATH), mode=os.RTLD_GLOBAL if hasattr(os, "RTLD_GLOBAL") else ctypes.DEFAULT_MODE)
+        self._protos = _parse_header(_HEADER.read_text())
+        for name, (ret, argt) in self._protos.items():
+            fn = getattr(dll, name, None)
+            if fn is None:
+                raise NativeError(f"symbol {name} declared in elfa_native.h is missing from the library")
+            fn.argtypes = argt
+            fn.restype = ctypes.c_char_p if ret != "int" else ctypes.c_int
+        self._dll = dll
+        return dll
+
+    def last_error(self) -> str:
+        return (self.load().elfa_last_error() or b"").decode()
+
+    def call(self, name: str, *args) -> None:
+        dll = self.load()
+        conv = []
+        for a in args:
+            if isinstance(a, torch.Tensor):
+                conv.append(a.data_ptr())
+            elif a is None:
+                conv.append(None)
+            else:
+                conv.append(a)
+        rc = getattr(dll, name)(*conv)
+        if rc != 0:
+            raise NativeError(f"{name} failed (code {rc}): {self.last_error()}")
+
+    def raw(self, name: str):
+        return getattr(self.load(), name)
+
+
+lib = _Lib()
+
+
+def stream_ptr(t: Optional[torch.Tensor] = None) -> int:
+    return torch.cuda.current_stream(t.device if t is not None else None).cuda_stream
+
+
+def status() -> int:
+    """Reads and clears the device status word (synchronises the device)."""
+    out = ctypes.c_uint(0)
+    rc = lib.load().elfa_status(ctypes.addressof(out))
+    if rc != 0:
+        raise NativeError(f"elfa_status failed: {lib.last_error()}")
+    return int(out.value)
+
+
+def check_status() -> None:
+    st = status()
+    if st & (ST_MBAR_TIMEOUT | ST_FLAG_TIMEOUT):
+        raise CommTimeout(f"a device-side wait timed out (status 0x{st:x})")
+    if st & ST_BAD_TARGET:
+        raise NativeError("token or target id outside the vocabulary")
+
+
+def require_native(t: torch.Tensor) -> bool:
+    """True when ``t`` must be handled by the native kernels (CUDA tensor). Raises if they are
+    not built: a GPU run never falls back to eager PyTorch silently."""
+    if not t.is_cuda:
+        return False
+    lib.load()
+    return True

@@ -1,0 +1,96 @@
+"""tcgen05 GEMM against an fp32 PyTorch reference: layouts, tails, epilogues."""
+import pytest
+import torch
+
+from elfa_b200 import native, ops
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, a_mn, b_mn):
+    af = (a.t() if a_mn else a).float()
+    bf = (b if b_mn else b.t()).float()
+    return af @ bf
+
+
+def _mk(M, N, K, a_mn, b_mn, dev, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    a = torch.randn((K, M) if a_mn else (M, K), generator=g).to(torch.bfloat16).to(dev)
+    b = torch.randn((K, N) if b_mn else (N, K), generator=g).to(torch.bfloat16).to(dev)
+    return a, b
+
+
+def _close(out, ref, K):
+    err = (out.float() - ref).abs().max().item()
+    tol = 0.02 * (K ** 0.5) + 0.05
+    assert err < tol, f"max err {err} > {tol}"
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 1376, 512), (200, 96, 136), (4096, 4096, 1024)])
+def test_gemm_layouts(cuda_device, M, N, K, a_mn, b_mn):
+    if a_mn and M % 8:
+        pytest.skip("MN-major A needs M % 8 == 0")
+    a, b = _mk(M, N, K, a_mn, b_mn, cuda_device)
+    out = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    torch.cuda.synchronize()
+    assert native.status() == 0
+    _close(out, _ref(a, b, a_mn, b_mn), K)
+
+
+@pytest.mark.parametrize("bn", [64, 128, 256])
+def test_gemm_tile_widths(cuda_device, bn):
+    a, b = _mk(512, 768, 320, False, True, cuda_device, seed=1)
+    out = ops.gemm(a, b, b_mn=True, force_bn=bn)
+    _close(out, _ref(a, b, False, True), 320)
+    assert native.status() == 0
+
+
+def test_gemm_epilogues(cuda_device):
+    M, N, K = 512, 1024, 256
+    a, b = _mk(M, N, K, False, True, cuda_device, seed=2)
+    bias = torch.randn(N, device=cuda_device).to(torch.bfloat16)
+    aux = torch.randn(M, N, device=cuda_device).to(torch.bfloat16)
+    base = _ref(a, b, False, True) + bias.float()
+    pre = torch.empty(M, N, dtype=torch.bfloat16, device=cuda_device)
+    out = ops.gemm(a, b, b_mn=True, bias=bias, gelu=True, preact=pre)
+    _close(pre, base, K)
+    _close(out, ops.gelu_tanh_ref(base), K)
+    out = ops.gemm(a, b, b_mn=True, aux=aux, dgelu_aux=True)
+    _close(out, _ref(a, b, False, True) * ops.dgelu_tanh_ref(aux.float()), K)
+    out = ops.gemm(a, b, b_mn=True, aux=aux, add_aux=True)
+    _close(out, _ref(a, b, False, True) + aux.float(), K)
+    acc = torch.randn(M, N, device=cuda_device)
+    acc0 = acc.clone()
+    ops.gemm(a, b, b_mn=True, out=acc, accumulate=True)
+    _close(acc, _ref(a, b, False, True) + acc0, K)
+    o32 = ops.gemm(a, b, b_mn=True, out_dtype=torch.float32, alpha=0.5)
+    assert o32.dtype == torch.float32
+    _close(o32, 0.5 * _ref(a, b, False, True), K)
+    assert native.status() == 0
+
+
+def test_gemm_many_tiles_persistent(cuda_device):
+    # more tiles than SMs and a CTA cap: every CTA loops over several tiles and both accumulator buffers
+    a, b = _mk(2048, 2048, 512, False, False, cuda_device, seed=3)
+    out = ops.gemm(a, b, max_ctas=7)
+    _close(out, _ref(a, b, False, False), 512)
+    out2 = ops.gemm(a, b)
+    assert torch.equal(out, out2), "result must not depend on the tile-to-CTA assignment"
+    assert native.status() == 0
+
+
+def test_linear_autograd(cuda_device):
+    torch.manual_seed(0)
+    x = torch.randn(4, 64, 256, device=cuda_device).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(256, 512, device=cuda_device) * 0.05).to(torch.bfloat16).requires_grad_(True)
+    y = ops.linear(x, w, None, "gelu")
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    yr = torch.nn.functional.gelu(xr @ wr, approximate="tanh")
+    yr.backward(g.float())
+    assert (y.float() - yr).abs().max() < 0.05
+    assert (x.grad.float() - xr.grad).abs().max() < 0.1
+    assert (w.grad.float() - wr.grad).abs().max() < 0.02 * (256 ** 0.5) + 0.3
