@@ -1,0 +1,331 @@
+// Causal (or full) softmax attention forward on tcgen05: S = Q K^T and O_j = P V are tensor-memory
+// MMAs, the online softmax runs in registers between them, K/V tiles arrive by TMA.
+//
+// The reference has no CUDA attention; its definition of the op is the Futhark sketch
+// (reference: src/futhark/attention.fut:28-51 causal SDPA, :94-165 blocked attention with
+// log-sum-exp). This kernel is the Blackwell realisation used by the GPT model family.
+//
+// One CTA handles a PAIR of 128-row query tiles (A = tile 2p, B = tile 2p+1) of one (batch, head):
+//   warp 0      : TMA producer (Q tiles once, then K_j / V_j per 128-key block)
+//   warp 1      : issues every tcgen05.mma
+//   warps 2-5   : softmax + output accumulation of tile A (one thread per query row)
+//   warps 6-9   : the same for tile B
+// While one warp group runs exp() on its S tile, the tensor core works on the other tile, so the
+// two pipelines hide each other. K_j and V_j are loaded once for both tiles.
+// Tensor memory: S_A | S_B | O_A | O_B (4 x 128 fp32 columns). P (bf16) goes through shared
+// memory in the 128-byte-swizzled K-major layout the MMA expects. O_j is read back per block and
+// accumulated in registers with the usual rescaling, so tensor memory never needs a rescale.
+// Every wait is bounded (status word + abort flag), as in the GEMM.
+#include "common.cuh"
+#include "elfa_native.h"
+
+namespace elfa {
+namespace {
+
+constexpr int ATT_THREADS = 320;
+constexpr int SUB_BYTES = 128 * 128;  // one [128 rows x 64 bf16] swizzled sub-tile
+
+struct AttnFwdParams {
+  int S, B, H, hd;
+  __nv_bfloat16* O;
+  long long o_stride_s, o_stride_b;  // elements; head stride = hd
+  float* lse;                        // [B, H, S]
+  float scale_log2;
+  int causal;
+  int n_qtiles;
+  unsigned int* status;
+};
+
+enum { BAR_Q = 0, BAR_KFULL, BAR_VFULL, BAR_KFREE, BAR_VFREE, BAR_SFULL0, BAR_SFULL1, BAR_PREADY0, BAR_PREADY1, BAR_OFULL0, BAR_OFULL1, BAR_COUNT };
+
+template <int HDP>
+struct AttnSmem {
+  static constexpr int NSUB = HDP / 64;
+  static constexpr int Q_OFF = 0;                              // [2 tiles][NSUB]
+  static constexpr int K_OFF = Q_OFF + 2 * NSUB * SUB_BYTES;   // [NSUB]
+  static constexpr int V_OFF = K_OFF + NSUB * SUB_BYTES;       // [NSUB]
+  static constexpr int P_OFF = V_OFF + NSUB * SUB_BYTES;       // [2 tiles][2]
+  static constexpr int BAR_OFF = P_OFF + 4 * SUB_BYTES;
+  static constexpr int TOTAL = BAR_OFF + BAR_COUNT * 8 + 16;
+  static constexpr int DYN = TOTAL + 1024;
+};
+
+template <int HDP>
+__global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnFwdParams p) {
+  using L = AttnSmem<HDP>;
+  constexpr int NSUB = L::NSUB;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int npairs = (p.n_qtiles + 1) / 2;
+  const int pair = npairs - 1 - (int)blockIdx.x;  // longest rows first
+  // tile B always exists; tile A is absent when the pair is a lone last tile
+  const bool has_a = 2 * pair + 1 < p.n_qtiles;
+  const int tile_a = 2 * pair, tile_b = has_a ? 2 * pair + 1 : 2 * pair;
+  const int n_kv = (p.S + 127) / 128;
+  const int n_a = has_a ? (p.causal ? tile_a + 1 : n_kv) : 0;
+  const int n_b = p.causal ? tile_b + 1 : n_kv;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmQKV);
+    for (int i = 0; i < BAR_COUNT; ++i) mbar_init(bar(i), (i == BAR_PREADY0 || i == BAR_PREADY1) ? 128 : 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t TM_S[2] = {tmem_base + 0, tmem_base + 128};
+  const uint32_t TM_O[2] = {tmem_base + 256, tmem_base + 256 + HDP};
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      const int ntile = has_a ? 2 : 1;
+      mbar_expect_tx(bar(BAR_Q), ntile * NSUB * SUB_BYTES);
+      for (int t = has_a ? 0 : 1; t < 2; ++t) {
+        const int q0 = (t == 0 ? tile_a : tile_b) * 128;
+        for (int s = 0; s < NSUB; ++s)
+          tma_load_4d(sbase + L::Q_OFF + (t * NSUB + s) * SUB_BYTES, &tmQKV, s * 64, 0 * p.H + h, b, q0, bar(BAR_Q));
+      }
+      for (int j = 0; j < n_b; ++j) {
+        if (j > 0 && !mbar_wait(bar(BAR_KFREE), (j - 1) & 1, abort_flag, p.status)) break;
+        mbar_expect_tx(bar(BAR_KFULL), NSUB * SUB_BYTES);
+        for (int s = 0; s < NSUB; ++s)
+          tma_load_4d(sbase + L::K_OFF + s * SUB_BYTES, &tmQKV, s * 64, 1 * p.H + h, b, j * 128, bar(BAR_KFULL));
+        if (j > 0 && !mbar_wait(bar(BAR_VFREE), (j - 1) & 1, abort_flag, p.status)) break;
+        mbar_expect_tx(bar(BAR_VFULL), NSUB * SUB_BYTES);
+        for (int s = 0; s < NSUB; ++s)
+          tma_load_4d(sbase + L::V_OFF + s * SUB_BYTES, &tmQKV, s * 64, 2 * p.H + h, b, j * 128, bar(BAR_VFULL));
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_o = make_idesc_bf16(128, HDP, false, true);
+      auto issue_s = [&](int t) {  // S_t = Q_t K^T
+        const uint32_t qb = sbase + L::Q_OFF + t * NSUB * SUB_BYTES, kb = sbase + L::K_OFF;
+#pragma unroll
+        for (int kk = 0; kk < HDP / 16; ++kk) {
+          const uint32_t off = (kk / 4) * SUB_BYTES + (kk % 4) * 32;
+          tc_mma_f16(TM_S[t], make_smem_desc(qb + off, 16, 1024, 2), make_smem_desc(kb + off, 16, 1024, 2), idesc_s, kk != 0);
+        }
+        tc_commit(bar(BAR_SFULL0 + t));
+      };
+      auto issue_o = [&](int t) {  // O_t(j) = P_t V
+        const uint32_t pb = sbase + L::P_OFF + t * 2 * SUB_BYTES, vb = sbase + L::V_OFF;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t poff = (kk / 4) * SUB_BYTES + (kk % 4) * 32;
+          tc_mma_f16(TM_O[t], make_smem_desc(pb + poff, 16, 1024, 2), make_smem_desc(vb + kk * 2048, SUB_BYTES, 1024, 2), idesc_o,
+                     kk != 0);
+        }
+        tc_commit(bar(BAR_OFULL0 + t));
+      };
+      bool ok = mbar_wait(bar(BAR_Q), 0, abort_flag, p.status) && mbar_wait(bar(BAR_KFULL), 0, abort_flag, p.status);
+      if (ok) {
+        tc_fence_after();
+        if (n_a > 0) issue_s(0);
+        issue_s(1);
+        tc_commit(bar(BAR_KFREE));
+      }
+      for (int j = 0; j < n_b && ok; ++j) {
+        const uint32_t ph = j & 1;
+        if (!mbar_wait(bar(BAR_VFULL), ph, abort_flag, p.status)) break;
+        if (j < n_a) {
+          if (!mbar_wait(bar(BAR_PREADY0), ph, abort_flag, p.status)) break;
+          tc_fence_after();
+          issue_o(0);
+          if (j + 1 < n_a) {
+            if (!mbar_wait(bar(BAR_KFULL), ph ^ 1, abort_flag, p.status)) break;
+            tc_fence_after();
+            issue_s(0);
+          }
+        }
+        if (!mbar_wait(bar(BAR_PREADY1), ph, abort_flag, p.status)) break;
+        tc_fence_after();
+        issue_o(1);
+        tc_commit(bar(BAR_VFREE));
+        if (j + 1 < n_b) {
+          if (!mbar_wait(bar(BAR_KFULL), ph ^ 1, abort_flag, p.status)) break;
+          tc_fence_after();
+          issue_s(1);
+          tc_commit(bar(BAR_KFREE));
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax warp groups
+    const int t = (warp - 2) >> 2;  // 0: tile A, 1: tile B
+    const int quarter = warp & 3;
+    const int n_t = t == 0 ? n_a : n_b;
+    const int tile = t == 0 ? tile_a : tile_b;
+    const int row_local = quarter * 32 + lane;
+    const int row = tile * 128 + row_local;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t p_row = sbase + L::P_OFF + t * 2 * SUB_BYTES + row_local * 128;
+    float m = -INFINITY, l = 0.f;
+    float o[HDP];
+#pragma unroll
+    for (int i = 0; i < HDP; ++i) o[i] = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_t; ++j) {
+      const uint32_t ph = j & 1;
+      ok = mbar_wait(bar(BAR_SFULL0 + t), ph, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int key0 = j * 128;
+      const int limit = p.causal ? row : (p.S - 1);       // last key this row may see
+      const bool need_mask = key0 + 127 > (p.causal ? tile * 128 : p.S - 1);
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(TM_S[t] + lane_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(r[i]);
+          if (need_mask && key0 + c * 32 + i > limit) s = -INFINITY;
+          mx = fmaxf(mx, s);
+        }
+      }
+      const float m_new = fmaxf(m, mx * p.scale_log2);
+      const float alpha = fast_exp2(m - m_new);
+      // pass 2: probabilities -> bf16 P tile in shared memory, row sum
+      float lsum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(TM_S[t] + lane_addr + c * 32, r);
+        tmem_ld_wait();
+        float pr[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float e = fast_exp2(__uint_as_float(r[i]) * p.scale_log2 - m_new);
+          if (need_mask && key0 + c * 32 + i > limit) e = 0.f;
+          pr[i] = e;
+          lsum += e;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int q8 = c * 4 + g;  // 16-byte chunk index along the 128 keys
+          const uint32_t addr = p_row + (q8 >> 3) * SUB_BYTES + (((q8 & 7) ^ (row_local & 7)) << 4);
+          const uint32_t w0 = pack_bf16(pr[g * 8 + 0], pr[g * 8 + 1]), w1 = pack_bf16(pr[g * 8 + 2], pr[g * 8 + 3]);
+          const uint32_t w2 = pack_bf16(pr[g * 8 + 4], pr[g * 8 + 5]), w3 = pack_bf16(pr[g * 8 + 6], pr[g * 8 + 7]);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+        }
+      }
+      l = l * alpha + lsum;
+      m = m_new;
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(bar(BAR_PREADY0 + t));
+#pragma unroll
+      for (int i = 0; i < HDP; ++i) o[i] *= alpha;
+      ok = mbar_wait(bar(BAR_OFULL0 + t), ph, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < HDP / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(TM_O[t] + lane_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(r[i]);
+      }
+    }
+    if (ok && n_t > 0 && row < p.S) {
+      const float inv = 1.f / l;
+      __nv_bfloat16* orow = p.O + (long long)row * p.o_stride_s + (long long)b * p.o_stride_b + (long long)h * p.hd;
+#pragma unroll
+      for (int g = 0; g < HDP / 8; ++g) {
+        if (g * 8 < p.hd) {
+          uint4 v = make_uint4(pack_bf16(o[g * 8 + 0] * inv, o[g * 8 + 1] * inv), pack_bf16(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv),
+                               pack_bf16(o[g * 8 + 4] * inv, o[g * 8 + 5] * inv), pack_bf16(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv));
+          *reinterpret_cast<uint4*>(orow + g * 8) = v;
+        }
+      }
+      if (p.lse) p.lse[((long long)b * p.H + h) * p.S + row] = (m + log2f(l)) * 0.6931471805599453f;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int HDP>
+int launch_attn_fwd(const CUtensorMap& tm, const AttnFwdParams& p, cudaStream_t stream) {
+  using L = AttnSmem<HDP>;
+  auto kern = attn_fwd_kernel<HDP>;
+  static bool configured = false;
+  if (!configured) {
+    ELFA_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
+    configured = true;
+  }
+  dim3 grid((p.n_qtiles + 1) / 2, p.H, p.B);
+  kern<<<grid, ATT_THREADS, L::DYN, stream>>>(tm, p);
+  ELFA_CUDA(cudaGetLastError());
+  return ELFA_OK;
+}
+
+}  // namespace
+
+// 4-D map over a fused qkv tensor: dims {hd, 3*H, B, S}, box {64, 1, 1, box_rows}.
+int make_qkv_tmap(CUtensorMap* tm, const void* qkv, int S, int B, int H, int hd, long long stride_s, long long stride_b,
+                  int planes, uint32_t box_rows) {
+  const uint64_t dims[4] = {(uint64_t)hd, (uint64_t)planes * H, (uint64_t)B, (uint64_t)S};
+  const uint64_t strides[3] = {(uint64_t)hd * 2, (uint64_t)stride_b * 2, (uint64_t)stride_s * 2};
+  const uint32_t box[4] = {64, 1, 1, box_rows};
+  return make_tmap_nd_bf16(tm, qkv, 4, dims, strides, box);
+}
+
+}  // namespace elfa
+
+using namespace elfa;
+
+// qkv: element (s, b, which, h, d) at s*stride_s + b*stride_b + (which*H + h)*hd + d (bf16).
+// out: element (s, b, h, d) at s*o_stride_s + b*o_stride_b + h*hd + d. lse: [B, H, S] fp32 or null.
+ELFA_API int elfa_attention_fwd(const void* qkv, long long stride_s, long long stride_b, void* out, long long o_stride_s,
+                                long long o_stride_b, float* lse, int S, int B, int H, int hd, float scale, int causal, void* stream) {
+  ELFA_REQUIRE(qkv && out && S > 0 && B > 0 && H > 0, "attention_fwd: bad arguments");
+  ELFA_REQUIRE(hd % 8 == 0 && hd >= 8 && hd <= 128, "attention_fwd: head_dim must be a multiple of 8 in [8, 128]");
+  ELFA_REQUIRE(stride_s % 8 == 0 && stride_b % 8 == 0 && o_stride_s % 8 == 0 && o_stride_b % 8 == 0, "attention_fwd: strides must be multiples of 8");
+  unsigned int* st = status_word();
+  ELFA_REQUIRE(st != nullptr, "attention_fwd: no status word");
+  CUtensorMap tm;
+  int rc = make_qkv_tmap(&tm, qkv, S, B, H, hd, stride_s, stride_b, 3, 128);
+  if (rc != ELFA_OK) return rc;
+  AttnFwdParams p{};
+  p.S = S; p.B = B; p.H = H; p.hd = hd;
+  p.O = static_cast<__nv_bfloat16*>(out);
+  p.o_stride_s = o_stride_s; p.o_stride_b = o_stride_b;
+  p.lse = lse;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.causal = causal;
+  p.n_qtiles = (S + 127) / 128;
+  p.status = st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return hd <= 64 ? launch_attn_fwd<64>(tm, p, s) : launch_attn_fwd<128>(tm, p, s);
+}

@@ -56,6 +56,9 @@ unsigned int* status_word();   // device pointer to this device's status word (l
 int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
                  uint64_t ld_bytes, uint32_t box_rows, uint32_t box_cols, bool swizzle128);
 
+int make_tmap_nd_bf16(CUtensorMap* out, const void* base, int ndim, const uint64_t* dims, const uint64_t* strides_bytes,
+                      const uint32_t* box);
+
 #ifdef __CUDACC__
 // ----------------------------------------------------------------------------------------------
 // device helpers
@@ -119,6 +122,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm,
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(tm), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm, int c0, int c1, int c2, int c3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
       : "memory");
 }
 // TMA: 2-D tiled store shared -> global.
@@ -255,6 +264,19 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, bool a_mn_m
 __host__ __device__ constexpr uint32_t make_idesc_mxf8(int M, int N, uint32_t sfa_id, uint32_t sfb_id) {
   return ((sfb_id & 3u) << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(N >> 3) << 17) | (1u << 23) |
          ((uint32_t)(M >> 4) << 24) | ((sfa_id & 3u) << 29);
+}
+
+template <int N>
+__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 // ---- misc -------------------------------------------------------------------------------------

@@ -67,6 +67,10 @@ int elfa_three_i_minus(void* g, int d, void* stream);
 int elfa_muon_apply(void* param, int param_type, float* master, const void* y, long long n, float lr, const void* scalars,
                     void* stream);
 
+// ---- attention_fwd.cu --------------------------------------------------------------------------
+int elfa_attention_fwd(const void* qkv, long long stride_s, long long stride_b, void* out, long long o_stride_s,
+                       long long o_stride_b, float* lse, int S, int B, int H, int hd, float scale, int causal, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

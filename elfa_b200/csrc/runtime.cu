@@ -76,6 +76,38 @@ int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t ro
   return ELFA_OK;
 }
 
+// General N-d (<= 5) tiled map, 16-bit elements, 128-byte swizzle. dims/box innermost first;
+// strides_bytes has ndim-1 entries (dims 1..).
+int make_tmap_nd_bf16(CUtensorMap* out, const void* base, int ndim, const uint64_t* dims, const uint64_t* strides_bytes,
+                      const uint32_t* box) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) {
+    set_last_error("cuTensorMapEncodeTiled is not available (no driver?)");
+    return ELFA_ERR_CUDA;
+  }
+  if (reinterpret_cast<uintptr_t>(base) & 15) {
+    set_last_error("tensor map: base address must be a multiple of 16 bytes");
+    return ELFA_ERR_ARG;
+  }
+  cuuint64_t d[5], st[4];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < ndim; ++i) { d[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
+  for (int i = 0; i + 1 < ndim; ++i) {
+    if (strides_bytes[i] & 15) {
+      set_last_error("tensor map: strides must be multiples of 16 bytes");
+      return ELFA_ERR_ARG;
+    }
+    st[i] = strides_bytes[i];
+  }
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, ndim, const_cast<void*>(base), d, st, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_error = "cuTensorMapEncodeTiled (nd) failed with code " + std::to_string((int)r);
+    return ELFA_ERR_CUDA;
+  }
+  return ELFA_OK;
+}
+
 }  // namespace elfa
 
 using namespace elfa;

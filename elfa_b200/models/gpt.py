@@ -1,0 +1,256 @@
+"""Pre-norm GPT decoder: learned positions, causal softmax attention, GELU MLP, tied embeddings.
+
+This is the attention-mixer family selected by ``model.efla.enabled: false`` (the reference's
+gen-1 distributed/quantisation code operates on exactly this QKVO + FFN parameter set:
+reference ``src/distributed/zero_sharding.zig:73-99``, ``src/quantization/stable_qat.zig:36-50``;
+attention math: ``src/futhark/attention.fut:28-51``). Block structure mirrors the reference block
+(``src/model/model.zig:229-272``): norm → mixer → residual → norm → MLP → residual.
+
+Tensor parallelism (Megatron style, with sequence parallelism): QKV and MLP-up are column
+parallel, attention-out and MLP-down are row parallel, embeddings are vocabulary parallel, and the
+residual stream / norms hold ``S/tp`` tokens per rank. Internal activation layout is
+``[S, B, D]`` (sequence first) so that sequence shards are contiguous.
+
+Parameter names (checkpoint keys) extend the reference's naming style
+(``src/model/model.zig:512-537``): ``embed_tokens.weight``, ``pos_embed.weight``,
+``blocks.{i}.ln1.{weight,bias}``, ``blocks.{i}.attn.w_qkv``, ``blocks.{i}.attn.w_o``,
+``blocks.{i}.ln2.{weight,bias}``, ``blocks.{i}.mlp_up.weight``, ``blocks.{i}.mlp_down.weight``,
+``final_norm.{weight,bias}``, ``lm_head.weight`` (untied only). Linear weights are ``[in, out]``.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from ..config import Config
+from ..parallel.mesh import ParallelContext
+from ..parallel import tp as tpl
+from ..quant.qat import QuantSpec, fake_quant
+
+
+def _dtype(name: str) -> torch.dtype:
+    return {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16, "fp8_e4m3": torch.bfloat16}[name]
+
+
+class Norm(nn.Module):
+    def __init__(self, dim: int, kind: str, dtype, device):
+        super().__init__()
+        self.kind = ops.LAYERNORM if kind == "layernorm" else ops.RMSNORM
+        self.eps = 1e-5 if kind == "layernorm" else 1e-6
+        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(dim, dtype=dtype, device=device)) if kind == "layernorm" else None
+        self.weight.no_decay = True
+        self.weight.tp_replicated = True
+        if self.bias is not None:
+            self.bias.no_decay = True
+            self.bias.tp_replicated = True
+
+    def forward(self, x, residual=None):
+        return ops.norm(x, self.weight, self.bias, eps=self.eps, kind=self.kind, residual=residual)
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg: Config, pc: ParallelContext, dtype, device, init_std: float, out_std: float):
+        super().__init__()
+        m = cfg.model
+        self.pc = pc
+        self.n_heads = m.num_heads // pc.tp_size
+        self.head_dim = m.head_dim
+        D = m.hidden_dim
+        local = self.n_heads * self.head_dim
+        self.w_qkv = nn.Parameter(torch.empty(D, 3 * local, dtype=dtype, device=device))
+        self.w_o = nn.Parameter(torch.empty(local, D, dtype=dtype, device=device))
+        self.w_qkv.tp_shard = ("col_qkv", pc.tp_size)
+        self.w_o.tp_shard = ("row", pc.tp_size)
+        self.init_std, self.out_std = init_std, out_std
+        self.quant = QuantSpec.from_config(cfg.quant.attention, cfg.quant)
+
+    def forward(self, x):            # x: [S(/tp), B, D]
+        h = tpl.column_parallel_linear(x, self.w_qkv, self.pc, quant=self.quant)      # [S, B, 3*local]
+        S, B = h.shape[0], h.shape[1]
+        o = ops.attention(h.view(S, B, 3, self.n_heads, self.head_dim), causal=True, seq_first=True)   # [S, B, local]
+        return tpl.row_parallel_linear(o, self.w_o, self.pc, quant=self.quant)        # [S(/tp), B, D]
+
+
+class MLP(nn.Module):
+    def __init__(self, cfg: Config, pc: ParallelContext, dtype, device):
+        super().__init__()
+        m = cfg.model
+        self.pc = pc
+        D, F = m.hidden_dim, m.intermediate_dim // pc.tp_size
+        self.act = m.activation
+        self.gated = m.activation == "swiglu"
+        self.up = nn.Parameter(torch.empty(D, F * (2 if self.gated else 1), dtype=dtype, device=device))
+        self.down = nn.Parameter(torch.empty(F, D, dtype=dtype, device=device))
+        self.up.tp_shard = ("col", pc.tp_size)
+        self.down.tp_shard = ("row", pc.tp_size)
+        self.quant = QuantSpec.from_config(cfg.quant.mlp, cfg.quant)
+
+    def forward(self, x):
+        if self.gated:
+            h = tpl.column_parallel_linear(x, self.up, self.pc, quant=self.quant)
+            g, u = h.chunk(2, dim=-1)
+            a = ops.activation(g.contiguous(), "silu") * u
+        elif self.act == "gelu":
+            a = tpl.column_parallel_linear(x, self.up, self.pc, act="gelu", quant=self.quant)
+        else:
+            a = ops.activation(tpl.column_parallel_linear(x, self.up, self.pc, quant=self.quant), self.act)
+        return tpl.row_parallel_linear(a, self.down, self.pc, quant=self.quant)
+
+
+class Block(nn.Module):
+    def __init__(self, cfg: Config, pc: ParallelContext, dtype, device, init_std, out_std):
+        super().__init__()
+        m = cfg.model
+        self.ln1 = Norm(m.hidden_dim, m.norm_type, dtype, device)
+        self.attn = Attention(cfg, pc, dtype, device, init_std, out_std)
+        self.ln2 = Norm(m.hidden_dim, m.norm_type, dtype, device)
+        self.mlp = MLP(cfg, pc, dtype, device)
+        self.dropout = m.dropout
+
+    def forward(self, x, pending):
+        """``pending`` is the previous sub-layer's output that has not been added to the residual
+        stream yet; the add is fused into the next norm kernel."""
+        n, x = self.ln1(x, pending)
+        a = self.attn(n)
+        if self.dropout > 0 and self.training:
+            a = torch.nn.functional.dropout(a, self.dropout)
+        n, x = self.ln2(x, a)
+        f = self.mlp(n)
+        if self.dropout > 0 and self.training:
+            f = torch.nn.functional.dropout(f, self.dropout)
+        return x, f
+
+
+class GPTModel(nn.Module):
+    def __init__(self, cfg: Config, pc: Optional[ParallelContext] = None, device=None):
+        super().__init__()
+        self.cfg = cfg
+        self.pc = pc or ParallelContext()
+        m = cfg.model
+        dtype = _dtype(m.dtype)
+        self.dtype = dtype
+        tp = self.pc.tp_size
+        if m.vocab_size % tp or m.num_heads % tp or m.intermediate_dim % tp:
+            raise ValueError("vocab_size, num_heads and intermediate_dim must be divisible by the tensor-parallel size")
+        self.vocab_local = m.vocab_size // tp
+        self.vocab_lo = self.pc.tp_rank * self.vocab_local
+        D = m.hidden_dim
+        std = cfg.bench.init_std
+        self.embed_tokens = nn.Parameter(torch.empty(self.vocab_local, D, dtype=dtype, device=device))
+        self.embed_tokens.tp_shard = ("vocab", tp)
+        self.pos_embed = None
+        if cfg.bench.learned_positions:
+            self.pos_embed = nn.Parameter(torch.empty(min(m.max_seq_len, max(cfg.data.seq_len, 1)), D, dtype=dtype, device=device))
+            self.pos_embed.tp_replicated = True
+        out_std = std if std > 0 else math.sqrt(2.0 / D)
+        self.blocks = nn.ModuleList([Block(cfg, self.pc, dtype, device, std, out_std) for _ in range(m.num_layers)])
+        self.final_norm = Norm(D, m.norm_type, dtype, device)
+        self.lm_head = None
+        if not m.tie_embeddings:
+            self.lm_head = nn.Parameter(torch.empty(self.vocab_local, D, dtype=dtype, device=device))
+            self.lm_head.tp_shard = ("vocab", tp)
+        self.reset_parameters(cfg.runtime.seed)
+
+    # ------------------------------------------------------------------ init
+    def reset_parameters(self, seed: int) -> None:
+        """N(0, init_std) when ``bench.init_std > 0``; otherwise the reference's He-style defaults
+        (Linear sigma = sqrt(2/in), Embedding sigma = sqrt(1/dim): reference ``src/nn/layers.zig:336,446``).
+        Full (unsharded) tensors are drawn from one generator and sliced, so a TP run starts from
+        the same weights as a single-GPU run."""
+        m, tp, r = self.cfg.model, self.pc.tp_size, self.pc.tp_rank
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        std = self.cfg.bench.init_std
+        D = m.hidden_dim
+
+        def draw(shape, sigma):
+            return torch.randn(shape, generator=g, dtype=torch.float32) * sigma
+
+        def put(p, full):
+            with torch.no_grad():
+                p.copy_(full.to(p.dtype))
+
+        emb = draw((m.vocab_size, D), std if std > 0 else math.sqrt(1.0 / D))
+        put(self.embed_tokens, emb[self.vocab_lo:self.vocab_lo + self.vocab_local])
+        if self.pos_embed is not None:
+            put(self.pos_embed, draw(tuple(self.pos_embed.shape), std if std > 0 else math.sqrt(1.0 / D)))
+        F = m.intermediate_dim
+        for blk in self.blocks:
+            s_in = std if std > 0 else math.sqrt(2.0 / D)
+            wqkv = draw((D, 3 * D), s_in)
+            put(blk.attn.w_qkv, tpl.shard_param(wqkv, "col_qkv", tp, r))
+            put(blk.attn.w_o, tpl.shard_param(draw((D, D), s_in), "row", tp, r))
+            gated = 2 if blk.mlp.gated else 1
+            up = draw((D, F * gated), s_in)
+            put(blk.mlp.up, tpl.shard_param(up, "col_gated" if blk.mlp.gated else "col", tp, r))
+            put(blk.mlp.down, tpl.shard_param(draw((F, D), std if std > 0 else math.sqrt(2.0 / F)), "row", tp, r))
+        if self.lm_head is not None:
+            head = draw((m.vocab_size, D), std if std > 0 else math.sqrt(2.0 / D))
+            put(self.lm_head, head[self.vocab_lo:self.vocab_lo + self.vocab_local])
+
+    # ------------------------------------------------------------------ names
+    def named_checkpoint_parameters(self):
+        """Yields ``(checkpoint_name, parameter)`` in a fixed order."""
+        yield "embed_tokens.weight", self.embed_tokens
+        if self.pos_embed is not None:
+            yield "pos_embed.weight", self.pos_embed
+        for i, b in enumerate(self.blocks):
+            yield f"blocks.{i}.ln1.weight", b.ln1.weight
+            if b.ln1.bias is not None:
+                yield f"blocks.{i}.ln1.bias", b.ln1.bias
+            yield f"blocks.{i}.attn.w_qkv", b.attn.w_qkv
+            yield f"blocks.{i}.attn.w_o", b.attn.w_o
+            yield f"blocks.{i}.ln2.weight", b.ln2.weight
+            if b.ln2.bias is not None:
+                yield f"blocks.{i}.ln2.bias", b.ln2.bias
+            yield f"blocks.{i}.mlp_up.weight", b.mlp.up
+            yield f"blocks.{i}.mlp_down.weight", b.mlp.down
+        yield "final_norm.weight", self.final_norm.weight
+        if self.final_norm.bias is not None:
+            yield "final_norm.bias", self.final_norm.bias
+        if self.lm_head is not None:
+            yield "lm_head.weight", self.lm_head
+
+    def count_parameters(self) -> int:
+        """Parameters of the full (unsharded) model."""
+        n = 0
+        for _, p in self.named_checkpoint_parameters():
+            k = p.numel()
+            if hasattr(p, "tp_shard"):
+                k *= p.tp_shard[1]
+            n += k
+        return n
+
+    # ---------------------------------------------------------------- forward
+    def hidden_states(self, ids: torch.Tensor, pos0: int = 0) -> torch.Tensor:
+        """ids ``[B, S]`` → final-norm output ``[S(/tp), B, D]``."""
+        pc = self.pc
+        ids_sb = ids.t().contiguous()                        # [S, B]
+        x = ops.embedding(ids_sb, self.embed_tokens, self.pos_embed, pos0, self.vocab_lo, seq_first=True)  # [S, B, D]
+        x = tpl.embedding_reduce(x, pc)                      # sum over vocab shards → [S(/tp), B, D]
+        pending = None
+        for blk in self.blocks:
+            if self.cfg.bench.activation_checkpointing and self.training:
+                x, pending = torch.utils.checkpoint.checkpoint(blk, x, pending, use_reentrant=False)
+            else:
+                x, pending = blk(x, pending)
+        n, _ = self.final_norm(x, pending)
+        return n
+
+    def forward(self, ids: torch.Tensor, targets: Optional[torch.Tensor] = None, pos0: int = 0,
+                loss_denominator: Optional[float] = None, grad_scale: float = 1.0):
+        """Returns logits ``[B, S, V]`` when ``targets`` is None (single-rank only), else the mean
+        cross-entropy over ``targets`` ``[B, S]`` (label smoothing from the config)."""
+        n = self.hidden_states(ids, pos0)
+        head = self.lm_head if self.lm_head is not None else self.embed_tokens
+        if targets is None:
+            logits = tpl.vocab_parallel_logits(n, head, self.pc, gather=True)    # [S, B, V]
+            return logits.transpose(0, 1)
+        logits = tpl.vocab_parallel_logits(n, head, self.pc, gather=False)       # [S, B, V/tp]
+        t_sb = targets.t().contiguous()
+        return tpl.vocab_parallel_cross_entropy(logits, t_sb, self.pc, self.vocab_lo, self.cfg.model.vocab_size,
+                                                self.cfg.training.label_smoothing, loss_denominator, grad_scale)

@@ -3,3 +3,4 @@ the PyTorch reference formula."""
 from .gemm import gemm, linear, linear_nt, gelu_tanh_ref, dgelu_tanh_ref  # noqa: F401
 from .nn import (LAYERNORM, RMSNORM, activation, cross_entropy, cross_entropy_ref, embedding, gelu, layer_norm, norm,  # noqa: F401
                  norm_ref, rms_norm)
+from .attention import attention, attention_ref  # noqa: F401

@@ -324,7 +324,6 @@ class _CrossEntropy(torch.autograd.Function):
         ctx.cpu = False
         ctx.save_for_backward(l2)
         ctx.shape = logits.shape
-        ctx.mark_dirty(logits)
         return per.sum() / denom
 
     @staticmethod

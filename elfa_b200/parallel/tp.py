@@ -1,0 +1,383 @@
+"""Tensor parallelism with sequence parallelism (Megatron style) and parameter sharding helpers.
+
+Capabilities of the reference's gen-1 tensor/sequence-parallel code
+(reference: ``src/distributed/tensor_parallel.zig:51-201`` shard / gather / all-reduce / broadcast,
+``src/distributed/sequence_parallel.zig:54-200`` split / gather / reduce-scatter,
+descriptors ``src/tensor/sharding.zig:183-287``), restated per rank:
+
+* column-parallel linear (QKV, MLP-up): input is the sequence shard ``[S/tp, B, D]``; the
+  all-gather along the sequence feeds the GEMM (**all-gather → GEMM**);
+* row-parallel linear (attention-out, MLP-down): the GEMM output is a partial sum that is
+  reduce-scattered along the sequence (**GEMM → reduce-scatter**). Partial sums are *summed*
+  (the reference's ``allReduceTensor`` divides by the world size, which is wrong for a
+  row-parallel product);
+* vocabulary-parallel embedding, logits and cross-entropy.
+
+Two backends implement the two fused primitives ``ag_gemm`` and ``gemm_rs``:
+``nccl`` (library all-gather / reduce-scatter around the GEMM - the baseline) and ``fused``
+(one kernel that moves the tiles over NVLink peer memory while the tensor cores run; see
+``elfa_b200/parallel/fused.py``).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..ops.gemm import gemm
+from ..quant.qat import QuantSpec, fake_quant
+from .mesh import ParallelContext
+
+
+# ------------------------------------------------------------------------------- parameter shards
+def shard_param(full: torch.Tensor, kind: str, tp: int, rank: int) -> torch.Tensor:
+    """Slice of a full parameter owned by ``rank``. Kinds: ``col`` (split dim 1), ``row`` and ``vocab``
+    (split dim 0), ``col_qkv`` (``[D, 3D]`` laid out ``[Q|K|V]`` → this rank's heads of each),
+    ``col_gated`` (``[D, 2F]`` laid out ``[gate|up]``), ``replicated``."""
+    if tp == 1 or kind == "replicated":
+        return full
+    if kind == "col":
+        n = full.shape[1] // tp
+        return full[:, rank * n:(rank + 1) * n]
+    if kind in ("row", "vocab"):
+        n = full.shape[0] // tp
+        return full[rank * n:(rank + 1) * n]
+    if kind in ("col_qkv", "col_gated"):
+        parts = 3 if kind == "col_qkv" else 2
+        w = full.shape[1] // parts
+        n = w // tp
+        return torch.cat([full[:, i * w + rank * n:i * w + (rank + 1) * n] for i in range(parts)], dim=1)
+    raise ValueError(kind)
+
+
+def unshard_param(shards: List[torch.Tensor], kind: str) -> torch.Tensor:
+    """Inverse of :func:`shard_param` (``shards[r]`` belongs to rank r)."""
+    tp = len(shards)
+    if tp == 1 or kind == "replicated":
+        return shards[0]
+    if kind == "col":
+        return torch.cat(shards, dim=1)
+    if kind in ("row", "vocab"):
+        return torch.cat(shards, dim=0)
+    if kind in ("col_qkv", "col_gated"):
+        parts = 3 if kind == "col_qkv" else 2
+        n = shards[0].shape[1] // parts
+        return torch.cat([torch.cat([s[:, i * n:(i + 1) * n] for s in shards], dim=1) for i in range(parts)], dim=1)
+    raise ValueError(kind)
+
+
+# ------------------------------------------------------------------------------------ collectives
+def _all_gather_dim0(x: torch.Tensor, pc: ParallelContext) -> torch.Tensor:
+    out = torch.empty((x.shape[0] * pc.tp_size, *x.shape[1:]), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(out, x.contiguous(), group=pc.tp_group)
+    return out
+
+
+def _reduce_scatter_dim0(x: torch.Tensor, pc: ParallelContext) -> torch.Tensor:
+    n = x.shape[0] // pc.tp_size
+    x = x.contiguous()
+    if x.is_cuda:
+        out = torch.empty((n, *x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.reduce_scatter_tensor(out, x, group=pc.tp_group)
+        return out
+    dist.all_reduce(x, group=pc.tp_group)           # gloo has no reduce-scatter
+    return x[pc.tp_rank * n:(pc.tp_rank + 1) * n].clone()
+
+
+class _GatherSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, pc):
+        ctx.pc = pc
+        return _all_gather_dim0(x, pc)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _reduce_scatter_dim0(g, ctx.pc), None
+
+
+class _ReduceScatterSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, pc):
+        ctx.pc = pc
+        return _reduce_scatter_dim0(x, pc)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _all_gather_dim0(g, ctx.pc), None
+
+
+class _CopyToTP(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, pc):
+        ctx.pc = pc
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        dist.all_reduce(g, group=ctx.pc.tp_group)
+        return g, None
+
+
+class _ReduceFromTP(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, pc):
+        x = x.contiguous()
+        dist.all_reduce(x, group=pc.tp_group)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+# ------------------------------------------------------------------- the two fused primitives
+def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, pc: ParallelContext, *, b_mn: bool, act: Optional[str] = None,
+            preact: bool = False) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """``y = act(all_gather_rows(x_local) @ op(w))``. Returns ``(y, x_full, pre)`` - the gathered
+    input is a by-product that backward needs for the weight gradient. ``w`` is ``[K, N]`` when
+    ``b_mn`` else ``[N, K]``."""
+    if pc.comm_backend == "fused" and x_local.is_cuda:
+        from . import fused
+        return fused.ag_gemm(x_local, w, pc, b_mn=b_mn, act=act, preact=preact)
+    x_full = _all_gather_dim0(x_local, pc)
+    pre = None
+    if act == "gelu":
+        pre = torch.empty((x_full.shape[0], w.shape[1] if b_mn else w.shape[0]), dtype=x_full.dtype, device=x_full.device) if preact else None
+        y = gemm(x_full, w, b_mn=b_mn, gelu=True, preact=pre, out_dtype=x_full.dtype)
+    else:
+        y = gemm(x_full, w, b_mn=b_mn, out_dtype=x_full.dtype)
+    return y, x_full, pre
+
+
+def gemm_rs(a: torch.Tensor, w: torch.Tensor, pc: ParallelContext, *, b_mn: bool) -> torch.Tensor:
+    """``reduce_scatter_rows(a @ op(w))``: every rank contributes a partial product over its slice of
+    the contraction dimension and receives the summed rows ``[M/tp, N]`` it owns."""
+    if pc.comm_backend == "fused" and a.is_cuda:
+        from . import fused
+        return fused.gemm_rs(a, w, pc, b_mn=b_mn)
+    return _reduce_scatter_dim0(gemm(a, w, b_mn=b_mn, out_dtype=a.dtype), pc)
+
+
+def _wgrad(w_ref: torch.Tensor, x2: torch.Tensor, dy2: torch.Tensor, w_dtype) -> Optional[torch.Tensor]:
+    """x2^T @ dy2 into ``w_ref.main_grad`` (returns None) or as a new tensor."""
+    mg = getattr(w_ref, "main_grad", None)
+    if mg is not None and dy2.is_cuda:
+        fresh = getattr(w_ref, "_grad_fresh", False)
+        gemm(x2, dy2, a_mn=True, b_mn=True, out=mg, accumulate=not fresh)
+        w_ref._grad_fresh = False
+        return None
+    return gemm(x2, dy2, a_mn=True, b_mn=True, out_dtype=w_dtype)
+
+
+class _ColumnParallelSP(torch.autograd.Function):
+    """x_local ``[S/tp, B, D]`` → ``act(all_gather(x) @ w_local)`` ``[S, B, N/tp]``."""
+
+    @staticmethod
+    def forward(ctx, x, w, pc, act, quant):
+        Sl, B, D = x.shape
+        xq = fake_quant(x.reshape(Sl * B, D), quant) if quant is not None else x.reshape(Sl * B, D)
+        wq = fake_quant(w, quant, weight=True) if quant is not None else w
+        y, x_full, pre = ag_gemm(xq, wq, pc, b_mn=True, act=act, preact=True)
+        ctx.save_for_backward(x_full, wq, pre)
+        ctx.pc, ctx.w_ref, ctx.shape = pc, w, (Sl, B, D)
+        return y.view(Sl * pc.tp_size, B, -1)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_full, wq, pre = ctx.saved_tensors
+        pc = ctx.pc
+        Sl, B, D = ctx.shape
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        if pre is not None:
+            if dy2.is_cuda:
+                from ..native import lib, stream_ptr
+                dpre = torch.empty_like(dy2)
+                lib.call("elfa_elementwise", 1, pre, dy2, dpre, dy2.numel(), 1.0, stream_ptr(dy2))
+                dy2 = dpre
+            else:
+                dy2 = (dy2.float() * ops.dgelu_tanh_ref(pre.float())).to(dy2.dtype)
+        dx = gemm_rs(dy2, wq, pc, b_mn=False)              # dy @ w^T, summed over ranks, rows scattered
+        dw = _wgrad(ctx.w_ref, x_full, dy2, wq.dtype)
+        return dx.view(Sl, B, D), dw, None, None, None
+
+
+class _RowParallelSP(torch.autograd.Function):
+    """x ``[S, B, K/tp]`` → ``reduce_scatter(x @ w_local)`` ``[S/tp, B, D]``."""
+
+    @staticmethod
+    def forward(ctx, x, w, pc, quant):
+        S, B, K = x.shape
+        x2 = x.reshape(S * B, K)
+        xq = fake_quant(x2, quant) if quant is not None else x2
+        wq = fake_quant(w, quant, weight=True) if quant is not None else w
+        y = gemm_rs(xq, wq, pc, b_mn=True)
+        ctx.save_for_backward(xq, wq)
+        ctx.pc, ctx.w_ref, ctx.shape = pc, w, (S, B, K)
+        return y.view(S // pc.tp_size, B, -1)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xq, wq = ctx.saved_tensors
+        pc = ctx.pc
+        S, B, K = ctx.shape
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx, dy_full, _ = ag_gemm(dy2, wq, pc, b_mn=False)   # all_gather(dy) @ w^T
+        dw = _wgrad(ctx.w_ref, xq, dy_full, wq.dtype)
+        return dx.view(S, B, K), dw, None, None
+
+
+class _QuantLinear(torch.autograd.Function):
+    """Single-rank linear with fake-quantised operands (straight-through backward)."""
+
+    @staticmethod
+    def forward(ctx, x, w, act, quant):
+        x2 = x.reshape(-1, x.shape[-1])
+        xq = fake_quant(x2, quant)
+        wq = fake_quant(w, quant, weight=True)
+        pre = None
+        if act == "gelu":
+            pre = torch.empty((x2.shape[0], w.shape[1]), dtype=x2.dtype, device=x2.device)
+            y = gemm(xq, wq, b_mn=True, gelu=True, preact=pre, out_dtype=x2.dtype)
+        else:
+            y = gemm(xq, wq, b_mn=True, out_dtype=x2.dtype)
+        ctx.save_for_backward(xq, wq, pre)
+        ctx.w_ref, ctx.shape = w, x.shape
+        return y.view(*x.shape[:-1], w.shape[1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        xq, wq, pre = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        if pre is not None:
+            if dy2.is_cuda:
+                from ..native import lib, stream_ptr
+                dpre = torch.empty_like(dy2)
+                lib.call("elfa_elementwise", 1, pre, dy2, dpre, dy2.numel(), 1.0, stream_ptr(dy2))
+                dy2 = dpre
+            else:
+                dy2 = (dy2.float() * ops.dgelu_tanh_ref(pre.float())).to(dy2.dtype)
+        dx = gemm(dy2, wq, out_dtype=dy2.dtype).view(ctx.shape)
+        dw = _wgrad(ctx.w_ref, xq, dy2, wq.dtype)
+        return dx, dw, None, None
+
+
+def column_parallel_linear(x: torch.Tensor, w: torch.Tensor, pc: ParallelContext, act: Optional[str] = None,
+                           quant: Optional[QuantSpec] = None) -> torch.Tensor:
+    if quant is not None and not quant.enabled:
+        quant = None
+    if pc.tp_size == 1:
+        return _QuantLinear.apply(x, w, act, quant) if quant is not None else ops.linear(x, w, None, act)
+    if pc.sequence_parallel:
+        return _ColumnParallelSP.apply(x, w, pc, act, quant)
+    x = _CopyToTP.apply(x, pc)
+    return _QuantLinear.apply(x, w, act, quant) if quant is not None else ops.linear(x, w, None, act)
+
+
+def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, pc: ParallelContext, quant: Optional[QuantSpec] = None) -> torch.Tensor:
+    if quant is not None and not quant.enabled:
+        quant = None
+    if pc.tp_size == 1:
+        return _QuantLinear.apply(x, w, None, quant) if quant is not None else ops.linear(x, w)
+    if pc.sequence_parallel:
+        return _RowParallelSP.apply(x, w, pc, quant)
+    y = _QuantLinear.apply(x, w, None, quant) if quant is not None else ops.linear(x, w)
+    return _ReduceFromTP.apply(y, pc)
+
+
+# ------------------------------------------------------------------ vocabulary-parallel pieces
+def embedding_reduce(x: torch.Tensor, pc: ParallelContext) -> torch.Tensor:
+    """Sum of the per-rank partial embeddings; with sequence parallelism the sum is scattered
+    along the sequence so that each rank keeps ``S/tp`` tokens."""
+    if pc.tp_size == 1:
+        return x
+    if pc.sequence_parallel:
+        return _ReduceScatterSeq.apply(x, pc)
+    return _ReduceFromTP.apply(x, pc)
+
+
+def vocab_parallel_logits(n: torch.Tensor, head: torch.Tensor, pc: ParallelContext, gather: bool) -> torch.Tensor:
+    """``n [S(/tp), B, D] @ head_local^T`` → ``[S, B, V/tp]`` (``[S, B, V]`` when ``gather``)."""
+    if pc.tp_size == 1:
+        return ops.linear_nt(n, head)
+    n_full = _GatherSeq.apply(n, pc) if pc.sequence_parallel else _CopyToTP.apply(n, pc)
+    logits = ops.linear_nt(n_full, head)
+    if gather:
+        parts = [torch.empty_like(logits) for _ in range(pc.tp_size)]
+        dist.all_gather(parts, logits.contiguous(), group=pc.tp_group)
+        logits = torch.cat(parts, dim=-1)
+    return logits
+
+
+class _VocabParallelCE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, targets, pc, vocab_lo, vocab_total, smoothing, denom, grad_scale):
+        Vl = logits.shape[-1]
+        l2 = logits.reshape(-1, Vl)
+        t1 = targets.reshape(-1)
+        rows = l2.shape[0]
+        ctx.shape = logits.shape
+        if l2.is_cuda:
+            from ..native import lib, stream_ptr
+            st = stream_ptr(l2)
+            mine = torch.empty((rows, 4), dtype=torch.float32, device=l2.device)
+            lib.call("elfa_xent_stats", l2, l2.stride(0), t1, mine, rows, Vl, vocab_lo, vocab_total, st)
+            allst = torch.empty((pc.tp_size, rows, 4), dtype=torch.float32, device=l2.device)
+            dist.all_gather_into_tensor(allst, mine, group=pc.tp_group)
+            per = torch.empty(rows, dtype=torch.float32, device=l2.device)
+            lib.call("elfa_xent_grad", l2, l2.stride(0), l2, l2.stride(0), t1, allst, pc.tp_size, per, rows, Vl, vocab_lo,
+                     vocab_total, float(smoothing), None, grad_scale / denom, st)
+            ctx.save_for_backward(l2)
+            ctx.cuda = True
+            return per.sum() / denom
+        # CPU (gloo) path: same algebra in fp32
+        lf = l2.float()
+        m_loc = lf.max(-1).values
+        m = m_loc.clone()
+        dist.all_reduce(m, op=dist.ReduceOp.MAX, group=pc.tp_group)
+        e = torch.exp(lf - m.unsqueeze(-1))
+        s = e.sum(-1)
+        sx = lf.sum(-1)
+        local_t = t1 - vocab_lo
+        mine = (local_t >= 0) & (local_t < Vl)
+        tl = torch.where(mine, lf.gather(-1, local_t.clamp(0, Vl - 1).unsqueeze(-1)).squeeze(-1), torch.zeros_like(m))
+        pack = torch.stack([s, sx, tl], 0)
+        dist.all_reduce(pack, group=pc.tp_group)
+        s, sx, tl = pack[0], pack[1], pack[2]
+        lse = m + torch.log(s)
+        valid = (t1 >= 0) & (t1 < vocab_total)
+        per = -((1 - smoothing) * (tl - lse) + (smoothing / vocab_total) * (sx - vocab_total * lse)) * valid
+        grad = torch.exp(lf - lse.unsqueeze(-1)) - smoothing / vocab_total
+        onehot = torch.zeros_like(grad)
+        onehot[mine, local_t[mine]] = 1 - smoothing
+        grad = (grad - onehot) * valid.unsqueeze(-1) * (grad_scale / denom)
+        ctx.save_for_backward(grad.to(logits.dtype))
+        ctx.cuda = False
+        return per.sum() / denom
+
+    @staticmethod
+    def backward(ctx, dloss):
+        (g,) = ctx.saved_tensors
+        if not ctx.cuda:
+            g = g * dloss
+        return g.view(ctx.shape), None, None, None, None, None, None, None
+
+
+def vocab_parallel_cross_entropy(logits: torch.Tensor, targets: torch.Tensor, pc: ParallelContext, vocab_lo: int, vocab_total: int,
+                                 smoothing: float = 0.0, denom: Optional[float] = None, grad_scale: float = 1.0) -> torch.Tensor:
+    """Mean cross-entropy over ``targets`` with the vocabulary split across the TP group. Each
+    rank reduces its slice to four numbers per token (max, sum-exp, target logit, sum of logits);
+    those are exchanged, and the loss and the in-place gradient follow from them."""
+    if denom is None:
+        denom = float(targets.numel())
+    if pc.tp_size == 1:
+        return ops.cross_entropy(logits, targets, smoothing, denom, grad_scale)
+    return _VocabParallelCE.apply(logits, targets, pc, vocab_lo, vocab_total, smoothing, denom, float(grad_scale))

@@ -1,0 +1,36 @@
+"""tcgen05 attention kernels against the fp32 PyTorch formula."""
+import pytest
+import torch
+
+from elfa_b200 import native, ops
+
+pytestmark = pytest.mark.gpu
+
+
+def _qkv(S, B, H, hd, dev, seq_first=True, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    shape = (S, B, 3, H, hd) if seq_first else (B, S, 3, H, hd)
+    return torch.randn(shape, generator=g).to(torch.bfloat16).to(dev)
+
+
+@pytest.mark.parametrize("S,B,H,hd", [(128, 1, 1, 64), (256, 2, 2, 128), (384, 1, 3, 128), (200, 2, 2, 32), (1024, 1, 4, 64),
+                                      (2048, 1, 2, 128)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention_forward(cuda_device, S, B, H, hd, causal):
+    qkv = _qkv(S, B, H, hd, cuda_device)
+    with torch.no_grad():
+        out = ops.attention(qkv, causal=causal)
+    torch.cuda.synchronize()
+    assert native.status() == 0
+    ref = ops.attention_ref(qkv.float(), causal=causal)
+    err = (out.float() - ref).abs().max().item()
+    assert err < 0.03, f"max err {err}"
+
+
+def test_attention_forward_batch_first(cuda_device):
+    qkv = _qkv(256, 2, 2, 64, cuda_device, seq_first=False, seed=3)
+    with torch.no_grad():
+        out = ops.attention(qkv, causal=True, seq_first=False)
+    ref = ops.attention_ref(qkv.float(), causal=True, seq_first=False)
+    assert (out.float() - ref).abs().max() < 0.03
+    assert native.status() == 0
