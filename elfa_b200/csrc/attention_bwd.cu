@@ -1,0 +1,374 @@
+// Attention backward on tcgen05, recompute style: only O and the row log-sum-exp are kept by
+// forward; the probabilities are rebuilt per [128 query x 128 key] block.
+//
+//   delta = rowsum(dO * O)                                    (small pre-pass)
+//   per block:  S = Q K^T, dP = dO V^T                         (tensor memory)
+//               P = exp(S*scale - lse), dS = P * (dP - delta) * scale   (registers -> bf16 in smem)
+//   MODE_DKV (CTA owns a key block, loops over query blocks):  dV += P^T dO,  dK += dS^T Q
+//   MODE_DQ  (CTA owns a query block, loops over key blocks):  dQ += dS K
+// Two passes instead of one keep every accumulator in tensor memory and make the result
+// deterministic (no floating-point atomics on dQ).
+//
+// No transposes are materialised: P / dS are written once as [query][key] swizzled tiles and read
+// by the MMAs either K-major (dS K) or MN-major (P^T dO, dS^T Q) through the descriptor only;
+// the same holds for the Q / K / dO tiles.
+//
+// reference: the op is defined by src/futhark/attention.fut:28-51; the reference ships no
+// attention backward at all.
+//
+// Roles per CTA (320 threads): warp 0 TMA, warp 1 MMA issue, warps 2-9 compute (warps w and w+4
+// share a tensor-memory lane quarter and split the 128 key columns in halves).
+#include "common.cuh"
+#include "elfa_native.h"
+
+namespace elfa {
+
+int make_qkv_tmap(CUtensorMap* tm, const void* qkv, int S, int B, int H, int hd, long long stride_s, long long stride_b,
+                  int planes, uint32_t box_rows);
+
+namespace {
+
+constexpr int ATTB_THREADS = 320;
+constexpr int SUBB = 128 * 128;
+
+struct AttnBwdParams {
+  int S, B, H, hd;
+  const float* lse;    // [B, H, S] natural log
+  const float* delta;  // [B, H, S]
+  __nv_bfloat16* dqkv;
+  long long d_stride_s, d_stride_b;
+  float scale, scale_log2;
+  int causal;
+  int n_tiles;
+  unsigned int* status;
+};
+
+enum { BB_RES = 0, BB_INFULL, BB_INFREE, BB_SDP, BB_PDS, BB_ACC, BB_COUNT };
+
+template <int HDP>
+struct BwdSmem {
+  static constexpr int NSUB = HDP / 64;
+  static constexpr int RES0 = 0;
+  static constexpr int RES1 = RES0 + NSUB * SUBB;
+  static constexpr int IN0 = RES1 + NSUB * SUBB;
+  static constexpr int IN1 = IN0 + NSUB * SUBB;
+  static constexpr int P_OFF = IN1 + NSUB * SUBB;
+  static constexpr int DS_OFF = P_OFF + 2 * SUBB;
+  static constexpr int BAR_OFF = DS_OFF + 2 * SUBB;
+  static constexpr int TOTAL = BAR_OFF + BB_COUNT * 8 + 16;
+  static constexpr int DYN = TOTAL + 1024;
+};
+
+// delta[b,h,s] = sum_d dO[s,b,h,d] * O[s,b,h,d]; one warp per (s,b,h).
+__global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                                         long long o_stride_s, long long o_stride_b, float* __restrict__ delta, int S,
+                                                         int B, int H, int hd) {
+  const long long gw = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)S * B * H;
+  if (gw >= total) return;
+  const int h = (int)(gw % H);
+  const int b = (int)((gw / H) % B);
+  const int s = (int)(gw / ((long long)H * B));
+  const long long off = (long long)s * o_stride_s + (long long)b * o_stride_b + (long long)h * hd;
+  float acc = 0.f;
+  for (int v = lane; v < hd / 8; v += 32) {
+    const uint4 a = *reinterpret_cast<const uint4*>(o + off + v * 8);
+    const uint4 d = *reinterpret_cast<const uint4*>(dout + off + v * 8);
+    const uint32_t* pa = reinterpret_cast<const uint32_t*>(&a);
+    const uint32_t* pd = reinterpret_cast<const uint32_t*>(&d);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc += bf16_lo(pa[j]) * bf16_lo(pd[j]) + bf16_hi(pa[j]) * bf16_hi(pd[j]);
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) delta[((long long)b * H + h) * S + s] = acc;
+}
+
+template <int HDP, bool DKV>
+__global__ void __launch_bounds__(ATTB_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO, const AttnBwdParams p) {
+  using L = BwdSmem<HDP>;
+  constexpr int NSUB = L::NSUB;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + BB_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, b = blockIdx.z;
+  // outer tile and the inner range it loops over
+  const int outer = DKV ? (int)blockIdx.x : p.n_tiles - 1 - (int)blockIdx.x;   // heaviest first in both modes
+  const int in_begin = DKV ? (p.causal ? outer : 0) : 0;
+  const int in_end = DKV ? p.n_tiles : (p.causal ? outer + 1 : p.n_tiles);
+  const int n_iter = in_end - in_begin;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmQKV);
+    prefetch_tmap(&tmDO);
+    for (int i = 0; i < BB_COUNT; ++i) mbar_init(bar(i), i == BB_PDS ? 256 : 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t TM_S = tmem_base, TM_DP = tmem_base + 128, TM_ACC0 = tmem_base + 256, TM_ACC1 = tmem_base + 256 + HDP;
+
+  // tile roles: in DKV mode the resident pair is (K_j, V_j) and the inner pair (Q_i, dO_i);
+  // in DQ mode the resident pair is (Q_i, dO_i) and the inner pair (K_j, V_j).
+  const uint32_t sQ = sbase + (DKV ? L::IN0 : L::RES0), sDO = sbase + (DKV ? L::IN1 : L::RES1);
+  const uint32_t sK = sbase + (DKV ? L::RES0 : L::IN0), sV = sbase + (DKV ? L::RES1 : L::IN1);
+  const uint32_t sP = sbase + L::P_OFF, sDS = sbase + L::DS_OFF;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      auto load_qdo = [&](int tile, int bar_id) {
+        for (int s = 0; s < NSUB; ++s) {
+          tma_load_4d(sQ + s * SUBB, &tmQKV, s * 64, 0 * p.H + h, b, tile * 128, bar(bar_id));
+          tma_load_4d(sDO + s * SUBB, &tmDO, s * 64, h, b, tile * 128, bar(bar_id));
+        }
+      };
+      auto load_kv = [&](int tile, int bar_id) {
+        for (int s = 0; s < NSUB; ++s) {
+          tma_load_4d(sK + s * SUBB, &tmQKV, s * 64, 1 * p.H + h, b, tile * 128, bar(bar_id));
+          tma_load_4d(sV + s * SUBB, &tmQKV, s * 64, 2 * p.H + h, b, tile * 128, bar(bar_id));
+        }
+      };
+      mbar_expect_tx(bar(BB_RES), 2 * NSUB * SUBB);
+      if (DKV) load_kv(outer, BB_RES); else load_qdo(outer, BB_RES);
+      for (int it = 0; it < n_iter; ++it) {
+        if (it > 0 && !mbar_wait(bar(BB_INFREE), (it - 1) & 1, abort_flag, p.status)) break;
+        mbar_expect_tx(bar(BB_INFULL), 2 * NSUB * SUBB);
+        if (DKV) load_qdo(in_begin + it, BB_INFULL); else load_kv(in_begin + it, BB_INFULL);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_tt = make_idesc_bf16(128, HDP, true, true);    // P^T dO, dS^T Q
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, HDP, false, true);   // dS K
+      bool ok = mbar_wait(bar(BB_RES), 0, abort_flag, p.status);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const uint32_t ph = it & 1;
+        if (!mbar_wait(bar(BB_INFULL), ph, abort_flag, p.status)) { ok = false; break; }
+        // S / dP of the previous iteration were consumed before BB_PDS completed (waited below)
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < HDP / 16; ++kk) {
+          const uint32_t off = (kk / 4) * SUBB + (kk % 4) * 32;
+          tc_mma_f16(TM_S, make_smem_desc(sQ + off, 16, 1024, 2), make_smem_desc(sK + off, 16, 1024, 2), idesc_s, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HDP / 16; ++kk) {
+          const uint32_t off = (kk / 4) * SUBB + (kk % 4) * 32;
+          tc_mma_f16(TM_DP, make_smem_desc(sDO + off, 16, 1024, 2), make_smem_desc(sV + off, 16, 1024, 2), idesc_s, kk != 0);
+        }
+        tc_commit(bar(BB_SDP));
+        if (!mbar_wait(bar(BB_PDS), ph, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        if (DKV) {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)   // dV[key, d] += sum_q P[q, key] dO[q, d]
+            tc_mma_f16(TM_ACC0, make_smem_desc(sP + kk * 2048, SUBB, 1024, 2), make_smem_desc(sDO + kk * 2048, SUBB, 1024, 2),
+                       idesc_tt, (it | kk) != 0);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)   // dK[key, d] += sum_q dS[q, key] Q[q, d]
+            tc_mma_f16(TM_ACC1, make_smem_desc(sDS + kk * 2048, SUBB, 1024, 2), make_smem_desc(sQ + kk * 2048, SUBB, 1024, 2),
+                       idesc_tt, (it | kk) != 0);
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)   // dQ[q, d] += sum_key dS[q, key] K[key, d]
+            tc_mma_f16(TM_ACC0, make_smem_desc(sDS + (kk / 4) * SUBB + (kk % 4) * 32, 16, 1024, 2),
+                       make_smem_desc(sK + kk * 2048, SUBB, 1024, 2), idesc_dq, (it | kk) != 0);
+        }
+        tc_commit(bar(BB_INFREE));
+      }
+      if (ok) tc_commit(bar(BB_ACC));
+    }
+  } else {
+    // ---------------------------------------------------------------- compute warps
+    const int cw = warp - 2;
+    const int quarter = warp & 3;
+    const int half = cw >> 2;                     // which 64 key columns of the block
+    const int row_local = quarter * 32 + lane;    // query row inside the tile
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const float LOG2E = 1.4426950408889634f;
+    bool ok = true;
+    float lse2 = 0.f, dlt = 0.f;
+    bool row_ok = false;
+    if (!DKV) {
+      const int row = outer * 128 + row_local;
+      row_ok = row < p.S;
+      if (row_ok) {
+        lse2 = p.lse[((long long)b * p.H + h) * p.S + row] * LOG2E;
+        dlt = p.delta[((long long)b * p.H + h) * p.S + row];
+      }
+    }
+    for (int it = 0; it < n_iter; ++it) {
+      const uint32_t ph = it & 1;
+      const int q_tile = DKV ? in_begin + it : outer;
+      const int k_tile = DKV ? outer : in_begin + it;
+      if (DKV) {
+        const int row = q_tile * 128 + row_local;
+        row_ok = row < p.S;
+        lse2 = row_ok ? p.lse[((long long)b * p.H + h) * p.S + row] * LOG2E : 0.f;
+        dlt = row_ok ? p.delta[((long long)b * p.H + h) * p.S + row] : 0.f;
+      }
+      ok = mbar_wait(bar(BB_SDP), ph, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const bool diag = p.causal && q_tile == k_tile;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        const int col0 = half * 64 + c * 32;
+        uint32_t rs[32], rd[32];
+        tmem_ld32(TM_S + lane_addr + col0, rs);
+        tmem_ld32(TM_DP + lane_addr + col0, rd);
+        tmem_ld_wait();
+        float pv[32], dv[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float e = fast_exp2(__uint_as_float(rs[i]) * p.scale_log2 - lse2);
+          if (!row_ok || (diag && col0 + i > row_local)) e = 0.f;
+          pv[i] = e;
+          dv[i] = e * (__uint_as_float(rd[i]) - dlt) * p.scale;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int q8 = (col0 >> 3) + g;
+          const uint32_t off = (q8 >> 3) * SUBB + row_local * 128 + (((q8 & 7) ^ (row_local & 7)) << 4);
+          if (DKV) {
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sP + off), "r"(pack_bf16(pv[g * 8], pv[g * 8 + 1])),
+                         "r"(pack_bf16(pv[g * 8 + 2], pv[g * 8 + 3])), "r"(pack_bf16(pv[g * 8 + 4], pv[g * 8 + 5])),
+                         "r"(pack_bf16(pv[g * 8 + 6], pv[g * 8 + 7]))
+                         : "memory");
+          }
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sDS + off), "r"(pack_bf16(dv[g * 8], dv[g * 8 + 1])),
+                       "r"(pack_bf16(dv[g * 8 + 2], dv[g * 8 + 3])), "r"(pack_bf16(dv[g * 8 + 4], dv[g * 8 + 5])),
+                       "r"(pack_bf16(dv[g * 8 + 6], dv[g * 8 + 7]))
+                       : "memory");
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(bar(BB_PDS));
+    }
+    // ---------------------------------------------------------------- epilogue
+    if (ok) {
+      ok = mbar_wait(bar(BB_ACC), 0, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const int row = outer * 128 + row_local;   // key row (DKV) or query row (DQ)
+      constexpr int CHUNKS = HDP / 32;           // 32-column chunks per accumulator
+      constexpr int NACC = DKV ? 2 : 1;
+      // split the NACC * CHUNKS chunks between the two warps that share this lane quarter
+      for (int idx = half; idx < NACC * CHUNKS; idx += 2) {
+        const int acc = idx / CHUNKS, c = idx % CHUNKS;
+        uint32_t r[32];
+        tmem_ld32((acc == 0 ? TM_ACC0 : TM_ACC1) + lane_addr + c * 32, r);
+        tmem_ld_wait();
+        // DKV: acc 0 = dV (plane 2), acc 1 = dK (plane 1); DQ: dQ (plane 0)
+        const int plane = DKV ? (acc == 0 ? 2 : 1) : 0;
+        if (row < p.S) {
+          __nv_bfloat16* dst = p.dqkv + (long long)row * p.d_stride_s + (long long)b * p.d_stride_b + ((long long)plane * p.H + h) * p.hd;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int d0 = c * 32 + g * 8;
+            if (d0 < p.hd) {
+              uint4 v = make_uint4(pack_bf16(__uint_as_float(r[g * 8]), __uint_as_float(r[g * 8 + 1])),
+                                   pack_bf16(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3])),
+                                   pack_bf16(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5])),
+                                   pack_bf16(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7])));
+              *reinterpret_cast<uint4*>(dst + d0) = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int HDP, bool DKV>
+int launch_attn_bwd(const CUtensorMap& tmQKV, const CUtensorMap& tmDO, const AttnBwdParams& p, cudaStream_t stream) {
+  using L = BwdSmem<HDP>;
+  auto kern = attn_bwd_kernel<HDP, DKV>;
+  static bool configured = false;
+  if (!configured) {
+    ELFA_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
+    configured = true;
+  }
+  dim3 grid(p.n_tiles, p.H, p.B);
+  kern<<<grid, ATTB_THREADS, L::DYN, stream>>>(tmQKV, tmDO, p);
+  ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
+  return ELFA_OK;
+}
+
+}  // namespace
+}  // namespace elfa
+
+using namespace elfa;
+
+// Gradients of attention w.r.t. the fused qkv tensor. `out`/`dout` share strides (o_stride_*),
+// `dqkv` has the layout of qkv with its own strides; `delta` is [B, H, S] fp32 scratch.
+ELFA_API int elfa_attention_bwd(const void* qkv, long long stride_s, long long stride_b, const void* out, const void* dout,
+                                long long o_stride_s, long long o_stride_b, const float* lse, float* delta, void* dqkv,
+                                long long d_stride_s, long long d_stride_b, int S, int B, int H, int hd, float scale, int causal,
+                                void* stream) {
+  ELFA_REQUIRE(qkv && out && dout && lse && delta && dqkv && S > 0 && B > 0 && H > 0, "attention_bwd: bad arguments");
+  ELFA_REQUIRE(hd % 8 == 0 && hd >= 8 && hd <= 128, "attention_bwd: head_dim must be a multiple of 8 in [8, 128]");
+  ELFA_REQUIRE(stride_s % 8 == 0 && stride_b % 8 == 0 && o_stride_s % 8 == 0 && o_stride_b % 8 == 0 && d_stride_s % 8 == 0 &&
+                   d_stride_b % 8 == 0,
+               "attention_bwd: strides must be multiples of 8");
+  unsigned int* st = status_word();
+  ELFA_REQUIRE(st != nullptr, "attention_bwd: no status word");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long long nwarps = (long long)S * B * H;
+  attn_delta_kernel<<<(unsigned)((nwarps + 7) / 8), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(out),
+                                                                 static_cast<const __nv_bfloat16*>(dout), o_stride_s, o_stride_b,
+                                                                 delta, S, B, H, hd);
+  ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
+  CUtensorMap tmQKV, tmDO;
+  int rc = make_qkv_tmap(&tmQKV, qkv, S, B, H, hd, stride_s, stride_b, 3, 128);
+  if (rc != ELFA_OK) return rc;
+  rc = make_qkv_tmap(&tmDO, dout, S, B, H, hd, o_stride_s, o_stride_b, 1, 128);
+  if (rc != ELFA_OK) return rc;
+  AttnBwdParams p{};
+  p.S = S; p.B = B; p.H = H; p.hd = hd;
+  p.lse = lse; p.delta = delta;
+  p.dqkv = static_cast<__nv_bfloat16*>(dqkv);
+  p.d_stride_s = d_stride_s; p.d_stride_b = d_stride_b;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.causal = causal;
+  p.n_tiles = (S + 127) / 128;
+  p.status = st;
+  if (hd <= 64) {
+    rc = launch_attn_bwd<64, true>(tmQKV, tmDO, p, s);
+    if (rc != ELFA_OK) return rc;
+    return launch_attn_bwd<64, false>(tmQKV, tmDO, p, s);
+  }
+  rc = launch_attn_bwd<128, true>(tmQKV, tmDO, p, s);
+  if (rc != ELFA_OK) return rc;
+  return launch_attn_bwd<128, false>(tmQKV, tmDO, p, s);
+}

@@ -287,6 +287,7 @@ int launch_attn_fwd(const CUtensorMap& tm, const AttnFwdParams& p, cudaStream_t 
   dim3 grid((p.n_qtiles + 1) / 2, p.H, p.B);
   kern<<<grid, ATT_THREADS, L::DYN, stream>>>(tm, p);
   ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
   return ELFA_OK;
 }
 

@@ -32,6 +32,7 @@ namespace elfa {
 void set_last_error(const char* msg);
 int cuda_fail(cudaError_t e, const char* what);
 unsigned int* status_word();   // device pointer to this device's status word (lazily created)
+void count_launches(int n);    // bookkeeping: kernels launched by this library (read by elfa_launch_count)
 
 #define ELFA_CUDA(call)                                   \
   do {                                                    \

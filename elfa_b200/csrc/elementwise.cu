@@ -63,10 +63,10 @@ __global__ void __launch_bounds__(256) ew_kernel(const __nv_bfloat16* __restrict
   }
 }
 
-// out[t, :] = tok_emb[ids[t], :] (+ pos_emb[pos0 + t % seq, :])
+// out[t, :] = tok_emb[ids[t], :] (+ pos_emb[pos0 + (t / pos_div) % seq, :]); pos_div = 1 for [B, S] ids, B for [S, B] ids
 __global__ void __launch_bounds__(256) embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ tok,
                                                             const __nv_bfloat16* __restrict__ pos, __nv_bfloat16* __restrict__ out,
-                                                            int tokens, int D, int seq, int pos0, int vocab_lo, int vocab_hi,
+                                                            int tokens, int D, int seq, int pos_div, int pos0, int vocab_lo, int vocab_hi,
                                                             unsigned int* status) {
   const int nvec = D / 8;
   for (int t = blockIdx.x; t < tokens; t += gridDim.x) {
@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(256) embedding_fwd_kernel(const long long* __r
     const bool mine = id >= vocab_lo && id < vocab_hi;
     if (!mine && vocab_lo == 0 && threadIdx.x == 0 && (id < 0 || id >= vocab_hi)) atomicOr(status, (unsigned)ELFA_ST_BAD_TARGET);
     const uint4* tr = reinterpret_cast<const uint4*>(tok + (long long)(mine ? id - vocab_lo : 0) * D);
-    const uint4* pr = pos ? reinterpret_cast<const uint4*>(pos + (long long)(pos0 + t % seq) * D) : nullptr;
+    const uint4* pr = pos ? reinterpret_cast<const uint4*>(pos + (long long)(pos0 + (t / pos_div) % seq) * D) : nullptr;
     uint4* orow = reinterpret_cast<uint4*>(out + (long long)t * D);
     for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
       uint4 a = mine ? tr[v] : make_uint4(0, 0, 0, 0);
@@ -90,17 +90,17 @@ __global__ void __launch_bounds__(256) embedding_fwd_kernel(const long long* __r
   }
 }
 
-// dtok[ids[t], :] += dy[t, :] (fp32 atomics); dpos[pos0 + t % seq, :] += dy[t, :]
+// dtok[ids[t], :] += dy[t, :] (atomics); dpos[pos0 + (t / pos_div) % seq, :] += dy[t, :]
 template <typename GradT>
 __global__ void __launch_bounds__(256) embedding_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ dy,
                                                             GradT* __restrict__ dtok, GradT* __restrict__ dpos, int tokens, int D,
-                                                            int seq, int pos0, int vocab_lo, int vocab_hi) {
+                                                            int seq, int pos_div, int pos0, int vocab_lo, int vocab_hi) {
   for (int t = blockIdx.x; t < tokens; t += gridDim.x) {
     const long long id = ids[t];
     const bool mine = id >= vocab_lo && id < vocab_hi;
     const __nv_bfloat16* g = dy + (long long)t * D;
     GradT* tr = dtok + (long long)(mine ? id - vocab_lo : 0) * D;
-    GradT* pr = (dpos && vocab_lo == 0) ? dpos + (long long)(pos0 + t % seq) * D : nullptr;
+    GradT* pr = (dpos && vocab_lo == 0) ? dpos + (long long)(pos0 + (t / pos_div) % seq) * D : nullptr;
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
       const float v = __bfloat162float(g[c]);
       if (mine) atomicAdd(tr + c, (GradT)v);
@@ -151,6 +151,7 @@ ELFA_API int elfa_elementwise(int op, const void* a, const void* b, void* out, l
     default: set_last_error("elementwise: unknown op"); return ELFA_ERR_ARG;
   }
   ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
   return ELFA_OK;
 }
 
@@ -158,33 +159,35 @@ ELFA_API int elfa_elementwise(int op, const void* a, const void* b, void* out, l
 // `tok` are local to that slice); other tokens give zeros, so a sum over vocabulary-parallel ranks
 // rebuilds the full embedding. Positions are added by the rank with vocab_lo == 0.
 ELFA_API int elfa_embedding_fwd(const long long* ids, const void* tok, const void* pos, void* out, int tokens, int D, int seq,
-                                int pos0, int vocab_lo, int vocab_hi, void* stream) {
-  ELFA_REQUIRE(ids && tok && out && tokens > 0 && D % 8 == 0 && seq > 0, "embedding_fwd: bad arguments");
+                                int pos_div, int pos0, int vocab_lo, int vocab_hi, void* stream) {
+  ELFA_REQUIRE(ids && tok && out && tokens > 0 && D % 8 == 0 && seq > 0 && pos_div > 0, "embedding_fwd: bad arguments");
   unsigned int* st = status_word();
   ELFA_REQUIRE(st != nullptr, "embedding_fwd: no status word");
   const int grid = tokens < 148 * 16 ? tokens : 148 * 16;
   const int threads = D / 8 >= 256 ? 256 : (D / 8 >= 128 ? 128 : 64);
   embedding_fwd_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
       ids, static_cast<const __nv_bfloat16*>(tok), static_cast<const __nv_bfloat16*>(pos), static_cast<__nv_bfloat16*>(out), tokens,
-      D, seq, pos0, vocab_lo, vocab_hi, st);
+      D, seq, pos_div, pos0, vocab_lo, vocab_hi, st);
   ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
   return ELFA_OK;
 }
 
 // Scatter-add of dy into fp32 (grads_f32 = 1) or bf16 gradient tables.
-ELFA_API int elfa_embedding_bwd(const long long* ids, const void* dy, void* dtok, void* dpos, int tokens, int D, int seq, int pos0,
+ELFA_API int elfa_embedding_bwd(const long long* ids, const void* dy, void* dtok, void* dpos, int tokens, int D, int seq, int pos_div, int pos0,
                                 int vocab_lo, int vocab_hi, int grads_f32, void* stream) {
-  ELFA_REQUIRE(ids && dy && dtok && tokens > 0 && seq > 0, "embedding_bwd: bad arguments");
+  ELFA_REQUIRE(ids && dy && dtok && tokens > 0 && seq > 0 && pos_div > 0, "embedding_bwd: bad arguments");
   const int grid = tokens < 148 * 16 ? tokens : 148 * 16;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (grads_f32)
     embedding_bwd_kernel<float><<<grid, 256, 0, s>>>(ids, static_cast<const __nv_bfloat16*>(dy), static_cast<float*>(dtok),
-                                                     static_cast<float*>(dpos), tokens, D, seq, pos0, vocab_lo, vocab_hi);
+                                                     static_cast<float*>(dpos), tokens, D, seq, pos_div, pos0, vocab_lo, vocab_hi);
   else
     embedding_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(ids, static_cast<const __nv_bfloat16*>(dy),
                                                              static_cast<__nv_bfloat16*>(dtok), static_cast<__nv_bfloat16*>(dpos),
-                                                             tokens, D, seq, pos0, vocab_lo, vocab_hi);
+                                                             tokens, D, seq, pos_div, pos0, vocab_lo, vocab_hi);
   ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
   return ELFA_OK;
 }
 
@@ -207,5 +210,6 @@ ELFA_API int elfa_cast(const void* src, int src_type, void* dst, int dst_type, l
     return ELFA_ERR_ARG;
   }
   ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
   return ELFA_OK;
 }

@@ -20,6 +20,7 @@ extern "C" {
 
 const char* elfa_last_error(void);
 int elfa_version(void);
+long long elfa_launch_count(int reset);
 int elfa_status(unsigned int* out);
 int elfa_device_info(int device, long long* out6);
 int elfa_is_blackwell(int device);
@@ -41,9 +42,9 @@ int elfa_norm_bwd(const void* dy, const void* x, const void* w, const float* mea
 
 // ---- elementwise.cu ----------------------------------------------------------------------------
 int elfa_elementwise(int op, const void* a, const void* b, void* out, long long n, float alpha, void* stream);
-int elfa_embedding_fwd(const long long* ids, const void* tok, const void* pos, void* out, int tokens, int D, int seq, int pos0,
+int elfa_embedding_fwd(const long long* ids, const void* tok, const void* pos, void* out, int tokens, int D, int seq, int pos_div, int pos0,
                        int vocab_lo, int vocab_hi, void* stream);
-int elfa_embedding_bwd(const long long* ids, const void* dy, void* dtok, void* dpos, int tokens, int D, int seq, int pos0,
+int elfa_embedding_bwd(const long long* ids, const void* dy, void* dtok, void* dpos, int tokens, int D, int seq, int pos_div, int pos0,
                        int vocab_lo, int vocab_hi, int grads_f32, void* stream);
 int elfa_cast(const void* src, int src_type, void* dst, int dst_type, long long n, float scale, void* stream);
 
@@ -70,6 +71,21 @@ int elfa_muon_apply(void* param, int param_type, float* master, const void* y, l
 // ---- attention_fwd.cu --------------------------------------------------------------------------
 int elfa_attention_fwd(const void* qkv, long long stride_s, long long stride_b, void* out, long long o_stride_s,
                        long long o_stride_b, float* lse, int S, int B, int H, int hd, float scale, int causal, void* stream);
+
+// ---- attention_bwd.cu --------------------------------------------------------------------------
+int elfa_attention_bwd(const void* qkv, long long stride_s, long long stride_b, const void* out, const void* dout,
+                       long long o_stride_s, long long o_stride_b, const float* lse, float* delta, void* dqkv,
+                       long long d_stride_s, long long d_stride_b, int S, int B, int H, int hd, float scale, int causal,
+                       void* stream);
+
+// ---- quant.cu ----------------------------------------------------------------------------------
+int elfa_mxfp8_fake_quant(const void* x, void* out, int rows, int cols, int axis, void* stream);
+int elfa_mxfp8_quantize(const void* x, void* payload, void* scales, int rows, int cols, void* stream);
+int elfa_nvfp4_fake_quant(const void* x, void* out, int rows, int cols, int axis, const float* tensor_amax, void* stream);
+int elfa_amax(const void* x, long long n, float* out, void* stream);
+int elfa_fp8_tensor_fake_quant(const void* x, void* out, long long n, const float* scale, int fmt, void* stream);
+int elfa_int_affine_fake_quant(const void* x, void* out, long long n, int bits, float* minmax, float* part, void* stream);
+int elfa_qat_surrogate_bwd(const void* x, const void* g, void* out, long long n, int mode, float p0, float p1, void* stream);
 
 #ifdef __cplusplus
 }

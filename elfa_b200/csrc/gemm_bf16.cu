@@ -358,6 +358,7 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, in
   int grid = tiles < max_ctas ? tiles : max_ctas;
   kern<<<grid, GEMM_THREADS, L::DYN, stream>>>(tmA, tmB, p);
   ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
   return ELFA_OK;
 }
 

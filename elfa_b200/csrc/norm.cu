@@ -261,6 +261,7 @@ ELFA_API int elfa_norm_fwd(const void* x, const void* res, const void* w, const 
   }
 #undef LAUNCH_FWD
   ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
   return ELFA_OK;
 }
 
@@ -303,5 +304,6 @@ ELFA_API int elfa_norm_bwd(const void* dy, const void* x, const void* w, const f
       reduce_partials_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(db_part, static_cast<__nv_bfloat16*>(db), P, D, accumulate);
   }
   ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(3);
   return ELFA_OK;
 }

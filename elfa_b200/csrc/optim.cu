@@ -211,6 +211,7 @@ ELFA_API int elfa_sumsq(const void* grad, int grad_type, long long n, float* par
   else sumsq_kernel<__nv_bfloat16><<<g, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(grad), n, part);
   sumsq_finish_kernel<<<1, 256, 0, s>>>(part, g, static_cast<StepScalars*>(scalars), accumulate);
   ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(2);
   return ELFA_OK;
 }
 
@@ -220,6 +221,7 @@ ELFA_API int elfa_clip_coef(void* scalars, float max_norm, float inv_loss_scale,
   ELFA_REQUIRE(st != nullptr, "clip_coef: no status word");
   clip_coef_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<StepScalars*>(scalars), max_norm, inv_loss_scale, st);
   ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
   return ELFA_OK;
 }
 
@@ -239,6 +241,7 @@ ELFA_API int elfa_adamw(void* param, int param_type, float* master, float* m, fl
   else ADAMW(__nv_bfloat16, __nv_bfloat16);
 #undef ADAMW
   ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
   return ELFA_OK;
 }
 
@@ -255,6 +258,7 @@ ELFA_API int elfa_lion(void* param, int param_type, float* master, float* m, con
   else LION(__nv_bfloat16, __nv_bfloat16);
 #undef LION
   ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
   return ELFA_OK;
 }
 
@@ -269,6 +273,7 @@ ELFA_API int elfa_muon_momentum(float* m, const void* grad, int grad_type, void*
   else muon_momentum_kernel<__nv_bfloat16><<<g, 256, 0, s>>>(m, static_cast<const __nv_bfloat16*>(grad), static_cast<__nv_bfloat16*>(y), n, beta, sc, part);
   muon_normalize_kernel<<<g, 256, 0, s>>>(static_cast<__nv_bfloat16*>(y), n, part, g, norm_out);
   ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(2);
   return ELFA_OK;
 }
 
@@ -276,6 +281,7 @@ ELFA_API int elfa_three_i_minus(void* g, int d, void* stream) {
   ELFA_REQUIRE(g && d > 0, "three_i_minus: bad arguments");
   three_i_minus_kernel<<<flat_grid((long long)d * d), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<__nv_bfloat16*>(g), d);
   ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
   return ELFA_OK;
 }
 
@@ -288,5 +294,6 @@ ELFA_API int elfa_muon_apply(void* param, int param_type, float* master, const v
   if (param_type == 0) muon_apply_kernel<float><<<g, 256, 0, s>>>(static_cast<float*>(param), master, static_cast<const __nv_bfloat16*>(y), n, lr, sc);
   else muon_apply_kernel<__nv_bfloat16><<<g, 256, 0, s>>>(static_cast<__nv_bfloat16*>(param), master, static_cast<const __nv_bfloat16*>(y), n, lr, sc);
   ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
   return ELFA_OK;
 }

@@ -3,6 +3,7 @@
 // Native counterpart of the reference's CUDA runtime shim (reference: src/runtime/cuda.zig:283-507,
 // src/cuda_bindings.zig:14-135): PyTorch owns contexts and streams, this file adds what the
 // kernels need beyond that.
+#include <atomic>
 #include <mutex>
 #include <string>
 #include <unordered_map>
@@ -17,6 +18,9 @@ int cuda_fail(cudaError_t e, const char* what) {
   g_last_error = std::string(what) + ": " + cudaGetErrorString(e);
   return ELFA_ERR_CUDA;
 }
+
+static std::atomic<long long> g_launches{0};
+void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 static std::mutex g_mu;
 static unsigned int* g_status[64] = {nullptr};
@@ -40,6 +44,13 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 static EncodeTiledFn g_encode = nullptr;
 
 static EncodeTiledFn get_encode() {
+  // The driver call needs a current context on the calling thread; autograd worker threads may
+  // not have bound the primary context yet. cudaFree(0) binds it (once per thread).
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(0);
+    ctx_bound = true;
+  }
   if (g_encode) return g_encode;
   void* fn = nullptr;
   cudaDriverEntryPointQueryResult q;
@@ -115,6 +126,13 @@ using namespace elfa;
 ELFA_API const char* elfa_last_error() { return g_last_error.c_str(); }
 
 ELFA_API int elfa_version() { return 100; }
+
+// Number of kernels this library has launched in this process (optionally reset).
+ELFA_API long long elfa_launch_count(int reset) {
+  long long v = g_launches.load();
+  if (reset) g_launches.store(0);
+  return v;
+}
 
 // Reads and clears the status word of the current device (synchronises the device).
 ELFA_API int elfa_status(unsigned int* out) {

@@ -144,6 +144,7 @@ ELFA_API int elfa_xent_stats(const void* logits, long long ld, const long long* 
   xent_stats_kernel<<<rows, XENT_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(logits), ld, targets, reinterpret_cast<RowStat*>(stats), V, vocab_lo, vocab_total, st);
   ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
   return ELFA_OK;
 }
 
@@ -159,5 +160,6 @@ ELFA_API int elfa_xent_grad(void* logits, long long ld, void* dlogits, long long
       static_cast<__nv_bfloat16*>(logits), ld, static_cast<__nv_bfloat16*>(dlogits), ldd, targets,
       reinterpret_cast<const RowStat*>(stats), nslices, rows, loss_out, V, vocab_lo, vocab_total, smoothing, grad_scale_ptr, grad_scale);
   ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
   return ELFA_OK;
 }

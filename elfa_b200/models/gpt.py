@@ -163,12 +163,13 @@ class GPTModel(nn.Module):
         Full (unsharded) tensors are drawn from one generator and sliced, so a TP run starts from
         the same weights as a single-GPU run."""
         m, tp, r = self.cfg.model, self.pc.tp_size, self.pc.tp_rank
-        g = torch.Generator(device="cpu").manual_seed(seed)
+        dev = self.embed_tokens.device
+        g = torch.Generator(device=dev).manual_seed(seed)
         std = self.cfg.bench.init_std
         D = m.hidden_dim
 
         def draw(shape, sigma):
-            return torch.randn(shape, generator=g, dtype=torch.float32) * sigma
+            return torch.randn(shape, generator=g, dtype=torch.float32, device=dev) * sigma
 
         def put(p, full):
             with torch.no_grad():

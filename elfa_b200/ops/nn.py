@@ -215,10 +215,13 @@ def gelu(x):
 # ---------------------------------------------------------------------------------------- embedding
 class _Embedding(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, ids, tok, pos, pos0, vocab_lo):
-        B, T = ids.shape
+    def forward(ctx, ids, tok, pos, pos0, vocab_lo, seq_first):
+        if seq_first:
+            T, B = ids.shape
+        else:
+            B, T = ids.shape
         D = tok.shape[1]
-        ctx.args = (B, T, D, pos0, vocab_lo, tok.shape[0], pos is not None)
+        ctx.args = (B, T, D, pos0, vocab_lo, tok.shape[0], pos is not None, seq_first)
         ctx.tok_ref, ctx.pos_ref = tok, pos
         ctx.save_for_backward(ids)
         if not tok.is_cuda:
@@ -226,17 +229,18 @@ class _Embedding(torch.autograd.Function):
             mask = (local >= 0) & (local < tok.shape[0])
             out = tok[local.clamp(0, tok.shape[0] - 1)] * mask.unsqueeze(-1).to(tok.dtype)
             if pos is not None and vocab_lo == 0:
-                out = out + pos[pos0:pos0 + T].unsqueeze(0)
+                out = out + pos[pos0:pos0 + T].unsqueeze(1 if seq_first else 0)
             return out
         idc = ids.contiguous().view(-1)
-        out = torch.empty((B, T, D), dtype=tok.dtype, device=tok.device)
-        lib.call("elfa_embedding_fwd", idc, tok, pos, out, B * T, D, T, pos0, vocab_lo, vocab_lo + tok.shape[0], stream_ptr(out))
+        out = torch.empty((*ids.shape, D), dtype=tok.dtype, device=tok.device)
+        lib.call("elfa_embedding_fwd", idc, tok, pos, out, B * T, D, T, B if seq_first else 1, pos0, vocab_lo,
+                 vocab_lo + tok.shape[0], stream_ptr(out))
         return out
 
     @staticmethod
     def backward(ctx, dy):
         (ids,) = ctx.saved_tensors
-        B, T, D, pos0, vocab_lo, vloc, has_pos = ctx.args
+        B, T, D, pos0, vocab_lo, vloc, has_pos, seq_first = ctx.args
         tok, pos = ctx.tok_ref, ctx.pos_ref
         if not dy.is_cuda:
             local = (ids - vocab_lo).view(-1)
@@ -247,9 +251,9 @@ class _Embedding(torch.autograd.Function):
             if has_pos:
                 dpos = torch.zeros_like(pos, dtype=torch.float32)
                 if vocab_lo == 0:
-                    dpos[pos0:pos0 + T] = dy.float().sum(0)
+                    dpos[pos0:pos0 + T] = dy.float().sum(1 if seq_first else 0)
                 dpos = dpos.to(pos.dtype)
-            return None, dtok.to(tok.dtype), dpos, None, None
+            return None, dtok.to(tok.dtype), dpos, None, None, None
         dyc = dy.contiguous()
         idc = ids.contiguous().view(-1)
         tt = _grad_target(tok)
@@ -269,20 +273,20 @@ class _Embedding(torch.autograd.Function):
                     dpos_buf.zero_()
             else:
                 dpos_buf = dpos_ret = torch.zeros(pos.shape, dtype=torch.float32, device=dy.device)
-        lib.call("elfa_embedding_bwd", idc, dyc, dtok_buf, dpos_buf, B * T, D, T, pos0, vocab_lo, vocab_lo + vloc, 1,
-                 stream_ptr(dyc))
+        lib.call("elfa_embedding_bwd", idc, dyc, dtok_buf, dpos_buf, B * T, D, T, B if seq_first else 1, pos0, vocab_lo,
+                 vocab_lo + vloc, 1, stream_ptr(dyc))
         if dtok_ret is not None:
             dtok_ret = dtok_ret.to(tok.dtype)
         if dpos_ret is not None:
             dpos_ret = dpos_ret.to(pos.dtype)
-        return None, dtok_ret, dpos_ret, None, None
+        return None, dtok_ret, dpos_ret, None, None, None
 
 
 def embedding(ids: torch.Tensor, tok: torch.Tensor, pos: Optional[torch.Tensor] = None, pos0: int = 0,
-              vocab_lo: int = 0) -> torch.Tensor:
+              vocab_lo: int = 0, seq_first: bool = False) -> torch.Tensor:
     """``tok[ids - vocab_lo] (+ pos[pos0 + t])`` for ids inside this rank's vocabulary slice, zeros
     for the others (summing over vocabulary-parallel ranks gives the full embedding)."""
-    return _Embedding.apply(ids, tok, pos, pos0, vocab_lo)
+    return _Embedding.apply(ids, tok, pos, pos0, vocab_lo, seq_first)
 
 
 # ------------------------------------------------------------------------------------ cross-entropy

@@ -1,0 +1,129 @@
+"""Flat parameter / gradient buffers.
+
+All parameters of a rank live in one contiguous buffer (model dtype) and all gradients in one fp32
+buffer of the same layout; ``param.main_grad`` is the parameter's view into the gradient buffer and
+the backward kernels accumulate into it directly (weight-gradient GEMM epilogue, norm backward,
+embedding scatter-add). One contiguous layout is what lets the optimizer be a handful of kernel
+launches and lets ZeRO shard optimizer state by plain index ranges:
+
+    [ TP-replicated params | TP-sharded params ]  each part ordered (decay, no-decay)
+
+* the TP-replicated prefix is the only region whose gradients need an all-reduce over the tensor
+  parallel group (norm weights, position embeddings);
+* ZeRO-1/2 give data-parallel rank ``r`` the slice ``[r * shard, (r+1) * shard)`` of the whole
+  buffer (the buffer is padded to a multiple of ``dp * 1024`` elements).
+
+reference: per-tensor ``len / num_gpus`` shards (``src/distributed/zero_sharding.zig:73-113``) and
+the 1 MiB round-robin ownership rule (``src/tensor/sharding.zig:331-342``); a flat range per rank
+replaces both because one kernel can then reduce, update and re-broadcast a whole bucket.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import torch
+
+ALIGN = 64          # elements; keeps every parameter 128-byte aligned in bf16 (TMA needs 16 bytes)
+
+
+@dataclass
+class Segment:
+    start: int
+    end: int
+    weight_decay: bool
+    replicated: bool
+
+
+class FlatParams:
+    def __init__(self, named_params: Iterable[Tuple[str, torch.nn.Parameter]], dp_size: int = 1, dp_rank: int = 0,
+                 grad_dtype: torch.dtype = torch.float32, allocator=None):
+        items = []
+        seen = set()
+        for name, p in named_params:
+            if id(p) in seen or not p.requires_grad:
+                continue
+            seen.add(id(p))
+            items.append((name, p))
+        if not items:
+            raise ValueError("no trainable parameters")
+        # stable sort: replicated first, then decay before no-decay
+        def key(it):
+            p = it[1]
+            return (0 if getattr(p, "tp_replicated", False) else 1, 1 if getattr(p, "no_decay", False) or p.dim() < 2 else 0)
+        items.sort(key=key)
+        self.names = [n for n, _ in items]
+        self.params = [p for _, p in items]
+        self.dtype = self.params[0].dtype
+        self.device = self.params[0].device
+        self.dp_size, self.dp_rank = dp_size, dp_rank
+        offsets, off = [], 0
+        for p in self.params:
+            offsets.append(off)
+            off += (p.numel() + ALIGN - 1) // ALIGN * ALIGN
+        quantum = dp_size * 1024
+        self.numel = (off + quantum - 1) // quantum * quantum
+        self.offsets = offsets
+        alloc = allocator or (lambda n, dt: torch.zeros(n, dtype=dt, device=self.device))
+        self.flat = alloc(self.numel, self.dtype)
+        self.grads = alloc(self.numel, grad_dtype)
+        self.flat.zero_()
+        self.grads.zero_()
+        self.segments: List[Segment] = []
+        for p, o in zip(self.params, offsets):
+            n = p.numel()
+            view = self.flat[o:o + n].view(p.shape)
+            with torch.no_grad():
+                view.copy_(p.data)
+            p.data = view
+            p.main_grad = self.grads[o:o + n].view(p.shape)
+            p._grad_fresh = False
+            k = key(("", p))
+            seg_end = o + (n + ALIGN - 1) // ALIGN * ALIGN
+            if self.segments and self.segments[-1].replicated == (k[0] == 0) and self.segments[-1].weight_decay == (k[1] == 0):
+                self.segments[-1].end = seg_end
+            else:
+                self.segments.append(Segment(o, seg_end, k[1] == 0, k[0] == 0))
+        self.segments[-1].end = self.numel
+        self.replicated_end = max((s.end for s in self.segments if s.replicated), default=0)
+        self.shard_size = self.numel // dp_size
+        self.shard_lo = dp_rank * self.shard_size
+        self.shard_hi = self.shard_lo + self.shard_size
+
+    # ------------------------------------------------------------------
+    def zero_grad(self) -> None:
+        self.grads.zero_()
+        for p in self.params:
+            p.grad = None
+
+    def fold_autograd_grads(self) -> None:
+        """Adds gradients that autograd left in ``p.grad`` (ops without a fused accumulate, CPU
+        runs) into the flat buffer."""
+        for p in self.params:
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.to(p.main_grad.dtype))
+                p.grad = None
+
+    def param_view(self, i: int) -> torch.Tensor:
+        return self.params[i].data
+
+    def grad_view(self, i: int) -> torch.Tensor:
+        return self.params[i].main_grad
+
+    def wd_ranges(self, lo: Optional[int] = None, hi: Optional[int] = None) -> List[Tuple[int, int, bool]]:
+        """Maximal ``(start, end, weight_decay)`` runs clipped to ``[lo, hi)``."""
+        lo = 0 if lo is None else lo
+        hi = self.numel if hi is None else hi
+        out: List[Tuple[int, int, bool]] = []
+        for s in self.segments:
+            a, b = max(s.start, lo), min(s.end, hi)
+            if a >= b:
+                continue
+            if out and out[-1][2] == s.weight_decay and out[-1][1] == a:
+                out[-1] = (out[-1][0], b, s.weight_decay)
+            else:
+                out.append((a, b, s.weight_decay))
+        return out
+
+    def param_slices(self) -> Dict[str, Tuple[int, int]]:
+        return {n: (o, o + p.numel()) for n, p, o in zip(self.names, self.params, self.offsets)}

@@ -1,0 +1,400 @@
+"""AdamW, Lion, Muon and the Lion+Muon router on flat buffers, with ZeRO-1/2 sharding of the
+optimizer state over the data-parallel group.
+
+Math (reference): Lion ``v = b1*m + (1-b1)*g; m = b2*m + (1-b2)*g; p = p*(1 - lr*wd) - lr*sign(v)``
+(``kernels/cuda/optim.cu:125-146``; CPU form ``src/optim/optimizer.zig:111-143``); AdamW
+bias-corrected with decoupled decay ``p -= lr*(m_hat/(sqrt(v_hat)+eps) + wd*p)``
+(``src/kernels/optim_kernels.zig:129-167``); Muon ``m = beta*m + g; Y = m/||m||_F;
+Y <- 0.5*Y*(3I - Y^T Y)`` x ``iters`` on the smaller Gram side, ``p -= lr*Y``, no decay
+(``src/optim/optimizer.zig:246-320``, ``kernels/cuda/optim.cu:378-398``); routing ``ndim == 2 →
+Muon, else Lion`` (``optimizer.zig:361-369``). Moments and master weights are fp32 (the reference's
+CUDA kernels keep bf16 moments).
+
+One optimizer step on CUDA is: [DP reduce] → sum of squares → clip coefficient / non-finite guard
+on the device → update kernels (which skip themselves when the guard fired) → [DP all-gather].
+Nothing in the step reads back to the host.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..native import lib, stream_ptr
+from ..ops.gemm import gemm
+from ..parallel.mesh import ParallelContext
+from .flat import FlatParams
+
+
+def _ptype(t: torch.Tensor) -> int:
+    return 0 if t.dtype == torch.float32 else 1
+
+
+class _Base:
+    """Common state: flat buffers, DP sharding, clipping scalars."""
+
+    def __init__(self, flat: FlatParams, pc: Optional[ParallelContext], zero_stage: int, lr: float, weight_decay: float,
+                 max_grad_norm: float):
+        self.flat, self.pc = flat, pc or ParallelContext()
+        self.zero_stage = zero_stage if self.pc.dp_size > 1 else 0
+        self.lr, self.weight_decay, self.max_grad_norm = lr, weight_decay, max_grad_norm
+        self.step_count = 0
+        self.loss_scale = 1.0
+        dev = flat.device
+        self.sharded = self.zero_stage >= 1
+        self.lo, self.hi = (flat.shard_lo, flat.shard_hi) if self.sharded else (0, flat.numel)
+        n = self.hi - self.lo
+        self.master_is_param = flat.dtype == torch.float32
+        self.master = flat.flat[self.lo:self.hi] if self.master_is_param else flat.flat[self.lo:self.hi].float()
+        self.scalars = torch.zeros(4, dtype=torch.float32, device=dev)     # sumsq, clip_coef, grad_norm, skip
+        self.part = torch.zeros(4096, dtype=torch.float32, device=dev)
+        self.n_local = n
+        self.last_grad_norm = 0.0
+
+    # --------------------------------------------------------------- gradient synchronisation
+    def reduce_gradients(self) -> None:
+        """TP: all-reduce the replicated prefix. DP: all-reduce (ZeRO-0) or reduce-scatter
+        (ZeRO>=1) the whole buffer; gradients are averaged over DP."""
+        pc, f = self.pc, self.flat
+        if pc.tp_size > 1 and f.replicated_end > 0:
+            dist.all_reduce(f.grads[:f.replicated_end], group=pc.tp_group)
+        if pc.dp_size > 1:
+            if self.sharded and f.grads.is_cuda:
+                shard = f.grads[self.lo:self.hi]
+                dist.reduce_scatter_tensor(shard, f.grads, op=dist.ReduceOp.AVG, group=pc.dp_group)
+            else:
+                dist.all_reduce(f.grads, group=pc.dp_group)
+                f.grads.div_(pc.dp_size)
+
+    def gather_params(self) -> None:
+        if self.sharded:
+            f, pc = self.flat, self.pc
+            if f.flat.is_cuda:
+                dist.all_gather_into_tensor(f.flat, f.flat[self.lo:self.hi], group=pc.dp_group)
+            else:
+                parts = [torch.empty_like(f.flat[self.lo:self.hi]) for _ in range(pc.dp_size)]
+                dist.all_gather(parts, f.flat[self.lo:self.hi].contiguous(), group=pc.dp_group)
+                f.flat.copy_(torch.cat(parts))
+
+    # --------------------------------------------------------------------------- norm / clip
+    def _norm_and_clip(self) -> None:
+        """Fills ``self.scalars`` (device). The squared norm counts TP-replicated gradients once."""
+        f, pc = self.flat, self.pc
+        g = f.grads[self.lo:self.hi]
+        inv_scale = 1.0 / self.loss_scale
+        if g.is_cuda:
+            st = stream_ptr(g)
+            distributed = (pc.tp_size > 1) or self.sharded
+            if not distributed:
+                lib.call("elfa_sumsq", g, _ptype(g), g.numel(), self.part, self.scalars, 0, st)
+            else:
+                # replicated prefix counted on tp_rank 0 only
+                rep_hi = min(max(f.replicated_end, self.lo), self.hi)
+                self.scalars[0].zero_()
+                acc = 0
+                if rep_hi > self.lo and pc.tp_rank == 0:
+                    lib.call("elfa_sumsq", f.grads[self.lo:rep_hi], _ptype(g), rep_hi - self.lo, self.part, self.scalars, 0, st)
+                    acc = 1
+                if self.hi > rep_hi:
+                    lib.call("elfa_sumsq", f.grads[rep_hi:self.hi], _ptype(g), self.hi - rep_hi, self.part, self.scalars, acc, st)
+                dist.all_reduce(self.scalars[0:1], group=None if self.sharded else pc.tp_group)
+            lib.call("elfa_clip_coef", self.scalars, float(self.max_grad_norm), float(inv_scale), st)
+            return
+        # CPU
+        sq = float(g.double().pow(2).sum())
+        if pc.tp_size > 1 or self.sharded:
+            rep_hi = min(max(f.replicated_end, self.lo), self.hi)
+            sq = float(f.grads[rep_hi:self.hi].double().pow(2).sum())
+            if pc.tp_rank == 0:
+                sq += float(f.grads[self.lo:rep_hi].double().pow(2).sum())
+            t = torch.tensor([sq], dtype=torch.float64)
+            dist.all_reduce(t, group=None if self.sharded else pc.tp_group)
+            sq = float(t)
+        norm = (sq ** 0.5) * inv_scale
+        finite = norm == norm and norm != float("inf")
+        coef = 1.0
+        if finite and self.max_grad_norm > 0 and norm > self.max_grad_norm and norm > 1e-8:
+            coef = self.max_grad_norm / norm
+        self.scalars[0], self.scalars[1], self.scalars[2], self.scalars[3] = sq, coef * inv_scale if finite else 0.0, norm, 0.0 if finite else 1.0
+
+    def grad_norm(self) -> float:
+        """Host read of the last step's (unscaled, pre-clip) gradient norm."""
+        return float(self.scalars[2])
+
+    def skipped(self) -> bool:
+        return bool(self.scalars[3] != 0)
+
+    # ------------------------------------------------------------------------------ stepping
+    def step(self, lr: Optional[float] = None) -> None:
+        if lr is not None:
+            self.lr = lr
+        self.flat.fold_autograd_grads()
+        self.reduce_gradients()
+        self._norm_and_clip()
+        self.step_count += 1
+        self._update()
+        self.gather_params()
+        from ..quant.qat import new_weight_epoch
+        new_weight_epoch()
+
+    def zero_grad(self) -> None:
+        self.flat.zero_grad()
+
+    def _update(self) -> None:
+        raise NotImplementedError
+
+    def _param_out(self):
+        """(tensor, type) of the working-precision copy to write, or (None, 0) when the master
+        weights are the parameters themselves."""
+        if self.master_is_param:
+            return None, 0
+        return self.flat.flat[self.lo:self.hi], 1
+
+    # ---------------------------------------------------------------------------- checkpoint
+    def state_tensors(self) -> Dict[str, torch.Tensor]:
+        raise NotImplementedError
+
+    def state_dict(self) -> Dict[str, object]:
+        return {"step": self.step_count, "lr": self.lr, "lo": self.lo, "hi": self.hi,
+                "tensors": {k: v.detach().cpu() for k, v in self.state_tensors().items()}}
+
+    def load_state_dict(self, sd) -> None:
+        self.step_count = int(sd["step"])
+        for k, v in self.state_tensors().items():
+            v.copy_(sd["tensors"][k].to(v.device))
+
+
+class AdamW(_Base):
+    def __init__(self, flat, pc=None, zero_stage=0, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, max_grad_norm=1.0):
+        super().__init__(flat, pc, zero_stage, lr, weight_decay, max_grad_norm)
+        self.betas, self.eps = betas, eps
+        self.m = torch.zeros(self.n_local, dtype=torch.float32, device=flat.device)
+        self.v = torch.zeros(self.n_local, dtype=torch.float32, device=flat.device)
+
+    def _update(self) -> None:
+        f = self.flat
+        b1, b2 = self.betas
+        pout, ptype = self._param_out()
+        for a, b, wd in f.wd_ranges(self.lo, self.hi):
+            s, e = a - self.lo, b - self.lo
+            g = f.grads[a:b]
+            wdv = self.weight_decay if wd else 0.0
+            if g.is_cuda:
+                lib.call("elfa_adamw", pout[s:e] if pout is not None else None, ptype, self.master[s:e], self.m[s:e], self.v[s:e], g,
+                         _ptype(g), e - s, float(self.lr), float(b1), float(b2), float(self.eps), float(wdv), self.step_count,
+                         self.scalars, stream_ptr(g))
+            else:
+                if self.skipped():
+                    continue
+                gg = g.float() * float(self.scalars[1])
+                m, v, p = self.m[s:e], self.v[s:e], self.master[s:e]
+                m.mul_(b1).add_(gg, alpha=1 - b1)
+                v.mul_(b2).addcmul_(gg, gg, value=1 - b2)
+                mh = m / (1 - b1 ** self.step_count)
+                vh = v / (1 - b2 ** self.step_count)
+                p.sub_(self.lr * (mh / (vh.sqrt() + self.eps) + wdv * p))
+                if pout is not None:
+                    pout[s:e].copy_(p.to(pout.dtype))
+
+    def state_tensors(self):
+        d = {"m": self.m, "v": self.v}
+        if not self.master_is_param:
+            d["master"] = self.master
+        return d
+
+
+class Lion(_Base):
+    def __init__(self, flat, pc=None, zero_stage=0, lr=1e-4, betas=(0.95, 0.98), weight_decay=0.1, max_grad_norm=1.0,
+                 ranges=None):
+        super().__init__(flat, pc, zero_stage, lr, weight_decay, max_grad_norm)
+        self.betas = betas
+        self.m = torch.zeros(self.n_local, dtype=torch.float32, device=flat.device)
+        self.ranges = ranges      # optional list of (start, end, wd) restricting the update (Lion+Muon)
+
+    def _update(self) -> None:
+        f = self.flat
+        b1, b2 = self.betas
+        pout, ptype = self._param_out()
+        rngs = self.ranges if self.ranges is not None else f.wd_ranges(self.lo, self.hi)
+        for a, b, wd in rngs:
+            a, b = max(a, self.lo), min(b, self.hi)
+            if a >= b:
+                continue
+            s, e = a - self.lo, b - self.lo
+            g = f.grads[a:b]
+            wdv = self.weight_decay if wd else 0.0
+            if g.is_cuda:
+                lib.call("elfa_lion", pout[s:e] if pout is not None else None, ptype, self.master[s:e], self.m[s:e], g, _ptype(g),
+                         e - s, float(self.lr), float(b1), float(b2), float(wdv), self.scalars, stream_ptr(g))
+            else:
+                if self.skipped():
+                    continue
+                gg = g.float() * float(self.scalars[1])
+                m, p = self.m[s:e], self.master[s:e]
+                u = b1 * m + (1 - b1) * gg
+                p.mul_(1 - self.lr * wdv).sub_(self.lr * torch.sign(u))
+                m.mul_(b2).add_(gg, alpha=1 - b2)
+                if pout is not None:
+                    pout[s:e].copy_(p.to(pout.dtype))
+
+    def state_tensors(self):
+        d = {"m": self.m}
+        if not self.master_is_param:
+            d["master"] = self.master
+        return d
+
+
+def newton_schulz(y: torch.Tensor, iters: int) -> torch.Tensor:
+    """``Y <- 0.5 * Y (3I - Y^T Y)`` (or the left form when rows < cols) for a Frobenius-normalised
+    matrix. CUDA bf16 matrices run on the tcgen05 GEMM with the 0.5 folded into ``alpha``."""
+    rows, cols = y.shape
+    right = cols <= rows
+    if not y.is_cuda:
+        yf = y.float()
+        for _ in range(iters):
+            if right:
+                g = 3 * torch.eye(cols) - yf.t() @ yf
+                yf = 0.5 * yf @ g
+            else:
+                g = 3 * torch.eye(rows) - yf @ yf.t()
+                yf = 0.5 * g @ yf
+        return yf.to(y.dtype)
+    st = stream_ptr(y)
+    for _ in range(iters):
+        if right:
+            g = gemm(y, y, a_mn=True, b_mn=True)                 # Y^T Y  [cols, cols]
+            lib.call("elfa_three_i_minus", g, cols, st)
+            y = gemm(y, g, b_mn=True, alpha=0.5)                 # Y G
+        else:
+            g = gemm(y, y)                                       # Y Y^T  [rows, rows]
+            lib.call("elfa_three_i_minus", g, rows, st)
+            y = gemm(g, y, b_mn=True, alpha=0.5)                 # G Y
+    return y
+
+
+class Muon(_Base):
+    """Momentum + Newton-Schulz orthogonalisation for the 2-D parameters listed in ``indices``."""
+
+    def __init__(self, flat, pc=None, zero_stage=0, lr=1e-4, momentum=0.95, iterations=5, max_grad_norm=1.0, indices=None):
+        super().__init__(flat, pc, 0, lr, 0.0, max_grad_norm)      # matrices are updated whole: no state sharding
+        self.momentum, self.iterations = momentum, iterations
+        self.indices = list(range(len(flat.params))) if indices is None else list(indices)
+        self.m = torch.zeros(flat.numel, dtype=torch.float32, device=flat.device)
+
+    def _update(self) -> None:
+        f = self.flat
+        for i in self.indices:
+            p = f.params[i]
+            o, n = f.offsets[i], p.numel()
+            g = f.grads[o:o + n]
+            m = self.m[o:o + n]
+            master = self.master[o:o + n]
+            rows, cols = p.shape[0], p.numel() // p.shape[0]
+            if g.is_cuda:
+                st = stream_ptr(g)
+                y = torch.empty(n, dtype=torch.bfloat16, device=g.device)
+                lib.call("elfa_muon_momentum", m, g, _ptype(g), y, n, float(self.momentum), self.scalars, self.part, None, st)
+                ok = rows % 8 == 0 and cols % 8 == 0
+                y2 = newton_schulz(y.view(rows, cols), self.iterations) if ok else \
+                    newton_schulz(y.view(rows, cols).float().cpu(), self.iterations).to(g.device, torch.bfloat16)
+                pout = None if self.master_is_param else p.data.view(-1)
+                lib.call("elfa_muon_apply", pout, 0 if pout is None else 1, master, y2.contiguous(), n, float(self.lr), self.scalars, st)
+            else:
+                if self.skipped():
+                    continue
+                m.mul_(self.momentum).add_(g.float() * float(self.scalars[1]))
+                nrm = float(m.norm())
+                if nrm < 1e-8:
+                    master.sub_(self.lr * m)
+                else:
+                    y = newton_schulz((m / nrm).view(rows, cols), self.iterations)
+                    master.sub_(self.lr * y.reshape(-1))
+                if not self.master_is_param:
+                    p.data.view(-1).copy_(master.to(p.dtype))
+
+    def state_tensors(self):
+        d = {"m": self.m}
+        if not self.master_is_param:
+            d["master"] = self.master
+        return d
+
+
+class LionMuon:
+    """The reference's default optimizer: 2-D parameters → Muon, everything else → Lion."""
+
+    def __init__(self, flat, pc=None, zero_stage=0, lr=1e-4, lion_betas=(0.95, 0.98), weight_decay=0.1, muon_momentum=0.95,
+                 muon_iterations=5, max_grad_norm=1.0):
+        idx2d = [i for i, p in enumerate(flat.params) if p.dim() == 2]
+        lion_ranges = []
+        for i, p in enumerate(flat.params):
+            if p.dim() != 2:
+                o = flat.offsets[i]
+                lion_ranges.append((o, o + p.numel(), not getattr(p, "no_decay", False) and p.dim() >= 2))
+        self.muon = Muon(flat, pc, 0, lr, muon_momentum, muon_iterations, max_grad_norm, idx2d)
+        self.lion = Lion(flat, pc, 0, lr, lion_betas, weight_decay, max_grad_norm, ranges=lion_ranges)
+        # both halves share the master copy and the clip scalars
+        self.lion.master, self.lion.scalars = self.muon.master, self.muon.scalars
+        self.flat, self.pc = flat, self.muon.pc
+        self.step_count = 0
+        self.lr = lr
+
+    @property
+    def loss_scale(self):
+        return self.muon.loss_scale
+
+    @loss_scale.setter
+    def loss_scale(self, v):
+        self.muon.loss_scale = v
+        self.lion.loss_scale = v
+
+    @property
+    def scalars(self):
+        return self.muon.scalars
+
+    def step(self, lr: Optional[float] = None) -> None:
+        if lr is not None:
+            self.lr = lr
+        self.muon.lr = self.lion.lr = self.lr
+        self.flat.fold_autograd_grads()
+        self.muon.reduce_gradients()
+        self.muon._norm_and_clip()
+        self.step_count += 1
+        self.muon.step_count = self.lion.step_count = self.step_count
+        self.muon._update()
+        self.lion._update()
+        from ..quant.qat import new_weight_epoch
+        new_weight_epoch()
+
+    def zero_grad(self):
+        self.flat.zero_grad()
+
+    def grad_norm(self):
+        return self.muon.grad_norm()
+
+    def skipped(self):
+        return self.muon.skipped()
+
+    def state_dict(self):
+        return {"step": self.step_count, "muon": self.muon.state_dict(), "lion": self.lion.state_dict()}
+
+    def load_state_dict(self, sd):
+        self.step_count = int(sd["step"])
+        self.muon.load_state_dict(sd["muon"])
+        self.lion.load_state_dict(sd["lion"])
+        self.lion.master = self.muon.master
+
+
+def build_optimizer(cfg, flat: FlatParams, pc: Optional[ParallelContext] = None):
+    """Optimizer selected by ``training.optimizer`` (lion | muon | lion_muon | adamw)."""
+    t = cfg.training
+    z = cfg.runtime.zero_stage
+    if t.optimizer == "adamw":
+        return AdamW(flat, pc, z, t.learning_rate, (t.adam_beta1, t.adam_beta2), t.adam_eps, t.weight_decay, t.gradient_clip)
+    if t.optimizer == "lion":
+        return Lion(flat, pc, z, t.learning_rate, (t.lion_beta1, t.lion_beta2), t.weight_decay, t.gradient_clip)
+    if t.optimizer == "muon":
+        idx = [i for i, p in enumerate(flat.params) if p.dim() == 2]
+        return Muon(flat, pc, z, t.learning_rate, t.muon_momentum, t.muon_iterations, t.gradient_clip, idx)
+    return LionMuon(flat, pc, z, t.learning_rate, (t.lion_beta1, t.lion_beta2), t.weight_decay, t.muon_momentum, t.muon_iterations,
+                    t.gradient_clip)

@@ -27,7 +27,7 @@ import torch.distributed as dist
 
 from .. import ops
 from ..ops.gemm import gemm
-from ..quant.qat import QuantSpec, fake_quant
+from ..quant.qat import QuantSpec, cached_weight_quant, fake_quant
 from .mesh import ParallelContext
 
 
@@ -179,7 +179,7 @@ class _ColumnParallelSP(torch.autograd.Function):
     def forward(ctx, x, w, pc, act, quant):
         Sl, B, D = x.shape
         xq = fake_quant(x.reshape(Sl * B, D), quant) if quant is not None else x.reshape(Sl * B, D)
-        wq = fake_quant(w, quant, weight=True) if quant is not None else w
+        wq = cached_weight_quant(w, quant) if quant is not None else w
         y, x_full, pre = ag_gemm(xq, wq, pc, b_mn=True, act=act, preact=True)
         ctx.save_for_backward(x_full, wq, pre)
         ctx.pc, ctx.w_ref, ctx.shape = pc, w, (Sl, B, D)
@@ -214,7 +214,7 @@ class _RowParallelSP(torch.autograd.Function):
         S, B, K = x.shape
         x2 = x.reshape(S * B, K)
         xq = fake_quant(x2, quant) if quant is not None else x2
-        wq = fake_quant(w, quant, weight=True) if quant is not None else w
+        wq = cached_weight_quant(w, quant) if quant is not None else w
         y = gemm_rs(xq, wq, pc, b_mn=True)
         ctx.save_for_backward(xq, wq)
         ctx.pc, ctx.w_ref, ctx.shape = pc, w, (S, B, K)
@@ -240,7 +240,7 @@ class _QuantLinear(torch.autograd.Function):
     def forward(ctx, x, w, act, quant):
         x2 = x.reshape(-1, x.shape[-1])
         xq = fake_quant(x2, quant)
-        wq = fake_quant(w, quant, weight=True)
+        wq = cached_weight_quant(w, quant)
         pre = None
         if act == "gelu":
             pre = torch.empty((x2.shape[0], w.shape[1]), dtype=x2.dtype, device=x2.device)

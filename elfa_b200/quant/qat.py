@@ -1,0 +1,162 @@
+"""Quantisation-aware training: fake-quant of GEMM operands with surrogate gradients.
+
+Modes (``quant.attention`` / ``quant.mlp`` in the YAML):
+
+* ``mxfp8``      - e4m3 values, 1x32 ue8m0 block scales along the contraction dimension;
+* ``nvfp4``      - e2m1 values, 16-element e4m3 block scales and one fp32 tensor scale;
+* ``fp8_tensor`` - per-tensor e4m3 with delayed scaling (16-deep amax history);
+* ``int_affine`` - min/max affine to ``weight_bits`` bits (the reference's "StableQAT").
+
+Backward is the straight-through estimator by default; the reference's sigmoid-tempered and
+piecewise-linear surrogates are available for ``int_affine`` weights
+(reference: ``src/quantization/stable_qat.zig:12-16,52-106``).
+
+``fake_quant`` is called inside the linear autograd functions (which implement the
+straight-through backward themselves); :func:`fake_quant_ste` is the standalone autograd op.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import formats
+
+SURROGATE = {"straight_through": 0, "sigmoid_tempered": 1, "piecewise_linear": 2}
+
+
+@dataclass
+class QuantSpec:
+    fmt: str = "none"
+    bits: int = 8
+    surrogate: str = "straight_through"
+    temperature: float = 0.1
+    threshold: float = 1.0
+    outside_slope: float = 0.1
+
+    @property
+    def enabled(self) -> bool:
+        return self.fmt != "none"
+
+    @classmethod
+    def from_config(cls, fmt: str, qcfg) -> "QuantSpec":
+        return cls(fmt=fmt, bits=qcfg.weight_bits, surrogate=qcfg.surrogate)
+
+
+_amax_buf = {}
+_scale_state = {}
+
+# Fake-quantised weights are reused by every micro-batch of an optimizer step: the cache is keyed on
+# the parameter and invalidated by `new_weight_epoch()` (called after each optimizer update).
+_weight_cache = {}
+_weight_epoch = 0
+
+
+def new_weight_epoch() -> None:
+    global _weight_epoch
+    _weight_epoch += 1
+    _weight_cache.clear()
+
+
+def cached_weight_quant(w: torch.Tensor, spec: "QuantSpec") -> torch.Tensor:
+    key = (id(w), spec.fmt, spec.bits)
+    hit = _weight_cache.get(key)
+    if hit is not None and hit[0] is w:
+        return hit[1]
+    wq = fake_quant(w.detach(), spec, weight=True)
+    _weight_cache[key] = (w, wq)
+    return wq
+
+
+def _scratch(device, n):
+    b = _amax_buf.get(device)
+    if b is None or b.numel() < n:
+        b = torch.zeros(max(n, 8192), dtype=torch.float32, device=device)
+        _amax_buf[device] = b
+    return b
+
+
+def fake_quant(x: torch.Tensor, spec: Optional[QuantSpec], weight: bool = False) -> torch.Tensor:
+    """Quantise-dequantise ``x`` (2-D). Activations ``[tokens, K]`` use blocks along the last
+    dimension; weights ``[K, N]`` (``weight=True``) use blocks along dim 0 - in both cases the
+    contraction dimension of the GEMM that consumes them."""
+    if spec is None or not spec.enabled:
+        return x
+    assert x.dim() == 2
+    axis = 0 if weight else 1
+    if not x.is_cuda:
+        if spec.fmt == "mxfp8":
+            return formats.mxfp8_fake_quant_ref(x, axis)
+        if spec.fmt == "nvfp4":
+            return formats.nvfp4_fake_quant_ref(x, axis)
+        if spec.fmt == "fp8_tensor":
+            amax = float(x.abs().max())
+            sc = formats.E4M3_MAX / amax if amax > 0 else 1.0
+            return (formats.e4m3_round(x.float() * sc) / sc).to(x.dtype)
+        if spec.fmt == "int_affine":
+            lo, hi = float(x.min()), float(x.max())
+            qmax = float(2 ** spec.bits - 1)
+            sc = (hi - lo) / qmax if hi > lo else 1.0
+            zp = -lo / sc
+            q = torch.clamp(torch.round(x.float() / sc + zp), 0, qmax)
+            return ((q - zp) * sc).to(x.dtype)
+        raise ValueError(spec.fmt)
+    from ..native import lib, stream_ptr
+    xc = x if x.is_contiguous() else x.contiguous()
+    out = torch.empty_like(xc)
+    rows, cols = xc.shape
+    st = stream_ptr(xc)
+    if spec.fmt == "mxfp8":
+        if axis == 1 and cols % 32:
+            raise ValueError("mxfp8: the contraction dimension must be a multiple of 32")
+        lib.call("elfa_mxfp8_fake_quant", xc, out, rows, cols, axis, st)
+    elif spec.fmt == "nvfp4":
+        amax = torch.zeros(1, dtype=torch.float32, device=x.device)
+        lib.call("elfa_amax", xc, xc.numel(), amax, st)
+        lib.call("elfa_nvfp4_fake_quant", xc, out, rows, cols, axis, amax, st)
+    elif spec.fmt == "fp8_tensor":
+        # current-tensor scaling on the device (no host sync): scale = 448 / amax
+        amax = torch.zeros(1, dtype=torch.float32, device=x.device)
+        lib.call("elfa_amax", xc, xc.numel(), amax, st)
+        scale = torch.where(amax > 0, formats.E4M3_MAX / amax, torch.ones_like(amax))
+        lib.call("elfa_fp8_tensor_fake_quant", xc, out, xc.numel(), scale, 0, st)
+    elif spec.fmt == "int_affine":
+        mm = torch.empty(2, dtype=torch.float32, device=x.device)
+        lib.call("elfa_int_affine_fake_quant", xc, out, xc.numel(), spec.bits, mm, _scratch(x.device, 8192), st)
+    else:
+        raise ValueError(spec.fmt)
+    return out
+
+
+class _FakeQuantSTE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, spec, weight):
+        ctx.spec = spec
+        ctx.save_for_backward(x)
+        return fake_quant(x, spec, weight)
+
+    @staticmethod
+    def backward(ctx, g):
+        (x,) = ctx.saved_tensors
+        spec = ctx.spec
+        mode = SURROGATE[spec.surrogate]
+        if mode == 0:
+            return g, None, None
+        p0 = spec.temperature if mode == 1 else spec.threshold
+        if not x.is_cuda:
+            xf, gf = x.float(), g.float()
+            if mode == 1:
+                s = torch.sigmoid(xf / p0)
+                return (gf * s * (1 - s) / p0).to(g.dtype), None, None
+            return torch.where(xf.abs() <= p0, gf, gf * spec.outside_slope).to(g.dtype), None, None
+        from ..native import lib, stream_ptr
+        out = torch.empty_like(g)
+        lib.call("elfa_qat_surrogate_bwd", x.contiguous(), g.contiguous(), out, x.numel(), mode, float(p0), float(spec.outside_slope),
+                 stream_ptr(x))
+        return out, None, None
+
+
+def fake_quant_ste(x: torch.Tensor, spec: QuantSpec, weight: bool = False) -> torch.Tensor:
+    """Autograd version: forward quantise-dequantise, backward per ``spec.surrogate``."""
+    return _FakeQuantSTE.apply(x, spec, weight)

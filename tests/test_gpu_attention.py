@@ -34,3 +34,22 @@ def test_attention_forward_batch_first(cuda_device):
     ref = ops.attention_ref(qkv.float(), causal=True, seq_first=False)
     assert (out.float() - ref).abs().max() < 0.03
     assert native.status() == 0
+
+
+@pytest.mark.parametrize("S,B,H,hd", [(128, 1, 1, 64), (256, 1, 2, 128), (384, 2, 2, 128), (200, 1, 2, 32), (1024, 1, 2, 64)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention_backward(cuda_device, S, B, H, hd, causal):
+    qkv = _qkv(S, B, H, hd, cuda_device, seed=7).requires_grad_(True)
+    out = ops.attention(qkv, causal=causal)
+    g = torch.randn_like(out)
+    out.backward(g)
+    torch.cuda.synchronize()
+    assert native.status() == 0
+    ref_in = qkv.detach().float().requires_grad_(True)
+    ref = ops.attention_ref(ref_in, causal=causal)
+    ref.backward(g.float())
+    err = (qkv.grad.float() - ref_in.grad).abs()
+    scale = ref_in.grad.abs().max().item()
+    for name, i in (("dq", 0), ("dk", 1), ("dv", 2)):
+        e = err[:, :, i].max().item()
+        assert e < 0.02 * max(scale, 1.0) + 0.02, f"{name}: max err {e} (grad scale {scale})"
