@@ -87,6 +87,15 @@ int elfa_fp8_tensor_fake_quant(const void* x, void* out, long long n, const floa
 int elfa_int_affine_fake_quant(const void* x, void* out, long long n, int bits, float* minmax, float* part, void* stream);
 int elfa_qat_surrogate_bwd(const void* x, const void* g, void* out, long long n, int mode, float p0, float p1, void* stream);
 
+// ---- fused GEMM + collective (gemm_bf16.cu) ----------------------------------------------------------
+int elfa_gemm_ag(const void* x_local, long long ldx, const unsigned long long* peer_xfull, const unsigned long long* peer_flags,
+                 const void* my_flags, unsigned int* arrivals_io, const void* B, void* C, int M, int N, int K, long long ldb,
+                 long long ldc, int b_mn_major, void* preact, long long ldpre, unsigned flags, int rank, int world, int wait_ms,
+                 void* stream);
+int elfa_gemm_rs(const void* A, long long lda, const void* B, long long ldb, int b_mn_major, int M, int N, int K,
+                 const unsigned long long* peer_recv, const unsigned long long* peer_flags, const void* my_flags,
+                 unsigned int* arrivals_io, void* out, long long ld_out, int rank, int world, int wait_ms, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -18,6 +18,20 @@
 //   warp 1   : allocates tensor memory; one lane issues tcgen05.mma (128 x BN x 16 per instruction)
 //   warps 2-5: epilogue - each owns one 32-lane quarter of the accumulator
 // Every wait is bounded; on a timeout the CTA sets the device status word, stops and tears down.
+//
+// Fused collectives (tensor + sequence parallel layers; reference call sites
+// src/distributed/tensor_parallel.zig:77-129, src/distributed/sequence_parallel.zig:79-128 gather then
+// GEMM, tensor_parallel.zig:154-170 / sequence_parallel.zig:184-200 GEMM then reduce), COMM template:
+//   COMM_AG: A = all_gather_rows(x_local). Two extra warps push this rank's shard into every peer's
+//            gathered buffer (plain stores over NVLink, one peer after the other, then a release
+//            increment of that peer's arrival counter). Tiles are scheduled own shard first, then
+//            the shards in the order they arrive; the TMA producer waits for a shard's counter
+//            before its first tile. Remote data crosses NVLink once, into local memory; the TMA
+//            loads themselves are always local and never cluster-multicast.
+//   COMM_RS: C = reduce_scatter_rows(A B). The epilogue stores each partial tile into the owner
+//            rank's receive slot [source rank] (peer stores), tiles of other owners first, and
+//            bumps the owner's counter. After its tiles every CTA helps to sum the slots of the
+//            rows this rank owns, in fixed rank order (deterministic), once all counters arrived.
 #include <mutex>
 #include <unordered_map>
 
@@ -47,6 +61,45 @@ struct GemmParams {
   int tiles_m, tiles_n, group_m;
 };
 
+enum { COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2 };
+constexpr int MAX_RANKS = 8;
+
+struct CommParams {
+  int rank, world;
+  int rows_per_rank;                       // M / world, a multiple of BM
+  long long wait_cycles;                   // limit of every flag wait
+  // all-gather of A
+  const __nv_bfloat16* x_local;            // [rows_per_rank, K]
+  long long ldx;
+  unsigned long long peer_xfull[MAX_RANKS];   // peers' gathered-A buffers [M, K] (ld = K)
+  unsigned long long peer_flags[MAX_RANKS];   // peers' counters, one u32 per source rank
+  const unsigned int* my_flags;            // this rank's counters
+  unsigned int flag_target;                // value a counter reaches when the source's push is complete
+  // reduce-scatter of C
+  unsigned long long peer_recv[MAX_RANKS];    // peers' receive buffers [world][rows_per_rank][N] bf16
+  const __nv_bfloat16* my_recv;
+  __nv_bfloat16* rs_out;                   // [rows_per_rank, N]
+  long long ld_out;
+};
+
+// Bounded wait until *flag >= target (wrap-safe). The counter is written by other GPUs.
+__device__ __forceinline__ bool flag_wait(const unsigned int* flag, unsigned int target, long long limit, volatile int* abort_flag,
+                                          unsigned int* status) {
+  const long long t0 = clock64();
+  for (;;) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if ((int)(v - target) >= 0) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > limit) {
+      *abort_flag = 1;
+      atomicOr(status, (unsigned)ELFA_ST_FLAG_TIMEOUT);
+      return false;
+    }
+    __nanosleep(100);
+  }
+}
+
 template <int BN, int STAGES>
 struct SmemLayout {
   static constexpr int A_BYTES = BM * BK * 2;
@@ -67,9 +120,29 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
   nb = r / gsz;
 }
 
-template <int BN, bool A_MN, bool B_MN, int STAGES>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+// Tile order of the fused variants: tiles are grouped by the rank that owns their rows ("shard").
+// COMM_AG visits the own shard first, then rank-1, rank-2, ... (the order in which pushes arrive);
+// COMM_RS visits rank+1, rank+2, ... and the own shard last (its partial does not travel).
+template <int COMM>
+__device__ __forceinline__ void tile_coords_comm(const GemmParams& p, const CommParams& c, int tile, int& mb, int& nb, int& shard) {
+  if (COMM == COMM_NONE) {
+    tile_coords(p, tile, mb, nb);
+    shard = 0;
+    return;
+  }
+  const int tm_shard = c.rows_per_rank / BM;
+  const int per_shard = tm_shard * p.tiles_n;
+  const int i = tile / per_shard;
+  const int lt = tile - i * per_shard;
+  shard = COMM == COMM_AG ? (c.rank - i + c.world) % c.world : (c.rank + 1 + i) % c.world;
+  mb = shard * tm_shard + lt % tm_shard;
+  nb = lt / tm_shard;
+}
+
+template <int BN, bool A_MN, bool B_MN, int STAGES, int COMM>
+__global__ void __launch_bounds__(COMM == COMM_NONE ? GEMM_THREADS : GEMM_THREADS + 64, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmA2, const GemmParams p, const CommParams cm) {
   using L = SmemLayout<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -120,10 +193,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      int ready_shard = -1;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int mb, nb;
-        tile_coords(p, tile, mb, nb);
+        int mb, nb, shard;
+        tile_coords_comm<COMM>(p, cm, tile, mb, nb, shard);
         const int m0 = mb * BM, n0 = nb * BN;
+        const bool own = COMM == COMM_AG && shard == cm.rank;
+        if (COMM == COMM_AG && !own && shard != ready_shard) {
+          // the shard was written by a peer GPU with ordinary stores: acquire its counter, then
+          // order those writes before this thread's TMA (async proxy) reads
+          if (!flag_wait(cm.my_flags + shard, cm.flag_target, cm.wait_cycles, abort_flag, p.status)) { ok = false; break; }
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          ready_shard = shard;
+        }
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -131,7 +213,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           mbar_expect_tx(full_bar(s), L::A_BYTES + L::B_BYTES);
           const uint32_t a_dst = smem_u32(sA + s * L::A_BYTES);
           const uint32_t b_dst = smem_u32(sB + s * L::B_BYTES);
-          if (!A_MN) {
+          if (own) {
+            tma_load_2d(a_dst, &tmA2, kb * BK, m0 - cm.rank * cm.rows_per_rank, full_bar(s));
+          } else if (!A_MN) {
             tma_load_2d(a_dst, &tmA, kb * BK, m0, full_bar(s));
           } else {
 #pragma unroll
@@ -186,14 +270,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (ok) tc_commit(tfull_bar(buf));
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;  // tensor-memory lane quarter this warp may read
     uint32_t tile_iter = 0;
     const unsigned fl = p.flags;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_iter) {
-      int mb, nb;
-      tile_coords(p, tile, mb, nb);
+      int mb, nb, shard;
+      tile_coords_comm<COMM>(p, cm, tile, mb, nb, shard);
       const int m0 = mb * BM, n0 = nb * BN;
       const uint32_t buf = tile_iter & 1, bph = (tile_iter >> 1) & 1;
       bool ok = mbar_wait(tfull_bar(buf), bph, abort_flag, p.status);
@@ -246,7 +330,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 }
               }
             }
-            if (fl & ELFA_EPI_OUT_F32) {
+            if (COMM == COMM_RS) {
+              // partial tile -> receive slot [this rank] of the rank that owns these rows
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(cm.peer_recv[shard]) +
+                                   ((long long)cm.rank * cm.rows_per_rank + (row - shard * cm.rows_per_rank)) * p.N + col;
+              uint4 o = make_uint4(pack_bf16(w[0], w[1]), pack_bf16(w[2], w[3]), pack_bf16(w[4], w[5]), pack_bf16(w[6], w[7]));
+              *reinterpret_cast<uint4*>(dst) = o;
+            } else if (fl & ELFA_EPI_OUT_F32) {
               float* cp = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col;
               float4 o0 = make_float4(w[0], w[1], w[2], w[3]), o1 = make_float4(w[4], w[5], w[6], w[7]);
               if (fl & ELFA_EPI_ACCUM) {
@@ -274,8 +364,65 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
       tc_fence_before();
+      if (COMM == COMM_RS) __threadfence_system();   // this thread's peer stores before the counter bump
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(buf));
+      if (lane == 0) {
+        mbar_arrive(tempty_bar(buf));
+        if (COMM == COMM_RS) {
+          unsigned int* cnt = reinterpret_cast<unsigned int*>(cm.peer_flags[shard]) + cm.rank;
+          asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
+        }
+      }
+    }
+  } else if (COMM == COMM_AG) {
+    // ------------------------------------------------------------------ push warps (6, 7)
+    // This CTA's slice of the local shard goes to peer rank+1 first, then rank+2, ...; the own
+    // copy (needed later by the weight-gradient GEMM) is written last.
+    const int t = threadIdx.x - 192;
+    const long long vec_per_row = p.K / 8;
+    const long long nvec = (long long)cm.rows_per_rank * vec_per_row;
+    const long long lo = nvec * blockIdx.x / gridDim.x, hi = nvec * (blockIdx.x + 1) / gridDim.x;
+    for (int i = 1; i <= cm.world; ++i) {
+      const int peer = (cm.rank + i) % cm.world;
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(cm.peer_xfull[peer]) + (long long)cm.rank * cm.rows_per_rank * p.K;
+      for (long long v = lo + t; v < hi; v += 64) {
+        const long long r = v / vec_per_row, cv = v - r * vec_per_row;
+        const uint4 q = *reinterpret_cast<const uint4*>(cm.x_local + r * cm.ldx + cv * 8);
+        *reinterpret_cast<uint4*>(dst + r * p.K + cv * 8) = q;
+      }
+      __threadfence_system();
+      named_bar_sync(1, 64);
+      if (t == 0 && peer != cm.rank) {
+        unsigned int* cnt = reinterpret_cast<unsigned int*>(cm.peer_flags[peer]) + cm.rank;
+        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
+      }
+    }
+  }
+
+  if (COMM == COMM_RS) {
+    // ------------------------------------------------------------------ reduce the owned rows
+    bool ok = true;
+    for (int src = 0; src < cm.world && ok; ++src)
+      ok = flag_wait(cm.my_flags + src, cm.flag_target, cm.wait_cycles, abort_flag, p.status);
+    if (ok) {
+      const long long vec_per_row = p.N / 8;
+      const long long nvec = (long long)cm.rows_per_rank * vec_per_row;
+      const long long slot = (long long)cm.rows_per_rank * p.N;
+      for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
+        const long long r = v / vec_per_row, cv = v - r * vec_per_row;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int src = 0; src < cm.world; ++src) {
+          const uint4 q = *reinterpret_cast<const uint4*>(cm.my_recv + src * slot + r * p.N + cv * 8);
+          const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[2 * j] += bf16_lo(qw[j]);
+            acc[2 * j + 1] += bf16_hi(qw[j]);
+          }
+        }
+        uint4 o = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+        *reinterpret_cast<uint4*>(cm.rs_out + r * cm.ld_out + cv * 8) = o;
+      }
     }
   }
 
@@ -341,11 +488,12 @@ int sm_count() {
   return g_sm_count;
 }
 
-template <int BN, bool A_MN, bool B_MN>
-int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int max_ctas, cudaStream_t stream) {
+template <int BN, bool A_MN, bool B_MN, int COMM = COMM_NONE>
+int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int max_ctas, cudaStream_t stream,
+                const CUtensorMap* tmA2 = nullptr, const CommParams* comm = nullptr) {
   constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
   using L = SmemLayout<BN, STAGES>;
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, STAGES>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, STAGES, COMM>;
   static bool configured = false;
   if (!configured) {
     ELFA_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
@@ -356,7 +504,9 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, in
   p.group_m = 8;
   int tiles = p.tiles_m * p.tiles_n;
   int grid = tiles < max_ctas ? tiles : max_ctas;
-  kern<<<grid, GEMM_THREADS, L::DYN, stream>>>(tmA, tmB, p);
+  CommParams c{};
+  if (comm) c = *comm;
+  kern<<<grid, COMM == COMM_NONE ? GEMM_THREADS : GEMM_THREADS + 64, L::DYN, stream>>>(tmA, tmB, tmA2 ? *tmA2 : tmA, p, c);
   ELFA_CUDA(cudaGetLastError());
   ::elfa::count_launches(1);
   return ELFA_OK;
@@ -430,4 +580,116 @@ ELFA_API int elfa_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
     case 128: return dispatch_layout<128>(a_mn_major, b_mn_major, tmA, tmB, p, ctas, s);
     default: return dispatch_layout<64>(a_mn_major, b_mn_major, tmA, tmB, p, ctas, s);
   }
+}
+
+
+namespace elfa {
+namespace {
+
+template <int COMM>
+int dispatch_comm(int BN, int b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmA2, const GemmParams& p,
+                  const CommParams& c, cudaStream_t s) {
+  const int ctas = sm_count();
+  if (BN == 256) {
+    return b_mn ? launch_gemm<256, false, true, COMM>(tmA, tmB, p, ctas, s, &tmA2, &c)
+                : launch_gemm<256, false, false, COMM>(tmA, tmB, p, ctas, s, &tmA2, &c);
+  }
+  return b_mn ? launch_gemm<128, false, true, COMM>(tmA, tmB, p, ctas, s, &tmA2, &c)
+              : launch_gemm<128, false, false, COMM>(tmA, tmB, p, ctas, s, &tmA2, &c);
+}
+
+int comm_grid(int M, int N, int BN) {
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  return tiles < sm_count() ? tiles : sm_count();
+}
+
+long long wait_cycles_of(int wait_ms) { return (long long)(wait_ms > 0 ? wait_ms : 10000) * 1900000LL; }
+
+}  // namespace
+}  // namespace elfa
+
+// C[M,N] = epilogue(all_gather_rows(x_local)[M,K] * op(B)), M = world * rows. One kernel: the shard
+// is pushed to every peer's `xfull` buffer while the tensor cores start on the local rows.
+//   peer_xfull / peer_flags : host arrays of `world` device addresses (entry `rank` = this rank's own)
+//   my_flags                : this rank's arrival counters (u32 per source rank), never reset
+//   arrivals_io             : host counter of arrivals expected so far on this flag set; updated
+// After the call xfull (this rank's entry) holds the gathered A (kept for the weight gradient).
+ELFA_API int elfa_gemm_ag(const void* x_local, long long ldx, const unsigned long long* peer_xfull,
+                          const unsigned long long* peer_flags, const void* my_flags, unsigned int* arrivals_io, const void* B,
+                          void* C, int M, int N, int K, long long ldb, long long ldc, int b_mn_major, void* preact, long long ldpre,
+                          unsigned flags, int rank, int world, int wait_ms, void* stream) {
+  ELFA_REQUIRE(x_local && peer_xfull && peer_flags && my_flags && arrivals_io && B && C, "gemm_ag: null argument");
+  ELFA_REQUIRE(world >= 2 && world <= MAX_RANKS && rank >= 0 && rank < world, "gemm_ag: bad rank/world");
+  ELFA_REQUIRE(M % world == 0 && (M / world) % BM == 0, "gemm_ag: rows per rank must be a multiple of 128");
+  ELFA_REQUIRE(N % 8 == 0 && K % 8 == 0 && ldx % 8 == 0 && ldb % 8 == 0 && ldc % 8 == 0, "gemm_ag: alignment");
+  ELFA_REQUIRE(!(flags & ~(ELFA_EPI_GELU | ELFA_EPI_STORE_PREACT)), "gemm_ag: unsupported epilogue flag");
+  ELFA_REQUIRE(!(flags & ELFA_EPI_STORE_PREACT) || (preact && ldpre % 8 == 0), "gemm_ag: preact flag without pointer");
+  unsigned int* st = status_word();
+  ELFA_REQUIRE(st != nullptr, "gemm_ag: no status word");
+  const int rows = M / world;
+  const int BN = (N >= 256 && (long long)(M / BM) * ((N + 255) / 256) >= sm_count()) ? 256 : 128;
+  CUtensorMap tmA, tmA2, tmB;
+  int rc = cached_tmap_bf16(&tmA, reinterpret_cast<const void*>(peer_xfull[rank]), (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, BK);
+  if (rc != ELFA_OK) return rc;
+  rc = cached_tmap_bf16(&tmA2, x_local, (uint64_t)rows, (uint64_t)K, (uint64_t)ldx, BM, BK);
+  if (rc != ELFA_OK) return rc;
+  if (!b_mn_major) rc = cached_tmap_bf16(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN, BK);
+  else rc = cached_tmap_bf16(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, 64);
+  if (rc != ELFA_OK) return rc;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc;
+  p.preact = static_cast<__nv_bfloat16*>(preact);
+  p.ldpre = ldpre;
+  p.alpha = 1.f;
+  p.flags = flags;
+  p.status = st;
+  CommParams c{};
+  c.rank = rank; c.world = world; c.rows_per_rank = rows;
+  c.wait_cycles = wait_cycles_of(wait_ms);
+  c.x_local = static_cast<const __nv_bfloat16*>(x_local);
+  c.ldx = ldx;
+  for (int i = 0; i < world; ++i) { c.peer_xfull[i] = peer_xfull[i]; c.peer_flags[i] = peer_flags[i]; }
+  c.my_flags = static_cast<const unsigned int*>(my_flags);
+  *arrivals_io += (unsigned)comm_grid(M, N, BN);        // every CTA of a source bumps the counter once
+  c.flag_target = *arrivals_io;
+  return dispatch_comm<COMM_AG>(BN, b_mn_major, tmA, tmB, tmA2, p, c, static_cast<cudaStream_t>(stream));
+}
+
+// out[M/world, N] = reduce_scatter_rows(A[M,K] * op(B)): partial tiles travel to the owner's receive
+// buffer ([world][M/world][N] bf16, symmetric) and are summed there in rank order.
+ELFA_API int elfa_gemm_rs(const void* A, long long lda, const void* B, long long ldb, int b_mn_major, int M, int N, int K,
+                          const unsigned long long* peer_recv, const unsigned long long* peer_flags, const void* my_flags,
+                          unsigned int* arrivals_io, void* out, long long ld_out, int rank, int world, int wait_ms, void* stream) {
+  ELFA_REQUIRE(A && B && peer_recv && peer_flags && my_flags && arrivals_io && out, "gemm_rs: null argument");
+  ELFA_REQUIRE(world >= 2 && world <= MAX_RANKS && rank >= 0 && rank < world, "gemm_rs: bad rank/world");
+  ELFA_REQUIRE(M % world == 0 && (M / world) % BM == 0, "gemm_rs: rows per rank must be a multiple of 128");
+  ELFA_REQUIRE(N % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ld_out % 8 == 0, "gemm_rs: alignment");
+  unsigned int* st = status_word();
+  ELFA_REQUIRE(st != nullptr, "gemm_rs: no status word");
+  const int rows = M / world;
+  const int BN = (N >= 256 && (long long)(M / BM) * ((N + 255) / 256) >= sm_count()) ? 256 : 128;
+  CUtensorMap tmA, tmB;
+  int rc = cached_tmap_bf16(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, BK);
+  if (rc != ELFA_OK) return rc;
+  if (!b_mn_major) rc = cached_tmap_bf16(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN, BK);
+  else rc = cached_tmap_bf16(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, 64);
+  if (rc != ELFA_OK) return rc;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.C = out; p.ldc = ld_out;
+  p.alpha = 1.f;
+  p.status = st;
+  CommParams c{};
+  c.rank = rank; c.world = world; c.rows_per_rank = rows;
+  c.wait_cycles = wait_cycles_of(wait_ms);
+  for (int i = 0; i < world; ++i) { c.peer_recv[i] = peer_recv[i]; c.peer_flags[i] = peer_flags[i]; }
+  c.my_flags = static_cast<const unsigned int*>(my_flags);
+  c.my_recv = reinterpret_cast<const __nv_bfloat16*>(peer_recv[rank]);
+  c.rs_out = static_cast<__nv_bfloat16*>(out);
+  c.ld_out = ld_out;
+  // per source rank: (tiles of one shard) x 4 epilogue warps
+  *arrivals_io += (unsigned)((rows / BM) * ((N + BN - 1) / BN) * 4);
+  c.flag_target = *arrivals_io;
+  return dispatch_comm<COMM_RS>(BN, b_mn_major, tmA, tmB, tmA, p, c, static_cast<cudaStream_t>(stream));
 }

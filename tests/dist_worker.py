@@ -1,0 +1,154 @@
+"""Worker run by the multi-process tests (one process per rank, launched by torch.distributed.run).
+
+modes:
+  fused   - fused ag_gemm / gemm_rs against the library (NCCL) path, repeated calls (GPU)
+  tp      - a small GPT trained with TP=world (+sequence parallel) against the same model on one rank
+  timeout - a fused wait that nothing satisfies must return with the timeout status, not hang (GPU)
+"""
+import os
+import sys
+import warnings
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+warnings.simplefilter("ignore")
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+from elfa_b200.config import Config  # noqa: E402
+from elfa_b200.parallel import tp as tpl  # noqa: E402
+from elfa_b200.parallel.mesh import build_context, init_distributed  # noqa: E402
+
+
+def small_cfg(dtype, tp, backend, quant="none"):
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = Config.from_file(os.path.join(root, "configs", "bench", "smoke_cpu.yaml"))
+    cfg.model.dtype = dtype
+    cfg.model.hidden_dim, cfg.model.num_heads, cfg.model.head_dim = 256, 4, 64
+    cfg.model.intermediate_dim = 1024
+    cfg.data.seq_len = 256
+    cfg.model.max_seq_len = 256
+    cfg.training.micro_batch_size, cfg.training.global_batch_size = 2, 2
+    cfg.runtime.tensor_parallel_size = tp
+    cfg.runtime.comm_backend = backend
+    cfg.quant.attention = cfg.quant.mlp = quant
+    cfg.checkpoint.dir = ""
+    cfg.checkpoint.save_interval = 0
+    cfg.telemetry.log_file = ""
+    return cfg
+
+
+def mode_fused(pc, dev):
+    from elfa_b200 import native
+    from elfa_b200.runtime.symm import SymmetricArena
+    pc.symm = SymmetricArena.for_group(pc.tp_group, dev, 1 << 30)
+    world, rank = pc.tp_size, pc.tp_rank
+    torch.manual_seed(1234)
+    worst = 0.0
+    for it, (Ml, K, N) in enumerate([(128, 256, 512), (256, 512, 1376), (512, 1024, 1536), (256, 512, 1376), (128, 256, 512),
+                                     (512, 4096, 1536)]):
+        g = torch.Generator(device="cpu").manual_seed(100 + it)
+        x_all = torch.randn(Ml * world, K, generator=g).to(torch.bfloat16).to(dev)
+        w = (torch.randn(K, N, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+        x_local = x_all[rank * Ml:(rank + 1) * Ml].contiguous()
+        pc.comm_backend = "fused"
+        y, x_full, pre = tpl.ag_gemm(x_local, w, pc, b_mn=True, act="gelu", preact=True)
+        pc.comm_backend = "nccl"
+        y_ref, x_ref, pre_ref = tpl.ag_gemm(x_local, w, pc, b_mn=True, act="gelu", preact=True)
+        torch.cuda.synchronize()
+        assert torch.equal(x_full, x_ref), "gathered input differs"
+        assert torch.equal(x_full, x_all)
+        e1 = (y.float() - y_ref.float()).abs().max().item()
+        e2 = (pre.float() - pre_ref.float()).abs().max().item()
+        # reduce-scatter: every rank holds a K-slice
+        a = torch.randn(Ml * world, K, generator=g).to(torch.bfloat16).to(dev)
+        w2 = (torch.randn(K, N, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+        kl = K // world
+        a_l = a[:, rank * kl:(rank + 1) * kl].contiguous()
+        w_l = w2[rank * kl:(rank + 1) * kl].contiguous()
+        pc.comm_backend = "fused"
+        o = tpl.gemm_rs(a_l, w_l, pc, b_mn=True)
+        torch.cuda.synchronize()
+        ref = (a.float() @ w2.float())[rank * Ml:(rank + 1) * Ml]
+        e3 = (o.float() - ref).abs().max().item()
+        tol = 0.02 * (K ** 0.5) * 0.05 * 4 + 0.05
+        assert e1 == 0.0 and e2 == 0.0, f"ag_gemm differs from the library path: {e1} {e2}"
+        assert e3 < tol, f"gemm_rs error {e3} > {tol}"
+        worst = max(worst, e3)
+    st = native.status()
+    assert st == 0, f"device status 0x{st:x}"
+    dist.barrier()
+    if rank == 0:
+        print(f"FUSED_OK worst_rs_err={worst:.4f}")
+
+
+def mode_tp(pc, dev, backend, dtype):
+    from elfa_b200.parallel.mesh import ParallelContext
+    from elfa_b200.trainer import Trainer
+    world = pc.tp_size
+    cfg = small_cfg(dtype, world, backend)
+    tr = Trainer(cfg, device=dev, pc=pc, telemetry=False)
+    losses = tr.run(max_steps=4)
+    ref = None
+    if pc.rank == 0:
+        cfg1 = small_cfg(dtype, 1, "nccl")
+        cfg1.runtime.world_size = 1
+        tr1 = Trainer(cfg1, device=dev, pc=ParallelContext(), telemetry=False)
+        ref = tr1.run(max_steps=4)
+        tol = 2e-4 if dtype == "fp32" else 0.05
+        for a, b in zip(losses, ref):
+            assert abs(a - b) < tol * max(1.0, abs(b)), f"TP losses {losses} differ from single-rank {ref}"
+        print(f"TP_OK backend={backend} losses={[round(x, 4) for x in losses]} ref={[round(x, 4) for x in ref]}")
+    dist.barrier()
+
+
+def mode_timeout(pc, dev):
+    """Only rank 0 launches the fused all-gather GEMM; its peers never push, so the wait on their
+    counters must give up after the limit and report it through the status word."""
+    import time
+    from elfa_b200 import native
+    from elfa_b200.parallel import fused
+    from elfa_b200.runtime.symm import SymmetricArena
+    pc.symm = SymmetricArena.for_group(pc.tp_group, dev, 256 << 20)
+    fused._WAIT_MS = 300
+    x = torch.randn(128, 256, device=dev).to(torch.bfloat16)
+    w = torch.randn(256, 256, device=dev).to(torch.bfloat16)
+    pc.comm_backend = "fused"
+    # every rank creates the slot (the creation barrier is collective) ...
+    st = fused._state(pc)
+    st.next_slot("ag", fused._round_class(128 * pc.tp_size * 256 * 2))
+    st.counter["ag"] -= 1
+    dist.barrier()
+    if pc.rank == 0:
+        t0 = time.time()
+        tpl.ag_gemm(x, w, pc, b_mn=True)
+        torch.cuda.synchronize()
+        dt = time.time() - t0
+        s = native.status()
+        assert s & native.ST_FLAG_TIMEOUT, f"expected the flag-timeout status, got 0x{s:x}"
+        assert dt < 5.0, f"bounded wait took {dt:.1f}s"
+        # the context is still usable
+        assert float((x.float() @ w.float()).abs().sum()) > 0
+        print(f"TIMEOUT_OK waited={dt:.2f}s")
+    dist.barrier()
+
+
+def main():
+    mode = sys.argv[1]
+    backend = sys.argv[2] if len(sys.argv) > 2 else "nccl"
+    dtype = sys.argv[3] if len(sys.argv) > 3 else "bf16"
+    use_cuda = torch.cuda.is_available() and mode != "tp_cpu"
+    world = init_distributed("nccl" if use_cuda else "gloo")
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if use_cuda else torch.device("cpu")
+    pc = build_context(world, True, backend)
+    if mode == "fused":
+        mode_fused(pc, dev)
+    elif mode in ("tp", "tp_cpu"):
+        mode_tp(pc, dev, backend, dtype)
+    elif mode == "timeout":
+        mode_timeout(pc, dev)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
