@@ -1,0 +1,87 @@
+"""Times the two tensor-parallel hot paths - all-gather→GEMM and GEMM→reduce-scatter - with the
+library baseline (NCCL collective + GEMM as separate kernels) and with the fused peer-memory
+kernels, on the per-rank shapes of the 7B TP configuration (tokens x 4096 hidden).
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29560 \
+        baseline/fused_vs_nccl.py [--tokens 16384]
+
+Device timing (CUDA events), max over ranks. The roofline of a fused op is the slower of
+FLOPs / measured GEMM peak and bytes over NVLink / 770 GB/s per direction (measured peer copy).
+"""
+import argparse
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+from elfa_b200.parallel import tp as tpl  # noqa: E402
+from elfa_b200.parallel.mesh import build_context, init_distributed  # noqa: E402
+from elfa_b200.runtime.symm import SymmetricArena  # noqa: E402
+
+
+def timed(fn, iters=20, warm=5):
+    for _ in range(warm):
+        fn()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=16384)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--ffn", type=int, default=11008)
+    a = ap.parse_args()
+    world = init_distributed("nccl")
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    pc = build_context(world, True, "nccl")
+    pc.symm = SymmetricArena.for_group(pc.tp_group, dev, 4 << 30)
+    peak = 1.4e15
+    try:
+        with open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")) as f:
+            peak = json.load(f)["bf16_tflops"] * 1e12
+    except OSError:
+        pass
+    link = 770e9
+    M, D, F = a.tokens, a.hidden, a.ffn
+    rows = []
+    for name, kind, K, N in [("qkv (AG->GEMM)", "ag", D, 3 * D // world), ("mlp_up (AG->GEMM)", "ag", D, F // world),
+                             ("attn_out (GEMM->RS)", "rs", D // world, D), ("mlp_down (GEMM->RS)", "rs", F // world, D)]:
+        w = (torch.randn(K, N, device=dev) * 0.02).to(torch.bfloat16)
+        res = {}
+        for backend in ("nccl", "fused"):
+            pc.comm_backend = backend
+            if kind == "ag":
+                x = torch.randn(M // world, K, device=dev).to(torch.bfloat16)
+                res[backend] = timed(lambda: tpl.ag_gemm(x, w, pc, b_mn=True))
+            else:
+                x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+                res[backend] = timed(lambda: tpl.gemm_rs(x, w, pc, b_mn=True))
+        flops = 2.0 * M * K * N
+        wire = (world - 1) / world * M * (K if kind == "ag" else N) * 2
+        floor_ms = max(flops / peak, wire / link) * 1e3
+        rows.append((name, M, N, K, res["nccl"], res["fused"], floor_ms))
+    if pc.rank == 0:
+        print(f"world={world} tokens={M}")
+        print(f"{'op':24s} {'M':>6s} {'N':>6s} {'K':>6s} {'nccl ms':>9s} {'fused ms':>9s} {'speedup':>8s} {'floor ms':>9s} {'fused/floor':>11s}")
+        for name, m, n, k, t0, t1, fl in rows:
+            print(f"{name:24s} {m:6d} {n:6d} {k:6d} {t0:9.3f} {t1:9.3f} {t0 / t1:8.2f} {fl:9.3f} {fl / t1:11.2f}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

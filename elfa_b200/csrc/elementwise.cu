@@ -67,12 +67,12 @@ __global__ void __launch_bounds__(256) ew_kernel(const __nv_bfloat16* __restrict
 __global__ void __launch_bounds__(256) embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ tok,
                                                             const __nv_bfloat16* __restrict__ pos, __nv_bfloat16* __restrict__ out,
                                                             int tokens, int D, int seq, int pos_div, int pos0, int vocab_lo, int vocab_hi,
-                                                            unsigned int* status) {
+                                                            int vocab_total, unsigned int* status) {
   const int nvec = D / 8;
   for (int t = blockIdx.x; t < tokens; t += gridDim.x) {
     const long long id = ids[t];
     const bool mine = id >= vocab_lo && id < vocab_hi;
-    if (!mine && vocab_lo == 0 && threadIdx.x == 0 && (id < 0 || id >= vocab_hi)) atomicOr(status, (unsigned)ELFA_ST_BAD_TARGET);
+    if (threadIdx.x == 0 && (id < 0 || id >= vocab_total)) atomicOr(status, (unsigned)ELFA_ST_BAD_TARGET);
     const uint4* tr = reinterpret_cast<const uint4*>(tok + (long long)(mine ? id - vocab_lo : 0) * D);
     const uint4* pr = pos ? reinterpret_cast<const uint4*>(pos + (long long)(pos0 + (t / pos_div) % seq) * D) : nullptr;
     uint4* orow = reinterpret_cast<uint4*>(out + (long long)t * D);
@@ -159,7 +159,7 @@ ELFA_API int elfa_elementwise(int op, const void* a, const void* b, void* out, l
 // `tok` are local to that slice); other tokens give zeros, so a sum over vocabulary-parallel ranks
 // rebuilds the full embedding. Positions are added by the rank with vocab_lo == 0.
 ELFA_API int elfa_embedding_fwd(const long long* ids, const void* tok, const void* pos, void* out, int tokens, int D, int seq,
-                                int pos_div, int pos0, int vocab_lo, int vocab_hi, void* stream) {
+                                int pos_div, int pos0, int vocab_lo, int vocab_hi, int vocab_total, void* stream) {
   ELFA_REQUIRE(ids && tok && out && tokens > 0 && D % 8 == 0 && seq > 0 && pos_div > 0, "embedding_fwd: bad arguments");
   unsigned int* st = status_word();
   ELFA_REQUIRE(st != nullptr, "embedding_fwd: no status word");
@@ -167,7 +167,7 @@ ELFA_API int elfa_embedding_fwd(const long long* ids, const void* tok, const voi
   const int threads = D / 8 >= 256 ? 256 : (D / 8 >= 128 ? 128 : 64);
   embedding_fwd_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
       ids, static_cast<const __nv_bfloat16*>(tok), static_cast<const __nv_bfloat16*>(pos), static_cast<__nv_bfloat16*>(out), tokens,
-      D, seq, pos_div, pos0, vocab_lo, vocab_hi, st);
+      D, seq, pos_div, pos0, vocab_lo, vocab_hi, vocab_total, st);
   ELFA_CUDA(cudaGetLastError());
   ::elfa::count_launches(1);
   return ELFA_OK;

@@ -43,7 +43,7 @@ int elfa_norm_bwd(const void* dy, const void* x, const void* w, const float* mea
 // ---- elementwise.cu ----------------------------------------------------------------------------
 int elfa_elementwise(int op, const void* a, const void* b, void* out, long long n, float alpha, void* stream);
 int elfa_embedding_fwd(const long long* ids, const void* tok, const void* pos, void* out, int tokens, int D, int seq, int pos_div, int pos0,
-                       int vocab_lo, int vocab_hi, void* stream);
+                       int vocab_lo, int vocab_hi, int vocab_total, void* stream);
 int elfa_embedding_bwd(const long long* ids, const void* dy, void* dtok, void* dpos, int tokens, int D, int seq, int pos_div, int pos0,
                        int vocab_lo, int vocab_hi, int grads_f32, void* stream);
 int elfa_cast(const void* src, int src_type, void* dst, int dst_type, long long n, float scale, void* stream);
@@ -95,6 +95,25 @@ int elfa_gemm_ag(const void* x_local, long long ldx, const unsigned long long* p
 int elfa_gemm_rs(const void* A, long long lda, const void* B, long long ldb, int b_mn_major, int M, int N, int K,
                  const unsigned long long* peer_recv, const unsigned long long* peer_flags, const void* my_flags,
                  unsigned int* arrivals_io, void* out, long long ld_out, int rank, int world, int wait_ms, void* stream);
+
+// ---- zero.cu -----------------------------------------------------------------------------------
+int elfa_symm_barrier(const unsigned long long* peer_flags, const void* my_flags, int rank, int world, unsigned int epoch,
+                      int wait_ms, void* stream);
+int elfa_zero_reduce(const unsigned long long* peer_grads, int rank, int world, long long lo, long long n, float* reduced,
+                     float scale, float* part, void* scalars, void* stream);
+int elfa_zero_adamw_allgather(const unsigned long long* peer_params, int rank, int world, long long lo, long long n, float* master,
+                              float* m, float* v, const float* reduced, float lr, float beta1, float beta2, float eps, float wd,
+                              int step, const void* scalars, long long wd_lo, long long wd_hi, void* stream);
+
+// ---- efla.cu -----------------------------------------------------------------------------------
+int elfa_efla_scan_fwd(const void* k, const void* v, const float* beta, const float* state0, void* o, float* state_out,
+                       float* ckpt, int B, int T, int H, int d, int chunk, void* stream);
+int elfa_efla_scan_bwd(const void* k, const void* v, const float* beta, const float* ckpt, const void* dout,
+                       const float* dstate_out, void* dk, void* dv, float* dbeta, float* dstate0, float* work, int B, int T,
+                       int H, int d, int chunk, void* stream);
+int elfa_shortconv_fwd(const void* x, const void* w, const void* bias, void* y, int B, int T, int C, int W, void* stream);
+int elfa_shortconv_bwd(const void* x, const void* w, const void* dy, void* dx, float* dw, float* db, int B, int T, int C, int W,
+                       void* stream);
 
 #ifdef __cplusplus
 }

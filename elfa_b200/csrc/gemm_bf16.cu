@@ -108,6 +108,14 @@ struct SmemLayout {
   static constexpr int NUM_BARS = 2 * STAGES + 4;
   static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16;
   static constexpr int DYN = TOTAL + 1024;  // slack for manual 1024-byte alignment
+  // reduce-scatter variant: two [128 x 64] bf16 staging tiles for the TMA stores to the owner rank
+  static constexpr int OUT_OFF = (TOTAL + 1023) / 1024 * 1024;
+  static constexpr int OUT_BYTES = 2 * BM * 128;
+  static constexpr int DYN_RS = OUT_OFF + OUT_BYTES + 1024;
+};
+
+struct OutMaps {   // tensor maps over every rank's receive buffer, viewed as [world * rows_per_rank, N] bf16
+  CUtensorMap m[MAX_RANKS];
 };
 
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& mb, int& nb) {
@@ -142,7 +150,8 @@ __device__ __forceinline__ void tile_coords_comm(const GemmParams& p, const Comm
 template <int BN, bool A_MN, bool B_MN, int STAGES, int COMM>
 __global__ void __launch_bounds__(COMM == COMM_NONE ? GEMM_THREADS : GEMM_THREADS + 64, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmA2, const GemmParams p, const CommParams cm) {
+                 const __grid_constant__ CUtensorMap tmA2, const GemmParams p, const CommParams cm,
+                 const __grid_constant__ OutMaps om) {
   using L = SmemLayout<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -275,6 +284,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;  // tensor-memory lane quarter this warp may read
     uint32_t tile_iter = 0;
     const unsigned fl = p.flags;
+    int pending_owner = -1;   // COMM_RS: owner of the previous tile, whose counter is still to be bumped
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_iter) {
       int mb, nb, shard;
       tile_coords_comm<COMM>(p, cm, tile, mb, nb, shard);
@@ -284,6 +294,60 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      if (COMM == COMM_RS) {
+        // partial tile -> shared staging (128-byte swizzle) -> TMA store into receive slot [this rank]
+        // of the rank that owns these rows; one counter bump per tile once the stores completed
+        const uint32_t out0 = smem_u32(smem + L::OUT_OFF);
+        const bool issuer = warp == 2 && lane == 0;
+        const int rloc = q * 32 + lane;
+        const int dst_row = cm.rank * cm.rows_per_rank + (m0 - shard * cm.rows_per_rank);
+#pragma unroll 1
+        for (int cc = 0; cc < BN / 64; ++cc) {
+          const uint32_t sbuf = out0 + (cc & 1) * (BM * 128);
+          if (issuer) tma_store_wait_read<1>();      // the store that last used this buffer has read it
+          named_bar_sync(2, 128);
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            uint32_t r[32];
+            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + cc * 64 + hf * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int idx = hf * 4 + g;
+              const uint32_t addr = sbuf + rloc * 128 + ((idx ^ (rloc & 7)) << 4);
+              const uint32_t w0 = pack_bf16(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
+              const uint32_t w1 = pack_bf16(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
+              const uint32_t w2 = pack_bf16(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
+              const uint32_t w3 = pack_bf16(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+            }
+          }
+          if (cc == BN / 64 - 1) {   // accumulator fully read: hand the buffer back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(buf));
+          }
+          fence_proxy_async();
+          named_bar_sync(2, 128);
+          if (issuer) {
+            if (n0 + cc * 64 < p.N) tma_store_2d(&om.m[shard], sbuf, n0 + cc * 64, dst_row);
+            tma_store_commit();
+          }
+        }
+        if (issuer) {
+          // The counter of a tile is bumped one tile late: by then its BN/64 store groups are the
+          // oldest ones in flight, so waiting for "all but the newest BN/64" covers them without
+          // stalling on the NVLink round trip of the tile just issued.
+          if (pending_owner >= 0) {
+            tma_store_wait<BN / 64>();
+            __threadfence_system();
+            unsigned int* cnt = reinterpret_cast<unsigned int*>(cm.peer_flags[pending_owner]) + cm.rank;
+            asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
+          }
+          pending_owner = shard;
+        }
+        continue;
+      }
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
 #pragma unroll 1
@@ -330,13 +394,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 }
               }
             }
-            if (COMM == COMM_RS) {
-              // partial tile -> receive slot [this rank] of the rank that owns these rows
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(cm.peer_recv[shard]) +
-                                   ((long long)cm.rank * cm.rows_per_rank + (row - shard * cm.rows_per_rank)) * p.N + col;
-              uint4 o = make_uint4(pack_bf16(w[0], w[1]), pack_bf16(w[2], w[3]), pack_bf16(w[4], w[5]), pack_bf16(w[6], w[7]));
-              *reinterpret_cast<uint4*>(dst) = o;
-            } else if (fl & ELFA_EPI_OUT_F32) {
+            if (fl & ELFA_EPI_OUT_F32) {
               float* cp = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col;
               float4 o0 = make_float4(w[0], w[1], w[2], w[3]), o1 = make_float4(w[4], w[5], w[6], w[7]);
               if (fl & ELFA_EPI_ACCUM) {
@@ -364,15 +422,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
       tc_fence_before();
-      if (COMM == COMM_RS) __threadfence_system();   // this thread's peer stores before the counter bump
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(tempty_bar(buf));
-        if (COMM == COMM_RS) {
-          unsigned int* cnt = reinterpret_cast<unsigned int*>(cm.peer_flags[shard]) + cm.rank;
-          asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
-        }
-      }
+      if (lane == 0) mbar_arrive(tempty_bar(buf));
+    }
+    if (COMM == COMM_RS && warp == 2 && lane == 0 && pending_owner >= 0) {
+      tma_store_wait<0>();
+      __threadfence_system();
+      unsigned int* cnt = reinterpret_cast<unsigned int*>(cm.peer_flags[pending_owner]) + cm.rank;
+      asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
     }
   } else if (COMM == COMM_AG) {
     // ------------------------------------------------------------------ push warps (6, 7)
@@ -401,9 +458,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (COMM == COMM_RS) {
     // ------------------------------------------------------------------ reduce the owned rows
-    bool ok = true;
-    for (int src = 0; src < cm.world && ok; ++src)
-      ok = flag_wait(cm.my_flags + src, cm.flag_target, cm.wait_cycles, abort_flag, p.status);
+    // Threads without a role park at this barrier (no spinning next to the producer / MMA lanes);
+    // one thread then polls the arrival counters for the whole CTA.
+    __syncthreads();
+    __shared__ int rs_ok;
+    if (threadIdx.x == 0) {
+      bool ok0 = true;
+      for (int src = 0; src < cm.world && ok0; ++src)
+        ok0 = flag_wait(cm.my_flags + src, cm.flag_target, cm.wait_cycles, abort_flag, p.status);
+      rs_ok = ok0 ? 1 : 0;
+    }
+    __syncthreads();
+    const bool ok = rs_ok != 0;
     if (ok) {
       const long long vec_per_row = p.N / 8;
       const long long nvec = (long long)cm.rows_per_rank * vec_per_row;
@@ -490,13 +556,14 @@ int sm_count() {
 
 template <int BN, bool A_MN, bool B_MN, int COMM = COMM_NONE>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int max_ctas, cudaStream_t stream,
-                const CUtensorMap* tmA2 = nullptr, const CommParams* comm = nullptr) {
+                const CUtensorMap* tmA2 = nullptr, const CommParams* comm = nullptr, const OutMaps* om = nullptr) {
   constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
   using L = SmemLayout<BN, STAGES>;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, STAGES, COMM>;
+  constexpr int DYN = COMM == COMM_RS ? L::DYN_RS : L::DYN;
   static bool configured = false;
   if (!configured) {
-    ELFA_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
+    ELFA_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN));
     configured = true;
   }
   p.tiles_m = (p.M + BM - 1) / BM;
@@ -506,7 +573,9 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, in
   int grid = tiles < max_ctas ? tiles : max_ctas;
   CommParams c{};
   if (comm) c = *comm;
-  kern<<<grid, COMM == COMM_NONE ? GEMM_THREADS : GEMM_THREADS + 64, L::DYN, stream>>>(tmA, tmB, tmA2 ? *tmA2 : tmA, p, c);
+  static const OutMaps no_maps{};
+  kern<<<grid, COMM == COMM_NONE ? GEMM_THREADS : GEMM_THREADS + 64, DYN, stream>>>(tmA, tmB, tmA2 ? *tmA2 : tmA, p, c,
+                                                                                     om ? *om : no_maps);
   ELFA_CUDA(cudaGetLastError());
   ::elfa::count_launches(1);
   return ELFA_OK;
@@ -588,14 +657,14 @@ namespace {
 
 template <int COMM>
 int dispatch_comm(int BN, int b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmA2, const GemmParams& p,
-                  const CommParams& c, cudaStream_t s) {
+                  const CommParams& c, cudaStream_t s, const OutMaps* om = nullptr) {
   const int ctas = sm_count();
   if (BN == 256) {
-    return b_mn ? launch_gemm<256, false, true, COMM>(tmA, tmB, p, ctas, s, &tmA2, &c)
-                : launch_gemm<256, false, false, COMM>(tmA, tmB, p, ctas, s, &tmA2, &c);
+    return b_mn ? launch_gemm<256, false, true, COMM>(tmA, tmB, p, ctas, s, &tmA2, &c, om)
+                : launch_gemm<256, false, false, COMM>(tmA, tmB, p, ctas, s, &tmA2, &c, om);
   }
-  return b_mn ? launch_gemm<128, false, true, COMM>(tmA, tmB, p, ctas, s, &tmA2, &c)
-              : launch_gemm<128, false, false, COMM>(tmA, tmB, p, ctas, s, &tmA2, &c);
+  return b_mn ? launch_gemm<128, false, true, COMM>(tmA, tmB, p, ctas, s, &tmA2, &c, om)
+              : launch_gemm<128, false, false, COMM>(tmA, tmB, p, ctas, s, &tmA2, &c, om);
 }
 
 int comm_grid(int M, int N, int BN) {
@@ -664,7 +733,7 @@ ELFA_API int elfa_gemm_rs(const void* A, long long lda, const void* B, long long
   ELFA_REQUIRE(A && B && peer_recv && peer_flags && my_flags && arrivals_io && out, "gemm_rs: null argument");
   ELFA_REQUIRE(world >= 2 && world <= MAX_RANKS && rank >= 0 && rank < world, "gemm_rs: bad rank/world");
   ELFA_REQUIRE(M % world == 0 && (M / world) % BM == 0, "gemm_rs: rows per rank must be a multiple of 128");
-  ELFA_REQUIRE(N % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ld_out % 8 == 0, "gemm_rs: alignment");
+  ELFA_REQUIRE(N % 64 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ld_out % 8 == 0, "gemm_rs: alignment (N must be a multiple of 64)");
   unsigned int* st = status_word();
   ELFA_REQUIRE(st != nullptr, "gemm_rs: no status word");
   const int rows = M / world;
@@ -688,8 +757,13 @@ ELFA_API int elfa_gemm_rs(const void* A, long long lda, const void* B, long long
   c.my_recv = reinterpret_cast<const __nv_bfloat16*>(peer_recv[rank]);
   c.rs_out = static_cast<__nv_bfloat16*>(out);
   c.ld_out = ld_out;
-  // per source rank: (tiles of one shard) x 4 epilogue warps
-  *arrivals_io += (unsigned)((rows / BM) * ((N + BN - 1) / BN) * 4);
+  // per source rank: one bump per tile of the shard
+  *arrivals_io += (unsigned)((rows / BM) * ((N + BN - 1) / BN));
   c.flag_target = *arrivals_io;
-  return dispatch_comm<COMM_RS>(BN, b_mn_major, tmA, tmB, tmA, p, c, static_cast<cudaStream_t>(stream));
+  OutMaps om{};
+  for (int i = 0; i < world; ++i) {
+    rc = cached_tmap_bf16(&om.m[i], reinterpret_cast<const void*>(peer_recv[i]), (uint64_t)M, (uint64_t)N, (uint64_t)N, BM, 64);
+    if (rc != ELFA_OK) return rc;
+  }
+  return dispatch_comm<COMM_RS>(BN, b_mn_major, tmA, tmB, tmA, p, c, static_cast<cudaStream_t>(stream), &om);
 }

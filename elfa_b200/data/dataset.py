@@ -233,6 +233,16 @@ class DataLoader:
             inp, tgt = inp.pin_memory(), tgt.pin_memory()
         return Batch(inp, tgt)
 
+    def skip(self, n_batches: int) -> None:
+        """Advances the read position by ``n_batches`` batches (rolling over epochs) without
+        materialising them; used to resume a run at the right place in the data."""
+        per_epoch = max(len(self._order) // self.batch_size, 1)
+        for _ in range(n_batches // per_epoch):
+            self.epoch += 1
+        if n_batches >= per_epoch:
+            self.reset()
+        self._pos = (n_batches % per_epoch) * self.batch_size
+
     def next_cycling(self) -> Batch:
         """Like :meth:`next` but rolls over to the next epoch (reshuffle) when exhausted."""
         b = self.next()

@@ -1,0 +1,243 @@
+"""The reference's own model family: pre-RMSNorm decoder whose token mixer is EFLA followed by
+PRISM, then a GELU MLP.
+
+Block (reference ``src/model/model.zig:229-272``)::
+
+    n = norm1(x); e = EFLA(n); q = PRISM(n, e); r = x + q; out = r + W_down gelu(W_up norm2(r))
+
+Model: token embedding → blocks → final norm → logits (``lm_head`` or tied embedding).
+Parameter names and shapes follow the reference checkpoint layout (``model.zig:512-537``):
+``embed_tokens.weight [V, D]``, per block ``blocks.{i}.ln1.weight``, ``.efla.w_k / .w_v [D, H*d]``,
+``.efla.w_o [H*d, D]``, ``.efla.beta_param [1] (fp32)``, ``.prism.w_beta.{j} / .w_k.{j} / .w_p.{j} [D, d]``,
+``.prism.shortconv.weight [D, W]`` (``.bias``), ``.ln2.weight``, ``.mlp_up.weight [D, I]``,
+``.mlp_down.weight [I, D]``, then ``final_norm.weight`` and ``lm_head.weight`` when untied.
+Initialisation uses the reference's He-style sigmas (``src/model/efla.zig:148``, ``prism.zig:163,889``,
+``src/nn/layers.zig:336,446``) unless ``bench.init_std`` overrides them.
+
+``forward_with_states`` streams a long sequence block by block, carrying the EFLA state (and the
+ShortConv tail) per layer - the reference's route to very long contexts
+(``model.zig:415-454``, ``efla.zig:681-733``).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from ..config import Config
+from ..ops import efla as eops
+from ..parallel.mesh import ParallelContext
+from .gpt import Norm, _dtype
+
+
+class EflaLayer(nn.Module):
+    def __init__(self, cfg: Config, dtype, device):
+        super().__init__()
+        m = cfg.model
+        self.H, self.d = m.num_heads, m.head_dim
+        D = m.hidden_dim
+        self.w_k = nn.Parameter(torch.empty(D, self.H * self.d, dtype=dtype, device=device))
+        self.w_v = nn.Parameter(torch.empty(D, self.H * self.d, dtype=dtype, device=device))
+        self.w_o = nn.Parameter(torch.empty(self.H * self.d, D, dtype=dtype, device=device))
+        self.learned_beta = m.efla.learned_beta
+        self.beta_param = nn.Parameter(torch.full((1,), float(m.efla.initial_beta), dtype=torch.float32, device=device),
+                                       requires_grad=m.efla.learned_beta)
+        self.beta_param.no_decay = True
+        self.chunk = max(1, min(m.efla.chunk_size, 16)) if m.efla.use_chunked_scan else 16
+
+    def forward(self, x, state=None):
+        B, T, D = x.shape
+        k = ops.linear(x, self.w_k).view(B, T, self.H, self.d)
+        v = ops.linear(x, self.w_v).view(B, T, self.H, self.d)
+        o, s = eops.efla_scan(k, v, self.beta_param, state, self.chunk)
+        return ops.linear(o.reshape(B, T, self.H * self.d).to(x.dtype), self.w_o), s
+
+
+class PrismLayer(nn.Module):
+    def __init__(self, cfg: Config, dtype, device):
+        super().__init__()
+        m = cfg.model
+        D, d, L = m.hidden_dim, m.head_dim, m.prism.num_iterations
+        self.d, self.L, self.forget = d, L, m.prism.forget_factor
+        self.w_beta = nn.ParameterList([nn.Parameter(torch.empty(D, d, dtype=dtype, device=device)) for _ in range(L)])
+        self.w_k = nn.ParameterList([nn.Parameter(torch.empty(D, d, dtype=dtype, device=device)) for _ in range(L)])
+        self.w_p = nn.ParameterList([nn.Parameter(torch.empty(D, d, dtype=dtype, device=device)) for _ in range(L)])
+        self.conv_weight = nn.Parameter(torch.empty(D, m.prism.shortconv_window, dtype=dtype, device=device))
+        self.conv_bias = nn.Parameter(torch.zeros(D, dtype=dtype, device=device))
+        self.conv_bias.no_decay = True
+
+    def forward(self, x, v, carry_state: Optional[torch.Tensor] = None, conv_tail: Optional[torch.Tensor] = None):
+        """x: normed hidden ``[B, T, D]``, v: EFLA output. Returns (y, new_state or None, new conv tail)."""
+        W = self.conv_weight.shape[1]
+        xin = x if conv_tail is None else torch.cat([conv_tail, x], dim=1)
+        u = eops.shortconv(xin, self.conv_weight, self.conv_bias)
+        if conv_tail is not None:
+            u = u[:, conv_tail.shape[1]:]
+        new_tail = xin[:, -(W - 1):].detach() if W > 1 else None
+        ps = [torch.sigmoid(ops.linear(u, self.w_p[l]).float()) for l in range(self.L)]
+        y = eops.prism_refine(u, v, ps, self.d)
+        new_state = None
+        if carry_state is not None:
+            with torch.no_grad():
+                B, T, D = u.shape
+                G = D // self.d
+                r = (v.float() - u.float()).view(B, T, G, self.d)
+                deltas, betas, ks = [], [], []
+                for l in range(self.L):
+                    delta = ops.gelu_tanh_ref(ps[l].unsqueeze(2) * r)
+                    r = r - delta
+                    deltas.append(delta)
+                    betas.append(torch.sigmoid(ops.linear(u, self.w_beta[l]).float().mean(-1)))
+                    kk = ops.linear(u, self.w_k[l]).float()
+                    nrm = kk.norm(dim=-1, keepdim=True)
+                    ks.append(kk / torch.where(nrm < 1e-12, torch.ones_like(nrm), nrm))
+                new_state = eops.prism_state_update(carry_state, deltas, betas, ks, self.forget)
+        return y, new_state, new_tail
+
+
+class EflaBlock(nn.Module):
+    def __init__(self, cfg: Config, dtype, device):
+        super().__init__()
+        m = cfg.model
+        self.ln1 = Norm(m.hidden_dim, m.norm_type, dtype, device)
+        self.efla = EflaLayer(cfg, dtype, device)
+        self.prism = PrismLayer(cfg, dtype, device) if m.prism.enabled else None
+        self.ln2 = Norm(m.hidden_dim, m.norm_type, dtype, device)
+        self.mlp_up = nn.Parameter(torch.empty(m.hidden_dim, m.intermediate_dim, dtype=dtype, device=device))
+        self.mlp_down = nn.Parameter(torch.empty(m.intermediate_dim, m.hidden_dim, dtype=dtype, device=device))
+        self.act = "gelu" if m.activation in ("gelu", "swiglu") else m.activation
+
+    def forward(self, x, states=None):
+        n, _ = self.ln1(x)
+        e_state = states["efla"] if states is not None else None
+        e, e_state = self.efla(n, e_state)
+        if self.prism is not None:
+            q, p_state, tail = self.prism(n, e, states["prism"] if states is not None else None,
+                                          states.get("conv_tail") if states is not None else None)
+        else:
+            q, p_state, tail = e, None, None
+        n2, r = self.ln2(q, x)                 # fused: r = x + q, n2 = norm2(r)
+        if self.act == "gelu":
+            h = ops.linear(n2, self.mlp_up, None, "gelu")
+        else:
+            h = ops.activation(ops.linear(n2, self.mlp_up), self.act)
+        out = r + ops.linear(h, self.mlp_down)
+        new_states = None
+        if states is not None:
+            new_states = {"efla": e_state, "prism": p_state, "conv_tail": tail}
+        return out, new_states
+
+
+class EflaModel(nn.Module):
+    def __init__(self, cfg: Config, pc: Optional[ParallelContext] = None, device=None):
+        super().__init__()
+        self.cfg = cfg
+        self.pc = pc or ParallelContext()
+        if self.pc.tp_size != 1:
+            raise ValueError("the EFLA family runs with tensor_parallel_size 1 (use data parallel / ZeRO)")
+        m = cfg.model
+        dtype = _dtype(m.dtype)
+        self.dtype = dtype
+        self.embed_tokens = nn.Parameter(torch.empty(m.vocab_size, m.hidden_dim, dtype=dtype, device=device))
+        self.blocks = nn.ModuleList([EflaBlock(cfg, dtype, device) for _ in range(m.num_layers)])
+        self.final_norm = Norm(m.hidden_dim, m.norm_type, dtype, device)
+        self.lm_head = None if m.tie_embeddings else nn.Parameter(torch.empty(m.vocab_size, m.hidden_dim, dtype=dtype, device=device))
+        self.reset_parameters(cfg.runtime.seed)
+
+    def reset_parameters(self, seed: int) -> None:
+        m = self.cfg.model
+        dev = self.embed_tokens.device
+        g = torch.Generator(device=dev).manual_seed(seed)
+        std = self.cfg.bench.init_std
+        D, I = m.hidden_dim, m.intermediate_dim
+
+        def fill(p, sigma):
+            with torch.no_grad():
+                p.copy_((torch.randn(p.shape, generator=g, dtype=torch.float32, device=dev) * (std if std > 0 else sigma)).to(p.dtype))
+
+        fill(self.embed_tokens, math.sqrt(1.0 / D))
+        for b in self.blocks:
+            for w in (b.efla.w_k, b.efla.w_v):
+                fill(w, math.sqrt(2.0 / D))
+            fill(b.efla.w_o, math.sqrt(2.0 / D))
+            if b.prism is not None:
+                for lst in (b.prism.w_beta, b.prism.w_k, b.prism.w_p):
+                    for w in lst:
+                        fill(w, math.sqrt(2.0 / D))
+                fill(b.prism.conv_weight, math.sqrt(1.0 / b.prism.conv_weight.shape[1]))
+            fill(b.mlp_up, math.sqrt(2.0 / D))
+            fill(b.mlp_down, math.sqrt(2.0 / I))
+        if self.lm_head is not None:
+            fill(self.lm_head, math.sqrt(2.0 / D))
+
+    def named_checkpoint_parameters(self):
+        yield "embed_tokens.weight", self.embed_tokens
+        for i, b in enumerate(self.blocks):
+            yield f"blocks.{i}.ln1.weight", b.ln1.weight
+            if b.ln1.bias is not None:
+                yield f"blocks.{i}.ln1.bias", b.ln1.bias
+            yield f"blocks.{i}.efla.w_k", b.efla.w_k
+            yield f"blocks.{i}.efla.w_v", b.efla.w_v
+            yield f"blocks.{i}.efla.w_o", b.efla.w_o
+            if b.efla.learned_beta:
+                yield f"blocks.{i}.efla.beta_param", b.efla.beta_param
+            if b.prism is not None:
+                for j, w in enumerate(b.prism.w_beta):
+                    yield f"blocks.{i}.prism.w_beta.{j}", w
+                for j, w in enumerate(b.prism.w_k):
+                    yield f"blocks.{i}.prism.w_k.{j}", w
+                for j, w in enumerate(b.prism.w_p):
+                    yield f"blocks.{i}.prism.w_p.{j}", w
+                yield f"blocks.{i}.prism.shortconv.weight", b.prism.conv_weight
+                yield f"blocks.{i}.prism.shortconv.bias", b.prism.conv_bias
+            yield f"blocks.{i}.ln2.weight", b.ln2.weight
+            if b.ln2.bias is not None:
+                yield f"blocks.{i}.ln2.bias", b.ln2.bias
+            yield f"blocks.{i}.mlp_up.weight", b.mlp_up
+            yield f"blocks.{i}.mlp_down.weight", b.mlp_down
+        yield "final_norm.weight", self.final_norm.weight
+        if self.final_norm.bias is not None:
+            yield "final_norm.bias", self.final_norm.bias
+        if self.lm_head is not None:
+            yield "lm_head.weight", self.lm_head
+
+    def count_parameters(self) -> int:
+        return sum(p.numel() for _, p in self.named_checkpoint_parameters())
+
+    def init_states(self, batch: int) -> List[dict]:
+        m = self.cfg.model
+        dev = self.embed_tokens.device
+        G = m.hidden_dim // m.head_dim
+        return [{"efla": torch.zeros(batch, m.num_heads, m.head_dim, m.head_dim, device=dev),
+                 "prism": torch.zeros(batch, G, m.head_dim, m.head_dim, device=dev) if m.prism.enabled else None,
+                 "conv_tail": None} for _ in self.blocks]
+
+    def hidden_states(self, ids: torch.Tensor, states: Optional[List[dict]] = None):
+        x = ops.embedding(ids, self.embed_tokens, None, 0, 0, seq_first=False, vocab_total=self.cfg.model.vocab_size)
+        new_states = [] if states is not None else None
+        for i, blk in enumerate(self.blocks):
+            x, ns = blk(x, states[i] if states is not None else None)
+            if new_states is not None:
+                new_states.append(ns)
+        n, _ = self.final_norm(x)
+        return n, new_states
+
+    def forward_with_states(self, ids: torch.Tensor, states: Optional[List[dict]] = None):
+        """ids ``[B, T]`` → (logits ``[B, T, V]``, per-layer states) for streaming / generation."""
+        if states is None:
+            states = self.init_states(ids.shape[0])
+        n, states = self.hidden_states(ids, states)
+        head = self.lm_head if self.lm_head is not None else self.embed_tokens
+        return ops.linear_nt(n, head), states
+
+    def forward(self, ids: torch.Tensor, targets: Optional[torch.Tensor] = None, pos0: int = 0,
+                loss_denominator: Optional[float] = None, grad_scale: float = 1.0):
+        n, _ = self.hidden_states(ids)
+        head = self.lm_head if self.lm_head is not None else self.embed_tokens
+        logits = ops.linear_nt(n, head)
+        if targets is None:
+            return logits
+        return ops.cross_entropy(logits, targets, self.cfg.training.label_smoothing, loss_denominator, grad_scale)

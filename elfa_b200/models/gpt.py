@@ -231,7 +231,8 @@ class GPTModel(nn.Module):
         """ids ``[B, S]`` → final-norm output ``[S(/tp), B, D]``."""
         pc = self.pc
         ids_sb = ids.t().contiguous()                        # [S, B]
-        x = ops.embedding(ids_sb, self.embed_tokens, self.pos_embed, pos0, self.vocab_lo, seq_first=True)  # [S, B, D]
+        x = ops.embedding(ids_sb, self.embed_tokens, self.pos_embed, pos0, self.vocab_lo, seq_first=True,
+                          vocab_total=self.cfg.model.vocab_size)  # [S, B, D]
         x = tpl.embedding_reduce(x, pc)                      # sum over vocab shards → [S(/tp), B, D]
         pending = None
         for blk in self.blocks:

@@ -215,7 +215,7 @@ def gelu(x):
 # ---------------------------------------------------------------------------------------- embedding
 class _Embedding(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, ids, tok, pos, pos0, vocab_lo, seq_first):
+    def forward(ctx, ids, tok, pos, pos0, vocab_lo, seq_first, vocab_total):
         if seq_first:
             T, B = ids.shape
         else:
@@ -234,7 +234,7 @@ class _Embedding(torch.autograd.Function):
         idc = ids.contiguous().view(-1)
         out = torch.empty((*ids.shape, D), dtype=tok.dtype, device=tok.device)
         lib.call("elfa_embedding_fwd", idc, tok, pos, out, B * T, D, T, B if seq_first else 1, pos0, vocab_lo,
-                 vocab_lo + tok.shape[0], stream_ptr(out))
+                 vocab_lo + tok.shape[0], vocab_total if vocab_total else vocab_lo + tok.shape[0], stream_ptr(out))
         return out
 
     @staticmethod
@@ -253,7 +253,7 @@ class _Embedding(torch.autograd.Function):
                 if vocab_lo == 0:
                     dpos[pos0:pos0 + T] = dy.float().sum(1 if seq_first else 0)
                 dpos = dpos.to(pos.dtype)
-            return None, dtok.to(tok.dtype), dpos, None, None, None
+            return None, dtok.to(tok.dtype), dpos, None, None, None, None
         dyc = dy.contiguous()
         idc = ids.contiguous().view(-1)
         tt = _grad_target(tok)
@@ -279,14 +279,14 @@ class _Embedding(torch.autograd.Function):
             dtok_ret = dtok_ret.to(tok.dtype)
         if dpos_ret is not None:
             dpos_ret = dpos_ret.to(pos.dtype)
-        return None, dtok_ret, dpos_ret, None, None, None
+        return None, dtok_ret, dpos_ret, None, None, None, None
 
 
 def embedding(ids: torch.Tensor, tok: torch.Tensor, pos: Optional[torch.Tensor] = None, pos0: int = 0,
-              vocab_lo: int = 0, seq_first: bool = False) -> torch.Tensor:
+              vocab_lo: int = 0, seq_first: bool = False, vocab_total: int = 0) -> torch.Tensor:
     """``tok[ids - vocab_lo] (+ pos[pos0 + t])`` for ids inside this rank's vocabulary slice, zeros
     for the others (summing over vocabulary-parallel ranks gives the full embedding)."""
-    return _Embedding.apply(ids, tok, pos, pos0, vocab_lo, seq_first)
+    return _Embedding.apply(ids, tok, pos, pos0, vocab_lo, seq_first, vocab_total)
 
 
 # ------------------------------------------------------------------------------------ cross-entropy

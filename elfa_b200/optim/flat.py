@@ -64,9 +64,19 @@ class FlatParams:
         quantum = dp_size * 1024
         self.numel = (off + quantum - 1) // quantum * quantum
         self.offsets = offsets
-        alloc = allocator or (lambda n, dt: torch.zeros(n, dtype=dt, device=self.device))
-        self.flat = alloc(self.numel, self.dtype)
-        self.grads = alloc(self.numel, grad_dtype)
+        self.symm = None
+        if allocator is not None:
+            # `allocator` is a symmetric arena: both buffers become regions that peers can address
+            esz = torch.empty(0, dtype=self.dtype).element_size()
+            gsz = torch.empty(0, dtype=grad_dtype).element_size()
+            r_flat = allocator.alloc(self.numel * esz, "flat.params")
+            r_grads = allocator.alloc(self.numel * gsz, "flat.grads")
+            self.flat = r_flat.view(self.dtype, (self.numel,))
+            self.grads = r_grads.view(grad_dtype, (self.numel,))
+            self.symm = (allocator, r_flat, r_grads)
+        else:
+            self.flat = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
+            self.grads = torch.zeros(self.numel, dtype=grad_dtype, device=self.device)
         self.flat.zero_()
         self.grads.zero_()
         self.segments: List[Segment] = []

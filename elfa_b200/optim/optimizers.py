@@ -51,14 +51,51 @@ class _Base:
         self.part = torch.zeros(4096, dtype=torch.float32, device=dev)
         self.n_local = n
         self.last_grad_norm = 0.0
+        # fused ZeRO path (peer-memory kernels): needs the flat buffers inside a symmetric arena
+        self.zero_fused = None
+        zf = getattr(flat, "symm", None)
+        if self.sharded and zf is not None and flat.flat.is_cuda and self.pc.comm_backend == "fused":
+            import ctypes
+            arena, r_flat, r_grads = zf
+            w = arena.world
+            flags = arena.alloc(1024, "zero.barrier")
+            self.zero_fused = {
+                "arena": arena,
+                "peer_params": (ctypes.c_uint64 * w)(*[arena.peer_address(r, r_flat) for r in range(w)]),
+                "peer_grads": (ctypes.c_uint64 * w)(*[arena.peer_address(r, r_grads) for r in range(w)]),
+                "peer_flags": (ctypes.c_uint64 * w)(*[arena.peer_address(r, flags) for r in range(w)]),
+                "flags": flags, "epoch": 0,
+            }
+            self.gshard = torch.zeros(n, dtype=torch.float32, device=dev)
+            arena.barrier()
 
     # --------------------------------------------------------------- gradient synchronisation
+    def _symm_barrier(self) -> None:
+        import ctypes
+        z = self.zero_fused
+        z["epoch"] += 1
+        lib.call("elfa_symm_barrier", ctypes.addressof(z["peer_flags"]), z["flags"].tensor, self.pc.dp_rank, self.pc.dp_size,
+                 z["epoch"], 0, stream_ptr(self.flat.flat))
+
+    def _grads(self, a: int, b: int) -> torch.Tensor:
+        """Gradient values of the global index range [a, b) this rank updates."""
+        if self.zero_fused is not None:
+            return self.gshard[a - self.lo:b - self.lo]
+        return self.flat.grads[a:b]
+
     def reduce_gradients(self) -> None:
         """TP: all-reduce the replicated prefix. DP: all-reduce (ZeRO-0) or reduce-scatter
         (ZeRO>=1) the whole buffer; gradients are averaged over DP."""
         pc, f = self.pc, self.flat
         if pc.tp_size > 1 and f.replicated_end > 0:
             dist.all_reduce(f.grads[:f.replicated_end], group=pc.tp_group)
+        if self.zero_fused is not None:
+            import ctypes
+            z = self.zero_fused
+            self._symm_barrier()          # every rank's gradients are complete and visible
+            lib.call("elfa_zero_reduce", ctypes.addressof(z["peer_grads"]), pc.dp_rank, pc.dp_size, self.lo, self.hi - self.lo,
+                     self.gshard, 1.0 / pc.dp_size, self.part, self.scalars, stream_ptr(f.grads))
+            return
         if pc.dp_size > 1:
             if self.sharded and f.grads.is_cuda:
                 shard = f.grads[self.lo:self.hi]
@@ -68,6 +105,13 @@ class _Base:
                 f.grads.div_(pc.dp_size)
 
     def gather_params(self) -> None:
+        if self.zero_fused is not None:
+            if not getattr(self, "_fused_gather_done", False):
+                # the update kernel did not broadcast (non-AdamW optimizers): library all-gather
+                dist.all_gather_into_tensor(self.flat.flat, self.flat.flat[self.lo:self.hi], group=self.pc.dp_group)
+            self._fused_gather_done = False
+            self._symm_barrier()          # all parameter stores have landed before the next forward
+            return
         if self.sharded:
             f, pc = self.flat, self.pc
             if f.flat.is_cuda:
@@ -81,7 +125,7 @@ class _Base:
     def _norm_and_clip(self) -> None:
         """Fills ``self.scalars`` (device). The squared norm counts TP-replicated gradients once."""
         f, pc = self.flat, self.pc
-        g = f.grads[self.lo:self.hi]
+        g = self._grads(self.lo, self.hi)
         inv_scale = 1.0 / self.loss_scale
         if g.is_cuda:
             st = stream_ptr(g)
@@ -94,10 +138,10 @@ class _Base:
                 self.scalars[0].zero_()
                 acc = 0
                 if rep_hi > self.lo and pc.tp_rank == 0:
-                    lib.call("elfa_sumsq", f.grads[self.lo:rep_hi], _ptype(g), rep_hi - self.lo, self.part, self.scalars, 0, st)
+                    lib.call("elfa_sumsq", self._grads(self.lo, rep_hi), _ptype(g), rep_hi - self.lo, self.part, self.scalars, 0, st)
                     acc = 1
                 if self.hi > rep_hi:
-                    lib.call("elfa_sumsq", f.grads[rep_hi:self.hi], _ptype(g), self.hi - rep_hi, self.part, self.scalars, acc, st)
+                    lib.call("elfa_sumsq", self._grads(rep_hi, self.hi), _ptype(g), self.hi - rep_hi, self.part, self.scalars, acc, st)
                 dist.all_reduce(self.scalars[0:1], group=None if self.sharded else pc.tp_group)
             lib.call("elfa_clip_coef", self.scalars, float(self.max_grad_norm), float(inv_scale), st)
             return
@@ -178,8 +222,16 @@ class AdamW(_Base):
         pout, ptype = self._param_out()
         for a, b, wd in f.wd_ranges(self.lo, self.hi):
             s, e = a - self.lo, b - self.lo
-            g = f.grads[a:b]
+            g = self._grads(a, b)
             wdv = self.weight_decay if wd else 0.0
+            if self.zero_fused is not None and not self.master_is_param:
+                import ctypes
+                z = self.zero_fused
+                lib.call("elfa_zero_adamw_allgather", ctypes.addressof(z["peer_params"]), self.pc.dp_rank, self.pc.dp_size, a, b - a,
+                         self.master[s:e], self.m[s:e], self.v[s:e], g, float(self.lr), float(b1), float(b2), float(self.eps),
+                         float(wdv), self.step_count, self.scalars, 0, 1 << 62, stream_ptr(g))
+                self._fused_gather_done = True
+                continue
             if g.is_cuda:
                 lib.call("elfa_adamw", pout[s:e] if pout is not None else None, ptype, self.master[s:e], self.m[s:e], self.v[s:e], g,
                          _ptype(g), e - s, float(self.lr), float(b1), float(b2), float(self.eps), float(wdv), self.step_count,
@@ -222,7 +274,7 @@ class Lion(_Base):
             if a >= b:
                 continue
             s, e = a - self.lo, b - self.lo
-            g = f.grads[a:b]
+            g = self._grads(a, b)
             wdv = self.weight_decay if wd else 0.0
             if g.is_cuda:
                 lib.call("elfa_lion", pout[s:e] if pout is not None else None, ptype, self.master[s:e], self.m[s:e], g, _ptype(g),

@@ -116,7 +116,7 @@ def gemm_rs(a: torch.Tensor, w: torch.Tensor, pc: ParallelContext, *, b_mn: bool
     world, rank = pc.tp_size, pc.tp_rank
     M, K = a.shape
     N = w.shape[1] if b_mn else w.shape[0]
-    if M % world or not supported(M // world, K, N) or a.dtype != torch.bfloat16:
+    if M % world or not supported(M // world, K, N) or N % 64 or a.dtype != torch.bfloat16:
         from . import tp
         saved, pc.comm_backend = pc.comm_backend, "nccl"
         try:

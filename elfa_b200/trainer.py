@@ -65,7 +65,13 @@ class Trainer:
             pc.symm = SymmetricArena.for_group(pc.tp_group, device)
         self.model = build_model(cfg, pc, device)
         self.model.train()
-        self.flat = FlatParams(self.model.named_checkpoint_parameters(), dp_size=pc.dp_size, dp_rank=pc.dp_rank)
+        dp_arena = None
+        if (pc.dp_size > 1 and cfg.runtime.zero_stage >= 1 and pc.comm_backend == "fused" and device.type == "cuda"
+                and cfg.model.dtype != "fp32"):
+            from .runtime.symm import SymmetricArena
+            n_est = sum(p.numel() + 64 for p in self.model.parameters()) + pc.dp_size * 1024
+            dp_arena = SymmetricArena.for_group(pc.dp_group, device, n_est * 6 + (16 << 20))
+        self.flat = FlatParams(self.model.named_checkpoint_parameters(), dp_size=pc.dp_size, dp_rank=pc.dp_rank, allocator=dp_arena)
         self.optimizer = build_optimizer(cfg, self.flat, pc)
         t = cfg.training
         self.scheduler = LRScheduler(t.lr_schedule, t.learning_rate, t.min_learning_rate, t.warmup_steps, t.total_steps)
@@ -141,6 +147,9 @@ class Trainer:
     def run(self, data_path: Optional[str] = None, max_steps: Optional[int] = None) -> List[float]:
         cfg = self.cfg
         loader = self.make_loader(data_path)
+        if self.step > 0:
+            loader.skip(self.step * self.accum)      # resumed run: continue where the data stream stopped
+            self.epoch = loader.epoch
         losses: List[float] = []
         total = cfg.training.total_steps if max_steps is None else min(cfg.training.total_steps, self.step + max_steps)
         t_last, tok_last = time.time(), self.tokens_seen

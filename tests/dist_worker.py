@@ -102,6 +102,37 @@ def mode_tp(pc, dev, backend, dtype):
     dist.barrier()
 
 
+def mode_zero(dev, backend, dtype, stage):
+    """Data parallel with ZeRO sharding (dp = world, tp = 1) against one rank on the global batch."""
+    from elfa_b200 import native
+    from elfa_b200.parallel.mesh import ParallelContext
+    from elfa_b200.trainer import Trainer
+    pc = build_context(1, False, backend)
+    world = pc.dp_size
+    cfg = small_cfg(dtype, 1, backend)
+    cfg.runtime.zero_stage = stage
+    cfg.training.micro_batch_size = 2
+    cfg.training.global_batch_size = 2 * world
+    tr = Trainer(cfg, device=dev, pc=pc, telemetry=False)
+    losses = tr.run(max_steps=4)
+    if dev.type == "cuda":
+        assert native.status() == 0
+    if pc.rank == 0:
+        cfg1 = small_cfg(dtype, 1, "nccl")
+        cfg1.runtime.world_size = 1
+        cfg1.runtime.zero_stage = 0
+        cfg1.training.micro_batch_size = 2 * world
+        cfg1.training.global_batch_size = 2 * world
+        tr1 = Trainer(cfg1, device=dev, pc=ParallelContext(), telemetry=False)
+        ref = tr1.run(max_steps=4)
+        tol = 2e-4 if dtype == "fp32" else 0.05
+        for a, b in zip(losses, ref):
+            assert abs(a - b) < tol * max(1.0, abs(b)), f"ZeRO losses {losses} differ from single-rank {ref}"
+        print(f"ZERO_OK stage={stage} backend={backend} fused={tr.optimizer.zero_fused is not None} "
+              f"losses={[round(x, 4) for x in losses]} ref={[round(x, 4) for x in ref]}")
+    dist.barrier()
+
+
 def mode_timeout(pc, dev):
     """Only rank 0 launches the fused all-gather GEMM; its peers never push, so the wait on their
     counters must give up after the limit and report it through the status word."""
@@ -137,9 +168,13 @@ def main():
     mode = sys.argv[1]
     backend = sys.argv[2] if len(sys.argv) > 2 else "nccl"
     dtype = sys.argv[3] if len(sys.argv) > 3 else "bf16"
-    use_cuda = torch.cuda.is_available() and mode != "tp_cpu"
+    use_cuda = torch.cuda.is_available() and mode not in ("tp_cpu", "zero_cpu")
     world = init_distributed("nccl" if use_cuda else "gloo")
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if use_cuda else torch.device("cpu")
+    if mode in ("zero", "zero_cpu"):
+        mode_zero(dev, backend, dtype, int(sys.argv[4]) if len(sys.argv) > 4 else 1)
+        dist.destroy_process_group()
+        return
     pc = build_context(world, True, backend)
     if mode == "fused":
         mode_fused(pc, dev)

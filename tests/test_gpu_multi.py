@@ -46,3 +46,12 @@ def test_missing_peer_signal_times_out_cleanly(cuda_device):
     r = _run(["timeout"], 29704)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "TIMEOUT_OK" in r.stdout
+
+
+@pytest.mark.parametrize("backend", ["nccl", "fused"])
+def test_zero1_data_parallel_matches_single_gpu(cuda_device, backend):
+    r = _run(["zero", backend, "bf16", "1"], 29705 if backend == "nccl" else 29706)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "ZERO_OK" in r.stdout
+    if backend == "fused":
+        assert "fused=True" in r.stdout
