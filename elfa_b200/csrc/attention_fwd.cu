@@ -13,8 +13,11 @@
 // While one warp group runs exp() on its S tile, the tensor core works on the other tile, so the
 // two pipelines hide each other. K_j and V_j are loaded once for both tiles.
 // Tensor memory: S_A | S_B | O_A | O_B (4 x 128 fp32 columns). P (bf16) goes through shared
-// memory in the 128-byte-swizzled K-major layout the MMA expects. O_j is read back per block and
-// accumulated in registers with the usual rescaling, so tensor memory never needs a rescale.
+// memory in the 128-byte-swizzled K-major layout the MMA expects. O accumulates in tensor memory
+// across the key blocks; the exponent uses a row maximum that is allowed to lag behind the true
+// one by up to 2^8, and only when a row's maximum grows by more than that is O rescaled in
+// tensor memory (tcgen05.ld / multiply / tcgen05.st), which is rare after the first blocks. Each
+// S row is read from tensor memory once.
 // Every wait is bounded (status word + abort flag), as in the GEMM.
 #include "common.cuh"
 #include "elfa_native.h"
@@ -126,13 +129,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
         }
         tc_commit(bar(BAR_SFULL0 + t));
       };
-      auto issue_o = [&](int t) {  // O_t(j) = P_t V
+      auto issue_o = [&](int t, int j) {  // O_t += P_t V_j
         const uint32_t pb = sbase + L::P_OFF + t * 2 * SUB_BYTES, vb = sbase + L::V_OFF;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t poff = (kk / 4) * SUB_BYTES + (kk % 4) * 32;
           tc_mma_f16(TM_O[t], make_smem_desc(pb + poff, 16, 1024, 2), make_smem_desc(vb + kk * 2048, SUB_BYTES, 1024, 2), idesc_o,
-                     kk != 0);
+                     (j | kk) != 0);
         }
         tc_commit(bar(BAR_OFULL0 + t));
       };
@@ -149,7 +152,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
         if (j < n_a) {
           if (!mbar_wait(bar(BAR_PREADY0), ph, abort_flag, p.status)) break;
           tc_fence_after();
-          issue_o(0);
+          issue_o(0, j);
           if (j + 1 < n_a) {
             if (!mbar_wait(bar(BAR_KFULL), ph ^ 1, abort_flag, p.status)) break;
             tc_fence_after();
@@ -158,7 +161,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
         }
         if (!mbar_wait(bar(BAR_PREADY1), ph, abort_flag, p.status)) break;
         tc_fence_after();
-        issue_o(1);
+        issue_o(1, j);
         tc_commit(bar(BAR_VFREE));
         if (j + 1 < n_b) {
           if (!mbar_wait(bar(BAR_KFULL), ph ^ 1, abort_flag, p.status)) break;
@@ -178,10 +181,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
     const int row = tile * 128 + row_local;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t p_row = sbase + L::P_OFF + t * 2 * SUB_BYTES + row_local * 128;
-    float m = -INFINITY, l = 0.f;
-    float o[HDP];
-#pragma unroll
-    for (int i = 0; i < HDP; ++i) o[i] = 0.f;
+    float m = -INFINITY, l = 0.f;   // m: the maximum used in the exponent (may lag the true maximum)
     bool ok = true;
     for (int j = 0; j < n_t; ++j) {
       const uint32_t ph = j & 1;
@@ -192,78 +192,101 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       const int key0 = j * 128;
       const int limit = p.causal ? row : (p.S - 1);       // last key this row may see
       const bool need_mask = key0 + 127 > (p.causal ? tile * 128 : p.S - 1);
-      // pass 1: row maximum
+      // the whole S row: four loads in flight, one wait
+      uint32_t r[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(TM_S[t] + lane_addr + c * 32, r[c]);
+      tmem_ld_wait();
       float mx = -INFINITY;
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(TM_S[t] + lane_addr + c * 32, r);
-        tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(r[i]);
-          if (need_mask && key0 + c * 32 + i > limit) s = -INFINITY;
-          mx = fmaxf(mx, s);
+          float sv = __uint_as_float(r[c][i]) * p.scale_log2;
+          if (need_mask && key0 + c * 32 + i > limit) sv = -INFINITY;
+          r[c][i] = __float_as_uint(sv);
+          mx = fmaxf(mx, sv);
         }
       }
-      const float m_new = fmaxf(m, mx * p.scale_log2);
-      const float alpha = fast_exp2(m - m_new);
-      // pass 2: probabilities -> bf16 P tile in shared memory, row sum
-      float lsum = 0.f;
+      if (j == 0) {
+        m = mx;
+      } else {
+        const bool grow = mx - m > 8.f;
+        if (__any_sync(0xffffffffu, grow)) {
+          // rescale this warp's O rows in tensor memory; the previous P V must have landed
+          ok = mbar_wait(bar(BAR_OFULL0 + t), (j - 1) & 1, abort_flag, p.status);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          const float m_new = grow ? mx : m;
+          const float alpha = fast_exp2(m - m_new);
 #pragma unroll 1
+          for (int c = 0; c < HDP / 32; ++c) {
+            uint32_t q[32];
+            tmem_ld32(TM_O[t] + lane_addr + c * 32, q);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) q[i] = __float_as_uint(__uint_as_float(q[i]) * alpha);
+            tmem_st32(TM_O[t] + lane_addr + c * 32, q);
+          }
+          tmem_st_wait();
+          l *= alpha;
+          m = m_new;
+        }
+      }
+      float lsum = 0.f;
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(TM_S[t] + lane_addr + c * 32, r);
-        tmem_ld_wait();
-        float pr[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float e = fast_exp2(__uint_as_float(r[i]) * p.scale_log2 - m_new);
-          if (need_mask && key0 + c * 32 + i > limit) e = 0.f;
-          pr[i] = e;
+          const float e = fast_exp2(__uint_as_float(r[c][i]) - m);
           lsum += e;
+          r[c][i] = __float_as_uint(e);
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           const int q8 = c * 4 + g;  // 16-byte chunk index along the 128 keys
           const uint32_t addr = p_row + (q8 >> 3) * SUB_BYTES + (((q8 & 7) ^ (row_local & 7)) << 4);
-          const uint32_t w0 = pack_bf16(pr[g * 8 + 0], pr[g * 8 + 1]), w1 = pack_bf16(pr[g * 8 + 2], pr[g * 8 + 3]);
-          const uint32_t w2 = pack_bf16(pr[g * 8 + 4], pr[g * 8 + 5]), w3 = pack_bf16(pr[g * 8 + 6], pr[g * 8 + 7]);
+          const uint32_t w0 = pack_bf16(__uint_as_float(r[c][g * 8 + 0]), __uint_as_float(r[c][g * 8 + 1]));
+          const uint32_t w1 = pack_bf16(__uint_as_float(r[c][g * 8 + 2]), __uint_as_float(r[c][g * 8 + 3]));
+          const uint32_t w2 = pack_bf16(__uint_as_float(r[c][g * 8 + 4]), __uint_as_float(r[c][g * 8 + 5]));
+          const uint32_t w3 = pack_bf16(__uint_as_float(r[c][g * 8 + 6]), __uint_as_float(r[c][g * 8 + 7]));
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
         }
       }
-      l = l * alpha + lsum;
-      m = m_new;
+      l += lsum;
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(bar(BAR_PREADY0 + t));
-#pragma unroll
-      for (int i = 0; i < HDP; ++i) o[i] *= alpha;
-      ok = mbar_wait(bar(BAR_OFULL0 + t), ph, abort_flag, p.status);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < HDP / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(TM_O[t] + lane_addr + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(r[i]);
-      }
     }
-    if (ok && n_t > 0 && row < p.S) {
+    if (ok && n_t > 0) {
+      ok = mbar_wait(bar(BAR_OFULL0 + t), (n_t - 1) & 1, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok && n_t > 0) {
+      tc_fence_after();
       const float inv = 1.f / l;
       __nv_bfloat16* orow = p.O + (long long)row * p.o_stride_s + (long long)b * p.o_stride_b + (long long)h * p.hd;
+#pragma unroll 1
+      for (int c = 0; c < HDP / 32; ++c) {
+        uint32_t q[32];
+        tmem_ld32(TM_O[t] + lane_addr + c * 32, q);
+        tmem_ld_wait();
+        if (row < p.S) {
 #pragma unroll
-      for (int g = 0; g < HDP / 8; ++g) {
-        if (g * 8 < p.hd) {
-          uint4 v = make_uint4(pack_bf16(o[g * 8 + 0] * inv, o[g * 8 + 1] * inv), pack_bf16(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv),
-                               pack_bf16(o[g * 8 + 4] * inv, o[g * 8 + 5] * inv), pack_bf16(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv));
-          *reinterpret_cast<uint4*>(orow + g * 8) = v;
+          for (int g = 0; g < 4; ++g) {
+            const int d0 = c * 32 + g * 8;
+            if (d0 < p.hd) {
+              uint4 vv = make_uint4(pack_bf16(__uint_as_float(q[g * 8 + 0]) * inv, __uint_as_float(q[g * 8 + 1]) * inv),
+                                    pack_bf16(__uint_as_float(q[g * 8 + 2]) * inv, __uint_as_float(q[g * 8 + 3]) * inv),
+                                    pack_bf16(__uint_as_float(q[g * 8 + 4]) * inv, __uint_as_float(q[g * 8 + 5]) * inv),
+                                    pack_bf16(__uint_as_float(q[g * 8 + 6]) * inv, __uint_as_float(q[g * 8 + 7]) * inv));
+              *reinterpret_cast<uint4*>(orow + d0) = vv;
+            }
+          }
         }
       }
-      if (p.lse) p.lse[((long long)b * p.H + h) * p.S + row] = (m + log2f(l)) * 0.6931471805599453f;
+      if (row < p.S && p.lse) p.lse[((long long)b * p.H + h) * p.S + row] = (m + log2f(l)) * 0.6931471805599453f;
     }
   }
 

@@ -247,7 +247,7 @@ ELFA_API int elfa_norm_fwd(const void* x, const void* res, const void* w, const 
   const auto* B = static_cast<const __nv_bfloat16*>(b);
   auto* Y = static_cast<__nv_bfloat16*>(y);
   auto* S = static_cast<__nv_bfloat16*>(sum_out);
-  const bool warp_row = D <= 32 * NORM_MAX_VEC * 8 / 4;  // <= 1024: one warp per row
+  const bool warp_row = D <= 32 * NORM_MAX_VEC * 8;  // <= 4096: one warp per row, 16 independent 16-byte loads per lane
   const bool rms = kind == 1, has_res = res != nullptr;
 #define LAUNCH_FWD(TPR, RMS_, RES_)                                                                                     \
   norm_fwd_kernel<TPR, RMS_, RES_><<<(rows + (256 / TPR) - 1) / (256 / TPR), 256, 0, s>>>(X, R, W, B, Y, S, mean_out, rstd_out, \
