@@ -1,23 +1,25 @@
 // Attention backward on tcgen05, recompute style: only O and the row log-sum-exp are kept by
-// forward; the probabilities are rebuilt per [128 query x 128 key] block.
+// forward; the probabilities are rebuilt per [128 x 128] block of (query, key) pairs.
 //
 //   delta = rowsum(dO * O)                                    (small pre-pass)
-//   per block:  S = Q K^T, dP = dO V^T                         (tensor memory)
-//               P = exp(S*scale - lse), dS = P * (dP - delta) * scale   (registers -> bf16 in smem)
-//   MODE_DKV (CTA owns a key block, loops over query blocks):  dV += P^T dO,  dK += dS^T Q
-//   MODE_DQ  (CTA owns a query block, loops over key blocks):  dQ += dS K
-// Two passes instead of one keep every accumulator in tensor memory and make the result
-// deterministic (no floating-point atomics on dQ).
-//
-// No transposes are materialised: P / dS are written once as [query][key] swizzled tiles and read
-// by the MMAs either K-major (dS K) or MN-major (P^T dO, dS^T Q) through the descriptor only;
-// the same holds for the Q / K / dO tiles.
+//   MODE_DKV (CTA owns a key tile, loops over query tiles), everything transposed so that the key
+//   index runs along the tensor-memory lanes:
+//       S^T = K Q^T, dP^T = V dO^T                                 (tensor memory, fp32)
+//       P^T = exp(S^T*scale - lse[q]), dS^T = P^T * (dP^T - delta[q]) * scale  -> bf16, written back
+//       into tensor memory over the fp32 values they were computed from
+//       dV += P^T dO,  dK += dS^T Q                                 (A operand read from tensor memory)
+//   MODE_DQ  (CTA owns a query tile, loops over key tiles):
+//       S = Q K^T, dP = dO V^T;  dS -> bf16 in tensor memory;  dQ += dS K
+// P / dS never touch shared memory; the Q / K / V / dO tiles are used K-major or MN-major through
+// the descriptor only, so no transpose is materialised. The inner tiles are double buffered (TMA
+// runs one iteration ahead). Two passes keep every accumulator in tensor memory and make the
+// result deterministic (no floating-point atomics on dQ).
 //
 // reference: the op is defined by src/futhark/attention.fut:28-51; the reference ships no
 // attention backward at all.
 //
 // Roles per CTA (320 threads): warp 0 TMA, warp 1 MMA issue, warps 2-9 compute (warps w and w+4
-// share a tensor-memory lane quarter and split the 128 key columns in halves).
+// share a tensor-memory lane quarter and split the 128 columns in halves).
 #include "common.cuh"
 #include "elfa_native.h"
 
@@ -43,18 +45,17 @@ struct AttnBwdParams {
   unsigned int* status;
 };
 
-enum { BB_RES = 0, BB_INFULL, BB_INFREE, BB_SDP, BB_PDS, BB_ACC, BB_COUNT };
+enum { BB_RES = 0, BB_INFULL0, BB_INFULL1, BB_INFREE0, BB_INFREE1, BB_SDP, BB_PDS, BB_ACC, BB_COUNT };
 
 template <int HDP>
 struct BwdSmem {
   static constexpr int NSUB = HDP / 64;
   static constexpr int RES0 = 0;
   static constexpr int RES1 = RES0 + NSUB * SUBB;
-  static constexpr int IN0 = RES1 + NSUB * SUBB;
-  static constexpr int IN1 = IN0 + NSUB * SUBB;
-  static constexpr int P_OFF = IN1 + NSUB * SUBB;
-  static constexpr int DS_OFF = P_OFF + 2 * SUBB;
-  static constexpr int BAR_OFF = DS_OFF + 2 * SUBB;
+  static constexpr int IN0 = RES1 + NSUB * SUBB;           // [2 slots][NSUB]
+  static constexpr int IN1 = IN0 + 2 * NSUB * SUBB;        // [2 slots][NSUB]
+  static constexpr int VEC_OFF = IN1 + 2 * NSUB * SUBB;    // lse2 / delta of the inner query tile: [2 slots][2][128] floats
+  static constexpr int BAR_OFF = VEC_OFF + 2 * 2 * 128 * 4;
   static constexpr int TOTAL = BAR_OFF + BB_COUNT * 8 + 16;
   static constexpr int DYN = TOTAL + 1024;
 };
@@ -94,6 +95,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + BB_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  float* svec = reinterpret_cast<float*>(smem + L::VEC_OFF);
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int i) { return bar0 + 8u * i; };
@@ -121,90 +123,90 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  // fp32 S (or S^T) and dP (or dP^T); their bf16 successors P / dS overwrite the first 64 columns
   const uint32_t TM_S = tmem_base, TM_DP = tmem_base + 128, TM_ACC0 = tmem_base + 256, TM_ACC1 = tmem_base + 256 + HDP;
 
-  // tile roles: in DKV mode the resident pair is (K_j, V_j) and the inner pair (Q_i, dO_i);
-  // in DQ mode the resident pair is (Q_i, dO_i) and the inner pair (K_j, V_j).
-  const uint32_t sQ = sbase + (DKV ? L::IN0 : L::RES0), sDO = sbase + (DKV ? L::IN1 : L::RES1);
-  const uint32_t sK = sbase + (DKV ? L::RES0 : L::IN0), sV = sbase + (DKV ? L::RES1 : L::IN1);
-  const uint32_t sP = sbase + L::P_OFF, sDS = sbase + L::DS_OFF;
+  // resident pair: (K_j, V_j) in DKV mode, (Q_i, dO_i) in DQ mode; the inner pair is the other one
+  const uint32_t sRes0 = sbase + L::RES0, sRes1 = sbase + L::RES1;
+  auto sIn0 = [&](int slot) { return sbase + L::IN0 + slot * NSUB * SUBB; };
+  auto sIn1 = [&](int slot) { return sbase + L::IN1 + slot * NSUB * SUBB; };
 
   if (warp == 0) {
     if (lane == 0) {
-      auto load_qdo = [&](int tile, int bar_id) {
+      auto load_qdo = [&](uint32_t dq, uint32_t ddo, int tile, int bar_id) {
         for (int s = 0; s < NSUB; ++s) {
-          tma_load_4d(sQ + s * SUBB, &tmQKV, s * 64, 0 * p.H + h, b, tile * 128, bar(bar_id));
-          tma_load_4d(sDO + s * SUBB, &tmDO, s * 64, h, b, tile * 128, bar(bar_id));
+          tma_load_4d(dq + s * SUBB, &tmQKV, s * 64, 0 * p.H + h, b, tile * 128, bar(bar_id));
+          tma_load_4d(ddo + s * SUBB, &tmDO, s * 64, h, b, tile * 128, bar(bar_id));
         }
       };
-      auto load_kv = [&](int tile, int bar_id) {
+      auto load_kv = [&](uint32_t dk, uint32_t dv, int tile, int bar_id) {
         for (int s = 0; s < NSUB; ++s) {
-          tma_load_4d(sK + s * SUBB, &tmQKV, s * 64, 1 * p.H + h, b, tile * 128, bar(bar_id));
-          tma_load_4d(sV + s * SUBB, &tmQKV, s * 64, 2 * p.H + h, b, tile * 128, bar(bar_id));
+          tma_load_4d(dk + s * SUBB, &tmQKV, s * 64, 1 * p.H + h, b, tile * 128, bar(bar_id));
+          tma_load_4d(dv + s * SUBB, &tmQKV, s * 64, 2 * p.H + h, b, tile * 128, bar(bar_id));
         }
       };
       mbar_expect_tx(bar(BB_RES), 2 * NSUB * SUBB);
-      if (DKV) load_kv(outer, BB_RES); else load_qdo(outer, BB_RES);
+      if (DKV) load_kv(sRes0, sRes1, outer, BB_RES); else load_qdo(sRes0, sRes1, outer, BB_RES);
       for (int it = 0; it < n_iter; ++it) {
-        if (it > 0 && !mbar_wait(bar(BB_INFREE), (it - 1) & 1, abort_flag, p.status)) break;
-        mbar_expect_tx(bar(BB_INFULL), 2 * NSUB * SUBB);
-        if (DKV) load_qdo(in_begin + it, BB_INFULL); else load_kv(in_begin + it, BB_INFULL);
+        const int slot = it & 1;
+        if (it >= 2 && !mbar_wait(bar(BB_INFREE0 + slot), ((it >> 1) - 1) & 1, abort_flag, p.status)) break;
+        mbar_expect_tx(bar(BB_INFULL0 + slot), 2 * NSUB * SUBB);
+        if (DKV) load_qdo(sIn0(slot), sIn1(slot), in_begin + it, BB_INFULL0 + slot);
+        else load_kv(sIn0(slot), sIn1(slot), in_begin + it, BB_INFULL0 + slot);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
-      constexpr uint32_t idesc_tt = make_idesc_bf16(128, HDP, true, true);    // P^T dO, dS^T Q
-      constexpr uint32_t idesc_dq = make_idesc_bf16(128, HDP, false, true);   // dS K
+      constexpr uint32_t idesc_acc = make_idesc_bf16(128, HDP, false, true);   // A from tensor memory, B MN-major
       bool ok = mbar_wait(bar(BB_RES), 0, abort_flag, p.status);
       for (int it = 0; it < n_iter && ok; ++it) {
-        const uint32_t ph = it & 1;
-        if (!mbar_wait(bar(BB_INFULL), ph, abort_flag, p.status)) { ok = false; break; }
-        // S / dP of the previous iteration were consumed before BB_PDS completed (waited below)
+        const int slot = it & 1;
+        if (!mbar_wait(bar(BB_INFULL0 + slot), (it >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
+        // DKV: S^T = K Q^T, dP^T = V dO^T (A = resident);  DQ: S = Q K^T, dP = dO V^T (A = resident)
+        const uint32_t a0 = sRes0, a1 = sRes1, b0 = sIn0(slot), b1 = sIn1(slot);
 #pragma unroll
         for (int kk = 0; kk < HDP / 16; ++kk) {
           const uint32_t off = (kk / 4) * SUBB + (kk % 4) * 32;
-          tc_mma_f16(TM_S, make_smem_desc(sQ + off, 16, 1024, 2), make_smem_desc(sK + off, 16, 1024, 2), idesc_s, kk != 0);
+          tc_mma_f16(TM_S, make_smem_desc(a0 + off, 16, 1024, 2), make_smem_desc(b0 + off, 16, 1024, 2), idesc_s, kk != 0);
         }
 #pragma unroll
         for (int kk = 0; kk < HDP / 16; ++kk) {
           const uint32_t off = (kk / 4) * SUBB + (kk % 4) * 32;
-          tc_mma_f16(TM_DP, make_smem_desc(sDO + off, 16, 1024, 2), make_smem_desc(sV + off, 16, 1024, 2), idesc_s, kk != 0);
+          tc_mma_f16(TM_DP, make_smem_desc(a1 + off, 16, 1024, 2), make_smem_desc(b1 + off, 16, 1024, 2), idesc_s, kk != 0);
         }
         tc_commit(bar(BB_SDP));
-        if (!mbar_wait(bar(BB_PDS), ph, abort_flag, p.status)) { ok = false; break; }
+        if (!mbar_wait(bar(BB_PDS), it & 1, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
         if (DKV) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)   // dV[key, d] += sum_q P[q, key] dO[q, d]
-            tc_mma_f16(TM_ACC0, make_smem_desc(sP + kk * 2048, SUBB, 1024, 2), make_smem_desc(sDO + kk * 2048, SUBB, 1024, 2),
-                       idesc_tt, (it | kk) != 0);
+          for (int kk = 0; kk < 8; ++kk)   // dV[key, d] += sum_q P^T[key, q] dO[q, d]
+            tc_mma_f16_ts(TM_ACC0, TM_S + kk * 8, make_smem_desc(b1 + kk * 2048, SUBB, 1024, 2), idesc_acc, (it | kk) != 0);
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)   // dK[key, d] += sum_q dS[q, key] Q[q, d]
-            tc_mma_f16(TM_ACC1, make_smem_desc(sDS + kk * 2048, SUBB, 1024, 2), make_smem_desc(sQ + kk * 2048, SUBB, 1024, 2),
-                       idesc_tt, (it | kk) != 0);
+          for (int kk = 0; kk < 8; ++kk)   // dK[key, d] += sum_q dS^T[key, q] Q[q, d]
+            tc_mma_f16_ts(TM_ACC1, TM_DP + kk * 8, make_smem_desc(b0 + kk * 2048, SUBB, 1024, 2), idesc_acc, (it | kk) != 0);
         } else {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)   // dQ[q, d] += sum_key dS[q, key] K[key, d]
-            tc_mma_f16(TM_ACC0, make_smem_desc(sDS + (kk / 4) * SUBB + (kk % 4) * 32, 16, 1024, 2),
-                       make_smem_desc(sK + kk * 2048, SUBB, 1024, 2), idesc_dq, (it | kk) != 0);
+            tc_mma_f16_ts(TM_ACC0, TM_DP + kk * 8, make_smem_desc(b0 + kk * 2048, SUBB, 1024, 2), idesc_acc, (it | kk) != 0);
         }
-        tc_commit(bar(BB_INFREE));
+        tc_commit(bar(BB_INFREE0 + slot));
       }
       if (ok) tc_commit(bar(BB_ACC));
     }
   } else {
     // ---------------------------------------------------------------- compute warps
     const int cw = warp - 2;
+    const int ct = threadIdx.x - 64;              // 0..255 inside the compute group
     const int quarter = warp & 3;
-    const int half = cw >> 2;                     // which 64 key columns of the block
-    const int row_local = quarter * 32 + lane;    // query row inside the tile
+    const int half = cw >> 2;                     // which 64 columns of the block
+    const int row_local = quarter * 32 + lane;    // lane of tensor memory: key row (DKV) or query row (DQ)
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const float LOG2E = 1.4426950408889634f;
     bool ok = true;
     float lse2 = 0.f, dlt = 0.f;
-    bool row_ok = false;
+    bool row_ok = true;
     if (!DKV) {
       const int row = outer * 128 + row_local;
       row_ok = row < p.S;
@@ -214,52 +216,71 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
       }
     }
     for (int it = 0; it < n_iter; ++it) {
-      const uint32_t ph = it & 1;
       const int q_tile = DKV ? in_begin + it : outer;
       const int k_tile = DKV ? outer : in_begin + it;
+      float* vl = svec + (it & 1) * 256;          // [0,128) lse2, [128,256) delta of the inner query tile
       if (DKV) {
-        const int row = q_tile * 128 + row_local;
-        row_ok = row < p.S;
-        lse2 = row_ok ? p.lse[((long long)b * p.H + h) * p.S + row] * LOG2E : 0.f;
-        dlt = row_ok ? p.delta[((long long)b * p.H + h) * p.S + row] : 0.f;
+        const int qi = ct & 127;
+        const int qrow = q_tile * 128 + qi;
+        const long long idx = ((long long)b * p.H + h) * p.S + qrow;
+        if (ct < 128) vl[qi] = qrow < p.S ? p.lse[idx] * LOG2E : INFINITY;   // +inf -> exp2(-inf) = 0 for rows past the end
+        else vl[128 + qi] = qrow < p.S ? p.delta[idx] : 0.f;
+        named_bar_sync(1, 256);
       }
-      ok = mbar_wait(bar(BB_SDP), ph, abort_flag, p.status);
+      // After a timeout the loop keeps running without touching tensor memory so that every warp
+      // still reaches the named barriers below (the waits return immediately once the abort flag is up).
+      if (ok) ok = mbar_wait(bar(BB_SDP), it & 1, abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
       tc_fence_after();
       const bool diag = p.causal && q_tile == k_tile;
-#pragma unroll 1
+      uint32_t keep_p[32], keep_d[32];   // this thread's 64 columns as bf16 pairs (P / dS)
+#pragma unroll
       for (int c = 0; c < 2; ++c) {
+        if (!ok) break;
         const int col0 = half * 64 + c * 32;
         uint32_t rs[32], rd[32];
         tmem_ld32(TM_S + lane_addr + col0, rs);
         tmem_ld32(TM_DP + lane_addr + col0, rd);
         tmem_ld_wait();
-        float pv[32], dv[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = fast_exp2(__uint_as_float(rs[i]) * p.scale_log2 - lse2);
-          if (!row_ok || (diag && col0 + i > row_local)) e = 0.f;
-          pv[i] = e;
-          dv[i] = e * (__uint_as_float(rd[i]) - dlt) * p.scale;
-        }
+        for (int i = 0; i < 32; i += 2) {
+          float e[2], d[2];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int q8 = (col0 >> 3) + g;
-          const uint32_t off = (q8 >> 3) * SUBB + row_local * 128 + (((q8 & 7) ^ (row_local & 7)) << 4);
-          if (DKV) {
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sP + off), "r"(pack_bf16(pv[g * 8], pv[g * 8 + 1])),
-                         "r"(pack_bf16(pv[g * 8 + 2], pv[g * 8 + 3])), "r"(pack_bf16(pv[g * 8 + 4], pv[g * 8 + 5])),
-                         "r"(pack_bf16(pv[g * 8 + 6], pv[g * 8 + 7]))
-                         : "memory");
+          for (int u = 0; u < 2; ++u) {
+            const int col = col0 + i + u;
+            const float l2 = DKV ? vl[col] : lse2;
+            const float dl = DKV ? vl[128 + col] : dlt;
+            float ev = fast_exp2(__uint_as_float(rs[i + u]) * p.scale_log2 - l2);
+            // DKV: lane = key, column = query -> masked when key > query; DQ: lane = query, column = key
+            const bool masked = DKV ? (diag && row_local > col) : (!row_ok || (diag && col > row_local));
+            if (masked) ev = 0.f;
+            e[u] = ev;
+            d[u] = ev * (__uint_as_float(rd[i + u]) - dl) * p.scale;
           }
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sDS + off), "r"(pack_bf16(dv[g * 8], dv[g * 8 + 1])),
-                       "r"(pack_bf16(dv[g * 8 + 2], dv[g * 8 + 3])), "r"(pack_bf16(dv[g * 8 + 4], dv[g * 8 + 5])),
-                       "r"(pack_bf16(dv[g * 8 + 6], dv[g * 8 + 7]))
-                       : "memory");
+          keep_p[c * 16 + (i >> 1)] = pack_bf16(e[0], e[1]);
+          keep_d[c * 16 + (i >> 1)] = pack_bf16(d[0], d[1]);
         }
       }
-      fence_proxy_async();
+      // The bf16 results go back into tensor memory on top of fp32 columns: a row's 128 values take
+      // 64 columns, so the upper half lands on columns the partner warp (other half, same lanes) was
+      // reading. All 256 compute threads therefore finish their loads before anyone stores.
+      tc_fence_before();
+      named_bar_sync(1, 256);
+      tc_fence_after();
+      if (ok) {
+        uint32_t t0[16], t1[16];
+        if (DKV) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) { t0[i] = keep_p[i]; t1[i] = keep_p[16 + i]; }
+          tmem_st16(TM_S + lane_addr + half * 32, t0);
+          tmem_st16(TM_S + lane_addr + half * 32 + 16, t1);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { t0[i] = keep_d[i]; t1[i] = keep_d[16 + i]; }
+        tmem_st16(TM_DP + lane_addr + half * 32, t0);
+        tmem_st16(TM_DP + lane_addr + half * 32 + 16, t1);
+        tmem_st_wait();
+      }
       tc_fence_before();
       mbar_arrive(bar(BB_PDS));
     }

@@ -442,10 +442,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int i = 1; i <= cm.world; ++i) {
       const int peer = (cm.rank + i) % cm.world;
       __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(cm.peer_xfull[peer]) + (long long)cm.rank * cm.rows_per_rank * p.K;
-      for (long long v = lo + t; v < hi; v += 64) {
-        const long long r = v / vec_per_row, cv = v - r * vec_per_row;
-        const uint4 q = *reinterpret_cast<const uint4*>(cm.x_local + r * cm.ldx + cv * 8);
-        *reinterpret_cast<uint4*>(dst + r * p.K + cv * 8) = q;
+      // eight independent 16-byte loads in flight per thread, then the eight peer stores
+      for (long long v0 = lo + t; v0 < hi; v0 += 64 * 8) {
+        uint4 q[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const long long v = v0 + u * 64;
+          if (v < hi) {
+            const long long r = v / vec_per_row, cv = v - r * vec_per_row;
+            q[u] = *reinterpret_cast<const uint4*>(cm.x_local + r * cm.ldx + cv * 8);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const long long v = v0 + u * 64;
+          if (v < hi) {
+            const long long r = v / vec_per_row, cv = v - r * vec_per_row;
+            *reinterpret_cast<uint4*>(dst + r * p.K + cv * 8) = q[u];
+          }
+        }
       }
       __threadfence_system();
       named_bar_sync(1, 64);
