@@ -137,6 +137,12 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, uint32_t src
                ::"l"(tm), "r"(src), "r"(x), "r"(y)
                : "memory");
 }
+// TMA: 2-D tiled reduce-add shared -> global (global += shared), element type from the tensor map.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* tm, uint32_t src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(tm), "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {

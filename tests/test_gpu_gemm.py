@@ -94,3 +94,29 @@ def test_linear_autograd(cuda_device):
     assert (y.float() - yr).abs().max() < 0.05
     assert (x.grad.float() - xr.grad).abs().max() < 0.1
     assert (w.grad.float() - wr.grad).abs().max() < 0.02 * (256 ** 0.5) + 0.3
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 4096, 16384), (4096, 1536, 8192), (1376, 4096, 4096)])
+def test_weight_gradient_split_k_accumulate(cuda_device, M, N, K):
+    # fp32 accumulate output with few tiles: the kernel splits K over several CTAs and adds atomically
+    a, b = _mk(M, N, K, True, True, cuda_device, seed=5)
+    acc = torch.randn(M, N, device=cuda_device)
+    acc0 = acc.clone()
+    ops.gemm(a, b, a_mn=True, b_mn=True, out=acc, accumulate=True)
+    ref = _ref(a, b, True, True) + acc0
+    err = (acc - ref).abs().max().item()
+    assert err < 0.01 * (K ** 0.5) + 0.05, err
+    assert native.status() == 0
+
+
+def test_staged_epilogue_tails_and_bias_gelu(cuda_device):
+    # plain bf16 outputs go through the shared-memory + TMA-store epilogue: odd M / N tails, bias, GELU
+    for (M, N, K) in [(200, 96, 136), (130, 1376, 64), (1000, 264, 512)]:
+        a, b = _mk(M, N, K, False, True, cuda_device, seed=6)
+        bias = torch.randn(N, device=cuda_device).to(torch.bfloat16)
+        out = torch.full((M + 8, N), 7.0, dtype=torch.bfloat16, device=cuda_device)   # guard rows must stay untouched
+        ops.gemm(a, b, b_mn=True, out=out[:M], bias=bias, gelu=True)
+        ref = ops.gelu_tanh_ref(_ref(a, b, False, True) + bias.float())
+        _close(out[:M], ref, K)
+        assert torch.all(out[M:] == 7.0)
+    assert native.status() == 0
