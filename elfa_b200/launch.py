@@ -1,0 +1,78 @@
+"""Single-node multi-GPU launcher: one process per GPU through ``torch.distributed.run``.
+
+    python -m elfa_b200.launch --gpus 8 train --config configs/train.yaml [--resume latest]
+    python -m elfa_b200.launch --gpus 1 smoke-test
+
+Plays the role of the reference's cloud launcher (reference: ``cloud/modal/train.py:198-339`` - an
+8-GPU job that shells out to the trainer binary with ``NCCL_DEBUG=INFO``,
+``NCCL_ASYNC_ERROR_HANDLING=1`` and resolves ``latest`` / the highest ``step_N`` checkpoint,
+``:84-124``) for a plain machine: it checks the GPU count, sets the environment, resolves
+``--resume latest`` against the configured checkpoint directory and starts the ranks on 127.0.0.1.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import socket
+import subprocess
+import sys
+from typing import List
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def resolve_resume(argv: List[str]) -> List[str]:
+    """Replaces ``--resume latest`` by the newest checkpoint of the config's checkpoint directory."""
+    if "--resume" not in argv:
+        return argv
+    i = argv.index("--resume")
+    if i + 1 >= len(argv) or argv[i + 1] != "latest":
+        return argv
+    from .checkpoint.manager import resolve_checkpoint
+    from .config import Config
+    ckdir = None
+    if "--checkpoint-dir" in argv:
+        ckdir = argv[argv.index("--checkpoint-dir") + 1]
+    elif "--config" in argv:
+        ckdir = Config.from_file(argv[argv.index("--config") + 1], env_override=False).checkpoint.dir
+    if not ckdir:
+        raise SystemExit("--resume latest needs --config or --checkpoint-dir")
+    out = list(argv)
+    out[i + 1] = resolve_checkpoint(ckdir)
+    return out
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--gpus", type=int, default=0, help="processes to start (0 = all visible GPUs)")
+    ap.add_argument("--port", type=int, default=0)
+    ap.add_argument("--nccl-debug", default="WARN")
+    ap.add_argument("rest", nargs=argparse.REMAINDER, help="elfa_b200 command line (train --config ...)")
+    a = ap.parse_args(argv)
+    if not a.rest:
+        ap.error("missing command, e.g. train --config configs/train.yaml")
+    import torch
+    n_visible = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    n = a.gpus or max(n_visible, 1)
+    if n_visible and n > n_visible:
+        raise SystemExit(f"--gpus {n} requested but only {n_visible} GPUs are visible")
+    rest = resolve_resume(a.rest)
+    env = dict(os.environ)
+    env.setdefault("NCCL_DEBUG", a.nccl_debug)
+    env.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "1")
+    env.setdefault("CUDA_DEVICE_ORDER", "PCI_BUS_ID")
+    env.setdefault("OMP_NUM_THREADS", "4")
+    if n == 1:
+        cmd = [sys.executable, "-m", "elfa_b200", *rest]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+               "--master-port", str(a.port or _free_port()), "-m", "elfa_b200", *rest]
+    return subprocess.call(cmd, env=env)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,137 @@
+"""Host / NVMe offload of tensors with asynchronous copies.
+
+reference: ``src/distributed/zero_sharding.zig:183-247`` (``offloadToCPU`` synchronous D2H,
+``offloadToNVMe`` / ``loadFromNVMe`` seek + write / read of one file, ``asyncOffload`` /
+``asyncPrefetch`` through a 1 GiB pinned staging buffer on per-GPU streams), ``src/io.zig:5-152``
+(``AsyncIO``: queued file reads / writes with pinned buffers), YAML flags ``runtime.cpu_offload``,
+``runtime.nvme_offload``, ``runtime.nvme_path``.
+
+``HostOffloader`` keeps a pinned mirror per registered tensor and moves data on a side stream;
+``NvmeStore`` persists mirrors to one file per tensor with positional I/O on a worker thread.
+With 180 GB per GPU the benchmark configurations never need this; it exists for larger models.
+"""
+from __future__ import annotations
+
+import os
+import queue
+import threading
+from typing import Dict, Optional
+
+import torch
+
+
+class HostOffloader:
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.cuda = device.type == "cuda"
+        self.stream = torch.cuda.Stream(device) if self.cuda else None
+        self.mirrors: Dict[str, torch.Tensor] = {}
+        self.events: Dict[str, object] = {}
+
+    def register(self, name: str, t: torch.Tensor) -> None:
+        m = torch.empty(t.shape, dtype=t.dtype, device="cpu")
+        if self.cuda:
+            m = m.pin_memory()
+        self.mirrors[name] = m
+
+    def offload(self, name: str, t: torch.Tensor, non_blocking: bool = True) -> None:
+        """device → pinned host. The copy runs on the side stream after the producer stream's work."""
+        if name not in self.mirrors:
+            self.register(name, t)
+        if not self.cuda:
+            self.mirrors[name].copy_(t)
+            return
+        self.stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(self.stream):
+            self.mirrors[name].copy_(t, non_blocking=non_blocking)
+            ev = torch.cuda.Event()
+            ev.record(self.stream)
+        self.events[name] = ev
+
+    def prefetch(self, name: str, out: torch.Tensor) -> None:
+        """pinned host → device on the side stream; call :meth:`wait` before using ``out``."""
+        if not self.cuda:
+            out.copy_(self.mirrors[name])
+            return
+        with torch.cuda.stream(self.stream):
+            out.copy_(self.mirrors[name], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self.stream)
+        self.events[name] = ev
+
+    def wait(self, name: Optional[str] = None) -> None:
+        if not self.cuda:
+            return
+        if name is None:
+            torch.cuda.current_stream(self.device).wait_stream(self.stream)
+        elif name in self.events:
+            torch.cuda.current_stream(self.device).wait_event(self.events[name])
+
+    def synchronize(self) -> None:
+        if self.cuda:
+            self.stream.synchronize()
+
+
+class NvmeStore:
+    """One file per tensor under ``root``; writes and reads are queued to a worker thread."""
+
+    def __init__(self, root: str):
+        self.root = root
+        os.makedirs(root, exist_ok=True)
+        self._q: "queue.Queue" = queue.Queue()
+        self._err: Optional[BaseException] = None
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+
+    def _path(self, name: str) -> str:
+        return os.path.join(self.root, name.replace("/", "_") + ".bin")
+
+    def _run(self) -> None:
+        while True:
+            job = self._q.get()
+            if job is None:
+                return
+            kind, name, t, done = job
+            try:
+                buf = t.view(torch.uint8).numpy() if t.dtype != torch.bfloat16 else t.view(torch.int16).numpy().view("uint8")
+                if kind == "w":
+                    fd = os.open(self._path(name), os.O_WRONLY | os.O_CREAT | os.O_TRUNC, 0o644)
+                    try:
+                        os.pwrite(fd, buf.tobytes(), 0)
+                    finally:
+                        os.close(fd)
+                else:
+                    fd = os.open(self._path(name), os.O_RDONLY)
+                    try:
+                        data = os.pread(fd, buf.nbytes, 0)
+                    finally:
+                        os.close(fd)
+                    if len(data) != buf.nbytes:
+                        raise IOError(f"short read for {name}")
+                    buf.reshape(-1)[:] = memoryview(data)
+            except BaseException as e:      # noqa: BLE001 - surfaced by flush()
+                self._err = e
+            finally:
+                done.set()
+
+    def write(self, name: str, host_tensor: torch.Tensor) -> threading.Event:
+        done = threading.Event()
+        self._q.put(("w", name, host_tensor.contiguous(), done))
+        return done
+
+    def read(self, name: str, host_tensor: torch.Tensor) -> threading.Event:
+        done = threading.Event()
+        self._q.put(("r", name, host_tensor, done))
+        return done
+
+    def flush(self) -> None:
+        done = threading.Event()
+        self._q.put(("w", "__flush__", torch.zeros(1, dtype=torch.uint8), done))
+        done.wait()
+        if self._err is not None:
+            e, self._err = self._err, None
+            raise e
+
+    def close(self) -> None:
+        self._q.put(None)
+        self._t.join()

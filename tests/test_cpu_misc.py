@@ -1,0 +1,134 @@
+"""Descriptors, RNGs, layout helpers, optimizer-state quantisation, offload, sequence-parallel helpers (CPU)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from elfa_b200.parallel.descriptors import ParallelConfig, SequenceParallelConfig, ShardSpec, TensorParallelConfig, ZeroConfig, split_sizes
+from elfa_b200.quant import optstate
+from elfa_b200.runtime.offload import HostOffloader, NvmeStore
+from elfa_b200.utils.layout import HostMemoryPool, PaddingStrategy, TensorCoreTiles
+from elfa_b200.utils.rng import DeterministicRng, DistributedRng, PhiloxRng
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_shard_arithmetic():
+    assert ShardSpec(0, 4, 1).local_shape((128, 7)) == (32, 7)
+    assert SequenceParallelConfig(4, 1).local_range(1000) == (250, 250)
+    assert split_sizes(10, 4) == [3, 3, 2, 2] and ShardSpec(0, 4, 2).offset(10) == 6
+    z = ZeroConfig(stage=2, partitions=4, rank=1)
+    assert z.owner_of(0) == 0 and z.owner_of(1 << 20) == 1 and z.owner_of(5 << 20) == 1 and z.owns((1 << 20) + 5)
+    assert z.should_shard_optimizer() and z.should_shard_gradients() and not z.should_shard_params()
+    assert z.flat_range(4096) == (1024, 2048)
+    assert TensorParallelConfig(8, 3).spec(1).local_size(4096) == 512
+    p = ParallelConfig(dp_size=2, tp_size=4, dp_rank=1, tp_rank=2)
+    assert p.global_rank() == 6 and p.world_size() == 8
+    q = ParallelConfig.from_global_rank(6, dp=2, tp=4)
+    assert (q.dp_rank, q.tp_rank) == (1, 2)
+
+
+def test_rngs_are_deterministic_and_rank_streams_differ():
+    a, b = DeterministicRng(42), DeterministicRng(42)
+    assert [a.next_u32() for _ in range(5)] == [b.next_u32() for _ in range(5)]
+    assert DeterministicRng(1).next_u32() != DeterministicRng(2).next_u32()
+    r = DeterministicRng(7)
+    assert all(0 <= r.range(10) < 10 for _ in range(100)) and all(0.0 <= r.uniform() < 1.0 for _ in range(100))
+    xs = [r.normal() for _ in range(4000)]
+    m = sum(xs) / len(xs)
+    assert abs(m) < 0.1 and abs(sum((x - m) ** 2 for x in xs) / len(xs) - 1.0) < 0.15
+    items = list(range(20))
+    DeterministicRng(3).shuffle(items)
+    assert sorted(items) == list(range(20)) and items != list(range(20))
+    d0, d1 = DistributedRng(5, 0), DistributedRng(5, 1)
+    assert d0["data"].next_u32() != d1["data"].next_u32() and d0["init"].next_u32() != d0["dropout"].next_u32()
+    ph = PhiloxRng(123)
+    assert ph.at(9) == PhiloxRng(123).at(9) and ph.at(9) != ph.at(10)
+
+
+def test_layout_helpers_and_host_pool():
+    assert PaddingStrategy(128).padded_bytes(130) == 256 and PaddingStrategy(128).optimal_leading_dimension(1000, 2) == 1024
+    assert TensorCoreTiles().block_m == 128 and TensorCoreTiles().tmem_columns == 512
+    pool = HostMemoryPool(4096, 128)
+    a, b, c = pool.alloc(1000), pool.alloc(1000), pool.alloc(1000)
+    assert (a, b, c) == (0, 1024, 2048) and pool.bytes_in_use() == 3072
+    pool.release(b)
+    assert pool.alloc(512) == 1024                     # best fit reuses the hole
+    pool.release(a)
+    pool.release(c)
+    with pytest.raises(MemoryError):
+        pool.alloc(4096)
+    pool.release(1024)
+    assert pool.free == [(0, 4096)]                    # fully coalesced
+
+
+def test_optimizer_state_quantisation_bounds():
+    torch.manual_seed(0)
+    x = torch.randn(1000) * 3
+    q, s = optstate.quantize_int8_absmax(x)
+    assert (optstate.dequantize_int8_absmax(q, s) - x).abs().max() <= s * 0.5 + 1e-6
+    for bits in (8, 4):
+        codes, scale, zp, n = optstate.quantize_blockwise(x, bits, 128)
+        back = optstate.dequantize_blockwise(codes, scale, zp, n, bits, 128)
+        assert back.shape == x.shape and (back - x).abs().max() <= scale.max() * 0.5 + 1e-5
+        assert codes.numel() == (1024 if bits == 8 else 512)
+    assert optstate.fake_quantize_state(x, 32) is x and optstate.fake_quantize_state(x, 8).unique().numel() <= 255
+    u, s8, lo = optstate.quantize_dynamic_u8(x)
+    assert (optstate.dequantize_dynamic_u8(u, s8, lo) - x).abs().max() <= s8 * 0.5 + 1e-5
+
+
+def test_offload_roundtrips(tmp_path):
+    off = HostOffloader(torch.device("cpu"))
+    t = torch.randn(64, 32).to(torch.bfloat16)
+    off.offload("m", t)
+    out = torch.empty_like(t)
+    off.prefetch("m", out)
+    off.wait("m")
+    assert torch.equal(out, t)
+    store = NvmeStore(str(tmp_path / "nvme"))
+    store.write("m", off.mirrors["m"]).wait()
+    back = torch.empty_like(t)
+    store.read("m", back).wait()
+    store.flush()
+    store.close()
+    assert torch.equal(back, t)
+
+
+def test_sequence_parallel_helpers_over_gloo():
+    code = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, %r)
+from elfa_b200.parallel import sp
+from elfa_b200.ops import efla as eops
+dist.init_process_group("gloo")
+r, w = dist.get_rank(), dist.get_world_size()
+torch.manual_seed(0)
+x = torch.arange(2 * 10 * 3, dtype=torch.float32).reshape(2, 10, 3)
+loc = sp.split_sequence(x, r, w)
+assert torch.equal(sp.gather_sequence(loc), x)
+got = sp.ring_exchange(torch.full((2,), float(r)), 1)
+assert got[0].item() == (r - 1) %% w
+halo = sp.halo_from_left(loc, 2)
+want = torch.zeros(2, 2, 3) if r == 0 else x[:, sum(sp.ShardSpec(1, w, i).local_size(10) for i in range(r)) - 2:][:, :2]
+assert torch.equal(halo, want)
+k = torch.randn(1, 12, 2, 8) * 0.4; v = torch.randn(1, 12, 2, 8); beta = torch.tensor(0.9)
+kl, vl = sp.split_sequence(k, r, w), sp.split_sequence(v, r, w)
+s_in = sp.efla_cross_rank_state(kl, vl, beta)
+o_loc, _ = eops.efla_scan_ref(kl, vl, beta, s_in)
+o_full, _ = eops.efla_scan_ref(k, v, beta)
+assert (o_loc - sp.split_sequence(o_full, r, w)).abs().max() < 1e-4
+g = torch.ones(4 * w, 3) * (r + 1)
+assert torch.equal(sp.reduce_scatter_gradients(g), torch.full((4, 3), float(sum(range(1, w + 1)))))
+if r == 0: print("SP_OK")
+''' % ROOT
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
+           "--master-port", "29631", "-c", code]
+    # torch.distributed.run needs a script path: write it out
+    path = os.path.join("/tmp", "elfa_sp_worker.py")
+    with open(path, "w") as f:
+        f.write(code)
+    cmd = cmd[:-2] + [path]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES=""))
+    assert r.returncode == 0 and "SP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
