@@ -212,7 +212,8 @@ def main() -> int:
         out = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16 tensor-core GEMMs on MXFP8 fake-quantised operands (QAT), fp32 master weights / moments / grad accumulation",
+            "dtype": "bf16 (MXFP8 QAT: forward GEMMs multiply e4m3 payloads with ue8m0 block scales - block-scaled tensor-core MMA at 1 GPU, "
+                     "fake-quantised bf16 operands in the tensor-parallel kernels; backward GEMMs bf16; fp32 master weights / moments / grad accumulation)",
             "data": "synthetic Zipf(1.1) token ids (seed 3), random-init N(0,0.02) weights",
             "config": {"model": cfg.model.name, "layers": cfg.model.num_layers, "d_model": cfg.model.hidden_dim,
                        "heads": cfg.model.num_heads, "ffn": cfg.model.intermediate_dim, "vocab": cfg.model.vocab_size,

@@ -224,6 +224,7 @@ class QuantConfig:
     surrogate: str = field(default="straight_through", metadata=_enum(SURROGATES))
     optimizer_state_bits: int = 32
     amax_history: int = 16
+    block_scaled_gemm: bool = True   # mxfp8 forward GEMMs on the block-scaled tensor-core path (same values as fake-quant + bf16 GEMM)
 
 
 @dataclass

@@ -59,6 +59,11 @@ int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t ro
 
 int make_tmap_nd_bf16(CUtensorMap* out, const void* base, int ndim, const uint64_t* dims, const uint64_t* strides_bytes,
                       const uint32_t* box);
+// cached 2-D tiled map (128-byte swizzle) over a row-major matrix of 1-, 2- or 4-byte elements
+int shared_tmap(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld_elems,
+                uint32_t box_rows, uint32_t box_cols);
+int device_sm_count();
+
 
 #ifdef __CUDACC__
 // ----------------------------------------------------------------------------------------------

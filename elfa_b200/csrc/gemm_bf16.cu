@@ -729,6 +729,13 @@ int dispatch_layout(int a_mn, int b_mn, const CUtensorMap& tmA, const CUtensorMa
 
 }  // namespace
 
+// entry points for the other GEMM translation units (tensor-map cache, SM count)
+int shared_tmap(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld_elems,
+                uint32_t box_rows, uint32_t box_cols) {
+  return cached_tmap(out, base, elem_bytes, rows, cols, ld_elems, box_rows, box_cols);
+}
+int device_sm_count() { return sm_count(); }
+
 int pick_bn(int M, int N, int forced) {
   if (forced == 64 || forced == 128 || forced == 256) return forced;
   const int sms = sm_count();

@@ -1,0 +1,429 @@
+// Block-scaled MXFP8 GEMM for sm_100a: e4m3 operands with one ue8m0 scale per 32 contraction
+// elements, multiplied by tcgen05.mma.kind::mxf8f6f4.block_scale with the scale factors in tensor
+// memory, fp32 accumulation, bf16 output.
+//
+// The reference only has a one-thread-per-output fp8 kernel with a single scalar scale
+// (kernels/cuda/gemm_sm100.cu:74-112) and PTX stubs named quantize_mxfp8 / tensor_parallel_matmul_fp4
+// (src/ptx/tcgen05_kernels.ptx:183,482) that hold no tensor-core instruction; the MX block format itself
+// is src/tensor/dtype.zig:117-147 and src/optimizer/stable_qat.zig:52-130.
+//
+//   C[M,N] = epilogue( sum_k  (A[m,k] * 2^(sfa[m,k/32]-127)) * (B[n,k] * 2^(sfb[n,k/32]-127)) )
+//
+// Both operands are K-major e4m3 ([M,K] and [N,K] row-major). Scale factors are stored the way the
+// tensor core wants to read them: 512-byte atoms covering 128 rows x 4 K-blocks (128 K-elements),
+// byte (r % 32) * 16 + (r / 32) * 4 + kb inside an atom, atoms ordered [row block][K block]. One atom
+// is one 32-lane x 128-bit tcgen05.cp into 4 tensor-memory columns (replicated to the 4 lane quarters);
+// the k-th MMA of a 128-wide K tile selects byte k of those columns through the instruction descriptor.
+//
+// Roles per CTA (192 threads, persistent, one CTA per SM):
+//   warp 0   : producer - TMA loads of the A / B tiles (128-byte swizzle) and bulk copies of the scale atoms
+//   warp 1   : tensor-memory owner; one lane copies scales to tensor memory and issues the MMAs
+//   warps 2-5: epilogue (one 32-lane quarter each): tcgen05.ld -> bias / GELU -> bf16 -> global
+// Every wait is bounded (status word + abort flag), like the bf16 kernel.
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+#include "elfa_native.h"
+
+namespace elfa {
+namespace {
+
+constexpr int QBM = 128;       // tile rows
+constexpr int QBK = 128;       // K elements (= bytes) per stage: one 128-byte swizzle row
+constexpr int QUMMA_K = 32;    // K per instruction for 8-bit operands
+constexpr int Q_THREADS = 192;
+constexpr int SF_ATOM = 512;   // bytes of one scale atom (128 rows x 4 K-blocks)
+
+struct QParams {
+  int M, N, K;
+  __nv_bfloat16* C;
+  long long ldc;
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  int kt;            // K tiles (= scale atoms per row block)
+  int sfb_atoms;     // row blocks of the B scale tensor
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* preact;
+  long long ldpre;
+  unsigned flags;
+  unsigned int* status;
+  int tiles_m, tiles_n, group_m;
+};
+
+template <int BN, int STAGES>
+struct QSmem {
+  static constexpr int NATOM = BN <= 128 ? 1 : 2;         // B scale atoms per tile (BN = 192 starts at +0 or +64 rows of an atom)
+  static constexpr int A_BYTES = QBM * QBK;
+  static constexpr int B_BYTES = BN * QBK;
+  static constexpr int SF_BYTES = (1 + NATOM) * SF_ATOM;
+  static constexpr int SF_OFF = STAGES * (A_BYTES + B_BYTES);
+  static constexpr int BAR_OFF = SF_OFF + STAGES * SF_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 4;
+  static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16;
+  static constexpr int DYN = TOTAL + 1024;
+  static constexpr uint32_t STAGE_TX = A_BYTES + B_BYTES + SF_BYTES;
+};
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void q_tile_coords(const QParams& p, int tile, int& mb, int& nb) {
+  const int per_group = p.group_m * p.tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * p.group_m;
+  const int gsz = min(p.group_m, p.tiles_m - first_m);
+  const int r = tile - g * per_group;
+  mb = first_m + r % gsz;
+  nb = r / gsz;
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(Q_THREADS, 1)
+gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const QParams p) {
+  using L = QSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * L::A_BYTES;
+  uint8_t* sSF = smem + L::SF_OFF;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + L::NUM_BARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  // tensor memory: accumulator 0 at column 0, scale factors behind it, accumulator 1 at column 256
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t ACC_STRIDE = 256;
+  constexpr uint32_t SFA_COL = BN;          // 4 columns
+  constexpr uint32_t SFB_COL = BN + 4;      // 4 columns per atom
+  static_assert(BN % 16 == 0 && BN + 4 + 4 * L::NATOM <= 256, "tile does not fit the tensor-memory plan");
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = p.kt;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int mb, nb;
+        q_tile_coords(p, tile, mb, nb);
+        const int m0 = mb * QBM, n0 = nb * BN;
+        const int atom0 = n0 / 128;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status)) { ok = false; break; }
+          mbar_expect_tx(full_bar(s), L::STAGE_TX);
+          tma_load_2d(smem_u32(sA + s * L::A_BYTES), &tmA, kb * QBK, m0, full_bar(s));
+          tma_load_2d(smem_u32(sB + s * L::B_BYTES), &tmB, kb * QBK, n0, full_bar(s));
+          const uint32_t sf_dst = smem_u32(sSF + s * L::SF_BYTES);
+          bulk_load(sf_dst, p.sfa + ((long long)mb * p.kt + kb) * SF_ATOM, SF_ATOM, full_bar(s));
+#pragma unroll
+          for (int j = 0; j < L::NATOM; ++j) {
+            const int atom = min(atom0 + j, p.sfb_atoms - 1);   // past the end: rows are zero-filled, any finite scale will do
+            bulk_load(sf_dst + (1 + j) * SF_ATOM, p.sfb + ((long long)atom * p.kt + kb) * SF_ATOM, SF_ATOM, full_bar(s));
+          }
+        }
+      }
+      if (!ok) {
+        for (uint32_t j = it > (uint32_t)STAGES ? it - STAGES : 0; j < it; ++j) {
+          const long long t0 = clock64();
+          while (!mbar_try(full_bar(j % STAGES), (j / STAGES) & 1) && clock64() - t0 < 4000000) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ scale copies + MMA issue
+    if (lane == 0) {
+      uint32_t it = 0, tile_iter = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
+        int mb, nb;
+        q_tile_coords(p, tile, mb, nb);
+        const uint32_t sfb_shift = (uint32_t)((nb * BN) % 128) / 32;   // tile starts inside an atom: skip its first columns
+        const uint32_t buf = tile_iter & 1, bph = (tile_iter >> 1) & 1;
+        if (!mbar_wait(tempty_bar(buf), bph ^ 1, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * ACC_STRIDE;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(full_bar(s), ph, abort_flag, p.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(sA + s * L::A_BYTES);
+          const uint32_t b_base = smem_u32(sB + s * L::B_BYTES);
+          const uint32_t sf_base = smem_u32(sSF + s * L::SF_BYTES);
+          // scale atoms: 32 rows of 16 bytes, no swizzle, 8-row core matrices 128 bytes apart
+          tc_cp_32x128b_warpx4(tmem_base + SFA_COL, make_smem_desc(sf_base, 0, 128, 0));
+#pragma unroll
+          for (int j = 0; j < L::NATOM; ++j)
+            tc_cp_32x128b_warpx4(tmem_base + SFB_COL + 4 * j, make_smem_desc(sf_base + (1 + j) * SF_ATOM, 0, 128, 0));
+#pragma unroll
+          for (int k = 0; k < QBK / QUMMA_K; ++k) {
+            const uint64_t da = make_smem_desc(a_base + k * 32, 16, 1024, 2);
+            const uint64_t db = make_smem_desc(b_base + k * 32, 16, 1024, 2);
+            tc_mma_mxf8(tmem_d, da, db, make_idesc_mxf8(QBM, BN, k, k), (kb | k) != 0 ? 1u : 0u, tmem_base + SFA_COL,
+                        tmem_base + SFB_COL + sfb_shift);
+          }
+          tc_commit(empty_bar(s));
+        }
+        if (ok) tc_commit(tfull_bar(buf));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;
+    uint32_t tile_iter = 0;
+    const unsigned fl = p.flags;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_iter) {
+      int mb, nb;
+      q_tile_coords(p, tile, mb, nb);
+      const int m0 = mb * QBM, n0 = nb * BN;
+      const uint32_t buf = tile_iter & 1, bph = (tile_iter >> 1) & 1;
+      bool ok = mbar_wait(tfull_bar(buf), bph, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t tcol0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * ACC_STRIDE;
+      uint32_t rnext[32];
+      tmem_ld32(tcol0, rnext);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = rnext[j];
+        if (c + 1 < BN / 32) tmem_ld32(tcol0 + (c + 1) * 32, rnext);
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) continue;   // uniform across the warp
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (fl & ELFA_EPI_BIAS) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = col0 + g * 8;
+            if (col + 8 > p.N) continue;
+            float* w = v + g * 8;
+            if (fl & ELFA_EPI_STORE_PREACT) {
+              const uint4 o = make_uint4(pack_bf16(w[0], w[1]), pack_bf16(w[2], w[3]), pack_bf16(w[4], w[5]), pack_bf16(w[6], w[7]));
+              *reinterpret_cast<uint4*>(p.preact + (long long)row * p.ldpre + col) = o;
+            }
+            if (fl & ELFA_EPI_GELU) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) w[j] = gelu_tanh(w[j]);
+            }
+            const uint4 o = make_uint4(pack_bf16(w[0], w[1]), pack_bf16(w[2], w[3]), pack_bf16(w[4], w[5]), pack_bf16(w[6], w[7]));
+            *reinterpret_cast<uint4*>(p.C + (long long)row * p.ldc + col) = o;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(buf));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN, int STAGES>
+int launch_q(const CUtensorMap& tmA, const CUtensorMap& tmB, QParams p, cudaStream_t stream) {
+  using L = QSmem<BN, STAGES>;
+  auto kern = gemm_mxfp8_kernel<BN, STAGES>;
+  static bool configured = false;
+  if (!configured) {
+    ELFA_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
+    configured = true;
+  }
+  p.tiles_m = (p.M + QBM - 1) / QBM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  p.group_m = 8;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < device_sm_count() ? tiles : device_sm_count();
+  kern<<<grid, Q_THREADS, L::DYN, stream>>>(tmA, tmB, p);
+  ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
+  return ELFA_OK;
+}
+
+// ---- quantiser ------------------------------------------------------------------------------------
+// One thread per 32-element block of a row: payload e4m3, scale byte into the atom layout, and an
+// optional bf16 copy of the dequantised values (what a fake-quantised bf16 GEMM would multiply).
+__device__ __forceinline__ uint8_t mx_scale_q(float amax, float* scale, float* inv) {
+  int e = (int)((__float_as_uint(amax) >> 23) & 0xff) - 127 - 8;
+  if (amax == 0.f) e = -127;
+  e = max(-127, min(127, e));
+  *scale = __uint_as_float((uint32_t)(e + 127) << 23);
+  if (e == -127) *scale = 5.877471754111438e-39f;
+  *inv = e == -127 ? 1.7014118346046923e38f : __uint_as_float((uint32_t)(127 - e) << 23);
+  return (uint8_t)(e + 127);
+}
+
+__global__ void __launch_bounds__(256) mxfp8_quantize_gemm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                                                                  uint8_t* __restrict__ payload, uint8_t* __restrict__ sf,
+                                                                  __nv_bfloat16* __restrict__ deq, int rows, int cols, int kt) {
+  const int bpr = cols / 32;
+  const long long nblocks = (long long)rows * bpr;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long blk = (long long)blockIdx.x * blockDim.x + threadIdx.x; blk < nblocks; blk += stride) {
+    const int r = (int)(blk / bpr), kb = (int)(blk - (long long)r * bpr);
+    const uint4* src = reinterpret_cast<const uint4*>(x + (long long)r * ldx + kb * 32);
+    float f[32];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 v = src[i];
+      const uint32_t pv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        f[i * 8 + 2 * j] = bf16_lo(pv[j]);
+        f[i * 8 + 2 * j + 1] = bf16_hi(pv[j]);
+        amax = fmaxf(amax, fmaxf(fabsf(f[i * 8 + 2 * j]), fabsf(f[i * 8 + 2 * j + 1])));
+      }
+    }
+    float sc, inv;
+    const uint8_t sb = mx_scale_q(amax, &sc, &inv);
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      uint32_t acc = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc |= (uint32_t)__nv_cvt_float_to_fp8(f[i * 4 + j] * inv, __NV_SATFINITE, __NV_E4M3) << (8 * j);
+      w[i] = acc;
+    }
+    uint4* dst = reinterpret_cast<uint4*>(payload + (long long)r * cols + kb * 32);
+    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    sf[((long long)(r >> 7) * kt + (kb >> 2)) * SF_ATOM + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (kb & 3)] = sb;
+    if (deq != nullptr) {
+      uint4* dd = reinterpret_cast<uint4*>(deq + (long long)r * cols + kb * 32);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t word = w[i * 2 + (j >> 1)];
+          const uint32_t two = (word >> (16 * (j & 1))) & 0xffffu;
+          const float lo = __half2float(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)(two & 0xff), __NV_E4M3))) * sc;
+          const float hi = __half2float(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)(two >> 8), __NV_E4M3))) * sc;
+          o[j] = pack_bf16(lo, hi);
+        }
+        dd[i] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+}
+
+}  // namespace
+}  // namespace elfa
+
+using namespace elfa;
+
+// Bytes of the scale tensor that belongs to a [rows, cols] operand.
+ELFA_API long long elfa_mxfp8_sf_bytes(int rows, int cols) {
+  return (long long)((rows + 127) / 128) * ((cols + 127) / 128) * SF_ATOM;
+}
+
+// x [rows, cols] bf16 (row pitch ldx elements) -> payload [rows, cols] e4m3 (dense), scale atoms, optional
+// dequantised bf16 copy [rows, cols]. `sf` must be zero-filled by the caller when rows or cols are not
+// multiples of 128 (entries of the padding are not written).
+ELFA_API int elfa_mxfp8_quantize_gemm(const void* x, long long ldx, void* payload, void* sf, void* deq, int rows, int cols,
+                                      void* stream) {
+  ELFA_REQUIRE(x && payload && sf && rows > 0 && cols > 0, "mxfp8_quantize_gemm: bad arguments");
+  ELFA_REQUIRE(cols % 32 == 0 && ldx % 8 == 0, "mxfp8_quantize_gemm: cols must be a multiple of 32 and the pitch of 8");
+  const long long nb = (long long)rows * (cols / 32);
+  const int grid = (int)((nb + 255) / 256 < 148 * 16 ? (nb + 255) / 256 : 148 * 16);
+  mxfp8_quantize_gemm_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<uint8_t*>(payload), static_cast<uint8_t*>(sf),
+      static_cast<__nv_bfloat16*>(deq), rows, cols, (cols + 127) / 128);
+  ELFA_CUDA(cudaGetLastError());
+  count_launches(1);
+  return ELFA_OK;
+}
+
+// C[M,N] bf16 = epilogue(A[M,K] * B[N,K]^T), e4m3 payloads with ue8m0 block scales (see the layout above).
+// flags: ELFA_EPI_BIAS | ELFA_EPI_GELU | ELFA_EPI_STORE_PREACT.
+ELFA_API int elfa_gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N, int K,
+                             long long ldc, const void* bias, void* preact, long long ldpre, unsigned flags, int force_bn,
+                             void* stream) {
+  ELFA_REQUIRE(A && B && C && sfa && sfb, "gemm_mxfp8: null operand");
+  ELFA_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_mxfp8: empty problem");
+  ELFA_REQUIRE(K % 32 == 0 && N % 8 == 0 && ldc % 8 == 0, "gemm_mxfp8: K must be a multiple of 32, N and ldc of 8");
+  ELFA_REQUIRE(!(flags & ~(ELFA_EPI_BIAS | ELFA_EPI_GELU | ELFA_EPI_STORE_PREACT)), "gemm_mxfp8: unsupported epilogue flag");
+  ELFA_REQUIRE(!(flags & ELFA_EPI_BIAS) || bias, "gemm_mxfp8: bias flag without pointer");
+  ELFA_REQUIRE(!(flags & ELFA_EPI_STORE_PREACT) || (preact && ldpre % 8 == 0), "gemm_mxfp8: preact flag without pointer");
+  ELFA_REQUIRE((reinterpret_cast<uintptr_t>(sfa) & 15) == 0 && (reinterpret_cast<uintptr_t>(sfb) & 15) == 0,
+               "gemm_mxfp8: scale tensors must be 16-byte aligned");
+  unsigned int* st = status_word();
+  ELFA_REQUIRE(st != nullptr, "gemm_mxfp8: no status word");
+  const int BN = (force_bn == 128 || force_bn == 192) ? force_bn : (N <= 128 ? 128 : 192);
+  CUtensorMap tmA, tmB;
+  int rc = shared_tmap(&tmA, A, 1, (uint64_t)M, (uint64_t)K, (uint64_t)K, QBM, QBK);
+  if (rc != ELFA_OK) return rc;
+  rc = shared_tmap(&tmB, B, 1, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)BN, QBK);
+  if (rc != ELFA_OK) return rc;
+  QParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.C = static_cast<__nv_bfloat16*>(C);
+  p.ldc = ldc;
+  p.sfa = static_cast<const uint8_t*>(sfa);
+  p.sfb = static_cast<const uint8_t*>(sfb);
+  p.kt = (K + QBK - 1) / QBK;
+  p.sfb_atoms = (N + 127) / 128;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.preact = static_cast<__nv_bfloat16*>(preact);
+  p.ldpre = ldpre;
+  p.flags = flags;
+  p.status = st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (BN == 192) return launch_q<192, 5>(tmA, tmB, p, s);
+  return launch_q<128, 6>(tmA, tmB, p, s);
+}

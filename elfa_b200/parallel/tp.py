@@ -27,7 +27,7 @@ import torch.distributed as dist
 
 from .. import ops
 from ..ops.gemm import gemm
-from ..quant.qat import QuantSpec, cached_weight_quant, fake_quant
+from ..quant.qat import QuantSpec, cached_weight_operand, cached_weight_quant, fake_quant, use_block_scaled_gemm
 from .mesh import ParallelContext
 
 
@@ -239,14 +239,20 @@ class _QuantLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, act, quant):
         x2 = x.reshape(-1, x.shape[-1])
-        xq = fake_quant(x2, quant)
         wq = cached_weight_quant(w, quant)
-        pre = None
-        if act == "gelu":
-            pre = torch.empty((x2.shape[0], w.shape[1]), dtype=x2.dtype, device=x2.device)
-            y = gemm(xq, wq, b_mn=True, gelu=True, preact=pre, out_dtype=x2.dtype)
+        pre = torch.empty((x2.shape[0], w.shape[1]), dtype=x2.dtype, device=x2.device) if act == "gelu" else None
+        if use_block_scaled_gemm(x2, w, quant):
+            # e4m3 payloads + ue8m0 scales straight into the block-scaled MMA; the bf16 copy of the
+            # quantised activations (same values) is kept for the weight gradient
+            from ..ops.gemm_mxfp8 import gemm_mxfp8, quantize_mxfp8
+            x_op, xq = quantize_mxfp8(x2 if x2.is_contiguous() else x2.contiguous(), dequantized=True)
+            y = gemm_mxfp8(x_op, cached_weight_operand(w, quant), gelu=act == "gelu", preact=pre)
         else:
-            y = gemm(xq, wq, b_mn=True, out_dtype=x2.dtype)
+            xq = fake_quant(x2, quant)
+            if act == "gelu":
+                y = gemm(xq, wq, b_mn=True, gelu=True, preact=pre, out_dtype=x2.dtype)
+            else:
+                y = gemm(xq, wq, b_mn=True, out_dtype=x2.dtype)
         ctx.save_for_backward(xq, wq, pre)
         ctx.w_ref, ctx.shape = w, x.shape
         return y.view(*x.shape[:-1], w.shape[1])

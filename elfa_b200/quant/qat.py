@@ -34,6 +34,7 @@ class QuantSpec:
     temperature: float = 0.1
     threshold: float = 1.0
     outside_slope: float = 0.1
+    block_scaled_gemm: bool = True
 
     @property
     def enabled(self) -> bool:
@@ -41,7 +42,8 @@ class QuantSpec:
 
     @classmethod
     def from_config(cls, fmt: str, qcfg) -> "QuantSpec":
-        return cls(fmt=fmt, bits=qcfg.weight_bits, surrogate=qcfg.surrogate)
+        return cls(fmt=fmt, bits=qcfg.weight_bits, surrogate=qcfg.surrogate,
+                   block_scaled_gemm=bool(getattr(qcfg, "block_scaled_gemm", True)))
 
 
 _amax_buf = {}
@@ -67,6 +69,25 @@ def cached_weight_quant(w: torch.Tensor, spec: "QuantSpec") -> torch.Tensor:
     wq = fake_quant(w.detach(), spec, weight=True)
     _weight_cache[key] = (w, wq)
     return wq
+
+
+def cached_weight_operand(w: torch.Tensor, spec: "QuantSpec"):
+    """MXFP8 tensor-core operand of a ``[K, N]`` weight: payload ``[N, K]`` e4m3 with scales along K,
+    the same 32-element blocks as ``fake_quant(w, weight=True)``. Cached like the bf16 copy."""
+    key = (id(w), "mxfp8_operand")
+    hit = _weight_cache.get(key)
+    if hit is not None and hit[0] is w:
+        return hit[1]
+    from ..ops.gemm_mxfp8 import quantize_mxfp8
+    op, _ = quantize_mxfp8(w.detach().t().contiguous())
+    _weight_cache[key] = (w, op)
+    return op
+
+
+def use_block_scaled_gemm(x2: torch.Tensor, w: torch.Tensor, spec: Optional["QuantSpec"]) -> bool:
+    """True when the forward GEMM ``x2 [T, K] @ w [K, N]`` can run on the block-scaled MXFP8 path."""
+    return (spec is not None and spec.fmt == "mxfp8" and spec.block_scaled_gemm and x2.is_cuda and x2.dtype == torch.bfloat16
+            and w.dtype == torch.bfloat16 and x2.shape[1] % 32 == 0 and w.shape[1] % 8 == 0)
 
 
 def _scratch(device, n):

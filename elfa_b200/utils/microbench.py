@@ -54,7 +54,7 @@ def timed(fn, iters, warm=3, flush=True):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "norm", "norm_bwd", "xent", "adamw", "mxfp8"])
+    ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "norm", "norm_bwd", "xent", "adamw", "mxfp8", "gemm_mxfp8"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -93,6 +93,20 @@ def main(argv=None) -> int:
             ms2 = timed(ref, a.iters)
             line += f" | torch.matmul {ms2:.4f} ms {fl / ms2 / 1e9:.1f} TFLOP/s"
         print(line)
+    elif a.kernel == "gemm_mxfp8":
+        from ..ops import gemm_mxfp8 as q8
+        M, N, K = a.m, a.n, a.k
+        xq, _ = q8.quantize_mxfp8(torch.randn(M, K, device=dev).to(bf))
+        wq, _ = q8.quantize_mxfp8(torch.randn(N, K, device=dev).to(bf))
+        out = torch.empty(M, N, dtype=bf, device=dev)
+        ms = timed(lambda: q8.gemm_mxfp8(xq, wq, out=out), a.iters)
+        fl = 2.0 * M * N * K
+        print(f"gemm_mxfp8 {M}x{N}x{K}: {ms:.4f} ms  {fl / ms / 1e9:.1f} TFLOP/s  {fl / ms / 1e-3 / flops_peak:.3f} of {src} cuBLAS bf16 peak "
+              f"(block-scaled e4m3, nominal fp8 peak is 2x bf16)")
+        x = torch.randn(M, K, device=dev).to(bf)
+        ms = timed(lambda: q8.quantize_mxfp8(x, dequantized=True), a.iters)
+        by = M * K * (2 + 1 + 2)
+        print(f"mxfp8 quantise (payload + scales + bf16 copy) {M}x{K}: {ms:.4f} ms  {by / ms / 1e6:.1f} GB/s  {by / ms / 1e-3 / hbm:.3f} of {src} copy bandwidth")
     elif a.kernel in ("attn_fwd", "attn_bwd"):
         S, B, H, hd = a.seq, a.batch, a.heads, a.hd
         qkv = torch.randn(S, B, 3, H, hd, device=dev).to(bf)
