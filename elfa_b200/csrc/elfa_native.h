@@ -80,8 +80,9 @@ int elfa_attention_bwd(const void* qkv, long long stride_s, long long stride_b, 
 
 // ---- gemm_mxfp8.cu ------------------------------------------------------------------------------
 // Block-scaled MXFP8 tensor-core GEMM (e4m3 payloads, ue8m0 scales per 32 K-elements in 512-byte atoms)
-long long elfa_mxfp8_sf_bytes(int rows, int cols);
-int elfa_mxfp8_quantize_gemm(const void* x, long long ldx, void* payload, void* sf, void* deq, int rows, int cols, void* stream);
+long long elfa_mxfp8_sf_bytes(int rows, int cols, int b_operand);
+int elfa_mxfp8_quantize_gemm(const void* x, long long ldx, void* payload, void* sf, void* deq, int rows, int cols, int b_operand,
+                             void* stream);
 int elfa_gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N, int K, long long ldc,
                     const void* bias, void* preact, long long ldpre, unsigned flags, int force_bn, void* stream);
 

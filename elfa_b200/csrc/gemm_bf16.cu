@@ -32,6 +32,7 @@
 //            rank's receive slot [source rank] (peer stores), tiles of other owners first, and
 //            bumps the owner's counter. After its tiles every CTA helps to sum the slots of the
 //            rows this rank owns, in fixed rank order (deterministic), once all counters arrived.
+#include <algorithm>
 #include <mutex>
 #include <unordered_map>
 
@@ -150,12 +151,19 @@ __device__ __forceinline__ void tile_coords_comm(const GemmParams& p, const Comm
   nb = lt / tm_shard;
 }
 
-template <int BN, bool A_MN, bool B_MN, int STAGES, int COMM>
+// TWO: the CTAs of a 2-CTA cluster work as a pair on 256 x BN tiles (tcgen05 cta_group::2). Each CTA
+// loads its 128 rows of A and its half of B (BN / 2 rows), the even CTA issues one MMA for both, and
+// each CTA ends up with its 128 rows of the accumulator in its own tensor memory. Per CTA this
+// needs a third less shared-memory fill per FLOP than a 128 x BN tile. Plain GEMM only.
+template <int BN, bool A_MN, bool B_MN, int STAGES, int COMM, bool TWO = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmA2, const GemmParams p, const CommParams cm,
                  const __grid_constant__ OutMaps om) {
-  using L = SmemLayout<BN, STAGES>;
+  static_assert(!TWO || COMM == COMM_NONE, "CTA pairs are implemented for the plain GEMM only");
+  constexpr int BN_CTA = TWO ? BN / 2 : BN;   // rows of B this CTA keeps in shared memory
+  constexpr int TILE_M = TWO ? 2 * BM : BM;   // rows of one work unit
+  using L = SmemLayout<BN_CTA, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -173,6 +181,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   constexpr uint32_t TMEM_COLS = 2 * BN;  // 128 / 256 / 512: a power of two >= 32
+  const uint32_t cta_rank = TWO ? cluster_ctarank() : 0u;                       // position in the pair; 0 issues the MMAs
+  const int wid = TWO ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;               // work slot: one per CTA, or one per pair
+  const int wstride = TWO ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmA);
@@ -183,17 +194,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), 4);
+      mbar_init(tempty_bar(b), TWO ? 8 : 4);   // pair: the epilogue warps of both CTAs release the even CTA's barrier
     }
     *abort_flag = 0;
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
-    tmem_relinquish();
+    if (TWO) {
+      tmem_alloc_pair(smem_u32(tmem_holder), TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (TWO) cluster_sync_all();   // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
@@ -209,12 +226,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t it = 0;
       bool ok = true;
       int ready_shard = -1;
-      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+      for (int unit = wid; unit < num_units && ok; unit += wstride) {
         const int tile = unit / splits;
         const int kb0 = (unit - tile * splits) * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
         int mb, nb, shard;
         tile_coords_comm<COMM>(p, cm, tile, mb, nb, shard);
-        const int m0 = mb * BM, n0 = nb * BN;
+        const int m0 = mb * TILE_M + (int)cta_rank * BM, n0 = nb * BN;
         const bool own = COMM == COMM_AG && shard == cm.rank;
         if (COMM == COMM_AG && !own && shard != ready_shard) {
           // the shard was written by a peer GPU with ordinary stores: acquire its counter, then
@@ -227,9 +244,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status)) { ok = false; break; }
-          mbar_expect_tx(full_bar(s), L::A_BYTES + L::B_BYTES);
           const uint32_t a_dst = smem_u32(sA + s * L::A_BYTES);
           const uint32_t b_dst = smem_u32(sB + s * L::B_BYTES);
+          if (TWO) {
+            // both CTAs' copies complete on the even CTA's barrier, which expects the bytes of both
+            const uint32_t fb = map_to_cta(full_bar(s), 0);
+            if (cta_rank == 0) mbar_expect_tx(full_bar(s), 2 * (L::A_BYTES + L::B_BYTES));
+            const int nB = n0 + (int)cta_rank * BN_CTA;
+            if (!A_MN) {
+              tma_load_2d_pair(a_dst, &tmA, kb * BK, m0, fb);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(a_dst + j * 8192, &tmA, m0 + j * 64, kb * BK, fb);
+            }
+            if (!B_MN) {
+              tma_load_2d_pair(b_dst, &tmB, kb * BK, nB, fb);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN_CTA / 64; ++j) tma_load_2d_pair(b_dst + j * 8192, &tmB, nB + j * 64, kb * BK, fb);
+            }
+            continue;
+          }
+          mbar_expect_tx(full_bar(s), L::A_BYTES + L::B_BYTES);
           if (own) {
             tma_load_2d(a_dst, &tmA2, kb * BK, m0 - cm.rank * cm.rows_per_rank, full_bar(s));
           } else if (!A_MN) {
@@ -256,11 +292,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(TILE_M, BN, A_MN, B_MN);
       uint32_t it = 0, tile_iter = 0;
       bool ok = true;
-      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++tile_iter) {
+      for (int unit = wid; unit < num_units && ok; unit += wstride, ++tile_iter) {
         const int kb0 = (unit % splits) * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
         const uint32_t buf = tile_iter & 1, bph = (tile_iter >> 1) & 1;
         if (!mbar_wait(tempty_bar(buf), bph ^ 1, abort_flag, p.status)) { ok = false; break; }
@@ -281,11 +317,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                      : make_smem_desc(a_base + k * 32, 16, 1024, 2);
             const uint64_t db = B_MN ? make_smem_desc(b_base + k * 2048, 8192, 1024, 2)
                                      : make_smem_desc(b_base + k * 32, 16, 1024, 2);
-            tc_mma_f16(tmem_d, da, db, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
+            if (TWO) tc_mma_f16_pair(tmem_d, da, db, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
+            else tc_mma_f16(tmem_d, da, db, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
           }
-          tc_commit(empty_bar(s));  // frees the smem slot once these MMAs have read it
+          // frees the smem slot (in both CTAs of a pair) once these MMAs have read it
+          if (TWO) tc_commit_pair(empty_bar(s)); else tc_commit(empty_bar(s));
         }
-        if (ok) tc_commit(tfull_bar(buf));
+        if (ok) {
+          if (TWO) tc_commit_pair(tfull_bar(buf)); else tc_commit(tfull_bar(buf));
+        }
       }
     }
   } else if (warp < 6) {
@@ -294,11 +334,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t tile_iter = 0;
     const unsigned fl = p.flags;
     bool dead = false;
-    for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, ++tile_iter) {
+    for (int unit = wid; unit < num_units; unit += wstride, ++tile_iter) {
       const int tile = unit / splits;
       int mb, nb, shard;
       tile_coords_comm<COMM>(p, cm, tile, mb, nb, shard);
-      const int m0 = mb * BM, n0 = nb * BN;
+      const int m0 = mb * TILE_M + (int)cta_rank * BM, n0 = nb * BN;
       const uint32_t buf = tile_iter & 1, bph = (tile_iter >> 1) & 1;
       bool ok = !dead && mbar_wait(tfull_bar(buf), bph, abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
@@ -381,7 +421,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (cc == nchunk - 1) {   // accumulator fully read: hand the buffer back to the MMA warp
               tc_fence_before();
               __syncwarp();
-              if (lane == 0) mbar_arrive(tempty_bar(buf));
+              if (lane == 0) {
+                if (TWO) mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0)); else mbar_arrive(tempty_bar(buf));
+              }
             }
           }
           fence_proxy_async();
@@ -473,7 +515,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(buf));
+      if (lane == 0) {
+                if (TWO) mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0)); else mbar_arrive(tempty_bar(buf));
+              }
     }
   } else if (staged && warp == 6) {
     // ------------------------------------------------------------------ store warp
@@ -484,17 +528,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int CPT = f32 ? BN / 32 : BN / 64;             // chunks per tile
     const int ccols = f32 ? 32 : 64;                     // output columns per chunk
     int my_tiles = 0;
-    for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) ++my_tiles;
+    for (int unit = wid; unit < num_units; unit += wstride) ++my_tiles;
     const uint32_t total_chunks = (uint32_t)my_tiles * CPT;
     const uint32_t out0 = smem_u32(smem + L::OUT_OFF);
     const bool reduce_add = f32 && (p.flags & ELFA_EPI_ACCUM);
     int pend[2] = {-1, -1};                              // owners of the two most recent tiles
     uint32_t g = 0;
-    for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
+    for (int unit = wid; unit < num_units; unit += wstride) {
       const int tile = unit / splits;
       int mb, nb, shard;
       tile_coords_comm<COMM>(p, cm, tile, mb, nb, shard);
-      const int m0 = mb * BM, n0 = nb * BN;
+      const int m0 = mb * TILE_M + (int)cta_rank * BM, n0 = nb * BN;
       const int dst_row = COMM == COMM_RS ? cm.rank * cm.rows_per_rank + (m0 - shard * cm.rows_per_rank) : m0;
       const int dst_map = COMM == COMM_RS ? shard : 0;
       for (int cc = 0; cc < CPT; ++cc, ++g) {
@@ -611,9 +655,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   tc_fence_before();
   __syncthreads();
+  if (TWO) cluster_sync_all();   // the peer no longer reads this CTA's shared memory or signals its barriers
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (TWO) tmem_dealloc_pair(tmem_base, TMEM_COLS); else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -676,21 +721,27 @@ int sm_count() {
   return g_sm_count;
 }
 
-template <int BN, bool A_MN, bool B_MN, int COMM = COMM_NONE>
+template <int BN, bool A_MN, bool B_MN, int COMM = COMM_NONE, bool TWO = false>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int max_ctas, cudaStream_t stream,
                 const CUtensorMap* tmA2 = nullptr, const CommParams* comm = nullptr, const OutMaps* om = nullptr) {
-  constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
-  using L = SmemLayout<BN, STAGES>;
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, STAGES, COMM>;
+  constexpr int STAGES = TWO ? 6 : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
+  constexpr int TILE_M = TWO ? 2 * BM : BM;
+  using L = SmemLayout<TWO ? BN / 2 : BN, STAGES>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, STAGES, COMM, TWO>;
   constexpr int DYN = L::DYN_RS;   // every variant carries the two staging tiles of the TMA-store epilogue
   static bool configured = false;
   if (!configured) {
     ELFA_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN));
     configured = true;
   }
-  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_m = (p.M + TILE_M - 1) / TILE_M;
   p.tiles_n = (p.N + BN - 1) / BN;
-  p.group_m = 8;
+  {
+    // tile order: sweep over N inside groups of M tiles whose rows of A (about 32 MB) stay in L2
+    const long long rows = std::max(512LL, std::min(4096LL, (32LL << 20) / ((long long)p.K * 2)));
+    p.group_m = (int)std::max(1LL, rows / TILE_M);
+  }
+  if (TWO) max_ctas /= 2;    // work slots are CTA pairs
   const int num_kb_host = (p.K + BK - 1) / BK;
   p.splits = 1;
   if (COMM == COMM_NONE && (p.flags & (ELFA_EPI_ACCUM | ELFA_EPI_OUT_F32)) == (ELFA_EPI_ACCUM | ELFA_EPI_OUT_F32)) {
@@ -711,11 +762,34 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, in
   CommParams c{};
   if (comm) c = *comm;
   static const OutMaps no_maps{};
-  kern<<<grid, GEMM_THREADS, DYN, stream>>>(tmA, tmB, tmA2 ? *tmA2 : tmA, p, c,
-                                                                                     om ? *om : no_maps);
+  if (TWO) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * grid, 1, 1);
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = DYN;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    ELFA_CUDA(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmA2 ? *tmA2 : tmA, p, c, om ? *om : no_maps));
+  } else {
+    kern<<<grid, GEMM_THREADS, DYN, stream>>>(tmA, tmB, tmA2 ? *tmA2 : tmA, p, c, om ? *om : no_maps);
+  }
   ELFA_CUDA(cudaGetLastError());
   ::elfa::count_launches(1);
   return ELFA_OK;
+}
+
+int dispatch_pair(int a_mn, int b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int max_ctas,
+                  cudaStream_t stream, const OutMaps* om) {
+  if (!a_mn && !b_mn) return launch_gemm<256, false, false, COMM_NONE, true>(tmA, tmB, p, max_ctas, stream, nullptr, nullptr, om);
+  if (!a_mn && b_mn) return launch_gemm<256, false, true, COMM_NONE, true>(tmA, tmB, p, max_ctas, stream, nullptr, nullptr, om);
+  if (a_mn && !b_mn) return launch_gemm<256, true, false, COMM_NONE, true>(tmA, tmB, p, max_ctas, stream, nullptr, nullptr, om);
+  return launch_gemm<256, true, true, COMM_NONE, true>(tmA, tmB, p, max_ctas, stream, nullptr, nullptr, om);
 }
 
 template <int BN>
@@ -765,13 +839,18 @@ ELFA_API int elfa_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   unsigned int* st = status_word();
   ELFA_REQUIRE(st != nullptr, "gemm: no status word");
 
-  const int BN = pick_bn(M, N, force_bn);
+  // force_bn 512 selects the CTA-pair kernel (256 x 256 tiles per pair); by default it is used when the
+  // problem fills at least one wave of pairs with such tiles
+  const int pairs = sm_count() / 2;
+  const bool pair = force_bn == 512 ||
+                    (force_bn == 0 && N >= 256 && (long long)((M + 255) / 256) * ((N + 255) / 256) >= pairs && (max_ctas <= 0 || max_ctas >= sm_count()));
+  const int BN = pair ? 256 : pick_bn(M, N, force_bn);
   CUtensorMap tmA, tmB;
   int rc;
   if (!a_mn_major) rc = cached_tmap_bf16(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, BK);
   else rc = cached_tmap_bf16(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, 64);
   if (rc != ELFA_OK) return rc;
-  if (!b_mn_major) rc = cached_tmap_bf16(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN, BK);
+  if (!b_mn_major) rc = cached_tmap_bf16(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, pair ? BN / 2 : BN, BK);
   else rc = cached_tmap_bf16(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, 64);
   if (rc != ELFA_OK) return rc;
 
@@ -797,6 +876,7 @@ ELFA_API int elfa_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
     if (rc != ELFA_OK) return rc;
     p.staged = 2;
   }
+  if (pair) return dispatch_pair(a_mn_major, b_mn_major, tmA, tmB, p, ctas, s, &om);
   switch (BN) {
     case 256: return dispatch_layout<256>(a_mn_major, b_mn_major, tmA, tmB, p, ctas, s, &om);
     case 128: return dispatch_layout<128>(a_mn_major, b_mn_major, tmA, tmB, p, ctas, s, &om);

@@ -20,7 +20,18 @@
 //   warp 1   : tensor-memory owner; one lane copies scales to tensor memory and issues the MMAs
 //   warps 2-5: epilogue (one 32-lane quarter each): tcgen05.ld -> bias / GELU -> bf16 -> global
 // Every wait is bounded (status word + abort flag), like the bf16 kernel.
+//
+// TWO = true: the two CTAs of a cluster form a pair (tcgen05 cta_group::2) on a 256 x BN tile. Each CTA
+// loads its 128 rows of A, its half of B and the scales it needs (its rows of A, all columns of B); the
+// even CTA issues the scale copies and the MMAs for both. Shared-memory fill per FLOP drops by a third,
+// which is what bounds the single-CTA kernel (about 100 GB/s of L2 -> SM fill per SM, measured).
+//
+// Scale tensor of B is stored [K tile][row block] so that the atoms a tile needs are one contiguous copy.
 #include <cuda_fp8.h>
+
+#include <algorithm>
+#include <mutex>
+#include <unordered_map>
 
 #include "common.cuh"
 #include "elfa_native.h"
@@ -50,11 +61,11 @@ struct QParams {
   int tiles_m, tiles_n, group_m;
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool TWO>
 struct QSmem {
   static constexpr int NATOM = BN <= 128 ? 1 : 2;         // B scale atoms per tile (BN = 192 starts at +0 or +64 rows of an atom)
   static constexpr int A_BYTES = QBM * QBK;
-  static constexpr int B_BYTES = BN * QBK;
+  static constexpr int B_BYTES = (TWO ? BN / 2 : BN) * QBK;
   static constexpr int SF_BYTES = (1 + NATOM) * SF_ATOM;
   static constexpr int SF_OFF = STAGES * (A_BYTES + B_BYTES);
   static constexpr int BAR_OFF = SF_OFF + STAGES * SF_BYTES;
@@ -63,12 +74,6 @@ struct QSmem {
   static constexpr int DYN = TOTAL + 1024;
   static constexpr uint32_t STAGE_TX = A_BYTES + B_BYTES + SF_BYTES;
 };
-
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
 
 __device__ __forceinline__ void q_tile_coords(const QParams& p, int tile, int& mb, int& nb) {
   const int per_group = p.group_m * p.tiles_n;
@@ -80,10 +85,12 @@ __device__ __forceinline__ void q_tile_coords(const QParams& p, int tile, int& m
   nb = r / gsz;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool TWO>
 __global__ void __launch_bounds__(Q_THREADS, 1)
-gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const QParams p) {
-  using L = QSmem<BN, STAGES>;
+gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB, const QParams p) {
+  using L = QSmem<BN, STAGES, TWO>;
+  constexpr int TILE_M = TWO ? 2 * QBM : QBM;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -101,7 +108,12 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  // tensor memory: accumulator 0 at column 0, scale factors behind it, accumulator 1 at column 256
+  const uint32_t cta_rank = TWO ? cluster_ctarank() : 0u;
+  const int wid = TWO ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int wstride = TWO ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  // tensor memory: accumulator b at column 256 * b, one set of scale-factor columns behind each accumulator.
+  // K tiles alternate between the two sets, so the copy of the next tile's scales does not have to
+  // wait for the MMAs that still read the current ones.
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t ACC_STRIDE = 256;
   constexpr uint32_t SFA_COL = BN;          // 4 columns
@@ -111,23 +123,31 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
+    prefetch_tmap(&tmSFA);
+    prefetch_tmap(&tmSFB);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), 4);
+      mbar_init(tempty_bar(b), TWO ? 8 : 4);
     }
     *abort_flag = 0;
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
-    tmem_relinquish();
+    if (TWO) {
+      tmem_alloc_pair(smem_u32(tmem_holder), TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (TWO) cluster_sync_all();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
@@ -139,24 +159,33 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = wid; tile < num_tiles && ok; tile += wstride) {
         int mb, nb;
         q_tile_coords(p, tile, mb, nb);
-        const int m0 = mb * QBM, n0 = nb * BN;
-        const int atom0 = n0 / 128;
+        const int m0 = mb * TILE_M + (int)cta_rank * QBM, n0 = nb * BN;
+        const int mblk = m0 / QBM;               // row block of the A scales
+        const int atom0 = n0 / 128;              // first row block of the B scales (the tensor is padded by one atom)
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status)) { ok = false; break; }
-          mbar_expect_tx(full_bar(s), L::STAGE_TX);
-          tma_load_2d(smem_u32(sA + s * L::A_BYTES), &tmA, kb * QBK, m0, full_bar(s));
-          tma_load_2d(smem_u32(sB + s * L::B_BYTES), &tmB, kb * QBK, n0, full_bar(s));
+          const uint32_t a_dst = smem_u32(sA + s * L::A_BYTES), b_dst = smem_u32(sB + s * L::B_BYTES);
           const uint32_t sf_dst = smem_u32(sSF + s * L::SF_BYTES);
-          bulk_load(sf_dst, p.sfa + ((long long)mb * p.kt + kb) * SF_ATOM, SF_ATOM, full_bar(s));
-#pragma unroll
-          for (int j = 0; j < L::NATOM; ++j) {
-            const int atom = min(atom0 + j, p.sfb_atoms - 1);   // past the end: rows are zero-filled, any finite scale will do
-            bulk_load(sf_dst + (1 + j) * SF_ATOM, p.sfb + ((long long)atom * p.kt + kb) * SF_ATOM, SF_ATOM, full_bar(s));
+          // scale atoms are rows of 128 32-bit words in two tensor maps (no swizzle); rows past the end read as zero
+          const int sfa_row = mblk * p.kt + kb, sfb_row = kb * (p.sfb_atoms + 1) + atom0;
+          if (TWO) {
+            const uint32_t fb = map_to_cta(full_bar(s), 0);
+            if (cta_rank == 0) mbar_expect_tx(full_bar(s), 2 * L::STAGE_TX);
+            tma_load_2d_pair(a_dst, &tmA, kb * QBK, m0, fb);
+            tma_load_2d_pair(b_dst, &tmB, kb * QBK, n0 + (int)cta_rank * (BN / 2), fb);
+            tma_load_2d_pair(sf_dst, &tmSFA, 0, sfa_row, fb);
+            tma_load_2d_pair(sf_dst + SF_ATOM, &tmSFB, 0, sfb_row, fb);
+          } else {
+            mbar_expect_tx(full_bar(s), L::STAGE_TX);
+            tma_load_2d(a_dst, &tmA, kb * QBK, m0, full_bar(s));
+            tma_load_2d(b_dst, &tmB, kb * QBK, n0, full_bar(s));
+            tma_load_2d(sf_dst, &tmSFA, 0, sfa_row, full_bar(s));
+            tma_load_2d(sf_dst + SF_ATOM, &tmSFB, 0, sfb_row, full_bar(s));
           }
         }
       }
@@ -169,10 +198,10 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ scale copies + MMA issue
-    if (lane == 0) {
+    if (lane == 0 && cta_rank == 0) {
       uint32_t it = 0, tile_iter = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
+      for (int tile = wid; tile < num_tiles && ok; tile += wstride, ++tile_iter) {
         int mb, nb;
         q_tile_coords(p, tile, mb, nb);
         const uint32_t sfb_shift = (uint32_t)((nb * BN) % 128) / 32;   // tile starts inside an atom: skip its first columns
@@ -189,20 +218,28 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           const uint32_t b_base = smem_u32(sB + s * L::B_BYTES);
           const uint32_t sf_base = smem_u32(sSF + s * L::SF_BYTES);
           // scale atoms: 32 rows of 16 bytes, no swizzle, 8-row core matrices 128 bytes apart
-          tc_cp_32x128b_warpx4(tmem_base + SFA_COL, make_smem_desc(sf_base, 0, 128, 0));
+          const uint32_t sf_tmem = tmem_base + (it & 1u) * ACC_STRIDE;
+          if (TWO) tc_cp_32x128b_warpx4_pair(sf_tmem + SFA_COL, make_smem_desc(sf_base, 0, 128, 0));
+          else tc_cp_32x128b_warpx4(sf_tmem + SFA_COL, make_smem_desc(sf_base, 0, 128, 0));
 #pragma unroll
-          for (int j = 0; j < L::NATOM; ++j)
-            tc_cp_32x128b_warpx4(tmem_base + SFB_COL + 4 * j, make_smem_desc(sf_base + (1 + j) * SF_ATOM, 0, 128, 0));
+          for (int j = 0; j < L::NATOM; ++j) {
+            if (TWO) tc_cp_32x128b_warpx4_pair(sf_tmem + SFB_COL + 4 * j, make_smem_desc(sf_base + (1 + j) * SF_ATOM, 0, 128, 0));
+            else tc_cp_32x128b_warpx4(sf_tmem + SFB_COL + 4 * j, make_smem_desc(sf_base + (1 + j) * SF_ATOM, 0, 128, 0));
+          }
 #pragma unroll
           for (int k = 0; k < QBK / QUMMA_K; ++k) {
             const uint64_t da = make_smem_desc(a_base + k * 32, 16, 1024, 2);
             const uint64_t db = make_smem_desc(b_base + k * 32, 16, 1024, 2);
-            tc_mma_mxf8(tmem_d, da, db, make_idesc_mxf8(QBM, BN, k, k), (kb | k) != 0 ? 1u : 0u, tmem_base + SFA_COL,
-                        tmem_base + SFB_COL + sfb_shift);
+            if (TWO) tc_mma_mxf8_pair(tmem_d, da, db, make_idesc_mxf8(TILE_M, BN, k, k), (kb | k) != 0 ? 1u : 0u, sf_tmem + SFA_COL,
+                                      sf_tmem + SFB_COL + sfb_shift);
+            else tc_mma_mxf8(tmem_d, da, db, make_idesc_mxf8(TILE_M, BN, k, k), (kb | k) != 0 ? 1u : 0u, sf_tmem + SFA_COL,
+                             sf_tmem + SFB_COL + sfb_shift);
           }
-          tc_commit(empty_bar(s));
+          if (TWO) tc_commit_pair(empty_bar(s)); else tc_commit(empty_bar(s));
         }
-        if (ok) tc_commit(tfull_bar(buf));
+        if (ok) {
+          if (TWO) tc_commit_pair(tfull_bar(buf)); else tc_commit(tfull_bar(buf));
+        }
       }
     }
   } else {
@@ -210,10 +247,10 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int q = warp & 3;
     uint32_t tile_iter = 0;
     const unsigned fl = p.flags;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_iter) {
+    for (int tile = wid; tile < num_tiles; tile += wstride, ++tile_iter) {
       int mb, nb;
       q_tile_coords(p, tile, mb, nb);
-      const int m0 = mb * QBM, n0 = nb * BN;
+      const int m0 = mb * TILE_M + (int)cta_rank * QBM, n0 = nb * BN;
       const uint32_t buf = tile_iter & 1, bph = (tile_iter >> 1) & 1;
       bool ok = mbar_wait(tfull_bar(buf), bph, abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
@@ -262,35 +299,91 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(buf));
+      if (lane == 0) {
+        if (TWO) mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0)); else mbar_arrive(tempty_bar(buf));
+      }
     }
   }
 
   tc_fence_before();
   __syncthreads();
+  if (TWO) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (TWO) tmem_dealloc_pair(tmem_base, TMEM_COLS); else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
-template <int BN, int STAGES>
-int launch_q(const CUtensorMap& tmA, const CUtensorMap& tmB, QParams p, cudaStream_t stream) {
-  using L = QSmem<BN, STAGES>;
-  auto kern = gemm_mxfp8_kernel<BN, STAGES>;
+template <int BN, int STAGES, bool TWO>
+int launch_q(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmSFA, const CUtensorMap& tmSFB, QParams p,
+             cudaStream_t stream) {
+  using L = QSmem<BN, STAGES, TWO>;
+  constexpr int TILE_M = TWO ? 2 * QBM : QBM;
+  auto kern = gemm_mxfp8_kernel<BN, STAGES, TWO>;
   static bool configured = false;
   if (!configured) {
     ELFA_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
     configured = true;
   }
-  p.tiles_m = (p.M + QBM - 1) / QBM;
+  p.tiles_m = (p.M + TILE_M - 1) / TILE_M;
   p.tiles_n = (p.N + BN - 1) / BN;
-  p.group_m = 8;
+  // rows of A that stay in L2 while the tile order sweeps over N: about 32 MB worth
+  const long long rows = std::max(512LL, std::min(4096LL, (32LL << 20) / (long long)p.K));
+  p.group_m = (int)std::max(1LL, rows / TILE_M);
   const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < device_sm_count() ? tiles : device_sm_count();
-  kern<<<grid, Q_THREADS, L::DYN, stream>>>(tmA, tmB, p);
+  const int slots = TWO ? device_sm_count() / 2 : device_sm_count();
+  const int grid = tiles < slots ? tiles : slots;
+  if (TWO) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * grid, 1, 1);
+    cfg.blockDim = dim3(Q_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = L::DYN;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    ELFA_CUDA(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmSFA, tmSFB, p));
+  } else {
+    kern<<<grid, Q_THREADS, L::DYN, stream>>>(tmA, tmB, tmSFA, tmSFB, p);
+  }
   ELFA_CUDA(cudaGetLastError());
   ::elfa::count_launches(1);
+  return ELFA_OK;
+}
+
+// Tensor map over a scale tensor viewed as [atoms, 128] 32-bit words, box = `box_atoms` rows. Small cache:
+// encoding costs a driver call and the same few tensors come back every step.
+struct SfKey {
+  const void* base;
+  uint64_t atoms;
+  uint32_t box;
+  bool operator==(const SfKey& o) const { return base == o.base && atoms == o.atoms && box == o.box; }
+};
+struct SfKeyHash {
+  size_t operator()(const SfKey& k) const { return reinterpret_cast<size_t>(k.base) * 1000003u ^ (k.atoms * 31u + k.box); }
+};
+std::mutex g_sf_mu;
+std::unordered_map<SfKey, CUtensorMap, SfKeyHash> g_sf_cache;
+
+int sf_tmap(CUtensorMap* out, const void* base, uint64_t atoms, uint32_t box_atoms) {
+  const SfKey key{base, atoms, box_atoms};
+  {
+    std::lock_guard<std::mutex> lk(g_sf_mu);
+    auto it = g_sf_cache.find(key);
+    if (it != g_sf_cache.end()) {
+      *out = it->second;
+      return ELFA_OK;
+    }
+  }
+  const int rc = make_tmap_2d(out, base, 4, atoms, 128, SF_ATOM, box_atoms, 128, false);
+  if (rc != ELFA_OK) return rc;
+  std::lock_guard<std::mutex> lk(g_sf_mu);
+  if (g_sf_cache.size() > 4096) g_sf_cache.clear();
+  g_sf_cache.emplace(key, *out);
   return ELFA_OK;
 }
 
@@ -309,7 +402,8 @@ __device__ __forceinline__ uint8_t mx_scale_q(float amax, float* scale, float* i
 
 __global__ void __launch_bounds__(256) mxfp8_quantize_gemm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                                                                   uint8_t* __restrict__ payload, uint8_t* __restrict__ sf,
-                                                                  __nv_bfloat16* __restrict__ deq, int rows, int cols, int kt) {
+                                                                  __nv_bfloat16* __restrict__ deq, int rows, int cols, int kt,
+                                                                  int b_atoms) {
   const int bpr = cols / 32;
   const long long nblocks = (long long)rows * bpr;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -342,7 +436,9 @@ __global__ void __launch_bounds__(256) mxfp8_quantize_gemm_kernel(const __nv_bfl
     uint4* dst = reinterpret_cast<uint4*>(payload + (long long)r * cols + kb * 32);
     dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
     dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-    sf[((long long)(r >> 7) * kt + (kb >> 2)) * SF_ATOM + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (kb & 3)] = sb;
+    // atom order: A operand [row block][K tile]; B operand [K tile][row block (+1 pad)]
+    const long long atom = b_atoms > 0 ? (long long)(kb >> 2) * b_atoms + (r >> 7) : (long long)(r >> 7) * kt + (kb >> 2);
+    sf[atom * SF_ATOM + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (kb & 3)] = sb;
     if (deq != nullptr) {
       uint4* dd = reinterpret_cast<uint4*>(deq + (long long)r * cols + kb * 32);
 #pragma unroll
@@ -368,22 +464,23 @@ __global__ void __launch_bounds__(256) mxfp8_quantize_gemm_kernel(const __nv_bfl
 using namespace elfa;
 
 // Bytes of the scale tensor that belongs to a [rows, cols] operand.
-ELFA_API long long elfa_mxfp8_sf_bytes(int rows, int cols) {
-  return (long long)((rows + 127) / 128) * ((cols + 127) / 128) * SF_ATOM;
+ELFA_API long long elfa_mxfp8_sf_bytes(int rows, int cols, int b_operand) {
+  return (long long)((rows + 127) / 128 + (b_operand ? 1 : 0)) * ((cols + 127) / 128) * SF_ATOM;
 }
 
 // x [rows, cols] bf16 (row pitch ldx elements) -> payload [rows, cols] e4m3 (dense), scale atoms, optional
-// dequantised bf16 copy [rows, cols]. `sf` must be zero-filled by the caller when rows or cols are not
-// multiples of 128 (entries of the padding are not written).
+// dequantised bf16 copy [rows, cols]. `b_operand` selects the atom order of the scales (A: [row block][K tile];
+// B: [K tile][row block + 1 pad]). `sf` must be zero-filled by the caller when rows or cols are not multiples
+// of 128 or for a B operand (entries of the padding are not written).
 ELFA_API int elfa_mxfp8_quantize_gemm(const void* x, long long ldx, void* payload, void* sf, void* deq, int rows, int cols,
-                                      void* stream) {
+                                      int b_operand, void* stream) {
   ELFA_REQUIRE(x && payload && sf && rows > 0 && cols > 0, "mxfp8_quantize_gemm: bad arguments");
   ELFA_REQUIRE(cols % 32 == 0 && ldx % 8 == 0, "mxfp8_quantize_gemm: cols must be a multiple of 32 and the pitch of 8");
   const long long nb = (long long)rows * (cols / 32);
   const int grid = (int)((nb + 255) / 256 < 148 * 16 ? (nb + 255) / 256 : 148 * 16);
   mxfp8_quantize_gemm_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), ldx, static_cast<uint8_t*>(payload), static_cast<uint8_t*>(sf),
-      static_cast<__nv_bfloat16*>(deq), rows, cols, (cols + 127) / 128);
+      static_cast<__nv_bfloat16*>(deq), rows, cols, (cols + 127) / 128, b_operand ? (rows + 127) / 128 + 1 : 0);
   ELFA_CUDA(cudaGetLastError());
   count_launches(1);
   return ELFA_OK;
@@ -404,11 +501,23 @@ ELFA_API int elfa_gemm_mxfp8(const void* A, const void* sfa, const void* B, cons
                "gemm_mxfp8: scale tensors must be 16-byte aligned");
   unsigned int* st = status_word();
   ELFA_REQUIRE(st != nullptr, "gemm_mxfp8: no status word");
-  const int BN = (force_bn == 128 || force_bn == 192) ? force_bn : (N <= 128 ? 128 : 192);
+  // force_bn: 128 / 192 single-CTA tiles, 384 = CTA pairs on 256 x 192 tiles (the default for problems that
+  // fill at least one wave of pairs)
+  const bool pair = force_bn == 384 ||
+                    (force_bn == 0 && N > 128 && (long long)((M + 255) / 256) * ((N + 191) / 192) >= device_sm_count() / 2);
+  const int BN = pair ? 192 : ((force_bn == 128 || force_bn == 192) ? force_bn : (N <= 128 ? 128 : 192));
   CUtensorMap tmA, tmB;
   int rc = shared_tmap(&tmA, A, 1, (uint64_t)M, (uint64_t)K, (uint64_t)K, QBM, QBK);
   if (rc != ELFA_OK) return rc;
-  rc = shared_tmap(&tmB, B, 1, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)BN, QBK);
+  rc = shared_tmap(&tmB, B, 1, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)(pair ? BN / 2 : BN), QBK);
+  if (rc != ELFA_OK) return rc;
+  // scale tensors as [atoms, 128] 32-bit words; one box = the atoms of one tile and K tile
+  const int kt = (K + QBK - 1) / QBK;
+  const int natom_b = BN <= 128 ? 1 : 2;
+  CUtensorMap tmSFA, tmSFB;
+  rc = sf_tmap(&tmSFA, sfa, (uint64_t)((M + 127) / 128) * kt, 1);
+  if (rc != ELFA_OK) return rc;
+  rc = sf_tmap(&tmSFB, sfb, (uint64_t)((N + 127) / 128 + 1) * kt, (uint32_t)natom_b);
   if (rc != ELFA_OK) return rc;
   QParams p{};
   p.M = M; p.N = N; p.K = K;
@@ -424,6 +533,7 @@ ELFA_API int elfa_gemm_mxfp8(const void* A, const void* sfa, const void* B, cons
   p.flags = flags;
   p.status = st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (BN == 192) return launch_q<192, 5>(tmA, tmB, p, s);
-  return launch_q<128, 6>(tmA, tmB, p, s);
+  if (pair) return launch_q<192, 7, true>(tmA, tmB, tmSFA, tmSFB, p, s);
+  if (BN == 192) return launch_q<192, 5, false>(tmA, tmB, tmSFA, tmSFB, p, s);
+  return launch_q<128, 6, false>(tmA, tmB, tmSFA, tmSFB, p, s);
 }

@@ -79,7 +79,7 @@ def cached_weight_operand(w: torch.Tensor, spec: "QuantSpec"):
     if hit is not None and hit[0] is w:
         return hit[1]
     from ..ops.gemm_mxfp8 import quantize_mxfp8
-    op, _ = quantize_mxfp8(w.detach().t().contiguous())
+    op, _ = quantize_mxfp8(w.detach().t().contiguous(), right=True)
     _weight_cache[key] = (w, op)
     return op
 

@@ -97,7 +97,7 @@ def main(argv=None) -> int:
         from ..ops import gemm_mxfp8 as q8
         M, N, K = a.m, a.n, a.k
         xq, _ = q8.quantize_mxfp8(torch.randn(M, K, device=dev).to(bf))
-        wq, _ = q8.quantize_mxfp8(torch.randn(N, K, device=dev).to(bf))
+        wq, _ = q8.quantize_mxfp8(torch.randn(N, K, device=dev).to(bf), right=True)
         out = torch.empty(M, N, dtype=bf, device=dev)
         ms = timed(lambda: q8.gemm_mxfp8(xq, wq, out=out), a.iters)
         fl = 2.0 * M * N * K

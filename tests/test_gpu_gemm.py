@@ -120,3 +120,36 @@ def test_staged_epilogue_tails_and_bias_gelu(cuda_device):
         _close(out[:M], ref, K)
         assert torch.all(out[M:] == 7.0)
     assert native.status() == 0
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 320), (200, 96, 136), (1000, 1376, 512), (2048, 2304, 1024)])
+def test_gemm_cta_pair_tiles(cuda_device, M, N, K, a_mn, b_mn):
+    """256 x 256 tiles computed by CTA pairs (cta_group::2), forced on shapes with row / column / K tails."""
+    a, b = _mk(M, N, K, a_mn, b_mn, cuda_device, seed=5)
+    out = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, force_bn=512)
+    torch.cuda.synchronize()
+    assert native.status() == 0
+    _close(out, _ref(a, b, a_mn, b_mn), K)
+
+
+def test_gemm_cta_pair_epilogues_and_persistence(cuda_device):
+    M, N, K = 1024, 1536, 512
+    a, b = _mk(M, N, K, True, True, cuda_device, seed=6)
+    ref = _ref(a, b, True, True)
+    acc = torch.randn(M, N, device=cuda_device)
+    acc0 = acc.clone()
+    ops.gemm(a, b, a_mn=True, b_mn=True, out=acc, accumulate=True, force_bn=512)       # staged fp32 reduce-add epilogue
+    _close(acc, ref + acc0, K)
+    few = ops.gemm(a, b, a_mn=True, b_mn=True, force_bn=512, max_ctas=6)                # 3 pairs loop over 24 tiles
+    full = ops.gemm(a, b, a_mn=True, b_mn=True, force_bn=512)
+    _close(full, ref, K)
+    assert torch.equal(few, full)
+    x, w = _mk(M, N, K, False, True, cuda_device, seed=7)
+    bias = torch.randn(N, device=cuda_device).to(torch.bfloat16)
+    pre = torch.empty(M, N, dtype=torch.bfloat16, device=cuda_device)
+    out = ops.gemm(x, w, b_mn=True, bias=bias, gelu=True, preact=pre, force_bn=512)
+    base = _ref(x, w, False, True) + bias.float()
+    _close(pre, base, K)
+    _close(out, ops.gelu_tanh_ref(base), K)
+    assert native.status() == 0

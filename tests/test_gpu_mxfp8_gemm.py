@@ -16,13 +16,15 @@ def _operands(M, N, K, seed):
 
 
 @pytest.mark.parametrize("M,N,K,bn", [(128, 128, 128, 0), (256, 384, 512, 0), (256, 384, 512, 128), (300, 200, 160, 0),
-                                      (1024, 1536, 4096, 0), (2048, 4096, 1024, 128), (384, 1000, 2048, 192)])
+                                      (1024, 1536, 4096, 0), (2048, 4096, 1024, 128), (384, 1000, 2048, 192),
+                                      (256, 192, 128, 384), (300, 200, 160, 384), (1024, 1536, 4096, 384), (4096, 4096, 2048, 0),
+                                      (2000, 1000, 512, 384)])
 def test_mxfp8_gemm_matches_dequantised_product(M, N, K, bn):
     from elfa_b200 import native
     from elfa_b200.ops import gemm_mxfp8 as q
     x, w = _operands(M, N, K, M + N + K)
     xq, xdeq = q.quantize_mxfp8(x, dequantized=True)
-    wq, _ = q.quantize_mxfp8(w)
+    wq, _ = q.quantize_mxfp8(w, right=True)
     y = q.gemm_mxfp8(xq, wq, force_bn=bn)
     torch.cuda.synchronize()
     native.check_status()
@@ -50,7 +52,7 @@ def test_mxfp8_gemm_epilogue():
     x, w = x * 0.05, w * 0.05
     bias = torch.randn(512, device="cuda").bfloat16()
     xq, _ = q.quantize_mxfp8(x)
-    wq, _ = q.quantize_mxfp8(w)
+    wq, _ = q.quantize_mxfp8(w, right=True)
     pre = torch.empty(256, 512, device="cuda", dtype=torch.bfloat16)
     y = q.gemm_mxfp8(xq, wq, bias=bias, gelu=True, preact=pre)
     ref_pre = q.dequantize_ref(xq) @ q.dequantize_ref(wq).t() + bias.float()
