@@ -103,6 +103,7 @@ def main() -> int:
     ap.add_argument("--micro-batch", type=int, default=0, help="sequences per micro-batch (0 = auto)")
     ap.add_argument("--comm", default=None, choices=[None, "fused", "nccl"])
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the result invalid)")
+    ap.add_argument("--global-batch", type=int, default=0, help="debug only: override the global batch (marks the result invalid)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -135,6 +136,8 @@ def main() -> int:
     cfg.telemetry.log_file = ""
     if args.layers:
         cfg.model.num_layers = args.layers
+    if args.global_batch:
+        cfg.training.global_batch_size = args.global_batch
     mb = args.micro_batch or (2 if world <= 2 else 4)
     cfg.training.micro_batch_size = mb
     cfg.training.gradient_accumulation_steps = cfg.training.global_batch_size // mb
@@ -228,8 +231,8 @@ def main() -> int:
             "model_tflops_per_gpu": value * flops / world / 1e12,
             "loss": loss, "device_status": st,
         }
-        if args.layers:
-            out["invalid"] = "layer count overridden for debugging"
+        if args.layers or args.global_batch:
+            out["invalid"] = "layer count or global batch overridden for debugging"
         print(json.dumps(out))
     if world > 1:
         dist.barrier()
