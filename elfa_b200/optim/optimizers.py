@@ -37,6 +37,10 @@ class _Base:
     def __init__(self, flat: FlatParams, pc: Optional[ParallelContext], zero_stage: int, lr: float, weight_decay: float,
                  max_grad_norm: float):
         self.flat, self.pc = flat, pc or ParallelContext()
+        # stage 3: `flat` holds only this rank's shards and reduces its gradients itself (parallel/zero3.py)
+        self.presharded = bool(getattr(flat, "presharded", False))
+        if self.presharded:
+            zero_stage = 0
         self.zero_stage = zero_stage if self.pc.dp_size > 1 else 0
         self.lr, self.weight_decay, self.max_grad_norm = lr, weight_decay, max_grad_norm
         self.step_count = 0
@@ -87,6 +91,8 @@ class _Base:
         """TP: all-reduce the replicated prefix. DP: all-reduce (ZeRO-0) or reduce-scatter
         (ZeRO>=1) the whole buffer; gradients are averaged over DP."""
         pc, f = self.pc, self.flat
+        if self.presharded:
+            return
         if pc.tp_size > 1 and f.replicated_end > 0:
             dist.all_reduce(f.grads[:f.replicated_end], group=pc.tp_group)
         if self.zero_fused is not None:
@@ -129,7 +135,7 @@ class _Base:
         inv_scale = 1.0 / self.loss_scale
         if g.is_cuda:
             st = stream_ptr(g)
-            distributed = (pc.tp_size > 1) or self.sharded
+            distributed = (pc.tp_size > 1) or self.sharded or (self.presharded and pc.dp_size > 1)
             if not distributed:
                 lib.call("elfa_sumsq", g, _ptype(g), g.numel(), self.part, self.scalars, 0, st)
             else:
@@ -142,18 +148,18 @@ class _Base:
                     acc = 1
                 if self.hi > rep_hi:
                     lib.call("elfa_sumsq", self._grads(rep_hi, self.hi), _ptype(g), self.hi - rep_hi, self.part, self.scalars, acc, st)
-                dist.all_reduce(self.scalars[0:1], group=None if self.sharded else pc.tp_group)
+                dist.all_reduce(self.scalars[0:1], group=pc.dp_group if self.presharded else (None if self.sharded else pc.tp_group))
             lib.call("elfa_clip_coef", self.scalars, float(self.max_grad_norm), float(inv_scale), st)
             return
         # CPU
         sq = float(g.double().pow(2).sum())
-        if pc.tp_size > 1 or self.sharded:
+        if pc.tp_size > 1 or self.sharded or (self.presharded and pc.dp_size > 1):
             rep_hi = min(max(f.replicated_end, self.lo), self.hi)
             sq = float(f.grads[rep_hi:self.hi].double().pow(2).sum())
             if pc.tp_rank == 0:
                 sq += float(f.grads[self.lo:rep_hi].double().pow(2).sum())
             t = torch.tensor([sq], dtype=torch.float64)
-            dist.all_reduce(t, group=None if self.sharded else pc.tp_group)
+            dist.all_reduce(t, group=pc.dp_group if self.presharded else (None if self.sharded else pc.tp_group))
             sq = float(t)
         norm = (sq ** 0.5) * inv_scale
         finite = norm == norm and norm != float("inf")
@@ -179,6 +185,8 @@ class _Base:
         self.step_count += 1
         self._update()
         self.gather_params()
+        if self.presharded:
+            self.flat.after_step()       # full-size copies of the parameters are stale now
         from ..quant.qat import new_weight_epoch
         new_weight_epoch()
 
@@ -441,6 +449,8 @@ def build_optimizer(cfg, flat: FlatParams, pc: Optional[ParallelContext] = None)
     """Optimizer selected by ``training.optimizer`` (lion | muon | lion_muon | adamw)."""
     t = cfg.training
     z = cfg.runtime.zero_stage
+    if getattr(flat, "presharded", False) and t.optimizer in ("muon", "lion_muon"):
+        raise ValueError("ZeRO stage 3 shards parameters element-wise: use the adamw or lion optimizer (Muon needs whole matrices)")
     if t.optimizer == "adamw":
         return AdamW(flat, pc, z, t.learning_rate, (t.adam_beta1, t.adam_beta2), t.adam_eps, t.weight_decay, t.gradient_clip)
     if t.optimizer == "lion":

@@ -1,0 +1,328 @@
+"""ZeRO stage 3: parameters, gradients and optimizer state sharded over the data-parallel group.
+
+At rest every rank holds ``1/dp`` of each bucket of parameters (model dtype), of its fp32 gradient
+and of the optimizer state. A bucket is one transformer block; everything outside the blocks
+(embeddings, final norm, head) forms the bucket ``rest``.
+
+* ``rest`` is gathered once per optimizer step (it is needed at both ends of forward and backward)
+  and its gradient is reduce-scattered once, after the last micro-batch.
+* A block is gathered right before its forward and again right before its backward, into one of two
+  full-size slots (block ``i`` always uses slot ``i % 2``, so the tensors autograd saved stay valid
+  once the slot is refilled). The gather of the next block is issued on a side stream while the
+  current block computes. The block's fp32 gradient is accumulated by the backward kernels in a
+  slot of the same shape and reduce-scattered (averaged) into the rank's gradient shard when the
+  next block's backward starts.
+* The optimizer sees only the local shards: :class:`Zero3Shards` has the interface of
+  ``optim.flat.FlatParams`` with ``presharded = True`` (no gradient reduction or parameter gather
+  in the optimizer; the gradient norm is summed over the group).
+
+reference: ``src/distributed/zero_sharding.zig:73-113`` (``shardParameter`` / ``gatherParameter``:
+``len / num_gpus`` per GPU), ``:115-157`` (``allGatherParameters`` before use), ``:159-181``
+(``reduceScatterGradients`` then x 1/N), stage predicates ``src/tensor/sharding.zig:344-354``. The
+reference gathers into a fresh full-size tensor per call and has no consumer; here the gather
+overlaps the previous block's compute and, on GPUs with a symmetric arena, is a peer-load kernel.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..optim.flat import ALIGN
+from .mesh import ParallelContext
+
+
+@dataclass
+class _Bucket:
+    name: str
+    names: List[str]
+    params: List[torch.nn.Parameter]
+    offsets: List[int] = field(default_factory=list)      # element offsets inside the bucket
+    numel: int = 0                                          # padded to dp * ALIGN
+    shard: int = 0                                          # numel / dp
+    base: int = 0                                           # offset of this bucket's shard in the local flat buffers
+    full: Optional[torch.Tensor] = None                     # full-size parameter slot (shared between blocks of equal parity)
+    full_grad: Optional[torch.Tensor] = None                # full-size fp32 gradient slot
+    module: Optional[torch.nn.Module] = None
+    state: str = "sharded"                                  # sharded | fwd | bwd
+    ready: Optional[object] = None                          # CUDA event: gather finished
+
+
+def _is_no_decay(p: torch.nn.Parameter) -> bool:
+    return bool(getattr(p, "no_decay", False)) or p.dim() < 2
+
+
+class Zero3Shards:
+    presharded = True
+    symm = None
+
+    def __init__(self, model: torch.nn.Module, pc: ParallelContext, blocks: Optional[Iterable[torch.nn.Module]] = None,
+                 grad_dtype: torch.dtype = torch.float32, prefetch: bool = True):
+        if pc.tp_size != 1:
+            raise ValueError("ZeRO stage 3 is implemented for pure data parallelism (tensor_parallel_size 1)")
+        self.pc, self.model = pc, model
+        self.dp, self.rank = pc.dp_size, pc.dp_rank
+        self.group = pc.dp_group
+        named = list(model.named_checkpoint_parameters()) if hasattr(model, "named_checkpoint_parameters") else list(model.named_parameters())
+        named = [(n, p) for n, p in named if p.requires_grad]
+        self.dtype = named[0][1].dtype
+        self.device = named[0][1].device
+        self.cuda = self.device.type == "cuda"
+        blocks = list(blocks if blocks is not None else getattr(model, "blocks", []))
+        by_id = {id(p): n for n, p in named}
+        taken = set()
+        self.buckets: List[_Bucket] = []
+        for i, m in enumerate(blocks):
+            ps = [p for p in m.parameters() if id(p) in by_id and id(p) not in taken]
+            for p in ps:
+                taken.add(id(p))
+            self.buckets.append(_Bucket(f"block{i}", [by_id[id(p)] for p in ps], ps, module=m))
+        rest = [(n, p) for n, p in named if id(p) not in taken]
+        self.rest = _Bucket("rest", [n for n, _ in rest], [p for _, p in rest])
+        self.block_buckets = list(self.buckets)
+        self.buckets.append(self.rest)
+        q = self.dp * ALIGN
+        base = 0
+        for b in self.buckets:
+            order = sorted(range(len(b.params)), key=lambda j: 1 if _is_no_decay(b.params[j]) else 0)   # decay first (stable)
+            b.params = [b.params[j] for j in order]
+            b.names = [b.names[j] for j in order]
+            off = 0
+            for p in b.params:
+                b.offsets.append(off)
+                off += (p.numel() + ALIGN - 1) // ALIGN * ALIGN
+            b.numel = (off + q - 1) // q * q
+            b.shard = b.numel // self.dp
+            b.base = base
+            base += b.shard
+        self.numel = base                       # local elements: what the optimizer updates
+        self.flat = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
+        self.grads = torch.zeros(self.numel, dtype=grad_dtype, device=self.device)
+        self.replicated_end = 0
+        self.shard_lo, self.shard_hi, self.shard_size = 0, self.numel, self.numel
+        self.params = [p for b in self.buckets for p in b.params]
+        self.names = [n for b in self.buckets for n in b.names]
+        # full-size slots: two for the blocks, one for the rest
+        nslot = max((b.numel for b in self.block_buckets), default=0)
+        self._pslots = [torch.zeros(nslot, dtype=self.dtype, device=self.device) for _ in range(2)] if nslot else []
+        self._gslots = [torch.zeros(nslot, dtype=grad_dtype, device=self.device) for _ in range(2)] if nslot else []
+        for i, b in enumerate(self.block_buckets):
+            b.full = self._pslots[i % 2][:b.numel]
+            b.full_grad = self._gslots[i % 2][:b.numel]
+        self.rest.full = torch.zeros(self.rest.numel, dtype=self.dtype, device=self.device)
+        self.rest.full_grad = torch.zeros(self.rest.numel, dtype=grad_dtype, device=self.device)
+        # move every parameter into its slot view; keep this rank's slice as the persistent shard
+        with torch.no_grad():
+            for b in self.buckets:
+                tmp = torch.zeros(b.numel, dtype=self.dtype, device=self.device)
+                for p, o in zip(b.params, b.offsets):
+                    tmp[o:o + p.numel()].copy_(p.data.reshape(-1))
+                self.flat[b.base:b.base + b.shard].copy_(tmp[self.rank * b.shard:(self.rank + 1) * b.shard])
+                for p, o in zip(b.params, b.offsets):
+                    p.data = b.full[o:o + p.numel()].view(p.shape)
+                    p.main_grad = b.full_grad[o:o + p.numel()].view(p.shape)
+                    p._grad_fresh = False
+        self.side = torch.cuda.Stream(self.device) if (self.cuda and prefetch) else None
+        self._pending_rs: List[_Bucket] = []
+        self._rest_valid = False
+        self.gathers = 0          # statistics (tests)
+        self.reduce_scatters = 0
+        for i, b in enumerate(self.block_buckets):
+            self._hook(i, b)
+
+    # ------------------------------------------------------------------ collectives on one bucket
+    def _gather_into(self, b: _Bucket) -> None:
+        shard = self.flat[b.base:b.base + b.shard]
+        self.gathers += 1
+        if self.dp == 1:
+            b.full.copy_(shard)
+        elif self.cuda:
+            dist.all_gather_into_tensor(b.full, shard, group=self.group)
+        else:
+            parts = [torch.empty_like(shard) for _ in range(self.dp)]
+            dist.all_gather(parts, shard.contiguous(), group=self.group)
+            b.full.copy_(torch.cat(parts))
+
+    def _gather(self, b: _Bucket, state: str, asynchronous: bool = False) -> None:
+        if b.state != "sharded":
+            b.state = state if b.state != "bwd" else b.state
+            return
+        if asynchronous and self.side is not None:
+            self.side.wait_stream(torch.cuda.current_stream(self.device))   # the slot's previous user is done
+            with torch.cuda.stream(self.side):
+                self._gather_into(b)
+                ev = torch.cuda.Event()
+                ev.record(self.side)
+            b.ready = ev
+        else:
+            self._gather_into(b)
+            b.ready = None
+        b.state = state
+
+    def _wait(self, b: _Bucket) -> None:
+        if b.ready is not None:
+            torch.cuda.current_stream(self.device).wait_event(b.ready)
+            b.ready = None
+
+    def _reduce_scatter(self, b: _Bucket) -> None:
+        """full fp32 gradient of ``b`` (plus what autograd left in ``.grad``) → averaged, added to the shard."""
+        for p in b.params:
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.to(p.main_grad.dtype))
+                p.grad = None
+        dst = self.grads[b.base:b.base + b.shard]
+        self.reduce_scatters += 1
+        if self.dp == 1:
+            dst.add_(b.full_grad)
+        elif self.cuda:
+            out = torch.empty_like(dst)
+            dist.reduce_scatter_tensor(out, b.full_grad, op=dist.ReduceOp.AVG, group=self.group)
+            dst.add_(out)
+        else:
+            g = b.full_grad.clone()
+            dist.all_reduce(g, group=self.group)
+            dst.add_(g[self.rank * b.shard:(self.rank + 1) * b.shard] / self.dp)
+
+    def _flush_pending(self) -> None:
+        for b in self._pending_rs:
+            self._reduce_scatter(b)
+            b.state = "sharded"
+        self._pending_rs = []
+
+    # ------------------------------------------------------------------ hooks on the blocks
+    def _hook(self, i: int, b: _Bucket) -> None:
+        blocks = self.block_buckets
+
+        def pre_forward(module, args):
+            if b.state == "sharded":
+                self._gather(b, "fwd")
+            self._wait(b)
+            if i + 1 < len(blocks) and blocks[i + 1].state == "sharded" and torch.is_grad_enabled() and b.state == "fwd":
+                # the other slot was last used by block i-1, whose forward has been issued already
+                self._gather(blocks[i + 1], "fwd", asynchronous=True)
+
+        def post_forward(module, args, out):
+            if b.state == "fwd":
+                b.state = "sharded"         # the slot may be overwritten; backward gathers again
+
+        def pre_backward(module, grad_out):
+            self._flush_pending()
+            if b.state != "bwd":
+                if b.state == "sharded":
+                    self._gather(b, "bwd")
+                b.state = "bwd"
+                b.full_grad.zero_()
+            self._wait(b)
+            if i - 1 >= 0 and blocks[i - 1].state == "sharded":
+                self._gather(blocks[i - 1], "bwd_prefetched", asynchronous=True)
+
+        def post_backward(module, grad_in, grad_out):
+            if b not in self._pending_rs:
+                self._pending_rs.append(b)
+
+        b.module.register_forward_pre_hook(pre_forward)
+        b.module.register_forward_hook(post_forward)
+        b.module.register_full_backward_pre_hook(pre_backward)
+        b.module.register_full_backward_hook(post_backward)
+
+    # ------------------------------------------------------------------ step protocol (called by the trainer / optimizer)
+    def before_forward(self) -> None:
+        """Makes the ``rest`` bucket valid (once per optimizer step) and resets block states."""
+        if not self._rest_valid:
+            self._gather_into(self.rest)
+            self._rest_valid = True
+        for b in self.block_buckets:
+            if b.state == "bwd_prefetched":
+                b.state = "sharded"
+
+    def after_backward(self) -> None:
+        """End of one micro-batch's backward: reduce-scatter what is still pending."""
+        self._flush_pending()
+        for b in self.block_buckets:
+            b.state = "sharded"
+            b.ready = None
+        if self.side is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self.side)
+
+    def fold_autograd_grads(self) -> None:
+        """Called by the optimizer before the update: the ``rest`` gradient (accumulated over all
+        micro-batches in its full-size buffer) is reduce-scattered now."""
+        self._flush_pending()
+        self._reduce_scatter(self.rest)
+        self.rest.full_grad.zero_()
+
+    def after_step(self) -> None:
+        self._rest_valid = False
+
+    def zero_grad(self) -> None:
+        self.grads.zero_()
+        self.rest.full_grad.zero_()
+        for p in self.params:
+            p.grad = None
+
+    # ------------------------------------------------------------------ FlatParams interface used by the optimizers
+    def wd_ranges(self, lo: Optional[int] = None, hi: Optional[int] = None) -> List[Tuple[int, int, bool]]:
+        lo = 0 if lo is None else lo
+        hi = self.numel if hi is None else hi
+        out: List[Tuple[int, int, bool]] = []
+        for b in self.buckets:
+            s0 = self.rank * b.shard                 # bucket coordinates of this rank's slice
+            decay_end = b.numel
+            for p, o in zip(b.params, b.offsets):
+                if _is_no_decay(p):
+                    decay_end = o
+                    break
+            for a, e, wd in ((0, decay_end, True), (decay_end, b.numel, False)):
+                a2, e2 = max(a, s0), min(e, s0 + b.shard)
+                if a2 >= e2:
+                    continue
+                ga, ge = b.base + a2 - s0, b.base + e2 - s0
+                ga, ge = max(ga, lo), min(ge, hi)
+                if ga >= ge:
+                    continue
+                if out and out[-1][2] == wd and out[-1][1] == ga:
+                    out[-1] = (out[-1][0], ge, wd)
+                else:
+                    out.append((ga, ge, wd))
+        return out
+
+    def param_slices(self) -> Dict[str, Tuple[int, int]]:
+        raise NotImplementedError("stage 3 shards do not hold whole parameters; use full_tensors()")
+
+    # ------------------------------------------------------------------ checkpoints
+    def full_tensors(self) -> List[Tuple[str, torch.Tensor]]:
+        """(name, full tensor) for every parameter, gathered bucket by bucket (every rank must call)."""
+        out = []
+        for b in self.buckets:
+            self._gather_into(b)
+            if self.cuda:
+                torch.cuda.current_stream(self.device).synchronize()
+            for n, p, o in zip(b.names, b.params, b.offsets):
+                out.append((n, b.full[o:o + p.numel()].view(p.shape).detach().clone()))
+            if b is not self.rest:
+                b.state = "sharded"
+        self._rest_valid = True
+        return out
+
+    @torch.no_grad()
+    def load_full(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """Writes full tensors (same on every rank) into the local shards."""
+        for b in self.buckets:
+            tmp = torch.zeros(b.numel, dtype=self.dtype, device=self.device)
+            for n, p, o in zip(b.names, b.params, b.offsets):
+                if n not in tensors:
+                    raise KeyError(f"checkpoint is missing tensor '{n}'")
+                t = tensors[n]
+                if tuple(t.shape) != tuple(p.shape):
+                    raise ValueError(f"tensor '{n}': checkpoint shape {tuple(t.shape)} != model shape {tuple(p.shape)}")
+                tmp[o:o + p.numel()].copy_(t.reshape(-1).to(self.device, self.dtype))
+            self.flat[b.base:b.base + b.shard].copy_(tmp[self.rank * b.shard:(self.rank + 1) * b.shard])
+        self._rest_valid = False
+
+    def memory_report(self) -> Dict[str, int]:
+        esz = self.flat.element_size()
+        full = sum(b.numel for b in self.buckets)
+        return {"param_bytes_at_rest": self.numel * esz, "param_bytes_unsharded": full * esz,
+                "transient_bytes": (sum(s.numel() for s in self._pslots) + self.rest.numel) * esz}

@@ -66,12 +66,17 @@ class Trainer:
         self.model = build_model(cfg, pc, device)
         self.model.train()
         dp_arena = None
-        if (pc.dp_size > 1 and cfg.runtime.zero_stage >= 1 and pc.comm_backend == "fused" and device.type == "cuda"
+        if (pc.dp_size > 1 and cfg.runtime.zero_stage in (1, 2) and pc.comm_backend == "fused" and device.type == "cuda"
                 and cfg.model.dtype != "fp32"):
             from .runtime.symm import SymmetricArena
             n_est = sum(p.numel() + 64 for p in self.model.parameters()) + pc.dp_size * 1024
             dp_arena = SymmetricArena.for_group(pc.dp_group, device, n_est * 6 + (16 << 20))
-        self.flat = FlatParams(self.model.named_checkpoint_parameters(), dp_size=pc.dp_size, dp_rank=pc.dp_rank, allocator=dp_arena)
+        if cfg.runtime.zero_stage == 3 and pc.dp_size > 1:
+            from .parallel.zero3 import Zero3Shards
+            self.flat = Zero3Shards(self.model, pc)
+        else:
+            self.flat = FlatParams(self.model.named_checkpoint_parameters(), dp_size=pc.dp_size, dp_rank=pc.dp_rank, allocator=dp_arena)
+        self.zero3 = bool(getattr(self.flat, "presharded", False))
         self.optimizer = build_optimizer(cfg, self.flat, pc)
         t = cfg.training
         self.scheduler = LRScheduler(t.lr_schedule, t.learning_rate, t.min_learning_rate, t.warmup_steps, t.total_steps)
@@ -115,11 +120,12 @@ class Trainer:
             ids = b.input.to(self.device, non_blocking=True)
             tgt = b.target.to(self.device, non_blocking=True)
             denom = float(tgt.numel() * n_micro)
+            if self.zero3:
+                self.flat.before_forward()
             loss = self.model(ids, tgt, loss_denominator=denom, grad_scale=scale)
-            if loss.is_cuda:
-                loss.backward()
-            else:
-                loss.backward()          # the CPU path applies grad_scale inside the loss op's backward
+            loss.backward()              # grad_scale is applied inside the loss op's backward
+            if self.zero3:
+                self.flat.after_backward()
             total = loss.detach() if total is None else total + loss.detach()
         lr = self.scheduler.get_lr()
         self.optimizer.step(lr)
@@ -201,6 +207,8 @@ class Trainer:
         """(name, full tensor) list on every rank of the TP group (rank 0 writes)."""
         import torch.distributed as dist
         pc = self.pc
+        if self.zero3:
+            return self.flat.full_tensors()
         out = []
         for name, p in self.model.named_checkpoint_parameters():
             t = p.detach()
@@ -232,8 +240,10 @@ class Trainer:
         mgr = self.ckpt or CheckpointManager(self.cfg.checkpoint.dir or os.path.dirname(path), 0)
         meta, tensors, opt, rng, _ = mgr.load_full(path)
         pc = self.pc
+        if self.zero3:
+            self.flat.load_full(tensors)
         with torch.no_grad():
-            for name, p in self.model.named_checkpoint_parameters():
+            for name, p in ([] if self.zero3 else self.model.named_checkpoint_parameters()):
                 if name not in tensors:
                     raise KeyError(f"checkpoint is missing tensor '{name}'")
                 full = tensors[name]

@@ -111,18 +111,26 @@ def mode_zero(dev, backend, dtype, stage):
     world = pc.dp_size
     cfg = small_cfg(dtype, 1, backend)
     cfg.runtime.zero_stage = stage
+    accum = 2 if stage == 3 else 1            # stage 3 also covers gradient accumulation over micro-batches
     cfg.training.micro_batch_size = 2
-    cfg.training.global_batch_size = 2 * world
+    cfg.training.global_batch_size = 2 * world * accum
     tr = Trainer(cfg, device=dev, pc=pc, telemetry=False)
     losses = tr.run(max_steps=4)
     if dev.type == "cuda":
         assert native.status() == 0
+    if stage == 3:
+        rep = tr.flat.memory_report()
+        assert tr.zero3 and rep["param_bytes_at_rest"] * world <= rep["param_bytes_unsharded"] + 4096 * world, rep
+        nb = len(tr.flat.block_buckets)
+        # per micro-batch: every block gathered for forward and for backward; the rest once per step
+        assert tr.flat.gathers == 4 * (accum * 2 * nb + 1), (tr.flat.gathers, nb)
+        assert tr.flat.reduce_scatters == 4 * (accum * nb + 1), tr.flat.reduce_scatters
     if pc.rank == 0:
         cfg1 = small_cfg(dtype, 1, "nccl")
         cfg1.runtime.world_size = 1
         cfg1.runtime.zero_stage = 0
-        cfg1.training.micro_batch_size = 2 * world
-        cfg1.training.global_batch_size = 2 * world
+        cfg1.training.micro_batch_size = 2 * world * accum
+        cfg1.training.global_batch_size = 2 * world * accum
         tr1 = Trainer(cfg1, device=dev, pc=ParallelContext(), telemetry=False)
         ref = tr1.run(max_steps=4)
         tol = 2e-4 if dtype == "fp32" else 0.05

@@ -22,7 +22,7 @@ def test_tp_sp_matches_single_rank_on_cpu(world):
     assert "TP_OK" in r.stdout
 
 
-@pytest.mark.parametrize("stage", [0, 1])
+@pytest.mark.parametrize("stage", [0, 1, 3])
 def test_zero_data_parallel_matches_single_rank_on_cpu(stage):
     r = _run(2, ["zero_cpu", "nccl", "fp32", str(stage)], 29621 + stage)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]

@@ -55,3 +55,10 @@ def test_zero1_data_parallel_matches_single_gpu(cuda_device, backend):
     assert "ZERO_OK" in r.stdout
     if backend == "fused":
         assert "fused=True" in r.stdout
+
+
+def test_zero3_parameter_sharding_matches_single_gpu(cuda_device):
+    """Stage 3: blocks gathered on demand (prefetch on a side stream), gradients reduce-scattered per block."""
+    r = _run(["zero", "nccl", "bf16", "3"], 29707)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "ZERO_OK stage=3" in r.stdout
