@@ -70,15 +70,27 @@ def main():
             else:
                 x = torch.randn(M, K, device=dev).to(torch.bfloat16)
                 res[backend] = timed(lambda: tpl.gemm_rs(x, w, pc, b_mn=True))
+        # the parts of the library path on their own: collective only, GEMM only
+        from elfa_b200.ops.gemm import gemm
+        if kind == "ag":
+            full = torch.empty(M, K, device=dev, dtype=torch.bfloat16)
+            coll = timed(lambda: dist.all_gather_into_tensor(full, x, group=pc.tp_group))
+            mm = timed(lambda: gemm(full, w, b_mn=True))
+        else:
+            y = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            out = torch.empty(M // world, N, device=dev, dtype=torch.bfloat16)
+            coll = timed(lambda: dist.reduce_scatter_tensor(out, y, group=pc.tp_group))
+            mm = timed(lambda: gemm(x, w, b_mn=True, out=y))
         flops = 2.0 * M * K * N
         wire = (world - 1) / world * M * (K if kind == "ag" else N) * 2
         floor_ms = max(flops / peak, wire / link) * 1e3
-        rows.append((name, M, N, K, res["nccl"], res["fused"], floor_ms))
+        rows.append((name, M, N, K, res["nccl"], res["fused"], floor_ms, coll, mm))
     if pc.rank == 0:
         print(f"world={world} tokens={M}")
-        print(f"{'op':24s} {'M':>6s} {'N':>6s} {'K':>6s} {'nccl ms':>9s} {'fused ms':>9s} {'speedup':>8s} {'floor ms':>9s} {'fused/floor':>11s}")
-        for name, m, n, k, t0, t1, fl in rows:
-            print(f"{name:24s} {m:6d} {n:6d} {k:6d} {t0:9.3f} {t1:9.3f} {t0 / t1:8.2f} {fl:9.3f} {fl / t1:11.2f}")
+        print(f"{'op':24s} {'M':>6s} {'N':>6s} {'K':>6s} {'nccl ms':>9s} {'fused ms':>9s} {'speedup':>8s} {'floor ms':>9s} {'floor/fused':>11s} "
+              f"{'coll only':>9s} {'gemm only':>9s}")
+        for name, m, n, k, t0, t1, fl, coll, mm in rows:
+            print(f"{name:24s} {m:6d} {n:6d} {k:6d} {t0:9.3f} {t1:9.3f} {t0 / t1:8.2f} {fl:9.3f} {fl / t1:11.2f} {coll:9.3f} {mm:9.3f}")
     dist.barrier()
     dist.destroy_process_group()
 

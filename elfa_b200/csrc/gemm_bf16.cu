@@ -75,6 +75,7 @@ struct CommParams {
   // all-gather of A
   const __nv_bfloat16* x_local;            // [rows_per_rank, K]
   long long ldx;
+  int piece_bytes, pieces_per_row;         // a row of x_local is pushed in `pieces_per_row` pieces of `piece_bytes` (<= 8 KB, x16)
   unsigned long long peer_xfull[MAX_RANKS];   // peers' gathered-A buffers [M, K] (ld = K)
   unsigned long long peer_flags[MAX_RANKS];   // peers' counters, one u32 per source rank
   const unsigned int* my_flags;            // this rank's counters
@@ -109,7 +110,7 @@ struct SmemLayout {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int BAR_OFF = STAGES * (A_BYTES + B_BYTES);
-  static constexpr int NUM_BARS = 2 * STAGES + 4;
+  static constexpr int NUM_BARS = 2 * STAGES + 4 + 4;   // ring full/empty, accumulator full/empty, push buffers (all-gather variant)
   static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16;
   static constexpr int DYN = TOTAL + 1024;  // slack for manual 1024-byte alignment
   // reduce-scatter variant: two [128 x 64] bf16 staging tiles for the TMA stores to the owner rank
@@ -196,6 +197,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(tfull_bar(b), 1);
       mbar_init(tempty_bar(b), TWO ? 8 : 4);   // pair: the epilogue warps of both CTAs release the even CTA's barrier
     }
+    for (int b = 0; b < 4; ++b) mbar_init(bar0 + 8u * (2 * STAGES + 4 + b), 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -579,40 +581,63 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (COMM == COMM_AG && warp >= 7) {
     // ------------------------------------------------------------------ push warps (7, 8)
-    // This CTA's slice of the local shard goes to peer rank+1 first, then rank+2, ...; the own
-    // copy (needed later by the weight-gradient GEMM) is written last.
-    const int t = threadIdx.x - 224;
-    const long long vec_per_row = p.K / 8;
-    const long long nvec = (long long)cm.rows_per_rank * vec_per_row;
-    const long long lo = nvec * blockIdx.x / gridDim.x, hi = nvec * (blockIdx.x + 1) / gridDim.x;
+    // This rank's shard goes to peer rank+1 first, then rank+2, ...; the own copy (needed later by
+    // the weight-gradient GEMM) is written last. One lane per warp drives a two-buffer pipeline of
+    // bulk copies: local global memory -> shared memory -> the peer's gathered buffer. The loads are
+    // local, the stores cross NVLink as large transactions; nothing here is a multicast.
+    const int w = warp - 7;
+    const uint32_t buf0 = smem_u32(smem + L::OUT_OFF) + w * 16384;
+    auto pbar = [&](int b) { return bar0 + 8u * (2 * STAGES + 4 + w * 2 + b); };
+    const long long nchunks = (long long)cm.rows_per_rank * cm.pieces_per_row;
+    const long long c_first = (long long)blockIdx.x * 2 + w, c_step = (long long)gridDim.x * 2;
+    const uint32_t pb = (uint32_t)cm.piece_bytes;
+    const char* src0 = reinterpret_cast<const char*>(cm.x_local);
+    uint32_t n_issued = 0, n_done = 0;   // loads issued / consumed: buffer = index & 1, phase = (index >> 1) & 1
+    bool okp = true;
+    auto src_of = [&](long long c) {
+      const long long r = c / cm.pieces_per_row, pc = c - r * cm.pieces_per_row;
+      return src0 + r * cm.ldx * 2 + pc * pb;
+    };
+    auto dst_off = [&](long long c) {
+      const long long r = c / cm.pieces_per_row, pc = c - r * cm.pieces_per_row;
+      return ((long long)cm.rank * cm.rows_per_rank + r) * p.K * 2 + pc * pb;
+    };
+    auto issue_load = [&](long long c) {
+      const int b = n_issued & 1;
+      tma_store_wait_read<0>();                       // the store that last used this buffer has read it
+      mbar_expect_tx(pbar(b), pb);
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(buf0 + b * 8192), "l"(src_of(c)), "r"(pb), "r"(pbar(b)) : "memory");
+      ++n_issued;
+    };
     for (int i = 1; i <= cm.world; ++i) {
       const int peer = (cm.rank + i) % cm.world;
-      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(cm.peer_xfull[peer]) + (long long)cm.rank * cm.rows_per_rank * p.K;
-      // eight independent 16-byte loads in flight per thread, then the eight peer stores
-      for (long long v0 = lo + t; v0 < hi; v0 += 64 * 8) {
-        uint4 q[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const long long v = v0 + u * 64;
-          if (v < hi) {
-            const long long r = v / vec_per_row, cv = v - r * vec_per_row;
-            q[u] = *reinterpret_cast<const uint4*>(cm.x_local + r * cm.ldx + cv * 8);
-          }
+      if (lane == 0) {
+        char* dst = reinterpret_cast<char*>(cm.peer_xfull[peer]);
+        if (okp && c_first < nchunks) issue_load(c_first);
+        for (long long c = c_first; c < nchunks && okp; c += c_step) {
+          if (c + c_step < nchunks) issue_load(c + c_step);
+          const int b = n_done & 1;
+          if (!mbar_wait(pbar(b), (n_done >> 1) & 1, abort_flag, p.status)) { okp = false; break; }
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                       ::"l"(dst + dst_off(c)), "r"(buf0 + b * 8192), "r"(pb) : "memory");
+          tma_store_commit();
+          ++n_done;
         }
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const long long v = v0 + u * 64;
-          if (v < hi) {
-            const long long r = v / vec_per_row, cv = v - r * vec_per_row;
-            *reinterpret_cast<uint4*>(dst + r * p.K + cv * 8) = q[u];
-          }
-        }
+        tma_store_wait<0>();                            // every store to this peer has completed
+        __threadfence_system();
       }
-      __threadfence_system();
-      named_bar_sync(1, 64);
-      if (t == 0 && peer != cm.rank) {
+      __syncwarp();
+      named_bar_sync(1, 64);                            // both push warps are done with this peer
+      if (w == 0 && lane == 0 && peer != cm.rank) {     // one counter increment per CTA
         unsigned int* cnt = reinterpret_cast<unsigned int*>(cm.peer_flags[peer]) + cm.rank;
         asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
+      }
+    }
+    if (lane == 0 && !okp) {   // give a load that is still in flight a bounded chance to land before the CTA exits
+      for (uint32_t j = n_done; j < n_issued; ++j) {
+        const long long t0 = clock64();
+        while (!mbar_try(pbar(j & 1), (j >> 1) & 1) && clock64() - t0 < 4000000) {}
       }
     }
   }
@@ -951,7 +976,21 @@ ELFA_API int elfa_gemm_ag(const void* x_local, long long ldx, const unsigned lon
   c.wait_cycles = wait_cycles_of(wait_ms);
   c.x_local = static_cast<const __nv_bfloat16*>(x_local);
   c.ldx = ldx;
-  for (int i = 0; i < world; ++i) { c.peer_xfull[i] = peer_xfull[i]; c.peer_flags[i] = peer_flags[i]; }
+  {
+    // a row travels in equal pieces of at most 8 KB whose size is a multiple of 16 bytes (bulk-copy rule)
+    const long long rb = (long long)K * 2;
+    int ppr = (int)((rb + 8191) / 8192);
+    while (ppr <= 64 && rb % ((long long)ppr * 16) != 0) ++ppr;
+    ELFA_REQUIRE(ppr <= 64, "gemm_ag: K * 2 bytes cannot be split into 16-byte aligned pieces of at most 8 KB");
+    c.pieces_per_row = ppr;
+    c.piece_bytes = (int)(rb / ppr);
+  }
+  ELFA_REQUIRE((reinterpret_cast<uintptr_t>(x_local) & 15) == 0, "gemm_ag: x_local must be 16-byte aligned");
+  for (int i = 0; i < world; ++i) {
+    ELFA_REQUIRE((peer_xfull[i] & 15) == 0, "gemm_ag: gathered buffers must be 16-byte aligned");
+    c.peer_xfull[i] = peer_xfull[i];
+    c.peer_flags[i] = peer_flags[i];
+  }
   c.my_flags = static_cast<const unsigned int*>(my_flags);
   *arrivals_io += (unsigned)comm_grid(M, N, BN);        // every CTA of a source bumps the counter once
   c.flag_target = *arrivals_io;

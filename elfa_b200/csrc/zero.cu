@@ -76,6 +76,48 @@ __global__ void __launch_bounds__(256) zero_reduce_kernel(PeerPtrs grads, int ra
   }
 }
 
+// ---- stage 3 -------------------------------------------------------------------------------------
+// Parameter gather with peer loads: dst[r * shard .. (r+1) * shard) = shard of rank r (16-byte vectors).
+__global__ void __launch_bounds__(256) zero3_gather_kernel(PeerPtrs shards, int world, long long src_off, long long shard_vecs,
+                                                           uint4* __restrict__ dst) {
+  const long long total = shard_vecs * world;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long v0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; v0 < total; v0 += 4 * stride) {
+    uint4 q[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {    // four independent peer loads in flight per thread
+      const long long v = v0 + u * stride;
+      if (v < total) {
+        const int r = (int)(v / shard_vecs);
+        const long long i = v - (long long)r * shard_vecs;
+        q[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(shards.p[r]) + src_off + i * 16);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long v = v0 + u * stride;
+      if (v < total) dst[v] = q[u];
+    }
+  }
+}
+
+// Gradient reduce-scatter with peer loads: acc[i] += scale * sum_r grads_r[lo + i] (fixed order).
+__global__ void __launch_bounds__(256) zero3_reduce_acc_kernel(PeerPtrs grads, int world, long long lo, long long n,
+                                                               float* __restrict__ acc, float scale) {
+  const long long nvec = n / 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += stride) {
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < world; ++r) {
+      const float4 g = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + lo + v * 4);
+      s.x += g.x; s.y += g.y; s.z += g.z; s.w += g.w;
+    }
+    float4 a = reinterpret_cast<float4*>(acc)[v];
+    a.x += s.x * scale; a.y += s.y * scale; a.z += s.z * scale; a.w += s.w * scale;
+    reinterpret_cast<float4*>(acc)[v] = a;
+  }
+}
+
 __global__ void zero_sumsq_finish_kernel(const float* __restrict__ part, int P, StepScalarsZ* scal) {
   __shared__ float sm[256];
   float a = 0.f;
@@ -202,6 +244,35 @@ ELFA_API int elfa_zero_adamw_allgather(const unsigned long long* peer_params, in
   zero_adamw_allgather_kernel<<<zgrid(n / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       pp, rank, world, lo, n, master, m, v, reduced, lr, beta1, beta2, eps, wd, bc1, bc2, static_cast<const StepScalarsZ*>(scalars),
       wd_lo, wd_hi);
+  ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
+  return ELFA_OK;
+}
+
+// Stage 3 parameter gather: dst (this rank's full-size slot) = concatenation of every rank's shard, which
+// starts `src_off_bytes` into the rank's shard buffer (peer_shards: `world` device addresses). Peer loads only.
+ELFA_API int elfa_zero3_gather(const unsigned long long* peer_shards, int world, long long src_off_bytes, long long shard_bytes,
+                               void* dst, void* stream) {
+  ELFA_REQUIRE(peer_shards && dst && world >= 1 && world <= ZMAX, "zero3_gather: bad arguments");
+  ELFA_REQUIRE(shard_bytes > 0 && shard_bytes % 16 == 0 && src_off_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0,
+               "zero3_gather: sizes and offsets must be multiples of 16 bytes");
+  PeerPtrs pp{};
+  for (int i = 0; i < world; ++i) pp.p[i] = peer_shards[i];
+  const long long vecs = shard_bytes / 16;
+  zero3_gather_kernel<<<zgrid(vecs * world / 4 + 1), 256, 0, static_cast<cudaStream_t>(stream)>>>(pp, world, src_off_bytes, vecs,
+                                                                                                static_cast<uint4*>(dst));
+  ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
+  return ELFA_OK;
+}
+
+// Stage 3 gradient reduce-scatter: acc[0..n) += scale * sum over ranks of grads_r[lo .. lo+n) (fp32 elements).
+ELFA_API int elfa_zero3_reduce_acc(const unsigned long long* peer_grads, int world, long long lo, long long n, float* acc, float scale,
+                                   void* stream) {
+  ELFA_REQUIRE(peer_grads && acc && world >= 1 && world <= ZMAX && n > 0 && n % 4 == 0 && lo % 4 == 0, "zero3_reduce_acc: bad arguments");
+  PeerPtrs pp{};
+  for (int i = 0; i < world; ++i) pp.p[i] = peer_grads[i];
+  zero3_reduce_acc_kernel<<<zgrid(n / 4), 256, 0, static_cast<cudaStream_t>(stream)>>>(pp, world, lo, n, acc, scale);
   ELFA_CUDA(cudaGetLastError());
   ::elfa::count_launches(1);
   return ELFA_OK;

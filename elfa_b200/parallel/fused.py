@@ -44,6 +44,8 @@ class _State:
         self.arena = arena
         self.slots: Dict[Tuple[str, int, int], _Slot] = {}
         self.counter = {"ag": 0, "rs": 0}
+        self.side: Optional[torch.cuda.Stream] = None      # copies of gathered inputs out of the ring
+        self.pending: Optional[torch.cuda.Event] = None
 
     def next_slot(self, kind: str, nbytes: int) -> _Slot:
         i = self.counter[kind] % RING
@@ -71,6 +73,16 @@ def _state(pc: ParallelContext) -> _State:
     return st
 
 
+def wait_pending_copies(pc: ParallelContext) -> None:
+    """Makes the current stream wait for the side-stream copy of the last gathered input. Called
+    before the next all-gather kernel (whose peers may overwrite the ring slot two calls later) and
+    before a backward pass reads such a copy."""
+    st = _states.get(id(pc.symm)) if pc.symm is not None else None
+    if st is not None and st.pending is not None:
+        torch.cuda.current_stream().wait_event(st.pending)
+        st.pending = None
+
+
 def _round_class(nbytes: int) -> int:
     q = 1 << 20
     return (nbytes + q - 1) // q * q
@@ -81,8 +93,12 @@ def supported(rows_local: int, K: int, N: int) -> bool:
 
 
 def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, pc: ParallelContext, *, b_mn: bool, act: Optional[str] = None,
-            preact: bool = False):
-    """``y = act(all_gather_rows(x_local) @ op(w))`` → ``(y, x_full, pre)``."""
+            preact: bool = False, keep: bool = True, defer_copy: bool = False):
+    """``y = act(all_gather_rows(x_local) @ op(w))`` → ``(y, x_full, pre)``. With ``keep`` the gathered
+    input is copied out of the ring (on a side stream; it outlives the slot). Without it ``x_full`` is
+    the ring slot itself, valid until the second all-gather after this one. ``defer_copy``: the caller
+    promises to call :func:`wait_pending_copies` before it reads ``x_full`` (the next fused all-gather
+    does so by itself); otherwise the current stream waits for the copy right away."""
     world, rank = pc.tp_size, pc.tp_rank
     Ml, K = x_local.shape
     N = w.shape[1] if b_mn else w.shape[0]
@@ -90,11 +106,12 @@ def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, pc: ParallelContext, *, b_mn
         from . import tp
         saved, pc.comm_backend = pc.comm_backend, "nccl"
         try:
-            return tp.ag_gemm(x_local, w, pc, b_mn=b_mn, act=act, preact=preact)
+            return tp.ag_gemm(x_local, w, pc, b_mn=b_mn, act=act, preact=preact, keep=keep, defer_copy=defer_copy)
         finally:
             pc.comm_backend = saved
     M = Ml * world
     st = _state(pc)
+    wait_pending_copies(pc)
     slot = st.next_slot("ag", _round_class(M * K * 2))
     xl = x_local if x_local.is_contiguous() else x_local.contiguous()
     y = torch.empty((M, N), dtype=torch.bfloat16, device=x_local.device)
@@ -107,7 +124,23 @@ def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, pc: ParallelContext, *, b_mn
     lib.call("elfa_gemm_ag", xl, xl.stride(0), ctypes.addressof(slot.peer_data), ctypes.addressof(slot.peer_flags),
              slot.flags.tensor, ctypes.addressof(slot.arrivals), w, y, M, N, K, w.stride(0), y.stride(0), int(b_mn), pre,
              pre.stride(0) if pre is not None else 0, flags, rank, world, _WAIT_MS, stream_ptr(xl))
-    x_full = slot.data.view(torch.bfloat16, (M, K)).clone()      # kept for the weight gradient
+    view = slot.data.view(torch.bfloat16, (M, K))
+    if not keep:
+        return y, view, pre
+    # kept for the weight gradient: copied while the following kernels run
+    if st.side is None:
+        st.side = torch.cuda.Stream(x_local.device)
+    x_full = torch.empty((M, K), dtype=torch.bfloat16, device=x_local.device)
+    cur = torch.cuda.current_stream()
+    st.side.wait_stream(cur)
+    with torch.cuda.stream(st.side):
+        x_full.copy_(view)
+        ev = torch.cuda.Event()
+        ev.record(st.side)
+    x_full.record_stream(st.side)
+    st.pending = ev
+    if not defer_copy:
+        wait_pending_copies(pc)
     return y, x_full, pre
 
 

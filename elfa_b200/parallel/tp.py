@@ -135,13 +135,13 @@ class _ReduceFromTP(torch.autograd.Function):
 
 # ------------------------------------------------------------------- the two fused primitives
 def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, pc: ParallelContext, *, b_mn: bool, act: Optional[str] = None,
-            preact: bool = False) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+            preact: bool = False, keep: bool = True, defer_copy: bool = False) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
     """``y = act(all_gather_rows(x_local) @ op(w))``. Returns ``(y, x_full, pre)`` - the gathered
     input is a by-product that backward needs for the weight gradient. ``w`` is ``[K, N]`` when
     ``b_mn`` else ``[N, K]``."""
     if pc.comm_backend == "fused" and x_local.is_cuda:
         from . import fused
-        return fused.ag_gemm(x_local, w, pc, b_mn=b_mn, act=act, preact=preact)
+        return fused.ag_gemm(x_local, w, pc, b_mn=b_mn, act=act, preact=preact, keep=keep, defer_copy=defer_copy)
     x_full = _all_gather_dim0(x_local, pc)
     pre = None
     if act == "gelu":
@@ -180,7 +180,7 @@ class _ColumnParallelSP(torch.autograd.Function):
         Sl, B, D = x.shape
         xq = fake_quant(x.reshape(Sl * B, D), quant) if quant is not None else x.reshape(Sl * B, D)
         wq = cached_weight_quant(w, quant) if quant is not None else w
-        y, x_full, pre = ag_gemm(xq, wq, pc, b_mn=True, act=act, preact=True)
+        y, x_full, pre = ag_gemm(xq, wq, pc, b_mn=True, act=act, preact=True, defer_copy=True)   # backward waits for the copy
         ctx.save_for_backward(x_full, wq, pre)
         ctx.pc, ctx.w_ref, ctx.shape = pc, w, (Sl, B, D)
         return y.view(Sl * pc.tp_size, B, -1)
@@ -189,6 +189,9 @@ class _ColumnParallelSP(torch.autograd.Function):
     def backward(ctx, dy):
         x_full, wq, pre = ctx.saved_tensors
         pc = ctx.pc
+        if pc.comm_backend == "fused" and x_full.is_cuda:
+            from . import fused
+            fused.wait_pending_copies(pc)        # x_full may have been copied on a side stream
         Sl, B, D = ctx.shape
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():
@@ -228,7 +231,7 @@ class _RowParallelSP(torch.autograd.Function):
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        dx, dy_full, _ = ag_gemm(dy2, wq, pc, b_mn=False)   # all_gather(dy) @ w^T
+        dx, dy_full, _ = ag_gemm(dy2, wq, pc, b_mn=False, keep=False)   # all_gather(dy) @ w^T; dy_full is consumed right below
         dw = _wgrad(ctx.w_ref, xq, dy_full, wq.dtype)
         return dx.view(S, B, K), dw, None, None
 

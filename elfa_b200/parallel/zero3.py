@@ -45,6 +45,7 @@ class _Bucket:
     base: int = 0                                           # offset of this bucket's shard in the local flat buffers
     full: Optional[torch.Tensor] = None                     # full-size parameter slot (shared between blocks of equal parity)
     full_grad: Optional[torch.Tensor] = None                # full-size fp32 gradient slot
+    slot: int = 0                                           # gradient slot index (-1: the rest bucket's own buffer)
     module: Optional[torch.nn.Module] = None
     state: str = "sharded"                                  # sharded | fwd | bwd
     ready: Optional[object] = None                          # CUDA event: gather finished
@@ -59,7 +60,11 @@ class Zero3Shards:
     symm = None
 
     def __init__(self, model: torch.nn.Module, pc: ParallelContext, blocks: Optional[Iterable[torch.nn.Module]] = None,
-                 grad_dtype: torch.dtype = torch.float32, prefetch: bool = True):
+                 grad_dtype: torch.dtype = torch.float32, prefetch: bool = True, arena=None):
+        """``arena``: a symmetric arena of the data-parallel group. With it the shards and the gradient
+        slots live in peer-addressable memory and both collectives are this library's peer-load kernels
+        (gather: every rank reads the peers' shards; reduce-scatter: every rank sums its slice of the
+        peers' gradient slots in fixed rank order), ordered by signal-word barriers."""
         if pc.tp_size != 1:
             raise ValueError("ZeRO stage 3 is implemented for pure data parallelism (tensor_parallel_size 1)")
         self.pc, self.model = pc, model
@@ -98,7 +103,14 @@ class Zero3Shards:
             b.base = base
             base += b.shard
         self.numel = base                       # local elements: what the optimizer updates
-        self.flat = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
+        self.arena = arena if (arena is not None and self.device.type == "cuda" and grad_dtype == torch.float32) else None
+        esz = torch.empty(0, dtype=self.dtype).element_size()
+        if self.arena is not None:
+            self._r_flat = self.arena.alloc(self.numel * esz, "zero3.shards")
+            self.flat = self._r_flat.view(self.dtype, (self.numel,))
+            self.flat.zero_()
+        else:
+            self.flat = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
         self.grads = torch.zeros(self.numel, dtype=grad_dtype, device=self.device)
         self.replicated_end = 0
         self.shard_lo, self.shard_hi, self.shard_size = 0, self.numel, self.numel
@@ -107,12 +119,31 @@ class Zero3Shards:
         # full-size slots: two for the blocks, one for the rest
         nslot = max((b.numel for b in self.block_buckets), default=0)
         self._pslots = [torch.zeros(nslot, dtype=self.dtype, device=self.device) for _ in range(2)] if nslot else []
-        self._gslots = [torch.zeros(nslot, dtype=grad_dtype, device=self.device) for _ in range(2)] if nslot else []
+        self._g_regions = []
+        if self.arena is not None:
+            import ctypes
+            self._g_regions = [self.arena.alloc(max(nslot, 4) * 4, f"zero3.gslot{j}") for j in range(2)]
+            self._gslots = [r.view(grad_dtype, (nslot,)) for r in self._g_regions] if nslot else []
+            self._r_rest_grad = self.arena.alloc(self.rest.numel * 4, "zero3.rest_grad")
+            rest_grad = self._r_rest_grad.view(grad_dtype, (self.rest.numel,))
+            flags = self.arena.alloc(1024, "zero3.barrier")
+            w = self.arena.world
+            mk = lambda region: (ctypes.c_uint64 * w)(*[self.arena.peer_address(r, region) for r in range(w)])
+            self._peer = {"flat": mk(self._r_flat), "gslot": [mk(r) for r in self._g_regions], "rest_grad": mk(self._r_rest_grad),
+                          "flags": mk(flags), "my_flags": flags, "epoch": 0}
+            for g in self._gslots:
+                g.zero_()
+            rest_grad.zero_()
+        else:
+            self._gslots = [torch.zeros(nslot, dtype=grad_dtype, device=self.device) for _ in range(2)] if nslot else []
+            rest_grad = torch.zeros(self.rest.numel, dtype=grad_dtype, device=self.device)
         for i, b in enumerate(self.block_buckets):
             b.full = self._pslots[i % 2][:b.numel]
             b.full_grad = self._gslots[i % 2][:b.numel]
+            b.slot = i % 2
         self.rest.full = torch.zeros(self.rest.numel, dtype=self.dtype, device=self.device)
-        self.rest.full_grad = torch.zeros(self.rest.numel, dtype=grad_dtype, device=self.device)
+        self.rest.full_grad = rest_grad
+        self.rest.slot = -1
         # move every parameter into its slot view; keep this rank's slice as the persistent shard
         with torch.no_grad():
             for b in self.buckets:
@@ -131,6 +162,17 @@ class Zero3Shards:
         self.reduce_scatters = 0
         for i, b in enumerate(self.block_buckets):
             self._hook(i, b)
+        if self.arena is not None:
+            self.arena.barrier()          # every rank's shards are in place before the first peer load
+
+    def _barrier(self) -> None:
+        """Device-side barrier over the group on the current stream (bounded wait)."""
+        import ctypes
+        from ..native import lib, stream_ptr
+        z = self._peer
+        z["epoch"] += 1
+        lib.call("elfa_symm_barrier", ctypes.addressof(z["flags"]), z["my_flags"].tensor, self.rank, self.dp, z["epoch"], 0,
+                 stream_ptr(self.flat))
 
     # ------------------------------------------------------------------ collectives on one bucket
     def _gather_into(self, b: _Bucket) -> None:
@@ -138,6 +180,12 @@ class Zero3Shards:
         self.gathers += 1
         if self.dp == 1:
             b.full.copy_(shard)
+        elif self.arena is not None:
+            import ctypes
+            from ..native import lib, stream_ptr
+            esz = self.flat.element_size()
+            lib.call("elfa_zero3_gather", ctypes.addressof(self._peer["flat"]), self.dp, b.base * esz, b.shard * esz, b.full,
+                     stream_ptr(b.full))
         elif self.cuda:
             dist.all_gather_into_tensor(b.full, shard, group=self.group)
         else:
@@ -176,6 +224,13 @@ class Zero3Shards:
         self.reduce_scatters += 1
         if self.dp == 1:
             dst.add_(b.full_grad)
+        elif self.arena is not None:
+            import ctypes
+            from ..native import lib, stream_ptr
+            self._barrier()               # every rank's gradient of this bucket is complete and visible
+            peers = self._peer["rest_grad"] if b.slot < 0 else self._peer["gslot"][b.slot]
+            lib.call("elfa_zero3_reduce_acc", ctypes.addressof(peers), self.dp, self.rank * b.shard, b.shard, dst, 1.0 / self.dp,
+                     stream_ptr(dst))
         elif self.cuda:
             out = torch.empty_like(dst)
             dist.reduce_scatter_tensor(out, b.full_grad, op=dist.ReduceOp.AVG, group=self.group)
@@ -255,6 +310,8 @@ class Zero3Shards:
 
     def after_step(self) -> None:
         self._rest_valid = False
+        if self.arena is not None and self.dp > 1:
+            self._barrier()               # all shards updated before anyone gathers them again
 
     def zero_grad(self) -> None:
         self.grads.zero_()

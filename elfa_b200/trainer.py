@@ -73,7 +73,14 @@ class Trainer:
             dp_arena = SymmetricArena.for_group(pc.dp_group, device, n_est * 6 + (16 << 20))
         if cfg.runtime.zero_stage == 3 and pc.dp_size > 1:
             from .parallel.zero3 import Zero3Shards
-            self.flat = Zero3Shards(self.model, pc)
+            arena3 = None
+            if pc.comm_backend == "fused" and device.type == "cuda" and pc.tp_size == 1:
+                from .runtime.symm import SymmetricArena
+                n_est = sum(p.numel() + 64 for p in self.model.parameters())
+                esz = 2 if cfg.model.dtype != "fp32" else 4
+                per_block = n_est // max(cfg.model.num_layers, 1) + (1 << 20)
+                arena3 = SymmetricArena.for_group(pc.dp_group, device, n_est * esz // pc.dp_size + 3 * per_block * 4 + n_est * 4 // 4 + (64 << 20))
+            self.flat = Zero3Shards(self.model, pc, arena=arena3)
         else:
             self.flat = FlatParams(self.model.named_checkpoint_parameters(), dp_size=pc.dp_size, dp_rank=pc.dp_rank, allocator=dp_arena)
         self.zero3 = bool(getattr(self.flat, "presharded", False))

@@ -137,6 +137,7 @@ def mode_zero(dev, backend, dtype, stage):
         for a, b in zip(losses, ref):
             assert abs(a - b) < tol * max(1.0, abs(b)), f"ZeRO losses {losses} differ from single-rank {ref}"
         print(f"ZERO_OK stage={stage} backend={backend} fused={tr.optimizer.zero_fused is not None} "
+              f"peer_kernels={getattr(tr.flat, 'arena', None) is not None} "
               f"losses={[round(x, 4) for x in losses]} ref={[round(x, 4) for x in ref]}")
     dist.barrier()
 

@@ -57,8 +57,12 @@ def test_zero1_data_parallel_matches_single_gpu(cuda_device, backend):
         assert "fused=True" in r.stdout
 
 
-def test_zero3_parameter_sharding_matches_single_gpu(cuda_device):
-    """Stage 3: blocks gathered on demand (prefetch on a side stream), gradients reduce-scattered per block."""
-    r = _run(["zero", "nccl", "bf16", "3"], 29707)
+@pytest.mark.parametrize("backend", ["nccl", "fused"])
+def test_zero3_parameter_sharding_matches_single_gpu(cuda_device, backend):
+    """Stage 3: blocks gathered on demand (prefetch on a side stream), gradients reduce-scattered per block;
+    `fused` = peer-load gather / reduce kernels on a symmetric arena instead of the library collectives."""
+    r = _run(["zero", backend, "bf16", "3"], 29707 if backend == "nccl" else 29708)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "ZERO_OK stage=3" in r.stdout
+    if backend == "fused":
+        assert "peer_kernels=True" in r.stdout
