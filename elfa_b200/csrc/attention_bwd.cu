@@ -45,7 +45,7 @@ struct AttnBwdParams {
   unsigned int* status;
 };
 
-enum { BB_RES = 0, BB_INFULL0, BB_INFULL1, BB_INFREE0, BB_INFREE1, BB_SDP, BB_PDS, BB_ACC, BB_COUNT };
+enum { BB_RES = 0, BB_INFULL0, BB_INFULL1, BB_INFREE0, BB_INFREE1, BB_S, BB_DP, BB_P, BB_DS, BB_ACC, BB_COUNT };
 
 template <int HDP>
 struct BwdSmem {
@@ -111,7 +111,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmQKV);
     prefetch_tmap(&tmDO);
-    for (int i = 0; i < BB_COUNT; ++i) mbar_init(bar(i), i == BB_PDS ? 256 : 1);
+    for (int i = 0; i < BB_COUNT; ++i) mbar_init(bar(i), (i == BB_P || i == BB_DS) ? 256 : 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -156,44 +156,63 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    // MMA issuer: the warp runs converged, one elected lane issues (descriptors stay in uniform registers)
+    {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
       constexpr uint32_t idesc_acc = make_idesc_bf16(128, HDP, false, true);   // A from tensor memory, B MN-major
-      bool ok = mbar_wait(bar(BB_RES), 0, abort_flag, p.status);
+      auto wait = [&](int bi, uint32_t ph) { return __all_sync(0xffffffffu, mbar_wait(bar(bi), ph, abort_flag, p.status)) != 0; };
+      bool ok = wait(BB_RES, 0);
       for (int it = 0; it < n_iter && ok; ++it) {
         const int slot = it & 1;
-        if (!mbar_wait(bar(BB_INFULL0 + slot), (it >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+        if (!wait(BB_INFULL0 + slot, (it >> 1) & 1)) { ok = false; break; }
         tc_fence_after();
         // DKV: S^T = K Q^T, dP^T = V dO^T (A = resident);  DQ: S = Q K^T, dP = dO V^T (A = resident)
         const uint32_t a0 = sRes0, a1 = sRes1, b0 = sIn0(slot), b1 = sIn1(slot);
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < HDP / 16; ++kk) {
-          const uint32_t off = (kk / 4) * SUBB + (kk % 4) * 32;
-          tc_mma_f16(TM_S, make_smem_desc(a0 + off, 16, 1024, 2), make_smem_desc(b0 + off, 16, 1024, 2), idesc_s, kk != 0);
-        }
+          for (int kk = 0; kk < HDP / 16; ++kk) {
+            const uint32_t off = (kk / 4) * SUBB + (kk % 4) * 32;
+            tc_mma_f16(TM_S, make_smem_desc(a0 + off, 16, 1024, 2), make_smem_desc(b0 + off, 16, 1024, 2), idesc_s, kk != 0);
+          }
+          tc_commit(bar(BB_S));      // the exponentials start while dP is still being multiplied
 #pragma unroll
-        for (int kk = 0; kk < HDP / 16; ++kk) {
-          const uint32_t off = (kk / 4) * SUBB + (kk % 4) * 32;
-          tc_mma_f16(TM_DP, make_smem_desc(a1 + off, 16, 1024, 2), make_smem_desc(b1 + off, 16, 1024, 2), idesc_s, kk != 0);
+          for (int kk = 0; kk < HDP / 16; ++kk) {
+            const uint32_t off = (kk / 4) * SUBB + (kk % 4) * 32;
+            tc_mma_f16(TM_DP, make_smem_desc(a1 + off, 16, 1024, 2), make_smem_desc(b1 + off, 16, 1024, 2), idesc_s, kk != 0);
+          }
+          tc_commit(bar(BB_DP));
         }
-        tc_commit(bar(BB_SDP));
-        if (!mbar_wait(bar(BB_PDS), it & 1, abort_flag, p.status)) { ok = false; break; }
-        tc_fence_after();
+        __syncwarp();
         if (DKV) {
+          if (!wait(BB_P, it & 1)) { ok = false; break; }
+          tc_fence_after();
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)   // dV[key, d] += sum_q P^T[key, q] dO[q, d]
-            tc_mma_f16_ts(TM_ACC0, TM_S + kk * 8, make_smem_desc(b1 + kk * 2048, SUBB, 1024, 2), idesc_acc, (it | kk) != 0);
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk)   // dK[key, d] += sum_q dS^T[key, q] Q[q, d]
-            tc_mma_f16_ts(TM_ACC1, TM_DP + kk * 8, make_smem_desc(b0 + kk * 2048, SUBB, 1024, 2), idesc_acc, (it | kk) != 0);
-        } else {
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk)   // dQ[q, d] += sum_key dS[q, key] K[key, d]
-            tc_mma_f16_ts(TM_ACC0, TM_DP + kk * 8, make_smem_desc(b0 + kk * 2048, SUBB, 1024, 2), idesc_acc, (it | kk) != 0);
+            for (int kk = 0; kk < 8; ++kk)   // dV[key, d] += sum_q P^T[key, q] dO[q, d]  (runs while dS is computed)
+              tc_mma_f16_ts(TM_ACC0, TM_S + kk * 8, make_smem_desc(b1 + kk * 2048, SUBB, 1024, 2), idesc_acc, (it | kk) != 0);
+          }
+          __syncwarp();
         }
-        tc_commit(bar(BB_INFREE0 + slot));
+        if (!wait(BB_DS, it & 1)) { ok = false; break; }
+        tc_fence_after();
+        if (elect_one()) {
+          if (DKV) {
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)   // dK[key, d] += sum_q dS^T[key, q] Q[q, d]
+              tc_mma_f16_ts(TM_ACC1, TM_DP + kk * 8, make_smem_desc(b0 + kk * 2048, SUBB, 1024, 2), idesc_acc, (it | kk) != 0);
+          } else {
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)   // dQ[q, d] += sum_key dS[q, key] K[key, d]
+              tc_mma_f16_ts(TM_ACC0, TM_DP + kk * 8, make_smem_desc(b0 + kk * 2048, SUBB, 1024, 2), idesc_acc, (it | kk) != 0);
+          }
+          tc_commit(bar(BB_INFREE0 + slot));
+        }
+        __syncwarp();
       }
-      if (ok) tc_commit(bar(BB_ACC));
+      if (ok) {
+        if (elect_one()) tc_commit(bar(BB_ACC));
+        __syncwarp();
+      }
     }
   } else {
     // ---------------------------------------------------------------- compute warps
@@ -229,60 +248,83 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
       }
       // After a timeout the loop keeps running without touching tensor memory so that every warp
       // still reaches the named barriers below (the waits return immediately once the abort flag is up).
-      if (ok) ok = mbar_wait(bar(BB_SDP), it & 1, abort_flag, p.status);
+      if (ok) ok = mbar_wait(bar(BB_S), it & 1, abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
       tc_fence_after();
       const bool diag = p.causal && q_tile == k_tile;
-      uint32_t keep_p[32], keep_d[32];   // this thread's 64 columns as bf16 pairs (P / dS)
+      float ev[64];                      // this thread's 64 probabilities (fp32, kept for dS)
+      uint32_t keep[32];                 // ... and as bf16 pairs (P, then dS)
+      // ---- phase 1: P = exp2(S * scale - lse)
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         if (!ok) break;
         const int col0 = half * 64 + c * 32;
-        uint32_t rs[32], rd[32];
+        uint32_t rs[32];
         tmem_ld32(TM_S + lane_addr + col0, rs);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int col = col0 + i;
+          const float l2 = DKV ? vl[col] : lse2;
+          float e = fast_exp2(fmaf(__uint_as_float(rs[i]), p.scale_log2, -l2));
+          // DKV: lane = key, column = query -> masked when key > query; DQ: lane = query, column = key
+          const bool masked = DKV ? (diag && row_local > col) : (!row_ok || (diag && col > row_local));
+          if (masked) e = 0.f;
+          ev[c * 32 + i] = e;
+        }
+      }
+      if (DKV) {
+        // The bf16 results go back into tensor memory on top of fp32 columns: a row's 128 values take
+        // 64 columns, so the upper half lands on columns the partner warp (other half, same lanes) was
+        // reading. All 256 compute threads therefore finish their loads before anyone stores.
+        tc_fence_before();
+        named_bar_sync(1, 256);
+        tc_fence_after();
+        if (ok) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) keep[i] = pack_bf16(ev[2 * i], ev[2 * i + 1]);
+          uint32_t t0[16], t1[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) { t0[i] = keep[i]; t1[i] = keep[16 + i]; }
+          tmem_st16(TM_S + lane_addr + half * 32, t0);
+          tmem_st16(TM_S + lane_addr + half * 32 + 16, t1);
+          tmem_st_wait();
+        }
+        tc_fence_before();
+        mbar_arrive(bar(BB_P));
+      }
+      // ---- phase 2: dS = P * (dP - delta) * scale
+      if (ok) ok = mbar_wait(bar(BB_DP), it & 1, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        if (!ok) break;
+        const int col0 = half * 64 + c * 32;
+        uint32_t rd[32];
         tmem_ld32(TM_DP + lane_addr + col0, rd);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float e[2], d[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = col0 + i + u;
-            const float l2 = DKV ? vl[col] : lse2;
-            const float dl = DKV ? vl[128 + col] : dlt;
-            float ev = fast_exp2(__uint_as_float(rs[i + u]) * p.scale_log2 - l2);
-            // DKV: lane = key, column = query -> masked when key > query; DQ: lane = query, column = key
-            const bool masked = DKV ? (diag && row_local > col) : (!row_ok || (diag && col > row_local));
-            if (masked) ev = 0.f;
-            e[u] = ev;
-            d[u] = ev * (__uint_as_float(rd[i + u]) - dl) * p.scale;
-          }
-          keep_p[c * 16 + (i >> 1)] = pack_bf16(e[0], e[1]);
-          keep_d[c * 16 + (i >> 1)] = pack_bf16(d[0], d[1]);
+          const float dl0 = DKV ? vl[128 + col0 + i] : dlt, dl1 = DKV ? vl[128 + col0 + i + 1] : dlt;
+          const float d0 = ev[c * 32 + i] * (__uint_as_float(rd[i]) - dl0) * p.scale;
+          const float d1 = ev[c * 32 + i + 1] * (__uint_as_float(rd[i + 1]) - dl1) * p.scale;
+          keep[c * 16 + (i >> 1)] = pack_bf16(d0, d1);
         }
       }
-      // The bf16 results go back into tensor memory on top of fp32 columns: a row's 128 values take
-      // 64 columns, so the upper half lands on columns the partner warp (other half, same lanes) was
-      // reading. All 256 compute threads therefore finish their loads before anyone stores.
       tc_fence_before();
-      named_bar_sync(1, 256);
+      named_bar_sync(1, 256);            // every thread has read its dP columns before dS overwrites them
       tc_fence_after();
       if (ok) {
         uint32_t t0[16], t1[16];
-        if (DKV) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) { t0[i] = keep_p[i]; t1[i] = keep_p[16 + i]; }
-          tmem_st16(TM_S + lane_addr + half * 32, t0);
-          tmem_st16(TM_S + lane_addr + half * 32 + 16, t1);
-        }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) { t0[i] = keep_d[i]; t1[i] = keep_d[16 + i]; }
+        for (int i = 0; i < 16; ++i) { t0[i] = keep[i]; t1[i] = keep[16 + i]; }
         tmem_st16(TM_DP + lane_addr + half * 32, t0);
         tmem_st16(TM_DP + lane_addr + half * 32 + 16, t1);
         tmem_st_wait();
       }
       tc_fence_before();
-      mbar_arrive(bar(BB_PDS));
+      mbar_arrive(bar(BB_DS));
     }
     // ---------------------------------------------------------------- epilogue
     if (ok) {

@@ -117,57 +117,69 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // The warp runs converged; one elected lane issues the tensor-core instructions (descriptors stay uniform).
+    {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
       constexpr uint32_t idesc_o = make_idesc_bf16(128, HDP, false, true);
+      auto wait = [&](int bi, uint32_t ph) { return __all_sync(0xffffffffu, mbar_wait(bar(bi), ph, abort_flag, p.status)) != 0; };
+      auto commit = [&](int bi) {
+        if (elect_one()) tc_commit(bar(bi));
+        __syncwarp();
+      };
       auto issue_s = [&](int t) {  // S_t = Q_t K^T
         const uint32_t qb = sbase + L::Q_OFF + t * NSUB * SUB_BYTES, kb = sbase + L::K_OFF;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < HDP / 16; ++kk) {
-          const uint32_t off = (kk / 4) * SUB_BYTES + (kk % 4) * 32;
-          tc_mma_f16(TM_S[t], make_smem_desc(qb + off, 16, 1024, 2), make_smem_desc(kb + off, 16, 1024, 2), idesc_s, kk != 0);
+          for (int kk = 0; kk < HDP / 16; ++kk) {
+            const uint32_t off = (kk / 4) * SUB_BYTES + (kk % 4) * 32;
+            tc_mma_f16(TM_S[t], make_smem_desc(qb + off, 16, 1024, 2), make_smem_desc(kb + off, 16, 1024, 2), idesc_s, kk != 0);
+          }
+          tc_commit(bar(BAR_SFULL0 + t));
         }
-        tc_commit(bar(BAR_SFULL0 + t));
+        __syncwarp();
       };
       auto issue_o = [&](int t, int j) {  // O_t += P_t V_j
         const uint32_t pb = sbase + L::P_OFF + t * 2 * SUB_BYTES, vb = sbase + L::V_OFF;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t poff = (kk / 4) * SUB_BYTES + (kk % 4) * 32;
-          tc_mma_f16(TM_O[t], make_smem_desc(pb + poff, 16, 1024, 2), make_smem_desc(vb + kk * 2048, SUB_BYTES, 1024, 2), idesc_o,
-                     (j | kk) != 0);
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t poff = (kk / 4) * SUB_BYTES + (kk % 4) * 32;
+            tc_mma_f16(TM_O[t], make_smem_desc(pb + poff, 16, 1024, 2), make_smem_desc(vb + kk * 2048, SUB_BYTES, 1024, 2), idesc_o,
+                       (j | kk) != 0);
+          }
+          tc_commit(bar(BAR_OFULL0 + t));
         }
-        tc_commit(bar(BAR_OFULL0 + t));
+        __syncwarp();
       };
-      bool ok = mbar_wait(bar(BAR_Q), 0, abort_flag, p.status) && mbar_wait(bar(BAR_KFULL), 0, abort_flag, p.status);
+      bool ok = wait(BAR_Q, 0) && wait(BAR_KFULL, 0);
       if (ok) {
         tc_fence_after();
         if (n_a > 0) issue_s(0);
         issue_s(1);
-        tc_commit(bar(BAR_KFREE));
+        commit(BAR_KFREE);
       }
       for (int j = 0; j < n_b && ok; ++j) {
         const uint32_t ph = j & 1;
-        if (!mbar_wait(bar(BAR_VFULL), ph, abort_flag, p.status)) break;
+        if (!wait(BAR_VFULL, ph)) break;
         if (j < n_a) {
-          if (!mbar_wait(bar(BAR_PREADY0), ph, abort_flag, p.status)) break;
+          if (!wait(BAR_PREADY0, ph)) break;
           tc_fence_after();
           issue_o(0, j);
           if (j + 1 < n_a) {
-            if (!mbar_wait(bar(BAR_KFULL), ph ^ 1, abort_flag, p.status)) break;
+            if (!wait(BAR_KFULL, ph ^ 1)) break;
             tc_fence_after();
             issue_s(0);
           }
         }
-        if (!mbar_wait(bar(BAR_PREADY1), ph, abort_flag, p.status)) break;
+        if (!wait(BAR_PREADY1, ph)) break;
         tc_fence_after();
         issue_o(1, j);
-        tc_commit(bar(BAR_VFREE));
+        commit(BAR_VFREE);
         if (j + 1 < n_b) {
-          if (!mbar_wait(bar(BAR_KFULL), ph ^ 1, abort_flag, p.status)) break;
+          if (!wait(BAR_KFULL, ph ^ 1)) break;
           tc_fence_after();
           issue_s(1);
-          tc_commit(bar(BAR_KFREE));
+          commit(BAR_KFREE);
         }
       }
     }
@@ -192,22 +204,25 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       const int key0 = j * 128;
       const int limit = p.causal ? row : (p.S - 1);       // last key this row may see
       const bool need_mask = key0 + 127 > (p.causal ? tile * 128 : p.S - 1);
-      // the whole S row: four loads in flight, one wait
-      uint32_t r[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(TM_S[t] + lane_addr + c * 32, r[c]);
-      tmem_ld_wait();
-      float mx = -INFINITY;
+      // Two passes over the S row in 32-column chunks (row maximum, then exponentials), each chunk loaded
+      // from tensor memory while the previous one is processed: about 64 live registers instead of 128.
+      uint32_t cb[2][32];
+      tmem_ld32(TM_S[t] + lane_addr, cb[0]);
+      // four independent chains for the maximum (scale > 0, so scaling commutes with it)
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
+        tmem_ld_wait();
+        if (c + 1 < 4) tmem_ld32(TM_S[t] + lane_addr + (c + 1) * 32, cb[(c + 1) & 1]);
+        else tmem_ld32(TM_S[t] + lane_addr, cb[(c + 1) & 1]);          // first chunk of the second pass
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float sv = __uint_as_float(r[c][i]) * p.scale_log2;
+          float sv = __uint_as_float(cb[c & 1][i]);
           if (need_mask && key0 + c * 32 + i > limit) sv = -INFINITY;
-          r[c][i] = __float_as_uint(sv);
-          mx = fmaxf(mx, sv);
+          mx4[i & 3] = fmaxf(mx4[i & 3], sv);
         }
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
       if (j == 0) {
         m = mx;
       } else {
@@ -220,6 +235,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
           tc_fence_after();
           const float m_new = grow ? mx : m;
           const float alpha = fast_exp2(m - m_new);
+          tmem_ld_wait();                                  // the chunk prefetched for the second pass
 #pragma unroll 1
           for (int c = 0; c < HDP / 32; ++c) {
             uint32_t q[32];
@@ -234,27 +250,33 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
           m = m_new;
         }
       }
-      float lsum = 0.f;
+      float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+      const float neg_m = (m == -INFINITY) ? 0.f : -m;   // a fully masked row so far: exp2(-inf) = 0 without inf - inf
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
+        tmem_ld_wait();
+        if (c + 1 < 4) tmem_ld32(TM_S[t] + lane_addr + (c + 1) * 32, cb[(c + 1) & 1]);
+        uint32_t (&r)[32] = cb[c & 1];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float e = fast_exp2(__uint_as_float(r[c][i]) - m);
-          lsum += e;
-          r[c][i] = __float_as_uint(e);
+          float sv = __uint_as_float(r[i]);
+          if (need_mask && key0 + c * 32 + i > limit) sv = -INFINITY;
+          const float e = fast_exp2(fmaf(sv, p.scale_log2, neg_m));
+          ls4[i & 3] += e;
+          r[i] = __float_as_uint(e);
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           const int q8 = c * 4 + g;  // 16-byte chunk index along the 128 keys
           const uint32_t addr = p_row + (q8 >> 3) * SUB_BYTES + (((q8 & 7) ^ (row_local & 7)) << 4);
-          const uint32_t w0 = pack_bf16(__uint_as_float(r[c][g * 8 + 0]), __uint_as_float(r[c][g * 8 + 1]));
-          const uint32_t w1 = pack_bf16(__uint_as_float(r[c][g * 8 + 2]), __uint_as_float(r[c][g * 8 + 3]));
-          const uint32_t w2 = pack_bf16(__uint_as_float(r[c][g * 8 + 4]), __uint_as_float(r[c][g * 8 + 5]));
-          const uint32_t w3 = pack_bf16(__uint_as_float(r[c][g * 8 + 6]), __uint_as_float(r[c][g * 8 + 7]));
+          const uint32_t w0 = pack_bf16(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
+          const uint32_t w1 = pack_bf16(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
+          const uint32_t w2 = pack_bf16(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
+          const uint32_t w3 = pack_bf16(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
         }
       }
-      l += lsum;
+      l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(bar(BAR_PREADY0 + t));

@@ -161,6 +161,16 @@ __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* tm) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tm) : "memory");
 }
 
+// One lane of a converged warp. Code that issues tcgen05 / TMA instructions should run warp-converged
+// and guard only the instruction itself with this: the descriptors then stay in uniform registers.
+// Inside an `if (lane == 0)` region they are ordinary registers and every instruction pays for moving
+// them, which made one tcgen05.mma cost about 130 cycles to issue whatever its shape.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+
 // ---- tcgen05 / tensor memory ------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
@@ -268,6 +278,16 @@ __device__ __forceinline__ void tc_mma_mxf8_pair(uint32_t tmem_d, uint64_t desc_
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
       : "memory");
 }
+// Block-scaled NVFP4 (e2m1 operands packed two per byte, one ue4m3 scale per 16 K-elements, K = 64 per instruction)
+__device__ __forceinline__ void tc_mma_nvf4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate, uint32_t tmem_sfa, uint32_t tmem_sfb) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
 // the same copy in both CTAs of a pair (each from its own shared memory into its own tensor memory)
 __device__ __forceinline__ void tc_cp_32x128b_warpx4_pair(uint32_t tmem_dst, uint64_t smem_desc) {
   asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(smem_desc) : "memory");
@@ -349,6 +369,11 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, bool a_mn_m
 __host__ __device__ constexpr uint32_t make_idesc_mxf8(int M, int N, uint32_t sfa_id, uint32_t sfb_id) {
   return ((sfb_id & 3u) << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(N >> 3) << 17) | (1u << 23) |
          ((uint32_t)(M >> 4) << 24) | ((sfa_id & 3u) << 29);
+}
+
+// Instruction descriptor for kind::mxf4nvf4.block_scale with e2m1 operands and ue4m3 scales (K = 64).
+__host__ __device__ constexpr uint32_t make_idesc_nvf4(int M, int N) {
+  return (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | (0u << 23) | ((uint32_t)(M >> 4) << 24);
 }
 
 template <int N>

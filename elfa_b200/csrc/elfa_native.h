@@ -86,6 +86,14 @@ int elfa_mxfp8_quantize_gemm(const void* x, long long ldx, void* payload, void* 
 int elfa_gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N, int K, long long ldc,
                     const void* bias, void* preact, long long ldpre, unsigned flags, int force_bn, void* stream);
 
+// Block-scaled NVFP4 tensor-core GEMM (e2m1 payloads two per byte, ue4m3 scales per 16 K-elements, fp32 tensor scale)
+long long elfa_nvfp4_sf_bytes(int rows, int cols, int b_operand);
+int elfa_nvfp4_quantize_gemm(const void* x, long long ldx, void* payload, void* sf, void* deq, int rows, int cols, int b_operand,
+                             const float* tensor_amax, void* stream);
+int elfa_gemm_nvfp4(const void* A, const void* sfa, const float* amax_a, const void* B, const void* sfb, const float* amax_b, void* C,
+                    int M, int N, int K, long long ldc, const void* bias, void* preact, long long ldpre, unsigned flags, int force_bn,
+                    void* stream);
+
 // ---- quant.cu ----------------------------------------------------------------------------------
 int elfa_mxfp8_fake_quant(const void* x, void* out, int rows, int cols, int axis, void* stream);
 int elfa_mxfp8_quantize(const void* x, void* payload, void* scales, int rows, int cols, void* stream);
@@ -117,6 +125,12 @@ int elfa_zero3_gather(const unsigned long long* peer_shards, int world, long lon
                       void* stream);
 int elfa_zero3_reduce_acc(const unsigned long long* peer_grads, int world, long long lo, long long n, float* acc, float scale,
                           void* stream);
+
+// ---- prism.cu ----------------------------------------------------------------------------------
+int elfa_prism_fwd(const void* u, const void* v, const unsigned long long* p, void* y, long long tokens, int G, int d, int L,
+                   void* stream);
+int elfa_prism_bwd(const void* u, const void* v, const unsigned long long* p, const void* dy, void* du, void* dv,
+                   const unsigned long long* dp, long long tokens, int G, int d, int L, void* stream);
 
 // ---- efla.cu -----------------------------------------------------------------------------------
 int elfa_efla_scan_fwd(const void* k, const void* v, const float* beta, const float* state0, void* o, float* state_out,

@@ -294,40 +294,47 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && cta_rank == 0) {
+    // The whole warp walks the loop (converged); one elected lane issues the tensor-core instructions.
+    if (cta_rank == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(TILE_M, BN, A_MN, B_MN);
       uint32_t it = 0, tile_iter = 0;
       bool ok = true;
       for (int unit = wid; unit < num_units && ok; unit += wstride, ++tile_iter) {
         const int kb0 = (unit % splits) * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
         const uint32_t buf = tile_iter & 1, bph = (tile_iter >> 1) & 1;
-        if (!mbar_wait(tempty_bar(buf), bph ^ 1, abort_flag, p.status)) { ok = false; break; }
+        ok = __all_sync(0xffffffffu, mbar_wait(tempty_bar(buf), bph ^ 1, abort_flag, p.status));
+        if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * BN;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(full_bar(s), ph, abort_flag, p.status)) { ok = false; break; }
+          ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, abort_flag, p.status));
+          if (!ok) break;
           tc_fence_after();
           const uint32_t a_base = smem_u32(sA + s * L::A_BYTES);
           const uint32_t b_base = smem_u32(sB + s * L::B_BYTES);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            // K-major: 16 elements = 32 bytes along the swizzled 128-byte row.
-            // MN-major: 16 K-rows of 128 bytes = two 1024-byte swizzle atoms.
-            const uint64_t da = A_MN ? make_smem_desc(a_base + k * 2048, 8192, 1024, 2)
-                                     : make_smem_desc(a_base + k * 32, 16, 1024, 2);
-            const uint64_t db = B_MN ? make_smem_desc(b_base + k * 2048, 8192, 1024, 2)
-                                     : make_smem_desc(b_base + k * 32, 16, 1024, 2);
-            if (TWO) tc_mma_f16_pair(tmem_d, da, db, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
-            else tc_mma_f16(tmem_d, da, db, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              // K-major: 16 elements = 32 bytes along the swizzled 128-byte row.
+              // MN-major: 16 K-rows of 128 bytes = two 1024-byte swizzle atoms.
+              const uint64_t da = A_MN ? make_smem_desc(a_base + k * 2048, 8192, 1024, 2)
+                                       : make_smem_desc(a_base + k * 32, 16, 1024, 2);
+              const uint64_t db = B_MN ? make_smem_desc(b_base + k * 2048, 8192, 1024, 2)
+                                       : make_smem_desc(b_base + k * 32, 16, 1024, 2);
+              if (TWO) tc_mma_f16_pair(tmem_d, da, db, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
+              else tc_mma_f16(tmem_d, da, db, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
+            }
+            // frees the smem slot (in both CTAs of a pair) once these MMAs have read it
+            if (TWO) tc_commit_pair(empty_bar(s)); else tc_commit(empty_bar(s));
           }
-          // frees the smem slot (in both CTAs of a pair) once these MMAs have read it
-          if (TWO) tc_commit_pair(empty_bar(s)); else tc_commit(empty_bar(s));
+          __syncwarp();
         }
-        if (ok) {
+        if (ok && elect_one()) {
           if (TWO) tc_commit_pair(tfull_bar(buf)); else tc_commit(tfull_bar(buf));
         }
+        __syncwarp();
       }
     }
   } else if (warp < 6) {

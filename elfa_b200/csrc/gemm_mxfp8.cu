@@ -27,6 +27,7 @@
 // which is what bounds the single-CTA kernel (about 100 GB/s of L2 -> SM fill per SM, measured).
 //
 // Scale tensor of B is stored [K tile][row block] so that the atoms a tile needs are one contiguous copy.
+#include <cuda_fp4.h>
 #include <cuda_fp8.h>
 
 #include <algorithm>
@@ -53,6 +54,8 @@ struct QParams {
   const uint8_t* sfb;
   int kt;            // K tiles (= scale atoms per row block)
   int sfb_atoms;     // row blocks of the B scale tensor
+  const float* amax_a;   // NVFP4 only: tensor-level abs-max of A and B (the fp32 scale is amax / (448 * 6))
+  const float* amax_b;
   const __nv_bfloat16* bias;
   __nv_bfloat16* preact;
   long long ldpre;
@@ -61,12 +64,13 @@ struct QParams {
   int tiles_m, tiles_n, group_m;
 };
 
-template <int BN, int STAGES, bool TWO>
+template <int BN, int STAGES, bool TWO, bool FP4 = false>
 struct QSmem {
   static constexpr int NATOM = BN <= 128 ? 1 : 2;         // B scale atoms per tile (BN = 192 starts at +0 or +64 rows of an atom)
+  static constexpr int KSF = FP4 ? 4 : 1;                 // scale atoms along K per stage: an atom covers 4 blocks of 32 (fp8) or 16 (fp4) elements
   static constexpr int A_BYTES = QBM * QBK;
   static constexpr int B_BYTES = (TWO ? BN / 2 : BN) * QBK;
-  static constexpr int SF_BYTES = (1 + NATOM) * SF_ATOM;
+  static constexpr int SF_BYTES = KSF * (1 + NATOM) * SF_ATOM;
   static constexpr int SF_OFF = STAGES * (A_BYTES + B_BYTES);
   static constexpr int BAR_OFF = SF_OFF + STAGES * SF_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 4;
@@ -85,11 +89,13 @@ __device__ __forceinline__ void q_tile_coords(const QParams& p, int tile, int& m
   nb = r / gsz;
 }
 
-template <int BN, int STAGES, bool TWO>
+template <int BN, int STAGES, bool TWO, bool FP4 = false>
 __global__ void __launch_bounds__(Q_THREADS, 1)
 gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB, const QParams p) {
-  using L = QSmem<BN, STAGES, TWO>;
+  using L = QSmem<BN, STAGES, TWO, FP4>;
+  static_assert(!(FP4 && TWO), "the NVFP4 variant is single-CTA");
+  constexpr int KSF = L::KSF;
   constexpr int TILE_M = TWO ? 2 * QBM : QBM;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -116,9 +122,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   // wait for the MMAs that still read the current ones.
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t ACC_STRIDE = 256;
-  constexpr uint32_t SFA_COL = BN;          // 4 columns
-  constexpr uint32_t SFB_COL = BN + 4;      // 4 columns per atom
-  static_assert(BN % 16 == 0 && BN + 4 + 4 * L::NATOM <= 256, "tile does not fit the tensor-memory plan");
+  constexpr uint32_t SFA_COL = BN;                 // 4 columns per atom, KSF atoms
+  constexpr uint32_t SFB_COL = BN + 4 * KSF;       // 4 columns per atom, KSF * NATOM atoms
+  static_assert(BN % 16 == 0 && BN + 4 * KSF * (1 + L::NATOM) <= 256, "tile does not fit the tensor-memory plan");
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmA);
@@ -172,7 +178,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           const uint32_t a_dst = smem_u32(sA + s * L::A_BYTES), b_dst = smem_u32(sB + s * L::B_BYTES);
           const uint32_t sf_dst = smem_u32(sSF + s * L::SF_BYTES);
           // scale atoms are rows of 128 32-bit words in two tensor maps (no swizzle); rows past the end read as zero
-          const int sfa_row = mblk * p.kt + kb, sfb_row = kb * (p.sfb_atoms + 1) + atom0;
+          const int sfa_row = (mblk * p.kt + kb) * KSF, sfb_row = kb * KSF * (p.sfb_atoms + 1) + atom0;
           if (TWO) {
             const uint32_t fb = map_to_cta(full_bar(s), 0);
             if (cta_rank == 0) mbar_expect_tx(full_bar(s), 2 * L::STAGE_TX);
@@ -184,8 +190,10 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             mbar_expect_tx(full_bar(s), L::STAGE_TX);
             tma_load_2d(a_dst, &tmA, kb * QBK, m0, full_bar(s));
             tma_load_2d(b_dst, &tmB, kb * QBK, n0, full_bar(s));
-            tma_load_2d(sf_dst, &tmSFA, 0, sfa_row, full_bar(s));
-            tma_load_2d(sf_dst + SF_ATOM, &tmSFB, 0, sfb_row, full_bar(s));
+            tma_load_2d(sf_dst, &tmSFA, 0, sfa_row, full_bar(s));                       // KSF atoms of A
+#pragma unroll
+            for (int q = 0; q < KSF; ++q)                                               // NATOM atoms of B per group of K blocks
+              tma_load_2d(sf_dst + (KSF + q * L::NATOM) * SF_ATOM, &tmSFB, 0, sfb_row + q * (p.sfb_atoms + 1), full_bar(s));
           }
         }
       }
@@ -198,7 +206,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ scale copies + MMA issue
-    if (lane == 0 && cta_rank == 0) {
+    // The warp walks the loop converged; one elected lane issues the tensor-core instructions.
+    if (cta_rank == 0) {
       uint32_t it = 0, tile_iter = 0;
       bool ok = true;
       for (int tile = wid; tile < num_tiles && ok; tile += wstride, ++tile_iter) {
@@ -206,38 +215,49 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         q_tile_coords(p, tile, mb, nb);
         const uint32_t sfb_shift = (uint32_t)((nb * BN) % 128) / 32;   // tile starts inside an atom: skip its first columns
         const uint32_t buf = tile_iter & 1, bph = (tile_iter >> 1) & 1;
-        if (!mbar_wait(tempty_bar(buf), bph ^ 1, abort_flag, p.status)) { ok = false; break; }
+        ok = __all_sync(0xffffffffu, mbar_wait(tempty_bar(buf), bph ^ 1, abort_flag, p.status));
+        if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * ACC_STRIDE;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(full_bar(s), ph, abort_flag, p.status)) { ok = false; break; }
+          ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, abort_flag, p.status));
+          if (!ok) break;
           tc_fence_after();
           const uint32_t a_base = smem_u32(sA + s * L::A_BYTES);
           const uint32_t b_base = smem_u32(sB + s * L::B_BYTES);
           const uint32_t sf_base = smem_u32(sSF + s * L::SF_BYTES);
           // scale atoms: 32 rows of 16 bytes, no swizzle, 8-row core matrices 128 bytes apart
           const uint32_t sf_tmem = tmem_base + (it & 1u) * ACC_STRIDE;
-          if (TWO) tc_cp_32x128b_warpx4_pair(sf_tmem + SFA_COL, make_smem_desc(sf_base, 0, 128, 0));
-          else tc_cp_32x128b_warpx4(sf_tmem + SFA_COL, make_smem_desc(sf_base, 0, 128, 0));
+          if (elect_one()) {
 #pragma unroll
-          for (int j = 0; j < L::NATOM; ++j) {
-            if (TWO) tc_cp_32x128b_warpx4_pair(sf_tmem + SFB_COL + 4 * j, make_smem_desc(sf_base + (1 + j) * SF_ATOM, 0, 128, 0));
-            else tc_cp_32x128b_warpx4(sf_tmem + SFB_COL + 4 * j, make_smem_desc(sf_base + (1 + j) * SF_ATOM, 0, 128, 0));
+          for (int q = 0; q < KSF; ++q) {
+            if (TWO) tc_cp_32x128b_warpx4_pair(sf_tmem + SFA_COL + 4 * q, make_smem_desc(sf_base + q * SF_ATOM, 0, 128, 0));
+            else tc_cp_32x128b_warpx4(sf_tmem + SFA_COL + 4 * q, make_smem_desc(sf_base + q * SF_ATOM, 0, 128, 0));
+          }
+#pragma unroll
+          for (int j = 0; j < KSF * L::NATOM; ++j) {
+            if (TWO) tc_cp_32x128b_warpx4_pair(sf_tmem + SFB_COL + 4 * j, make_smem_desc(sf_base + (KSF + j) * SF_ATOM, 0, 128, 0));
+            else tc_cp_32x128b_warpx4(sf_tmem + SFB_COL + 4 * j, make_smem_desc(sf_base + (KSF + j) * SF_ATOM, 0, 128, 0));
           }
 #pragma unroll
           for (int k = 0; k < QBK / QUMMA_K; ++k) {
             const uint64_t da = make_smem_desc(a_base + k * 32, 16, 1024, 2);
             const uint64_t db = make_smem_desc(b_base + k * 32, 16, 1024, 2);
-            if (TWO) tc_mma_mxf8_pair(tmem_d, da, db, make_idesc_mxf8(TILE_M, BN, k, k), (kb | k) != 0 ? 1u : 0u, sf_tmem + SFA_COL,
+            if (FP4)   // all four scale bytes of a column belong to this instruction's 64 K-elements
+              tc_mma_nvf4(tmem_d, da, db, make_idesc_nvf4(TILE_M, BN), (kb | k) != 0 ? 1u : 0u, sf_tmem + SFA_COL + 4 * k,
+                          sf_tmem + SFB_COL + 4 * L::NATOM * k + sfb_shift);
+            else if (TWO) tc_mma_mxf8_pair(tmem_d, da, db, make_idesc_mxf8(TILE_M, BN, k, k), (kb | k) != 0 ? 1u : 0u, sf_tmem + SFA_COL,
                                       sf_tmem + SFB_COL + sfb_shift);
             else tc_mma_mxf8(tmem_d, da, db, make_idesc_mxf8(TILE_M, BN, k, k), (kb | k) != 0 ? 1u : 0u, sf_tmem + SFA_COL,
                              sf_tmem + SFB_COL + sfb_shift);
           }
           if (TWO) tc_commit_pair(empty_bar(s)); else tc_commit(empty_bar(s));
+          }
+          __syncwarp();
         }
-        if (ok) {
+        if (ok && elect_one()) {
           if (TWO) tc_commit_pair(tfull_bar(buf)); else tc_commit(tfull_bar(buf));
         }
       }
@@ -247,6 +267,11 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int q = warp & 3;
     uint32_t tile_iter = 0;
     const unsigned fl = p.flags;
+    float alpha = 1.f;
+    if (FP4) {   // product of the two tensor-level scales
+      const float aa = *p.amax_a, ab = *p.amax_b;
+      alpha = (aa > 0.f ? aa / (448.f * 6.f) : 1.f) * (ab > 0.f ? ab / (448.f * 6.f) : 1.f);
+    }
     for (int tile = wid; tile < num_tiles; tile += wstride, ++tile_iter) {
       int mb, nb;
       q_tile_coords(p, tile, mb, nb);
@@ -272,7 +297,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (col0 >= p.N) continue;   // uniform across the warp
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        for (int j = 0; j < 32; ++j) v[j] = FP4 ? __uint_as_float(r[j]) * alpha : __uint_as_float(r[j]);
         if (fl & ELFA_EPI_BIAS) {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
@@ -314,12 +339,12 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
 }
 
-template <int BN, int STAGES, bool TWO>
+template <int BN, int STAGES, bool TWO, bool FP4 = false>
 int launch_q(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmSFA, const CUtensorMap& tmSFB, QParams p,
              cudaStream_t stream) {
-  using L = QSmem<BN, STAGES, TWO>;
+  using L = QSmem<BN, STAGES, TWO, FP4>;
   constexpr int TILE_M = TWO ? 2 * QBM : QBM;
-  auto kern = gemm_mxfp8_kernel<BN, STAGES, TWO>;
+  auto kern = gemm_mxfp8_kernel<BN, STAGES, TWO, FP4>;
   static bool configured = false;
   if (!configured) {
     ELFA_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
@@ -328,7 +353,7 @@ int launch_q(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& 
   p.tiles_m = (p.M + TILE_M - 1) / TILE_M;
   p.tiles_n = (p.N + BN - 1) / BN;
   // rows of A that stay in L2 while the tile order sweeps over N: about 32 MB worth
-  const long long rows = std::max(512LL, std::min(4096LL, (32LL << 20) / (long long)p.K));
+  const long long rows = std::max(512LL, std::min(4096LL, (32LL << 20) / (long long)(FP4 ? p.K / 2 : p.K)));
   p.group_m = (int)std::max(1LL, rows / TILE_M);
   const int tiles = p.tiles_m * p.tiles_n;
   const int slots = TWO ? device_sm_count() / 2 : device_sm_count();
@@ -536,4 +561,132 @@ ELFA_API int elfa_gemm_mxfp8(const void* A, const void* sfa, const void* B, cons
   if (pair) return launch_q<192, 7, true>(tmA, tmB, tmSFA, tmSFB, p, s);
   if (BN == 192) return launch_q<192, 5, false>(tmA, tmB, tmSFA, tmSFB, p, s);
   return launch_q<128, 6, false>(tmA, tmB, tmSFA, tmSFB, p, s);
+}
+
+// ---- NVFP4 ------------------------------------------------------------------------------------------
+namespace elfa {
+namespace {
+
+// One thread per 16-element block: e2m1 payload (two values per byte, even element in the low nibble),
+// ue4m3 block scale into the atom layout (an atom covers 128 rows x 64 K-elements), optional bf16 copy
+// of the dequantised values. tensor scale = amax_tensor / (448 * 6), as in the fake-quant kernel.
+__global__ void __launch_bounds__(256) nvfp4_quantize_gemm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                                                                  uint8_t* __restrict__ payload, uint8_t* __restrict__ sf,
+                                                                  __nv_bfloat16* __restrict__ deq, int rows, int cols, int k64_stride,
+                                                                  int b_atoms, const float* __restrict__ tensor_amax) {
+  const float ta = *tensor_amax;
+  const float ts = ta > 0.f ? ta / (448.f * 6.f) : 1.f;
+  const int bpr = cols / 16;
+  const long long nblocks = (long long)rows * bpr;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long blk = (long long)blockIdx.x * blockDim.x + threadIdx.x; blk < nblocks; blk += stride) {
+    const int r = (int)(blk / bpr), kb = (int)(blk - (long long)r * bpr);
+    const uint4* src = reinterpret_cast<const uint4*>(x + (long long)r * ldx + kb * 16);
+    float f[16];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const uint4 v = src[i];
+      const uint32_t pv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        f[i * 8 + 2 * j] = bf16_lo(pv[j]);
+        f[i * 8 + 2 * j + 1] = bf16_hi(pv[j]);
+        amax = fmaxf(amax, fmaxf(fabsf(f[i * 8 + 2 * j]), fabsf(f[i * 8 + 2 * j + 1])));
+      }
+    }
+    const __nv_fp8_storage_t sbq = __nv_cvt_float_to_fp8(amax / (6.f * ts), __NV_SATFINITE, __NV_E4M3);
+    const float sb = __half2float(__half(__nv_cvt_fp8_to_halfraw(sbq, __NV_E4M3)));
+    const float full = sb * ts;
+    const float inv = full > 0.f ? 1.f / full : 0.f;
+    uint32_t w[2] = {0u, 0u};
+    float dq[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const __nv_fp4_storage_t q = __nv_cvt_float_to_fp4(f[i] * inv, __NV_E2M1, cudaRoundNearest);
+      w[i >> 3] |= (uint32_t)(q & 0xf) << (4 * (i & 7));
+      dq[i] = __half2float(__half(__nv_cvt_fp4_to_halfraw(q, __NV_E2M1))) * full;
+    }
+    *reinterpret_cast<uint2*>(payload + (long long)r * (cols / 2) + kb * 8) = make_uint2(w[0], w[1]);
+    const long long atom = b_atoms > 0 ? (long long)(kb >> 2) * b_atoms + (r >> 7) : (long long)(r >> 7) * k64_stride + (kb >> 2);
+    sf[atom * SF_ATOM + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (kb & 3)] = (uint8_t)sbq;
+    if (deq != nullptr) {
+      uint4* dd = reinterpret_cast<uint4*>(deq + (long long)r * cols + kb * 16);
+      dd[0] = make_uint4(pack_bf16(dq[0], dq[1]), pack_bf16(dq[2], dq[3]), pack_bf16(dq[4], dq[5]), pack_bf16(dq[6], dq[7]));
+      dd[1] = make_uint4(pack_bf16(dq[8], dq[9]), pack_bf16(dq[10], dq[11]), pack_bf16(dq[12], dq[13]), pack_bf16(dq[14], dq[15]));
+    }
+  }
+}
+
+}  // namespace
+}  // namespace elfa
+
+// Bytes of the scale tensor of a [rows, cols] NVFP4 operand: atoms of 128 rows x 64 K-elements, the K extent
+// padded to a multiple of 256 (one pipeline stage), one extra row block of padding for a B operand.
+ELFA_API long long elfa_nvfp4_sf_bytes(int rows, int cols, int b_operand) {
+  return (long long)((rows + 127) / 128 + (b_operand ? 1 : 0)) * ((cols + 255) / 256 * 4) * SF_ATOM;
+}
+
+// x [rows, cols] bf16 -> payload [rows, cols / 2] (two e2m1 per byte), ue4m3 scale atoms, optional dequantised
+// bf16 copy. tensor_amax: device pointer to max |x| (see elfa_amax). `sf` must be zero-filled by the caller.
+ELFA_API int elfa_nvfp4_quantize_gemm(const void* x, long long ldx, void* payload, void* sf, void* deq, int rows, int cols,
+                                      int b_operand, const float* tensor_amax, void* stream) {
+  ELFA_REQUIRE(x && payload && sf && tensor_amax && rows > 0 && cols > 0, "nvfp4_quantize_gemm: bad arguments");
+  ELFA_REQUIRE(cols % 32 == 0 && ldx % 8 == 0, "nvfp4_quantize_gemm: cols must be a multiple of 32 and the pitch of 8");
+  const long long nb = (long long)rows * (cols / 16);
+  const int grid = (int)((nb + 255) / 256 < 148 * 16 ? (nb + 255) / 256 : 148 * 16);
+  nvfp4_quantize_gemm_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<uint8_t*>(payload), static_cast<uint8_t*>(sf),
+      static_cast<__nv_bfloat16*>(deq), rows, cols, (cols + 255) / 256 * 4, b_operand ? (rows + 127) / 128 + 1 : 0, tensor_amax);
+  ELFA_CUDA(cudaGetLastError());
+  count_launches(1);
+  return ELFA_OK;
+}
+
+// C[M,N] bf16 = epilogue(s_a * s_b * A[M,K] * B[N,K]^T): e2m1 payloads, ue4m3 scales per 16 K-elements, fp32 tensor
+// scales s = amax / (448 * 6) read from device memory. flags: ELFA_EPI_BIAS | ELFA_EPI_GELU | ELFA_EPI_STORE_PREACT.
+ELFA_API int elfa_gemm_nvfp4(const void* A, const void* sfa, const float* amax_a, const void* B, const void* sfb, const float* amax_b,
+                             void* C, int M, int N, int K, long long ldc, const void* bias, void* preact, long long ldpre,
+                             unsigned flags, int force_bn, void* stream) {
+  ELFA_REQUIRE(A && B && C && sfa && sfb && amax_a && amax_b, "gemm_nvfp4: null operand");
+  ELFA_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_nvfp4: empty problem");
+  ELFA_REQUIRE(K % 32 == 0 && N % 8 == 0 && ldc % 8 == 0, "gemm_nvfp4: K must be a multiple of 32, N and ldc of 8");
+  ELFA_REQUIRE(!(flags & ~(ELFA_EPI_BIAS | ELFA_EPI_GELU | ELFA_EPI_STORE_PREACT)), "gemm_nvfp4: unsupported epilogue flag");
+  ELFA_REQUIRE(!(flags & ELFA_EPI_BIAS) || bias, "gemm_nvfp4: bias flag without pointer");
+  ELFA_REQUIRE(!(flags & ELFA_EPI_STORE_PREACT) || (preact && ldpre % 8 == 0), "gemm_nvfp4: preact flag without pointer");
+  ELFA_REQUIRE((reinterpret_cast<uintptr_t>(sfa) & 15) == 0 && (reinterpret_cast<uintptr_t>(sfb) & 15) == 0,
+               "gemm_nvfp4: scale tensors must be 16-byte aligned");
+  unsigned int* st = status_word();
+  ELFA_REQUIRE(st != nullptr, "gemm_nvfp4: no status word");
+  const int BN = force_bn == 128 ? 128 : (N <= 128 ? 128 : 192);
+  const uint64_t kbytes = (uint64_t)K / 2;
+  CUtensorMap tmA, tmB, tmSFA, tmSFB;
+  int rc = shared_tmap(&tmA, A, 1, (uint64_t)M, kbytes, kbytes, QBM, QBK);
+  if (rc != ELFA_OK) return rc;
+  rc = shared_tmap(&tmB, B, 1, (uint64_t)N, kbytes, kbytes, (uint32_t)BN, QBK);
+  if (rc != ELFA_OK) return rc;
+  const int kt = (int)((kbytes + QBK - 1) / QBK);          // pipeline stages along K (256 elements each)
+  const int natom_b = BN <= 128 ? 1 : 2;
+  rc = sf_tmap(&tmSFA, sfa, (uint64_t)((M + 127) / 128) * kt * 4, 4);
+  if (rc != ELFA_OK) return rc;
+  rc = sf_tmap(&tmSFB, sfb, (uint64_t)((N + 127) / 128 + 1) * kt * 4, (uint32_t)natom_b);
+  if (rc != ELFA_OK) return rc;
+  QParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.C = static_cast<__nv_bfloat16*>(C);
+  p.ldc = ldc;
+  p.sfa = static_cast<const uint8_t*>(sfa);
+  p.sfb = static_cast<const uint8_t*>(sfb);
+  p.kt = kt;
+  p.sfb_atoms = (N + 127) / 128;
+  p.amax_a = amax_a;
+  p.amax_b = amax_b;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.preact = static_cast<__nv_bfloat16*>(preact);
+  p.ldpre = ldpre;
+  p.flags = flags;
+  p.status = st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (BN == 192) return launch_q<192, 4, false, true>(tmA, tmB, tmSFA, tmSFB, p, s);
+  return launch_q<128, 5, false, true>(tmA, tmB, tmSFA, tmSFB, p, s);
 }

@@ -168,8 +168,48 @@ def shortconv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor
 
 
 # ------------------------------------------------------------------------------------------- PRISM
+class _PrismRefine(torch.autograd.Function):
+    """CUDA path: one kernel forward, one backward (recomputes the residuals; the gradient of the
+    gates is summed over the groups inside the thread that owns the channel: no atomics)."""
+
+    @staticmethod
+    def forward(ctx, u, v, group_dim, *ps):
+        import ctypes
+        B, T, D = u.shape
+        uc, vc = u.contiguous(), v.contiguous()
+        pcs = [p.contiguous() for p in ps]
+        y = torch.empty_like(uc)
+        arr = (ctypes.c_uint64 * len(pcs))(*[p.data_ptr() for p in pcs])
+        lib.call("elfa_prism_fwd", uc, vc, ctypes.addressof(arr), y, B * T, D // group_dim, group_dim, len(pcs), stream_ptr(uc))
+        ctx.save_for_backward(uc, vc, *pcs)
+        ctx.group_dim = group_dim
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        import ctypes
+        uc, vc, *pcs = ctx.saved_tensors
+        B, T, D = uc.shape
+        d = ctx.group_dim
+        dyc = dy.contiguous()
+        du, dv = torch.empty_like(uc), torch.empty_like(vc)
+        dps = [torch.empty((B, T, d), dtype=torch.float32, device=uc.device) for _ in pcs]
+        parr = (ctypes.c_uint64 * len(pcs))(*[p.data_ptr() for p in pcs])
+        darr = (ctypes.c_uint64 * len(pcs))(*[p.data_ptr() for p in dps])
+        lib.call("elfa_prism_bwd", uc, vc, ctypes.addressof(parr), dyc, du, dv, ctypes.addressof(darr), B * T, D // d, d, len(pcs),
+                 stream_ptr(uc))
+        return (du, dv, None) + tuple(g.to(p.dtype) for g, p in zip(dps, pcs))
+
+
 def prism_refine(u: torch.Tensor, v: torch.Tensor, p_list, group_dim: int) -> torch.Tensor:
     """``u``, ``v`` ``[B, T, D]``; ``p_list[l]`` ``[B, T, d]`` (already sigmoid-ed). Returns ``u + refined``."""
+    if u.is_cuda and u.dtype == torch.bfloat16 and 1 <= len(p_list) <= 8 and all(p.dtype == torch.bfloat16 for p in p_list):
+        return _PrismRefine.apply(u, v, group_dim, *p_list)
+    return prism_refine_ref(u, v, p_list, group_dim)
+
+
+def prism_refine_ref(u: torch.Tensor, v: torch.Tensor, p_list, group_dim: int) -> torch.Tensor:
+    """Plain PyTorch form (CPU path and test oracle)."""
     B, T, D = u.shape
     G = D // group_dim
     r = (v.float() - u.float()).view(B, T, G, group_dim)

@@ -68,6 +68,7 @@ def main(argv=None) -> int:
     ap.add_argument("--vocab", type=int, default=32000)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--compare", action="store_true", help="also time the PyTorch / library op")
+    ap.add_argument("--bn", type=int, default=0, help="gemm: force the tile width (64 / 128 / 256, 512 = CTA pairs; 0 = automatic)")
     a = ap.parse_args(argv)
     from .. import native, ops
     from ..native import lib, stream_ptr
@@ -84,7 +85,7 @@ def main(argv=None) -> int:
         else:                     # x[K,M]^T @ dy[K,N]
             A, B, kw = torch.randn(K, M, device=dev).to(bf), torch.randn(K, N, device=dev).to(bf), dict(a_mn=True, b_mn=True)
         out = torch.empty(M, N, dtype=bf, device=dev)
-        ms = timed(lambda: ops.gemm(A, B, out=out, **kw), a.iters)
+        ms = timed(lambda: ops.gemm(A, B, out=out, force_bn=a.bn, **kw), a.iters)
         fl = 2.0 * M * N * K
         line = f"gemm {a.layout} {M}x{N}x{K}: {ms:.4f} ms  {fl / ms / 1e9:.1f} TFLOP/s  {fl / ms / 1e-3 / flops_peak:.3f} of {src} cuBLAS bf16 peak"
         if a.compare:
@@ -99,7 +100,7 @@ def main(argv=None) -> int:
         xq, _ = q8.quantize_mxfp8(torch.randn(M, K, device=dev).to(bf))
         wq, _ = q8.quantize_mxfp8(torch.randn(N, K, device=dev).to(bf), right=True)
         out = torch.empty(M, N, dtype=bf, device=dev)
-        ms = timed(lambda: q8.gemm_mxfp8(xq, wq, out=out), a.iters)
+        ms = timed(lambda: q8.gemm_mxfp8(xq, wq, out=out, force_bn=a.bn), a.iters)
         fl = 2.0 * M * N * K
         print(f"gemm_mxfp8 {M}x{N}x{K}: {ms:.4f} ms  {fl / ms / 1e9:.1f} TFLOP/s  {fl / ms / 1e-3 / flops_peak:.3f} of {src} cuBLAS bf16 peak "
               f"(block-scaled e4m3, nominal fp8 peak is 2x bf16)")

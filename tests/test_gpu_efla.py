@@ -95,3 +95,23 @@ def test_efla_model_trains_on_gpu(cuda_device):
     assert native.status() == 0
     for a, b in zip(losses["gpu"], losses["cpu"]):
         assert abs(a - b) < 0.08 * abs(b), losses
+
+
+def test_prism_refine_kernel_matches_reference(cuda_device):
+    from elfa_b200.ops import efla as eops
+    torch.manual_seed(0)
+    B, T, G, d, L = 2, 64, 8, 64, 3
+    u = (torch.randn(B, T, G * d, device=cuda_device) * 0.5).bfloat16().requires_grad_(True)
+    v = (torch.randn(B, T, G * d, device=cuda_device) * 0.5).bfloat16().requires_grad_(True)
+    ps = [torch.sigmoid(torch.randn(B, T, d, device=cuda_device)).bfloat16().requires_grad_(True) for _ in range(L)]
+    go = torch.randn(B, T, G * d, device=cuda_device).bfloat16()
+    y = eops.prism_refine(u, v, ps, d)
+    y.backward(go)
+    got = [y.detach().float(), u.grad.float(), v.grad.float()] + [p.grad.float() for p in ps]
+    u2, v2 = u.detach().float().requires_grad_(True), v.detach().float().requires_grad_(True)
+    ps2 = [p.detach().float().requires_grad_(True) for p in ps]
+    y2 = eops.prism_refine_ref(u2, v2, ps2, d)
+    y2.backward(go.float())
+    want = [y2.detach(), u2.grad, v2.grad] + [p.grad for p in ps2]
+    for a, b in zip(got, want):
+        assert (a - b).abs().max() <= 0.02 * b.abs().max() + 0.02, ((a - b).abs().max(), b.abs().max())
