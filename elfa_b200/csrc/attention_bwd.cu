@@ -20,6 +20,8 @@
 //
 // Roles per CTA (320 threads): warp 0 TMA, warp 1 MMA issue, warps 2-9 compute (warps w and w+4
 // share a tensor-memory lane quarter and split the 128 columns in halves).
+#include <type_traits>
+
 #include "common.cuh"
 #include "elfa_native.h"
 
@@ -229,9 +231,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
     if (!DKV) {
       const int row = outer * 128 + row_local;
       row_ok = row < p.S;
-      if (row_ok) {
-        lse2 = p.lse[((long long)b * p.H + h) * p.S + row] * LOG2E;
-        dlt = p.delta[((long long)b * p.H + h) * p.S + row];
+      if (row_ok) {   // negated / pre-scaled like the shared-memory vectors of the other mode
+        lse2 = -p.lse[((long long)b * p.H + h) * p.S + row] * LOG2E;
+        dlt = -p.delta[((long long)b * p.H + h) * p.S + row] * p.scale;
       }
     }
     for (int it = 0; it < n_iter; ++it) {
@@ -242,8 +244,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
         const int qi = ct & 127;
         const int qrow = q_tile * 128 + qi;
         const long long idx = ((long long)b * p.H + h) * p.S + qrow;
-        if (ct < 128) vl[qi] = qrow < p.S ? p.lse[idx] * LOG2E : INFINITY;   // +inf -> exp2(-inf) = 0 for rows past the end
-        else vl[128 + qi] = qrow < p.S ? p.delta[idx] : 0.f;
+        // stored negated (and delta pre-multiplied by the softmax scale) so that both uses are one fused multiply-add
+        if (ct < 128) vl[qi] = qrow < p.S ? -p.lse[idx] * LOG2E : -INFINITY;   // -inf -> exp2(-inf) = 0 for rows past the end
+        else vl[128 + qi] = qrow < p.S ? -p.delta[idx] * p.scale : 0.f;
         named_bar_sync(1, 256);
       }
       // After a timeout the loop keeps running without touching tensor memory so that every warp
@@ -254,24 +257,51 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
       const bool diag = p.causal && q_tile == k_tile;
       float ev[64];                      // this thread's 64 probabilities (fp32, kept for dS)
       uint32_t keep[32];                 // ... and as bf16 pairs (P, then dS)
-      // ---- phase 1: P = exp2(S * scale - lse)
+      // ---- phase 1: P = exp2(S * scale - lse). `diag` (and a ragged last tile) is uniform over the CTA: only
+      // those tiles pay for the per-element mask test. The per-query vectors come from shared memory four at a time.
+      const float sc2 = p.scale_log2;
+      const uint64_t sc2x2 = pack_f32x2(sc2, sc2), scx2 = pack_f32x2(p.scale, p.scale);
+      auto phase1 = [&](auto masked_tag) {
+        constexpr bool MASK = decltype(masked_tag)::value;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        if (!ok) break;
-        const int col0 = half * 64 + c * 32;
-        uint32_t rs[32];
-        tmem_ld32(TM_S + lane_addr + col0, rs);
-        tmem_ld_wait();
+        for (int c = 0; c < 2; ++c) {
+          const int col0 = half * 64 + c * 32;
+          uint32_t rs[32];
+          tmem_ld32(TM_S + lane_addr + col0, rs);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int col = col0 + i;
-          const float l2 = DKV ? vl[col] : lse2;
-          float e = fast_exp2(fmaf(__uint_as_float(rs[i]), p.scale_log2, -l2));
-          // DKV: lane = key, column = query -> masked when key > query; DQ: lane = query, column = key
-          const bool masked = DKV ? (diag && row_local > col) : (!row_ok || (diag && col > row_local));
-          if (masked) e = 0.f;
-          ev[c * 32 + i] = e;
+          for (int i = 0; i < 32; i += 4) {
+            float l4[4] = {lse2, lse2, lse2, lse2};
+            if (DKV) {
+              const float4 t4 = *reinterpret_cast<const float4*>(vl + col0 + i);
+              l4[0] = t4.x; l4[1] = t4.y; l4[2] = t4.z; l4[3] = t4.w;
+            }
+            if (MASK) {
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const int col = col0 + i + u;
+                float e = fast_exp2(fmaf(__uint_as_float(rs[i + u]), sc2, l4[u]));
+                // DKV: lane = key, column = query -> masked when key > query; DQ: lane = query, column = key
+                const bool masked = DKV ? (diag && row_local > col) : (!row_ok || (diag && col > row_local));
+                if (masked) e = 0.f;
+                ev[c * 32 + i + u] = e;
+              }
+            } else {
+#pragma unroll
+              for (int u = 0; u < 4; u += 2) {   // packed pairs: one FFMA instruction per two elements
+                float x0, x1;
+                unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(rs[i + u]), __uint_as_float(rs[i + u + 1])), sc2x2,
+                                       pack_f32x2(l4[u], l4[u + 1])), x0, x1);
+                ev[c * 32 + i + u] = fast_exp2(x0);
+                ev[c * 32 + i + u + 1] = fast_exp2(x1);
+              }
+            }
+          }
         }
+      };
+      if (ok) {
+        const bool any_mask = diag || (!DKV && (outer + 1) * 128 > p.S);
+        if (any_mask) phase1(std::true_type{}); else phase1(std::false_type{});
       }
       if (DKV) {
         // The bf16 results go back into tensor memory on top of fp32 columns: a row's 128 values take
@@ -305,11 +335,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
         tmem_ld32(TM_DP + lane_addr + col0, rd);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float dl0 = DKV ? vl[128 + col0 + i] : dlt, dl1 = DKV ? vl[128 + col0 + i + 1] : dlt;
-          const float d0 = ev[c * 32 + i] * (__uint_as_float(rd[i]) - dl0) * p.scale;
-          const float d1 = ev[c * 32 + i + 1] * (__uint_as_float(rd[i + 1]) - dl1) * p.scale;
-          keep[c * 16 + (i >> 1)] = pack_bf16(d0, d1);
+        for (int i = 0; i < 32; i += 4) {
+          float d4[4] = {dlt, dlt, dlt, dlt};
+          if (DKV) {
+            const float4 t4 = *reinterpret_cast<const float4*>(vl + 128 + col0 + i);
+            d4[0] = t4.x; d4[1] = t4.y; d4[2] = t4.z; d4[3] = t4.w;
+          }
+          // dS = P * (dP * scale - delta * scale): one packed FFMA and one packed FMUL per two elements
+          float x0, x1, x2, x3;
+          const uint64_t t01 = fma_f32x2(pack_f32x2(__uint_as_float(rd[i]), __uint_as_float(rd[i + 1])), scx2, pack_f32x2(d4[0], d4[1]));
+          const uint64_t t23 = fma_f32x2(pack_f32x2(__uint_as_float(rd[i + 2]), __uint_as_float(rd[i + 3])), scx2, pack_f32x2(d4[2], d4[3]));
+          unpack_f32x2(fma_f32x2(pack_f32x2(ev[c * 32 + i], ev[c * 32 + i + 1]), t01, 0ull), x0, x1);
+          unpack_f32x2(fma_f32x2(pack_f32x2(ev[c * 32 + i + 2], ev[c * 32 + i + 3]), t23, 0ull), x2, x3);
+          keep[c * 16 + (i >> 1)] = pack_bf16(x0, x1);
+          keep[c * 16 + (i >> 1) + 1] = pack_bf16(x2, x3);
         }
       }
       tc_fence_before();

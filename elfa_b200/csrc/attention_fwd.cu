@@ -19,6 +19,8 @@
 // tensor memory (tcgen05.ld / multiply / tcgen05.st), which is rare after the first blocks. Each
 // S row is read from tensor memory once.
 // Every wait is bounded (status word + abort flag), as in the GEMM.
+#include <type_traits>
+
 #include "common.cuh"
 #include "elfa_native.h"
 
@@ -210,18 +212,29 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       tmem_ld32(TM_S[t] + lane_addr, cb[0]);
       // four independent chains for the maximum (scale > 0, so scaling commutes with it)
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      // `need_mask` is the same for the whole warp: only diagonal / tail tiles pay for the per-element test
+      auto row_max = [&](auto masked) {
+        constexpr bool MASK = decltype(masked)::value;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld_wait();
-        if (c + 1 < 4) tmem_ld32(TM_S[t] + lane_addr + (c + 1) * 32, cb[(c + 1) & 1]);
-        else tmem_ld32(TM_S[t] + lane_addr, cb[(c + 1) & 1]);          // first chunk of the second pass
+        for (int c = 0; c < 4; ++c) {
+          tmem_ld_wait();
+          if (c + 1 < 4) tmem_ld32(TM_S[t] + lane_addr + (c + 1) * 32, cb[(c + 1) & 1]);
+          else tmem_ld32(TM_S[t] + lane_addr, cb[(c + 1) & 1]);          // first chunk of the second pass
+          if (MASK) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float sv = __uint_as_float(cb[c & 1][i]);
-          if (need_mask && key0 + c * 32 + i > limit) sv = -INFINITY;
-          mx4[i & 3] = fmaxf(mx4[i & 3], sv);
+            for (int i = 0; i < 32; ++i) {
+              float sv = __uint_as_float(cb[c & 1][i]);
+              if (key0 + c * 32 + i > limit) sv = -INFINITY;
+              mx4[i & 3] = fmaxf(mx4[i & 3], sv);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2)   // 3-input maximum: half an instruction per element
+              mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(cb[c & 1][i]), __uint_as_float(cb[c & 1][i + 1]));
+          }
         }
-      }
+      };
+      if (need_mask) row_max(std::true_type{}); else row_max(std::false_type{});
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
       if (j == 0) {
         m = mx;
@@ -252,31 +265,56 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       }
       float ls4[4] = {0.f, 0.f, 0.f, 0.f};
       const float neg_m = (m == -INFINITY) ? 0.f : -m;   // a fully masked row so far: exp2(-inf) = 0 without inf - inf
+      const float sc2 = p.scale_log2;
+      const uint64_t sc2x2 = pack_f32x2(sc2, sc2), negm_x2 = pack_f32x2(neg_m, neg_m);
+      uint64_t lsp[2] = {0ull, 0ull};      // two packed pairs of partial sums (unmasked path)
+      auto row_exp = [&](auto masked) {
+        constexpr bool MASK = decltype(masked)::value;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld_wait();
-        if (c + 1 < 4) tmem_ld32(TM_S[t] + lane_addr + (c + 1) * 32, cb[(c + 1) & 1]);
-        uint32_t (&r)[32] = cb[c & 1];
+        for (int c = 0; c < 4; ++c) {
+          tmem_ld_wait();
+          if (c + 1 < 4) tmem_ld32(TM_S[t] + lane_addr + (c + 1) * 32, cb[(c + 1) & 1]);
+          uint32_t (&r)[32] = cb[c & 1];
+          if (MASK) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float sv = __uint_as_float(r[i]);
-          if (need_mask && key0 + c * 32 + i > limit) sv = -INFINITY;
-          const float e = fast_exp2(fmaf(sv, p.scale_log2, neg_m));
-          ls4[i & 3] += e;
-          r[i] = __float_as_uint(e);
+            for (int i = 0; i < 32; ++i) {
+              float sv = __uint_as_float(r[i]);
+              if (key0 + c * 32 + i > limit) sv = -INFINITY;
+              const float e = fast_exp2(fmaf(sv, sc2, neg_m));
+              ls4[i & 3] += e;
+              r[i] = __float_as_uint(e);
+            }
+          } else {
+            // packed fp32 pairs: one FFMA and one FADD instruction per two elements
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              float x0, x1;
+              unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), sc2x2, negm_x2), x0, x1);
+              const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+              lsp[(i >> 1) & 1] = add_f32x2(lsp[(i >> 1) & 1], pack_f32x2(e0, e1));
+              r[i] = __float_as_uint(e0);
+              r[i + 1] = __float_as_uint(e1);
+            }
+          }
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int q8 = c * 4 + g;  // 16-byte chunk index along the 128 keys
+            const uint32_t addr = p_row + (q8 >> 3) * SUB_BYTES + (((q8 & 7) ^ (row_local & 7)) << 4);
+            const uint32_t w0 = pack_bf16(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
+            const uint32_t w1 = pack_bf16(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
+            const uint32_t w2 = pack_bf16(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
+            const uint32_t w3 = pack_bf16(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+          }
         }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int q8 = c * 4 + g;  // 16-byte chunk index along the 128 keys
-          const uint32_t addr = p_row + (q8 >> 3) * SUB_BYTES + (((q8 & 7) ^ (row_local & 7)) << 4);
-          const uint32_t w0 = pack_bf16(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
-          const uint32_t w1 = pack_bf16(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
-          const uint32_t w2 = pack_bf16(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
-          const uint32_t w3 = pack_bf16(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
-        }
+      };
+      if (need_mask) row_exp(std::true_type{}); else row_exp(std::false_type{});
+      {
+        float a0, a1, a2, a3;
+        unpack_f32x2(lsp[0], a0, a1);
+        unpack_f32x2(lsp[1], a2, a3);
+        l += ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3])) + ((a0 + a1) + (a2 + a3));
       }
-      l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(bar(BAR_PREADY0 + t));
