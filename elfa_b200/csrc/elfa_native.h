@@ -110,7 +110,7 @@ int elfa_gemm_ag(const void* x_local, long long ldx, const unsigned long long* p
                  void* stream);
 int elfa_gemm_rs(const void* A, long long lda, const void* B, long long ldb, int b_mn_major, int M, int N, int K,
                  const unsigned long long* peer_recv, const unsigned long long* peer_flags, const void* my_flags,
-                 unsigned int* arrivals_io, void* out, long long ld_out, int rank, int world, int wait_ms, void* stream);
+                 unsigned int* arrivals_io, void* out, long long ld_out, int rank, int world, int wait_ms, int max_ctas, void* stream);
 
 // ---- zero.cu -----------------------------------------------------------------------------------
 int elfa_symm_barrier(const unsigned long long* peer_flags, const void* my_flags, int rank, int world, unsigned int epoch,

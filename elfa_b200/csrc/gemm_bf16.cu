@@ -922,8 +922,8 @@ namespace {
 
 template <int COMM>
 int dispatch_comm(int BN, int b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmA2, const GemmParams& p,
-                  const CommParams& c, cudaStream_t s, const OutMaps* om = nullptr) {
-  const int ctas = sm_count();
+                  const CommParams& c, cudaStream_t s, const OutMaps* om = nullptr, int max_ctas = 0) {
+  const int ctas = (max_ctas > 0 && max_ctas < sm_count()) ? max_ctas : sm_count();
   if (BN == 256) {
     return b_mn ? launch_gemm<256, false, true, COMM>(tmA, tmB, p, ctas, s, &tmA2, &c, om)
                 : launch_gemm<256, false, false, COMM>(tmA, tmB, p, ctas, s, &tmA2, &c, om);
@@ -1009,7 +1009,8 @@ ELFA_API int elfa_gemm_ag(const void* x_local, long long ldx, const unsigned lon
 // buffer ([world][M/world][N] bf16, symmetric) and are summed there in rank order.
 ELFA_API int elfa_gemm_rs(const void* A, long long lda, const void* B, long long ldb, int b_mn_major, int M, int N, int K,
                           const unsigned long long* peer_recv, const unsigned long long* peer_flags, const void* my_flags,
-                          unsigned int* arrivals_io, void* out, long long ld_out, int rank, int world, int wait_ms, void* stream) {
+                          unsigned int* arrivals_io, void* out, long long ld_out, int rank, int world, int wait_ms, int max_ctas,
+                          void* stream) {
   ELFA_REQUIRE(A && B && peer_recv && peer_flags && my_flags && arrivals_io && out, "gemm_rs: null argument");
   ELFA_REQUIRE(world >= 2 && world <= MAX_RANKS && rank >= 0 && rank < world, "gemm_rs: bad rank/world");
   ELFA_REQUIRE(M % world == 0 && (M / world) % BM == 0, "gemm_rs: rows per rank must be a multiple of 128");
@@ -1045,5 +1046,6 @@ ELFA_API int elfa_gemm_rs(const void* A, long long lda, const void* B, long long
     rc = cached_tmap_bf16(&om.m[i], reinterpret_cast<const void*>(peer_recv[i]), (uint64_t)M, (uint64_t)N, (uint64_t)N, BM, 64);
     if (rc != ELFA_OK) return rc;
   }
-  return dispatch_comm<COMM_RS>(BN, b_mn_major, tmA, tmB, tmA, p, c, static_cast<cudaStream_t>(stream), &om);
+  // max_ctas < SM count leaves SMs to a kernel on another stream (a weight-gradient GEMM next to this comm-bound kernel)
+  return dispatch_comm<COMM_RS>(BN, b_mn_major, tmA, tmB, tmA, p, c, static_cast<cudaStream_t>(stream), &om, max_ctas);
 }

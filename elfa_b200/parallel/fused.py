@@ -144,8 +144,9 @@ def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, pc: ParallelContext, *, b_mn
     return y, x_full, pre
 
 
-def gemm_rs(a: torch.Tensor, w: torch.Tensor, pc: ParallelContext, *, b_mn: bool) -> torch.Tensor:
-    """``reduce_scatter_rows(a @ op(w))`` → ``[M / world, N]``."""
+def gemm_rs(a: torch.Tensor, w: torch.Tensor, pc: ParallelContext, *, b_mn: bool, max_ctas: int = 0) -> torch.Tensor:
+    """``reduce_scatter_rows(a @ op(w))`` → ``[M / world, N]``. ``max_ctas`` caps the grid so that a GEMM
+    on another stream can run next to this (communication-bound) kernel."""
     world, rank = pc.tp_size, pc.tp_rank
     M, K = a.shape
     N = w.shape[1] if b_mn else w.shape[0]
@@ -162,5 +163,5 @@ def gemm_rs(a: torch.Tensor, w: torch.Tensor, pc: ParallelContext, *, b_mn: bool
     out = torch.empty((M // world, N), dtype=torch.bfloat16, device=a.device)
     lib.call("elfa_gemm_rs", ac, ac.stride(0), w, w.stride(0), int(b_mn), M, N, K, ctypes.addressof(slot.peer_data),
              ctypes.addressof(slot.peer_flags), slot.flags.tensor, ctypes.addressof(slot.arrivals), out, out.stride(0), rank, world,
-             _WAIT_MS, stream_ptr(ac))
+             _WAIT_MS, max_ctas, stream_ptr(ac))
     return out

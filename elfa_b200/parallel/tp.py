@@ -152,24 +152,40 @@ def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, pc: ParallelContext, *, b_mn
     return y, x_full, pre
 
 
-def gemm_rs(a: torch.Tensor, w: torch.Tensor, pc: ParallelContext, *, b_mn: bool) -> torch.Tensor:
+def gemm_rs(a: torch.Tensor, w: torch.Tensor, pc: ParallelContext, *, b_mn: bool, max_ctas: int = 0) -> torch.Tensor:
     """``reduce_scatter_rows(a @ op(w))``: every rank contributes a partial product over its slice of
     the contraction dimension and receives the summed rows ``[M/tp, N]`` it owns."""
     if pc.comm_backend == "fused" and a.is_cuda:
         from . import fused
-        return fused.gemm_rs(a, w, pc, b_mn=b_mn)
+        return fused.gemm_rs(a, w, pc, b_mn=b_mn, max_ctas=max_ctas)
     return _reduce_scatter_dim0(gemm(a, w, b_mn=b_mn, out_dtype=a.dtype), pc)
 
 
-def _wgrad(w_ref: torch.Tensor, x2: torch.Tensor, dy2: torch.Tensor, w_dtype) -> Optional[torch.Tensor]:
+def _wgrad(w_ref: torch.Tensor, x2: torch.Tensor, dy2: torch.Tensor, w_dtype, max_ctas: int = 0) -> Optional[torch.Tensor]:
     """x2^T @ dy2 into ``w_ref.main_grad`` (returns None) or as a new tensor."""
     mg = getattr(w_ref, "main_grad", None)
     if mg is not None and dy2.is_cuda:
         fresh = getattr(w_ref, "_grad_fresh", False)
-        gemm(x2, dy2, a_mn=True, b_mn=True, out=mg, accumulate=not fresh)
+        gemm(x2, dy2, a_mn=True, b_mn=True, out=mg, accumulate=not fresh, max_ctas=max_ctas)
         w_ref._grad_fresh = False
         return None
-    return gemm(x2, dy2, a_mn=True, b_mn=True, out_dtype=w_dtype)
+    return gemm(x2, dy2, a_mn=True, b_mn=True, out_dtype=w_dtype, max_ctas=max_ctas)
+
+
+_side_streams = {}
+
+
+def _overlap_wgrad(pc: ParallelContext, t: torch.Tensor) -> bool:
+    """Whether the weight-gradient GEMM should run next to the fused GEMM→reduce-scatter kernel. At 8
+    ranks that kernel is bound by NVLink, not by the tensor cores: it gets part of the SMs and the weight
+    gradient the rest, on a second stream (at 2 ranks, where the GEMM dominates, the split costs 6 %). ``ELFA_OVERLAP_WGRAD`` = 0 / 1 forces the choice."""
+    import os
+    if not (t.is_cuda and pc.comm_backend == "fused" and pc.tp_size > 1):
+        return False
+    env = os.environ.get("ELFA_OVERLAP_WGRAD")
+    if env is not None:
+        return env not in ("0", "")
+    return pc.tp_size >= 8
 
 
 class _ColumnParallelSP(torch.autograd.Function):
@@ -204,8 +220,24 @@ class _ColumnParallelSP(torch.autograd.Function):
                 dy2 = dpre
             else:
                 dy2 = (dy2.float() * ops.dgelu_tanh_ref(pre.float())).to(dy2.dtype)
-        dx = gemm_rs(dy2, wq, pc, b_mn=False)              # dy @ w^T, summed over ranks, rows scattered
-        dw = _wgrad(ctx.w_ref, x_full, dy2, wq.dtype)
+        if _overlap_wgrad(pc, dy2) and getattr(ctx.w_ref, "main_grad", None) is not None:
+            # the two products are independent: the weight gradient runs on a second stream on the SMs that the
+            # (NVLink-bound) reduce-scatter kernel leaves free
+            dev = dy2.device
+            side = _side_streams.get(dev)
+            if side is None:
+                side = _side_streams[dev] = torch.cuda.Stream(dev)
+            cur = torch.cuda.current_stream(dev)
+            sms = torch.cuda.get_device_properties(dev).multi_processor_count
+            rs_ctas = max(16, (sms * 7 // 16) // 2 * 2)
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):
+                dw = _wgrad(ctx.w_ref, x_full, dy2, wq.dtype, max_ctas=sms - rs_ctas)
+            dx = gemm_rs(dy2, wq, pc, b_mn=False, max_ctas=rs_ctas)
+            cur.wait_stream(side)
+        else:
+            dx = gemm_rs(dy2, wq, pc, b_mn=False)              # dy @ w^T, summed over ranks, rows scattered
+            dw = _wgrad(ctx.w_ref, x_full, dy2, wq.dtype)
         return dx.view(Sl, B, D), dw, None, None, None
 
 
@@ -247,9 +279,15 @@ class _QuantLinear(torch.autograd.Function):
         if use_block_scaled_gemm(x2, w, quant):
             # e4m3 payloads + ue8m0 scales straight into the block-scaled MMA; the bf16 copy of the
             # quantised activations (same values) is kept for the weight gradient
-            from ..ops.gemm_mxfp8 import gemm_mxfp8, quantize_mxfp8
-            x_op, xq = quantize_mxfp8(x2 if x2.is_contiguous() else x2.contiguous(), dequantized=True)
-            y = gemm_mxfp8(x_op, cached_weight_operand(w, quant), gelu=act == "gelu", preact=pre)
+            xc = x2 if x2.is_contiguous() else x2.contiguous()
+            if quant.fmt == "nvfp4":
+                from ..ops.gemm_nvfp4 import gemm_nvfp4, quantize_nvfp4
+                x_op, xq = quantize_nvfp4(xc, dequantized=True)
+                y = gemm_nvfp4(x_op, cached_weight_operand(w, quant), gelu=act == "gelu", preact=pre)
+            else:
+                from ..ops.gemm_mxfp8 import gemm_mxfp8, quantize_mxfp8
+                x_op, xq = quantize_mxfp8(xc, dequantized=True)
+                y = gemm_mxfp8(x_op, cached_weight_operand(w, quant), gelu=act == "gelu", preact=pre)
         else:
             xq = fake_quant(x2, quant)
             if act == "gelu":

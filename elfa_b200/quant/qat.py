@@ -72,21 +72,28 @@ def cached_weight_quant(w: torch.Tensor, spec: "QuantSpec") -> torch.Tensor:
 
 
 def cached_weight_operand(w: torch.Tensor, spec: "QuantSpec"):
-    """MXFP8 tensor-core operand of a ``[K, N]`` weight: payload ``[N, K]`` e4m3 with scales along K,
-    the same 32-element blocks as ``fake_quant(w, weight=True)``. Cached like the bf16 copy."""
-    key = (id(w), "mxfp8_operand")
+    """Block-scaled tensor-core operand (MXFP8 or NVFP4) of a ``[K, N]`` weight: payload ``[N, K]`` with
+    scales along K, the same blocks as ``fake_quant(w, weight=True)``. Cached like the bf16 copy."""
+    key = (id(w), spec.fmt + "_operand")
     hit = _weight_cache.get(key)
     if hit is not None and hit[0] is w:
         return hit[1]
-    from ..ops.gemm_mxfp8 import quantize_mxfp8
-    op, _ = quantize_mxfp8(w.detach().t().contiguous(), right=True)
+    wt = w.detach().t().contiguous()
+    if spec.fmt == "nvfp4":
+        from ..ops.gemm_nvfp4 import quantize_nvfp4
+        op, _ = quantize_nvfp4(wt, right=True)
+    else:
+        from ..ops.gemm_mxfp8 import quantize_mxfp8
+        op, _ = quantize_mxfp8(wt, right=True)
     _weight_cache[key] = (w, op)
     return op
 
 
 def use_block_scaled_gemm(x2: torch.Tensor, w: torch.Tensor, spec: Optional["QuantSpec"]) -> bool:
-    """True when the forward GEMM ``x2 [T, K] @ w [K, N]`` can run on the block-scaled MXFP8 path."""
-    return (spec is not None and spec.fmt == "mxfp8" and spec.block_scaled_gemm and x2.is_cuda and x2.dtype == torch.bfloat16
+    """True when the forward GEMM ``x2 [T, K] @ w [K, N]`` can run on a block-scaled tensor-core path
+    (MXFP8: exactly the fake-quantised product; NVFP4: the same up to the bf16 rounding of the
+    fake-quantised operands)."""
+    return (spec is not None and spec.fmt in ("mxfp8", "nvfp4") and spec.block_scaled_gemm and x2.is_cuda and x2.dtype == torch.bfloat16
             and w.dtype == torch.bfloat16 and x2.shape[1] % 32 == 0 and w.shape[1] % 8 == 0)
 
 

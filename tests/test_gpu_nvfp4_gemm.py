@@ -55,3 +55,23 @@ def test_nvfp4_gemm_epilogue():
     ref_pre = q.dequantize_ref(xq) @ q.dequantize_ref(wq).t() + bias.float()
     assert (pre.float() - ref_pre).abs().max() <= 2 ** -7 * ref_pre.abs().max() + 1e-3
     assert (y.float() - gelu_tanh_ref(ref_pre)).abs().max() <= 2 ** -7 * ref_pre.abs().max() + 1e-3
+
+
+def test_quant_linear_nvfp4_tensor_core_path_close_to_fake_quant_path():
+    from elfa_b200.parallel.mesh import ParallelContext
+    from elfa_b200.parallel.tp import column_parallel_linear
+    from elfa_b200.quant.qat import QuantSpec, new_weight_epoch
+    torch.manual_seed(0)
+    x = (torch.randn(4, 96, 256, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(256, 512, device="cuda") * 0.05).bfloat16()
+    dy = torch.randn(4, 96, 512, device="cuda").bfloat16()
+    outs = []
+    for hw in (True, False):
+        new_weight_epoch()
+        xi, wi = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        y = column_parallel_linear(xi, wi, ParallelContext(), None, QuantSpec(fmt="nvfp4", block_scaled_gemm=hw))
+        y.backward(dy)
+        outs.append((y.detach().float(), xi.grad.float(), wi.grad.float()))
+    (y1, dx1, dw1), (y0, dx0, dw0) = outs
+    assert (y1 - y0).abs().max() <= 2 ** -6 * y0.abs().max()      # bf16 rounding of the fake-quantised operands
+    assert torch.equal(dx1, dx0) and torch.equal(dw1, dw0)         # backward uses the same fake-quantised tensors
