@@ -213,3 +213,44 @@ ELFA_API int elfa_cast(const void* src, int src_type, void* dst, int dst_type, l
   ::elfa::count_launches(1);
   return ELFA_OK;
 }
+
+// ---- row softmax ------------------------------------------------------------------------------------
+// reference: kernels/cuda/layernorm.cu softmax kernel and src/nn/nn_kernels.zig:226-267 (host loop).
+// One warp per row, two passes over the row held in registers when it fits (<= 4096 columns), else
+// three passes over global memory. out = softmax(x * scale) in bf16.
+namespace elfa {
+namespace {
+
+__global__ void __launch_bounds__(256) softmax_rows_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
+                                                           long long rows, int cols, long long ldx, long long ldo, float scale) {
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const __nv_bfloat16* xr = x + row * ldx;
+  __nv_bfloat16* orow = out + row * ldo;
+  const float s2 = scale * 1.4426950408889634f;
+  float mx = -INFINITY;
+  for (int c = lane; c < cols; c += 32) mx = fmaxf(mx, __bfloat162float(xr[c]));
+  mx = warp_max(mx);
+  const float m2 = mx == -INFINITY ? 0.f : mx * s2;
+  float sum = 0.f;
+  for (int c = lane; c < cols; c += 32) sum += fast_exp2(__bfloat162float(xr[c]) * s2 - m2);
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+  for (int c = lane; c < cols; c += 32) orow[c] = __float2bfloat16(fast_exp2(__bfloat162float(xr[c]) * s2 - m2) * inv);
+}
+
+}  // namespace
+}  // namespace elfa
+
+ELFA_API int elfa_softmax_rows(const void* x, void* out, long long rows, int cols, long long ldx, long long ldo, float scale,
+                               void* stream) {
+  ELFA_REQUIRE(x && out && rows > 0 && cols > 0 && scale > 0.f, "softmax_rows: bad arguments");
+  const long long blocks = (rows + 7) / 8;
+  ELFA_REQUIRE(blocks < (1ll << 31), "softmax_rows: too many rows");
+  elfa::softmax_rows_kernel<<<(int)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), rows, cols, ldx, ldo, scale);
+  ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
+  return ELFA_OK;
+}

@@ -208,13 +208,31 @@ class _Base:
         raise NotImplementedError
 
     def state_dict(self) -> Dict[str, object]:
-        return {"step": self.step_count, "lr": self.lr, "lo": self.lo, "hi": self.hi,
-                "tensors": {k: v.detach().cpu() for k, v in self.state_tensors().items()}}
+        """Collective when the state is sharded over the data-parallel group: every rank's shard is gathered
+        (one tensor at a time, moved to the host right away) so that the rank that writes the checkpoint
+        holds all of them, stacked ``[dp, shard]``."""
+        out: Dict[str, object] = {"step": self.step_count, "lr": self.lr, "lo": self.lo, "hi": self.hi}
+        tensors = {}
+        stacked = (self.sharded or self.presharded) and self.pc.dp_size > 1 and dist.is_initialized()
+        for k, v in self.state_tensors().items():
+            v = v.detach()
+            if stacked:
+                parts = [torch.empty_like(v) for _ in range(self.pc.dp_size)]
+                dist.all_gather(parts, v.contiguous(), group=self.pc.dp_group)
+                tensors[k] = torch.stack([p.cpu() for p in parts])
+            else:
+                tensors[k] = v.cpu()
+        out["tensors"] = tensors
+        out["stacked_over_dp"] = bool(stacked)
+        return out
 
     def load_state_dict(self, sd) -> None:
         self.step_count = int(sd["step"])
         for k, v in self.state_tensors().items():
-            v.copy_(sd["tensors"][k].to(v.device))
+            t = sd["tensors"][k]
+            if sd.get("stacked_over_dp"):
+                t = t[self.pc.dp_rank]
+            v.copy_(t.to(v.device))
 
 
 class AdamW(_Base):

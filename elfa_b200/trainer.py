@@ -97,6 +97,8 @@ class Trainer:
         self.best_loss = float("inf")
         self.accum = cfg.accumulation_steps()
         self.last_loss = float("nan")
+        from .utils.history import LossHistory
+        self.history = LossHistory()
 
     # ------------------------------------------------------------------ data
     def make_loader(self, data_path: Optional[str] = None) -> DataLoader:
@@ -157,7 +159,8 @@ class Trainer:
         return loss
 
     # ------------------------------------------------------------------- run
-    def run(self, data_path: Optional[str] = None, max_steps: Optional[int] = None) -> List[float]:
+    def run(self, data_path: Optional[str] = None, max_steps: Optional[int] = None, early_stop_patience: int = 0,
+            early_stop_min_delta: float = 0.0) -> List[float]:
         cfg = self.cfg
         loader = self.make_loader(data_path)
         if self.step > 0:
@@ -175,6 +178,9 @@ class Trainer:
                     self.epoch = loader.epoch
             loss = self.finish_step(self.train_step(batches))
             losses.append(loss)
+            self.history.record(self.step, loss)
+            if early_stop_patience > 0 and self.history.should_stop_early(early_stop_patience, early_stop_min_delta):
+                break
             if self.telemetry is not None and self.step % max(cfg.telemetry.metrics_interval, 1) == 0:
                 now = time.time()
                 thr = (self.tokens_seen - tok_last) / max(now - t_last, 1e-9)

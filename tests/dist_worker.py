@@ -142,6 +142,36 @@ def mode_zero(dev, backend, dtype, stage):
     dist.barrier()
 
 
+def mode_ckpt(dev, stage, ckpt_dir):
+    """Sharded optimizer state survives a checkpoint: train 2 + save + 2 more == resume + 2."""
+    from elfa_b200.trainer import Trainer
+    pc = build_context(1, False, "nccl")
+    def make():
+        cfg = small_cfg("fp32", 1, "nccl")
+        cfg.runtime.zero_stage = stage
+        cfg.training.micro_batch_size = 2
+        cfg.training.global_batch_size = 2 * pc.dp_size
+        cfg.checkpoint.dir = ckpt_dir
+        cfg.checkpoint.save_optimizer = True
+        cfg.checkpoint.async_save = False
+        return Trainer(cfg, device=dev, pc=pc, telemetry=False)
+    tr = make()
+    tr.run(max_steps=2)
+    path = tr.save_checkpoint()
+    dist.barrier()
+    paths = [path]
+    dist.broadcast_object_list(paths, src=0)
+    cont = tr.run(max_steps=2)
+    tr2 = make()
+    tr2.resume(paths[0])
+    again = tr2.run(max_steps=2)
+    for a, b in zip(cont, again):
+        assert abs(a - b) < 1e-5 * max(1.0, abs(a)), f"resume diverges: {cont} vs {again}"
+    if pc.rank == 0:
+        print(f"CKPT_OK stage={stage} cont={[round(x, 5) for x in cont]} again={[round(x, 5) for x in again]}")
+    dist.barrier()
+
+
 def mode_timeout(pc, dev):
     """Only rank 0 launches the fused all-gather GEMM; its peers never push, so the wait on their
     counters must give up after the limit and report it through the status word."""
@@ -177,9 +207,13 @@ def main():
     mode = sys.argv[1]
     backend = sys.argv[2] if len(sys.argv) > 2 else "nccl"
     dtype = sys.argv[3] if len(sys.argv) > 3 else "bf16"
-    use_cuda = torch.cuda.is_available() and mode not in ("tp_cpu", "zero_cpu")
+    use_cuda = torch.cuda.is_available() and mode not in ("tp_cpu", "zero_cpu", "ckpt_cpu")
     world = init_distributed("nccl" if use_cuda else "gloo")
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if use_cuda else torch.device("cpu")
+    if mode == "ckpt_cpu":
+        mode_ckpt(dev, int(sys.argv[2]), sys.argv[3])
+        dist.destroy_process_group()
+        return
     if mode in ("zero", "zero_cpu"):
         mode_zero(dev, backend, dtype, int(sys.argv[4]) if len(sys.argv) > 4 else 1)
         dist.destroy_process_group()

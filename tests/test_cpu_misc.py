@@ -132,3 +132,19 @@ if r == 0: print("SP_OK")
     cmd = cmd[:-2] + [path]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES=""))
     assert r.returncode == 0 and "SP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+def test_loss_history_moving_average_early_stop_manifest(tmp_path):
+    import json
+    from elfa_b200.utils.history import LossHistory
+    h = LossHistory()
+    for i, x in enumerate([5.0, 4.0, 3.0, 2.5, float("nan"), 2.4]):
+        h.record(i + 1, x)
+    assert h.best() == 2.4 and abs(h.moving_average(3) - (2.5 + 2.4) / 2) < 1e-9
+    assert not h.should_stop_early(patience=2)
+    for i in range(4):
+        h.record(10 + i, 2.45)
+    assert h.should_stop_early(patience=3) and not h.should_stop_early(patience=3, min_delta=-1.0)
+    h.record_eval(12, perplexity=11.0)
+    doc = json.load(open(h.write_manifest(str(tmp_path / "run"), {"config_hash": "abc"})))
+    assert doc["num_steps"] == 10 and doc["best_loss"] == 2.4 and doc["evals"][0]["perplexity"] == 11.0 and doc["config_hash"] == "abc"
