@@ -148,3 +148,34 @@ def test_loss_history_moving_average_early_stop_manifest(tmp_path):
     h.record_eval(12, perplexity=11.0)
     doc = json.load(open(h.write_manifest(str(tmp_path / "run"), {"config_hash": "abc"})))
     assert doc["num_steps"] == 10 and doc["best_loss"] == 2.4 and doc["evals"][0]["perplexity"] == 11.0 and doc["config_hash"] == "abc"
+
+
+def test_entropy_tokenizer_roundtrip_merges_and_file(tmp_path):
+    from elfa_b200.data.entropy_tokenizer import BOS, EOD, EOS, EntropyTokenizer
+    tok = EntropyTokenizer(400)
+    texts = ["the cat sat on the mat.", "the dog sat, the cat ran!", "that is the end"]
+    plain = tok.encode(texts[0])
+    assert plain[0] == BOS and plain[-1] == EOS and all(6 <= t < 262 for t in plain[1:-1])
+    tok.train(texts, 20)
+    ids = tok.encode(texts[0])
+    assert len(ids) < len(plain) and tok.decode(ids) == texts[0].encode()
+    assert tok.decode(tok.encode("zebra: ünïcode")) == "zebra: ünïcode".encode()
+    p = str(tmp_path / "tok.bin")
+    tok.save(p)
+    tok2 = EntropyTokenizer(400)
+    tok2.load(p)
+    assert tok2.encode(texts[1]) == tok.encode(texts[1]) and tok2.eod_token() == EOD
+    b = tok.batch(ids, 8)
+    assert b.tokens == ids[:8] and b.targets == ids[1:9]
+
+
+def test_hash_helpers(tmp_path):
+    from elfa_b200.utils import hashing as H
+    assert H.sha256_hex(b"abc") == "ba7816bf8f01cfea414140de5dae2223b00361a396177a9cb410ff61f20015ad"
+    p = tmp_path / "f.bin"
+    p.write_bytes(b"x" * 3_000_000)
+    assert H.sha256_file(str(p)) == H.sha256_bytes(b"x" * 3_000_000) and H.verify_sha256(b"abc", H.sha256_bytes(b"abc"))
+    # XXH64 reference vectors (seed 0): empty input and "a"
+    assert H.xxh64(b"") == 0xEF46DB3751D8E999 and H.xxh64(b"a") == 0xD24EC4F1A98C6E5B
+    assert H.xxh64(b"a" * 100) != H.xxh64(b"a" * 101) and H.hash_string("k") == H.xxh64(b"k")
+    assert H.combine(1, 2) != H.combine(2, 1) and H.hash_fields([1, "a", 2.5]) != H.hash_fields([1, "a", 2.0])
