@@ -66,7 +66,9 @@ struct QParams {
 
 template <int BN, int STAGES, bool TWO, bool FP4 = false>
 struct QSmem {
-  static constexpr int NATOM = BN <= 128 ? 1 : 2;         // B scale atoms per tile (BN = 192 starts at +0 or +64 rows of an atom)
+  // B scale atoms per tile: a tile starts 0 / 32 / 64 / 96 rows into a 128-row atom depending on BN
+  // (128: always 0 -> 1 atom; 192: 0 or 64 -> 2; 224: 0 / 32 / 64 / 96 -> 3)
+  static constexpr int NATOM = BN <= 128 ? 1 : (BN <= 192 ? 2 : 3);
   static constexpr int KSF = FP4 ? 4 : 1;                 // scale atoms along K per stage: an atom covers 4 blocks of 32 (fp8) or 16 (fp4) elements
   static constexpr int A_BYTES = QBM * QBK;
   static constexpr int B_BYTES = (TWO ? BN / 2 : BN) * QBK;
@@ -526,11 +528,12 @@ ELFA_API int elfa_gemm_mxfp8(const void* A, const void* sfa, const void* B, cons
                "gemm_mxfp8: scale tensors must be 16-byte aligned");
   unsigned int* st = status_word();
   ELFA_REQUIRE(st != nullptr, "gemm_mxfp8: no status word");
-  // force_bn: 128 / 192 single-CTA tiles, 384 = CTA pairs on 256 x 192 tiles (the default for problems that
-  // fill at least one wave of pairs)
-  const bool pair = force_bn == 384 ||
-                    (force_bn == 0 && N > 128 && (long long)((M + 255) / 256) * ((N + 191) / 192) >= device_sm_count() / 2);
-  const int BN = pair ? 192 : ((force_bn == 128 || force_bn == 192) ? force_bn : (N <= 128 ? 128 : 192));
+  // force_bn: 128 / 192 single-CTA tiles, 384 / 448 = CTA pairs on 256 x 192 / 256 x 224 tiles. Pairs are the default for
+  // problems that fill at least one wave of them; 224 columns bring the instruction closest to the ~120 cycles an
+  // M = 128 instruction costs anyway while still leaving room for the scale factors next to two accumulators.
+  const bool pair = force_bn == 384 || force_bn == 448 ||
+                    (force_bn == 0 && N > 128 && (long long)((M + 255) / 256) * ((N + 223) / 224) >= device_sm_count() / 2);
+  const int BN = pair ? (force_bn == 384 ? 192 : 224) : ((force_bn == 128 || force_bn == 192) ? force_bn : (N <= 128 ? 128 : 192));
   CUtensorMap tmA, tmB;
   int rc = shared_tmap(&tmA, A, 1, (uint64_t)M, (uint64_t)K, (uint64_t)K, QBM, QBK);
   if (rc != ELFA_OK) return rc;
@@ -538,7 +541,7 @@ ELFA_API int elfa_gemm_mxfp8(const void* A, const void* sfa, const void* B, cons
   if (rc != ELFA_OK) return rc;
   // scale tensors as [atoms, 128] 32-bit words; one box = the atoms of one tile and K tile
   const int kt = (K + QBK - 1) / QBK;
-  const int natom_b = BN <= 128 ? 1 : 2;
+  const int natom_b = BN <= 128 ? 1 : (BN <= 192 ? 2 : 3);
   CUtensorMap tmSFA, tmSFB;
   rc = sf_tmap(&tmSFA, sfa, (uint64_t)((M + 127) / 128) * kt, 1);
   if (rc != ELFA_OK) return rc;
@@ -558,6 +561,7 @@ ELFA_API int elfa_gemm_mxfp8(const void* A, const void* sfa, const void* B, cons
   p.flags = flags;
   p.status = st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (pair && BN == 224) return launch_q<224, 6, true>(tmA, tmB, tmSFA, tmSFB, p, s);
   if (pair) return launch_q<192, 7, true>(tmA, tmB, tmSFA, tmSFB, p, s);
   if (BN == 192) return launch_q<192, 5, false>(tmA, tmB, tmSFA, tmSFB, p, s);
   return launch_q<128, 6, false>(tmA, tmB, tmSFA, tmSFB, p, s);
