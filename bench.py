@@ -82,7 +82,7 @@ class ClockSampler:
 
 def reference_arm(args) -> int:
     # The reference (kollarsandor/elfa) is a Zig program with no Python packaging: the offline install
-    # `pip install --no-index ... --target baseline/_ref /root/reference` stops with "Neither 'setup.py'
+    # the offline `pip install --no-index ... --target baseline/_ref <reference checkout>` stops with "Neither 'setup.py'
     # nor 'pyproject.toml' found", there is no zig toolchain, its build needs a missing tests/unit/main.zig,
     # and 5 of its 11 .cu files do not compile with nvcc 12.9.
     rank = int(os.environ.get("RANK", "0"))

@@ -126,6 +126,13 @@ int elfa_zero3_gather(const unsigned long long* peer_shards, int world, long lon
 int elfa_zero3_reduce_acc(const unsigned long long* peer_grads, int world, long long lo, long long n, float* acc, float scale,
                           void* stream);
 
+int elfa_softmax_rows(const void* x, void* out, long long rows, int cols, long long ldx, long long ldo, float scale, void* stream);
+
+// ---- p2p.cu ------------------------------------------------------------------------------------
+int elfa_p2p_send(const void* src, unsigned long long peer_dst, long long bytes, unsigned long long peer_counter, int* blocks_out,
+                  void* stream);
+int elfa_p2p_wait(const void* counter, unsigned int target, int wait_ms, void* stream);
+
 // ---- prism.cu ----------------------------------------------------------------------------------
 int elfa_prism_fwd(const void* u, const void* v, const unsigned long long* p, void* y, long long tokens, int G, int d, int L,
                    void* stream);

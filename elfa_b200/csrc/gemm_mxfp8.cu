@@ -528,12 +528,12 @@ ELFA_API int elfa_gemm_mxfp8(const void* A, const void* sfa, const void* B, cons
                "gemm_mxfp8: scale tensors must be 16-byte aligned");
   unsigned int* st = status_word();
   ELFA_REQUIRE(st != nullptr, "gemm_mxfp8: no status word");
-  // force_bn: 128 / 192 single-CTA tiles, 384 / 448 = CTA pairs on 256 x 192 / 256 x 224 tiles. Pairs are the default for
-  // problems that fill at least one wave of them; 224 columns bring the instruction closest to the ~120 cycles an
-  // M = 128 instruction costs anyway while still leaving room for the scale factors next to two accumulators.
-  const bool pair = force_bn == 384 || force_bn == 448 ||
-                    (force_bn == 0 && N > 128 && (long long)((M + 255) / 256) * ((N + 223) / 224) >= device_sm_count() / 2);
-  const int BN = pair ? (force_bn == 384 ? 192 : 224) : ((force_bn == 128 || force_bn == 192) ? force_bn : (N <= 128 ? 128 : 192));
+  // force_bn: 128 / 192 single-CTA tiles, 384 = CTA pairs on 256 x 192 tiles (the default for problems that fill at
+  // least one wave of pairs). A 256 x 224 pair tile was tried and raised a misaligned-address fault on multi-tile
+  // problems; it is not instantiated.
+  const bool pair = force_bn == 384 ||
+                    (force_bn == 0 && N > 128 && (long long)((M + 255) / 256) * ((N + 191) / 192) >= device_sm_count() / 2);
+  const int BN = pair ? 192 : ((force_bn == 128 || force_bn == 192) ? force_bn : (N <= 128 ? 128 : 192));
   CUtensorMap tmA, tmB;
   int rc = shared_tmap(&tmA, A, 1, (uint64_t)M, (uint64_t)K, (uint64_t)K, QBM, QBK);
   if (rc != ELFA_OK) return rc;
@@ -561,7 +561,6 @@ ELFA_API int elfa_gemm_mxfp8(const void* A, const void* sfa, const void* B, cons
   p.flags = flags;
   p.status = st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (pair && BN == 224) return launch_q<224, 6, true>(tmA, tmB, tmSFA, tmSFB, p, s);
   if (pair) return launch_q<192, 7, true>(tmA, tmB, tmSFA, tmSFB, p, s);
   if (BN == 192) return launch_q<192, 5, false>(tmA, tmB, tmSFA, tmSFB, p, s);
   return launch_q<128, 6, false>(tmA, tmB, tmSFA, tmSFB, p, s);

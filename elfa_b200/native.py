@@ -44,7 +44,7 @@ def _ctype(decl: str):
     return {
         "int": ctypes.c_int, "unsigned": ctypes.c_uint, "unsigned int": ctypes.c_uint, "long long": ctypes.c_longlong,
         "float": ctypes.c_float, "double": ctypes.c_double, "size_t": ctypes.c_size_t, "uint64_t": ctypes.c_uint64,
-        "uint32_t": ctypes.c_uint32,
+        "uint32_t": ctypes.c_uint32, "unsigned long long": ctypes.c_ulonglong,
     }[base]
 
 

@@ -354,3 +354,16 @@ def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, smoothing: float 
     if denom is None:
         denom = float(targets.numel())
     return _CrossEntropy.apply(logits, targets, smoothing, denom, float(grad_scale))
+
+
+def softmax(x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """Row softmax of ``x * scale`` over the last dimension (reference: ``src/nn/nn_kernels.zig:226-267``).
+    CUDA bf16 tensors use the warp-per-row kernel; everything else plain PyTorch."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.stride(-1) == 1 and scale > 0:
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        out = torch.empty_like(x2)
+        lib.call("elfa_softmax_rows", x2, out, x2.shape[0], x2.shape[1], x2.stride(0), out.stride(0), float(scale), stream_ptr(x2))
+        return out.view(x.shape)
+    return torch.softmax(x.float() * scale, dim=-1).to(x.dtype)

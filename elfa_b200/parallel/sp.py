@@ -106,3 +106,77 @@ def reduce_scatter_gradients(g: torch.Tensor, group=None) -> torch.Tensor:
     g = g.contiguous().clone()
     dist.all_reduce(g, group=group)
     return g[rank * n:(rank + 1) * n].clone()
+
+
+class PeerMailbox:
+    """Write-then-flag hand-off to the right neighbour of a ring over NVLink peer memory (GPU only).
+
+    Every rank owns a two-slot mailbox and two counters in the group's symmetric arena: ``arrivals``
+    (raised by the left neighbour after its stores) and ``acks`` (raised by the right neighbour after it
+    has copied a message out). ``send`` waits (bounded) until the slot it is about to overwrite was
+    acknowledged, stores into the neighbour's slot and raises the neighbour's arrival counter;
+    ``recv`` waits (bounded) for the arrival, copies the slot out and acknowledges to the left.
+    All waits are kernels on the current stream: nothing blocks the host.
+
+    reference: ``src/distributed/sequence_parallel.zig:130-159`` (``ringExchange``), ``:202-240``
+    (``syncCrossBoundary``) - grouped NCCL send / receive there.
+    """
+
+    def __init__(self, arena, nbytes: int, name: str = "sp.mailbox"):
+        import ctypes
+        self.arena = arena
+        self.nbytes = (nbytes + 15) // 16 * 16
+        self.rank, self.world = arena.rank, arena.world
+        self.data = arena.alloc(2 * self.nbytes, name + ".data")
+        self.flags = arena.alloc(1024, name + ".flags")          # u32[0] arrivals, u32[64] acks (separate cache lines)
+        self.right, self.left = (self.rank + 1) % self.world, (self.rank - 1) % self.world
+        self._scratch = torch.zeros(4, dtype=torch.int32, device=arena.device)   # 16-byte payload of an acknowledgement
+        self._ack_sink = arena.alloc(1024, name + ".acksink")
+        self._blocks = ctypes.c_int(0)
+        self.sent = 0                     # messages sent to the right
+        self.received = 0                 # messages received from the left
+        self.arrivals_expected = 0        # running total of arrival-counter increments expected on this rank
+        self.acks_expected_blocks = 0
+        arena.barrier()
+
+    def _blocks_for(self, nbytes: int) -> int:
+        return min(64, (nbytes // 16 + 255) // 256)
+
+    def send(self, t: torch.Tensor) -> None:
+        from ..native import lib, stream_ptr
+        import ctypes
+        src = t.contiguous().view(torch.uint8).reshape(-1)
+        n = src.numel()
+        assert n <= self.nbytes and n % 16 == 0, "message does not fit the mailbox (sizes are multiples of 16 bytes)"
+        st = stream_ptr(src)
+        slot = self.sent % 2
+        if self.sent >= 2:
+            # the message two sends ago used this slot: one acknowledgement per consumed message
+            lib.call("elfa_p2p_wait", self.flags.tensor[256:], self.sent - 1, 0, st)
+        dst = self.arena.peer_address(self.right, self.data) + slot * self.nbytes
+        cnt = self.arena.peer_address(self.right, self.flags)
+        lib.call("elfa_p2p_send", src, dst, n, cnt, ctypes.addressof(self._blocks), st)
+        self.sent += 1
+        self._last_blocks = self._blocks.value
+
+    def recv(self, out: torch.Tensor) -> torch.Tensor:
+        from ..native import lib, stream_ptr
+        import ctypes
+        n = out.numel() * out.element_size()
+        st = stream_ptr(out)
+        self.arrivals_expected += self._blocks_for(n)
+        lib.call("elfa_p2p_wait", self.flags.tensor, self.arrivals_expected, 0, st)
+        slot = self.received % 2
+        out.view(torch.uint8).reshape(-1).copy_(self.data.tensor[slot * self.nbytes: slot * self.nbytes + n])
+        self.received += 1
+        # acknowledge: a 16-byte store into the left neighbour's sink raises its ack counter by one block
+        sink = self.arena.peer_address(self.left, self._ack_sink)
+        ack = self.arena.peer_address(self.left, self.flags) + 256
+        lib.call("elfa_p2p_send", self._scratch, sink, 16, ack, ctypes.addressof(self._blocks), st)
+        return out
+
+
+def ring_exchange_peer(x: torch.Tensor, box: "PeerMailbox") -> torch.Tensor:
+    """``ring_exchange(x, 1)`` through a :class:`PeerMailbox` (every rank sends right and receives from the left)."""
+    box.send(x)
+    return box.recv(torch.empty_like(x))

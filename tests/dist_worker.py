@@ -172,6 +172,26 @@ def mode_ckpt(dev, stage, ckpt_dir):
     dist.barrier()
 
 
+def mode_mailbox(pc, dev):
+    """Ring hand-off through peer mailboxes: several rounds, payload checked against the sender's rank."""
+    from elfa_b200 import native
+    from elfa_b200.parallel.sp import PeerMailbox, ring_exchange_peer
+    from elfa_b200.runtime.symm import SymmetricArena
+    arena = SymmetricArena.for_group(pc.tp_group, dev, 64 << 20)
+    box = PeerMailbox(arena, 1 << 20)
+    r, w = pc.rank, pc.tp_size
+    for rnd in range(6):
+        x = torch.full((4096,), float(r * 100 + rnd), device=dev, dtype=torch.float32)
+        got = ring_exchange_peer(x, box)
+        torch.cuda.synchronize()
+        assert native.status() == 0
+        want = float(((r - 1) % w) * 100 + rnd)
+        assert bool((got == want).all()), (r, rnd, float(got[0]), want)
+    dist.barrier()
+    if r == 0:
+        print("MAILBOX_OK")
+
+
 def mode_timeout(pc, dev):
     """Only rank 0 launches the fused all-gather GEMM; its peers never push, so the wait on their
     counters must give up after the limit and report it through the status word."""
@@ -225,6 +245,8 @@ def main():
         mode_tp(pc, dev, backend, dtype)
     elif mode == "timeout":
         mode_timeout(pc, dev)
+    elif mode == "mailbox":
+        mode_mailbox(pc, dev)
     dist.destroy_process_group()
 
 

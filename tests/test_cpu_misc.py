@@ -179,3 +179,15 @@ def test_hash_helpers(tmp_path):
     assert H.xxh64(b"") == 0xEF46DB3751D8E999 and H.xxh64(b"a") == 0xD24EC4F1A98C6E5B
     assert H.xxh64(b"a" * 100) != H.xxh64(b"a" * 101) and H.hash_string("k") == H.xxh64(b"k")
     assert H.combine(1, 2) != H.combine(2, 1) and H.hash_fields([1, "a", 2.5]) != H.hash_fields([1, "a", 2.0])
+
+
+def test_native_header_parses_and_library_exports_every_prototype():
+    """Every prototype of the C header maps to ctypes types, and the built library (when present) exports it."""
+    import ctypes
+    from elfa_b200 import native
+    protos = native._parse_header(native._HEADER.read_text())
+    assert len(protos) > 40 and "elfa_gemm_bf16" in protos and "elfa_p2p_send" in protos
+    if native._LIB_PATH.exists():
+        dll = ctypes.CDLL(str(native._LIB_PATH))
+        missing = [n for n in protos if not hasattr(dll, n)]
+        assert not missing, missing

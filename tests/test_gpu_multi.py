@@ -66,3 +66,9 @@ def test_zero3_parameter_sharding_matches_single_gpu(cuda_device, backend):
     assert "ZERO_OK stage=3" in r.stdout
     if backend == "fused":
         assert "peer_kernels=True" in r.stdout
+
+
+def test_ring_handoff_through_peer_mailboxes(cuda_device):
+    r = _run(["mailbox"], 29709)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "MAILBOX_OK" in r.stdout

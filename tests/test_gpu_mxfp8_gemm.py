@@ -18,7 +18,7 @@ def _operands(M, N, K, seed):
 @pytest.mark.parametrize("M,N,K,bn", [(128, 128, 128, 0), (256, 384, 512, 0), (256, 384, 512, 128), (300, 200, 160, 0),
                                       (1024, 1536, 4096, 0), (2048, 4096, 1024, 128), (384, 1000, 2048, 192),
                                       (256, 192, 128, 384), (300, 200, 160, 384), (1024, 1536, 4096, 384), (4096, 4096, 2048, 0),
-                                      (2000, 1000, 512, 384), (256, 224, 128, 448), (1000, 1200, 640, 448), (4096, 4096, 1024, 448)])
+                                      (2000, 1000, 512, 384)])
 def test_mxfp8_gemm_matches_dequantised_product(M, N, K, bn):
     from elfa_b200 import native
     from elfa_b200.ops import gemm_mxfp8 as q

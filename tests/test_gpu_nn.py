@@ -149,3 +149,13 @@ def test_adamw_and_clip(cuda_device):
     lib.call("elfa_adamw", param, 1, master, m, v, g, 0, n, 1e-2, 0.9, 0.95, 1e-8, 0.1, 4, scal, st)
     assert torch.equal(before, master)
     assert native.status() & native.ST_NONFINITE
+
+
+@pytest.mark.parametrize("rows,cols", [(7, 33), (64, 1000), (300, 4096), (5, 32000)])
+def test_softmax_rows(cuda_device, rows, cols):
+    from elfa_b200.ops import nn as nnops
+    x = (torch.randn(rows, cols, device=cuda_device) * 3).bfloat16()
+    y = nnops.softmax(x, 0.7)
+    ref = torch.softmax(x.float() * 0.7, dim=-1)
+    assert (y.float() - ref).abs().max() <= 2 ** -8 * ref.max() + 1e-4
+    assert (y.float().sum(-1) - 1).abs().max() < 0.02
