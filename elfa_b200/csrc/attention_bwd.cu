@@ -163,20 +163,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
       constexpr uint32_t idesc_acc = make_idesc_bf16(128, HDP, false, true);   // A from tensor memory, B MN-major
       auto wait = [&](int bi, uint32_t ph) { return __all_sync(0xffffffffu, mbar_wait(bar(bi), ph, abort_flag, p.status)) != 0; };
-      bool ok = wait(BB_RES, 0);
-      for (int it = 0; it < n_iter && ok; ++it) {
-        const int slot = it & 1;
-        if (!wait(BB_INFULL0 + slot, (it >> 1) & 1)) { ok = false; break; }
-        tc_fence_after();
-        // DKV: S^T = K Q^T, dP^T = V dO^T (A = resident);  DQ: S = Q K^T, dP = dO V^T (A = resident)
-        const uint32_t a0 = sRes0, a1 = sRes1, b0 = sIn0(slot), b1 = sIn1(slot);
+      // Issue order per iteration: [dV(it)] S(it+1) | dK or dQ (it) dP(it+1). The products of the next inner tile are
+      // queued as soon as the tensor-memory columns they overwrite have been consumed (S after the probabilities were
+      // read, dP after dS was multiplied), so the exponentials of tile it+1 overlap the accumulator MMAs of tile it.
+      // DKV: S^T = K Q^T, dP^T = V dO^T (A = resident);  DQ: S = Q K^T, dP = dO V^T (A = resident)
+      auto issue_s = [&](int it) {
+        const uint32_t a0 = sRes0, b0 = sIn0(it & 1);
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < HDP / 16; ++kk) {
             const uint32_t off = (kk / 4) * SUBB + (kk % 4) * 32;
             tc_mma_f16(TM_S, make_smem_desc(a0 + off, 16, 1024, 2), make_smem_desc(b0 + off, 16, 1024, 2), idesc_s, kk != 0);
           }
-          tc_commit(bar(BB_S));      // the exponentials start while dP is still being multiplied
+          tc_commit(bar(BB_S));
+        }
+        __syncwarp();
+      };
+      auto issue_dp = [&](int it) {
+        const uint32_t a1 = sRes1, b1 = sIn1(it & 1);
+        if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < HDP / 16; ++kk) {
             const uint32_t off = (kk / 4) * SUBB + (kk % 4) * 32;
@@ -185,15 +190,33 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
           tc_commit(bar(BB_DP));
         }
         __syncwarp();
-        if (DKV) {
-          if (!wait(BB_P, it & 1)) { ok = false; break; }
+      };
+      bool ok = wait(BB_RES, 0);
+      if (ok && n_iter > 0) {
+        ok = wait(BB_INFULL0, 0);
+        if (ok) {
           tc_fence_after();
+          issue_s(0);
+          issue_dp(0);
+        }
+      }
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int slot = it & 1;
+        const uint32_t b0 = sIn0(slot), b1 = sIn1(slot);
+        if (!wait(BB_P, it & 1)) { ok = false; break; }      // the S columns have been read (DKV: P is in place)
+        tc_fence_after();
+        if (DKV) {
           if (elect_one()) {
 #pragma unroll
-            for (int kk = 0; kk < 8; ++kk)   // dV[key, d] += sum_q P^T[key, q] dO[q, d]  (runs while dS is computed)
+            for (int kk = 0; kk < 8; ++kk)   // dV[key, d] += sum_q P^T[key, q] dO[q, d]
               tc_mma_f16_ts(TM_ACC0, TM_S + kk * 8, make_smem_desc(b1 + kk * 2048, SUBB, 1024, 2), idesc_acc, (it | kk) != 0);
           }
           __syncwarp();
+        }
+        if (it + 1 < n_iter) {
+          if (!wait(BB_INFULL0 + ((it + 1) & 1), ((it + 1) >> 1) & 1)) { ok = false; break; }
+          tc_fence_after();
+          issue_s(it + 1);
         }
         if (!wait(BB_DS, it & 1)) { ok = false; break; }
         tc_fence_after();
@@ -210,6 +233,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
           tc_commit(bar(BB_INFREE0 + slot));
         }
         __syncwarp();
+        if (it + 1 < n_iter) issue_dp(it + 1);
       }
       if (ok) {
         if (elect_one()) tc_commit(bar(BB_ACC));
@@ -322,6 +346,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
         }
         tc_fence_before();
         mbar_arrive(bar(BB_P));
+      } else {
+        tc_fence_before();
+        mbar_arrive(bar(BB_P));            // the S columns have been read: the next S product may overwrite them
       }
       // ---- phase 2: dS = P * (dP - delta) * scale
       if (ok) ok = mbar_wait(bar(BB_DP), it & 1, abort_flag, p.status);
