@@ -99,6 +99,12 @@ class Trainer:
         self.last_loss = float("nan")
         from .utils.history import LossHistory
         self.history = LossHistory()
+        # host-side failure detection / fault injection (both off unless their environment variables are set)
+        from .runtime.fault import FaultPlan, Heartbeat
+        self.faults = FaultPlan.from_env()
+        hb_dir = os.environ.get("ELFA_HEARTBEAT_DIR", "")
+        self.heartbeat = Heartbeat(hb_dir, pc.rank, pc.world_size) if hb_dir and pc.world_size > 1 else None
+        self.heartbeat_timeout = float(os.environ.get("ELFA_HEARTBEAT_TIMEOUT_S", "30"))
 
     # ------------------------------------------------------------------ data
     def make_loader(self, data_path: Optional[str] = None) -> DataLoader:
@@ -120,6 +126,17 @@ class Trainer:
         """One optimizer step over ``batches`` (micro-batches). Returns the mean loss as a device
         scalar (no host synchronisation here)."""
         cfg = self.cfg
+        if self.faults:
+            f = self.faults.active("kill_rank", self.pc.rank, self.step)
+            if f is not None:       # leaves between steps: nothing of this rank is in flight
+                raise SystemExit(int(f.args.get("code", 17)))
+            f = self.faults.active("delay_ms", self.pc.rank, self.step)
+            if f is not None:
+                time.sleep(f.args.get("ms", 10.0) / 1e3)
+        if self.heartbeat is not None:
+            # soft barrier on the host: a peer that died between steps is reported here instead of blocking the next collective
+            self.heartbeat.beat(self.step)
+            self.heartbeat.wait_for_peers(self.step, self.heartbeat_timeout)
         self.optimizer.zero_grad()
         n_micro = len(batches)
         total = None
@@ -136,6 +153,8 @@ class Trainer:
             if self.zero3:
                 self.flat.after_backward()
             total = loss.detach() if total is None else total + loss.detach()
+        if self.faults and self.faults.active("nan_grad", self.pc.rank, self.step) is not None:
+            self.flat.grads[:1].fill_(float("nan"))     # the optimizer's non-finite guard must skip this step
         lr = self.scheduler.get_lr()
         self.optimizer.step(lr)
         self.scheduler.step()

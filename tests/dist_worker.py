@@ -192,6 +192,24 @@ def mode_mailbox(pc, dev):
         print("MAILBOX_OK")
 
 
+def mode_killrank(dev):
+    """A rank leaves between steps; the survivors notice through the heartbeat files before their next collective."""
+    from elfa_b200.runtime.fault import RankFailure
+    from elfa_b200.trainer import Trainer
+    pc = build_context(1, False, "nccl")
+    cfg = small_cfg("fp32", 1, "nccl")
+    cfg.runtime.zero_stage = 0
+    cfg.training.micro_batch_size = 2
+    cfg.training.global_batch_size = 2 * pc.dp_size
+    tr = Trainer(cfg, device=dev, pc=pc, telemetry=False)
+    try:
+        tr.run(max_steps=6)
+        print(f"rank {pc.rank}: NO_FAILURE_SEEN")
+    except RankFailure as e:
+        print(f"DETECTED rank={pc.rank} missing={e.ranks} step={e.step}", flush=True)
+    os._exit(0)          # the group is broken: leave without the collective teardown
+
+
 def mode_timeout(pc, dev):
     """Only rank 0 launches the fused all-gather GEMM; its peers never push, so the wait on their
     counters must give up after the limit and report it through the status word."""
@@ -227,9 +245,12 @@ def main():
     mode = sys.argv[1]
     backend = sys.argv[2] if len(sys.argv) > 2 else "nccl"
     dtype = sys.argv[3] if len(sys.argv) > 3 else "bf16"
-    use_cuda = torch.cuda.is_available() and mode not in ("tp_cpu", "zero_cpu", "ckpt_cpu")
+    use_cuda = torch.cuda.is_available() and mode not in ("tp_cpu", "zero_cpu", "ckpt_cpu", "killrank_cpu")
     world = init_distributed("nccl" if use_cuda else "gloo")
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if use_cuda else torch.device("cpu")
+    if mode == "killrank_cpu":
+        mode_killrank(dev)
+        return
     if mode == "ckpt_cpu":
         mode_ckpt(dev, int(sys.argv[2]), sys.argv[3])
         dist.destroy_process_group()

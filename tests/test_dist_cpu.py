@@ -8,10 +8,11 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(nproc, args, port, timeout=600):
+def _run(nproc, args, port, timeout=600, extra_env=None, allow_fail=False):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), os.path.join(ROOT, "tests", "dist_worker.py"), *args]
     env = dict(os.environ, OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES="")
+    env.update(extra_env or {})
     return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
 
 
@@ -34,3 +35,39 @@ def test_sharded_optimizer_state_survives_checkpoint(stage, tmp_path):
     r = _run(2, ["ckpt_cpu", str(stage), str(tmp_path / "ck")], 29641 + stage)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "CKPT_OK" in r.stdout
+
+
+def test_rank_that_leaves_between_steps_is_detected_on_the_host(tmp_path):
+    """Host-side fault injection (kill_rank) + heartbeat soft barrier: survivors raise RankFailure, nobody hangs."""
+    env = {"ELFA_FAULT": "kill_rank:rank=2,step=3,code=0", "ELFA_HEARTBEAT_DIR": str(tmp_path / "hb"), "ELFA_HEARTBEAT_TIMEOUT_S": "3"}
+    r = _run(3, ["killrank_cpu"], 29651, extra_env=env, allow_fail=True)
+    out = r.stdout + r.stderr
+    assert "DETECTED rank=0 missing=[2] step=3" in out and "DETECTED rank=1 missing=[2] step=3" in out, out[-3000:]
+    assert "NO_FAILURE_SEEN" not in out
+
+
+def test_fault_plan_parsing_and_nan_gradient_skips_the_step():
+    import torch
+    from elfa_b200.config import Config
+    from elfa_b200.runtime.fault import FaultPlan
+    from elfa_b200.trainer import Trainer
+    plan = FaultPlan.parse("nan_grad:rank=0,step=1; delay_ms:rank=1,step=2,ms=5")
+    assert plan.active("nan_grad", 0, 1) and not plan.active("nan_grad", 0, 2) and plan.active("delay_ms", 1, 2).args["ms"] == 5
+    with pytest.raises(ValueError):
+        FaultPlan.parse("explode:rank=0")
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = Config.from_file(os.path.join(root, "configs", "bench", "smoke_cpu.yaml"), env_override=False)
+    cfg.checkpoint.dir = ""
+    cfg.telemetry.log_file = ""
+    cfg.training.mixed_precision = True
+    cfg.training.dynamic_loss_scale = True
+    cfg.training.loss_scale = 1024.0
+    tr = Trainer(cfg, device=torch.device("cpu"), telemetry=False)
+    tr.faults = plan
+    w0 = tr.flat.flat.clone()
+    tr.run(max_steps=1)                       # step 0: normal
+    w1 = tr.flat.flat.clone()
+    assert not torch.equal(w0, w1) and tr.scaler.scale == 1024.0
+    tr.run(max_steps=1)                       # step 1: NaN injected -> update skipped, loss scale halved
+    assert torch.equal(tr.flat.flat, w1) and tr.scaler.scale == 512.0 and tr.scaler.skipped_steps == 1
