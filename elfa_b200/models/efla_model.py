@@ -48,10 +48,16 @@ class EflaLayer(nn.Module):
         self.beta_param.no_decay = True
         self.chunk = max(1, min(m.efla.chunk_size, 16)) if m.efla.use_chunked_scan else 16
 
-    def forward(self, x, state=None):
+    def forward(self, x, state=None, sp_group=None):
         B, T, D = x.shape
         k = ops.linear(x, self.w_k).view(B, T, self.H, self.d)
         v = ops.linear(x, self.w_v).view(B, T, self.H, self.d)
+        if sp_group is not None:
+            # sequence parallel: the state at the start of this rank's token block is the composition of the
+            # affine maps of the ranks before it (exact for the delta rule)
+            from ..parallel import sp
+            with torch.no_grad():
+                state = sp.efla_cross_rank_state(k, v, self.beta_param, sp_group)
         o, s = eops.efla_scan(k, v, self.beta_param, state, self.chunk)
         return ops.linear(o.reshape(B, T, self.H * self.d).to(x.dtype), self.w_o), s
 
@@ -69,9 +75,12 @@ class PrismLayer(nn.Module):
         self.conv_bias = nn.Parameter(torch.zeros(D, dtype=dtype, device=device))
         self.conv_bias.no_decay = True
 
-    def forward(self, x, v, carry_state: Optional[torch.Tensor] = None, conv_tail: Optional[torch.Tensor] = None):
+    def forward(self, x, v, carry_state: Optional[torch.Tensor] = None, conv_tail: Optional[torch.Tensor] = None, sp_group=None):
         """x: normed hidden ``[B, T, D]``, v: EFLA output. Returns (y, new_state or None, new conv tail)."""
         W = self.conv_weight.shape[1]
+        if sp_group is not None and W > 1:
+            from ..parallel import sp
+            conv_tail = sp.halo_from_left(x, W - 1, sp_group)      # the left neighbour's last W-1 positions (zeros on rank 0)
         xin = x if conv_tail is None else torch.cat([conv_tail, x], dim=1)
         u = eops.shortconv(xin, self.conv_weight, self.conv_bias)
         if conv_tail is not None:
@@ -110,13 +119,13 @@ class EflaBlock(nn.Module):
         self.mlp_down = nn.Parameter(torch.empty(m.intermediate_dim, m.hidden_dim, dtype=dtype, device=device))
         self.act = "gelu" if m.activation in ("gelu", "swiglu") else m.activation
 
-    def forward(self, x, states=None):
+    def forward(self, x, states=None, sp_group=None):
         n, _ = self.ln1(x)
         e_state = states["efla"] if states is not None else None
-        e, e_state = self.efla(n, e_state)
+        e, e_state = self.efla(n, e_state, sp_group)
         if self.prism is not None:
             q, p_state, tail = self.prism(n, e, states["prism"] if states is not None else None,
-                                          states.get("conv_tail") if states is not None else None)
+                                          states.get("conv_tail") if states is not None else None, sp_group)
         else:
             q, p_state, tail = e, None, None
         n2, r = self.ln2(q, x)                 # fused: r = x + q, n2 = norm2(r)
@@ -224,6 +233,21 @@ class EflaModel(nn.Module):
                 new_states.append(ns)
         n, _ = self.final_norm(x)
         return n, new_states
+
+    @torch.no_grad()
+    def forward_sequence_parallel(self, ids_local: torch.Tensor, group=None) -> torch.Tensor:
+        """Long-context forward with the sequence split over ``group``: ``ids_local [B, T / world]`` is this rank's
+        contiguous token block; returns its logits. Per layer the ranks exchange the ShortConv halo (window - 1 normed
+        positions from the left neighbour) and the EFLA state as an affine prefix, so the result equals the
+        single-rank forward of the whole sequence. Forward only (evaluation, prefill).
+        reference: ``src/distributed/sequence_parallel.zig:54-77,202-240`` (split, boundary exchange); the reference never
+        connects them to its model."""
+        x = ops.embedding(ids_local, self.embed_tokens, None, 0, 0, seq_first=False, vocab_total=self.cfg.model.vocab_size)
+        for blk in self.blocks:
+            x, _ = blk(x, None, group if group is not None else torch.distributed.group.WORLD)
+        n, _ = self.final_norm(x)
+        head = self.lm_head if self.lm_head is not None else self.embed_tokens
+        return ops.linear_nt(n, head)
 
     def forward_with_states(self, ids: torch.Tensor, states: Optional[List[dict]] = None):
         """ids ``[B, T]`` → (logits ``[B, T, V]``, per-layer states) for streaming / generation."""
