@@ -28,25 +28,27 @@ def split_sequence(x: torch.Tensor, rank: int, world: int, dim: int = 1) -> torc
 
 
 def gather_sequence(x_local: torch.Tensor, group=None, dim: int = 1) -> torch.Tensor:
+    """Concatenation of every rank's block along ``dim`` (blocks may differ in length by one)."""
     world = dist.get_world_size(group)
-    sizes = [torch.zeros(1, dtype=torch.int64, device=x_local.device) for _ in range(world)]
-    dist.all_gather(sizes, torch.tensor([x_local.shape[dim]], dtype=torch.int64, device=x_local.device), group=group)
+    rank = dist.get_rank(group)
+    n_local = torch.tensor([x_local.shape[dim]], dtype=torch.int64, device=x_local.device)
+    sizes = [torch.zeros_like(n_local) for _ in range(world)]
+    dist.all_gather(sizes, n_local, group=group)
     parts = []
     for s in sizes:
         shp = list(x_local.shape)
         shp[dim] = int(s)
         parts.append(torch.empty(shp, dtype=x_local.dtype, device=x_local.device))
-    dist.all_gather(parts, x_local.contiguous(), group=group) if len({p.shape for p in parts}) == 1 else _uneven_all_gather(parts, x_local, group)
+    if len({p.shape for p in parts}) == 1:
+        dist.all_gather(parts, x_local.contiguous(), group=group)
+    else:
+        # uneven blocks: one broadcast per rank
+        ranks = dist.get_process_group_ranks(group) if group is not None else list(range(world))
+        for r in range(world):
+            if r == rank:
+                parts[r].copy_(x_local)
+            dist.broadcast(parts[r], src=ranks[r], group=group)
     return torch.cat(parts, dim=dim)
-
-
-def _uneven_all_gather(parts, x_local, group):
-    rank, world = dist.get_rank(group), dist.get_world_size(group)
-    ranks = dist.get_process_group_ranks(group) if group is not None else list(range(world))
-    for r in range(world):
-        if r == rank:
-            parts[r].copy_(x_local)
-        dist.broadcast(parts[r], src=ranks[r], group=group)
 
 
 def ring_exchange(x: torch.Tensor, step: int = 1, group=None) -> torch.Tensor:
