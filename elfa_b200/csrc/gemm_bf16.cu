@@ -137,13 +137,14 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
 // COMM_AG visits the own shard first, then rank-1, rank-2, ... (the order in which pushes arrive);
 // COMM_RS visits rank+1, rank+2, ... and the own shard last (its partial does not travel).
 template <int COMM>
-__device__ __forceinline__ void tile_coords_comm(const GemmParams& p, const CommParams& c, int tile, int& mb, int& nb, int& shard) {
+__device__ __forceinline__ void tile_coords_comm(const GemmParams& p, const CommParams& c, int tile, int& mb, int& nb, int& shard,
+                                                 int tile_m = BM) {
   if (COMM == COMM_NONE) {
     tile_coords(p, tile, mb, nb);
     shard = 0;
     return;
   }
-  const int tm_shard = c.rows_per_rank / BM;
+  const int tm_shard = c.rows_per_rank / tile_m;   // tiles (of tile_m rows: 128, or 256 for CTA pairs) per shard
   const int per_shard = tm_shard * p.tiles_n;
   const int i = tile / per_shard;
   const int lt = tile - i * per_shard;
@@ -155,13 +156,13 @@ __device__ __forceinline__ void tile_coords_comm(const GemmParams& p, const Comm
 // TWO: the CTAs of a 2-CTA cluster work as a pair on 256 x BN tiles (tcgen05 cta_group::2). Each CTA
 // loads its 128 rows of A and its half of B (BN / 2 rows), the even CTA issues one MMA for both, and
 // each CTA ends up with its 128 rows of the accumulator in its own tensor memory. Per CTA this
-// needs a third less shared-memory fill per FLOP than a 128 x BN tile. Plain GEMM only.
+// needs a third less shared-memory fill per FLOP than a 128 x BN tile. In the fused variants a pair's 256 rows lie
+// inside one rank's shard (rows per rank a multiple of 256); flags, pushes and the reduce phase work per CTA as before.
 template <int BN, bool A_MN, bool B_MN, int STAGES, int COMM, bool TWO = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmA2, const GemmParams p, const CommParams cm,
                  const __grid_constant__ OutMaps om) {
-  static_assert(!TWO || COMM == COMM_NONE, "CTA pairs are implemented for the plain GEMM only");
   constexpr int BN_CTA = TWO ? BN / 2 : BN;   // rows of B this CTA keeps in shared memory
   constexpr int TILE_M = TWO ? 2 * BM : BM;   // rows of one work unit
   using L = SmemLayout<BN_CTA, STAGES>;
@@ -232,7 +233,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int tile = unit / splits;
         const int kb0 = (unit - tile * splits) * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
         int mb, nb, shard;
-        tile_coords_comm<COMM>(p, cm, tile, mb, nb, shard);
+        tile_coords_comm<COMM>(p, cm, tile, mb, nb, shard, TILE_M);
         const int m0 = mb * TILE_M + (int)cta_rank * BM, n0 = nb * BN;
         const bool own = COMM == COMM_AG && shard == cm.rank;
         if (COMM == COMM_AG && !own && shard != ready_shard) {
@@ -253,7 +254,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const uint32_t fb = map_to_cta(full_bar(s), 0);
             if (cta_rank == 0) mbar_expect_tx(full_bar(s), 2 * (L::A_BYTES + L::B_BYTES));
             const int nB = n0 + (int)cta_rank * BN_CTA;
-            if (!A_MN) {
+            if (own) {
+              tma_load_2d_pair(a_dst, &tmA2, kb * BK, m0 - cm.rank * cm.rows_per_rank, fb);
+            } else if (!A_MN) {
               tma_load_2d_pair(a_dst, &tmA, kb * BK, m0, fb);
             } else {
 #pragma unroll
@@ -346,7 +349,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int unit = wid; unit < num_units; unit += wstride, ++tile_iter) {
       const int tile = unit / splits;
       int mb, nb, shard;
-      tile_coords_comm<COMM>(p, cm, tile, mb, nb, shard);
+      tile_coords_comm<COMM>(p, cm, tile, mb, nb, shard, TILE_M);
       const int m0 = mb * TILE_M + (int)cta_rank * BM, n0 = nb * BN;
       const uint32_t buf = tile_iter & 1, bph = (tile_iter >> 1) & 1;
       bool ok = !dead && mbar_wait(tfull_bar(buf), bph, abort_flag, p.status);
@@ -546,7 +549,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int unit = wid; unit < num_units; unit += wstride) {
       const int tile = unit / splits;
       int mb, nb, shard;
-      tile_coords_comm<COMM>(p, cm, tile, mb, nb, shard);
+      tile_coords_comm<COMM>(p, cm, tile, mb, nb, shard, TILE_M);
       const int m0 = mb * TILE_M + (int)cta_rank * BM, n0 = nb * BN;
       const int dst_row = COMM == COMM_RS ? cm.rank * cm.rows_per_rank + (m0 - shard * cm.rows_per_rank) : m0;
       const int dst_map = COMM == COMM_RS ? shard : 0;
@@ -922,8 +925,12 @@ namespace {
 
 template <int COMM>
 int dispatch_comm(int BN, int b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmA2, const GemmParams& p,
-                  const CommParams& c, cudaStream_t s, const OutMaps* om = nullptr, int max_ctas = 0) {
+                  const CommParams& c, cudaStream_t s, const OutMaps* om = nullptr, int max_ctas = 0, bool pair = false) {
   const int ctas = (max_ctas > 0 && max_ctas < sm_count()) ? max_ctas : sm_count();
+  if (pair) {
+    return b_mn ? launch_gemm<256, false, true, COMM, true>(tmA, tmB, p, ctas, s, &tmA2, &c, om)
+                : launch_gemm<256, false, false, COMM, true>(tmA, tmB, p, ctas, s, &tmA2, &c, om);
+  }
   if (BN == 256) {
     return b_mn ? launch_gemm<256, false, true, COMM>(tmA, tmB, p, ctas, s, &tmA2, &c, om)
                 : launch_gemm<256, false, false, COMM>(tmA, tmB, p, ctas, s, &tmA2, &c, om);
@@ -932,9 +939,19 @@ int dispatch_comm(int BN, int b_mn, const CUtensorMap& tmA, const CUtensorMap& t
               : launch_gemm<128, false, false, COMM>(tmA, tmB, p, ctas, s, &tmA2, &c, om);
 }
 
-int comm_grid(int M, int N, int BN) {
+int comm_grid(int M, int N, int BN, bool pair = false) {
+  if (pair) {   // CTAs of the pair launch: two per 256 x 256 tile, at most one pair per two SMs
+    const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+    const int pairs = sm_count() / 2;
+    return 2 * (tiles < pairs ? tiles : pairs);
+  }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   return tiles < sm_count() ? tiles : sm_count();
+}
+
+// CTA pairs for a fused kernel: 256-wide tiles, every pair's 256 rows inside one shard, at least one wave of pairs
+bool comm_pair(int M, int N, int rows_per_rank) {
+  return N >= 256 && rows_per_rank % (2 * BM) == 0 && (long long)(M / (2 * BM)) * ((N + 255) / 256) >= sm_count() / 2;
 }
 
 long long wait_cycles_of(int wait_ms) { return (long long)(wait_ms > 0 ? wait_ms : 10000) * 1900000LL; }
@@ -961,13 +978,14 @@ ELFA_API int elfa_gemm_ag(const void* x_local, long long ldx, const unsigned lon
   unsigned int* st = status_word();
   ELFA_REQUIRE(st != nullptr, "gemm_ag: no status word");
   const int rows = M / world;
-  const int BN = (N >= 256 && (long long)(M / BM) * ((N + 255) / 256) >= sm_count()) ? 256 : 128;
+  const bool pair = comm_pair(M, N, rows);
+  const int BN = (pair || (N >= 256 && (long long)(M / BM) * ((N + 255) / 256) >= sm_count())) ? 256 : 128;
   CUtensorMap tmA, tmA2, tmB;
   int rc = cached_tmap_bf16(&tmA, reinterpret_cast<const void*>(peer_xfull[rank]), (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, BK);
   if (rc != ELFA_OK) return rc;
   rc = cached_tmap_bf16(&tmA2, x_local, (uint64_t)rows, (uint64_t)K, (uint64_t)ldx, BM, BK);
   if (rc != ELFA_OK) return rc;
-  if (!b_mn_major) rc = cached_tmap_bf16(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN, BK);
+  if (!b_mn_major) rc = cached_tmap_bf16(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, pair ? BN / 2 : BN, BK);
   else rc = cached_tmap_bf16(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, 64);
   if (rc != ELFA_OK) return rc;
   GemmParams p{};
@@ -999,10 +1017,10 @@ ELFA_API int elfa_gemm_ag(const void* x_local, long long ldx, const unsigned lon
     c.peer_flags[i] = peer_flags[i];
   }
   c.my_flags = static_cast<const unsigned int*>(my_flags);
-  *arrivals_io += (unsigned)comm_grid(M, N, BN);        // every CTA of a source bumps the counter once
+  *arrivals_io += (unsigned)comm_grid(M, N, BN, pair);        // every CTA of a source bumps the counter once
   c.flag_target = *arrivals_io;
   OutMaps om{};
-  return dispatch_comm<COMM_AG>(BN, b_mn_major, tmA, tmB, tmA2, p, c, static_cast<cudaStream_t>(stream), &om);
+  return dispatch_comm<COMM_AG>(BN, b_mn_major, tmA, tmB, tmA2, p, c, static_cast<cudaStream_t>(stream), &om, 0, pair);
 }
 
 // out[M/world, N] = reduce_scatter_rows(A[M,K] * op(B)): partial tiles travel to the owner's receive
@@ -1018,11 +1036,12 @@ ELFA_API int elfa_gemm_rs(const void* A, long long lda, const void* B, long long
   unsigned int* st = status_word();
   ELFA_REQUIRE(st != nullptr, "gemm_rs: no status word");
   const int rows = M / world;
-  const int BN = (N >= 256 && (long long)(M / BM) * ((N + 255) / 256) >= sm_count()) ? 256 : 128;
+  const bool pair = comm_pair(M, N, rows) && (max_ctas <= 0 || max_ctas >= sm_count());
+  const int BN = (pair || (N >= 256 && (long long)(M / BM) * ((N + 255) / 256) >= sm_count())) ? 256 : 128;
   CUtensorMap tmA, tmB;
   int rc = cached_tmap_bf16(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, BK);
   if (rc != ELFA_OK) return rc;
-  if (!b_mn_major) rc = cached_tmap_bf16(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN, BK);
+  if (!b_mn_major) rc = cached_tmap_bf16(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, pair ? BN / 2 : BN, BK);
   else rc = cached_tmap_bf16(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, 64);
   if (rc != ELFA_OK) return rc;
   GemmParams p{};
@@ -1047,5 +1066,5 @@ ELFA_API int elfa_gemm_rs(const void* A, long long lda, const void* B, long long
     if (rc != ELFA_OK) return rc;
   }
   // max_ctas < SM count leaves SMs to a kernel on another stream (a weight-gradient GEMM next to this comm-bound kernel)
-  return dispatch_comm<COMM_RS>(BN, b_mn_major, tmA, tmB, tmA, p, c, static_cast<cudaStream_t>(stream), &om, max_ctas);
+  return dispatch_comm<COMM_RS>(BN, b_mn_major, tmA, tmB, tmA, p, c, static_cast<cudaStream_t>(stream), &om, max_ctas, pair);
 }

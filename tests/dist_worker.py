@@ -46,7 +46,7 @@ def mode_fused(pc, dev):
     torch.manual_seed(1234)
     worst = 0.0
     for it, (Ml, K, N) in enumerate([(128, 256, 512), (256, 512, 1376), (512, 1024, 1536), (256, 512, 1376), (128, 256, 512),
-                                     (512, 4096, 1536)]):
+                                     (512, 4096, 1536), (2048, 1024, 2560), (1024, 512, 4096)]):   # the last two: CTA-pair tiles
         g = torch.Generator(device="cpu").manual_seed(100 + it)
         x_all = torch.randn(Ml * world, K, generator=g).to(torch.bfloat16).to(dev)
         w = (torch.randn(K, N, generator=g) * 0.05).to(torch.bfloat16).to(dev)
