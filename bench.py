@@ -230,6 +230,7 @@ def main() -> int:
             "mfu_of_measured_sustained_bf16": value * flops / (peak * world),
             "model_tflops_per_gpu": value * flops / world / 1e12,
             "loss": loss, "device_status": st,
+            "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
         }
         if args.layers or args.global_batch:
             out["invalid"] = "layer count or global batch overridden for debugging"
