@@ -39,7 +39,8 @@ def find_nvcc() -> str:
 
 
 def _newest_header_mtime() -> float:
-    return max((p.stat().st_mtime for p in CSRC.glob("*.h*")), default=0.0)
+    headers = [p for pat in ("*.h", "*.hpp", "*.cuh") for p in CSRC.glob(pat)]
+    return max((p.stat().st_mtime for p in headers), default=0.0)
 
 
 def _compile(nvcc: str, src: Path, obj: Path, verbose: bool) -> str:

@@ -402,6 +402,11 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -420,16 +425,23 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&t);
 }
+// tanh-form GELU with the hardware tanh (one special-function instruction per element, relative error
+// 2^-11, below the bf16 rounding of the result); the library tanhf costs two plus a division.
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float k = 0.7978845608028654f;
-  float u = k * (x + 0.044715f * x * x * x);
-  return 0.5f * x * (1.0f + tanhf(u));
+  const float u = k * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.0f + tanh_fast(u));
 }
 __device__ __forceinline__ float dgelu_tanh(float x) {
   const float k = 0.7978845608028654f;
-  float x2 = x * x;
-  float u = k * (x + 0.044715f * x * x2);
-  float t = tanhf(u);
+  const float x2 = x * x;
+  const float u = k * (x + 0.044715f * x * x2);
+  const float t = tanh_fast(u);
   return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * k * (1.0f + 3.0f * 0.044715f * x2);
 }
 __device__ __forceinline__ float warp_sum(float v) {

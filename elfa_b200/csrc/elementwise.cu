@@ -42,18 +42,33 @@ __global__ void __launch_bounds__(256) ew_kernel(const __nv_bfloat16* __restrict
                                                  __nv_bfloat16* __restrict__ out, long long n, float alpha) {
   const long long nvec = n / 8;
   const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
-    const uint4 av = reinterpret_cast<const uint4*>(a)[i];
-    uint4 bv = make_uint4(0, 0, 0, 0);
-    if (BINARY) bv = reinterpret_cast<const uint4*>(b)[i];
-    const uint32_t* pa = reinterpret_cast<const uint32_t*>(&av);
-    const uint32_t* pb = reinterpret_cast<const uint32_t*>(&bv);
-    uint4 o;
-    uint32_t* po = reinterpret_cast<uint32_t*>(&o);
+  constexpr int U = 4;   // 16-byte loads in flight per thread and operand
+  for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < nvec; i0 += U * stride) {
+    uint4 av[U], bv[U];
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      po[j] = pack_bf16(apply<OP>(bf16_lo(pa[j]), bf16_lo(pb[j]), alpha), apply<OP>(bf16_hi(pa[j]), bf16_hi(pb[j]), alpha));
-    reinterpret_cast<uint4*>(out)[i] = o;
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      av[u] = make_uint4(0, 0, 0, 0);
+      bv[u] = make_uint4(0, 0, 0, 0);
+      if (i < nvec) {
+        av[u] = reinterpret_cast<const uint4*>(a)[i];
+        if (BINARY) bv[u] = reinterpret_cast<const uint4*>(b)[i];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < nvec) {
+        const uint32_t* pa = reinterpret_cast<const uint32_t*>(&av[u]);
+        const uint32_t* pb = reinterpret_cast<const uint32_t*>(&bv[u]);
+        uint4 o;
+        uint32_t* po = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          po[j] = pack_bf16(apply<OP>(bf16_lo(pa[j]), bf16_lo(pb[j]), alpha), apply<OP>(bf16_hi(pa[j]), bf16_hi(pb[j]), alpha));
+        reinterpret_cast<uint4*>(out)[i] = o;
+      }
+    }
   }
   // tail (n not a multiple of 8)
   const long long tail0 = nvec * 8;

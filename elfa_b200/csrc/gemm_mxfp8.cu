@@ -415,8 +415,8 @@ int sf_tmap(CUtensorMap* out, const void* base, uint64_t atoms, uint32_t box_ato
 }
 
 // ---- quantiser ------------------------------------------------------------------------------------
-// One thread per 32-element block of a row: payload e4m3, scale byte into the atom layout, and an
-// optional bf16 copy of the dequantised values (what a fake-quantised bf16 GEMM would multiply).
+// Per 32-element block of a row: payload e4m3, scale byte into the atom layout, and an optional bf16
+// copy of the dequantised values (what a fake-quantised bf16 GEMM would multiply).
 __device__ __forceinline__ uint8_t mx_scale_q(float amax, float* scale, float* inv) {
   int e = (int)((__float_as_uint(amax) >> 23) & 0xff) - 127 - 8;
   if (amax == 0.f) e = -127;
@@ -427,59 +427,61 @@ __device__ __forceinline__ uint8_t mx_scale_q(float amax, float* scale, float* i
   return (uint8_t)(e + 127);
 }
 
+// Four adjacent lanes share one 32-element block: a thread owns 8 elements (one 16-byte load, one 8-byte
+// payload store, one 16-byte store of the dequantised copy, all contiguous across the warp), the block's
+// maximum comes from two shuffles, and the first lane of the four writes the scale byte.
 __global__ void __launch_bounds__(256) mxfp8_quantize_gemm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                                                                   uint8_t* __restrict__ payload, uint8_t* __restrict__ sf,
                                                                   __nv_bfloat16* __restrict__ deq, int rows, int cols, int kt,
                                                                   int b_atoms) {
-  const int bpr = cols / 32;
-  const long long nblocks = (long long)rows * bpr;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long blk = (long long)blockIdx.x * blockDim.x + threadIdx.x; blk < nblocks; blk += stride) {
-    const int r = (int)(blk / bpr), kb = (int)(blk - (long long)r * bpr);
-    const uint4* src = reinterpret_cast<const uint4*>(x + (long long)r * ldx + kb * 32);
-    float f[32];
+  const uint32_t vpr = (uint32_t)cols / 8;             // vectors per row, a multiple of 4
+  const uint32_t nvec = (uint32_t)rows * vpr;
+  const uint32_t stride = gridDim.x * blockDim.x;      // a multiple of 32: lane % 4 == vector % 4
+  const uint32_t lane = threadIdx.x & 31;
+  for (uint32_t v = blockIdx.x * blockDim.x + threadIdx.x; v - lane < nvec; v += stride) {
+    const bool ok = v < nvec;
+    const uint32_t r = ok ? v / vpr : 0, c8 = ok ? v - r * vpr : 0;
+    uint4 q = make_uint4(0, 0, 0, 0);
+    if (ok) q = *reinterpret_cast<const uint4*>(x + (long long)r * ldx + c8 * 8);
+    const uint32_t pv[4] = {q.x, q.y, q.z, q.w};
+    float f[8];
     float amax = 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint4 v = src[i];
-      const uint32_t pv[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        f[i * 8 + 2 * j] = bf16_lo(pv[j]);
-        f[i * 8 + 2 * j + 1] = bf16_hi(pv[j]);
-        amax = fmaxf(amax, fmaxf(fabsf(f[i * 8 + 2 * j]), fabsf(f[i * 8 + 2 * j + 1])));
-      }
+    for (int j = 0; j < 4; ++j) {
+      f[2 * j] = bf16_lo(pv[j]);
+      f[2 * j + 1] = bf16_hi(pv[j]);
+      amax = fmaxf(amax, fmaxf(fabsf(f[2 * j]), fabsf(f[2 * j + 1])));
     }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     float sc, inv;
     const uint8_t sb = mx_scale_q(amax, &sc, &inv);
-    uint32_t w[8];
+    uint32_t w[2];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 2; ++i) {
       uint32_t acc = 0;
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc |= (uint32_t)__nv_cvt_float_to_fp8(f[i * 4 + j] * inv, __NV_SATFINITE, __NV_E4M3) << (8 * j);
       w[i] = acc;
     }
-    uint4* dst = reinterpret_cast<uint4*>(payload + (long long)r * cols + kb * 32);
-    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-    // atom order: A operand [row block][K tile]; B operand [K tile][row block (+1 pad)]
-    const long long atom = b_atoms > 0 ? (long long)(kb >> 2) * b_atoms + (r >> 7) : (long long)(r >> 7) * kt + (kb >> 2);
-    sf[atom * SF_ATOM + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (kb & 3)] = sb;
-    if (deq != nullptr) {
-      uint4* dd = reinterpret_cast<uint4*>(deq + (long long)r * cols + kb * 32);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
+    if (ok) {
+      *reinterpret_cast<uint2*>(payload + (long long)r * cols + c8 * 8) = make_uint2(w[0], w[1]);
+      const uint32_t kb = c8 >> 2;
+      if ((c8 & 3) == 0) {
+        // atom order: A operand [row block][K tile]; B operand [K tile][row block (+1 pad)]
+        const long long atom = b_atoms > 0 ? (long long)(kb >> 2) * b_atoms + (r >> 7) : (long long)(r >> 7) * kt + (kb >> 2);
+        sf[atom * SF_ATOM + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (kb & 3)] = sb;
+      }
+      if (deq != nullptr) {
         uint32_t o[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const uint32_t word = w[i * 2 + (j >> 1)];
-          const uint32_t two = (word >> (16 * (j & 1))) & 0xffffu;
+          const uint32_t two = (w[j >> 1] >> (16 * (j & 1))) & 0xffffu;
           const float lo = __half2float(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)(two & 0xff), __NV_E4M3))) * sc;
           const float hi = __half2float(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)(two >> 8), __NV_E4M3))) * sc;
           o[j] = pack_bf16(lo, hi);
         }
-        dd[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4*>(deq + (long long)r * cols + c8 * 8) = make_uint4(o[0], o[1], o[2], o[3]);
       }
     }
   }
@@ -503,8 +505,9 @@ ELFA_API int elfa_mxfp8_quantize_gemm(const void* x, long long ldx, void* payloa
                                       int b_operand, void* stream) {
   ELFA_REQUIRE(x && payload && sf && rows > 0 && cols > 0, "mxfp8_quantize_gemm: bad arguments");
   ELFA_REQUIRE(cols % 32 == 0 && ldx % 8 == 0, "mxfp8_quantize_gemm: cols must be a multiple of 32 and the pitch of 8");
-  const long long nb = (long long)rows * (cols / 32);
-  const int grid = (int)((nb + 255) / 256 < 148 * 16 ? (nb + 255) / 256 : 148 * 16);
+  const long long nv = (long long)rows * (cols / 8);
+  ELFA_REQUIRE(nv < (1ll << 31) - (1 << 20), "mxfp8_quantize_gemm: tensor too large (2^34 elements at most)");
+  const int grid = (int)((nv + 255) / 256 < 148 * 16 ? (nv + 255) / 256 : 148 * 16);
   mxfp8_quantize_gemm_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), ldx, static_cast<uint8_t*>(payload), static_cast<uint8_t*>(sf),
       static_cast<__nv_bfloat16*>(deq), rows, cols, (cols + 127) / 128, b_operand ? (rows + 127) / 128 + 1 : 0);

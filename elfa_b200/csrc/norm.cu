@@ -16,71 +16,85 @@ namespace {
 
 constexpr int NORM_MAX_VEC = 16;  // uint4 (8 x bf16) per thread held in registers
 
-// TPR = threads per row (32: one warp per row; 256: one CTA per row).
-template <int TPR, bool RMS, bool HAS_RES>
-__global__ void __launch_bounds__(256) norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+__device__ __forceinline__ uint4 ld_or_zero(const uint4* p, bool ok) {
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (ok) v = *p;
+  return v;
+}
+
+// TPR = threads per row (32 ... 256, a CTA of 256 threads holds 256 / TPR rows), NV = 16-byte vectors per
+// thread. Every load of a row is issued before the first use (NV independent loads per thread in
+// flight), then the statistics, then the output pass from registers: x is read once.
+template <int TPR, int NV, bool RMS, bool HAS_RES>
+__global__ void __launch_bounds__(256, NV <= 8 ? (HAS_RES ? 2 : 3) : 1) norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                                                        const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b,
                                                        __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ sum_out,
                                                        float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows,
                                                        int D, float eps) {
   constexpr int ROWS_PER_BLOCK = 256 / TPR;
+  constexpr int ROW_WARPS = TPR / 32;
   __shared__ float red[2][8];
   const int t = threadIdx.x % TPR;
   const int row = blockIdx.x * ROWS_PER_BLOCK + threadIdx.x / TPR;
-  if (TPR == 32 && row >= rows) return;
+  const bool valid = row < rows;
   const int nvec = D / 8;
-  const uint4* xr = reinterpret_cast<const uint4*>(x + (long long)row * D);
-  const uint4* rr = HAS_RES ? reinterpret_cast<const uint4*>(res + (long long)row * D) : nullptr;
-  uint4 buf[NORM_MAX_VEC];
+  const long long off = (long long)(valid ? row : 0) * D;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + off);
+  uint4 buf[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) buf[i] = ld_or_zero(xr + t + i * TPR, valid && t + i * TPR < nvec);
+  if (HAS_RES) {
+    const uint4* rr = reinterpret_cast<const uint4*>(res + off);
+    uint4 rb[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) rb[i] = ld_or_zero(rr + t + i * TPR, valid && t + i * TPR < nvec);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      uint32_t* pv = reinterpret_cast<uint32_t*>(&buf[i]);
+      const uint32_t* pr = reinterpret_cast<const uint32_t*>(&rb[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) pv[j] = pack_bf16(bf16_lo(pv[j]) + bf16_lo(pr[j]), bf16_hi(pv[j]) + bf16_hi(pr[j]));
+      if (valid && t + i * TPR < nvec) reinterpret_cast<uint4*>(sum_out + off)[t + i * TPR] = buf[i];
+    }
+  }
   float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-  for (int i = 0; i < NORM_MAX_VEC; ++i) {
-    const int vi = t + i * TPR;
-    if (vi < nvec) {
-      uint4 v = xr[vi];
-      uint32_t* pv = reinterpret_cast<uint32_t*>(&v);
-      if (HAS_RES) {
-        uint4 r = rr[vi];
-        const uint32_t* pr = reinterpret_cast<const uint32_t*>(&r);
+  for (int i = 0; i < NV; ++i) {
+    const uint32_t* pv = reinterpret_cast<const uint32_t*>(&buf[i]);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) pv[j] = pack_bf16(bf16_lo(pv[j]) + bf16_lo(pr[j]), bf16_hi(pv[j]) + bf16_hi(pr[j]));
-        reinterpret_cast<uint4*>(sum_out + (long long)row * D)[vi] = v;
-      }
-      buf[i] = v;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float a = bf16_lo(pv[j]), c = bf16_hi(pv[j]);
-        s1 += a + c;
-        s2 += a * a + c * c;
-      }
+    for (int j = 0; j < 4; ++j) {
+      const float a = bf16_lo(pv[j]), c = bf16_hi(pv[j]);
+      s1 += a + c;
+      s2 += a * a + c * c;
     }
   }
   s1 = warp_sum(s1);
   s2 = warp_sum(s2);
-  if (TPR > 32) {
+  if (ROW_WARPS > 1) {
     const int wid = threadIdx.x >> 5;
     if ((threadIdx.x & 31) == 0) { red[0][wid] = s1; red[1][wid] = s2; }
     __syncthreads();
+    const int w0 = (threadIdx.x / TPR) * ROW_WARPS;
     s1 = 0.f; s2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { s1 += red[0][i]; s2 += red[1][i]; }
+    for (int i = 0; i < ROW_WARPS; ++i) { s1 += red[0][w0 + i]; s2 += red[1][w0 + i]; }
   }
   const float inv_d = 1.0f / (float)D;
   float mean = RMS ? 0.f : s1 * inv_d;
   float var = s2 * inv_d - mean * mean;
   var = fmaxf(var, 0.f);
   const float rstd = rsqrtf(var + eps);
-  if (t == 0) {
+  if (t == 0 && valid) {
     if (mean_out) mean_out[row] = mean;
     if (rstd_out) rstd_out[row] = rstd;
   }
   const uint4* wv = reinterpret_cast<const uint4*>(w);
   const uint4* bv = reinterpret_cast<const uint4*>(b);
-  uint4* yr = reinterpret_cast<uint4*>(y + (long long)row * D);
+  uint4* yr = reinterpret_cast<uint4*>(y + off);
 #pragma unroll
-  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+  for (int i = 0; i < NV; ++i) {
     const int vi = t + i * TPR;
-    if (vi < nvec) {
+    if (valid && vi < nvec) {
       const uint32_t* pv = reinterpret_cast<const uint32_t*>(&buf[i]);
       uint4 wq = wv[vi];
       const uint32_t* pw = reinterpret_cast<const uint32_t*>(&wq);
@@ -100,93 +114,115 @@ __global__ void __launch_bounds__(256) norm_fwd_kernel(const __nv_bfloat16* __re
   }
 }
 
+// two bf16 values of one 32-bit word as a packed fp32 pair
+__device__ __forceinline__ uint64_t bf16x2_to_f32x2(uint32_t u) { return pack_f32x2(bf16_lo(u), bf16_hi(u)); }
+
 // Backward. One CTA works on one row at a time (rows strided over the grid); thread t owns the 8
 // columns of vector t (+ i*blockDim for D > 8192), so its share of dw/db lives in registers for
 // the whole kernel and is written once, as row blockIdx.x of the [gridDim.x, D] partial buffers.
-// The two per-row scalars are reduced across warps through a double-buffered shared array.
+// The two per-row scalars are reduced across warps through a double-buffered shared array (one
+// value per warp, summed again by a warp reduction). The next row's dy / x / residual gradient are
+// requested before the reduction of the current row (V == 1), so the loads overlap the barrier and
+// the output pass. The kernel is bound by instruction issue, not by memory, so the arithmetic runs
+// on packed fp32 pairs and dy / x stay packed in registers (unpacked twice, never kept as fp32).
 template <bool RMS, int V>
 __global__ void __launch_bounds__(1024) norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                                         const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean,
                                                         const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ dres,
                                                         __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_part,
                                                         float* __restrict__ db_part, int rows, int D) {
+  constexpr bool PREFETCH = V == 1;
   __shared__ float red[2][2][32];
   const int t = threadIdx.x, lane = t & 31, wid = t >> 5, nt = blockDim.x, nwarps = nt >> 5;
   const int nvec = D / 8;
-  float accw[V][8], accb[V][8], wf[V][8];
+  uint64_t accw[V][4], accb[V][4], wf[V][4];
   const uint4* wv = reinterpret_cast<const uint4*>(w);
 #pragma unroll
   for (int i = 0; i < V; ++i) {
-    const int vi = t + i * nt;
-    uint4 wq = make_uint4(0, 0, 0, 0);
-    if (vi < nvec) wq = wv[vi];
+    const uint4 wq = ld_or_zero(wv + t + i * nt, t + i * nt < nvec);
     const uint32_t* pw = reinterpret_cast<const uint32_t*>(&wq);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      wf[i][2 * j] = bf16_lo(pw[j]);
-      wf[i][2 * j + 1] = bf16_hi(pw[j]);
+      wf[i][j] = bf16x2_to_f32x2(pw[j]);
+      accw[i][j] = 0ull;
+      accb[i][j] = 0ull;
     }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { accw[i][j] = 0.f; accb[i][j] = 0.f; }
   }
   const float inv_d = 1.0f / (float)D;
+  uint4 dn[V], xn[V], rn[V];
+  float mu_n = 0.f, rs_n = 0.f;
+  auto fetch = [&](int row) {
+    const bool ok = row < rows;
+    const long long off = (long long)(ok ? row : 0) * D;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const int vi = t + i * nt;
+      dn[i] = ld_or_zero(reinterpret_cast<const uint4*>(dy + off) + vi, ok && vi < nvec);
+      xn[i] = ld_or_zero(reinterpret_cast<const uint4*>(x + off) + vi, ok && vi < nvec);
+      rn[i] = ld_or_zero(reinterpret_cast<const uint4*>(dres + off) + vi, ok && dres != nullptr && vi < nvec);
+    }
+    if (ok) {
+      mu_n = RMS ? 0.f : mean[row];
+      rs_n = rstd[row];
+    }
+  };
+  if (PREFETCH) fetch(blockIdx.x);
   int iter = 0;
   for (int row = blockIdx.x; row < rows; row += gridDim.x, ++iter) {
-    const uint4* dyr = reinterpret_cast<const uint4*>(dy + (long long)row * D);
-    const uint4* xr = reinterpret_cast<const uint4*>(x + (long long)row * D);
-    const float mu = RMS ? 0.f : mean[row];
-    const float rs = rstd[row];
-    float g[V][8], xh[V][8];
-    float c1 = 0.f, c2 = 0.f;
+    if (!PREFETCH) fetch(row);
+    uint4 dq[V], xq[V], rq[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) { dq[i] = dn[i]; xq[i] = xn[i]; rq[i] = rn[i]; }
+    const float rs = rs_n;
+    const uint64_t rs2 = pack_f32x2(rs, rs), nmurs2 = pack_f32x2(-mu_n * rs, -mu_n * rs);
+    if (PREFETCH) fetch(row + gridDim.x);
+    // a zero-filled vector (beyond D) has dy = 0, so every product below is 0 whatever its x-hat is
+    uint64_t s1 = 0ull, s2 = 0ull;
 #pragma unroll
     for (int i = 0; i < V; ++i) {
-      const int vi = t + i * nt;
-      if (vi < nvec) {
-        const uint4 dq = dyr[vi], xq = xr[vi];
-        const uint32_t* pd = reinterpret_cast<const uint32_t*>(&dq);
-        const uint32_t* px = reinterpret_cast<const uint32_t*>(&xq);
+      const uint32_t* pd = reinterpret_cast<const uint32_t*>(&dq[i]);
+      const uint32_t* px = reinterpret_cast<const uint32_t*>(&xq[i]);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float d0 = bf16_lo(pd[j]), d1 = bf16_hi(pd[j]);
-          const float x0 = (bf16_lo(px[j]) - mu) * rs, x1 = (bf16_hi(px[j]) - mu) * rs;
-          accw[i][2 * j] += d0 * x0;
-          accw[i][2 * j + 1] += d1 * x1;
-          accb[i][2 * j] += d0;
-          accb[i][2 * j + 1] += d1;
-          const float g0 = d0 * wf[i][2 * j], g1 = d1 * wf[i][2 * j + 1];
-          g[i][2 * j] = g0; g[i][2 * j + 1] = g1;
-          xh[i][2 * j] = x0; xh[i][2 * j + 1] = x1;
-          c1 += g0 + g1;
-          c2 += g0 * x0 + g1 * x1;
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { g[i][j] = 0.f; xh[i][j] = 0.f; }
+      for (int j = 0; j < 4; ++j) {
+        const uint64_t d2 = bf16x2_to_f32x2(pd[j]);
+        const uint64_t xh2 = fma_f32x2(bf16x2_to_f32x2(px[j]), rs2, nmurs2);
+        accw[i][j] = fma_f32x2(d2, xh2, accw[i][j]);
+        accb[i][j] = add_f32x2(accb[i][j], d2);
+        const uint64_t g2 = mul_f32x2(d2, wf[i][j]);
+        s1 = add_f32x2(s1, g2);
+        s2 = fma_f32x2(g2, xh2, s2);
       }
     }
-    c1 = warp_sum(c1);
-    c2 = warp_sum(c2);
+    float c1, c2, hi1, hi2;
+    unpack_f32x2(s1, c1, hi1);
+    unpack_f32x2(s2, c2, hi2);
+    c1 = warp_sum(c1 + hi1);
+    c2 = warp_sum(c2 + hi2);
     if (lane == 0) { red[iter & 1][0][wid] = c1; red[iter & 1][1][wid] = c2; }
     __syncthreads();
-    c1 = 0.f; c2 = 0.f;
-    for (int k = 0; k < nwarps; ++k) { c1 += red[iter & 1][0][k]; c2 += red[iter & 1][1][k]; }
+    c1 = warp_sum(lane < nwarps ? red[iter & 1][0][lane] : 0.f);
+    c2 = warp_sum(lane < nwarps ? red[iter & 1][1][lane] : 0.f);
     c1 = RMS ? 0.f : c1 * inv_d;
     c2 *= inv_d;
+    const uint64_t nc1 = pack_f32x2(-c1, -c1), nc2 = pack_f32x2(-c2, -c2);
     uint4* dxr = reinterpret_cast<uint4*>(dx + (long long)row * D);
-    const uint4* drr = dres ? reinterpret_cast<const uint4*>(dres + (long long)row * D) : nullptr;
 #pragma unroll
     for (int i = 0; i < V; ++i) {
       const int vi = t + i * nt;
       if (vi < nvec) {
-        uint4 rq = make_uint4(0, 0, 0, 0);
-        if (drr) rq = drr[vi];
-        const uint32_t* pr = reinterpret_cast<const uint32_t*>(&rq);
+        const uint32_t* pd = reinterpret_cast<const uint32_t*>(&dq[i]);
+        const uint32_t* px = reinterpret_cast<const uint32_t*>(&xq[i]);
+        const uint32_t* pr = reinterpret_cast<const uint32_t*>(&rq[i]);
         uint4 o;
         uint32_t* po = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float lo = rs * (g[i][2 * j] - c1 - xh[i][2 * j] * c2) + bf16_lo(pr[j]);
-          const float hi = rs * (g[i][2 * j + 1] - c1 - xh[i][2 * j + 1] * c2) + bf16_hi(pr[j]);
+          const uint64_t g2 = mul_f32x2(bf16x2_to_f32x2(pd[j]), wf[i][j]);
+          const uint64_t xh2 = fma_f32x2(bf16x2_to_f32x2(px[j]), rs2, nmurs2);
+          // dx = rs * (g - c1 - xhat * c2) + dres
+          const uint64_t o2 = fma_f32x2(fma_f32x2(xh2, nc2, add_f32x2(g2, nc1)), rs2, bf16x2_to_f32x2(pr[j]));
+          float lo, hi;
+          unpack_f32x2(o2, lo, hi);
           po[j] = pack_bf16(lo, hi);
         }
         dxr[vi] = o;
@@ -197,27 +233,46 @@ __global__ void __launch_bounds__(1024) norm_bwd_kernel(const __nv_bfloat16* __r
   for (int i = 0; i < V; ++i) {
     const int vi = t + i * nt;
     if (vi < nvec) {
+      float a[8], c[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        unpack_f32x2(accw[i][j], a[2 * j], a[2 * j + 1]);
+        unpack_f32x2(accb[i][j], c[2 * j], c[2 * j + 1]);
+      }
       float4* pw = reinterpret_cast<float4*>(dw_part + (long long)blockIdx.x * D + vi * 8);
-      pw[0] = make_float4(accw[i][0], accw[i][1], accw[i][2], accw[i][3]);
-      pw[1] = make_float4(accw[i][4], accw[i][5], accw[i][6], accw[i][7]);
+      pw[0] = make_float4(a[0], a[1], a[2], a[3]);
+      pw[1] = make_float4(a[4], a[5], a[6], a[7]);
       if (!RMS) {
         float4* pb = reinterpret_cast<float4*>(db_part + (long long)blockIdx.x * D + vi * 8);
-        pb[0] = make_float4(accb[i][0], accb[i][1], accb[i][2], accb[i][3]);
-        pb[1] = make_float4(accb[i][4], accb[i][5], accb[i][6], accb[i][7]);
+        pb[0] = make_float4(c[0], c[1], c[2], c[3]);
+        pb[1] = make_float4(c[4], c[5], c[6], c[7]);
       }
     }
   }
 }
 
-// out[c] (+)= sum_p part[p, c]; out is bf16 or fp32.
+// out[c] (+)= sum_p part[p, c] in a fixed order; out is bf16 or fp32. grid (ceil(D / 32), 1 or 2): blockIdx.y
+// selects (part0, out0) or (part1, out1); block (32, 16): thread (c, r) adds rows r, r + 16, ... of column c.
 template <typename OutT>
-__global__ void reduce_partials_kernel(const float* __restrict__ part, OutT* __restrict__ out, int P, int D, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= D) return;
+__global__ void __launch_bounds__(512) reduce_partials_kernel(const float* __restrict__ part0, const float* __restrict__ part1,
+                                                              OutT* __restrict__ out0, OutT* __restrict__ out1, int P, int D,
+                                                              int accumulate) {
+  __shared__ float red[16][33];
+  const float* part = blockIdx.y ? part1 : part0;
+  OutT* out = blockIdx.y ? out1 : out0;
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
-  for (int p = 0; p < P; ++p) s += part[(long long)p * D + c];
-  if (accumulate) s += (float)out[c];
-  out[c] = (OutT)s;
+  if (c < D)
+    for (int p = threadIdx.y; p < P; p += 16) s += part[(long long)p * D + c];
+  red[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < D) {
+    float tot = 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) tot += red[k][threadIdx.x];
+    if (accumulate) tot += (float)out[c];
+    out[c] = (OutT)tot;
+  }
 }
 
 }  // namespace
@@ -247,18 +302,25 @@ ELFA_API int elfa_norm_fwd(const void* x, const void* res, const void* w, const 
   const auto* B = static_cast<const __nv_bfloat16*>(b);
   auto* Y = static_cast<__nv_bfloat16*>(y);
   auto* S = static_cast<__nv_bfloat16*>(sum_out);
-  const bool warp_row = D <= 32 * NORM_MAX_VEC * 8;  // <= 4096: one warp per row, 16 independent 16-byte loads per lane
   const bool rms = kind == 1, has_res = res != nullptr;
-#define LAUNCH_FWD(TPR, RMS_, RES_)                                                                                     \
-  norm_fwd_kernel<TPR, RMS_, RES_><<<(rows + (256 / TPR) - 1) / (256 / TPR), 256, 0, s>>>(X, R, W, B, Y, S, mean_out, rstd_out, \
-                                                                                           rows, D, eps)
-  if (warp_row) {
-    if (rms) { if (has_res) LAUNCH_FWD(32, true, true); else LAUNCH_FWD(32, true, false); }
-    else { if (has_res) LAUNCH_FWD(32, false, true); else LAUNCH_FWD(32, false, false); }
-  } else {
-    if (rms) { if (has_res) LAUNCH_FWD(256, true, true); else LAUNCH_FWD(256, true, false); }
-    else { if (has_res) LAUNCH_FWD(256, false, true); else LAUNCH_FWD(256, false, false); }
-  }
+#define LAUNCH_FWD(TPR, NV)                                                                                                  \
+  do {                                                                                                                       \
+    const int grid = (rows + (256 / TPR) - 1) / (256 / TPR);                                                                 \
+    if (rms) {                                                                                                               \
+      if (has_res) norm_fwd_kernel<TPR, NV, true, true><<<grid, 256, 0, s>>>(X, R, W, B, Y, S, mean_out, rstd_out, rows, D, eps);  \
+      else norm_fwd_kernel<TPR, NV, true, false><<<grid, 256, 0, s>>>(X, R, W, B, Y, S, mean_out, rstd_out, rows, D, eps);    \
+    } else {                                                                                                                 \
+      if (has_res) norm_fwd_kernel<TPR, NV, false, true><<<grid, 256, 0, s>>>(X, R, W, B, Y, S, mean_out, rstd_out, rows, D, eps); \
+      else norm_fwd_kernel<TPR, NV, false, false><<<grid, 256, 0, s>>>(X, R, W, B, Y, S, mean_out, rstd_out, rows, D, eps);   \
+    }                                                                                                                        \
+  } while (0)
+  // at most 8 vectors (128 bytes) per thread up to D = 16384, so that several rows per SM are in flight
+  if (D <= 1024) LAUNCH_FWD(32, 4);
+  else if (D <= 2048) LAUNCH_FWD(32, 8);
+  else if (D <= 4096) LAUNCH_FWD(64, 8);
+  else if (D <= 8192) LAUNCH_FWD(128, 8);
+  else if (D <= 16384) LAUNCH_FWD(256, 8);
+  else LAUNCH_FWD(256, 16);
 #undef LAUNCH_FWD
   ELFA_CUDA(cudaGetLastError());
   ::elfa::count_launches(1);
@@ -266,9 +328,17 @@ ELFA_API int elfa_norm_fwd(const void* x, const void* res, const void* w, const 
 }
 
 // Number of partial rows the backward kernel writes for a given problem (scratch = 2 * P * D floats).
+static int norm_bwd_threads(int D) {
+  const int nvec = D / 8;
+  const int V = nvec > 1024 ? 2 : 1;
+  return ((nvec + V - 1) / V + 31) / 32 * 32;
+}
+
 ELFA_API int elfa_norm_bwd_partials(int rows, int D) {
-  (void)D;
-  return rows < 592 ? rows : 592;
+  int per_sm = 1024 / norm_bwd_threads(D > 0 ? D : 8);   // 64 registers per thread: 1024 threads resident per SM
+  per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
+  const int P = device_sm_count() * per_sm;
+  return rows < P ? rows : P;
 }
 
 // dx = norm backward (+ dres); dw/db (bf16 or fp32 per `grads_f32`) are accumulated when
@@ -286,24 +356,25 @@ ELFA_API int elfa_norm_bwd(const void* dy, const void* x, const void* w, const f
   float* dw_part = scratch;
   float* db_part = scratch + (long long)P * D;
   const bool rms = kind == 1;
-  const int nvec = D / 8;
-  const int V = nvec > 1024 ? 2 : 1;
-  int threads = ((nvec + V - 1) / V + 31) / 32 * 32;
-#define LAUNCH_BWD(RMS_, V_)                                                                                                    norm_bwd_kernel<RMS_, V_><<<P, threads, 0, s>>>(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),                                                   static_cast<const __nv_bfloat16*>(w), mean, rstd,                                                                             static_cast<const __nv_bfloat16*>(dres), static_cast<__nv_bfloat16*>(dx),                                                     dw_part, db_part, rows, D)
+  const int V = D / 8 > 1024 ? 2 : 1;
+  const int threads = norm_bwd_threads(D);
+#define LAUNCH_BWD(RMS_, V_)                                                                                                     \
+  norm_bwd_kernel<RMS_, V_><<<P, threads, 0, s>>>(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),   \
+                                                  static_cast<const __nv_bfloat16*>(w), mean, rstd,                              \
+                                                  static_cast<const __nv_bfloat16*>(dres), static_cast<__nv_bfloat16*>(dx),      \
+                                                  dw_part, db_part, rows, D)
   if (V == 1) { if (rms) LAUNCH_BWD(true, 1); else LAUNCH_BWD(false, 1); }
   else { if (rms) LAUNCH_BWD(true, 2); else LAUNCH_BWD(false, 2); }
 #undef LAUNCH_BWD
   ELFA_CUDA(cudaGetLastError());
-  const int blocks = (D + 255) / 256;
-  if (grads_f32) {
-    reduce_partials_kernel<float><<<blocks, 256, 0, s>>>(dw_part, static_cast<float*>(dw), P, D, accumulate);
-    if (!rms && db) reduce_partials_kernel<float><<<blocks, 256, 0, s>>>(db_part, static_cast<float*>(db), P, D, accumulate);
-  } else {
-    reduce_partials_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(dw_part, static_cast<__nv_bfloat16*>(dw), P, D, accumulate);
-    if (!rms && db)
-      reduce_partials_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(db_part, static_cast<__nv_bfloat16*>(db), P, D, accumulate);
-  }
+  const dim3 rgrid((D + 31) / 32, (!rms && db) ? 2 : 1), rblock(32, 16);
+  if (grads_f32)
+    reduce_partials_kernel<float><<<rgrid, rblock, 0, s>>>(dw_part, db_part, static_cast<float*>(dw), static_cast<float*>(db), P, D,
+                                                           accumulate);
+  else
+    reduce_partials_kernel<__nv_bfloat16><<<rgrid, rblock, 0, s>>>(dw_part, db_part, static_cast<__nv_bfloat16*>(dw),
+                                                                   static_cast<__nv_bfloat16*>(db), P, D, accumulate);
   ELFA_CUDA(cudaGetLastError());
-  ::elfa::count_launches(3);
+  ::elfa::count_launches(2);
   return ELFA_OK;
 }

@@ -20,12 +20,46 @@ struct StepScalars {   // device-resident scalars shared by the kernels of one o
   int skip;            // 1 if the norm is not finite -> every update kernel leaves state untouched
 };
 
+__device__ __forceinline__ float sumsq16(const uint4& v, float) {
+  const float4 f = *reinterpret_cast<const float4*>(&v);
+  return f.x * f.x + f.y * f.y + f.z * f.z + f.w * f.w;
+}
+__device__ __forceinline__ float sumsq16(const uint4& v, __nv_bfloat16) {
+  const uint32_t* p = reinterpret_cast<const uint32_t*>(&v);
+  float a = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) a += bf16_lo(p[j]) * bf16_lo(p[j]) + bf16_hi(p[j]) * bf16_hi(p[j]);
+  return a;
+}
+
+// part[block] = sum of squares of this block's share. The 16-byte aligned body is read as vectors, four
+// loads in flight per thread; the unaligned head and the tail are read element by element.
 template <typename GradT>
 __global__ void __launch_bounds__(256) sumsq_kernel(const GradT* __restrict__ g, long long n, float* __restrict__ part) {
   __shared__ float sm[8];
-  float acc = 0.f;
+  constexpr int E = 16 / (int)sizeof(GradT);
+  long long head = (long long)(((16 - (reinterpret_cast<uintptr_t>(g) & 15)) & 15) / sizeof(GradT));
+  if (head > n) head = n;
+  const long long nvec = (n - head) / E;
+  const uint4* gv = reinterpret_cast<const uint4*>(g + head);
   const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  float acc = 0.f;
+  for (long long i0 = tid; i0 < nvec; i0 += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      v[u] = make_uint4(0, 0, 0, 0);
+      if (i0 + u * stride < nvec) v[u] = gv[i0 + u * stride];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc += sumsq16(v[u], GradT());
+  }
+  for (long long i = tid; i < head; i += stride) {
+    const float v = (float)g[i];
+    acc += v * v;
+  }
+  for (long long i = head + nvec * E + tid; i < n; i += stride) {
     const float v = (float)g[i];
     acc += v * v;
   }
@@ -69,10 +103,32 @@ __global__ void clip_coef_kernel(StepScalars* scal, float max_norm, float inv_sc
   scal->clip_coef = c * inv_scale;
 }
 
-template <typename GradT, typename ParamT>
+__device__ __forceinline__ void load4(const float* p, float (&o)[4]) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&o)[4]) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  o[0] = bf16_lo(v.x); o[1] = bf16_hi(v.x); o[2] = bf16_lo(v.y); o[3] = bf16_hi(v.y);
+}
+__device__ __forceinline__ void store4(float* p, const float (&o)[4]) { *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]); }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&o)[4]) {
+  *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
+}
+
+__device__ __forceinline__ void adamw_update(float& p, float& mi, float& vi, float g, float lr, float beta1, float beta2, float eps,
+                                             float wd, float inv_bc1, float inv_bc2) {
+  mi = beta1 * mi + (1.f - beta1) * g;
+  vi = beta2 * vi + (1.f - beta2) * g * g;
+  const float mh = mi * inv_bc1, vh = vi * inv_bc2;
+  p -= lr * (mh / (sqrtf(vh) + eps) + wd * p);
+}
+
+// VEC = 4: every pointer is aligned for 4-element accesses and `n` counts groups of four; VEC = 1: element by element.
+template <typename GradT, typename ParamT, int VEC>
 __global__ void __launch_bounds__(256) adamw_kernel(ParamT* __restrict__ param, float* __restrict__ master, float* __restrict__ m,
                                                     float* __restrict__ v, const GradT* __restrict__ grad, long long n, float lr,
-                                                    float beta1, float beta2, float eps, float wd, float bc1, float bc2,
+                                                    float beta1, float beta2, float eps, float wd, float inv_bc1, float inv_bc2,
                                                     const StepScalars* __restrict__ scal) {
   float gscale = 1.f;
   if (scal) {
@@ -81,16 +137,26 @@ __global__ void __launch_bounds__(256) adamw_kernel(ParamT* __restrict__ param, 
   }
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-    const float g = (float)grad[i] * gscale;
-    float p = master[i];
-    const float mi = beta1 * m[i] + (1.f - beta1) * g;
-    const float vi = beta2 * v[i] + (1.f - beta2) * g * g;
-    const float mh = mi / bc1, vh = vi / bc2;
-    p -= lr * (mh / (sqrtf(vh) + eps) + wd * p);
-    m[i] = mi;
-    v[i] = vi;
-    master[i] = p;
-    if (param) param[i] = (ParamT)p;
+    if (VEC == 4) {
+      float g[4], p[4], mm[4], vv[4];
+      load4(grad + 4 * i, g);
+      load4(master + 4 * i, p);
+      load4(m + 4 * i, mm);
+      load4(v + 4 * i, vv);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) adamw_update(p[j], mm[j], vv[j], g[j] * gscale, lr, beta1, beta2, eps, wd, inv_bc1, inv_bc2);
+      store4(m + 4 * i, mm);
+      store4(v + 4 * i, vv);
+      store4(master + 4 * i, p);
+      if (param) store4(param + 4 * i, p);
+    } else {
+      float p = master[i], mi = m[i], vi = v[i];
+      adamw_update(p, mi, vi, (float)grad[i] * gscale, lr, beta1, beta2, eps, wd, inv_bc1, inv_bc2);
+      m[i] = mi;
+      v[i] = vi;
+      master[i] = p;
+      if (param) param[i] = (ParamT)p;
+    }
   }
 }
 
@@ -231,10 +297,24 @@ ELFA_API int elfa_adamw(void* param, int param_type, float* master, float* m, fl
                         float lr, float beta1, float beta2, float eps, float wd, int step, const void* scalars, void* stream) {
   ELFA_REQUIRE(master && m && v && grad && n > 0 && step >= 1, "adamw: bad arguments");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const float bc1 = 1.f - powf(beta1, (float)step), bc2 = 1.f - powf(beta2, (float)step);
-  const int g = flat_grid(n);
+  const float inv_bc1 = 1.f / (1.f - powf(beta1, (float)step)), inv_bc2 = 1.f / (1.f - powf(beta2, (float)step));
   const auto* sc = static_cast<const StepScalars*>(scalars);
-#define ADAMW(GT, PT) adamw_kernel<GT, PT><<<g, 256, 0, s>>>(static_cast<PT*>(param), master, m, v, static_cast<const GT*>(grad), n, lr, beta1, beta2, eps, wd, bc1, bc2, sc)
+  const size_t gsz = grad_type == 0 ? 4 : 2, psz = param_type == 0 ? 4 : 2;
+  auto aligned = [](const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; };
+  const bool vec = n >= 4 && aligned(master, 16) && aligned(m, 16) && aligned(v, 16) && aligned(grad, 4 * gsz) &&
+                   (!param || aligned(param, 4 * psz));
+  const long long body = vec ? n / 4 * 4 : 0, tail = n - body;
+#define ADAMW(GT, PT)                                                                                                            \
+  do {                                                                                                                           \
+    if (body)                                                                                                                    \
+      adamw_kernel<GT, PT, 4><<<flat_grid(body / 4), 256, 0, s>>>(static_cast<PT*>(param), master, m, v,                          \
+                                                                  static_cast<const GT*>(grad), body / 4, lr, beta1, beta2, eps, \
+                                                                  wd, inv_bc1, inv_bc2, sc);                                     \
+    if (tail)                                                                                                                    \
+      adamw_kernel<GT, PT, 1><<<flat_grid(tail), 256, 0, s>>>(param ? static_cast<PT*>(param) + body : nullptr, master + body,   \
+                                                              m + body, v + body, static_cast<const GT*>(grad) + body, tail, lr, \
+                                                              beta1, beta2, eps, wd, inv_bc1, inv_bc2, sc);                      \
+  } while (0)
   if (grad_type == 0 && param_type == 0) ADAMW(float, float);
   else if (grad_type == 0) ADAMW(float, __nv_bfloat16);
   else if (param_type == 0) ADAMW(__nv_bfloat16, float);

@@ -7,6 +7,9 @@
     python -m elfa_b200.utils.microbench xent --rows 8192 --vocab 32000
     python -m elfa_b200.utils.microbench adamw --n 268435456
     python -m elfa_b200.utils.microbench mxfp8 --rows 16384 --dim 4096
+    python -m elfa_b200.utils.microbench gemm_nvfp4 --m 8192 --n 8192 --k 8192
+    python -m elfa_b200.utils.microbench gelu | softmax | embedding | efla
+    python -m elfa_b200.utils.microbench suite --iters 2      # every bandwidth-bound kernel once, small sizes (the ncu capture)
 
 Prints one line with the achieved rate and its fraction of the measured peak
 (``MEASURED_PEAKS.json`` at the repository root when present). These are the commands the ncu
@@ -54,7 +57,8 @@ def timed(fn, iters, warm=3, flush=True):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "norm", "norm_bwd", "xent", "adamw", "mxfp8", "gemm_mxfp8"])
+    ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "norm", "norm_bwd", "xent", "adamw", "mxfp8", "gemm_mxfp8",
+                                      "gemm_nvfp4", "gelu", "softmax", "embedding", "efla", "suite"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -70,6 +74,14 @@ def main(argv=None) -> int:
     ap.add_argument("--compare", action="store_true", help="also time the PyTorch / library op")
     ap.add_argument("--bn", type=int, default=0, help="gemm: force the tile width (64 / 128 / 256, 512 = CTA pairs; 0 = automatic)")
     a = ap.parse_args(argv)
+    if a.kernel == "suite":
+        # inputs larger than the 126 MB L2, about 1 GB on the device at most
+        rc = 0
+        for sub in (["norm", "--rows", "16384"], ["norm_bwd", "--rows", "16384"], ["gelu", "--rows", "16384"],
+                    ["softmax", "--rows", "16384"], ["embedding", "--rows", "16384"], ["xent", "--rows", "4096"],
+                    ["mxfp8", "--rows", "16384"], ["adamw", "--n", str(1 << 26)]):
+            rc |= main(sub + ["--iters", str(a.iters)])
+        return rc
     from .. import native, ops
     from ..native import lib, stream_ptr
     native.lib.load()
@@ -108,6 +120,49 @@ def main(argv=None) -> int:
         ms = timed(lambda: q8.quantize_mxfp8(x, dequantized=True), a.iters)
         by = M * K * (2 + 1 + 2)
         print(f"mxfp8 quantise (payload + scales + bf16 copy) {M}x{K}: {ms:.4f} ms  {by / ms / 1e6:.1f} GB/s  {by / ms / 1e-3 / hbm:.3f} of {src} copy bandwidth")
+    elif a.kernel == "gemm_nvfp4":
+        from ..ops import gemm_nvfp4 as q4
+        M, N, K = a.m, a.n, a.k
+        xq, _ = q4.quantize_nvfp4(torch.randn(M, K, device=dev).to(bf))
+        wq, _ = q4.quantize_nvfp4(torch.randn(N, K, device=dev).to(bf), right=True)
+        out = torch.empty(M, N, dtype=bf, device=dev)
+        ms = timed(lambda: q4.gemm_nvfp4(xq, wq, out=out, force_bn=a.bn), a.iters)
+        fl = 2.0 * M * N * K
+        print(f"gemm_nvfp4 {M}x{N}x{K}: {ms:.4f} ms  {fl / ms / 1e9:.1f} TFLOP/s  {fl / ms / 1e-3 / flops_peak:.3f} of {src} cuBLAS bf16 peak "
+              f"(block-scaled e2m1, nominal fp4 peak is 4x bf16)")
+        x = torch.randn(M, K, device=dev).to(bf)
+        amax = x.abs().max().float().reshape(1)
+        ms = timed(lambda: q4.quantize_nvfp4(x, dequantized=True, amax=amax), a.iters)
+        by = M * K * (2 + 0.5 + 2)
+        print(f"nvfp4 quantise (payload + scales + bf16 copy) {M}x{K}: {ms:.4f} ms  {by / ms / 1e6:.1f} GB/s  {by / ms / 1e-3 / hbm:.3f} of {src} copy bandwidth")
+    elif a.kernel in ("gelu", "softmax", "embedding"):
+        R, D = a.rows, a.dim
+        if a.kernel == "embedding":
+            tok = torch.randn(a.vocab, D, device=dev).to(bf)
+            ids = torch.randint(0, a.vocab, (R // 4096 if R >= 4096 else 1, min(R, 4096)), device=dev)
+            with torch.no_grad():
+                ms = timed(lambda: ops.embedding(ids, tok), a.iters)
+            by = 2.0 * ids.numel() * D * 2
+        else:
+            x = torch.randn(R, D, device=dev).to(bf)
+            from ..ops.nn import softmax as _softmax
+            fn = ops.gelu if a.kernel == "gelu" else _softmax
+            with torch.no_grad():
+                ms = timed(lambda: fn(x), a.iters)
+            by = 2.0 * R * D * 2
+        print(f"{a.kernel} {R}x{D}: {ms:.4f} ms  {by / ms / 1e6:.1f} GB/s  {by / ms / 1e-3 / hbm:.3f} of {src} copy bandwidth")
+    elif a.kernel == "efla":
+        from ..ops.efla import efla_scan
+        B, T, H, hd = a.batch, a.seq, a.heads, a.hd
+        k = torch.nn.functional.normalize(torch.randn(B, T, H, hd, device=dev), dim=-1).to(bf).requires_grad_(True)
+        v = torch.randn(B, T, H, hd, device=dev).to(bf).requires_grad_(True)
+        beta = torch.tensor(0.5, device=dev, requires_grad=True)
+        with torch.no_grad():
+            ms = timed(lambda: efla_scan(k, v, beta), a.iters)
+        o, _ = efla_scan(k, v, beta)
+        g = torch.randn_like(o)
+        ms_b = timed(lambda: torch.autograd.grad(o, (k, v, beta), g, retain_graph=True), a.iters)
+        print(f"efla scan B{B} T{T} H{H} d{hd}: forward {ms:.3f} ms ({B * T / ms / 1e3:.2f} M tokens/s), backward {ms_b:.3f} ms")
     elif a.kernel in ("attn_fwd", "attn_bwd"):
         S, B, H, hd = a.seq, a.batch, a.heads, a.hd
         qkv = torch.randn(S, B, 3, H, hd, device=dev).to(bf)
