@@ -83,6 +83,7 @@ int elfa_attention_bwd(const void* qkv, long long stride_s, long long stride_b, 
 long long elfa_mxfp8_sf_bytes(int rows, int cols, int b_operand);
 int elfa_mxfp8_quantize_gemm(const void* x, long long ldx, void* payload, void* sf, void* deq, int rows, int cols, int b_operand,
                              void* stream);
+int elfa_mxfp8_dequantize(const void* payload, const void* sf, void* out, int rows, int cols, int b_operand, void* stream);
 int elfa_gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N, int K, long long ldc,
                     const void* bias, void* preact, long long ldpre, unsigned flags, int force_bn, void* stream);
 

@@ -487,6 +487,33 @@ __global__ void __launch_bounds__(256) mxfp8_quantize_gemm_kernel(const __nv_bfl
   }
 }
 
+// Inverse of the quantiser: out[r, c] = e4m3(payload[r, c]) * 2^(scale(r, c / 32) - 127) as bf16 (exact: three
+// mantissa bits times a power of two). A thread converts 8 values (8-byte load, 16-byte store).
+__global__ void __launch_bounds__(256) mxfp8_dequantize_kernel(const uint8_t* __restrict__ payload, const uint8_t* __restrict__ sf,
+                                                               __nv_bfloat16* __restrict__ out, int rows, int cols, int kt,
+                                                               int b_atoms) {
+  const uint32_t vpr = (uint32_t)cols / 8;
+  const uint32_t nvec = (uint32_t)rows * vpr;
+  const uint32_t stride = gridDim.x * blockDim.x;
+  for (uint32_t v = blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += stride) {
+    const uint32_t r = v / vpr, c8 = v - r * vpr, kb = c8 >> 2;
+    const uint2 q = *reinterpret_cast<const uint2*>(payload + (long long)r * cols + c8 * 8);
+    const long long atom = b_atoms > 0 ? (long long)(kb >> 2) * b_atoms + (r >> 7) : (long long)(r >> 7) * kt + (kb >> 2);
+    const uint32_t sb = sf[atom * SF_ATOM + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (kb & 3)];
+    const float sc = sb == 0 ? 5.877471754111438e-39f : __uint_as_float(sb << 23);
+    const uint32_t w[2] = {q.x, q.y};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t two = (w[j >> 1] >> (16 * (j & 1))) & 0xffffu;
+      const float lo = __half2float(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)(two & 0xff), __NV_E4M3))) * sc;
+      const float hi = __half2float(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)(two >> 8), __NV_E4M3))) * sc;
+      o[j] = pack_bf16(lo, hi);
+    }
+    *reinterpret_cast<uint4*>(out + (long long)r * cols + c8 * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 }  // namespace
 }  // namespace elfa
 
@@ -511,6 +538,23 @@ ELFA_API int elfa_mxfp8_quantize_gemm(const void* x, long long ldx, void* payloa
   mxfp8_quantize_gemm_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), ldx, static_cast<uint8_t*>(payload), static_cast<uint8_t*>(sf),
       static_cast<__nv_bfloat16*>(deq), rows, cols, (cols + 127) / 128, b_operand ? (rows + 127) / 128 + 1 : 0);
+  ELFA_CUDA(cudaGetLastError());
+  count_launches(1);
+  return ELFA_OK;
+}
+
+// payload [rows, cols] e4m3 + scale atoms (order per `b_operand`) -> out [rows, cols] bf16, the values the block-scaled
+// GEMM multiplies. Used where an operand arrives quantised (all-gather of payloads) and backward needs it in bf16.
+ELFA_API int elfa_mxfp8_dequantize(const void* payload, const void* sf, void* out, int rows, int cols, int b_operand, void* stream) {
+  ELFA_REQUIRE(payload && sf && out && rows > 0 && cols > 0 && cols % 32 == 0, "mxfp8_dequantize: bad arguments");
+  const long long nv = (long long)rows * (cols / 8);
+  ELFA_REQUIRE(nv < (1ll << 31) - (1 << 20), "mxfp8_dequantize: tensor too large (2^34 elements at most)");
+  ELFA_REQUIRE((reinterpret_cast<uintptr_t>(payload) & 7) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
+               "mxfp8_dequantize: payload must be 8-byte and out 16-byte aligned");
+  const int grid = (int)((nv + 255) / 256 < 148 * 16 ? (nv + 255) / 256 : 148 * 16);
+  mxfp8_dequantize_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(payload), static_cast<const uint8_t*>(sf), static_cast<__nv_bfloat16*>(out), rows, cols,
+      (cols + 127) / 128, b_operand ? (rows + 127) / 128 + 1 : 0);
   ELFA_CUDA(cudaGetLastError());
   count_launches(1);
   return ELFA_OK;

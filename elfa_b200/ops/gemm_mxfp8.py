@@ -69,6 +69,14 @@ def gemm_mxfp8(a: Mxfp8Operand, b: Mxfp8Operand, *, bias: Optional[torch.Tensor]
     return out
 
 
+def dequantize_mxfp8(op: Mxfp8Operand, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bf16 tensor of the values an operand stands for (exact), by the native kernel."""
+    if out is None:
+        out = torch.empty((op.rows, op.cols), dtype=torch.bfloat16, device=op.payload.device)
+    lib.call("elfa_mxfp8_dequantize", op.payload, op.scales, out, op.rows, op.cols, int(op.right), stream_ptr(op.payload))
+    return out
+
+
 def dequantize_ref(op: Mxfp8Operand) -> torch.Tensor:
     """fp32 values of an operand, decoded with plain PyTorch (test oracle)."""
     rows, cols = op.rows, op.cols

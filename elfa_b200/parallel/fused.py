@@ -3,7 +3,11 @@
 * ``ag_gemm``  - all-gather → GEMM in one kernel (reference call sites:
   ``src/distributed/tensor_parallel.zig:77-129``, ``src/distributed/sequence_parallel.zig:79-128``);
 * ``gemm_rs``  - GEMM → reduce-scatter in one kernel (``tensor_parallel.zig:154-170``,
-  ``sequence_parallel.zig:184-200``).
+  ``sequence_parallel.zig:184-200``);
+* ``ag_gemm_mxfp8`` - the quantise-before-send form of the all-gather for MXFP8 layers: every rank
+  quantises its rows into its ring slot (e4m3 payload + scale atoms, 1.03 bytes per element instead
+  of 2), a signal barrier, a peer-load gather of the other ranks' payloads and scales, then the
+  block-scaled tensor-core GEMM on the gathered operand.
 
 Buffers live in the group's :class:`~elfa_b200.runtime.symm.SymmetricArena`. Each primitive owns a
 ring of two slots (gathered-A buffers / receive buffers) with one set of arrival counters per
@@ -43,7 +47,10 @@ class _State:
     def __init__(self, arena):
         self.arena = arena
         self.slots: Dict[Tuple[str, int, int], _Slot] = {}
-        self.counter = {"ag": 0, "rs": 0}
+        self.counter = {"ag": 0, "rs": 0, "agq": 0}
+        self.bar = None                                     # signal words of the stream-ordered barrier
+        self.bar_peers = None
+        self.bar_epoch = 0
         self.side: Optional[torch.cuda.Stream] = None      # copies of gathered inputs out of the ring
         self.pending: Optional[torch.cuda.Event] = None
 
@@ -60,6 +67,18 @@ class _State:
             # (and zeroed counters are visible) before any peer writes into it
             self.arena.barrier()
         return s
+
+
+    def stream_barrier(self, stream: int) -> None:
+        """Barrier over the group's ranks as a kernel on ``stream`` (bounded wait on peer signal words)."""
+        a = self.arena
+        if self.bar is None:
+            self.bar = a.alloc(1024, "fused.barrier")
+            self.bar_peers = (ctypes.c_uint64 * a.world)(*[a.peer_address(r, self.bar) for r in range(a.world)])
+            a.barrier()                                     # zeroed words visible everywhere before the first signal
+        self.bar_epoch += 1
+        lib.call("elfa_symm_barrier", ctypes.addressof(self.bar_peers), self.bar.tensor, a.rank, a.world, self.bar_epoch,
+                 _WAIT_MS, stream)
 
 
 _states: Dict[int, _State] = {}
@@ -141,6 +160,59 @@ def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, pc: ParallelContext, *, b_mn
     st.pending = ev
     if not defer_copy:
         wait_pending_copies(pc)
+    return y, x_full, pre
+
+
+def supported_mxfp8(rows_local: int, K: int, N: int) -> bool:
+    return rows_local % 128 == 0 and K % 128 == 0 and N % 8 == 0
+
+
+def ag_gemm_mxfp8(x_local: torch.Tensor, w_op, pc: ParallelContext, *, act: Optional[str] = None, preact: bool = False):
+    """``y = act(all_gather_rows(q(x_local)) @ w_op^T)`` with MXFP8 operands → ``(y, x_full, pre)``.
+    ``x_local [M / world, K]`` bf16 is quantised here; ``w_op`` is the cached right-hand operand
+    (``[N, K]`` payload). ``x_full`` is the bf16 tensor of the gathered quantised rows (what backward
+    multiplies for the weight gradient), produced on a side stream: call :func:`wait_pending_copies`
+    before reading it. Only the payload and the scales cross NVLink."""
+    from ..ops.gemm_mxfp8 import Mxfp8Operand, gemm_mxfp8
+    world, rank = pc.tp_size, pc.tp_rank
+    Ml, K = x_local.shape
+    M, N = Ml * world, w_op.rows
+    kt = K // 128
+    pay_l, sf_l = Ml * K, (Ml // 128) * kt * 512            # this rank's share of payload / scale atoms
+    st = _state(pc)
+    wait_pending_copies(pc)
+    slot = st.next_slot("agq", _round_class(world * (pay_l + sf_l)))
+    xl = x_local if x_local.is_contiguous() else x_local.contiguous()
+    stream = stream_ptr(xl)
+    buf = slot.data.tensor
+    payload = buf[: world * pay_l].view(M, K)
+    scales = buf[world * pay_l: world * (pay_l + sf_l)]
+    # 1. quantise the local rows into this rank's own slot, at the place they have in the gathered operand
+    lib.call("elfa_mxfp8_quantize_gemm", xl, xl.stride(0), payload[rank * Ml:], scales[rank * sf_l:], None, Ml, K, 0, stream)
+    # 2. every rank's rows are in its slot
+    st.stream_barrier(stream)
+    # 3. pull the other ranks' payloads and scale atoms (peer loads)
+    base = [int(slot.peer_data[r]) for r in range(world)]
+    src_pay = (ctypes.c_uint64 * world)(*[base[r] + r * pay_l for r in range(world)])
+    src_sf = (ctypes.c_uint64 * world)(*[base[r] + world * pay_l + r * sf_l for r in range(world)])
+    lib.call("elfa_zero3_gather", ctypes.addressof(src_pay), world, 0, pay_l, payload, stream)
+    lib.call("elfa_zero3_gather", ctypes.addressof(src_sf), world, 0, sf_l, scales, stream)
+    # 4. block-scaled GEMM on the gathered operand
+    a_op = Mxfp8Operand(payload, scales, M, K, False)
+    pre = torch.empty((M, N), dtype=torch.bfloat16, device=x_local.device) if (act == "gelu" and preact) else None
+    y = gemm_mxfp8(a_op, w_op, gelu=act == "gelu", preact=pre)
+    # 5. bf16 copy of the gathered rows for the weight gradient, out of the ring on the side stream
+    if st.side is None:
+        st.side = torch.cuda.Stream(x_local.device)
+    x_full = torch.empty((M, K), dtype=torch.bfloat16, device=x_local.device)
+    cur = torch.cuda.current_stream()
+    st.side.wait_stream(cur)
+    with torch.cuda.stream(st.side):
+        lib.call("elfa_mxfp8_dequantize", payload, scales, x_full, M, K, 0, st.side.cuda_stream)
+        ev = torch.cuda.Event()
+        ev.record(st.side)
+    x_full.record_stream(st.side)
+    st.pending = ev
     return y, x_full, pre
 
 

@@ -186,15 +186,34 @@ def _overlap_wgrad(pc: ParallelContext, t: torch.Tensor) -> bool:
     return os.environ.get("ELFA_OVERLAP_WGRAD", "0") not in ("0", "")
 
 
+def _quantised_gather(x2: torch.Tensor, w: torch.Tensor, pc: ParallelContext, quant) -> bool:
+    """Whether a column-parallel MXFP8 layer all-gathers quantised payloads (``fused.ag_gemm_mxfp8``) instead of
+    fake-quantised bf16 rows. ``ELFA_AG_MXFP8=0`` switches it off."""
+    import os
+    if quant is None or quant.fmt != "mxfp8" or pc.comm_backend != "fused" or pc.tp_size == 1:
+        return False
+    if os.environ.get("ELFA_AG_MXFP8", "1") in ("0", ""):
+        return False
+    from . import fused
+    return use_block_scaled_gemm(x2, w, quant) and fused.supported_mxfp8(x2.shape[0], x2.shape[1], w.shape[1])
+
+
 class _ColumnParallelSP(torch.autograd.Function):
     """x_local ``[S/tp, B, D]`` → ``act(all_gather(x) @ w_local)`` ``[S, B, N/tp]``."""
 
     @staticmethod
     def forward(ctx, x, w, pc, act, quant):
         Sl, B, D = x.shape
-        xq = fake_quant(x.reshape(Sl * B, D), quant) if quant is not None else x.reshape(Sl * B, D)
+        x2 = x.reshape(Sl * B, D)
         wq = cached_weight_quant(w, quant) if quant is not None else w
-        y, x_full, pre = ag_gemm(xq, wq, pc, b_mn=True, act=act, preact=True, defer_copy=True)   # backward waits for the copy
+        if _quantised_gather(x2, w, pc, quant):
+            # quantise before sending: e4m3 payloads and scales cross NVLink (half the bytes), the product runs on
+            # the block-scaled tensor-core path; x_full is the bf16 form of the gathered quantised rows
+            from . import fused
+            y, x_full, pre = fused.ag_gemm_mxfp8(x2, cached_weight_operand(w, quant), pc, act=act, preact=True)
+        else:
+            xq = fake_quant(x2, quant) if quant is not None else x2
+            y, x_full, pre = ag_gemm(xq, wq, pc, b_mn=True, act=act, preact=True, defer_copy=True)   # backward waits for the copy
         ctx.save_for_backward(x_full, wq, pre)
         ctx.pc, ctx.w_ref, ctx.shape = pc, w, (Sl, B, D)
         return y.view(Sl * pc.tp_size, B, -1)

@@ -75,6 +75,26 @@ def mode_fused(pc, dev):
         assert e1 == 0.0 and e2 == 0.0, f"ag_gemm differs from the library path: {e1} {e2}"
         assert e3 < tol, f"gemm_rs error {e3} > {tol}"
         worst = max(worst, e3)
+    # quantise-before-send all-gather -> block-scaled GEMM: bit-identical to the one-GPU path on the whole input
+    from elfa_b200.ops.gemm_mxfp8 import gemm_mxfp8, quantize_mxfp8
+    from elfa_b200.parallel import fused
+    pc.comm_backend = "fused"
+    for it, (Ml, K, N) in enumerate([(128, 256, 512), (256, 512, 1376), (512, 4096, 1536), (128, 256, 512), (1024, 1024, 2048),
+                                     (256, 512, 1376)]):
+        g = torch.Generator(device="cpu").manual_seed(300 + it)
+        x_all = torch.randn(Ml * world, K, generator=g).to(torch.bfloat16).to(dev)
+        w = (torch.randn(K, N, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+        w_op, _ = quantize_mxfp8(w.t().contiguous(), right=True)
+        x_local = x_all[rank * Ml:(rank + 1) * Ml].contiguous()
+        assert fused.supported_mxfp8(Ml, K, N)
+        y, x_full, pre = fused.ag_gemm_mxfp8(x_local, w_op, pc, act="gelu", preact=True)
+        fused.wait_pending_copies(pc)
+        xa_op, xq_all = quantize_mxfp8(x_all, dequantized=True)
+        pre_ref = torch.empty_like(pre)
+        y_ref = gemm_mxfp8(xa_op, w_op, gelu=True, preact=pre_ref)
+        torch.cuda.synchronize()
+        assert torch.equal(x_full, xq_all), f"gathered quantised rows differ ({Ml}, {K}, {N})"
+        assert torch.equal(y, y_ref) and torch.equal(pre, pre_ref), f"quantised all-gather GEMM differs ({Ml}, {K}, {N})"
     st = native.status()
     assert st == 0, f"device status 0x{st:x}"
     dist.barrier()
@@ -86,12 +106,13 @@ def mode_tp(pc, dev, backend, dtype):
     from elfa_b200.parallel.mesh import ParallelContext
     from elfa_b200.trainer import Trainer
     world = pc.tp_size
-    cfg = small_cfg(dtype, world, backend)
+    quant = os.environ.get("ELFA_TEST_QUANT", "none")      # "mxfp8": the quantised all-gather path of the fused backend
+    cfg = small_cfg(dtype, world, backend, quant)
     tr = Trainer(cfg, device=dev, pc=pc, telemetry=False)
     losses = tr.run(max_steps=4)
     ref = None
     if pc.rank == 0:
-        cfg1 = small_cfg(dtype, 1, "nccl")
+        cfg1 = small_cfg(dtype, 1, "nccl", quant)
         cfg1.runtime.world_size = 1
         tr1 = Trainer(cfg1, device=dev, pc=ParallelContext(), telemetry=False)
         ref = tr1.run(max_steps=4)

@@ -19,13 +19,13 @@ def _ngpus():
     return min(n, want)
 
 
-def _run(args, port, timeout=600):
+def _run(args, port, timeout=600, extra_env=None):
     n = _ngpus()
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), os.path.join(ROOT, "tests", "dist_worker.py"), *args]
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **(extra_env or {}))
     return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
 
 
@@ -38,6 +38,13 @@ def test_fused_ag_gemm_and_gemm_rs(cuda_device):
 @pytest.mark.parametrize("backend", ["nccl", "fused"])
 def test_tp_training_matches_single_gpu(cuda_device, backend):
     r = _run(["tp", backend, "bf16"], 29702 if backend == "nccl" else 29703)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "TP_OK" in r.stdout
+
+
+def test_tp_mxfp8_quantised_all_gather_matches_single_gpu(cuda_device):
+    """MXFP8 QAT with the fused backend: column-parallel layers all-gather e4m3 payloads + scales."""
+    r = _run(["tp", "fused", "bf16"], 29708, extra_env={"ELFA_TEST_QUANT": "mxfp8"})
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "TP_OK" in r.stdout
 

@@ -80,3 +80,18 @@ def test_quant_linear_block_scaled_path_equals_fake_quant_path(act):
     assert (y1 - y0).abs().max() <= 2 ** -7 * y0.abs().max()
     assert (dx1 - dx0).abs().max() <= 2 ** -6 * dx0.abs().max()      # GELU' of a pre-activation that differs in the last bf16 bit
     assert (dw1 - dw0).abs().max() <= 2 ** -6 * dw0.abs().max()
+
+
+@pytest.mark.parametrize("rows,cols,right", [(128, 128, False), (300, 160, False), (1024, 4096, False), (200, 512, True),
+                                             (1536, 1024, True)])
+def test_mxfp8_dequantise_kernel_is_exact(rows, cols, right):
+    """The native dequantiser returns exactly the bf16 copy the quantiser wrote and the PyTorch decode."""
+    from elfa_b200 import native
+    from elfa_b200.ops import gemm_mxfp8 as q
+    x, _ = _operands(rows, 128, cols, rows + cols)
+    op, deq = q.quantize_mxfp8(x, dequantized=True, right=right)
+    out = q.dequantize_mxfp8(op)
+    torch.cuda.synchronize()
+    assert native.status() == 0
+    assert torch.equal(out, deq)
+    assert torch.equal(out.float(), q.dequantize_ref(op))
