@@ -167,6 +167,10 @@ class RuntimeConfig:
     # collectives; "nccl" = the unfused library baseline).
     comm_backend: str = field(default="fused", metadata=_enum(("fused", "nccl")))
     sequence_parallel: bool = True
+    # extension: ranks of one data-parallel replica that split the sequence dimension of a batch (ring attention)
+    context_parallel_size: int = 1
+    # "ring": key / value blocks travel round the group; "ulysses": all-to-all to a head split and back
+    context_parallel_mode: str = field(default="ring", metadata=_enum(("ring", "ulysses")))
 
     def validate(self) -> None:
         if self.world_size <= 0:
@@ -177,6 +181,8 @@ class RuntimeConfig:
             raise ConfigError("runtime.world_size must be a multiple of tensor_parallel_size")
         if self.zero_stage not in (0, 1, 2, 3):
             raise ConfigError("runtime.zero_stage must be 0..3")
+        if self.context_parallel_size <= 0 or self.data_parallel_size % self.context_parallel_size != 0:
+            raise ConfigError("runtime.context_parallel_size must divide the data-parallel size")
 
     @property
     def data_parallel_size(self) -> int:

@@ -72,7 +72,15 @@ class Attention(nn.Module):
     def forward(self, x):            # x: [S(/tp), B, D]
         h = tpl.column_parallel_linear(x, self.w_qkv, self.pc, quant=self.quant)      # [S, B, 3*local]
         S, B = h.shape[0], h.shape[1]
-        o = ops.attention(h.view(S, B, 3, self.n_heads, self.head_dim), causal=True, seq_first=True)   # [S, B, local]
+        qkv = h.view(S, B, 3, self.n_heads, self.head_dim)
+        if self.pc.cp_size > 1 and self.pc.cp_mode == "ulysses":     # all-to-all to whole sequences of H / cp heads and back
+            from ..parallel.ulysses import ulysses_attention
+            o = ulysses_attention(qkv, self.pc.cp_group, causal=True)
+        elif self.pc.cp_size > 1:    # the sequence is split over the context-parallel group: keys / values travel the ring
+            from ..parallel.ring_attention import ring_attention
+            o = ring_attention(qkv, self.pc.cp_group, causal=True, seq_first=True)
+        else:
+            o = ops.attention(qkv, causal=True, seq_first=True)                      # [S, B, local]
         return tpl.row_parallel_linear(o, self.w_o, self.pc, quant=self.quant)        # [S(/tp), B, D]
 
 

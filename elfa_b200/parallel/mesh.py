@@ -30,6 +30,13 @@ class ParallelContext:
     tp_ranks: List[int] = field(default_factory=lambda: [0])
     dp_ranks: List[int] = field(default_factory=lambda: [0])
     symm: Optional[object] = None       # runtime.symm.SymmetricArena of the TP group (fused backend)
+    # context parallelism: ``cp_size`` consecutive members of the data-parallel group share one batch and
+    # split its sequence dimension (ring attention); for gradients they are ordinary data-parallel ranks
+    cp_size: int = 1
+    cp_rank: int = 0
+    cp_group: Optional[object] = None
+    cp_ranks: List[int] = field(default_factory=lambda: [0])
+    cp_mode: str = "ring"               # "ring" or "ulysses" (all-to-all head scatter)
 
     @property
     def is_distributed(self) -> bool:
@@ -67,8 +74,11 @@ def init_distributed(backend: Optional[str] = None, timeout_s: float = 600.0) ->
     return dist.get_world_size()
 
 
-def build_context(tp_size: int = 1, sequence_parallel: bool = True, comm_backend: str = "nccl") -> ParallelContext:
-    """Creates the (dp, tp) groups. Every rank must call this with the same arguments."""
+def build_context(tp_size: int = 1, sequence_parallel: bool = True, comm_backend: str = "nccl", cp_size: int = 1,
+                  cp_mode: str = "ring") -> ParallelContext:
+    """Creates the (dp, tp) groups, and with ``cp_size > 1`` the context-parallel groups inside every
+    data-parallel group (``dp_rank = replica * cp_size + cp_rank``). Every rank must call this with the
+    same arguments."""
     if not dist.is_initialized():
         return ParallelContext(sequence_parallel=False, comm_backend=comm_backend)
     world, rank = dist.get_world_size(), dist.get_rank()
@@ -88,4 +98,14 @@ def build_context(tp_size: int = 1, sequence_parallel: bool = True, comm_backend
         g = dist.new_group(ranks) if dp_size > 1 else None
         if t == tp_rank:
             ctx.dp_group, ctx.dp_ranks = g, ranks
+    if cp_size > 1:
+        if dp_size % cp_size != 0:
+            raise ValueError(f"data-parallel size {dp_size} is not a multiple of context_parallel_size {cp_size}")
+        ctx.cp_size, ctx.cp_rank, ctx.cp_mode = cp_size, dp_rank % cp_size, cp_mode
+        for t in range(tp_size):
+            for rep in range(dp_size // cp_size):
+                ranks = [global_rank(rep * cp_size + c, t, tp_size) for c in range(cp_size)]
+                g = dist.new_group(ranks)
+                if t == tp_rank and rep == dp_rank // cp_size:
+                    ctx.cp_group, ctx.cp_ranks = g, ranks
     return ctx

@@ -54,7 +54,9 @@ class Trainer:
         if pc is None:
             world = init_distributed()
             tp = min(cfg.runtime.tensor_parallel_size, world)
-            pc = build_context(tp, cfg.runtime.sequence_parallel, cfg.runtime.comm_backend) if world > 1 else ParallelContext()
+            cp = cfg.runtime.context_parallel_size if world > 1 else 1
+            pc = (build_context(tp, cfg.runtime.sequence_parallel, cfg.runtime.comm_backend, cp, cfg.runtime.context_parallel_mode)
+                  if world > 1 else ParallelContext())
         self.pc = pc
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
@@ -113,13 +115,15 @@ class Trainer:
         S, mb = cfg.data.seq_len, cfg.training.micro_batch_size
         if cfg.bench.synthetic != "none" or not path:
             kind = cfg.bench.synthetic if cfg.bench.synthetic != "none" else "uniform"
-            need = S * mb * self.accum * pc.dp_size * 4 + 1
+            need = S * mb * self.accum * (pc.dp_size // pc.cp_size) * 4 + 1
             ds = SyntheticDataset(cfg.model.vocab_size, max(need, S * 64 + 1), kind, cfg.bench.data_seed, cfg.bench.zipf_s)
             shuffle = False
         else:
             ds = BinaryDataset.open(path)
             shuffle = True
-        return DataLoader(ds, mb, S, shuffle=shuffle, seed=cfg.runtime.seed, dp_rank=pc.dp_rank, dp_size=pc.dp_size)
+        # the ranks of a context-parallel group read the same batch and keep their slice of the sequence
+        return DataLoader(ds, mb, S, shuffle=shuffle, seed=cfg.runtime.seed, dp_rank=pc.dp_rank // pc.cp_size,
+                          dp_size=pc.dp_size // pc.cp_size)
 
     # ------------------------------------------------------------------ step
     def train_step(self, batches: List[Batch]) -> torch.Tensor:
@@ -145,10 +149,15 @@ class Trainer:
         for b in batches:
             ids = b.input.to(self.device, non_blocking=True)
             tgt = b.target.to(self.device, non_blocking=True)
+            pos0 = 0
+            if self.pc.cp_size > 1:
+                sl = ids.shape[1] // self.pc.cp_size
+                pos0 = self.pc.cp_rank * sl
+                ids, tgt = ids[:, pos0:pos0 + sl].contiguous(), tgt[:, pos0:pos0 + sl].contiguous()
             denom = float(tgt.numel() * n_micro)
             if self.zero3:
                 self.flat.before_forward()
-            loss = self.model(ids, tgt, loss_denominator=denom, grad_scale=scale)
+            loss = self.model(ids, tgt, pos0=pos0, loss_denominator=denom, grad_scale=scale)
             loss.backward()              # grad_scale is applied inside the loss op's backward
             if self.zero3:
                 self.flat.after_backward()
@@ -159,7 +168,7 @@ class Trainer:
         self.optimizer.step(lr)
         self.scheduler.step()
         self.step += 1
-        self.tokens_seen += sum(b.num_tokens for b in batches) * self.pc.dp_size
+        self.tokens_seen += sum(b.num_tokens for b in batches) * (self.pc.dp_size // self.pc.cp_size)
         return total
 
     def finish_step(self, loss_dev: torch.Tensor) -> float:

@@ -3,6 +3,7 @@
 modes:
   fused   - fused ag_gemm / gemm_rs against the library (NCCL) path, repeated calls (GPU)
   tp      - a small GPT trained with TP=world (+sequence parallel) against the same model on one rank
+  cp      - ring attention and a context-parallel GPT against the single-rank result
   timeout - a fused wait that nothing satisfies must return with the timeout status, not hang (GPU)
 """
 import os
@@ -120,6 +121,57 @@ def mode_tp(pc, dev, backend, dtype):
         for a, b in zip(losses, ref):
             assert abs(a - b) < tol * max(1.0, abs(b)), f"TP losses {losses} differ from single-rank {ref}"
         print(f"TP_OK backend={backend} losses={[round(x, 4) for x in losses]} ref={[round(x, 4) for x in ref]}")
+    dist.barrier()
+
+
+def mode_cp(dev, dtype, tp, cp_mode="ring"):
+    """Ring attention against attention over the whole sequence (forward and gradients), then a small GPT
+    trained with the sequence split over a context-parallel group against the same model on one rank."""
+    from elfa_b200.ops.attention import attention_ref
+    from elfa_b200.parallel.mesh import ParallelContext
+    from elfa_b200.parallel.ring_attention import ring_attention
+    from elfa_b200.parallel.ulysses import ulysses_attention
+    from elfa_b200.trainer import Trainer
+    world, rank = dist.get_world_size(), dist.get_rank()
+    cp = world // tp
+    pc = build_context(tp, True, "nccl", cp_size=cp, cp_mode=cp_mode)
+    assert pc.cp_size == cp and len(pc.cp_ranks) == cp
+    tdt = torch.float32 if dtype == "fp32" else torch.bfloat16
+    g = torch.Generator().manual_seed(5)
+    S, B, H, hd = 128 * cp, 2, 2, 64
+    full = torch.randn(S, B, 3, H, hd, generator=g).to(dev, tdt)
+    dout = torch.randn(S, B, H * hd, generator=g).to(dev, tdt)
+    sl, c = S // cp, pc.cp_rank
+    for causal in (True, False):
+        ref_in = full.float().clone().requires_grad_(True)
+        ref = attention_ref(ref_in, causal=causal)
+        ref.backward(dout.float())
+        loc = full[c * sl:(c + 1) * sl].clone().requires_grad_(True)
+        if cp_mode == "ulysses":
+            out = ulysses_attention(loc, pc.cp_group, causal=causal)
+        else:
+            out = ring_attention(loc, pc.cp_group, causal=causal)
+        out.backward(dout[c * sl:(c + 1) * sl])
+        tol = 1e-4 if dtype == "fp32" else 3e-2
+        tol_g = tol * (1.0 + max(1.0, ref_in.grad.abs().max().item()))
+        e_o = (out.float() - ref[c * sl:(c + 1) * sl]).abs().max().item()
+        e_g = (loc.grad.float() - ref_in.grad[c * sl:(c + 1) * sl]).abs().max().item()
+        assert e_o < tol and e_g < tol_g, f"ring attention causal={causal}: out err {e_o}, grad err {e_g}"
+    cfg = small_cfg(dtype, tp, "nccl")
+    cfg.runtime.world_size = world
+    cfg.runtime.context_parallel_size = cp
+    cfg.runtime.context_parallel_mode = cp_mode
+    cfg.runtime.zero_stage = 1
+    tr = Trainer(cfg, device=dev, pc=pc, telemetry=False)
+    losses = tr.run(max_steps=4)
+    if rank == 0:
+        cfg1 = small_cfg(dtype, 1, "nccl")
+        cfg1.runtime.world_size = 1
+        ref_l = Trainer(cfg1, device=dev, pc=ParallelContext(), telemetry=False).run(max_steps=4)
+        tol = 2e-4 if dtype == "fp32" else 0.05
+        for a, b in zip(losses, ref_l):
+            assert abs(a - b) < tol * max(1.0, abs(b)), f"context-parallel losses {losses} differ from single-rank {ref_l}"
+        print(f"CP_OK mode={cp_mode} cp={cp} tp={tp} losses={[round(x, 4) for x in losses]} ref={[round(x, 4) for x in ref_l]}")
     dist.barrier()
 
 
@@ -266,7 +318,7 @@ def main():
     mode = sys.argv[1]
     backend = sys.argv[2] if len(sys.argv) > 2 else "nccl"
     dtype = sys.argv[3] if len(sys.argv) > 3 else "bf16"
-    use_cuda = torch.cuda.is_available() and mode not in ("tp_cpu", "zero_cpu", "ckpt_cpu", "killrank_cpu")
+    use_cuda = torch.cuda.is_available() and mode not in ("tp_cpu", "zero_cpu", "ckpt_cpu", "killrank_cpu", "cp_cpu")
     world = init_distributed("nccl" if use_cuda else "gloo")
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if use_cuda else torch.device("cpu")
     if mode == "killrank_cpu":
@@ -274,6 +326,10 @@ def main():
         return
     if mode == "ckpt_cpu":
         mode_ckpt(dev, int(sys.argv[2]), sys.argv[3])
+        dist.destroy_process_group()
+        return
+    if mode in ("cp", "cp_cpu"):
+        mode_cp(dev, dtype, int(sys.argv[4]) if len(sys.argv) > 4 else 1, sys.argv[5] if len(sys.argv) > 5 else "ring")
         dist.destroy_process_group()
         return
     if mode in ("zero", "zero_cpu"):

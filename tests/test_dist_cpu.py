@@ -23,6 +23,13 @@ def test_tp_sp_matches_single_rank_on_cpu(world):
     assert "TP_OK" in r.stdout
 
 
+@pytest.mark.parametrize("world,tp,mode", [(2, 1, "ring"), (4, 2, "ring"), (2, 1, "ulysses")])
+def test_context_parallel_attention_and_training_on_cpu(world, tp, mode):
+    r = _run(world, ["cp_cpu", "nccl", "fp32", str(tp), mode], 29660 + world + (10 if mode == "ulysses" else 0))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "CP_OK" in r.stdout
+
+
 @pytest.mark.parametrize("stage", [0, 1, 3])
 def test_zero_data_parallel_matches_single_rank_on_cpu(stage):
     r = _run(2, ["zero_cpu", "nccl", "fp32", str(stage)], 29621 + stage)

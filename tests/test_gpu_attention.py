@@ -53,3 +53,23 @@ def test_attention_backward(cuda_device, S, B, H, hd, causal):
     for name, i in (("dq", 0), ("dk", 1), ("dv", 2)):
         e = err[:, :, i].max().item()
         assert e < 0.02 * max(scale, 1.0) + 0.02, f"{name}: max err {e} (grad scale {scale})"
+
+
+@pytest.mark.parametrize("S,B,H,hd,world", [(512, 1, 2, 128, 4), (768, 2, 2, 64, 3), (256, 1, 1, 128, 2)])
+def test_ring_attention_blocks_on_one_gpu(cuda_device, S, B, H, hd, world):
+    """The block kernels of ring attention (unmasked blocks, log-sum-exp merge, backward with the global
+    log-sum-exp) for every rank of a ring, run one after the other on this GPU, against fp32 attention
+    over the whole sequence."""
+    from elfa_b200.parallel.ring_attention import ring_attention_emulated
+    qkv = _qkv(S, B, H, hd, cuda_device, seed=11)
+    g = torch.randn(S, B, H * hd, device=cuda_device, dtype=torch.bfloat16)
+    out, dqkv = ring_attention_emulated(qkv, world, causal=True, dout=g)
+    torch.cuda.synchronize()
+    assert native.status() == 0
+    ref_in = qkv.float().requires_grad_(True)
+    ref = ops.attention_ref(ref_in, causal=True)
+    ref.backward(g.float())
+    assert (out.float() - ref).abs().max().item() < 0.03
+    scale = ref_in.grad.abs().max().item()
+    e = (dqkv.float() - ref_in.grad).abs().max().item()
+    assert e < 0.03 * max(scale, 1.0) + 0.03, f"max gradient err {e} (grad scale {scale})"

@@ -35,6 +35,13 @@ def test_fused_ag_gemm_and_gemm_rs(cuda_device):
     assert "FUSED_OK" in r.stdout
 
 
+@pytest.mark.parametrize("mode", ["ring", "ulysses"])
+def test_context_parallel_attention_and_training(cuda_device, mode):
+    r = _run(["cp", "nccl", "bf16", "1", mode], 29710 if mode == "ring" else 29711)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "CP_OK" in r.stdout
+
+
 @pytest.mark.parametrize("backend", ["nccl", "fused"])
 def test_tp_training_matches_single_gpu(cuda_device, backend):
     r = _run(["tp", backend, "bf16"], 29702 if backend == "nccl" else 29703)
