@@ -16,6 +16,11 @@ CUDA events (max over ranks):
     from pinned host memory and the loss read back to the host every step.
 The working set of a step (tens of GB) is far larger than L2, so no explicit L2 flush is needed.
 Prints ONE JSON line on rank 0.
+
+``--config configs/bench/gpt350m_zero1.yaml`` (or ``gpt1p3b_zero3.yaml``, ``gpt13b_tp4dp2_nvfp4.yaml``) runs the
+other benchmark configurations with the parallelism their file names: tensor parallel size ``min(file, N)``,
+the remaining ranks data parallel with the file's ZeRO stage; pure data-parallel files keep the micro-batch
+per GPU fixed (weak scaling).
 """
 from __future__ import annotations
 
@@ -126,9 +131,8 @@ def main() -> int:
     native.lib.load()
 
     cfg = Config.from_file(args.config)
+    yaml_tp, yaml_world = cfg.runtime.tensor_parallel_size, cfg.runtime.world_size
     cfg.runtime.world_size = world
-    cfg.runtime.tensor_parallel_size = world
-    cfg.runtime.zero_stage = 0
     if args.comm:
         cfg.runtime.comm_backend = args.comm
     cfg.checkpoint.dir = ""
@@ -138,13 +142,31 @@ def main() -> int:
         cfg.model.num_layers = args.layers
     if args.global_batch:
         cfg.training.global_batch_size = args.global_batch
-    mb = args.micro_batch or 4      # 4 sequences of 4096 tokens per micro-batch: 160 GB peak on one GPU, less with tensor parallelism
+    if yaml_tp == yaml_world:
+        # the headline configuration: tensor + sequence parallel over all N GPUs, fixed global batch (strong scaling)
+        cfg.runtime.tensor_parallel_size = world
+        cfg.runtime.zero_stage = 0
+        mb = args.micro_batch or 4      # 4 sequences of 4096 tokens per micro-batch: 160 GB peak on one GPU, less with tensor parallelism
+        scaling, metric = "strong", METRIC
+    else:
+        # the data-parallel configurations (ZeRO stage from the file): tp = min(file's tp, N), the rest is data parallel
+        tp = min(yaml_tp, world)
+        dp = world // tp
+        cfg.runtime.tensor_parallel_size = tp
+        if dp == 1:
+            cfg.runtime.zero_stage = 0
+        mb = args.micro_batch or cfg.training.micro_batch_size
+        if yaml_tp == 1 and not args.global_batch:      # fixed micro-batch per GPU: weak scaling
+            cfg.training.global_batch_size = mb * dp
+        scaling = "weak" if yaml_tp == 1 else "strong"
+        metric = f"tokens/sec/box (max over ranks) {cfg.model.name}"
     cfg.training.micro_batch_size = mb
-    cfg.training.gradient_accumulation_steps = cfg.training.global_batch_size // mb
+    dp_size = world // cfg.runtime.tensor_parallel_size
+    cfg.training.gradient_accumulation_steps = max(1, cfg.training.global_batch_size // (mb * dp_size))
     trainer = Trainer(cfg, telemetry=False)
     rank = trainer.pc.rank
     S, G = cfg.data.seq_len, cfg.training.global_batch_size
-    n_micro = G // mb
+    n_micro = cfg.training.gradient_accumulation_steps
     tokens_per_step = G * S
 
     # synthetic Zipf tokens, one global batch per step, staged in pinned host memory
@@ -211,16 +233,25 @@ def main() -> int:
         except OSError:
             pass
         flops = model_flops_per_token(cfg)
+        tpn = cfg.runtime.tensor_parallel_size
+        if cfg.quant.attention == "none" and cfg.quant.mlp == "none":
+            dtype_note = "bf16 (fp32 master weights / moments / grad accumulation)"
+        else:
+            dtype_note = (f"bf16 ({cfg.quant.attention.upper()} / {cfg.quant.mlp.upper()} QAT on the attention / MLP GEMMs: forward GEMMs multiply block-scaled "
+                          "payloads on the tensor cores at N = 1; at N > 1 the column-parallel layers all-gather quantised payloads and multiply them block-scaled, "
+                          "the row-parallel GEMM->reduce-scatter kernel multiplies fake-quantised bf16 operands (the same product); backward GEMMs bf16; "
+                          "fp32 master weights / moments / grad accumulation)")
+        parallelism = "single" if world == 1 else "+".join(
+            ([f"tp{tpn}+sp"] if tpn > 1 else []) + ([f"dp{dp_size}-zero{cfg.runtime.zero_stage}"] if dp_size > 1 else []))
         peak = peaks.get("bf16_tflops_sustained", 1400.0) * 1e12
         out = {
-            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16 (MXFP8 QAT: forward GEMMs multiply e4m3 payloads with ue8m0 block scales - block-scaled tensor-core MMA at 1 GPU, "
-                     "fake-quantised bf16 operands in the tensor-parallel kernels; backward GEMMs bf16; fp32 master weights / moments / grad accumulation)",
-            "data": "synthetic Zipf(1.1) token ids (seed 3), random-init N(0,0.02) weights",
+            "metric": metric, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+            "dtype": dtype_note,
+            "data": f"synthetic Zipf({cfg.bench.zipf_s}) token ids (seed {cfg.bench.data_seed}), random-init N(0,{cfg.bench.init_std}) weights",
             "config": {"model": cfg.model.name, "layers": cfg.model.num_layers, "d_model": cfg.model.hidden_dim,
                        "heads": cfg.model.num_heads, "ffn": cfg.model.intermediate_dim, "vocab": cfg.model.vocab_size,
-                       "global_batch": G, "seq_len": S, "micro_batch": mb, "parallelism": f"tp{world}+sp" if world > 1 else "single",
+                       "global_batch": G, "seq_len": S, "micro_batch": mb, "parallelism": parallelism,
                        "comm_backend": cfg.runtime.comm_backend, "quant": {"attention": cfg.quant.attention, "mlp": cfg.quant.mlp},
                        "l2": "per-step working set (tens of GB) exceeds the 126 MB L2; no explicit flush"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 2 * G * S * 8, "d2h_bytes_per_step": 4,
