@@ -1,0 +1,142 @@
+"""A host model of the device-side flag protocols, with threads as ranks and random delays.
+
+``compute-sanitizer --tool racecheck`` sees one GPU; the protocols here synchronise several. Their rules are
+therefore also written down as plain Python over shared lists, run with one thread per rank and random sleeps
+between every step, and checked for the two properties that matter: nothing is read before it was written
+for this operation, and nothing is overwritten while a peer may still read it.
+
+Modelled (same rules as the kernels and their host bookkeeping):
+
+* :class:`PushGatherModel` - the all-gather of the fused all-gather->GEMM kernel (``parallel/fused.py``,
+  ``csrc/gemm_bf16.cu``): a ring of ``ring`` slots per rank, every rank pushes its shard into the slot of
+  every peer and then raises that peer's arrival counter; counters only grow, the wait target of the
+  ``n``-th use of a slot is ``(n + 1) * world``. With ``ring=2`` the protocol is safe; ``ring=1`` is the
+  negative control (a fast rank overwrites data a slow one has not read yet).
+* :class:`MailboxModel` - the two-slot neighbour mailbox of ``parallel/sp.py`` (``csrc/p2p.cu``):
+  arrival counter on the receiver, acknowledgement counter on the sender, a send waits for the
+  acknowledgement of the message that used the same slot two sends ago.
+
+Every wait is bounded, as on the device: when the limit passes the rank records a timeout status and stops
+(`status` is non-zero), it never spins for ever.
+
+reference: ``scripts/profile.sh:43-57`` (``compute-sanitizer`` memcheck / racecheck on the single-GPU smoke test
+is all the reference has).
+"""
+from __future__ import annotations
+
+import random
+import threading
+import time
+from typing import List, Optional
+
+TIMEOUT = 1
+
+
+class _Rank:
+    def __init__(self):
+        self.status = 0
+        self.errors: List[str] = []
+
+
+def _wait(pred, limit_s: float) -> bool:
+    t0 = time.perf_counter()
+    while not pred():
+        if time.perf_counter() - t0 > limit_s:
+            return False
+        time.sleep(0)
+    return True
+
+
+class PushGatherModel:
+    def __init__(self, world: int, ring: int = 2, seed: int = 0, max_delay_s: float = 2e-4, wait_limit_s: float = 5.0,
+                 skip_signal: Optional[tuple] = None):
+        self.world, self.ring = world, ring
+        self.rng = random.Random(seed)
+        self.max_delay, self.limit = max_delay_s, wait_limit_s
+        self.skip_signal = skip_signal                    # (rank, op): that rank does not raise the counters of that op
+        # slots[rank][slot][source] = stamp (op, source) of the shard last written there
+        self.slots = [[[None] * world for _ in range(ring)] for _ in range(world)]
+        self.arrivals = [[0] * ring for _ in range(world)]
+        self.lock = threading.Lock()                      # stands for the atomicity of one counter increment
+        self.ranks = [_Rank() for _ in range(world)]
+
+    def _delay(self, rng):
+        time.sleep(rng.random() * self.max_delay)
+
+    def _run_rank(self, r: int, ops: int):
+        rng = random.Random(self.rng.random() + r)
+        me = self.ranks[r]
+        for n in range(ops):
+            slot = n % self.ring
+            target = (n // self.ring + 1) * self.world   # arrivals promised to this slot so far (host bookkeeping)
+            for peer in range(self.world):               # push: data first, then the counter (release order)
+                self._delay(rng)
+                self.slots[peer][slot][r] = (n, r)
+                if self.skip_signal == (r, n):
+                    continue
+                with self.lock:
+                    self.arrivals[peer][slot] += 1
+            if not _wait(lambda: self.arrivals[r][slot] >= target, self.limit):
+                me.status = TIMEOUT                      # the kernel sets the status word and returns
+                return
+            for src in range(self.world):                # consume (the GEMM's tile loads)
+                self._delay(rng)
+                got = self.slots[r][slot][src]
+                if got != (n, src):
+                    me.errors.append(f"rank {r} op {n}: slot {slot} source {src} holds {got}")
+
+    def run(self, ops: int) -> List[_Rank]:
+        ts = [threading.Thread(target=self._run_rank, args=(r, ops)) for r in range(self.world)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+        return self.ranks
+
+
+class MailboxModel:
+    """Ring of ``world`` ranks, each sends ``msgs`` messages to its right neighbour and receives as many from the left."""
+
+    def __init__(self, world: int, seed: int = 0, max_delay_s: float = 2e-4, wait_limit_s: float = 5.0, wait_for_ack: bool = True):
+        self.world = world
+        self.rng = random.Random(seed)
+        self.max_delay, self.limit, self.wait_for_ack = max_delay_s, wait_limit_s, wait_for_ack
+        self.box = [[None, None] for _ in range(world)]   # two slots per receiver
+        self.arrivals = [0] * world
+        self.acks = [0] * world                           # on the sender: messages its right neighbour has consumed
+        self.ranks = [_Rank() for _ in range(world)]
+
+    def _sender(self, r: int, msgs: int):
+        rng = random.Random(self.rng.random() + r)
+        right = (r + 1) % self.world
+        for m in range(msgs):
+            if m >= 2 and self.wait_for_ack and not _wait(lambda: self.acks[r] >= m - 1, self.limit):
+                self.ranks[r].status = TIMEOUT
+                return
+            time.sleep(rng.random() * self.max_delay)
+            self.box[right][m % 2] = (m, r)
+            self.arrivals[right] = m + 1                  # single writer: the left neighbour
+
+    def _receiver(self, r: int, msgs: int):
+        rng = random.Random(self.rng.random() + 100 + r)
+        left = (r - 1) % self.world
+        for m in range(msgs):
+            if not _wait(lambda: self.arrivals[r] >= m + 1, self.limit):
+                self.ranks[r].status = TIMEOUT
+                return
+            time.sleep(rng.random() * self.max_delay)
+            got = self.box[r][m % 2]
+            if got != (m, left):
+                self.ranks[r].errors.append(f"rank {r} message {m}: slot holds {got}")
+            self.acks[left] = m + 1                       # acknowledge after the copy out of the slot
+
+    def run(self, msgs: int) -> List[_Rank]:
+        ts = []
+        for r in range(self.world):
+            ts.append(threading.Thread(target=self._sender, args=(r, msgs)))
+            ts.append(threading.Thread(target=self._receiver, args=(r, msgs)))
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+        return self.ranks

@@ -107,6 +107,9 @@ class Trainer:
         hb_dir = os.environ.get("ELFA_HEARTBEAT_DIR", "")
         self.heartbeat = Heartbeat(hb_dir, pc.rank, pc.world_size) if hb_dir and pc.world_size > 1 else None
         self.heartbeat_timeout = float(os.environ.get("ELFA_HEARTBEAT_TIMEOUT_S", "30"))
+        # phase timer + NVTX ranges (ELFA_TRACE=1); inactive it costs one branch per phase
+        from .utils.tracing import PhaseTimer
+        self.tracer = PhaseTimer(self.device)
 
     # ------------------------------------------------------------------ data
     def make_loader(self, data_path: Optional[str] = None) -> DataLoader:
@@ -157,15 +160,18 @@ class Trainer:
             denom = float(tgt.numel() * n_micro)
             if self.zero3:
                 self.flat.before_forward()
-            loss = self.model(ids, tgt, pos0=pos0, loss_denominator=denom, grad_scale=scale)
-            loss.backward()              # grad_scale is applied inside the loss op's backward
+            with self.tracer.phase("forward"):
+                loss = self.model(ids, tgt, pos0=pos0, loss_denominator=denom, grad_scale=scale)
+            with self.tracer.phase("backward"):
+                loss.backward()          # grad_scale is applied inside the loss op's backward
             if self.zero3:
                 self.flat.after_backward()
             total = loss.detach() if total is None else total + loss.detach()
         if self.faults and self.faults.active("nan_grad", self.pc.rank, self.step) is not None:
             self.flat.grads[:1].fill_(float("nan"))     # the optimizer's non-finite guard must skip this step
         lr = self.scheduler.get_lr()
-        self.optimizer.step(lr)
+        with self.tracer.phase("optimizer"):
+            self.optimizer.step(lr)
         self.scheduler.step()
         self.step += 1
         self.tokens_seen += sum(b.num_tokens for b in batches) * (self.pc.dp_size // self.pc.cp_size)

@@ -242,3 +242,43 @@ def test_launcher_runs_a_command_and_resolves_latest_checkpoint(tmp_path):
         assert out[-1].endswith("step_12")
     except (FileNotFoundError, ValueError, SystemExit):
         pass          # directories without a manifest are not checkpoints for the resolver: that refusal is fine too
+
+
+def test_flag_protocol_models_with_threads_as_ranks():
+    """The slot / counter rules of the fused all-gather and of the neighbour mailbox, run with one thread per
+    rank and random delays: two slots are safe, one slot is not, a missing signal ends in a timeout status."""
+    from elfa_b200.runtime.protocol_model import TIMEOUT, MailboxModel, PushGatherModel
+    for seed in range(3):
+        ranks = PushGatherModel(4, ring=2, seed=seed).run(40)
+        assert all(r.status == 0 and not r.errors for r in ranks), [r.errors[:2] for r in ranks]
+    broken = 0
+    for seed in range(6):            # negative control: a single slot is overwritten before slow ranks have read it
+        ranks = PushGatherModel(4, ring=1, seed=seed).run(60)
+        broken += any(r.errors for r in ranks)
+    assert broken > 0
+    ranks = PushGatherModel(3, ring=2, seed=1, wait_limit_s=0.3, skip_signal=(1, 2)).run(6)
+    assert any(r.status == TIMEOUT for r in ranks)           # bounded: every thread returned
+    ranks = MailboxModel(4, seed=2).run(50)
+    assert all(r.status == 0 and not r.errors for r in ranks), [r.errors[:2] for r in ranks]
+
+
+def test_phase_timer_and_chrome_trace(tmp_path):
+    import json
+    import torch
+    from elfa_b200.utils.tracing import PhaseTimer, nvtx_range
+    t = PhaseTimer(torch.device("cpu"), active=True)
+    for _ in range(3):
+        with t.phase("forward"):
+            with nvtx_range("inner"):
+                torch.randn(64, 64) @ torch.randn(64, 64)
+        with t.phase("backward"):
+            pass
+    s = t.summary()
+    assert s["forward"]["calls"] == 3 and s["backward"]["calls"] == 3 and s["forward"]["ms"] >= 0.0
+    t.write_chrome_trace(str(tmp_path / "trace.json"))
+    ev = json.load(open(tmp_path / "trace.json"))["traceEvents"]
+    assert len(ev) == 6 and ev[0]["name"] == "forward" and ev[0]["ph"] == "X"
+    off = PhaseTimer(torch.device("cpu"), active=False)
+    with off.phase("x"):
+        pass
+    assert off.summary() == {}
