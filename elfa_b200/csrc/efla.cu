@@ -2,8 +2,8 @@
 //
 // EFLA, per (batch, head), state S [d, d] fp32 (row = key index i, column = value index j):
 //   lam = |k|^2, c = (1 - exp(-beta lam)) / lam, p = S^T k, e = v - p, S += c k e^T, o = p + c lam e
-// (o equals S_new^T k). One CTA per (batch, head); thread j keeps column j of S in registers for the
-// whole sequence (forward) so the state never leaves the chip and is never rounded to bf16 - the
+// (o equals S_new^T k). Forward: one warp per (batch, head, 32 value columns); lane j keeps column j of S in
+// registers for the whole sequence so the state never leaves the chip and is never rounded to bf16 - the
 // reference rounds the bf16 state in global memory on every token and launches once per chunk
 // (reference: kernels/cuda/efla.cu:121-197 forward, :199-271 state history, :273-401 backward
 // without the beta gradient; fp32 variant kernels/cuda/efla_scan.cu:99-260 with grad_beta via
@@ -35,174 +35,297 @@ __device__ __forceinline__ void efla_coeff(float beta, float lam, float& c, floa
   }
 }
 
-// block-wide sum of one float per thread (blockDim.x = d <= 128), result broadcast
-__device__ __forceinline__ float block_sum(float v, float* red, int nwarps) {
-  v = warp_sum(v);
-  __syncthreads();
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
-  __syncthreads();
-  float s = 0.f;
-  for (int i = 0; i < nwarps; ++i) s += red[i];
-  return s;
-}
-
 // k, v, o: [B, T, H, D] bf16. state0 / state_out: [B, H, D, D] fp32. ckpt: [B, H, nchunks, D, D] holds the
 // state at the START of every chunk.
+// The columns of S evolve independently (column j needs k_t, c_t and v_t[j] only), so a CTA is ONE warp that
+// owns 32 columns: grid (B*H, D/32), no block-wide barrier anywhere. Time is walked in tiles of EFLA_TT tokens:
+// the warp first brings the tile's keys (fp32) and its 32 value columns into shared memory with independent
+// coalesced loads and computes lam / c for all EFLA_TT tokens at once (lane r owns token r), then the
+// sequential part reads keys as 16-byte shared-memory broadcasts and touches global memory only for the
+// output. The dot product runs on four accumulators to shorten its dependency chain.
+constexpr int EFLA_TT = 32;
+
 template <int D>
-__global__ void __launch_bounds__(D) efla_scan_fwd_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
-                                                          const float* __restrict__ beta_ptr, const float* __restrict__ state0,
-                                                          __nv_bfloat16* __restrict__ o, float* __restrict__ state_out,
-                                                          float* __restrict__ ckpt, int T, int H, int chunk) {
-  __shared__ float sk[D];
-  __shared__ float red[4];
-  const int bh = blockIdx.x, b = bh / H, h = bh % H, j = threadIdx.x;
+__global__ void __launch_bounds__(32) efla_scan_fwd_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+                                                           const float* __restrict__ beta_ptr, const float* __restrict__ state0,
+                                                           __nv_bfloat16* __restrict__ o, float* __restrict__ state_out,
+                                                           float* __restrict__ ckpt, int T, int H, int chunk) {
+  __shared__ __align__(16) float sk[EFLA_TT][D];
+  __shared__ float sv[EFLA_TT][32];
+  __shared__ float sc[EFLA_TT], slam[EFLA_TT];
+  const int bh = blockIdx.x, b = bh / H, h = bh % H, lane = threadIdx.x;
+  const int col = blockIdx.y * 32 + lane;
   const float beta = *beta_ptr;
   float S[D];
   if (state0) {
 #pragma unroll
-    for (int i = 0; i < D; ++i) S[i] = state0[((long long)bh * D + i) * D + j];
+    for (int i = 0; i < D; ++i) S[i] = state0[((long long)bh * D + i) * D + col];
   } else {
 #pragma unroll
     for (int i = 0; i < D; ++i) S[i] = 0.f;
   }
   const int nchunks = (T + chunk - 1) / chunk;
-  for (int t = 0; t < T; ++t) {
-    if (ckpt && t % chunk == 0) {
-      float* dst = ckpt + ((long long)bh * nchunks + t / chunk) * D * D;
+  for (int t0 = 0; t0 < T; t0 += EFLA_TT) {
+    const int n = min(EFLA_TT, T - t0);
+    __syncwarp();                                        // the previous tile has been consumed
+    for (int r = 0; r < n; ++r) {
+      const long long row = (((long long)b * T + t0 + r) * H + h) * D;
 #pragma unroll
-      for (int i = 0; i < D; ++i) dst[i * D + j] = S[i];
+      for (int c = 0; c < D; c += 32) sk[r][c + lane] = __bfloat162float(k[row + c + lane]);
+      sv[r][lane] = __bfloat162float(v[row + col]);
     }
-    const long long off = (((long long)b * T + t) * H + h) * D + j;
-    const float kj = __bfloat162float(k[off]), vj = __bfloat162float(v[off]);
-    __syncthreads();
-    sk[j] = kj;
-    const float lam = block_sum(kj * kj, red, D / 32);   // contains the barrier that publishes sk
-    float c, d1, d2;
-    efla_coeff(beta, lam, c, d1, d2);
-    float p = 0.f;
+    __syncwarp();
+    if (lane < n) {                                      // lam and c of token `lane`; the rotated index keeps the banks apart
+      float lam = 0.f;
+#pragma unroll 8
+      for (int c = 0; c < D; ++c) {
+        const float x = sk[lane][(c + lane) % D];
+        lam += x * x;
+      }
+      float c_, d1, d2;
+      efla_coeff(beta, lam, c_, d1, d2);
+      slam[lane] = lam;
+      sc[lane] = c_;
+    }
+    __syncwarp();
+    for (int r = 0; r < n; ++r) {
+      const int t = t0 + r;
+      if (ckpt && t % chunk == 0) {
+        float* dst = ckpt + ((long long)bh * nchunks + t / chunk) * D * D;
 #pragma unroll
-    for (int i = 0; i < D; ++i) p += sk[i] * S[i];
-    const float e = vj - p;
-    const float ce = c * e;
+        for (int i = 0; i < D; ++i) dst[i * D + col] = S[i];
+      }
+      const float4* kr = reinterpret_cast<const float4*>(sk[r]);
+      float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
 #pragma unroll
-    for (int i = 0; i < D; ++i) S[i] += sk[i] * ce;
-    o[off] = __float2bfloat16(p + c * lam * e);
+      for (int i = 0; i < D / 4; ++i) {
+        const float4 kk = kr[i];
+        p0 += kk.x * S[4 * i];
+        p1 += kk.y * S[4 * i + 1];
+        p2 += kk.z * S[4 * i + 2];
+        p3 += kk.w * S[4 * i + 3];
+      }
+      const float p = (p0 + p1) + (p2 + p3);
+      const float c_ = sc[r], lam = slam[r];
+      const float e = sv[r][lane] - p;
+      const float ce = c_ * e;
+#pragma unroll
+      for (int i = 0; i < D / 4; ++i) {
+        const float4 kk = kr[i];
+        S[4 * i] += kk.x * ce;
+        S[4 * i + 1] += kk.y * ce;
+        S[4 * i + 2] += kk.z * ce;
+        S[4 * i + 3] += kk.w * ce;
+      }
+      o[(((long long)b * T + t) * H + h) * D + col] = __float2bfloat16(p + c_ * lam * e);
+    }
   }
   if (state_out) {
 #pragma unroll
-    for (int i = 0; i < D; ++i) state_out[((long long)bh * D + i) * D + j] = S[i];
+    for (int i = 0; i < D; ++i) state_out[((long long)bh * D + i) * D + col] = S[i];
   }
 }
 
-// Backward. Shared memory: S and dS as [D][D+1] fp32, vectors of D floats.
-// work: [B*H][chunk][D][D] fp32 scratch (state BEFORE each token of the current chunk).
+// Backward: the same warp-per-32-columns layout. Lane j keeps column j of G = dL/dS (the gradient with respect to
+// the state AFTER the current token) in registers for the whole sequence. Chunks are walked in reverse; inside a
+// chunk the states are recomputed from the chunk's saved boundary state and the state BEFORE every token goes to a
+// global workspace ([chunk, D, D] per (batch, head); a CTA touches only its own columns, so the lines stay in
+// L1 / L2), then the reverse-time recursion streams each of them twice:
+//   pass 1: p_j = sum_i k_i S_ij ;  e_j = v_j - p_j ;  G_ij += k_i do_j ;  w_j = sum_i G_ij k_i ;
+//           dv_j = de_j = c w_j ;  dp_j = -de_j ;  dc += e_j w_j (summed over the lanes, then over the column blocks)
+//   pass 2: r_ij = (S_ij + c k_i e_j) do_j + c G_ij e_j + S_ij dp_j ;  G_ij += k_i dp_j
+// dk_i = sum_j r_ij + 2 k_i dc dc/dlam needs a sum over ALL value columns: within the warp it goes through a
+// padded shared-memory transpose (lane j writes r_.j, lane i adds up row i), across the D/32 column blocks
+// through fp32 partial buffers that efla_bwd_finish_kernel adds up (fixed order: deterministic) together with
+// the lam term and the per-token beta gradient.
+// work: [B*H][chunk][D][D] fp32. dk_part: [D/32][rows][D] fp32, dc_part: [D/32][rows] fp32, rows = B*T*H.
 template <int D>
-__global__ void __launch_bounds__(D) efla_scan_bwd_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
-                                                          const float* __restrict__ beta_ptr, const float* __restrict__ ckpt,
-                                                          const __nv_bfloat16* __restrict__ dout, const float* __restrict__ dstate_out,
-                                                          __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv,
-                                                          float* __restrict__ dbeta, float* __restrict__ dstate0,
-                                                          float* __restrict__ work, int T, int H, int chunk) {
-  extern __shared__ float sm[];
-  constexpr int LD = D + 1;
-  float* sS = sm;                 // [D][LD]  state before the current token
-  float* sG = sS + D * LD;        // [D][LD]  gradient w.r.t. the state after the current token
-  float* sk = sG + D * LD;        // [D]
-  float* se = sk + D;             // [D] e = v - p
-  float* sdo = se + D;            // [D]
-  float* sde = sdo + D;           // [D]
-  float* sdp = sde + D;           // [D]
-  float* red = sdp + D;           // [4]
-  const int bh = blockIdx.x, b = bh / H, h = bh % H, x = threadIdx.x;
+__global__ void __launch_bounds__(32) efla_scan_bwd_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+                                                           const float* __restrict__ beta_ptr, const float* __restrict__ ckpt,
+                                                           const __nv_bfloat16* __restrict__ dout, const float* __restrict__ dstate_out,
+                                                           float* __restrict__ dk_part, __nv_bfloat16* __restrict__ dv,
+                                                           float* __restrict__ dc_part, float* __restrict__ dstate0,
+                                                           float* __restrict__ work, int B, int T, int H, int chunk) {
+  __shared__ __align__(16) float sk[EFLA_TT][D];
+  __shared__ float sv[EFLA_TT][32], sdo[EFLA_TT][32];
+  __shared__ float sc[EFLA_TT];
+  __shared__ float sred[D][33];
+  const int bh = blockIdx.x, b = bh / H, h = bh % H, lane = threadIdx.x;
+  const int col = blockIdx.y * 32 + lane;
+  const long long rows = (long long)B * T * H;
   const float beta = *beta_ptr;
   const int nchunks = (T + chunk - 1) / chunk;
   float* wk = work + (long long)bh * chunk * D * D;
-  for (int i = 0; i < D; ++i) sG[i * LD + x] = dstate_out ? dstate_out[((long long)bh * D + i) * D + x] : 0.f;
-  float dbeta_acc = 0.f;
+  float* dkp = dk_part + (long long)blockIdx.y * rows * D;
+  float* dcp = dc_part + (long long)blockIdx.y * rows;
+  float G[D];
+#pragma unroll
+  for (int i = 0; i < D; ++i) G[i] = dstate_out ? dstate_out[((long long)bh * D + i) * D + col] : 0.f;
+
+  // brings tokens [s0, s0 + n) into shared memory: keys (all D), this CTA's value / dout columns, c per token
+  auto load_tile = [&](int s0, int n, bool with_do) {
+    __syncwarp();
+    for (int r = 0; r < n; ++r) {
+      const long long row = (((long long)b * T + s0 + r) * H + h) * D;
+#pragma unroll
+      for (int c = 0; c < D; c += 32) sk[r][c + lane] = __bfloat162float(k[row + c + lane]);
+      sv[r][lane] = __bfloat162float(v[row + col]);
+      if (with_do) sdo[r][lane] = __bfloat162float(dout[row + col]);
+    }
+    __syncwarp();
+    if (lane < n) {
+      float lam = 0.f;
+#pragma unroll 8
+      for (int c = 0; c < D; ++c) {
+        const float x = sk[lane][(c + lane) % D];
+        lam += x * x;
+      }
+      float c_, d1, d2;
+      efla_coeff(beta, lam, c_, d1, d2);
+      sc[lane] = c_;
+    }
+    __syncwarp();
+  };
+
   for (int ch = nchunks - 1; ch >= 0; --ch) {
     const int t0 = ch * chunk, t1 = min(T, t0 + chunk);
-    // ---- recompute the states of this chunk (column x in registers), store S_before per token
+    // ---- recompute the states of this chunk, store the state BEFORE every token
     {
       float S[D];
       const float* src = ckpt + ((long long)bh * nchunks + ch) * D * D;
 #pragma unroll
-      for (int i = 0; i < D; ++i) S[i] = src[i * D + x];
-      for (int t = t0; t < t1; ++t) {
-        float* dst = wk + (long long)(t - t0) * D * D;
+      for (int i = 0; i < D; ++i) S[i] = src[i * D + col];
+      for (int s0 = t0; s0 < t1; s0 += EFLA_TT) {
+        const int n = min(EFLA_TT, t1 - s0);
+        load_tile(s0, n, false);
+        for (int r = 0; r < n; ++r) {
+          float* dst = wk + (long long)(s0 + r - t0) * D * D;
 #pragma unroll
-        for (int i = 0; i < D; ++i) dst[i * D + x] = S[i];
-        const long long off = (((long long)b * T + t) * H + h) * D + x;
-        const float kx = __bfloat162float(k[off]), vx = __bfloat162float(v[off]);
-        __syncthreads();
-        sk[x] = kx;
-        const float lam = block_sum(kx * kx, red, D / 32);
-        float c, d1, d2;
-        efla_coeff(beta, lam, c, d1, d2);
-        float p = 0.f;
+          for (int i = 0; i < D; ++i) dst[i * D + col] = S[i];
+          const float4* kr = reinterpret_cast<const float4*>(sk[r]);
+          float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
 #pragma unroll
-        for (int i = 0; i < D; ++i) p += sk[i] * S[i];
-        const float ce = c * (vx - p);
+          for (int i = 0; i < D / 4; ++i) {
+            const float4 kk = kr[i];
+            p0 += kk.x * S[4 * i];
+            p1 += kk.y * S[4 * i + 1];
+            p2 += kk.z * S[4 * i + 2];
+            p3 += kk.w * S[4 * i + 3];
+          }
+          const float ce = sc[r] * (sv[r][lane] - ((p0 + p1) + (p2 + p3)));
 #pragma unroll
-        for (int i = 0; i < D; ++i) S[i] += sk[i] * ce;
+          for (int i = 0; i < D / 4; ++i) {
+            const float4 kk = kr[i];
+            S[4 * i] += kk.x * ce;
+            S[4 * i + 1] += kk.y * ce;
+            S[4 * i + 2] += kk.z * ce;
+            S[4 * i + 3] += kk.w * ce;
+          }
+        }
       }
     }
-    __syncthreads();
-    // ---- reverse-time recursion over the chunk
-    for (int t = t1 - 1; t >= t0; --t) {
-      const long long off = (((long long)b * T + t) * H + h) * D + x;
-      const float kx = __bfloat162float(k[off]), vx = __bfloat162float(v[off]);
-      const float gox = __bfloat162float(dout[off]);
-      const float* src = wk + (long long)(t - t0) * D * D;
-      __syncthreads();
-      for (int i = 0; i < D; ++i) sS[i * LD + x] = src[i * D + x];   // S before token t
-      sk[x] = kx;
-      sdo[x] = gox;
-      const float lam = block_sum(kx * kx, red, D / 32);
-      float c, dc_db, dc_dl;
-      efla_coeff(beta, lam, c, dc_db, dc_dl);
-      // column sweep (x = value index j): p_j, e_j
-      float p = 0.f;
-      for (int i = 0; i < D; ++i) p += sk[i] * sS[i * LD + x];
-      const float e = vx - p;
-      se[x] = e;
-      __syncthreads();
-      // o = S'^T k: dS' += k do^T (column x gets k_i * do_x)
-      for (int i = 0; i < D; ++i) sG[i * LD + x] += sk[i] * gox;
-      __syncthreads();
-      // row sweep (x = key index i): a_i = sum_j S'_ij do_j, b_i = sum_j dS'_ij e_j
-      float a = 0.f, bsum = 0.f;
-      const float ck = c * kx;
-      for (int jj = 0; jj < D; ++jj) {
-        const float sp = sS[x * LD + jj] + ck * se[jj];     // S'_ij
-        a += sp * sdo[jj];
-        bsum += sG[x * LD + jj] * se[jj];
+    // ---- reverse-time recursion over the chunk (sub-tiles of EFLA_TT tokens, last one first)
+    const int ntiles = (t1 - t0 + EFLA_TT - 1) / EFLA_TT;
+    for (int ti = ntiles - 1; ti >= 0; --ti) {
+      const int s0 = t0 + ti * EFLA_TT, n = min(EFLA_TT, t1 - s0);
+      load_tile(s0, n, true);
+      for (int r = n - 1; r >= 0; --r) {
+        const int t = s0 + r;
+        const float* Sb = wk + (long long)(t - t0) * D * D + col;       // S before token t, column `col`: Sb[i * D]
+        const float4* kr = reinterpret_cast<const float4*>(sk[r]);
+        const float c_ = sc[r], go = sdo[r][lane];
+        // pass 1
+        float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f, w0 = 0.f, w1 = 0.f, w2 = 0.f, w3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < D / 4; ++i) {
+          const float4 kk = kr[i];
+          p0 += kk.x * Sb[(4 * i) * D];
+          p1 += kk.y * Sb[(4 * i + 1) * D];
+          p2 += kk.z * Sb[(4 * i + 2) * D];
+          p3 += kk.w * Sb[(4 * i + 3) * D];
+          G[4 * i] += kk.x * go;
+          G[4 * i + 1] += kk.y * go;
+          G[4 * i + 2] += kk.z * go;
+          G[4 * i + 3] += kk.w * go;
+          w0 += G[4 * i] * kk.x;
+          w1 += G[4 * i + 1] * kk.y;
+          w2 += G[4 * i + 2] * kk.z;
+          w3 += G[4 * i + 3] * kk.w;
+        }
+        const float e = sv[r][lane] - ((p0 + p1) + (p2 + p3));
+        const float w = (w0 + w1) + (w2 + w3);
+        const float de = c_ * w, dp = -de;
+        const long long row = ((long long)b * T + t) * H + h;
+        dv[row * D + col] = __float2bfloat16(de);
+        const float dc = warp_sum(e * w);
+        if (lane == 0) dcp[row] = dc;
+        // pass 2
+        const float ce = c_ * e;
+#pragma unroll
+        for (int i = 0; i < D / 4; ++i) {
+          const float4 kk = kr[i];
+          const float kv[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int ii = 4 * i + u;
+            const float sb = Sb[ii * D];
+            sred[ii][lane] = (sb + kv[u] * ce) * go + ce * G[ii] + sb * dp;
+            G[ii] += kv[u] * dp;
+          }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int m = 0; m < D / 32; ++m) {
+          const int ii = m * 32 + lane;
+          float acc = 0.f;
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) acc += sred[ii][jj];
+          dkp[row * D + ii] = acc;
+        }
+        __syncwarp();
       }
-      // dc = sum_i k_i b_i
-      const float dc = block_sum(kx * bsum, red, D / 32);
-      // column sweep: de_j = c * sum_i dS'_ij k_i ; dp = -de
-      float de = 0.f;
-      for (int i = 0; i < D; ++i) de += sG[i * LD + x] * sk[i];
-      de *= c;
-      sde[x] = de;
-      sdp[x] = -de;
-      __syncthreads();
-      // row sweep: g_i = sum_j S_ij dp_j  (p = S^T k -> dk += S dp)
-      float g = 0.f;
-      for (int jj = 0; jj < D; ++jj) g += sS[x * LD + jj] * sdp[jj];
-      const float dlam = dc * dc_dl;
-      const float dkx = a + c * bsum + g + 2.f * kx * dlam;
-      dbeta_acc += (x == 0) ? dc * dc_db : 0.f;
-      dk[off] = __float2bfloat16(dkx);
-      dv[off] = __float2bfloat16(de);
-      // dS (before token) = dS' + k dp^T
-      for (int i = 0; i < D; ++i) sG[i * LD + x] += sk[i] * sdp[x];
     }
   }
-  __syncthreads();
-  if (dstate0)
-    for (int i = 0; i < D; ++i) dstate0[((long long)bh * D + i) * D + x] = sG[i * LD + x];
-  if (x == 0) dbeta[bh] = dbeta_acc;
+  if (dstate0) {
+#pragma unroll
+    for (int i = 0; i < D; ++i) dstate0[((long long)bh * D + i) * D + col] = G[i];
+  }
 }
+
+// dk = sum of the column blocks' partial rows + 2 k dc dc/dlam (bf16); dbeta_tok[row] = dc dc/dbeta. One warp per row.
+__global__ void __launch_bounds__(256) efla_bwd_finish_kernel(const __nv_bfloat16* __restrict__ k, const float* __restrict__ beta_ptr,
+                                                              const float* __restrict__ dk_part, const float* __restrict__ dc_part,
+                                                              __nv_bfloat16* __restrict__ dk, float* __restrict__ dbeta_tok,
+                                                              long long rows, int D, int nb) {
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const float beta = *beta_ptr;
+  float kx[4], lam = 0.f;
+#pragma unroll
+  for (int m = 0; m < 4; ++m) {
+    const int c = m * 32 + lane;
+    kx[m] = c < D ? __bfloat162float(k[row * D + c]) : 0.f;
+    lam += kx[m] * kx[m];
+  }
+  lam = warp_sum(lam);
+  float dc = 0.f;
+  for (int q = 0; q < nb; ++q) dc += dc_part[q * rows + row];
+  float c_, dc_db, dc_dl;
+  efla_coeff(beta, lam, c_, dc_db, dc_dl);
+  const float dlam = dc * dc_dl;
+#pragma unroll
+  for (int m = 0; m < 4; ++m) {
+    const int c = m * 32 + lane;
+    if (c < D) {
+      float acc = 0.f;
+      for (int q = 0; q < nb; ++q) acc += dk_part[((long long)q * rows + row) * D + c];
+      dk[row * D + c] = __float2bfloat16(acc + 2.f * kx[m] * dlam);
+    }
+  }
+  if (lane == 0) dbeta_tok[row] = dc * dc_db;
+}
+
 
 // ------------------------------------------------------------------------------------ ShortConv
 __global__ void __launch_bounds__(256) shortconv_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
@@ -266,7 +389,7 @@ __global__ void __launch_bounds__(256) shortconv_bwd_dw_kernel(const __nv_bfloat
 template <int D>
 int launch_efla_fwd(const void* k, const void* v, const float* beta, const float* state0, void* o, float* state_out, float* ckpt, int B,
                     int T, int H, int chunk, cudaStream_t s) {
-  efla_scan_fwd_kernel<D><<<B * H, D, 0, s>>>(static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), beta, state0,
+  efla_scan_fwd_kernel<D><<<dim3(B * H, D / 32), 32, 0, s>>>(static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), beta, state0,
                                               static_cast<__nv_bfloat16*>(o), state_out, ckpt, T, H, chunk);
   ELFA_CUDA(cudaGetLastError());
   ::elfa::count_launches(1);
@@ -275,15 +398,17 @@ int launch_efla_fwd(const void* k, const void* v, const float* beta, const float
 
 template <int D>
 int launch_efla_bwd(const void* k, const void* v, const float* beta, const float* ckpt, const void* dout, const float* dstate_out,
-                    void* dk, void* dv, float* dbeta, float* dstate0, float* work, int B, int T, int H, int chunk, cudaStream_t s) {
-  const size_t smem = (size_t)(2 * D * (D + 1) + 5 * D + 8) * sizeof(float);
-  auto kern = efla_scan_bwd_kernel<D>;
-  if (smem > 48 * 1024) ELFA_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<B * H, D, smem, s>>>(static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), beta, ckpt,
-                              static_cast<const __nv_bfloat16*>(dout), dstate_out, static_cast<__nv_bfloat16*>(dk),
-                              static_cast<__nv_bfloat16*>(dv), dbeta, dstate0, work, T, H, chunk);
+                    void* dk, void* dv, float* dbeta_tok, float* dstate0, float* work, float* dk_part, float* dc_part, int B, int T,
+                    int H, int chunk, cudaStream_t s) {
+  efla_scan_bwd_kernel<D><<<dim3(B * H, D / 32), 32, 0, s>>>(
+      static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), beta, ckpt, static_cast<const __nv_bfloat16*>(dout),
+      dstate_out, dk_part, static_cast<__nv_bfloat16*>(dv), dc_part, dstate0, work, B, T, H, chunk);
   ELFA_CUDA(cudaGetLastError());
-  ::elfa::count_launches(1);
+  const long long rows = (long long)B * T * H;
+  efla_bwd_finish_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(k), beta, dk_part, dc_part,
+                                                                    static_cast<__nv_bfloat16*>(dk), dbeta_tok, rows, D, D / 32);
+  ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(2);
   return ELFA_OK;
 }
 
@@ -307,18 +432,20 @@ ELFA_API int elfa_efla_scan_fwd(const void* k, const void* v, const float* beta,
   }
 }
 
-// Gradients of elfa_efla_scan_fwd. dbeta: [B*H] partial sums (add them up); work: [B*H, chunk, d, d] fp32.
+// Gradients of elfa_efla_scan_fwd. dbeta_tok: [B*T*H] per-token terms (add them up); work: [B*H, chunk, d, d] fp32;
+// dk_part: [d/32, B*T*H, d] fp32 and dc_part: [d/32, B*T*H] fp32 are scratch (one slice per block of 32 value columns).
 ELFA_API int elfa_efla_scan_bwd(const void* k, const void* v, const float* beta, const float* ckpt, const void* dout,
-                                const float* dstate_out, void* dk, void* dv, float* dbeta, float* dstate0, float* work, int B, int T,
-                                int H, int d, int chunk, void* stream) {
-  ELFA_REQUIRE(k && v && beta && ckpt && dout && dk && dv && dbeta && work && B > 0 && T > 0 && H > 0 && chunk > 0,
+                                const float* dstate_out, void* dk, void* dv, float* dbeta_tok, float* dstate0, float* work,
+                                float* dk_part, float* dc_part, int B, int T, int H, int d, int chunk, void* stream) {
+  ELFA_REQUIRE(k && v && beta && ckpt && dout && dk && dv && dbeta_tok && work && dk_part && dc_part && B > 0 && T > 0 && H > 0 &&
+                   chunk > 0,
                "efla_scan_bwd: bad arguments");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (d) {
-    case 32: return launch_efla_bwd<32>(k, v, beta, ckpt, dout, dstate_out, dk, dv, dbeta, dstate0, work, B, T, H, chunk, s);
-    case 64: return launch_efla_bwd<64>(k, v, beta, ckpt, dout, dstate_out, dk, dv, dbeta, dstate0, work, B, T, H, chunk, s);
-    case 96: return launch_efla_bwd<96>(k, v, beta, ckpt, dout, dstate_out, dk, dv, dbeta, dstate0, work, B, T, H, chunk, s);
-    case 128: return launch_efla_bwd<128>(k, v, beta, ckpt, dout, dstate_out, dk, dv, dbeta, dstate0, work, B, T, H, chunk, s);
+    case 32: return launch_efla_bwd<32>(k, v, beta, ckpt, dout, dstate_out, dk, dv, dbeta_tok, dstate0, work, dk_part, dc_part, B, T, H, chunk, s);
+    case 64: return launch_efla_bwd<64>(k, v, beta, ckpt, dout, dstate_out, dk, dv, dbeta_tok, dstate0, work, dk_part, dc_part, B, T, H, chunk, s);
+    case 96: return launch_efla_bwd<96>(k, v, beta, ckpt, dout, dstate_out, dk, dv, dbeta_tok, dstate0, work, dk_part, dc_part, B, T, H, chunk, s);
+    case 128: return launch_efla_bwd<128>(k, v, beta, ckpt, dout, dstate_out, dk, dv, dbeta_tok, dstate0, work, dk_part, dc_part, B, T, H, chunk, s);
     default: set_last_error("efla_scan_bwd: head dimension must be 32, 64, 96 or 128"); return ELFA_ERR_UNSUPPORTED;
   }
 }

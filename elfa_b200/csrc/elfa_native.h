@@ -144,8 +144,8 @@ int elfa_prism_bwd(const void* u, const void* v, const unsigned long long* p, co
 int elfa_efla_scan_fwd(const void* k, const void* v, const float* beta, const float* state0, void* o, float* state_out,
                        float* ckpt, int B, int T, int H, int d, int chunk, void* stream);
 int elfa_efla_scan_bwd(const void* k, const void* v, const float* beta, const float* ckpt, const void* dout,
-                       const float* dstate_out, void* dk, void* dv, float* dbeta, float* dstate0, float* work, int B, int T,
-                       int H, int d, int chunk, void* stream);
+                       const float* dstate_out, void* dk, void* dv, float* dbeta_tok, float* dstate0, float* work,
+                       float* dk_part, float* dc_part, int B, int T, int H, int d, int chunk, void* stream);
 int elfa_shortconv_fwd(const void* x, const void* w, const void* bias, void* y, int B, int T, int C, int W, void* stream);
 int elfa_shortconv_bwd(const void* x, const void* w, const void* dy, void* dx, float* dw, float* db, int B, int T, int C, int W,
                        void* stream);

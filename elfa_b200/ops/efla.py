@@ -54,8 +54,9 @@ def efla_scan_ref(k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, state: O
 
 
 class _EflaScan(torch.autograd.Function):
-    """CUDA path: sequential-in-time kernels with the fp32 state on chip; backward recomputes the
-    states inside each chunk from the chunk-boundary states saved by forward."""
+    """CUDA path: sequential-in-time kernels, one warp per (batch, head, 32 value columns) with its columns
+    of the fp32 state in registers; backward recomputes the states inside each chunk from the
+    chunk-boundary states saved by forward."""
 
     @staticmethod
     def forward(ctx, k, v, beta, state, chunk):
@@ -78,12 +79,15 @@ class _EflaScan(torch.autograd.Function):
         B, T, H, d, chunk, has_state = ctx.cfg
         dk = torch.empty_like(kc)
         dv = torch.empty_like(vc)
-        dbeta = torch.zeros(B * H, dtype=torch.float32, device=kc.device)
+        rows = B * T * H
+        dbeta = torch.empty(rows, dtype=torch.float32, device=kc.device)                 # per-token terms, summed below
         ds0 = torch.empty((B, H, d, d), dtype=torch.float32, device=kc.device)
         work = torch.empty((B * H, chunk, d, d), dtype=torch.float32, device=kc.device)
+        dk_part = torch.empty((d // 32, rows, d), dtype=torch.float32, device=kc.device)  # one slice per block of 32 value columns
+        dc_part = torch.empty((d // 32, rows), dtype=torch.float32, device=kc.device)
         dso = ds_out.float().contiguous() if ds_out is not None else None
-        lib.call("elfa_efla_scan_bwd", kc, vc, bt, ckpt, do.contiguous(), dso, dk, dv, dbeta, ds0, work, B, T, H, d, chunk,
-                 stream_ptr(kc))
+        lib.call("elfa_efla_scan_bwd", kc, vc, bt, ckpt, do.contiguous(), dso, dk, dv, dbeta, ds0, work, dk_part, dc_part,
+                 B, T, H, d, chunk, stream_ptr(kc))
         return dk, dv, dbeta.sum().reshape(1), (ds0 if has_state else None), None
 
 

@@ -8,7 +8,7 @@ from elfa_b200.ops import efla as eops
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("B,T,H,d,chunk", [(1, 16, 1, 32, 16), (2, 50, 2, 64, 16), (1, 40, 2, 128, 8)])
+@pytest.mark.parametrize("B,T,H,d,chunk", [(1, 16, 1, 32, 16), (2, 50, 2, 64, 16), (1, 40, 2, 128, 8), (1, 70, 1, 96, 16), (2, 100, 2, 64, 32)])
 @pytest.mark.parametrize("with_state", [False, True])
 def test_efla_scan_forward_backward(cuda_device, B, T, H, d, chunk, with_state):
     torch.manual_seed(d + T)
