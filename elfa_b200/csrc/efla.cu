@@ -45,6 +45,51 @@ __device__ __forceinline__ void efla_coeff(float beta, float lam, float& c, floa
 // output. The dot product runs on four accumulators to shorten its dependency chain.
 constexpr int EFLA_TT = 32;
 
+// Brings tokens [s0, s0 + n) of (batch b, head h) into shared memory as fp32: all D key channels, the 32 value
+// (and dout) columns of this warp, and c (optionally lam) per token. Eight rows are fetched per batch so that their
+// global loads are in flight together; lane r then owns token r for lam / c (the rotated index keeps the banks apart).
+template <int D>
+__device__ __forceinline__ void efla_load_tile(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+                                               const __nv_bfloat16* __restrict__ dout, float (*sk)[D], float (*sv)[32], float (*sdo)[32],
+                                               float* sc, float* slam, float beta, long long row0, long long row_stride, int col,
+                                               int n, int lane) {
+  __syncwarp();                                          // the previous tile has been consumed
+#pragma unroll 1
+  for (int r0 = 0; r0 < EFLA_TT; r0 += 8) {
+    if (r0 >= n) break;
+    __nv_bfloat16 kq[8][D / 32], vq[8], dq[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const long long row = row0 + (long long)min(r0 + u, n - 1) * row_stride;      // clamped: rows past the end re-read the last one
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) kq[u][c] = k[row + c * 32 + lane];
+      vq[u] = v[row + col];
+      if (dout) dq[u] = dout[row + col];
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) sk[r0 + u][c * 32 + lane] = __bfloat162float(kq[u][c]);
+      sv[r0 + u][lane] = __bfloat162float(vq[u]);
+      if (dout) sdo[r0 + u][lane] = __bfloat162float(dq[u]);
+    }
+  }
+  __syncwarp();
+  if (lane < n) {
+    float lam = 0.f;
+#pragma unroll 8
+    for (int c = 0; c < D; ++c) {
+      const float x = sk[lane][(c + lane) % D];
+      lam += x * x;
+    }
+    float c_, d1, d2;
+    efla_coeff(beta, lam, c_, d1, d2);
+    sc[lane] = c_;
+    if (slam) slam[lane] = lam;
+  }
+  __syncwarp();
+}
+
 template <int D>
 __global__ void __launch_bounds__(32) efla_scan_fwd_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
                                                            const float* __restrict__ beta_ptr, const float* __restrict__ state0,
@@ -67,27 +112,8 @@ __global__ void __launch_bounds__(32) efla_scan_fwd_kernel(const __nv_bfloat16* 
   const int nchunks = (T + chunk - 1) / chunk;
   for (int t0 = 0; t0 < T; t0 += EFLA_TT) {
     const int n = min(EFLA_TT, T - t0);
-    __syncwarp();                                        // the previous tile has been consumed
-    for (int r = 0; r < n; ++r) {
-      const long long row = (((long long)b * T + t0 + r) * H + h) * D;
-#pragma unroll
-      for (int c = 0; c < D; c += 32) sk[r][c + lane] = __bfloat162float(k[row + c + lane]);
-      sv[r][lane] = __bfloat162float(v[row + col]);
-    }
-    __syncwarp();
-    if (lane < n) {                                      // lam and c of token `lane`; the rotated index keeps the banks apart
-      float lam = 0.f;
-#pragma unroll 8
-      for (int c = 0; c < D; ++c) {
-        const float x = sk[lane][(c + lane) % D];
-        lam += x * x;
-      }
-      float c_, d1, d2;
-      efla_coeff(beta, lam, c_, d1, d2);
-      slam[lane] = lam;
-      sc[lane] = c_;
-    }
-    __syncwarp();
+    efla_load_tile<D>(k, v, nullptr, sk, sv, nullptr, sc, slam, beta, (((long long)b * T + t0) * H + h) * D, (long long)H * D, col, n,
+                      lane);
     for (int r = 0; r < n; ++r) {
       const int t = t0 + r;
       if (ckpt && t % chunk == 0) {
@@ -162,29 +188,9 @@ __global__ void __launch_bounds__(32) efla_scan_bwd_kernel(const __nv_bfloat16* 
 #pragma unroll
   for (int i = 0; i < D; ++i) G[i] = dstate_out ? dstate_out[((long long)bh * D + i) * D + col] : 0.f;
 
-  // brings tokens [s0, s0 + n) into shared memory: keys (all D), this CTA's value / dout columns, c per token
   auto load_tile = [&](int s0, int n, bool with_do) {
-    __syncwarp();
-    for (int r = 0; r < n; ++r) {
-      const long long row = (((long long)b * T + s0 + r) * H + h) * D;
-#pragma unroll
-      for (int c = 0; c < D; c += 32) sk[r][c + lane] = __bfloat162float(k[row + c + lane]);
-      sv[r][lane] = __bfloat162float(v[row + col]);
-      if (with_do) sdo[r][lane] = __bfloat162float(dout[row + col]);
-    }
-    __syncwarp();
-    if (lane < n) {
-      float lam = 0.f;
-#pragma unroll 8
-      for (int c = 0; c < D; ++c) {
-        const float x = sk[lane][(c + lane) % D];
-        lam += x * x;
-      }
-      float c_, d1, d2;
-      efla_coeff(beta, lam, c_, d1, d2);
-      sc[lane] = c_;
-    }
-    __syncwarp();
+    efla_load_tile<D>(k, v, with_do ? dout : nullptr, sk, sv, sdo, sc, nullptr, beta, (((long long)b * T + s0) * H + h) * D,
+                      (long long)H * D, col, n, lane);
   };
 
   for (int ch = nchunks - 1; ch >= 0; --ch) {
