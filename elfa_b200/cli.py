@@ -43,6 +43,11 @@ def _device():
 def cmd_train(a) -> int:
     from .trainer import Trainer
     cfg = _load_cfg(a.config)
+    if a.set:
+        from .utils.errors import apply_overrides, parse_key_value
+        for text in a.set:                       # --set training.learning_rate=1e-4,runtime.zero_stage=1
+            apply_overrides(cfg, parse_key_value(text))
+        cfg.validate()
     if a.checkpoint_dir:
         cfg.checkpoint.dir = a.checkpoint_dir
     if a.data:
@@ -184,6 +189,8 @@ def build_parser() -> argparse.ArgumentParser:
     t.add_argument("--resume")
     t.add_argument("--data")
     t.add_argument("--checkpoint-dir")
+    t.add_argument("--set", action="append", default=[], metavar="SECTION.KEY=VALUE[,...]",
+                   help="configuration overrides applied after the file is read")
     t.set_defaults(fn=cmd_train)
     e = sub.add_parser("evaluate", allow_abbrev=False)
     e.add_argument("--checkpoint", required=True)

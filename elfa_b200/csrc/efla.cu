@@ -2,8 +2,8 @@
 //
 // EFLA, per (batch, head), state S [d, d] fp32 (row = key index i, column = value index j):
 //   lam = |k|^2, c = (1 - exp(-beta lam)) / lam, p = S^T k, e = v - p, S += c k e^T, o = p + c lam e
-// (o equals S_new^T k). Forward: one warp per (batch, head, 32 value columns); lane j keeps column j of S in
-// registers for the whole sequence so the state never leaves the chip and is never rounded to bf16 - the
+// (o equals S_new^T k). Forward: one CTA of four warps per (batch, head, 32 value columns); its threads keep the
+// state in registers for the whole sequence so it never leaves the chip and is never rounded to bf16 - the
 // reference rounds the bf16 state in global memory on every token and launches once per chunk
 // (reference: kernels/cuda/efla.cu:121-197 forward, :199-271 state history, :273-401 backward
 // without the beta gradient; fp32 variant kernels/cuda/efla_scan.cu:99-260 with grad_beta via
@@ -37,26 +37,25 @@ __device__ __forceinline__ void efla_coeff(float beta, float lam, float& c, floa
 
 // k, v, o: [B, T, H, D] bf16. state0 / state_out: [B, H, D, D] fp32. ckpt: [B, H, nchunks, D, D] holds the
 // state at the START of every chunk.
-// The columns of S evolve independently (column j needs k_t, c_t and v_t[j] only), so a CTA is ONE warp that
-// owns 32 columns: grid (B*H, D/32), no block-wide barrier anywhere. Time is walked in tiles of EFLA_TT tokens:
-// the warp first brings the tile's keys (fp32) and its 32 value columns into shared memory with independent
-// coalesced loads and computes lam / c for all EFLA_TT tokens at once (lane r owns token r), then the
-// sequential part reads keys as 16-byte shared-memory broadcasts and touches global memory only for the
-// output. The dot product runs on four accumulators to shorten its dependency chain.
+// The columns of S evolve independently (column j needs k_t, c_t and v_t[j] only), so a CTA owns 32 value columns:
+// grid (B*H, D/32). Its four warps split the D key rows: warp w keeps rows [w D/4, (w+1) D/4) of the 32 columns in
+// registers (lane = column), so the dependent instruction chain of a step is a quarter as long and the four
+// schedulers of the SM all have a warp. A step costs one block barrier: the warps exchange their partial dot
+// products through a parity-double-buffered shared array. Time is walked in tiles of EFLA_TT tokens: every warp
+// fetches eight of the tile's rows with all loads in flight together (keys as fp32, the CTA's 32 value columns),
+// warp 0 computes lam / c for the whole tile (lane r owns token r), and the sequential part touches global memory
+// only for the output.
 constexpr int EFLA_TT = 32;
+constexpr int EFLA_W = 4;
 
-// Brings tokens [s0, s0 + n) of (batch b, head h) into shared memory as fp32: all D key channels, the 32 value
-// (and dout) columns of this warp, and c (optionally lam) per token. Eight rows are fetched per batch so that their
-// global loads are in flight together; lane r then owns token r for lam / c (the rotated index keeps the banks apart).
 template <int D>
 __device__ __forceinline__ void efla_load_tile(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
                                                const __nv_bfloat16* __restrict__ dout, float (*sk)[D], float (*sv)[32], float (*sdo)[32],
                                                float* sc, float* slam, float beta, long long row0, long long row_stride, int col,
-                                               int n, int lane) {
-  __syncwarp();                                          // the previous tile has been consumed
-#pragma unroll 1
-  for (int r0 = 0; r0 < EFLA_TT; r0 += 8) {
-    if (r0 >= n) break;
+                                               int n, int warp, int lane) {
+  __syncthreads();                                       // the previous tile has been consumed
+  const int r0 = warp * (EFLA_TT / EFLA_W);
+  if (r0 < n) {
     __nv_bfloat16 kq[8][D / 32], vq[8], dq[8];
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
@@ -74,8 +73,8 @@ __device__ __forceinline__ void efla_load_tile(const __nv_bfloat16* __restrict__
       if (dout) sdo[r0 + u][lane] = __bfloat162float(dq[u]);
     }
   }
-  __syncwarp();
-  if (lane < n) {
+  __syncthreads();
+  if (warp == 0 && lane < n) {                           // the rotated index keeps the banks apart
     float lam = 0.f;
 #pragma unroll 8
     for (int c = 0; c < D; ++c) {
@@ -87,146 +86,134 @@ __device__ __forceinline__ void efla_load_tile(const __nv_bfloat16* __restrict__
     sc[lane] = c_;
     if (slam) slam[lane] = lam;
   }
-  __syncwarp();
+  __syncthreads();
+}
+
+// One step of the recurrence for this warp's R rows: returns p (complete, after the exchange) and applies the update.
+template <int R>
+__device__ __forceinline__ float efla_step(float (&S)[R], const float* __restrict__ krow, float c_, float vj, float* part, int warp,
+                                           int lane) {
+  const float4* kr = reinterpret_cast<const float4*>(krow);
+  float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+#pragma unroll
+  for (int i = 0; i < R / 4; ++i) {
+    const float4 kk = kr[i];
+    p0 += kk.x * S[4 * i];
+    p1 += kk.y * S[4 * i + 1];
+    p2 += kk.z * S[4 * i + 2];
+    p3 += kk.w * S[4 * i + 3];
+  }
+  part[warp * 32 + lane] = (p0 + p1) + (p2 + p3);
+  __syncthreads();
+  const float p = (part[lane] + part[32 + lane]) + (part[64 + lane] + part[96 + lane]);
+  const float ce = c_ * (vj - p);
+#pragma unroll
+  for (int i = 0; i < R / 4; ++i) {
+    const float4 kk = kr[i];
+    S[4 * i] += kk.x * ce;
+    S[4 * i + 1] += kk.y * ce;
+    S[4 * i + 2] += kk.z * ce;
+    S[4 * i + 3] += kk.w * ce;
+  }
+  return p;
 }
 
 template <int D>
-__global__ void __launch_bounds__(32) efla_scan_fwd_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
-                                                           const float* __restrict__ beta_ptr, const float* __restrict__ state0,
-                                                           __nv_bfloat16* __restrict__ o, float* __restrict__ state_out,
-                                                           float* __restrict__ ckpt, int T, int H, int chunk) {
+__global__ void __launch_bounds__(32 * EFLA_W) efla_scan_fwd_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+                                                                    const float* __restrict__ beta_ptr, const float* __restrict__ state0,
+                                                                    __nv_bfloat16* __restrict__ o, float* __restrict__ state_out,
+                                                                    float* __restrict__ ckpt, int T, int H, int chunk) {
+  constexpr int R = D / EFLA_W;
   __shared__ __align__(16) float sk[EFLA_TT][D];
   __shared__ float sv[EFLA_TT][32];
   __shared__ float sc[EFLA_TT], slam[EFLA_TT];
-  const int bh = blockIdx.x, b = bh / H, h = bh % H, lane = threadIdx.x;
-  const int col = blockIdx.y * 32 + lane;
+  __shared__ float spart[2][EFLA_W * 32];
+  const int bh = blockIdx.x, b = bh / H, h = bh % H, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = blockIdx.y * 32 + lane, i0 = warp * R;
   const float beta = *beta_ptr;
-  float S[D];
-  if (state0) {
+  float S[R];
 #pragma unroll
-    for (int i = 0; i < D; ++i) S[i] = state0[((long long)bh * D + i) * D + col];
-  } else {
-#pragma unroll
-    for (int i = 0; i < D; ++i) S[i] = 0.f;
-  }
+  for (int i = 0; i < R; ++i) S[i] = state0 ? state0[((long long)bh * D + i0 + i) * D + col] : 0.f;
   const int nchunks = (T + chunk - 1) / chunk;
   for (int t0 = 0; t0 < T; t0 += EFLA_TT) {
     const int n = min(EFLA_TT, T - t0);
     efla_load_tile<D>(k, v, nullptr, sk, sv, nullptr, sc, slam, beta, (((long long)b * T + t0) * H + h) * D, (long long)H * D, col, n,
-                      lane);
+                      warp, lane);
     for (int r = 0; r < n; ++r) {
       const int t = t0 + r;
       if (ckpt && t % chunk == 0) {
         float* dst = ckpt + ((long long)bh * nchunks + t / chunk) * D * D;
 #pragma unroll
-        for (int i = 0; i < D; ++i) dst[i * D + col] = S[i];
+        for (int i = 0; i < R; ++i) dst[(i0 + i) * D + col] = S[i];
       }
-      const float4* kr = reinterpret_cast<const float4*>(sk[r]);
-      float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
-#pragma unroll
-      for (int i = 0; i < D / 4; ++i) {
-        const float4 kk = kr[i];
-        p0 += kk.x * S[4 * i];
-        p1 += kk.y * S[4 * i + 1];
-        p2 += kk.z * S[4 * i + 2];
-        p3 += kk.w * S[4 * i + 3];
-      }
-      const float p = (p0 + p1) + (p2 + p3);
-      const float c_ = sc[r], lam = slam[r];
-      const float e = sv[r][lane] - p;
-      const float ce = c_ * e;
-#pragma unroll
-      for (int i = 0; i < D / 4; ++i) {
-        const float4 kk = kr[i];
-        S[4 * i] += kk.x * ce;
-        S[4 * i + 1] += kk.y * ce;
-        S[4 * i + 2] += kk.z * ce;
-        S[4 * i + 3] += kk.w * ce;
-      }
-      o[(((long long)b * T + t) * H + h) * D + col] = __float2bfloat16(p + c_ * lam * e);
+      const float c_ = sc[r], vj = sv[r][lane];
+      const float p = efla_step<R>(S, sk[r] + i0, c_, vj, spart[r & 1], warp, lane);
+      if (warp == 0) o[(((long long)b * T + t) * H + h) * D + col] = __float2bfloat16(p + c_ * slam[r] * (vj - p));
     }
   }
   if (state_out) {
 #pragma unroll
-    for (int i = 0; i < D; ++i) state_out[((long long)bh * D + i) * D + col] = S[i];
+    for (int i = 0; i < R; ++i) state_out[((long long)bh * D + i0 + i) * D + col] = S[i];
   }
 }
 
-// Backward: the same warp-per-32-columns layout. Lane j keeps column j of G = dL/dS (the gradient with respect to
-// the state AFTER the current token) in registers for the whole sequence. Chunks are walked in reverse; inside a
-// chunk the states are recomputed from the chunk's saved boundary state and the state BEFORE every token goes to a
-// global workspace ([chunk, D, D] per (batch, head); a CTA touches only its own columns, so the lines stay in
-// L1 / L2), then the reverse-time recursion streams each of them twice:
-//   pass 1: p_j = sum_i k_i S_ij ;  e_j = v_j - p_j ;  G_ij += k_i do_j ;  w_j = sum_i G_ij k_i ;
-//           dv_j = de_j = c w_j ;  dp_j = -de_j ;  dc += e_j w_j (summed over the lanes, then over the column blocks)
+// Backward: the same layout (CTA = 32 value columns, warp w = key rows [w D/4, (w+1) D/4), lane = column). Every warp
+// keeps its rows of G = dL/dS (the gradient with respect to the state AFTER the current token) in registers for
+// the whole sequence. Chunks are walked in reverse; inside a chunk the states are recomputed from the chunk's saved
+// boundary state and the state BEFORE every token goes to a global workspace ([chunk, D, D] per (batch, head); a
+// thread reads back only what it wrote), then the reverse-time recursion streams each of them twice:
+//   pass 1: p_j = sum_i k_i S_ij ;  G_ij += k_i do_j ;  w_j = sum_i G_ij k_i   (partial over the warp's rows; ONE block
+//           barrier per step exchanges both partial sums) ;  e_j = v_j - p_j ;  dv_j = de_j = c w_j ;  dp_j = -de_j ;
+//           dc = sum_j e_j w_j (over the lanes here, over the column blocks in the finishing kernel)
 //   pass 2: r_ij = (S_ij + c k_i e_j) do_j + c G_ij e_j + S_ij dp_j ;  G_ij += k_i dp_j
 // dk_i = sum_j r_ij + 2 k_i dc dc/dlam needs a sum over ALL value columns: within the warp it goes through a
-// padded shared-memory transpose (lane j writes r_.j, lane i adds up row i), across the D/32 column blocks
-// through fp32 partial buffers that efla_bwd_finish_kernel adds up (fixed order: deterministic) together with
-// the lam term and the per-token beta gradient.
+// padded shared-memory transpose private to the warp (lane j writes r_.j, lane i adds up row i), across the D/32
+// column blocks through fp32 partial buffers that efla_bwd_finish_kernel adds up (fixed order: deterministic)
+// together with the lam term and the per-token beta gradient.
 // work: [B*H][chunk][D][D] fp32. dk_part: [D/32][rows][D] fp32, dc_part: [D/32][rows] fp32, rows = B*T*H.
 template <int D>
-__global__ void __launch_bounds__(32) efla_scan_bwd_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
-                                                           const float* __restrict__ beta_ptr, const float* __restrict__ ckpt,
-                                                           const __nv_bfloat16* __restrict__ dout, const float* __restrict__ dstate_out,
-                                                           float* __restrict__ dk_part, __nv_bfloat16* __restrict__ dv,
-                                                           float* __restrict__ dc_part, float* __restrict__ dstate0,
-                                                           float* __restrict__ work, int B, int T, int H, int chunk) {
+__global__ void __launch_bounds__(32 * EFLA_W) efla_scan_bwd_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+                                                                    const float* __restrict__ beta_ptr, const float* __restrict__ ckpt,
+                                                                    const __nv_bfloat16* __restrict__ dout,
+                                                                    const float* __restrict__ dstate_out, float* __restrict__ dk_part,
+                                                                    __nv_bfloat16* __restrict__ dv, float* __restrict__ dc_part,
+                                                                    float* __restrict__ dstate0, float* __restrict__ work, int B, int T,
+                                                                    int H, int chunk) {
+  constexpr int R = D / EFLA_W;
   __shared__ __align__(16) float sk[EFLA_TT][D];
   __shared__ float sv[EFLA_TT][32], sdo[EFLA_TT][32];
   __shared__ float sc[EFLA_TT];
-  __shared__ float sred[D][33];
-  const int bh = blockIdx.x, b = bh / H, h = bh % H, lane = threadIdx.x;
-  const int col = blockIdx.y * 32 + lane;
+  __shared__ float spart[2][2 * EFLA_W * 32];            // [parity][p partials | w partials]
+  __shared__ float sred[EFLA_W][R][33];
+  const int bh = blockIdx.x, b = bh / H, h = bh % H, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = blockIdx.y * 32 + lane, i0 = warp * R;
   const long long rows = (long long)B * T * H;
   const float beta = *beta_ptr;
   const int nchunks = (T + chunk - 1) / chunk;
-  float* wk = work + (long long)bh * chunk * D * D;
+  float* wk = work + (long long)bh * chunk * D * D + (long long)i0 * D + col;     // this thread's first element of a token's state
   float* dkp = dk_part + (long long)blockIdx.y * rows * D;
   float* dcp = dc_part + (long long)blockIdx.y * rows;
-  float G[D];
+  float G[R];
 #pragma unroll
-  for (int i = 0; i < D; ++i) G[i] = dstate_out ? dstate_out[((long long)bh * D + i) * D + col] : 0.f;
-
-  auto load_tile = [&](int s0, int n, bool with_do) {
-    efla_load_tile<D>(k, v, with_do ? dout : nullptr, sk, sv, sdo, sc, nullptr, beta, (((long long)b * T + s0) * H + h) * D,
-                      (long long)H * D, col, n, lane);
-  };
+  for (int i = 0; i < R; ++i) G[i] = dstate_out ? dstate_out[((long long)bh * D + i0 + i) * D + col] : 0.f;
 
   for (int ch = nchunks - 1; ch >= 0; --ch) {
     const int t0 = ch * chunk, t1 = min(T, t0 + chunk);
     // ---- recompute the states of this chunk, store the state BEFORE every token
     {
-      float S[D];
+      float S[R];
       const float* src = ckpt + ((long long)bh * nchunks + ch) * D * D;
 #pragma unroll
-      for (int i = 0; i < D; ++i) S[i] = src[i * D + col];
+      for (int i = 0; i < R; ++i) S[i] = src[(i0 + i) * D + col];
       for (int s0 = t0; s0 < t1; s0 += EFLA_TT) {
         const int n = min(EFLA_TT, t1 - s0);
-        load_tile(s0, n, false);
+        efla_load_tile<D>(k, v, nullptr, sk, sv, nullptr, sc, nullptr, beta, (((long long)b * T + s0) * H + h) * D, (long long)H * D,
+                          col, n, warp, lane);
         for (int r = 0; r < n; ++r) {
           float* dst = wk + (long long)(s0 + r - t0) * D * D;
 #pragma unroll
-          for (int i = 0; i < D; ++i) dst[i * D + col] = S[i];
-          const float4* kr = reinterpret_cast<const float4*>(sk[r]);
-          float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
-#pragma unroll
-          for (int i = 0; i < D / 4; ++i) {
-            const float4 kk = kr[i];
-            p0 += kk.x * S[4 * i];
-            p1 += kk.y * S[4 * i + 1];
-            p2 += kk.z * S[4 * i + 2];
-            p3 += kk.w * S[4 * i + 3];
-          }
-          const float ce = sc[r] * (sv[r][lane] - ((p0 + p1) + (p2 + p3)));
-#pragma unroll
-          for (int i = 0; i < D / 4; ++i) {
-            const float4 kk = kr[i];
-            S[4 * i] += kk.x * ce;
-            S[4 * i + 1] += kk.y * ce;
-            S[4 * i + 2] += kk.z * ce;
-            S[4 * i + 3] += kk.w * ce;
-          }
+          for (int i = 0; i < R; ++i) dst[i * D] = S[i];
+          efla_step<R>(S, sk[r] + i0, sc[r], sv[r][lane], spart[r & 1], warp, lane);
         }
       }
     }
@@ -234,16 +221,17 @@ __global__ void __launch_bounds__(32) efla_scan_bwd_kernel(const __nv_bfloat16* 
     const int ntiles = (t1 - t0 + EFLA_TT - 1) / EFLA_TT;
     for (int ti = ntiles - 1; ti >= 0; --ti) {
       const int s0 = t0 + ti * EFLA_TT, n = min(EFLA_TT, t1 - s0);
-      load_tile(s0, n, true);
+      efla_load_tile<D>(k, v, dout, sk, sv, sdo, sc, nullptr, beta, (((long long)b * T + s0) * H + h) * D, (long long)H * D, col, n,
+                        warp, lane);
       for (int r = n - 1; r >= 0; --r) {
         const int t = s0 + r;
-        const float* Sb = wk + (long long)(t - t0) * D * D + col;       // S before token t, column `col`: Sb[i * D]
-        const float4* kr = reinterpret_cast<const float4*>(sk[r]);
+        const float* Sb = wk + (long long)(t - t0) * D * D;            // S before token t: element (i0 + i, col) at Sb[i * D]
+        const float4* kr = reinterpret_cast<const float4*>(sk[r] + i0);
         const float c_ = sc[r], go = sdo[r][lane];
         // pass 1
         float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f, w0 = 0.f, w1 = 0.f, w2 = 0.f, w3 = 0.f;
 #pragma unroll
-        for (int i = 0; i < D / 4; ++i) {
+        for (int i = 0; i < R / 4; ++i) {
           const float4 kk = kr[i];
           p0 += kk.x * Sb[(4 * i) * D];
           p1 += kk.y * Sb[(4 * i + 1) * D];
@@ -258,35 +246,40 @@ __global__ void __launch_bounds__(32) efla_scan_bwd_kernel(const __nv_bfloat16* 
           w2 += G[4 * i + 2] * kk.z;
           w3 += G[4 * i + 3] * kk.w;
         }
-        const float e = sv[r][lane] - ((p0 + p1) + (p2 + p3));
-        const float w = (w0 + w1) + (w2 + w3);
+        float* part = spart[r & 1];
+        part[warp * 32 + lane] = (p0 + p1) + (p2 + p3);
+        part[EFLA_W * 32 + warp * 32 + lane] = (w0 + w1) + (w2 + w3);
+        __syncthreads();
+        const float p = (part[lane] + part[32 + lane]) + (part[64 + lane] + part[96 + lane]);
+        const float w = (part[128 + lane] + part[160 + lane]) + (part[192 + lane] + part[224 + lane]);
+        const float e = sv[r][lane] - p;
         const float de = c_ * w, dp = -de;
         const long long row = ((long long)b * T + t) * H + h;
-        dv[row * D + col] = __float2bfloat16(de);
         const float dc = warp_sum(e * w);
-        if (lane == 0) dcp[row] = dc;
+        if (warp == 0) {
+          dv[row * D + col] = __float2bfloat16(de);
+          if (lane == 0) dcp[row] = dc;
+        }
         // pass 2
         const float ce = c_ * e;
 #pragma unroll
-        for (int i = 0; i < D / 4; ++i) {
+        for (int i = 0; i < R / 4; ++i) {
           const float4 kk = kr[i];
           const float kv[4] = {kk.x, kk.y, kk.z, kk.w};
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int ii = 4 * i + u;
             const float sb = Sb[ii * D];
-            sred[ii][lane] = (sb + kv[u] * ce) * go + ce * G[ii] + sb * dp;
+            sred[warp][ii][lane] = (sb + kv[u] * ce) * go + ce * G[ii] + sb * dp;
             G[ii] += kv[u] * dp;
           }
         }
         __syncwarp();
-#pragma unroll
-        for (int m = 0; m < D / 32; ++m) {
-          const int ii = m * 32 + lane;
+        if (lane < R) {
           float acc = 0.f;
 #pragma unroll
-          for (int jj = 0; jj < 32; ++jj) acc += sred[ii][jj];
-          dkp[row * D + ii] = acc;
+          for (int jj = 0; jj < 32; ++jj) acc += sred[warp][lane][jj];
+          dkp[row * D + i0 + lane] = acc;
         }
         __syncwarp();
       }
@@ -294,7 +287,7 @@ __global__ void __launch_bounds__(32) efla_scan_bwd_kernel(const __nv_bfloat16* 
   }
   if (dstate0) {
 #pragma unroll
-    for (int i = 0; i < D; ++i) dstate0[((long long)bh * D + i) * D + col] = G[i];
+    for (int i = 0; i < R; ++i) dstate0[((long long)bh * D + i0 + i) * D + col] = G[i];
   }
 }
 
@@ -395,7 +388,7 @@ __global__ void __launch_bounds__(256) shortconv_bwd_dw_kernel(const __nv_bfloat
 template <int D>
 int launch_efla_fwd(const void* k, const void* v, const float* beta, const float* state0, void* o, float* state_out, float* ckpt, int B,
                     int T, int H, int chunk, cudaStream_t s) {
-  efla_scan_fwd_kernel<D><<<dim3(B * H, D / 32), 32, 0, s>>>(static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), beta, state0,
+  efla_scan_fwd_kernel<D><<<dim3(B * H, D / 32), 32 * EFLA_W, 0, s>>>(static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), beta, state0,
                                               static_cast<__nv_bfloat16*>(o), state_out, ckpt, T, H, chunk);
   ELFA_CUDA(cudaGetLastError());
   ::elfa::count_launches(1);
@@ -406,7 +399,7 @@ template <int D>
 int launch_efla_bwd(const void* k, const void* v, const float* beta, const float* ckpt, const void* dout, const float* dstate_out,
                     void* dk, void* dv, float* dbeta_tok, float* dstate0, float* work, float* dk_part, float* dc_part, int B, int T,
                     int H, int chunk, cudaStream_t s) {
-  efla_scan_bwd_kernel<D><<<dim3(B * H, D / 32), 32, 0, s>>>(
+  efla_scan_bwd_kernel<D><<<dim3(B * H, D / 32), 32 * EFLA_W, 0, s>>>(
       static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), beta, ckpt, static_cast<const __nv_bfloat16*>(dout),
       dstate_out, dk_part, static_cast<__nv_bfloat16*>(dv), dc_part, dstate0, work, B, T, H, chunk);
   ELFA_CUDA(cudaGetLastError());

@@ -282,3 +282,31 @@ def test_phase_timer_and_chrome_trace(tmp_path):
     with off.phase("x"):
         pass
     assert off.summary() == {}
+
+
+def test_error_codes_finite_checks_and_overrides():
+    import math
+    import torch
+    from elfa_b200.config import Config
+    from elfa_b200.utils.errors import NotFiniteError, TrainingError, apply_overrides, check_finite, parse_key_value
+    check_finite(1.0)
+    check_finite(torch.zeros(4, 4))
+    with pytest.raises(NotFiniteError) as e:
+        check_finite(math.nan)
+    assert e.value.code == "NaN" and e.value.area == "training"
+    with pytest.raises(NotFiniteError) as e:
+        check_finite(torch.tensor([1.0, float("inf")]), "loss")
+    assert e.value.code == "Inf" and "loss" in str(e.value)
+    err = TrainingError("CheckpointCorrupted", "sha256 mismatch")
+    assert err.area == "checkpoint" and "CheckpointCorrupted: sha256 mismatch" in str(err) and err.file.endswith("test_cpu_misc.py")
+    with pytest.raises(ValueError):
+        TrainingError("NoSuchCode")
+    assert parse_key_value("a=b, c.d = e ,junk,x=1=2") == {"a": "b", "c.d": "e", "x": "1=2"}
+    cfg = Config.from_file(os.path.join(ROOT, "configs", "smoke.yaml"), env_override=False)
+    apply_overrides(cfg, parse_key_value("training.learning_rate=1e-4,runtime.zero_stage=1,runtime.sequence_parallel=false,model.name=x"))
+    assert cfg.training.learning_rate == 1e-4 and cfg.runtime.zero_stage == 1 and cfg.runtime.sequence_parallel is False
+    assert cfg.model.name == "x"
+    with pytest.raises(TrainingError):
+        apply_overrides(cfg, {"training.no_such_key": "1"})
+    with pytest.raises(TrainingError):
+        apply_overrides(cfg, {"runtime.zero_stage": "many"})
