@@ -310,3 +310,22 @@ def test_error_codes_finite_checks_and_overrides():
         apply_overrides(cfg, {"training.no_such_key": "1"})
     with pytest.raises(TrainingError):
         apply_overrides(cfg, {"runtime.zero_stage": "many"})
+
+
+def test_trainer_reports_phase_times_when_tracing_is_on():
+    from elfa_b200.config import Config
+    from elfa_b200.trainer import Trainer
+    from elfa_b200.utils import tracing
+    cfg = Config.from_file(os.path.join(ROOT, "configs", "bench", "smoke_cpu.yaml"), env_override=False)
+    cfg.checkpoint.dir = ""
+    cfg.telemetry.log_file = ""
+    tracing.enable(True)
+    try:
+        tr = Trainer(cfg, device=torch.device("cpu"), telemetry=False)
+        tr.run(max_steps=2)
+        s = tr.tracer.summary()
+    finally:
+        tracing.enable(False)
+    assert set(s) == {"forward", "backward", "optimizer"}
+    assert s["optimizer"]["calls"] == 2 and s["forward"]["calls"] == s["backward"]["calls"] >= 2
+    assert all(v["ms"] > 0 for v in s.values())
