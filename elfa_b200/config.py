@@ -169,8 +169,9 @@ class RuntimeConfig:
     sequence_parallel: bool = True
     # extension: ranks of one data-parallel replica that split the sequence dimension of a batch (ring attention)
     context_parallel_size: int = 1
-    # "ring": key / value blocks travel round the group; "ulysses": all-to-all to a head split and back
-    context_parallel_mode: str = field(default="ring", metadata=_enum(("ring", "ulysses")))
+    # "ring": key / value blocks travel round the group (contiguous sequence split); "zigzag": the ring with every rank
+    # holding chunks r and 2N-1-r, which evens out the causal work; "ulysses": all-to-all to a head split and back
+    context_parallel_mode: str = field(default="ring", metadata=_enum(("ring", "zigzag", "ulysses")))
 
     def validate(self) -> None:
         if self.world_size <= 0:

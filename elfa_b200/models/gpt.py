@@ -78,7 +78,7 @@ class Attention(nn.Module):
             o = ulysses_attention(qkv, self.pc.cp_group, causal=True)
         elif self.pc.cp_size > 1:    # the sequence is split over the context-parallel group: keys / values travel the ring
             from ..parallel.ring_attention import ring_attention
-            o = ring_attention(qkv, self.pc.cp_group, causal=True, seq_first=True)
+            o = ring_attention(qkv, self.pc.cp_group, causal=True, seq_first=True, zigzag=self.pc.cp_mode == "zigzag")
         else:
             o = ops.attention(qkv, causal=True, seq_first=True)                      # [S, B, local]
         return tpl.row_parallel_linear(o, self.w_o, self.pc, quant=self.quant)        # [S(/tp), B, D]
@@ -239,8 +239,14 @@ class GPTModel(nn.Module):
         """ids ``[B, S]`` → final-norm output ``[S(/tp), B, D]``."""
         pc = self.pc
         ids_sb = ids.t().contiguous()                        # [S, B]
-        x = ops.embedding(ids_sb, self.embed_tokens, self.pos_embed, pos0, self.vocab_lo, seq_first=True,
-                          vocab_total=self.cfg.model.vocab_size)  # [S, B, D]
+        if isinstance(pos0, (tuple, list)):
+            # the local sequence is several equal segments of the whole one (zig-zag context parallelism): one offset each
+            n = ids_sb.shape[0] // len(pos0)
+            x = torch.cat([ops.embedding(ids_sb[i * n:(i + 1) * n].contiguous(), self.embed_tokens, self.pos_embed, int(p0), self.vocab_lo,
+                                         seq_first=True, vocab_total=self.cfg.model.vocab_size) for i, p0 in enumerate(pos0)], 0)
+        else:
+            x = ops.embedding(ids_sb, self.embed_tokens, self.pos_embed, pos0, self.vocab_lo, seq_first=True,
+                              vocab_total=self.cfg.model.vocab_size)  # [S, B, D]
         x = tpl.embedding_reduce(x, pc)                      # sum over vocab shards → [S(/tp), B, D]
         pending = None
         for blk in self.blocks:

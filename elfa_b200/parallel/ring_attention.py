@@ -3,7 +3,8 @@ process group, every rank keeps its query block and the key / value blocks trave
 
 Rank ``r`` holds tokens ``[r * S_l, (r + 1) * S_l)``. At step ``t`` it owns the key / value block of rank
 ``j = (r - t) mod N``; blocks with ``j > r`` lie entirely in the future of its queries and are skipped,
-``j == r`` is the causal diagonal block and ``j < r`` is a full (unmasked) block. Every block product
+``j == r`` is the causal diagonal block and ``j < r`` is a full (unmasked) block (the zig-zag split of
+:func:`block_schedule` gives every rank the same number of block products instead). Every block product
 runs on the tcgen05 attention kernel (CUDA) and returns the block output with its row log-sum-exp; the
 partial results are merged with the usual log-sum-exp rescaling, so the result equals attention over
 the whole sequence. The exchange of step ``t + 1`` is started before the block of step ``t`` is
@@ -113,51 +114,86 @@ class _Exchange:
         return self.out
 
 
+def block_schedule(rank: int, j: int, causal: bool, zigzag: bool):
+    """Block products rank ``rank`` owes to the key / value block of rank ``j``: ``(query part, key part, masked)``.
+
+    Contiguous split: one part per rank; ``j > rank`` is all future (nothing), ``j == rank`` the masked diagonal.
+    Zig-zag split (causal only): a rank holds two half blocks, chunk ``rank`` and chunk ``2N - 1 - rank`` of ``2N``
+    chunks (parts 0 and 1). Part 0 of any rank lies before part 1 of every rank, so every step has two half-size
+    products whatever ``j`` is (three on the diagonal, two of them masked): the work is the same on all ranks."""
+    if not zigzag:
+        if not causal:
+            return [(0, 0, False)]
+        return [(0, 0, j == rank)] if j <= rank else []
+    if j == rank:
+        return [(0, 0, True), (1, 0, False), (1, 1, True)]
+    if j < rank:
+        return [(0, 0, False), (1, 0, False)]
+    return [(1, 0, False), (1, 1, False)]
+
+
 class _RingAttention(torch.autograd.Function):
+    """``q, k, v [S_l, B, H, hd]``; with ``zigzag`` the local sequence is two half blocks (see :func:`block_schedule`)."""
+
     @staticmethod
-    def forward(ctx, q, k, v, group, scale, causal):
+    def forward(ctx, q, k, v, group, scale, causal, zigzag):
         rank, world = dist.get_rank(group), dist.get_world_size(group)
+        parts = 2 if zigzag else 1
+        hl = q.shape[0] // parts
         kv = torch.stack((k, v), dim=0).contiguous()                       # travels as one message
-        o_acc = lse_acc = None
+        qs = [q[i * hl:(i + 1) * hl] for i in range(parts)]
+        acc = [[None, None] for _ in range(parts)]                        # (o, lse) per query part
         for t in range(world):
             j = (rank - t) % world
-            nxt = _Exchange([kv], group) if t + 1 < world else None          # overlaps the block below
-            if not causal or j <= rank:
-                o_blk, lse_blk = block_forward(q, kv[0], kv[1], causal and j == rank, scale)
-                o_acc, lse_acc = merge_partial(o_acc, lse_acc, o_blk, lse_blk)
+            nxt = _Exchange([kv], group) if t + 1 < world else None          # overlaps the blocks below
+            for qi, ki, masked in block_schedule(rank, j, causal, zigzag):
+                o_blk, lse_blk = block_forward(qs[qi], kv[0, ki * hl:(ki + 1) * hl], kv[1, ki * hl:(ki + 1) * hl], masked, scale)
+                acc[qi] = list(merge_partial(acc[qi][0], acc[qi][1], o_blk, lse_blk))
             if nxt is not None:
                 kv = nxt.wait()[0]
-        out = o_acc.to(q.dtype).contiguous()
-        ctx.save_for_backward(q, k, v, out, lse_acc)
-        ctx.cfg = (group, scale, causal)
+        out = torch.cat([a[0] for a in acc], 0).to(q.dtype).contiguous()
+        lse = torch.stack([a[1] for a in acc], 0)                          # [parts, B, H, hl]
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.cfg = (group, scale, causal, zigzag)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, out, lse = ctx.saved_tensors
-        group, scale, causal = ctx.cfg
+        group, scale, causal, zigzag = ctx.cfg
         rank, world = dist.get_rank(group), dist.get_world_size(group)
+        parts = 2 if zigzag else 1
+        hl = q.shape[0] // parts
         dout = dout.contiguous()
         kv = torch.stack((k, v), dim=0).contiguous()
         dkv = torch.zeros(kv.shape, dtype=torch.float32, device=kv.device)   # gradient of the block in hand
         dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+        sl = [slice(i * hl, (i + 1) * hl) for i in range(parts)]
         for t in range(world):
             j = (rank - t) % world
             nxt = _Exchange([kv], group) if t + 1 < world else None          # the block itself can leave at once
-            if not causal or j <= rank:
-                dq_b, dk_b, dv_b = block_backward(q, kv[0], kv[1], out, dout, lse, causal and j == rank, scale)
-                dq += dq_b
-                dkv[0] += dk_b
-                dkv[1] += dv_b
+            for qi, ki, masked in block_schedule(rank, j, causal, zigzag):
+                dq_b, dk_b, dv_b = block_backward(q[sl[qi]], kv[0, sl[ki]], kv[1, sl[ki]], out[sl[qi]], dout[sl[qi]], lse[qi], masked, scale)
+                dq[sl[qi]] += dq_b
+                dkv[0, sl[ki]] += dk_b
+                dkv[1, sl[ki]] += dv_b
             dkv = _Exchange([dkv], group).wait()[0]                           # after N hops the block is home
             if nxt is not None:
                 kv = nxt.wait()[0]
-        return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype), None, None, None
+        return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype), None, None, None, None
+
+
+def zigzag_slices(seq_len: int, rank: int, world: int):
+    """The two ``(start, stop)`` ranges of the sequence that rank ``rank`` holds under the zig-zag split."""
+    hl = seq_len // (2 * world)
+    return (rank * hl, (rank + 1) * hl), ((2 * world - 1 - rank) * hl, (2 * world - rank) * hl)
 
 
 def ring_attention(qkv_local: torch.Tensor, group=None, causal: bool = True, seq_first: bool = True,
-                   scale: Optional[float] = None) -> torch.Tensor:
-    """Attention over a sequence split in equal contiguous blocks over ``group`` (rank order = token order).
+                   scale: Optional[float] = None, zigzag: bool = False) -> torch.Tensor:
+    """Attention over a sequence split in equal contiguous blocks over ``group`` (rank order = token order), or with
+    ``zigzag`` split in ``2N`` chunks of which this rank holds chunk ``rank`` followed by chunk ``2N - 1 - rank``
+    (:func:`zigzag_slices`; causal only - it evens out the work that the causal mask leaves to each rank).
     ``qkv_local``: this rank's ``[S_l, B, 3, H, hd]`` (or ``[B, S_l, 3, H, hd]``); returns ``[S_l, B, H*hd]``
     (``[B, S_l, H*hd]``), differentiable. With a group of one it is :func:`elfa_b200.ops.attention`."""
     from ..ops.attention import attention
@@ -168,7 +204,8 @@ def ring_attention(qkv_local: torch.Tensor, group=None, causal: bool = True, seq
     S, B, _, H, hd = x.shape
     sc = scale if scale is not None else 1.0 / math.sqrt(hd)
     q, k, v = (x[:, :, i].contiguous() for i in range(3))
-    o = _RingAttention.apply(q, k, v, group, sc, causal).reshape(S, B, H * hd)
+    assert not zigzag or (causal and S % 2 == 0), "the zig-zag split is for causal attention over two equal half blocks"
+    o = _RingAttention.apply(q, k, v, group, sc, causal, zigzag).reshape(S, B, H * hd)
     return o if seq_first else o.transpose(0, 1).contiguous()
 
 

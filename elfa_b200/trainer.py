@@ -153,7 +153,13 @@ class Trainer:
             ids = b.input.to(self.device, non_blocking=True)
             tgt = b.target.to(self.device, non_blocking=True)
             pos0 = 0
-            if self.pc.cp_size > 1:
+            if self.pc.cp_size > 1 and self.pc.cp_mode == "zigzag":
+                from .parallel.ring_attention import zigzag_slices
+                (a0, a1), (b0, b1) = zigzag_slices(ids.shape[1], self.pc.cp_rank, self.pc.cp_size)
+                pos0 = (a0, b0)
+                ids = torch.cat((ids[:, a0:a1], ids[:, b0:b1]), 1).contiguous()
+                tgt = torch.cat((tgt[:, a0:a1], tgt[:, b0:b1]), 1).contiguous()
+            elif self.pc.cp_size > 1:
                 sl = ids.shape[1] // self.pc.cp_size
                 pos0 = self.pc.cp_rank * sl
                 ids, tgt = ids[:, pos0:pos0 + sl].contiguous(), tgt[:, pos0:pos0 + sl].contiguous()

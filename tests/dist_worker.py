@@ -129,7 +129,7 @@ def mode_cp(dev, dtype, tp, cp_mode="ring"):
     trained with the sequence split over a context-parallel group against the same model on one rank."""
     from elfa_b200.ops.attention import attention_ref
     from elfa_b200.parallel.mesh import ParallelContext
-    from elfa_b200.parallel.ring_attention import ring_attention
+    from elfa_b200.parallel.ring_attention import ring_attention, zigzag_slices
     from elfa_b200.parallel.ulysses import ulysses_attention
     from elfa_b200.trainer import Trainer
     world, rank = dist.get_world_size(), dist.get_rank()
@@ -138,7 +138,7 @@ def mode_cp(dev, dtype, tp, cp_mode="ring"):
     assert pc.cp_size == cp and len(pc.cp_ranks) == cp
     tdt = torch.float32 if dtype == "fp32" else torch.bfloat16
     g = torch.Generator().manual_seed(5)
-    S, B, H, hd = 128 * cp, 2, 2, 64
+    S, B, H, hd = 256 * cp, 2, 2, 64
     full = torch.randn(S, B, 3, H, hd, generator=g).to(dev, tdt)
     dout = torch.randn(S, B, H * hd, generator=g).to(dev, tdt)
     sl, c = S // cp, pc.cp_rank
@@ -146,16 +146,23 @@ def mode_cp(dev, dtype, tp, cp_mode="ring"):
         ref_in = full.float().clone().requires_grad_(True)
         ref = attention_ref(ref_in, causal=causal)
         ref.backward(dout.float())
-        loc = full[c * sl:(c + 1) * sl].clone().requires_grad_(True)
+        if cp_mode == "zigzag":
+            if not causal:
+                continue
+            (a0, a1), (b0, b1) = zigzag_slices(S, c, cp)
+            take = lambda t: torch.cat((t[a0:a1], t[b0:b1]), 0)
+        else:
+            take = lambda t: t[c * sl:(c + 1) * sl]
+        loc = take(full).clone().requires_grad_(True)
         if cp_mode == "ulysses":
             out = ulysses_attention(loc, pc.cp_group, causal=causal)
         else:
-            out = ring_attention(loc, pc.cp_group, causal=causal)
-        out.backward(dout[c * sl:(c + 1) * sl])
+            out = ring_attention(loc, pc.cp_group, causal=causal, zigzag=cp_mode == "zigzag")
+        out.backward(take(dout).contiguous())
         tol = 1e-4 if dtype == "fp32" else 3e-2
         tol_g = tol * (1.0 + max(1.0, ref_in.grad.abs().max().item()))
-        e_o = (out.float() - ref[c * sl:(c + 1) * sl]).abs().max().item()
-        e_g = (loc.grad.float() - ref_in.grad[c * sl:(c + 1) * sl]).abs().max().item()
+        e_o = (out.float() - take(ref)).abs().max().item()
+        e_g = (loc.grad.float() - take(ref_in.grad)).abs().max().item()
         assert e_o < tol and e_g < tol_g, f"ring attention causal={causal}: out err {e_o}, grad err {e_g}"
     cfg = small_cfg(dtype, tp, "nccl")
     cfg.runtime.world_size = world

@@ -23,9 +23,9 @@ def test_tp_sp_matches_single_rank_on_cpu(world):
     assert "TP_OK" in r.stdout
 
 
-@pytest.mark.parametrize("world,tp,mode", [(2, 1, "ring"), (4, 2, "ring"), (2, 1, "ulysses")])
+@pytest.mark.parametrize("world,tp,mode", [(2, 1, "ring"), (4, 2, "ring"), (2, 1, "ulysses"), (2, 1, "zigzag")])
 def test_context_parallel_attention_and_training_on_cpu(world, tp, mode):
-    r = _run(world, ["cp_cpu", "nccl", "fp32", str(tp), mode], 29660 + world + (10 if mode == "ulysses" else 0))
+    r = _run(world, ["cp_cpu", "nccl", "fp32", str(tp), mode], 29660 + world + {"ring": 0, "ulysses": 10, "zigzag": 20}[mode])
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "CP_OK" in r.stdout
 

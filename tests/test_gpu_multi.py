@@ -35,9 +35,9 @@ def test_fused_ag_gemm_and_gemm_rs(cuda_device):
     assert "FUSED_OK" in r.stdout
 
 
-@pytest.mark.parametrize("mode", ["ring", "ulysses"])
+@pytest.mark.parametrize("mode", ["ring", "zigzag", "ulysses"])
 def test_context_parallel_attention_and_training(cuda_device, mode):
-    r = _run(["cp", "nccl", "bf16", "1", mode], 29710 if mode == "ring" else 29711)
+    r = _run(["cp", "nccl", "bf16", "1", mode], {"ring": 29710, "zigzag": 29712, "ulysses": 29711}[mode])
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "CP_OK" in r.stdout
 
