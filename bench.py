@@ -107,6 +107,9 @@ def main() -> int:
     ap.add_argument("--config", default=os.path.join(ROOT, "configs", "bench", "gpt7b_tp8_mxfp8.yaml"))
     ap.add_argument("--micro-batch", type=int, default=0, help="sequences per micro-batch (0 = auto)")
     ap.add_argument("--comm", default=None, choices=[None, "fused", "nccl"])
+    ap.add_argument("--twin", type=int, default=0, metavar="N",
+                    help="measurement aid, one GPU: play rank 0 of an N-rank job with every collective replaced by a no-op "
+                         "(torch's fake process group): the per-rank compute time without communication. Marks the result invalid")
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the result invalid)")
     ap.add_argument("--global-batch", type=int, default=0, help="debug only: override the global batch (marks the result invalid)")
     args = ap.parse_args()
@@ -123,6 +126,9 @@ def main() -> int:
     from elfa_b200.trainer import Trainer, model_flops_per_token
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.twin and (world != 1 or args.gpus != 1):
+        print("bench.py: --twin runs as a single process on one GPU", file=sys.stderr)
+        return 2
     if world != args.gpus:
         print(f"bench.py: --gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run for N > 1", file=sys.stderr)
         return 2
@@ -132,6 +138,13 @@ def main() -> int:
 
     cfg = Config.from_file(args.config)
     yaml_tp, yaml_world = cfg.runtime.tensor_parallel_size, cfg.runtime.world_size
+    real_world = world
+    if args.twin:
+        # the job's shapes and call sequence at N ranks, on this one GPU: collectives return at once and move nothing
+        from torch.testing._internal.distributed.fake_pg import FakeStore
+        dist.init_process_group(backend="fake", store=FakeStore(), rank=0, world_size=args.twin)
+        world = args.twin
+        args.comm = "nccl"          # the library call sites; the fused kernels need real peers
     cfg.runtime.world_size = world
     if args.comm:
         cfg.runtime.comm_backend = args.comm
@@ -163,7 +176,11 @@ def main() -> int:
     cfg.training.micro_batch_size = mb
     dp_size = world // cfg.runtime.tensor_parallel_size
     cfg.training.gradient_accumulation_steps = max(1, cfg.training.global_batch_size // (mb * dp_size))
-    trainer = Trainer(cfg, telemetry=False)
+    pc = None
+    if args.twin:
+        from elfa_b200.parallel.mesh import build_context
+        pc = build_context(cfg.runtime.tensor_parallel_size, cfg.runtime.sequence_parallel, "nccl")
+    trainer = Trainer(cfg, telemetry=False, pc=pc)
     rank = trainer.pc.rank
     S, G = cfg.data.seq_len, cfg.training.global_batch_size
     n_micro = cfg.training.gradient_accumulation_steps
@@ -245,7 +262,7 @@ def main() -> int:
             ([f"tp{tpn}+sp"] if tpn > 1 else []) + ([f"dp{dp_size}-zero{cfg.runtime.zero_stage}"] if dp_size > 1 else []))
         peak = peaks.get("bf16_tflops_sustained", 1400.0) * 1e12
         out = {
-            "metric": metric, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "metric": metric, "value": value, "unit": "tokens/s", "n_gpus": real_world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
             "dtype": dtype_note,
             "data": f"synthetic Zipf({cfg.bench.zipf_s}) token ids (seed {cfg.bench.data_seed}), random-init N(0,{cfg.bench.init_std}) weights",
@@ -265,6 +282,10 @@ def main() -> int:
         }
         if args.layers or args.global_batch:
             out["invalid"] = "layer count or global batch overridden for debugging"
+        if args.twin:
+            out["twin_of_n_gpus"] = args.twin
+            out["invalid"] = (f"communication-free twin of rank 0 of a {args.twin}-GPU job on one GPU (collectives are no-ops, numbers are "
+                              "garbage): ms_per_step is the per-rank compute time; exposed communication = measured ms_per_step at N - this")
         print(json.dumps(out))
     if world > 1:
         dist.barrier()
