@@ -82,6 +82,8 @@ class Generator:
             gen = torch.Generator(device="cpu").manual_seed(seed)
         ids = list(prompt_ids) or [0]
         stateful = hasattr(self.model, "forward_with_states")
+        if stateful and len(ids) + max_new_tokens > getattr(self.model, "max_positions", 1 << 62):
+            stateful = False        # learned positions run out: slide a window over the context instead
         states = None
         if stateful:
             logits, states = self.model.forward_with_states(torch.tensor([ids], device=self.device), None)

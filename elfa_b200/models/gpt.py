@@ -53,6 +53,19 @@ class Norm(nn.Module):
         return ops.norm(x, self.weight, self.bias, eps=self.eps, kind=self.kind, residual=residual)
 
 
+def _attend_cached(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """``q [s, B, H, hd]`` (the last ``s`` positions) against ``k, v [t, B, H, hd]`` (all positions so far), causal;
+    fp32 math on a handful of rows. Returns ``[s, B, H * hd]``."""
+    s_, B, H, hd = q.shape
+    t = k.shape[0]
+    sc = torch.einsum("sbhd,tbhd->bhst", q.float(), k.float()) / math.sqrt(hd)
+    if s_ > 1:
+        future = torch.arange(t, device=q.device)[None, :] > (torch.arange(s_, device=q.device)[:, None] + (t - s_))
+        sc = sc.masked_fill(future, float("-inf"))
+    o = torch.einsum("bhst,tbhd->sbhd", torch.softmax(sc, -1), v.float())
+    return o.reshape(s_, B, H * hd).to(q.dtype)
+
+
 class Attention(nn.Module):
     def __init__(self, cfg: Config, pc: ParallelContext, dtype, device, init_std: float, out_std: float):
         super().__init__()
@@ -69,10 +82,19 @@ class Attention(nn.Module):
         self.init_std, self.out_std = init_std, out_std
         self.quant = QuantSpec.from_config(cfg.quant.attention, cfg.quant)
 
-    def forward(self, x):            # x: [S(/tp), B, D]
+    def forward(self, x, cache: Optional[dict] = None):            # x: [S(/tp), B, D]
         h = tpl.column_parallel_linear(x, self.w_qkv, self.pc, quant=self.quant)      # [S, B, 3*local]
         S, B = h.shape[0], h.shape[1]
         qkv = h.view(S, B, 3, self.n_heads, self.head_dim)
+        if cache is not None and cache.get("k") is not None:
+            # incremental decoding: the new rows attend to the cached keys / values and, causally, to each other
+            k_all = torch.cat((cache["k"], qkv[:, :, 1]), 0)
+            v_all = torch.cat((cache["v"], qkv[:, :, 2]), 0)
+            cache["k"], cache["v"] = k_all, v_all
+            o = _attend_cached(qkv[:, :, 0], k_all, v_all)
+            return tpl.row_parallel_linear(o, self.w_o, self.pc, quant=self.quant)
+        if cache is not None:        # prefill: the ordinary kernel, and keep what decoding will need
+            cache["k"], cache["v"] = qkv[:, :, 1].contiguous(), qkv[:, :, 2].contiguous()
         if self.pc.cp_size > 1 and self.pc.cp_mode == "ulysses":     # all-to-all to whole sequences of H / cp heads and back
             from ..parallel.ulysses import ulysses_attention
             o = ulysses_attention(qkv, self.pc.cp_group, causal=True)
@@ -120,11 +142,12 @@ class Block(nn.Module):
         self.mlp = MLP(cfg, pc, dtype, device)
         self.dropout = m.dropout
 
-    def forward(self, x, pending):
+    def forward(self, x, pending, cache: Optional[dict] = None):
         """``pending`` is the previous sub-layer's output that has not been added to the residual
-        stream yet; the add is fused into the next norm kernel."""
+        stream yet; the add is fused into the next norm kernel. ``cache``: this layer's key / value cache
+        when decoding incrementally."""
         n, x = self.ln1(x, pending)
-        a = self.attn(n)
+        a = self.attn(n, cache)
         if self.dropout > 0 and self.training:
             a = torch.nn.functional.dropout(a, self.dropout)
         n, x = self.ln2(x, a)
@@ -235,7 +258,7 @@ class GPTModel(nn.Module):
         return n
 
     # ---------------------------------------------------------------- forward
-    def hidden_states(self, ids: torch.Tensor, pos0: int = 0) -> torch.Tensor:
+    def hidden_states(self, ids: torch.Tensor, pos0: int = 0, caches: Optional[list] = None) -> torch.Tensor:
         """ids ``[B, S]`` → final-norm output ``[S(/tp), B, D]``."""
         pc = self.pc
         ids_sb = ids.t().contiguous()                        # [S, B]
@@ -249,13 +272,35 @@ class GPTModel(nn.Module):
                               vocab_total=self.cfg.model.vocab_size)  # [S, B, D]
         x = tpl.embedding_reduce(x, pc)                      # sum over vocab shards → [S(/tp), B, D]
         pending = None
-        for blk in self.blocks:
-            if self.cfg.bench.activation_checkpointing and self.training:
+        for i, blk in enumerate(self.blocks):
+            if caches is not None:
+                x, pending = blk(x, pending, caches[i])
+            elif self.cfg.bench.activation_checkpointing and self.training:
                 x, pending = torch.utils.checkpoint.checkpoint(blk, x, pending, use_reentrant=False)
             else:
                 x, pending = blk(x, pending)
         n, _ = self.final_norm(x, pending)
         return n
+
+    @property
+    def max_positions(self) -> int:
+        return self.cfg.model.max_seq_len
+
+    def forward_with_states(self, ids: torch.Tensor, states: Optional[dict] = None):
+        """Incremental decoding on one rank: ids ``[B, T]`` (the prompt, then one or a few new tokens per call) →
+        (logits ``[B, T, V]``, states). ``states`` holds the position reached and a key / value cache per layer; the
+        first call (``states=None``) runs the ordinary attention kernel over the prompt, later calls attend to the
+        cache. The learned positions end at ``max_positions``.
+        (reference: ``src/eval/evaluator.zig:419-470`` generates by running the whole context again for every token.)"""
+        assert self.pc.tp_size == 1 and self.pc.cp_size == 1, "incremental decoding runs on one rank"
+        if states is None:
+            states = {"pos": 0, "layers": [{"k": None, "v": None} for _ in self.blocks]}
+        if states["pos"] + ids.shape[1] > self.max_positions:
+            raise ValueError(f"position {states['pos'] + ids.shape[1]} is past the model's {self.max_positions} learned positions")
+        n = self.hidden_states(ids, states["pos"], states["layers"])
+        states["pos"] += ids.shape[1]
+        head = self.lm_head if self.lm_head is not None else self.embed_tokens
+        return tpl.vocab_parallel_logits(n, head, self.pc, gather=True).transpose(0, 1), states
 
     def forward(self, ids: torch.Tensor, targets: Optional[torch.Tensor] = None, pos0: int = 0,
                 loss_denominator: Optional[float] = None, grad_scale: float = 1.0):

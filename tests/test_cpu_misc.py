@@ -329,3 +329,38 @@ def test_trainer_reports_phase_times_when_tracing_is_on():
     assert set(s) == {"forward", "backward", "optimizer"}
     assert s["optimizer"]["calls"] == 2 and s["forward"]["calls"] == s["backward"]["calls"] >= 2
     assert all(v["ms"] > 0 for v in s.values())
+
+
+def test_gpt_incremental_decoding_matches_full_forward():
+    """Key / value cache: prompt in one call, then token by token - the logits equal those of a forward pass over
+    the whole sequence, and greedy generation gives the same tokens with and without the cache."""
+    from elfa_b200.config import Config
+    from elfa_b200.eval.evaluator import Generator
+    from elfa_b200.models.gpt import GPTModel
+    cfg = Config.from_file(os.path.join(ROOT, "configs", "bench", "smoke_cpu.yaml"), env_override=False)
+    model = GPTModel(cfg, None, torch.device("cpu"))
+    model.reset_parameters(3)
+    model.eval()
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, cfg.model.vocab_size, (2, 24), generator=g)
+    with torch.no_grad():
+        full = model(ids)                                            # [B, S, V]
+        logits, st = model.forward_with_states(ids[:, :10])
+        parts = [logits]
+        for t in range(10, 20):
+            logits, st = model.forward_with_states(ids[:, t:t + 1], st)
+            parts.append(logits)
+        logits, st = model.forward_with_states(ids[:, 20:24], st)   # several new tokens at once
+        parts.append(logits)
+    inc = torch.cat(parts, 1)
+    assert st["pos"] == 24 and inc.shape == full.shape
+    assert (inc - full).abs().max().item() < 2e-4
+    gen = Generator(model, device=torch.device("cpu"))
+    with_cache = gen.generate_greedy([5, 6, 7], 12)
+    model_max = cfg.model.max_seq_len
+    try:
+        cfg.model.max_seq_len = 8        # positions "run out": the generator takes the windowed path (positions stay valid: 15 <= real table)
+        windowed = gen.generate_greedy([5, 6, 7], 12)
+    finally:
+        cfg.model.max_seq_len = model_max
+    assert with_cache == windowed and len(with_cache) == 15
