@@ -364,3 +364,30 @@ def test_gpt_incremental_decoding_matches_full_forward():
     finally:
         cfg.model.max_seq_len = model_max
     assert with_cache == windowed and len(with_cache) == 15
+
+
+def test_ring_attention_block_schedule_covers_the_causal_triangle_evenly():
+    from elfa_b200.parallel.ring_attention import block_schedule, zigzag_slices
+    for world in (2, 3, 8):
+        # contiguous split: rank r computes r full blocks and one masked one
+        for r in range(world):
+            sched = [block_schedule(r, j, True, False) for j in range(world)]
+            assert sum(len(s) for s in sched) == r + 1 and sched[r] == [(0, 0, True)]
+        # zig-zag split: every (query chunk, key chunk) pair of the 2N-chunk causal triangle appears exactly once ...
+        seen = set()
+        work = []
+        for r in range(world):
+            chunk_of = lambda rank, part: rank if part == 0 else 2 * world - 1 - rank
+            w = 0.0
+            for j in range(world):
+                for qi, ki, masked in block_schedule(r, j, True, True):
+                    qc, kc = chunk_of(r, qi), chunk_of(j, ki)
+                    assert (qc, kc) not in seen and (kc < qc or (kc == qc and masked)) and (masked == (kc == qc))
+                    seen.add((qc, kc))
+                    w += 0.5 if masked else 1.0
+            work.append(w)
+        n2 = 2 * world
+        assert seen == {(q, k) for q in range(n2) for k in range(q + 1)}
+        assert len(set(work)) == 1                      # ... and every rank has the same amount of work
+        (a0, a1), (b0, b1) = zigzag_slices(64 * n2, 1, world)
+        assert (a0, a1) == (64, 128) and (b0, b1) == (64 * (n2 - 2), 64 * (n2 - 1))
