@@ -160,7 +160,8 @@ def main() -> int:
         cfg.runtime.tensor_parallel_size = world
         cfg.runtime.zero_stage = 0
         mb = args.micro_batch or 4      # 4 sequences of 4096 tokens per micro-batch: 160 GB peak on one GPU, less with tensor parallelism
-        scaling, metric = "strong", METRIC
+        scaling = "strong"
+        metric = METRIC if cfg.model.name.startswith("gpt-7b") else f"tokens/sec/box (max over ranks) {cfg.model.name}"
     else:
         # the data-parallel configurations (ZeRO stage from the file): tp = min(file's tp, N), the rest is data parallel
         tp = min(yaml_tp, world)
@@ -277,8 +278,9 @@ def main() -> int:
                     "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": launches,
             "clocks": clocks,
-            "mfu_of_measured_sustained_bf16": value * flops / (peak * world),
-            "model_tflops_per_gpu": value * flops / world / 1e12,
+            # the FLOP model covers the GPT family (dense GEMMs + softmax attention) only
+            "mfu_of_measured_sustained_bf16": value * flops / (peak * world) if cfg.mixer() == "attention" else None,
+            "model_tflops_per_gpu": value * flops / world / 1e12 if cfg.mixer() == "attention" else None,
             "loss": loss, "device_status": st,
             "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
         }
