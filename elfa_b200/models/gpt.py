@@ -29,7 +29,7 @@ from .. import ops
 from ..config import Config
 from ..parallel.mesh import ParallelContext
 from ..parallel import tp as tpl
-from ..quant.qat import QuantSpec, fake_quant
+from ..quant.qat import QuantSpec
 
 
 def _dtype(name: str) -> torch.dtype:

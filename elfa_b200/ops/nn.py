@@ -14,7 +14,7 @@ from typing import Optional, Tuple
 import torch
 
 from ..native import lib, stream_ptr
-from .gemm import dgelu_tanh_ref, gelu_tanh_ref
+from .gemm import gelu_tanh_ref
 
 LAYERNORM, RMSNORM = 0, 1
 

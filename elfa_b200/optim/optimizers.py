@@ -16,7 +16,7 @@ Nothing in the step reads back to the host.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from typing import Dict, Optional
 
 import torch
 import torch.distributed as dist

@@ -12,8 +12,6 @@ All functions work on any ``torch.distributed`` backend (NCCL on GPUs, gloo on C
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
-
 import torch
 import torch.distributed as dist
 
