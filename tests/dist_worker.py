@@ -164,7 +164,9 @@ def mode_cp(dev, dtype, tp, cp_mode="ring"):
         e_o = (out.float() - take(ref)).abs().max().item()
         e_g = (loc.grad.float() - take(ref_in.grad)).abs().max().item()
         assert e_o < tol and e_g < tol_g, f"ring attention causal={causal}: out err {e_o}, grad err {e_g}"
+    seq = 256 * cp                   # every block product gets at least one full 128-row tile, also under the zig-zag split
     cfg = small_cfg(dtype, tp, "nccl")
+    cfg.data.seq_len = cfg.model.max_seq_len = seq
     cfg.runtime.world_size = world
     cfg.runtime.context_parallel_size = cp
     cfg.runtime.context_parallel_mode = cp_mode
@@ -173,6 +175,7 @@ def mode_cp(dev, dtype, tp, cp_mode="ring"):
     losses = tr.run(max_steps=4)
     if rank == 0:
         cfg1 = small_cfg(dtype, 1, "nccl")
+        cfg1.data.seq_len = cfg1.model.max_seq_len = seq
         cfg1.runtime.world_size = 1
         ref_l = Trainer(cfg1, device=dev, pc=ParallelContext(), telemetry=False).run(max_steps=4)
         tol = 2e-4 if dtype == "fp32" else 0.05
