@@ -327,61 +327,93 @@ __global__ void __launch_bounds__(256) efla_bwd_finish_kernel(const __nv_bfloat1
 
 
 // ------------------------------------------------------------------------------------ ShortConv
-__global__ void __launch_bounds__(256) shortconv_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                                                            const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ y, int B,
-                                                            int T, int C, int W) {
-  const long long n = (long long)B * T * C;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-    const int c = (int)(i % C);
-    const int t = (int)((i / C) % T);
-    float acc = bias ? __bfloat162float(bias[c]) : 0.f;
-    const int wmax = min(W, t + 1);
-    for (int j = 0; j < wmax; ++j) acc += __bfloat162float(x[i - (long long)j * C]) * __bfloat162float(w[c * W + j]);
-    y[i] = __float2bfloat16(acc);
+// Forward and input gradient share one kernel (DX = false: y[t] = bias + sum_j x[t - j] w[j]; DX = true:
+// dx[t] = sum_j dy[t + j] w[j]). A lane owns a PAIR of adjacent channels (4-byte loads, 128 bytes per warp); the
+// CTA's 64 channels x W weights sit transposed in shared memory (the [C, W] layout read directly would touch a
+// different cache line in every lane); a warp walks SC_ROWS / 8 consecutive time steps, so the W - 1 re-reads of an
+// input element come from L1. grid (ceil(B T / SC_ROWS), ceil(C / 64)), block (32, 8), dynamic smem W * 64 floats.
+constexpr int SC_ROWS = 64;
+
+template <bool DX>
+__global__ void __launch_bounds__(256) shortconv_apply_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ w,
+                                                              const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out,
+                                                              int B, int T, int C, int W) {
+  extern __shared__ float sw[];                          // [W][64]
+  const int lane = threadIdx.x, warp = threadIdx.y;
+  const int c0 = blockIdx.y * 64;
+  for (int i = warp * 32 + lane; i < W * 64; i += 256) {
+    const int cl = i / W, j = i % W;                     // consecutive threads read consecutive weights of a channel
+    sw[j * 64 + cl] = c0 + cl < C ? __bfloat162float(w[(long long)(c0 + cl) * W + j]) : 0.f;
+  }
+  __syncthreads();
+  const int c = c0 + 2 * lane;
+  if (c >= C) return;
+  const long long rows = (long long)B * T;
+  const long long r0 = (long long)blockIdx.x * SC_ROWS + warp * (SC_ROWS / 8);
+  float b0 = 0.f, b1 = 0.f;
+  if (!DX && bias) {
+    b0 = __bfloat162float(bias[c]);
+    b1 = __bfloat162float(bias[c + 1]);
+  }
+  for (long long r = r0; r < min(rows, r0 + SC_ROWS / 8); ++r) {
+    const int t = (int)(r % T);
+    const int taps = DX ? min(W, T - t) : min(W, t + 1);
+    const __nv_bfloat162* src = reinterpret_cast<const __nv_bfloat162*>(in + r * C + c);
+    const long long step = DX ? (long long)(C / 2) : -(long long)(C / 2);
+    float a0 = b0, a1 = b1;
+#pragma unroll 4
+    for (int j = 0; j < taps; ++j) {
+      const float2 xv = __bfloat1622float2(src[j * step]);
+      const float2 wv = *reinterpret_cast<const float2*>(sw + j * 64 + 2 * lane);
+      a0 += xv.x * wv.x;
+      a1 += xv.y * wv.y;
+    }
+    *reinterpret_cast<__nv_bfloat162*>(out + r * C + c) = __floats2bfloat162_rn(a0, a1);
   }
 }
 
-// dx[b,t,c] = sum_w dy[b,t+w,c] weight[c,w]
-__global__ void __launch_bounds__(256) shortconv_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ w,
-                                                               __nv_bfloat16* __restrict__ dx, int B, int T, int C, int W) {
-  const long long n = (long long)B * T * C;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-    const int c = (int)(i % C);
-    const int t = (int)((i / C) % T);
-    float acc = 0.f;
-    const int wmax = min(W, T - t);
-    for (int j = 0; j < wmax; ++j) acc += __bfloat162float(dy[i + (long long)j * C]) * __bfloat162float(w[c * W + j]);
-    dx[i] = __float2bfloat16(acc);
-  }
-}
+// dw[c,w] = sum_{b,t>=w} dy[b,t,c] x[b,t-w,c]; db[c] = sum dy. A CTA owns 32 channels (lane = channel) and SC_TAPS taps;
+// its 32 warps stride over all B T rows (four rows in flight per warp), every row's dy is read once and multiplied with
+// the SC_TAPS shifted inputs; the warps' partial sums are added in warp order (no atomics). grid (ceil(C / 32),
+// ceil(W / SC_TAPS)), block (32, 32); the CTAs with blockIdx.y == 0 also produce the bias gradient.
+constexpr int SC_TAPS = 4;
 
-// dw[c,w] = sum_{b,t>=w} dy[b,t,c] x[b,t-w,c]; db[c] = sum dy. grid (ceil(C/32), W + 1), block (32, 8):
-// blockIdx.y == W computes the bias gradient.
-__global__ void __launch_bounds__(256) shortconv_bwd_dw_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
-                                                               float* __restrict__ dw, float* __restrict__ db, int B, int T, int C,
-                                                               int W) {
-  __shared__ float sm[8][33];
-  const int c = blockIdx.x * 32 + threadIdx.x;
-  const int wj = blockIdx.y;
-  float acc = 0.f;
+__global__ void __launch_bounds__(1024) shortconv_bwd_dw_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                                                                float* __restrict__ dw, float* __restrict__ db, int B, int T, int C,
+                                                                int W) {
+  __shared__ float sm[32][SC_TAPS + 1][33];
+  const int lane = threadIdx.x, warp = threadIdx.y;
+  const int c = blockIdx.x * 32 + lane;
+  const int w0 = blockIdx.y * SC_TAPS;
+  float acc[SC_TAPS], accb = 0.f;
+#pragma unroll
+  for (int u = 0; u < SC_TAPS; ++u) acc[u] = 0.f;
   if (c < C) {
     const long long rows = (long long)B * T;
-    for (long long r = threadIdx.y; r < rows; r += 8) {
+#pragma unroll 4
+    for (long long r = warp; r < rows; r += 32) {
       const int t = (int)(r % T);
       const float g = __bfloat162float(dy[r * C + c]);
-      if (wj == W) acc += g;
-      else if (t >= wj) acc += g * __bfloat162float(x[(r - wj) * C + c]);
+      accb += g;
+#pragma unroll
+      for (int u = 0; u < SC_TAPS; ++u) {
+        const int wj = w0 + u;
+        if (wj < W && t >= wj) acc[u] += g * __bfloat162float(x[(r - wj) * C + c]);
+      }
     }
   }
-  sm[threadIdx.y][threadIdx.x] = acc;
+#pragma unroll
+  for (int u = 0; u < SC_TAPS; ++u) sm[warp][u][lane] = acc[u];
+  sm[warp][SC_TAPS][lane] = accb;
   __syncthreads();
-  if (threadIdx.y == 0 && c < C) {
+  if (warp <= SC_TAPS && c < C) {                        // warp u adds up tap u, warp SC_TAPS the bias column
     float s = 0.f;
-    for (int i = 0; i < 8; ++i) s += sm[i][threadIdx.x];
-    if (wj == W) { if (db) db[c] = s; }
-    else dw[c * W + wj] = s;
+    for (int i = 0; i < 32; ++i) s += sm[i][warp][lane];
+    if (warp == SC_TAPS) {
+      if (db && blockIdx.y == 0) db[c] = s;
+    } else if (w0 + warp < W) {
+      dw[(long long)c * W + w0 + warp] = s;
+    }
   }
 }
 
@@ -451,10 +483,10 @@ ELFA_API int elfa_efla_scan_bwd(const void* k, const void* v, const float* beta,
 
 ELFA_API int elfa_shortconv_fwd(const void* x, const void* w, const void* bias, void* y, int B, int T, int C, int W, void* stream) {
   ELFA_REQUIRE(x && w && y && B > 0 && T > 0 && C > 0 && W > 0, "shortconv_fwd: bad arguments");
-  const long long n = (long long)B * T * C;
-  long long blocks = (n + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  shortconv_fwd_kernel<<<(int)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  ELFA_REQUIRE(C % 2 == 0 && W <= 128, "shortconv_fwd: the channel count must be even and the window at most 128");
+  const long long rows = (long long)B * T;
+  dim3 grid((unsigned)((rows + SC_ROWS - 1) / SC_ROWS), (C + 63) / 64), block(32, 8);
+  shortconv_apply_kernel<false><<<grid, block, (size_t)W * 64 * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(bias),
       static_cast<__nv_bfloat16*>(y), B, T, C, W);
   ELFA_CUDA(cudaGetLastError());
@@ -466,15 +498,15 @@ ELFA_API int elfa_shortconv_fwd(const void* x, const void* w, const void* bias, 
 ELFA_API int elfa_shortconv_bwd(const void* x, const void* w, const void* dy, void* dx, float* dw, float* db, int B, int T, int C, int W,
                                 void* stream) {
   ELFA_REQUIRE(x && w && dy && dx && dw && B > 0 && T > 0 && C > 0 && W > 0, "shortconv_bwd: bad arguments");
+  ELFA_REQUIRE(C % 2 == 0 && W <= 128, "shortconv_bwd: the channel count must be even and the window at most 128");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const long long n = (long long)B * T * C;
-  long long blocks = (n + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  shortconv_bwd_dx_kernel<<<(int)blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(w),
-                                                      static_cast<__nv_bfloat16*>(dx), B, T, C, W);
-  dim3 grid((C + 31) / 32, W + 1), block(32, 8);
-  shortconv_bwd_dw_kernel<<<grid, block, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy), dw, db, B,
-                                                 T, C, W);
+  const long long rows = (long long)B * T;
+  dim3 grid((unsigned)((rows + SC_ROWS - 1) / SC_ROWS), (C + 63) / 64), block(32, 8);
+  shortconv_apply_kernel<true><<<grid, block, (size_t)W * 64 * sizeof(float), s>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(w), nullptr, static_cast<__nv_bfloat16*>(dx), B, T, C, W);
+  dim3 grid2((C + 31) / 32, (W + SC_TAPS - 1) / SC_TAPS), block2(32, 32);
+  shortconv_bwd_dw_kernel<<<grid2, block2, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy), dw, db, B,
+                                                   T, C, W);
   ELFA_CUDA(cudaGetLastError());
   ::elfa::count_launches(2);
   return ELFA_OK;
