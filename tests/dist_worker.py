@@ -3,6 +3,7 @@
 modes:
   fused   - fused ag_gemm / gemm_rs against the library (NCCL) path, repeated calls (GPU)
   tp      - a small GPT trained with TP=world (+sequence parallel) against the same model on one rank
+  hybrid  - tensor parallel x data parallel with ZeRO-2 and mixed NVFP4 / MXFP8 QAT against the single-rank result
   cp      - ring attention and a context-parallel GPT against the single-rank result
   timeout - a fused wait that nothing satisfies must return with the timeout status, not hang (GPU)
 """
@@ -225,6 +226,36 @@ def mode_zero(dev, backend, dtype, stage):
     dist.barrier()
 
 
+def mode_hybrid(dev, backend, dtype, tp):
+    """The layout of the 13B benchmark configuration in small: tensor parallel groups of ``tp`` ranks x data parallel
+    with ZeRO-2, NVFP4 QAT on the MLP GEMMs and MXFP8 on the attention GEMMs, against one rank on the global batch."""
+    from elfa_b200.parallel.mesh import ParallelContext
+    from elfa_b200.trainer import Trainer
+    pc = build_context(tp, True, backend)
+    assert pc.tp_size == tp and pc.dp_size == dist.get_world_size() // tp
+    assert pc.tp_ranks == [pc.dp_rank * tp + t for t in range(tp)]          # tensor-parallel ranks are neighbours
+    cfg = small_cfg(dtype, tp, backend)
+    cfg.runtime.world_size = dist.get_world_size()
+    cfg.runtime.zero_stage = 2
+    cfg.quant.attention, cfg.quant.mlp = "mxfp8", "nvfp4"
+    cfg.training.micro_batch_size = 2
+    cfg.training.global_batch_size = 2 * pc.dp_size
+    tr = Trainer(cfg, device=dev, pc=pc, telemetry=False)
+    losses = tr.run(max_steps=4)
+    if pc.rank == 0:
+        cfg1 = small_cfg(dtype, 1, "nccl")
+        cfg1.runtime.world_size = 1
+        cfg1.runtime.zero_stage = 0
+        cfg1.quant.attention, cfg1.quant.mlp = "mxfp8", "nvfp4"
+        cfg1.training.micro_batch_size = cfg1.training.global_batch_size = 2 * pc.dp_size
+        ref = Trainer(cfg1, device=dev, pc=ParallelContext(), telemetry=False).run(max_steps=4)
+        tol = 2e-3 if dtype == "fp32" else 0.05
+        for a, b in zip(losses, ref):
+            assert abs(a - b) < tol * max(1.0, abs(b)), f"hybrid losses {losses} differ from single-rank {ref}"
+        print(f"HYBRID_OK tp={tp} dp={pc.dp_size} losses={[round(x, 4) for x in losses]} ref={[round(x, 4) for x in ref]}")
+    dist.barrier()
+
+
 def mode_ckpt(dev, stage, ckpt_dir):
     """Sharded optimizer state survives a checkpoint: train 2 + save + 2 more == resume + 2."""
     from elfa_b200.trainer import Trainer
@@ -328,7 +359,7 @@ def main():
     mode = sys.argv[1]
     backend = sys.argv[2] if len(sys.argv) > 2 else "nccl"
     dtype = sys.argv[3] if len(sys.argv) > 3 else "bf16"
-    use_cuda = torch.cuda.is_available() and mode not in ("tp_cpu", "zero_cpu", "ckpt_cpu", "killrank_cpu", "cp_cpu")
+    use_cuda = torch.cuda.is_available() and mode not in ("tp_cpu", "zero_cpu", "ckpt_cpu", "killrank_cpu", "cp_cpu", "hybrid_cpu")
     world = init_distributed("nccl" if use_cuda else "gloo")
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if use_cuda else torch.device("cpu")
     if mode == "killrank_cpu":
@@ -336,6 +367,10 @@ def main():
         return
     if mode == "ckpt_cpu":
         mode_ckpt(dev, int(sys.argv[2]), sys.argv[3])
+        dist.destroy_process_group()
+        return
+    if mode in ("hybrid", "hybrid_cpu"):
+        mode_hybrid(dev, backend, dtype, int(sys.argv[4]) if len(sys.argv) > 4 else 2)
         dist.destroy_process_group()
         return
     if mode in ("cp", "cp_cpu"):

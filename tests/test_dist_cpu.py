@@ -30,6 +30,13 @@ def test_context_parallel_attention_and_training_on_cpu(world, tp, mode):
     assert "CP_OK" in r.stdout
 
 
+def test_tensor_parallel_times_data_parallel_zero2_mixed_quant_on_cpu():
+    """The layout of the 13B benchmark configuration in small: TP 2 x DP 2, ZeRO-2, NVFP4 MLP + MXFP8 attention QAT."""
+    r = _run(4, ["hybrid_cpu", "nccl", "fp32", "2"], 29691)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "HYBRID_OK tp=2 dp=2" in r.stdout
+
+
 @pytest.mark.parametrize("stage", [0, 1, 3])
 def test_zero_data_parallel_matches_single_rank_on_cpu(stage):
     r = _run(2, ["zero_cpu", "nccl", "fp32", str(stage)], 29621 + stage)
