@@ -325,7 +325,8 @@ class Lion(_Base):
 
 def newton_schulz(y: torch.Tensor, iters: int) -> torch.Tensor:
     """``Y <- 0.5 * Y (3I - Y^T Y)`` (or the left form when rows < cols) for a Frobenius-normalised
-    matrix. CUDA bf16 matrices run on the tcgen05 GEMM with the 0.5 folded into ``alpha``."""
+    matrix. CUDA bf16 matrices run on the tcgen05 GEMM with the 0.5 folded into ``alpha`` and ``3I -`` into the
+    epilogue (``alpha = -1`` plus an additive ``3I`` term): two launches per iteration."""
     rows, cols = y.shape
     right = cols <= rows
     if not y.is_cuda:
@@ -338,17 +339,28 @@ def newton_schulz(y: torch.Tensor, iters: int) -> torch.Tensor:
                 g = 3 * torch.eye(rows) - yf @ yf.t()
                 yf = 0.5 * g @ yf
         return yf.to(y.dtype)
-    st = stream_ptr(y)
+    eye3 = _three_eye(cols if right else rows, y.device)
     for _ in range(iters):
         if right:
-            g = gemm(y, y, a_mn=True, b_mn=True)                 # Y^T Y  [cols, cols]
-            lib.call("elfa_three_i_minus", g, cols, st)
+            g = gemm(y, y, a_mn=True, b_mn=True, alpha=-1.0, aux=eye3, add_aux=True)     # 3I - Y^T Y  [cols, cols], one launch
             y = gemm(y, g, b_mn=True, alpha=0.5)                 # Y G
         else:
-            g = gemm(y, y)                                       # Y Y^T  [rows, rows]
-            lib.call("elfa_three_i_minus", g, rows, st)
+            g = gemm(y, y, alpha=-1.0, aux=eye3, add_aux=True)   # 3I - Y Y^T  [rows, rows]
             y = gemm(g, y, b_mn=True, alpha=0.5)                 # G Y
     return y
+
+
+_EYE3: Dict[tuple, torch.Tensor] = {}
+
+
+def _three_eye(n: int, device) -> torch.Tensor:
+    """``3 I`` in bf16, kept per size: the additive term of the Newton-Schulz product's epilogue."""
+    key = (n, str(device))
+    t = _EYE3.get(key)
+    if t is None:
+        t = (3.0 * torch.eye(n, device=device)).to(torch.bfloat16)
+        _EYE3[key] = t
+    return t
 
 
 class Muon(_Base):

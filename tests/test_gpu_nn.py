@@ -159,3 +159,18 @@ def test_softmax_rows(cuda_device, rows, cols):
     ref = torch.softmax(x.float() * 0.7, dim=-1)
     assert (y.float() - ref).abs().max() <= 2 ** -8 * ref.max() + 1e-4
     assert (y.float().sum(-1) - 1).abs().max() < 0.02
+
+
+def test_newton_schulz_on_the_gemm_matches_fp32(cuda_device):
+    """Muon's orthogonalisation on the tcgen05 GEMM (``3I -`` and the 0.5 folded into epilogues) against the fp32 loop,
+    for the right (tall) and the left (wide) form."""
+    from elfa_b200.optim.optimizers import newton_schulz
+    g = torch.Generator().manual_seed(4)
+    for rows, cols in ((512, 256), (256, 768)):
+        m = torch.randn(rows, cols, generator=g)
+        m = (m / m.norm()).to(torch.bfloat16)
+        got = newton_schulz(m.to(cuda_device), 3).float().cpu()
+        ref = newton_schulz(m.float(), 3).float()
+        assert (got - ref).abs().max().item() < 0.02 * ref.abs().max().item() + 1e-3
+    torch.cuda.synchronize()
+    assert native.status() == 0
