@@ -391,3 +391,19 @@ def test_ring_attention_block_schedule_covers_the_causal_triangle_evenly():
         assert len(set(work)) == 1                      # ... and every rank has the same amount of work
         (a0, a1), (b0, b1) = zigzag_slices(64 * n2, 1, world)
         assert (a0, a1) == (64, 128) and (b0, b1) == (64 * (n2 - 2), 64 * (n2 - 1))
+
+
+def test_ncu_summary_reads_raw_csv():
+    from elfa_b200.utils import ncu_summary
+    text = "\n".join([
+        "==PROF== noise that is not CSV",
+        '"ID","Kernel Name","gpu__time_duration.sum","launch__grid_size","smsp__average_warps_issue_stalled_wait_per_issue_active.ratio",'
+        '"smsp__average_warps_issue_stalled_barrier_per_issue_active.ratio","smsp__average_warps_issue_stalled_selected_per_issue_active.ratio"',
+        '"","","us","","inst","inst","inst"',
+        '"0","my_kernel<64>(const float *)","12.5","148","1.25","0.5","1.0"',
+    ])
+    launches = ncu_summary.parse(text)
+    assert len(launches) == 1 and launches[0]["gpu__time_duration.sum"] == "12.5 us"
+    md = ncu_summary.summarise(launches[0])
+    assert "my_kernel<64>" in md and "| duration | 12.5 us |" in md and "| grid | 148 |" in md
+    assert "wait 1.25, barrier 0.50" in md and "selected" not in md
