@@ -177,6 +177,10 @@ def cmd_profile(a) -> int:
     print("Profiling recipes (run on a GPU machine):\n"
           "  ncu --set full --clock-control none -k regex:gemm_bf16_kernel -c 3 -o prof python bench.py --layers 2 --steps 1 --warmup 1\n"
           "  ncu --metrics gpu__time_duration.sum --clock-control none --csv --log-file launches.csv python bench.py --steps 1 --warmup 1\n"
+          "  python -m elfa_b200.utils.ncu_summary prof.ncu-rep        # roofline counters + top stall reasons as a table (no GPU needed)\n"
+          "  python -m elfa_b200.utils.microbench gemm|attn_fwd|efla|...   # one kernel, device-timed, for a small capture\n"
+          "  ELFA_TRACE=1 adds NVTX ranges and per-phase device times (trainer.tracer.summary())\n"
+          "  python bench.py --twin 8    # per-rank compute time of an 8-rank job without communication, on one GPU\n"
           "  ELFA_FLAG_TIMEOUT_MS=500 shortens every device-side wait; the status word reports a timeout")
     return 0
 
