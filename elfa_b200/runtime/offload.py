@@ -135,3 +135,64 @@ class NvmeStore:
     def close(self) -> None:
         self._q.put(None)
         self._t.join()
+
+
+class OptimizerStateOffload:
+    """Keeps the optimizer's moment buffers on the host (and optionally on NVMe) between steps.
+
+    ``evict()`` after ``optimizer.step`` copies every state tensor to its pinned mirror on the side stream and then
+    releases the device storage (the tensor objects the optimizer holds stay the same, their storage shrinks to
+    zero bytes); ``fetch()`` before the next step gives the storage back and refills it. With ``nvme_dir`` the
+    mirrors are also written to one file per tensor and read back from there, which is what survives when the host
+    memory is needed for something else. Tensors whose storage cannot be resized (slices of a symmetric arena)
+    are left where they are.
+
+    reference: ``src/distributed/zero_sharding.zig:183-247`` (``offloadToCPU`` / ``offloadToNVMe`` /
+    ``loadFromNVMe``), YAML ``runtime.cpu_offload``, ``runtime.nvme_offload``, ``runtime.nvme_path``.
+    """
+
+    def __init__(self, tensors: Dict[str, torch.Tensor], device: torch.device, nvme_dir: Optional[str] = None):
+        self.host = HostOffloader(device)
+        self.nvme = NvmeStore(nvme_dir) if nvme_dir else None
+        self.tensors: Dict[str, torch.Tensor] = {}
+        self.nbytes: Dict[str, int] = {}
+        for name, t in tensors.items():
+            st = t.untyped_storage()
+            # only whole, privately owned storages can be released and re-created
+            if t.is_contiguous() and t.storage_offset() == 0 and st.nbytes() == t.numel() * t.element_size() and st.resizable():
+                self.tensors[name] = t
+                self.nbytes[name] = st.nbytes()
+        self.resident = True
+
+    def evict(self) -> None:
+        if not self.resident:
+            return
+        for name, t in self.tensors.items():
+            self.host.offload(name, t)
+        self.host.synchronize()                       # the copies have left the device before its memory is released
+        for name, t in self.tensors.items():
+            if self.nvme is not None:
+                self.nvme.write(name, self.host.mirrors[name])
+            t.untyped_storage().resize_(0)
+        if self.nvme is not None:
+            self.nvme.flush()
+        self.resident = False
+
+    def fetch(self) -> None:
+        if self.resident:
+            return
+        for name, t in self.tensors.items():
+            t.untyped_storage().resize_(self.nbytes[name])
+            if self.nvme is not None:
+                self.nvme.read(name, self.host.mirrors[name]).wait()
+            self.host.prefetch(name, t)
+        self.host.wait()
+        self.resident = True
+
+    def device_bytes(self) -> int:
+        return sum(t.untyped_storage().nbytes() for t in self.tensors.values())
+
+    def close(self) -> None:
+        self.fetch()
+        if self.nvme is not None:
+            self.nvme.close()

@@ -87,6 +87,13 @@ class Trainer:
             self.flat = FlatParams(self.model.named_checkpoint_parameters(), dp_size=pc.dp_size, dp_rank=pc.dp_rank, allocator=dp_arena)
         self.zero3 = bool(getattr(self.flat, "presharded", False))
         self.optimizer = build_optimizer(cfg, self.flat, pc)
+        # runtime.cpu_offload / nvme_offload: optimizer state lives on the host (and NVMe) between steps
+        self.offload = None
+        if cfg.runtime.cpu_offload or cfg.runtime.nvme_offload:
+            from .runtime.offload import OptimizerStateOffload
+            nvme = os.path.join(cfg.runtime.nvme_path, f"rank{pc.rank}") if cfg.runtime.nvme_offload else None
+            self.offload = OptimizerStateOffload(self._optimizer_state_tensors(), self.device, nvme)
+            self.offload.evict()
         t = cfg.training
         self.scheduler = LRScheduler(t.lr_schedule, t.learning_rate, t.min_learning_rate, t.warmup_steps, t.total_steps)
         self.scaler = LossScaler(t.loss_scale if t.mixed_precision else 1.0, t.dynamic_loss_scale and t.mixed_precision)
@@ -177,7 +184,13 @@ class Trainer:
             self.flat.grads[:1].fill_(float("nan"))     # the optimizer's non-finite guard must skip this step
         lr = self.scheduler.get_lr()
         with self.tracer.phase("optimizer"):
+            if self.offload is not None:
+                self.offload.fetch()
             self.optimizer.step(lr)
+            if self.offload is not None:
+                if self.device.type != "cuda" and self.ckpt is not None:
+                    self.ckpt.wait()        # an asynchronous save may still be reading the state tensors themselves
+                self.offload.evict()
         self.scheduler.step()
         self.step += 1
         self.tokens_seen += sum(b.num_tokens for b in batches) * (self.pc.dp_size // self.pc.cp_size)
@@ -273,13 +286,26 @@ class Trainer:
             out.append((name, t))
         return out
 
+    def _optimizer_state_tensors(self) -> dict:
+        opt = self.optimizer
+        if hasattr(opt, "muon"):            # Lion + Muon: two moment buffers, one shared master copy
+            d = {"muon.m": opt.muon.m, "lion.m": opt.lion.m}
+            if not opt.muon.master_is_param:
+                d["master"] = opt.muon.master
+            return d
+        return dict(opt.state_tensors())
+
     def save_checkpoint(self) -> Optional[str]:
         cfg = self.cfg
+        if self.offload is not None:
+            self.offload.fetch()
         tensors = self._gather_logical()
         opt_state = None
         if cfg.checkpoint.save_optimizer:
             opt_state = {"optimizer": self.optimizer.state_dict(), "scheduler": self.scheduler.state_dict(),
                          "scaler": self.scaler.state_dict(), "world": (self.pc.dp_size, self.pc.tp_size)}
+        if self.offload is not None and self.device.type == "cuda":
+            self.offload.evict()            # state_dict made host copies; on a CPU device it returns the tensors themselves
         if self.ckpt is None:
             return None
         meta = CheckpointMetadata(step=self.step, epoch=self.epoch, tokens_seen=self.tokens_seen,
@@ -290,6 +316,15 @@ class Trainer:
         return self.ckpt.save(self.step, tensors, meta, opt_state, rng, cfg.to_yaml())
 
     def resume(self, path: str) -> CheckpointMetadata:
+        if self.offload is not None:
+            self.offload.fetch()
+        try:
+            return self._resume(path)
+        finally:
+            if self.offload is not None:
+                self.offload.evict()
+
+    def _resume(self, path: str) -> CheckpointMetadata:
         mgr = self.ckpt or CheckpointManager(self.cfg.checkpoint.dir or os.path.dirname(path), 0)
         meta, tensors, opt, rng, _ = mgr.load_full(path)
         pc = self.pc
@@ -325,6 +360,8 @@ class Trainer:
         return meta
 
     def close(self) -> None:
+        if self.offload is not None:
+            self.offload.close()
         if self.ckpt is not None:
             self.ckpt.wait()
         if self.telemetry is not None:

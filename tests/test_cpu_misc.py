@@ -407,3 +407,35 @@ def test_ncu_summary_reads_raw_csv():
     md = ncu_summary.summarise(launches[0])
     assert "my_kernel<64>" in md and "| duration | 12.5 us |" in md and "| grid | 148 |" in md
     assert "wait 1.25, barrier 0.50" in md and "selected" not in md
+
+
+@pytest.mark.parametrize("nvme", [False, True])
+def test_optimizer_state_offload_between_steps(tmp_path, nvme):
+    """runtime.cpu_offload / nvme_offload: the moments leave the device after every step and come back for the next;
+    the loss curve and a save / resume are the same as without offload."""
+    from elfa_b200.config import Config
+    from elfa_b200.trainer import Trainer
+
+    def run(offload, ckpt_dir=""):
+        cfg = Config.from_file(os.path.join(ROOT, "configs", "bench", "smoke_cpu.yaml"), env_override=False)
+        cfg.checkpoint.dir = ckpt_dir
+        cfg.checkpoint.save_interval = 0
+        cfg.telemetry.log_file = ""
+        cfg.runtime.cpu_offload = offload and not nvme
+        cfg.runtime.nvme_offload = offload and nvme
+        cfg.runtime.nvme_path = str(tmp_path / "nvme")
+        return Trainer(cfg, device=torch.device("cpu"), telemetry=False)
+
+    base = run(False)
+    ref = base.run(max_steps=4)
+    tr = run(True, str(tmp_path / "ck"))
+    assert tr.offload is not None and tr.offload.device_bytes() == 0 and len(tr.offload.tensors) >= 2
+    got = tr.run(max_steps=2)
+    assert tr.offload.device_bytes() == 0                 # evicted again after the step
+    path = tr.save_checkpoint()
+    tr.close()
+    tr2 = run(True, str(tmp_path / "ck"))
+    tr2.resume(path)
+    got += tr2.run(max_steps=2)
+    tr2.close()
+    assert got == pytest.approx(ref, abs=1e-5)
