@@ -260,3 +260,74 @@ class DataLoader:
             if b is None:
                 return
             yield b
+
+
+class PrefetchLoader:
+    """Assembles batches ahead of the training loop on a worker thread.
+
+    Wraps a :class:`DataLoader`: ``next_cycling()`` hands out the batches in exactly the order the wrapped loader
+    would, but up to ``depth`` of them (``data.prefetch_factor x data.num_workers``) are already read, shifted into
+    input / target and pinned when they are asked for. ``epoch`` is the epoch of the batch handed out last, not of
+    the one the worker is reading. ``skip`` (resume) must come before the first batch.
+
+    reference: ``src/data/dataset.zig:288-340`` (``DataLoader``: batches are built inline in the training loop; the
+    YAML keys ``data.prefetch_factor`` / ``data.num_workers`` are parsed and unused there).
+    """
+
+    def __init__(self, loader: DataLoader, depth: int = 2):
+        import queue
+        import threading
+        self.loader = loader
+        self.depth = max(1, depth)
+        self.epoch = loader.epoch
+        self._q: "queue.Queue" = queue.Queue(maxsize=self.depth)
+        self._stop = threading.Event()
+        self._thread: Optional["threading.Thread"] = None
+        self._threading, self._queue = threading, queue
+
+    # the attributes callers read from a plain loader
+    @property
+    def num_samples(self) -> int:
+        return self.loader.num_samples
+
+    def num_batches(self) -> int:
+        return self.loader.num_batches()
+
+    def skip(self, n_batches: int) -> None:
+        assert self._thread is None, "skip() must be called before the first batch is taken"
+        self.loader.skip(n_batches)
+        self.epoch = self.loader.epoch
+
+    def _work(self) -> None:
+        try:
+            while not self._stop.is_set():
+                item = (self.loader.next_cycling(), self.loader.epoch)
+                while not self._stop.is_set():
+                    try:
+                        self._q.put(item, timeout=0.1)
+                        break
+                    except self._queue.Full:
+                        continue
+        except BaseException as e:          # handed to the consumer, which re-raises it
+            self._q.put(e)
+
+    def next_cycling(self) -> Batch:
+        if self._thread is None:
+            self._thread = self._threading.Thread(target=self._work, name="elfa-data-prefetch", daemon=True)
+            self._thread.start()
+        item = self._q.get()
+        if isinstance(item, BaseException):
+            raise item
+        batch, self.epoch = item
+        return batch
+
+    def close(self) -> None:
+        self._stop.set()
+        if self._thread is not None:
+            while self._thread.is_alive():
+                try:
+                    self._q.get_nowait()
+                except self._queue.Empty:
+                    pass
+                self._thread.join(timeout=0.05)
+            self._thread = None

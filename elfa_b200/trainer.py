@@ -132,8 +132,13 @@ class Trainer:
             ds = BinaryDataset.open(path)
             shuffle = True
         # the ranks of a context-parallel group read the same batch and keep their slice of the sequence
-        return DataLoader(ds, mb, S, shuffle=shuffle, seed=cfg.runtime.seed, dp_rank=pc.dp_rank // pc.cp_size,
-                          dp_size=pc.dp_size // pc.cp_size)
+        loader = DataLoader(ds, mb, S, shuffle=shuffle, seed=cfg.runtime.seed, dp_rank=pc.dp_rank // pc.cp_size,
+                            dp_size=pc.dp_size // pc.cp_size)
+        depth = cfg.data.prefetch_factor * cfg.data.num_workers
+        if depth > 0:       # data.prefetch_factor x data.num_workers batches are assembled ahead on a worker thread
+            from .data.dataset import PrefetchLoader
+            return PrefetchLoader(loader, depth)
+        return loader
 
     # ------------------------------------------------------------------ step
     def train_step(self, batches: List[Batch]) -> torch.Tensor:
@@ -253,6 +258,8 @@ class Trainer:
                 self.save_checkpoint()
         if self.ckpt is not None:
             self.ckpt.wait()
+        if hasattr(loader, "close"):
+            loader.close()          # stops the prefetch thread
         return losses
 
     def smoke_test(self, steps: int = 3) -> List[float]:

@@ -234,3 +234,21 @@ def test_telemetry_jsonl_schema_and_prometheus(tmp_path):
     s.update(3.0, 10)
     s.update(5.0, 10)
     assert s.average_loss() == 4.0 and s.tokens == 30
+
+
+def test_prefetch_loader_keeps_order_epochs_and_resume_position():
+    from elfa_b200.data.dataset import DataLoader, PrefetchLoader, SyntheticDataset
+    ds = SyntheticDataset(1000, 16 * 10 + 1, "uniform", 0, 1.1)
+    plain = DataLoader(ds, 2, 16, shuffle=True, seed=3, pin_memory=False)
+    want = [(plain.next_cycling(), plain.epoch) for _ in range(12)]          # 5 batches per epoch: rolls over twice
+    pre = PrefetchLoader(DataLoader(ds, 2, 16, shuffle=True, seed=3, pin_memory=False), depth=3)
+    for b, ep in want:
+        got = pre.next_cycling()
+        assert torch.equal(got.input, b.input) and torch.equal(got.target, b.target) and pre.epoch == ep
+    pre.close()
+    resumed = PrefetchLoader(DataLoader(ds, 2, 16, shuffle=True, seed=3, pin_memory=False), depth=2)
+    resumed.skip(7)
+    assert resumed.epoch == 1
+    got = resumed.next_cycling()
+    assert torch.equal(got.input, want[7][0].input)
+    resumed.close()
