@@ -193,6 +193,8 @@ def main() -> int:
     host_steps = []
     for _ in range(min(total_steps, 4)):
         host_steps.append([loader.next_cycling() for _ in range(n_micro)])
+    if hasattr(loader, "close"):
+        loader.close()              # the prefetch thread is not needed once the steps are staged
     dev = trainer.device
     dev_steps = [[Batch(b.input.to(dev), b.target.to(dev)) for b in st] for st in host_steps[:2]]
 
