@@ -168,6 +168,9 @@ class GPTModel(nn.Module):
         tp = self.pc.tp_size
         if m.vocab_size % tp or m.num_heads % tp or m.intermediate_dim % tp:
             raise ValueError("vocab_size, num_heads and intermediate_dim must be divisible by the tensor-parallel size")
+        if m.num_kv_heads != m.num_heads:
+            raise ValueError(f"model.num_kv_heads ({m.num_kv_heads}) must equal model.num_heads ({m.num_heads}): the attention "
+                             "kernels have no grouped-query form")
         self.vocab_local = m.vocab_size // tp
         self.vocab_lo = self.pc.tp_rank * self.vocab_local
         D = m.hidden_dim
