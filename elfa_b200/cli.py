@@ -161,6 +161,45 @@ def cmd_tokenizer(a) -> int:
     return 0
 
 
+def cmd_dataset(a) -> int:
+    """Token files in the binary dataset format: ``synth`` (seeded random tokens, what the reference's smoke script
+    generates with an inline Python snippet), ``pack`` (one document per line or per JSONL ``text`` field, tokenised and
+    packed into rows of ``--seq-len`` with end-of-document separators), ``info`` (header and size).
+    reference: ``scripts/run_local_smoke.sh:29-52``, ``src/data_packer.zig:5-240``."""
+    import json
+    import numpy as np
+    from .data.dataset import BinaryDataset, write_token_file
+    if a.action == "synth":
+        toks = np.random.default_rng(a.seed).integers(0, a.vocab_size, size=a.tokens, dtype=np.int64)
+        write_token_file(a.output, toks)
+        print(f"{a.tokens} random tokens < {a.vocab_size} (seed {a.seed}) -> {a.output}")
+        return 0
+    if a.action == "info":
+        ds = BinaryDataset.open(a.path)
+        n = len(ds)
+        head = ds.get_tokens(0, min(n, 8)).tolist()
+        print(f"{a.path}: {n} tokens, {os.path.getsize(a.path)} bytes, first tokens {head}")
+        return 0
+    from .data.packing import StreamingPacker
+    from .data.tokenizer import Tokenizer
+    tok = Tokenizer.load(a.tokenizer)
+    packer = StreamingPacker(a.seq_len, eod_token=a.eod_token, shuffle=a.shuffle, seed=a.seed)
+    docs = 0
+    with open(a.input, "r", encoding="utf-8") as f:
+        for line in f:
+            line = line.rstrip("\n")
+            if not line:
+                continue
+            if a.jsonl:
+                line = json.loads(line).get(a.field, "")
+            packer.add_document(tok.encode(line))
+            docs += 1
+    rows = packer.finish(pad_token=a.pad_token)
+    write_token_file(a.output, rows.reshape(-1))
+    print(f"{docs} documents -> {rows.shape[0]} rows of {a.seq_len} tokens -> {a.output}")
+    return 0
+
+
 def cmd_validate(a) -> int:
     cfg = _load_cfg(a.config)
     cfg.validate()
@@ -224,6 +263,27 @@ def build_parser() -> argparse.ArgumentParser:
     cc.add_argument("--output", required=True)
     cc.add_argument("--format", default="efla_native", choices=["efla_native", "safetensors", "pytorch"])
     c.set_defaults(fn=cmd_checkpoint)
+    d = sub.add_parser("dataset", allow_abbrev=False)
+    dsub = d.add_subparsers(dest="action", required=True)
+    dsy = dsub.add_parser("synth", allow_abbrev=False)
+    dsy.add_argument("--output", required=True)
+    dsy.add_argument("--tokens", type=int, default=10000)
+    dsy.add_argument("--vocab-size", type=int, default=8192)
+    dsy.add_argument("--seed", type=int, default=42)
+    dpk = dsub.add_parser("pack", allow_abbrev=False)
+    dpk.add_argument("--input", required=True)
+    dpk.add_argument("--tokenizer", required=True)
+    dpk.add_argument("--output", required=True)
+    dpk.add_argument("--seq-len", type=int, required=True)
+    dpk.add_argument("--jsonl", action="store_true", help="every line is a JSON object; the document is its --field")
+    dpk.add_argument("--field", default="text")
+    dpk.add_argument("--eod-token", type=int, default=259, help="separator appended to every document (259 = <eos> of the BPE tokenizer)")
+    dpk.add_argument("--pad-token", type=int, default=256)
+    dpk.add_argument("--shuffle", action="store_true")
+    dpk.add_argument("--seed", type=int, default=0)
+    din = dsub.add_parser("info", allow_abbrev=False)
+    din.add_argument("path")
+    d.set_defaults(fn=cmd_dataset)
     k = sub.add_parser("tokenizer", allow_abbrev=False)
     ks = k.add_subparsers(dest="action", required=True)
     kt = ks.add_parser("train", allow_abbrev=False)

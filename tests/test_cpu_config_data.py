@@ -252,3 +252,29 @@ def test_prefetch_loader_keeps_order_epochs_and_resume_position():
     got = resumed.next_cycling()
     assert torch.equal(got.input, want[7][0].input)
     resumed.close()
+
+
+def test_dataset_cli_synth_pack_info(tmp_path, capsys):
+    from elfa_b200 import cli
+    from elfa_b200.data.dataset import BinaryDataset
+    from elfa_b200.data.tokenizer import EOS, PAD, Tokenizer
+    out = str(tmp_path / "smoke.bin")
+    assert cli.main(["dataset", "synth", "--output", out, "--tokens", "1000", "--vocab-size", "8192", "--seed", "42"]) == 0
+    ds = BinaryDataset.open(out)
+    assert len(ds) == 1000 and int(ds.get_tokens(0, 1000).max()) < 8192
+    assert cli.main(["dataset", "synth", "--output", str(tmp_path / "again.bin"), "--tokens", "1000"]) == 0
+    assert np.array_equal(BinaryDataset.open(str(tmp_path / "again.bin")).get_tokens(0, 1000), ds.get_tokens(0, 1000))   # seeded
+    tok = Tokenizer.train_from_text("the quick brown fox jumps over the lazy dog " * 20, 300)
+    tok.save(str(tmp_path / "tok.bin"))
+    docs = tmp_path / "docs.jsonl"
+    docs.write_text("\n".join(json.dumps({"text": t}) for t in ["the quick fox", "lazy dog", "brown fox jumps over"]) + "\n")
+    packed = str(tmp_path / "packed.bin")
+    assert cli.main(["dataset", "pack", "--input", str(docs), "--tokenizer", str(tmp_path / "tok.bin"), "--output", packed,
+                     "--seq-len", "8", "--jsonl"]) == 0
+    p = BinaryDataset.open(packed)
+    toks = p.get_tokens(0, len(p)).tolist()
+    assert len(p) % 8 == 0 and toks.count(EOS) == 3 and (toks[-1] == PAD or toks[-1] == EOS)
+    first_doc = toks[:toks.index(EOS)]
+    assert tok.decode(first_doc) == "the quick fox"
+    assert cli.main(["dataset", "info", packed]) == 0
+    assert f"{len(p)} tokens" in capsys.readouterr().out
