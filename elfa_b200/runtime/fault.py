@@ -38,7 +38,10 @@ class Fault:
     args: Dict[str, float] = field(default_factory=dict)
 
     def matches(self, rank: int, step: int) -> bool:
-        return int(self.args.get("rank", rank)) == rank and int(self.args.get("step", step)) == step
+        # ``attempt=k`` limits a fault to the k-th start of the job under the restarting launcher (0 = first start)
+        attempt = int(os.environ.get("ELFA_RESTART_ATTEMPT", "0"))
+        return (int(self.args.get("rank", rank)) == rank and int(self.args.get("step", step)) == step
+                and int(self.args.get("attempt", attempt)) == attempt)
 
 
 class FaultPlan:

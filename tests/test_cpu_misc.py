@@ -439,3 +439,22 @@ def test_optimizer_state_offload_between_steps(tmp_path, nvme):
     got += tr2.run(max_steps=2)
     tr2.close()
     assert got == pytest.approx(ref, abs=1e-5)
+
+
+def test_launcher_restarts_a_failed_job_from_its_newest_checkpoint(tmp_path):
+    """A rank leaves between steps on the first start (host-side fault plan); the launcher starts the job again, which
+    resumes from the last checkpoint and finishes."""
+    ck = str(tmp_path / "ck")
+    launch = [sys.executable, "-m", "elfa_b200.launch", "--gpus", "1"]
+    train = ["train", "--config", os.path.join(ROOT, "configs", "bench", "smoke_cpu.yaml"), "--checkpoint-dir", ck,
+             "--set", "checkpoint.save_interval=2,training.total_steps=6,telemetry.log_file="]
+    cmd = launch + ["--max-restarts", "1"] + train
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", ELFA_FAULT="kill_rank:step=3,attempt=0,code=17")
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-3000:]
+    assert "exit code 17: restart 1 of 1" in out and "resumed from step 2" in out and "finished at step 6" in out
+    # without restarts the same fault ends the job with the rank's exit code
+    r = subprocess.run(launch + train, capture_output=True, text=True, timeout=600, cwd=ROOT,
+                       env=dict(env, ELFA_FAULT="kill_rank:step=1,code=17"))
+    assert r.returncode == 17
