@@ -167,6 +167,10 @@ class Telemetry:
                 h.memory_healthy = free > 0.02 * total
             except RuntimeError:
                 h.gpu_healthy = False
+            from .health import probe       # temperature, throttle reasons, ECC through NVML (read-only)
+            n, _ = probe(device.index or 0)
+            h.gpu_healthy = h.gpu_healthy and n.gpu_healthy
+            h.temperature_ok = n.temperature_ok
         return h
 
     # -------------------------------------------------------------- prometheus

@@ -250,6 +250,10 @@ class Trainer:
                 extra: Dict[str, float] = {"loss_scale": self.scaler.scale}
                 if self.device.type == "cuda":
                     extra["mfu"] = thr * model_flops_per_token(cfg) / (2.25e15 * self.pc.world_size)
+                if self.step == 1 or self.step % (50 * max(cfg.telemetry.metrics_interval, 1)) == 0:
+                    h = self.telemetry.health(loss, self.device)       # finite loss, free memory, NVML temperature / throttle / ECC
+                    if self.step == 1 or not h.ok():
+                        self.telemetry.log_health_check(h)
                 self.telemetry.log_metrics(StepMetrics(self.step, self.tokens_seen, loss, self.scheduler.get_lr(),
                                                        self.optimizer.grad_norm(), thr if cfg.telemetry.track_throughput else 0.0,
                                                        used, total_mem, int(now), extra))

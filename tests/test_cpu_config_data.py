@@ -278,3 +278,55 @@ def test_dataset_cli_synth_pack_info(tmp_path, capsys):
     assert tok.decode(first_doc) == "the quick fox"
     assert cli.main(["dataset", "info", packed]) == 0
     assert f"{len(p)} tokens" in capsys.readouterr().out
+
+
+def test_health_probe_against_a_stand_in_nvml():
+    from types import SimpleNamespace
+    from elfa_b200.telemetry import health
+
+    class FakeNvml:
+        def __init__(self, temp=55, used=10, total=100, reasons=0, ecc=0, dead=False):
+            self.temp, self.used, self.total, self.reasons, self.ecc, self.dead = temp, used, total, reasons, ecc, dead
+            self.calls = []
+
+        def nvmlInit(self):
+            self.calls.append("init")
+
+        def nvmlShutdown(self):
+            self.calls.append("shutdown")
+
+        def nvmlDeviceGetHandleByIndex(self, i):
+            if self.dead:
+                raise RuntimeError("GPU is lost")
+            return i
+
+        def nvmlDeviceGetTemperature(self, dev, sensor):
+            return self.temp
+
+        def nvmlDeviceGetMemoryInfo(self, dev):
+            return SimpleNamespace(used=self.used, total=self.total)
+
+        def nvmlDeviceGetCurrentClocksEventReasons(self, dev):
+            return self.reasons
+
+        def nvmlDeviceGetTotalEccErrors(self, dev, kind, counter):
+            return self.ecc
+
+    fake = FakeNvml()
+    h, r = health.probe(0, fake)
+    assert h.ok() and r["temperature_c"] == 55 and fake.calls == ["init", "shutdown"]       # only reads, and it closes NVML
+    h, _ = health.probe(0, FakeNvml(reasons=health.SW_POWER_CAP))
+    assert h.ok()                                                                            # a power cap is not a fault
+    h, _ = health.probe(0, FakeNvml(temp=95))
+    assert not h.temperature_ok and h.gpu_healthy
+    h, _ = health.probe(0, FakeNvml(reasons=health.HW_THERMAL_SLOWDOWN))
+    assert not h.temperature_ok
+    h, _ = health.probe(0, FakeNvml(reasons=health.HW_SLOWDOWN))
+    assert not h.gpu_healthy
+    h, _ = health.probe(0, FakeNvml(ecc=2))
+    assert not h.gpu_healthy
+    h, _ = health.probe(0, FakeNvml(used=99, total=100))
+    assert not h.memory_healthy
+    h, _ = health.probe(0, FakeNvml(dead=True))
+    assert not h.gpu_healthy
+    assert health.describe(health.SW_POWER_CAP | health.HW_SLOWDOWN) == "sw_power_cap,hw_slowdown" and health.describe(0) == "none"
