@@ -22,10 +22,12 @@ HW_POWER_BRAKE = 0x80
 SW_POWER_CAP = 0x4           # normal under a dense GEMM on a power-capped part: reported, not a fault
 
 
-def probe(index: int = 0, nvml: Any = None, max_temperature_c: int = 90, min_free_fraction: float = 0.02
-          ) -> Tuple[HealthStatus, Dict[str, float]]:
-    """Health of GPU ``index``. ``nvml`` defaults to ``pynvml``; when it cannot be imported or initialised the
-    status is returned with ``gpu_healthy`` left True and an ``"nvml": 0`` reading (no information is not a fault)."""
+def probe(index: int = 0, nvml: Any = None, max_temperature_c: int = 90, min_free_fraction: float = 0.02,
+          uuid: Optional[str] = None) -> Tuple[HealthStatus, Dict[str, float]]:
+    """Health of GPU ``index`` (NVML numbering) or, when ``uuid`` is given and NVML knows it, of that GPU - CUDA's
+    device numbers follow ``CUDA_VISIBLE_DEVICES``, NVML's do not. ``nvml`` defaults to ``pynvml``; when it cannot be
+    imported or initialised the status is returned with ``gpu_healthy`` left True and an ``"nvml": 0`` reading (no
+    information is not a fault)."""
     h = HealthStatus()
     r: Dict[str, float] = {"nvml": 0}
     if nvml is None:
@@ -38,7 +40,16 @@ def probe(index: int = 0, nvml: Any = None, max_temperature_c: int = 90, min_fre
     except Exception:
         return h, r
     try:
-        dev = nvml.nvmlDeviceGetHandleByIndex(index)
+        dev = None
+        if uuid is not None and hasattr(nvml, "nvmlDeviceGetHandleByUUID"):
+            for form in (uuid, uuid.encode()):
+                try:
+                    dev = nvml.nvmlDeviceGetHandleByUUID(form)
+                    break
+                except Exception:
+                    dev = None
+        if dev is None:
+            dev = nvml.nvmlDeviceGetHandleByIndex(index)
         r["nvml"] = 1
         r["temperature_c"] = float(nvml.nvmlDeviceGetTemperature(dev, 0))          # 0 = NVML_TEMPERATURE_GPU
         mem = nvml.nvmlDeviceGetMemoryInfo(dev)

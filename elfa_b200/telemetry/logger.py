@@ -168,7 +168,11 @@ class Telemetry:
             except RuntimeError:
                 h.gpu_healthy = False
             from .health import probe       # temperature, throttle reasons, ECC through NVML (read-only)
-            n, _ = probe(device.index or 0)
+            try:
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(device).uuid).replace("GPU-", "")
+            except (AttributeError, RuntimeError):
+                uuid = None
+            n, _ = probe(device.index or 0, uuid=uuid)
             h.gpu_healthy = h.gpu_healthy and n.gpu_healthy
             h.temperature_ok = n.temperature_ok
         return h
