@@ -51,7 +51,10 @@ def probe(index: int = 0, nvml: Any = None, max_temperature_c: int = 90, min_fre
         if dev is None:
             dev = nvml.nvmlDeviceGetHandleByIndex(index)
         r["nvml"] = 1
-        r["temperature_c"] = float(nvml.nvmlDeviceGetTemperature(dev, 0))          # 0 = NVML_TEMPERATURE_GPU
+        try:
+            r["temperature_c"] = float(nvml.nvmlDeviceGetTemperature(dev, 0))      # 0 = NVML_TEMPERATURE_GPU
+        except Exception:
+            r["temperature_c"] = 0.0                                                  # this driver has no such reading: no information
         mem = nvml.nvmlDeviceGetMemoryInfo(dev)
         r["memory_used"], r["memory_total"] = float(mem.used), float(mem.total)
         try:
