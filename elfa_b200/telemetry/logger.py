@@ -183,7 +183,16 @@ class Telemetry:
         return ("# HELP efla_training_step Current training step\n# TYPE efla_training_step gauge\nefla_training_step %d\n"
                 "# HELP efla_training_loss Current training loss\n# TYPE efla_training_loss gauge\nefla_training_loss %.6f\n"
                 "# HELP efla_training_throughput Tokens per second\n# TYPE efla_training_throughput gauge\nefla_training_throughput %.2f\n"
-                % (last.step, last.loss, last.throughput))
+                % (last.step, last.loss, last.throughput)) + self._extra_gauges(last)
+
+    @staticmethod
+    def _extra_gauges(m: StepMetrics) -> str:
+        """Gauges beyond the reference's three: what a dashboard of a long run needs."""
+        rows = [("efla_training_tokens", "Tokens consumed", float(m.tokens)), ("efla_training_lr", "Learning rate", m.lr),
+                ("efla_training_grad_norm", "Global gradient norm", m.grad_norm),
+                ("efla_memory_used_bytes", "Device memory in use", float(m.memory_used))]
+        rows += [(f"efla_training_{k}", k.replace("_", " "), float(v)) for k, v in sorted(m.extra.items())]
+        return "".join(f"# HELP {n} {h}\n# TYPE {n} gauge\n{n} {v:.6g}\n" for n, h, v in rows)
 
     def _serve(self, port: int) -> None:
         import http.server

@@ -228,6 +228,8 @@ def test_telemetry_jsonl_schema_and_prometheus(tmp_path):
     assert "step=3 loss=8.2500" in open(log).read()
     prom = t.export_prometheus()
     assert "efla_training_step 3" in prom and "efla_training_loss 8.25" in prom and "efla_training_throughput 1234.50" in prom
+    assert "efla_training_lr 0.0003" in prom and "efla_training_grad_norm 1.5" in prom and "efla_training_mfu 0.5" in prom
+    assert "efla_memory_used_bytes 10" in prom and "efla_training_tokens 1536" in prom
     assert check_nan_inf([1.0, 2.0]) and not check_nan_inf(torch.tensor([1.0, float("nan")]))
     s = TrainingStats(window=2)
     s.update(1.0, 10)
