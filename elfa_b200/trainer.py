@@ -58,6 +58,9 @@ class Trainer:
             pc = (build_context(tp, cfg.runtime.sequence_parallel, cfg.runtime.comm_backend, cp, cfg.runtime.context_parallel_mode)
                   if world > 1 else ParallelContext())
         self.pc = pc
+        if pc.cp_size > 1 and cfg.mixer() != "attention":
+            raise ValueError("runtime.context_parallel_size > 1 splits softmax attention; the EFLA family splits long sequences with "
+                             "EflaModel.forward_sequence_parallel (state hand-off between ranks) instead")
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
         self.device = device
