@@ -86,8 +86,33 @@ def _load_for_inference(ckpt: str, config: Optional[str]):
 def cmd_evaluate(a) -> int:
     from .eval import Evaluator
     tr, cfg = _load_for_inference(a.checkpoint, a.config)
-    r = Evaluator(tr.model, cfg, tr.device).evaluate_perplexity(a.data, max_tokens=a.max_tokens)
-    print(f"tokens={r['tokens']} loss={r['loss']:.6f} perplexity={r['perplexity']:.4f}")
+    ev = Evaluator(tr.model, cfg, tr.device)
+    if a.data:
+        r = ev.evaluate_perplexity(a.data, max_tokens=a.max_tokens)
+        print(f"tokens={r['tokens']} loss={r['loss']:.6f} perplexity={r['perplexity']:.4f}")
+        if a.long_context:
+            from .data.dataset import BinaryDataset
+            lengths = [int(x) for x in a.long_context.split(",") if x.strip()]
+            for row in ev.evaluate_long_context(BinaryDataset.open(a.data), lengths):
+                print(f"context={row['context']} loss={row['loss']:.6f} perplexity={row['perplexity']:.4f}")
+    if a.needle or a.summary:
+        from .eval.harness import EvalHarness
+        from .eval.needle import depth_accuracy, generate_needle_case
+        from .eval.summary import generate_summary_case
+        h = EvalHarness(tr.model, tr.device)
+        length = a.haystack_len or min(cfg.data.seq_len, cfg.model.max_seq_len) // 2
+        if a.needle:
+            cases = [generate_needle_case(length, cfg.model.vocab_size, seed=i) for i in range(a.needle)]
+            r = h.needle_recall(cases)
+            print(f"needle cases={r['cases']} length={length} recall={r['recall']:.4f} precision={r['precision']:.4f}")
+            per_case = [(c.depth, h.needle_recall([c])["recall"] == 1.0) for c in cases]
+            print("needle accuracy by depth decile: " + " ".join("-" if x != x else f"{x:.2f}" for x in depth_accuracy(per_case)))
+        if a.summary:
+            cases = [generate_summary_case(length, cfg.model.vocab_size, seed=i) for i in range(a.summary)]
+            r = h.summary_rouge(cases, max_new_tokens=32)
+            print(f"summary cases={a.summary} rouge1={r['rouge1']:.4f} rouge2={r['rouge2']:.4f} rougeL={r['rougeL']:.4f}")
+    if not (a.data or a.needle or a.summary):
+        raise SystemExit("evaluate needs --data and / or --needle N / --summary N")
     return 0
 
 
@@ -237,9 +262,13 @@ def build_parser() -> argparse.ArgumentParser:
     t.set_defaults(fn=cmd_train)
     e = sub.add_parser("evaluate", allow_abbrev=False)
     e.add_argument("--checkpoint", required=True)
-    e.add_argument("--data", required=True)
+    e.add_argument("--data", help="token file: perplexity (token-weighted mean loss)")
     e.add_argument("--config")
     e.add_argument("--max-tokens", type=int)
+    e.add_argument("--long-context", metavar="N1,N2,...", help="with --data: perplexity at these context lengths")
+    e.add_argument("--needle", type=int, default=0, metavar="CASES", help="synthetic needle-in-a-haystack recall / precision")
+    e.add_argument("--summary", type=int, default=0, metavar="CASES", help="synthetic long-form summary ROUGE-1/2/L")
+    e.add_argument("--haystack-len", type=int, default=0, help="tokens per synthetic case (default: half the context)")
     e.set_defaults(fn=cmd_evaluate)
     g = sub.add_parser("generate", allow_abbrev=False)
     g.add_argument("--checkpoint", required=True)

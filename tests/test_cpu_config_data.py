@@ -332,3 +332,26 @@ def test_health_probe_against_a_stand_in_nvml():
     h, _ = health.probe(0, FakeNvml(dead=True))
     assert not h.gpu_healthy
     assert health.describe(health.SW_POWER_CAP | health.HW_SLOWDOWN) == "sw_power_cap,hw_slowdown" and health.describe(0) == "none"
+
+
+def test_cli_evaluate_perplexity_long_context_needle_summary(tmp_path, capsys):
+    """evaluate on a freshly saved checkpoint of the small GPT: perplexity, a context-length sweep and the synthetic tasks."""
+    from elfa_b200 import cli
+    from elfa_b200.config import Config
+    from elfa_b200.trainer import Trainer
+    cfg = Config.from_file(os.path.join(ROOT, "configs", "bench", "smoke_cpu.yaml"), env_override=False)
+    cfg.checkpoint.dir = str(tmp_path / "ck")
+    cfg.telemetry.log_file = ""
+    tr = Trainer(cfg, device=torch.device("cpu"), telemetry=False)
+    tr.run(max_steps=1)
+    path = tr.save_checkpoint()
+    tr.close()
+    data = str(tmp_path / "eval.bin")
+    assert cli.main(["dataset", "synth", "--output", data, "--tokens", "2000", "--vocab-size", str(cfg.model.vocab_size)]) == 0
+    capsys.readouterr()
+    rc = cli.main(["evaluate", "--checkpoint", path, "--data", data, "--max-tokens", "512", "--long-context", "32,64",
+                   "--needle", "2", "--summary", "1", "--haystack-len", "40"])
+    out = capsys.readouterr().out
+    assert rc == 0, out
+    assert "perplexity=" in out and "context=32" in out and "context=64" in out
+    assert "needle cases=2 length=40" in out and "needle accuracy by depth decile:" in out and "rouge1=" in out
