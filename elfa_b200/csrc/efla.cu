@@ -8,14 +8,15 @@
 // (reference: kernels/cuda/efla.cu:121-197 forward, :199-271 state history, :273-401 backward
 // without the beta gradient; fp32 variant kernels/cuda/efla_scan.cu:99-260 with grad_beta via
 // atomics; CPU math src/model/efla.zig:27-49,275-329,509-588).
-// Backward walks the chunks in reverse: the states inside a chunk are recomputed from the chunk's
-// saved boundary state into a global workspace ([chunk, d, d] per CTA), then the reverse-time
-// recursion runs with S and dS in shared memory (padded rows, so both column and row sweeps are
-// conflict free). beta gets its gradient; reductions are fixed-order (deterministic).
+// Backward walks the chunks in reverse with the same thread layout: the states inside a chunk are
+// recomputed from the chunk's saved boundary state into a global workspace ([chunk, d, d] per (batch,
+// head)), then the reverse-time recursion keeps the state gradient in registers and sums the key-gradient
+// rows through a per-warp shared-memory transpose. beta gets its gradient; reductions are fixed-order
+// (deterministic).
 //
 // ShortConv: y[b,t,c] = bias[c] + sum_w x[b,t-w,c] weight[c,w] (reference:
-// kernels/cuda/convolution.cu:4-57,126-189; src/model/prism.zig:948-973). The weight gradient is a
-// per-(channel, tap) reduction without atomics.
+// kernels/cuda/convolution.cu:4-57,126-189; src/model/prism.zig:948-973). The weight gradient is one
+// pass over the rows per (32 channels, 4 taps) without atomics.
 #include "common.cuh"
 #include "elfa_native.h"
 
