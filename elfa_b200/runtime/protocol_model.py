@@ -15,6 +15,7 @@ Modelled (same rules as the kernels and their host bookkeeping):
 * :class:`MailboxModel` - the two-slot neighbour mailbox of ``parallel/sp.py`` (``csrc/p2p.cu``):
   arrival counter on the receiver, acknowledgement counter on the sender, a send waits for the
   acknowledgement of the message that used the same slot two sends ago.
+* :class:`BarrierModel` - the epoch barrier on per-sender signal words (``csrc/zero.cu`` ``elfa_symm_barrier``).
 
 Every wait is bounded, as on the device: when the limit passes the rank records a timeout status and stops
 (`status` is non-zero), it never spins for ever.
@@ -135,6 +136,52 @@ class MailboxModel:
         for r in range(self.world):
             ts.append(threading.Thread(target=self._sender, args=(r, msgs)))
             ts.append(threading.Thread(target=self._receiver, args=(r, msgs)))
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+        return self.ranks
+
+
+class BarrierModel:
+    """The stream-ordered barrier of ``csrc/zero.cu`` (``elfa_symm_barrier``): rank r adds one to word ``[r]`` of every
+    peer's signal array, then waits until each word ``[p]`` of its own array has reached the barrier's epoch. The words
+    only grow (one increment per barrier and sender), so a fast rank that already signals barrier ``e + 1`` cannot be
+    mistaken for, or hide, barrier ``e``. Between barriers every rank does one epoch of "work"; the model records a violation
+    when some rank starts epoch ``e + 1``'s work before every rank has finished epoch ``e``'s."""
+
+    def __init__(self, world: int, seed: int = 0, max_delay_s: float = 2e-4, wait_limit_s: float = 5.0, absent: Optional[tuple] = None):
+        self.world = world
+        self.rng = random.Random(seed)
+        self.max_delay, self.limit = max_delay_s, wait_limit_s
+        self.absent = absent                               # (rank, epoch): that rank never signals that barrier (it left)
+        self.words = [[0] * world for _ in range(world)]   # words[receiver][sender]
+        self.lock = threading.Lock()
+        self.done = [[False] * world for _ in range(64)]   # done[epoch][rank]: work of that epoch finished
+        self.ranks = [_Rank() for _ in range(world)]
+
+    def _run_rank(self, r: int, epochs: int):
+        rng = random.Random(self.rng.random() + r)
+        me = self.ranks[r]
+        for e in range(1, epochs + 1):
+            # work of epoch e: everybody must be through barrier e - 1, i.e. have finished the work of epoch e - 1
+            if e > 1 and not all(self.done[e - 1]):
+                me.errors.append(f"rank {r} began epoch {e} while {[p for p in range(self.world) if not self.done[e - 1][p]]} were in {e - 1}")
+            time.sleep(rng.random() * self.max_delay)
+            self.done[e][r] = True
+            if self.absent == (r, e):
+                return
+            for p in range(self.world):                   # signal: one increment per peer
+                if p != r:
+                    with self.lock:
+                        self.words[p][r] += 1
+            for p in range(self.world):                   # wait: signed comparison against the epoch, bounded
+                if p != r and not _wait(lambda: self.words[r][p] - e >= 0, self.limit):
+                    me.status = TIMEOUT
+                    return
+
+    def run(self, epochs: int) -> List[_Rank]:
+        ts = [threading.Thread(target=self._run_rank, args=(r, epochs)) for r in range(self.world)]
         for t in ts:
             t.start()
         for t in ts:

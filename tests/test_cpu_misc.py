@@ -260,6 +260,11 @@ def test_flag_protocol_models_with_threads_as_ranks():
     assert any(r.status == TIMEOUT for r in ranks)           # bounded: every thread returned
     ranks = MailboxModel(4, seed=2).run(50)
     assert all(r.status == 0 and not r.errors for r in ranks), [r.errors[:2] for r in ranks]
+    from elfa_b200.runtime.protocol_model import BarrierModel
+    ranks = BarrierModel(4, seed=3).run(40)
+    assert all(r.status == 0 and not r.errors for r in ranks), [r.errors[:2] for r in ranks]
+    ranks = BarrierModel(3, seed=4, wait_limit_s=0.3, absent=(2, 5)).run(8)       # a rank leaves before barrier 5
+    assert ranks[0].status == TIMEOUT and ranks[1].status == TIMEOUT and not any(r.errors for r in ranks)
 
 
 def test_phase_timer_and_chrome_trace(tmp_path):
