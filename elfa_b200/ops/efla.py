@@ -53,6 +53,43 @@ def efla_scan_ref(k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, state: O
     return torch.stack(outs, 1), S
 
 
+def efla_scan_chunked_ref(k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, state: Optional[torch.Tensor] = None, chunk: int = 64
+                          ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The same recurrence in chunk-parallel (WY) form: everything inside a chunk of ``C`` tokens is matrix products,
+    only ``T / C`` steps remain sequential. With ``K, V [C, d]`` the chunk's keys / values, ``c`` its coefficients and
+    ``S0`` the state at its start, the pseudo-values ``u_t = c_t (v_t - S_{t-1}^T k_t)`` satisfy
+    ``(I + diag(c) tril(K K^T, -1)) U = diag(c) (V - K S0)``, so with ``Tm = (I + diag(c) tril(K K^T, -1))^{-1} diag(c)``
+    (a unit-lower-triangular solve, independent of the state and hence parallel over all chunks):
+    ``U = Tm V - (Tm K) S0``, ``O = K S0 + tril(K K^T) U``, ``S_end = S0 + K^T U``.
+    fp32, differentiable; equal to :func:`efla_scan_ref` up to rounding. It is the oracle for a tensor-core kernel of this
+    form (the CUDA kernels here are sequential in time) and a faster CPU path for long sequences."""
+    B, T, H, d = k.shape
+    C = min(chunk, T)
+    pad = (-T) % C
+    kf, vf = k.float(), v.float()
+    if pad:        # zero keys change nothing: their update and their output are zero
+        kf = torch.nn.functional.pad(kf, (0, 0, 0, 0, 0, pad))
+        vf = torch.nn.functional.pad(vf, (0, 0, 0, 0, 0, pad))
+    nc = (T + pad) // C
+    K = kf.view(B, nc, C, H, d).permute(0, 3, 1, 2, 4)                     # [B, H, nc, C, d]
+    V = vf.view(B, nc, C, H, d).permute(0, 3, 1, 2, 4)
+    c = stable_coefficient(beta.float().reshape(()), (K * K).sum(-1))      # [B, H, nc, C]
+    G = K @ K.transpose(-1, -2)                                            # [B, H, nc, C, C]
+    A = torch.eye(C, dtype=torch.float32, device=k.device) + c.unsqueeze(-1) * torch.tril(G, -1)
+    W = torch.linalg.solve_triangular(A, c.unsqueeze(-1) * torch.cat((V, K), -1), upper=False, unitriangular=True)
+    Wv, Wk = W[..., :d], W[..., d:]                                        # Tm V, Tm K
+    Gi = torch.tril(G)
+    S = torch.zeros(B, H, d, d, dtype=torch.float32, device=k.device) if state is None else state.float()
+    outs = []
+    for n in range(nc):                                                     # the only sequential part
+        Kn = K[:, :, n]
+        U = Wv[:, :, n] - Wk[:, :, n] @ S
+        outs.append(Kn @ S + Gi[:, :, n] @ U)
+        S = S + Kn.transpose(-1, -2) @ U
+    o = torch.stack(outs, 2).permute(0, 2, 3, 1, 4).reshape(B, nc * C, H, d)
+    return o[:, :T], S
+
+
 class _EflaScan(torch.autograd.Function):
     """CUDA path: sequential-in-time kernels, one warp per (batch, head, 32 value columns) with its columns
     of the fp32 state in registers; backward recomputes the states inside each chunk from the

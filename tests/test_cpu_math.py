@@ -316,3 +316,24 @@ def test_fused_collective_oracles_equal_the_unsharded_computation():
         topt.step()
         C.adamw_update(q2, gr, mq, vq, step, 1e-2, 0.9, 0.95, 1e-8, 0.1)
     assert torch.allclose(q.detach(), q2, atol=1e-6)
+
+
+@pytest.mark.parametrize("B,T,H,d,C,with_state", [(2, 50, 2, 16, 16, True), (1, 128, 2, 32, 64, False), (1, 37, 1, 8, 64, True)])
+def test_efla_chunk_parallel_form_equals_the_sequential_recurrence(B, T, H, d, C, with_state):
+    """WY / chunk-parallel restatement (triangular solve per chunk, T / C sequential steps) against the token-by-token
+    oracle: outputs, final state and every gradient (keys, values, beta, initial state)."""
+    from elfa_b200.ops.efla import efla_scan_chunked_ref, efla_scan_ref
+    torch.manual_seed(T)
+    k = (torch.randn(B, T, H, d) * 0.5).requires_grad_(True)
+    v = torch.randn(B, T, H, d).requires_grad_(True)
+    beta = torch.tensor(0.8, requires_grad=True)
+    s0 = (0.1 * torch.randn(B, H, d, d)).requires_grad_(True) if with_state else None
+    ins = [k, v, beta] + ([s0] if with_state else [])
+    o, s = efla_scan_ref(k, v, beta, s0)
+    go, gs = torch.randn_like(o), torch.randn_like(s)
+    g_ref = torch.autograd.grad([o, s], ins, [go, gs])
+    o2, s2 = efla_scan_chunked_ref(k, v, beta, s0, C)
+    g_chk = torch.autograd.grad([o2, s2], ins, [go, gs])
+    assert o2.shape == o.shape and (o - o2).abs().max() < 1e-4 and (s - s2).abs().max() < 1e-4
+    for a, b in zip(g_ref, g_chk):
+        assert (a - b).abs().max() < 1e-4 * max(1.0, a.abs().max().item())
