@@ -136,7 +136,9 @@ def efla_scan(k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, state: Optio
     if k.is_cuda and k.dtype == torch.bfloat16 and d % 32 == 0 and d <= 128:
         o, s = _EflaScan.apply(k, v, beta.reshape(1), state, chunk)
         return o, s
-    o, s = efla_scan_ref(k, v, beta, state)
+    # CPU / unsupported shapes: the chunk-parallel form for long sequences (same values up to fp32 rounding, a fraction of
+    # the Python-loop time), the token-by-token oracle otherwise
+    o, s = efla_scan_chunked_ref(k, v, beta, state, 64) if k.shape[1] > 64 else efla_scan_ref(k, v, beta, state)
     return o.to(k.dtype), s
 
 
