@@ -150,19 +150,13 @@ def compose_affine(a1: torch.Tensor, b1: torch.Tensor, a2: torch.Tensor, b2: tor
 def chunk_affine_map(k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """The affine map ``(A, B)`` of a block of tokens: ``S_end = A S_start + B`` with
     ``A = prod_t (I - c_t k_t k_t^T)`` and ``B`` the final state from a zero start. k, v ``[B, T, H, d]``.
-    Used to stitch chunks or sequence-parallel ranks together exactly."""
+    Used to stitch chunks or sequence-parallel ranks together exactly. Both come out of the scan itself:
+    ``B`` is its final state from a zero start, ``A`` its final state for zero values started from the identity
+    (then ``S_end = A I + 0``), so a block of any length costs two scans instead of a Python loop over its tokens."""
     B_, T, H, d = k.shape
-    eye = torch.eye(d, dtype=torch.float32, device=k.device).expand(B_, H, d, d)
-    A = eye.clone()
-    Bm = torch.zeros(B_, H, d, d, dtype=torch.float32, device=k.device)
-    b = beta.float().reshape(())
-    kf, vf = k.float(), v.float()
-    for t in range(T):
-        kt, vt = kf[:, t], vf[:, t]
-        c = stable_coefficient(b, (kt * kt).sum(-1))[..., None, None]
-        M = eye - c * kt[..., :, None] * kt[..., None, :]
-        A = M @ A
-        Bm = M @ Bm + c * kt[..., :, None] * vt[..., None, :]
+    eye = torch.eye(d, dtype=torch.float32, device=k.device).expand(B_, H, d, d).contiguous()
+    _, Bm = efla_scan(k, v, beta)
+    _, A = efla_scan(k, torch.zeros_like(v), beta, eye)
     return A, Bm
 
 
