@@ -465,3 +465,12 @@ def test_launcher_restarts_a_failed_job_from_its_newest_checkpoint(tmp_path):
     r = subprocess.run(launch + train, capture_output=True, text=True, timeout=600, cwd=ROOT,
                        env=dict(env, ELFA_FAULT="kill_rank:step=1,code=17"))
     assert r.returncode == 17
+
+
+def test_bench_reference_arm_reports_unavailable_as_json():
+    import json
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "1"], capture_output=True,
+                       text=True, timeout=300, cwd=ROOT, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and "unavailable" in line and len(line["unavailable"]) > 10
