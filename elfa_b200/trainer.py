@@ -36,6 +36,22 @@ def build_model(cfg: Config, pc: ParallelContext, device):
     return GPTModel(cfg, pc, device)
 
 
+def peak_flops_per_gpu() -> float:
+    """The bf16 rate the MFU figure is taken against: ``ELFA_PEAK_TFLOPS`` if set, else the sustained cuBLAS rate measured
+    on this machine (``MEASURED_PEAKS.json`` next to the package, written by whoever benchmarked the box), else the
+    1.4 PFLOP/s a power-capped B200 sustains. Not the datasheet number."""
+    env = os.environ.get("ELFA_PEAK_TFLOPS")
+    if env:
+        return float(env) * 1e12
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    try:
+        import json
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops_sustained"]) * 1e12
+    except (OSError, KeyError, ValueError):
+        return 1.4e15
+
+
 def model_flops_per_token(cfg: Config) -> float:
     """Training FLOPs per token (forward + backward = 3x forward) for the GPT family: dense GEMMs
     (2 FLOPs per weight) plus causal attention (2 * 2 * S * D / 2 per layer)."""
@@ -120,6 +136,7 @@ class Trainer:
         # phase timer + NVTX ranges (ELFA_TRACE=1); inactive it costs one branch per phase
         from .utils.tracing import PhaseTimer
         self.tracer = PhaseTimer(self.device)
+        self._peak = peak_flops_per_gpu()
 
     # ------------------------------------------------------------------ data
     def make_loader(self, data_path: Optional[str] = None) -> DataLoader:
@@ -252,7 +269,7 @@ class Trainer:
                     used = total_mem - free
                 extra: Dict[str, float] = {"loss_scale": self.scaler.scale}
                 if self.device.type == "cuda":
-                    extra["mfu"] = thr * model_flops_per_token(cfg) / (2.25e15 * self.pc.world_size)
+                    extra["mfu"] = thr * model_flops_per_token(cfg) / (self._peak * self.pc.world_size)
                 if self.step == 1 or self.step % (50 * max(cfg.telemetry.metrics_interval, 1)) == 0:
                     h = self.telemetry.health(loss, self.device)       # finite loss, free memory, NVML temperature / throttle / ECC
                     if self.step == 1 or not h.ok():
