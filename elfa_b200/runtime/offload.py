@@ -196,3 +196,40 @@ class OptimizerStateOffload:
         self.fetch()
         if self.nvme is not None:
             self.nvme.close()
+
+
+class PinnedPool:
+    """One page-locked host slab handed out as aligned tensor views by a bump pointer (``reset`` frees everything at
+    once): staging buffers for host <-> device copies without a ``cudaHostAlloc`` per tensor. On a machine without CUDA
+    the slab is ordinary host memory.
+
+    reference: ``src/memory.zig:73-106`` (``PinnedMemoryPool``: bump allocation out of one pinned buffer).
+    """
+
+    ALIGN = 256
+
+    def __init__(self, nbytes: int, pin: Optional[bool] = None):
+        self.capacity = (nbytes + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+        self.slab = torch.empty(self.capacity, dtype=torch.uint8)
+        if torch.cuda.is_available() if pin is None else pin:
+            self.slab = self.slab.pin_memory()
+        self.offset = 0
+        self.peak = 0
+
+    def alloc(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        start = (self.offset + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+        if start + nbytes > self.capacity:
+            raise MemoryError(f"pinned pool exhausted: {nbytes} bytes requested, {self.capacity - start} left of {self.capacity}")
+        self.offset = start + nbytes
+        self.peak = max(self.peak, self.offset)
+        return self.slab[start:start + nbytes].view(dtype).view(*shape)
+
+    def reset(self) -> None:
+        self.offset = 0
+
+    def bytes_free(self) -> int:
+        return self.capacity - self.offset

@@ -87,6 +87,19 @@ def test_offload_roundtrips(tmp_path):
     off.prefetch("m", out)
     off.wait("m")
     assert torch.equal(out, t)
+    from elfa_b200.runtime.offload import PinnedPool
+    pool = PinnedPool(4096, pin=False)
+    a = pool.alloc((10, 3), torch.float32)
+    b = pool.alloc((7,), torch.bfloat16)
+    assert a.shape == (10, 3) and b.dtype == torch.bfloat16 and a.data_ptr() % 256 == pool.slab.data_ptr() % 256
+    assert b.data_ptr() - a.data_ptr() == 256 and pool.bytes_free() == 4096 - 256 - 14
+    a.fill_(1.0)
+    b.fill_(2.0)
+    assert float(a.sum()) == 30.0                       # the views do not overlap
+    with pytest.raises(MemoryError):
+        pool.alloc((5000,), torch.uint8)
+    pool.reset()
+    assert pool.bytes_free() == 4096 and pool.peak == 256 + 14
     store = NvmeStore(str(tmp_path / "nvme"))
     store.write("m", off.mirrors["m"]).wait()
     back = torch.empty_like(t)
