@@ -58,7 +58,7 @@ def timed(fn, iters, warm=3, flush=True):
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "norm", "norm_bwd", "xent", "adamw", "mxfp8", "gemm_mxfp8",
-                                      "gemm_nvfp4", "gelu", "softmax", "embedding", "efla", "suite"])
+                                      "gemm_nvfp4", "gelu", "softmax", "embedding", "efla", "shortconv", "suite"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -70,6 +70,7 @@ def main(argv=None) -> int:
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--dim", type=int, default=4096)
     ap.add_argument("--vocab", type=int, default=32000)
+    ap.add_argument("--window", type=int, default=16, help="shortconv: taps per channel")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--compare", action="store_true", help="also time the PyTorch / library op")
     ap.add_argument("--bn", type=int, default=0, help="gemm: force the tile width (64 / 128 / 256, 512 = CTA pairs; 0 = automatic)")
@@ -151,6 +152,20 @@ def main(argv=None) -> int:
                 ms = timed(lambda: fn(x), a.iters)
             by = 2.0 * R * D * 2
         print(f"{a.kernel} {R}x{D}: {ms:.4f} ms  {by / ms / 1e6:.1f} GB/s  {by / ms / 1e-3 / hbm:.3f} of {src} copy bandwidth")
+    elif a.kernel == "shortconv":
+        from ..ops.efla import shortconv
+        B, T, C, W = a.batch, a.seq, a.dim, a.window
+        x = torch.randn(B, T, C, device=dev).to(bf).requires_grad_(True)
+        w = (0.1 * torch.randn(C, W, device=dev)).to(bf).requires_grad_(True)
+        b = torch.zeros(C, device=dev, dtype=bf, requires_grad=True)
+        with torch.no_grad():
+            ms = timed(lambda: shortconv(x, w, b), a.iters)
+        y = shortconv(x, w, b)
+        g = torch.randn_like(y)
+        ms_b = timed(lambda: torch.autograd.grad(y, (x, w, b), g, retain_graph=True), a.iters)
+        by = 2.0 * B * T * C * 2
+        print(f"shortconv B{B} T{T} C{C} W{W}: forward {ms:.4f} ms ({by / ms / 1e-3 / hbm:.3f} of {src} copy bandwidth), "
+              f"backward (dx + dw + db) {ms_b:.4f} ms")
     elif a.kernel == "efla":
         from ..ops.efla import efla_scan
         B, T, H, hd = a.batch, a.seq, a.heads, a.hd
