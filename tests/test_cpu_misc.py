@@ -487,3 +487,11 @@ def test_bench_reference_arm_reports_unavailable_as_json():
     assert r.returncode == 0, r.stderr[-2000:]
     line = json.loads(r.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and "unavailable" in line and len(line["unavailable"]) > 10
+    # argument checks that need no GPU: the twin is a single-process aid, N ranks need the distributed launcher
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", WORLD_SIZE="1")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--twin", "4", "--gpus", "2"], capture_output=True, text=True,
+                       timeout=300, cwd=ROOT, env=env)
+    assert r.returncode == 2 and "--twin" in r.stderr
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--gpus", "2"], capture_output=True, text=True, timeout=300,
+                       cwd=ROOT, env=env)
+    assert r.returncode == 2 and "WORLD_SIZE" in r.stderr
