@@ -98,6 +98,32 @@ def reference_arm(args) -> int:
     return 0
 
 
+def plan_run(cfg, yaml_tp: int, yaml_world: int, world: int, micro_batch: int = 0, keep_global_batch: bool = False):
+    """Chooses the parallel layout for ``world`` GPUs from the sizes the configuration FILE names (``yaml_tp``,
+    ``yaml_world``: read before any launcher variable touches them) and writes it into ``cfg``.
+    Returns (micro_batch, scaling, metric)."""
+    if yaml_tp == yaml_world:
+        # the headline configuration: tensor + sequence parallel over all N GPUs, fixed global batch (strong scaling)
+        cfg.runtime.tensor_parallel_size = world
+        cfg.runtime.zero_stage = 0
+        mb = micro_batch or 4      # 4 sequences of 4096 tokens per micro-batch: 160 GB peak on one GPU, less with tensor parallelism
+        scaling = "strong"
+        metric = METRIC if cfg.model.name.startswith("gpt-7b") else f"tokens/sec/box (max over ranks) {cfg.model.name}"
+    else:
+        # the data-parallel configurations (ZeRO stage from the file): tp = min(file's tp, N), the rest is data parallel
+        tp = min(yaml_tp, world)
+        dp = world // tp
+        cfg.runtime.tensor_parallel_size = tp
+        if dp == 1:
+            cfg.runtime.zero_stage = 0
+        mb = micro_batch or cfg.training.micro_batch_size
+        if yaml_tp == 1 and not keep_global_batch:      # fixed micro-batch per GPU: weak scaling
+            cfg.training.global_batch_size = mb * dp
+        scaling = "weak" if yaml_tp == 1 else "strong"
+        metric = f"tokens/sec/box (max over ranks) {cfg.model.name}"
+    return mb, scaling, metric
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--gpus", type=int, default=1)
@@ -136,8 +162,10 @@ def main() -> int:
     torch.cuda.set_device(local)
     native.lib.load()
 
-    cfg = Config.from_file(args.config)
+    # the file's own world / tensor-parallel sizes choose the branch; the launcher's WORLD_SIZE must not overwrite them first
+    cfg = Config.from_file(args.config, env_override=False)
     yaml_tp, yaml_world = cfg.runtime.tensor_parallel_size, cfg.runtime.world_size
+    cfg.runtime.rank = int(os.environ.get("RANK", "0"))
     real_world = world
     if args.twin:
         # the job's shapes and call sequence at N ranks, on this one GPU: collectives return at once and move nothing
@@ -155,25 +183,7 @@ def main() -> int:
         cfg.model.num_layers = args.layers
     if args.global_batch:
         cfg.training.global_batch_size = args.global_batch
-    if yaml_tp == yaml_world:
-        # the headline configuration: tensor + sequence parallel over all N GPUs, fixed global batch (strong scaling)
-        cfg.runtime.tensor_parallel_size = world
-        cfg.runtime.zero_stage = 0
-        mb = args.micro_batch or 4      # 4 sequences of 4096 tokens per micro-batch: 160 GB peak on one GPU, less with tensor parallelism
-        scaling = "strong"
-        metric = METRIC if cfg.model.name.startswith("gpt-7b") else f"tokens/sec/box (max over ranks) {cfg.model.name}"
-    else:
-        # the data-parallel configurations (ZeRO stage from the file): tp = min(file's tp, N), the rest is data parallel
-        tp = min(yaml_tp, world)
-        dp = world // tp
-        cfg.runtime.tensor_parallel_size = tp
-        if dp == 1:
-            cfg.runtime.zero_stage = 0
-        mb = args.micro_batch or cfg.training.micro_batch_size
-        if yaml_tp == 1 and not args.global_batch:      # fixed micro-batch per GPU: weak scaling
-            cfg.training.global_batch_size = mb * dp
-        scaling = "weak" if yaml_tp == 1 else "strong"
-        metric = f"tokens/sec/box (max over ranks) {cfg.model.name}"
+    mb, scaling, metric = plan_run(cfg, yaml_tp, yaml_world, world, args.micro_batch, bool(args.global_batch))
     cfg.training.micro_batch_size = mb
     dp_size = world // cfg.runtime.tensor_parallel_size
     cfg.training.gradient_accumulation_steps = max(1, cfg.training.global_batch_size // (mb * dp_size))

@@ -495,3 +495,28 @@ def test_bench_reference_arm_reports_unavailable_as_json():
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--gpus", "2"], capture_output=True, text=True, timeout=300,
                        cwd=ROOT, env=env)
     assert r.returncode == 2 and "WORLD_SIZE" in r.stderr
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_bench_takes_the_headline_branch_at_every_world_size(world, monkeypatch):
+    """The launcher's WORLD_SIZE must not change which branch of bench.py a configuration file selects."""
+    import importlib.util
+    from elfa_b200.config import Config
+    spec = importlib.util.spec_from_file_location("elfa_bench_script", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    monkeypatch.setenv("WORLD_SIZE", str(world))
+    monkeypatch.setenv("RANK", "0")
+    path = os.path.join(ROOT, "configs", "bench", "gpt7b_tp8_mxfp8.yaml")
+    cfg = Config.from_file(path, env_override=False)
+    assert (cfg.runtime.tensor_parallel_size, cfg.runtime.world_size) == (8, 8)
+    cfg.runtime.world_size = world
+    mb, scaling, metric = bench.plan_run(cfg, 8, 8, world)
+    assert mb == 4 and scaling == "strong" and metric == bench.METRIC
+    assert cfg.runtime.tensor_parallel_size == world and cfg.training.global_batch_size == 32
+    # a data-parallel file keeps its micro-batch per GPU (weak scaling)
+    cfg = Config.from_file(os.path.join(ROOT, "configs", "bench", "gpt350m_zero1.yaml"), env_override=False)
+    ytp, yw = cfg.runtime.tensor_parallel_size, cfg.runtime.world_size
+    cfg.runtime.world_size = world
+    mb, scaling, _ = bench.plan_run(cfg, ytp, yw, world)
+    assert scaling == "weak" and cfg.training.global_batch_size == mb * world and cfg.runtime.tensor_parallel_size == 1
