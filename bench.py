@@ -44,12 +44,13 @@ class ClockSampler:
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index: int, uuid: str = ""):
+        # nvidia-smi numbers GPUs by PCI order, not by CUDA_VISIBLE_DEVICES: address the device by its UUID when known
+        self.index, self.uuid, self.rows, self.proc = index, uuid, [], None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.uuid or self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                           "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -82,7 +83,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "gpu_uuid": self.uuid or None}
 
 
 def reference_arm(args) -> int:
@@ -223,7 +224,11 @@ def main() -> int:
         print(f"bench.py: device status 0x{st:x} after warm-up", file=sys.stderr)
         return 3
 
-    sampler = ClockSampler(local)
+    try:
+        uuid = "GPU-" + str(torch.cuda.get_device_properties(local).uuid)
+    except Exception:
+        uuid = ""
+    sampler = ClockSampler(local, uuid)
     sampler.start()
     # ---- device-side timing
     native.lib.raw("elfa_launch_count")(1)
@@ -269,9 +274,12 @@ def main() -> int:
         if cfg.quant.attention == "none" and cfg.quant.mlp == "none":
             dtype_note = "bf16 (fp32 master weights / moments / grad accumulation)"
         else:
+            bwd = ("input-gradient GEMMs multiply MXFP8-quantised dy and weights (block-scaled on the tensor cores where the fused "
+                   "kernels allow, gathered as e4m3 payloads under tensor parallelism), weight-gradient GEMMs bf16 on the dequantised dy"
+                   if cfg.quant.backward == "mxfp8" else "backward GEMMs bf16")
             dtype_note = (f"bf16 ({cfg.quant.attention.upper()} / {cfg.quant.mlp.upper()} QAT on the attention / MLP GEMMs: forward GEMMs multiply block-scaled "
                           "payloads on the tensor cores at N = 1; at N > 1 the column-parallel layers all-gather quantised payloads and multiply them block-scaled, "
-                          "the row-parallel GEMM->reduce-scatter kernel multiplies fake-quantised bf16 operands (the same product); backward GEMMs bf16; "
+                          f"the row-parallel GEMM->reduce-scatter kernel multiplies fake-quantised bf16 operands (the same product); {bwd}; "
                           "fp32 master weights / moments / grad accumulation)")
         parallelism = "single" if world == 1 else "+".join(
             ([f"tp{tpn}+sp"] if tpn > 1 else []) + ([f"dp{dp_size}-zero{cfg.runtime.zero_stage}"] if dp_size > 1 else []))
@@ -284,7 +292,7 @@ def main() -> int:
             "config": {"model": cfg.model.name, "layers": cfg.model.num_layers, "d_model": cfg.model.hidden_dim,
                        "heads": cfg.model.num_heads, "ffn": cfg.model.intermediate_dim, "vocab": cfg.model.vocab_size,
                        "global_batch": G, "seq_len": S, "micro_batch": mb, "parallelism": parallelism,
-                       "comm_backend": cfg.runtime.comm_backend, "quant": {"attention": cfg.quant.attention, "mlp": cfg.quant.mlp},
+                       "comm_backend": cfg.runtime.comm_backend, "quant": {"attention": cfg.quant.attention, "mlp": cfg.quant.mlp, "backward": cfg.quant.backward},
                        "l2": "per-step working set (tens of GB) exceeds the 126 MB L2; no explicit flush"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 2 * G * S * 8, "d2h_bytes_per_step": 4,
                     "ms_per_step": e2e_ms / args.steps},
@@ -306,6 +314,9 @@ def main() -> int:
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if st & 0x3 and not args.twin:
+        print(f"bench.py: device status 0x{st:x}: a bounded device-side wait timed out inside the timed region", file=sys.stderr)
+        return 4
     return 0
 
 

@@ -43,8 +43,21 @@ def _newest_header_mtime() -> float:
     return max((p.stat().st_mtime for p in headers), default=0.0)
 
 
-def _compile(nvcc: str, src: Path, obj: Path, verbose: bool) -> str:
-    cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+def source_hash() -> str:
+    """SHA-256 over the names and contents of every native source and header: the identity of the sources a library was
+    built from. It is compiled into the library (``elfa_source_hash``) and checked when the library is loaded."""
+    import hashlib
+    h = hashlib.sha256()
+    for p in sorted(q for pat in ("*.cu", "*.cpp", "*.h", "*.hpp", "*.cuh") for q in CSRC.glob(pat)):
+        h.update(p.name.encode())
+        h.update(b"\0")
+        h.update(p.read_bytes())
+        h.update(b"\0")
+    return h.hexdigest()
+
+
+def _compile(nvcc: str, src: Path, obj: Path, verbose: bool, extra=()) -> str:
+    cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
@@ -61,15 +74,22 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if not sources:
         raise RuntimeError("no native sources found")
     hdr_m = _newest_header_mtime()
+    digest = source_hash()
+    stamp = OBJ_DIR / "source_hash.txt"
+    hash_changed = not stamp.exists() or stamp.read_text().strip() != digest
     jobs = []
     for src in sources:
         obj = OBJ_DIR / (src.stem + ".o")
         stale = force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_m)
+        if src.name == "runtime.cu" and hash_changed:
+            stale = True            # carries the hash of all sources
         if stale:
             jobs.append((src, obj))
     if jobs:
+        def flags(src):
+            return (f'-DELFA_SOURCE_HASH="{digest}"',) if src.name == "runtime.cu" else ()
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
-            for log in ex.map(lambda j: _compile(nvcc, j[0], j[1], verbose), jobs):
+            for log in ex.map(lambda j: _compile(nvcc, j[0], j[1], verbose, flags(j[0])), jobs):
                 if verbose and log:
                     print(log, file=sys.stderr)
     objs = [OBJ_DIR / (s.stem + ".o") for s in sources]
@@ -78,6 +98,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    stamp.write_text(digest + "\n")
     return LIB
 
 

@@ -232,6 +232,10 @@ class QuantConfig:
     optimizer_state_bits: int = 32
     amax_history: int = 16
     block_scaled_gemm: bool = True   # mxfp8 forward GEMMs on the block-scaled tensor-core path (same values as fake-quant + bf16 GEMM)
+    # quantisation of the backward pass: "mxfp8" quantises the output gradient (1x32 blocks along its last dimension) and the
+    # weight along the output dimension, so that the input-gradient GEMMs run block-scaled and tensor-parallel layers gather
+    # e4m3 payloads of dy; the weight gradient multiplies the dequantised dy in bf16
+    backward: str = field(default="none", metadata=_enum(("none", "mxfp8")))
 
 
 @dataclass

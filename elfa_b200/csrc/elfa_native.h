@@ -20,6 +20,8 @@ extern "C" {
 
 const char* elfa_last_error(void);
 int elfa_version(void);
+// SHA-256 (hex) over the sources this library was built from; the Python side compares it with the sources it finds
+const char* elfa_source_hash(void);
 long long elfa_launch_count(int reset);
 int elfa_status(unsigned int* out);
 int elfa_device_info(int device, long long* out6);

@@ -127,6 +127,11 @@ ELFA_API const char* elfa_last_error() { return g_last_error.c_str(); }
 
 ELFA_API int elfa_version() { return 100; }
 
+#ifndef ELFA_SOURCE_HASH
+#define ELFA_SOURCE_HASH "unknown"
+#endif
+ELFA_API const char* elfa_source_hash() { return ELFA_SOURCE_HASH; }
+
 // Number of kernels this library has launched in this process (optionally reset).
 ELFA_API long long elfa_launch_count(int reset) {
   long long v = g_launches.load();

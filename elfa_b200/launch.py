@@ -1,6 +1,6 @@
 """Single-node multi-GPU launcher: one process per GPU through ``torch.distributed.run``.
 
-    python -m elfa_b200.launch --gpus 8 train --config configs/train.yaml [--resume latest]
+    python -m elfa_b200.launch --gpus 8 train --config configs/bench/gpt7b_tp8_mxfp8.yaml [--resume latest]
     python -m elfa_b200.launch --gpus 1 smoke-test
 
 Plays the role of the reference's cloud launcher (reference: ``cloud/modal/train.py:198-339`` - an
@@ -85,6 +85,11 @@ def main(argv=None) -> int:
     env.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "1")
     env.setdefault("CUDA_DEVICE_ORDER", "PCI_BUS_ID")
     env.setdefault("OMP_NUM_THREADS", "4")
+    if a.max_restarts > 0 or env.get("ELFA_FAULT") or env.get("ELFA_HEARTBEAT_DIR"):
+        # a job in which ranks may leave: no NVLink multicast bindings anywhere (NCCL's NVLS, the symmetric arena's)
+        env.setdefault("NCCL_NVLS_ENABLE", "0")
+        env.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        env["ELFA_NVLS"] = "0"
     attempt = 0
     rest = resolve_resume(a.rest)
     while True:

@@ -80,6 +80,13 @@ class _Lib:
                 raise NativeError(f"symbol {name} declared in elfa_native.h is missing from the library")
             fn.argtypes = argt
             fn.restype = ctypes.c_char_p if ret != "int" else ctypes.c_int
+        # the binary must come from the sources next to it: a stale library (sources edited, not rebuilt) is an error
+        if os.environ.get("ELFA_SKIP_HASH_CHECK", "0") != "1":
+            from .build import source_hash
+            built, here = (dll.elfa_source_hash() or b"").decode(), source_hash()
+            if built != here:
+                raise NativeError(f"native library {_LIB_PATH} was built from other sources (library {built[:12]}, sources {here[:12]}): "
+                                  "run `python -m elfa_b200.build`")
         self._dll = dll
         return dll
 

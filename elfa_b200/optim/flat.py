@@ -137,3 +137,49 @@ class FlatParams:
 
     def param_slices(self) -> Dict[str, Tuple[int, int]]:
         return {n: (o, o + p.numel()) for n, p, o in zip(self.names, self.params, self.offsets)}
+
+    # ------------------------------------------------------------------ optimizer state as logical tensors (checkpoints)
+    def logical_state(self, v: torch.Tensor, lo: int, hi: int, pc) -> Dict[str, torch.Tensor]:
+        """One optimizer-state buffer (``v`` covers the flat range ``[lo, hi)`` of this rank) as full per-parameter host
+        tensors, independent of the data- and tensor-parallel sizes. Collective over both groups: every rank must call."""
+        import torch.distributed as dist
+        from ..parallel import tp as tpl
+        v = v.detach()
+        if hi - lo != self.numel:
+            if v.is_cuda:
+                full = torch.empty(self.numel, dtype=v.dtype, device=v.device)
+                dist.all_gather_into_tensor(full, v.contiguous(), group=pc.dp_group)
+            else:
+                parts = [torch.empty_like(v) for _ in range(pc.dp_size)]
+                dist.all_gather(parts, v.contiguous(), group=pc.dp_group)
+                full = torch.cat(parts)
+        else:
+            full = v
+        out: Dict[str, torch.Tensor] = {}
+        for name, p, o in zip(self.names, self.params, self.offsets):
+            t = full[o:o + p.numel()].view(p.shape)
+            shard = getattr(p, "tp_shard", None)
+            if pc.tp_size > 1 and shard is not None:
+                parts = [torch.empty_like(t) for _ in range(pc.tp_size)]
+                dist.all_gather(parts, t.contiguous(), group=pc.tp_group)
+                t = tpl.unshard_param(parts, "vocab" if shard[0] == "vocab" else shard[0])
+            out[name] = t.cpu().clone()
+        return out
+
+    @torch.no_grad()
+    def load_logical_state(self, tensors: Dict[str, torch.Tensor], v: torch.Tensor, lo: int, hi: int, pc) -> None:
+        """Inverse of :meth:`logical_state` for this rank's layout; padding elements are set to zero."""
+        from ..parallel import tp as tpl
+        v.zero_()
+        for name, p, o in zip(self.names, self.params, self.offsets):
+            if name not in tensors:
+                raise KeyError(f"optimizer state is missing tensor '{name}'")
+            full = tensors[name]
+            shard = getattr(p, "tp_shard", None)
+            if pc.tp_size > 1 and shard is not None:
+                full = tpl.shard_param(full, shard[0], pc.tp_size, pc.tp_rank)
+            if full.numel() != p.numel():
+                raise ValueError(f"optimizer state '{name}': {full.numel()} elements, parameter has {p.numel()}")
+            a, b = max(o, lo), min(o + p.numel(), hi)
+            if a < b:
+                v[a - lo:b - lo].copy_(full.reshape(-1)[a - o:b - o].to(v.device, v.dtype))

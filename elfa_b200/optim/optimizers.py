@@ -208,31 +208,25 @@ class _Base:
         raise NotImplementedError
 
     def state_dict(self) -> Dict[str, object]:
-        """Collective when the state is sharded over the data-parallel group: every rank's shard is gathered
-        (one tensor at a time, moved to the host right away) so that the rank that writes the checkpoint
-        holds all of them, stacked ``[dp, shard]``."""
-        out: Dict[str, object] = {"step": self.step_count, "lr": self.lr, "lo": self.lo, "hi": self.hi}
-        tensors = {}
-        stacked = (self.sharded or self.presharded) and self.pc.dp_size > 1 and dist.is_initialized()
-        for k, v in self.state_tensors().items():
-            v = v.detach()
-            if stacked:
-                parts = [torch.empty_like(v) for _ in range(self.pc.dp_size)]
-                dist.all_gather(parts, v.contiguous(), group=self.pc.dp_group)
-                tensors[k] = torch.stack([p.cpu() for p in parts])
-            else:
-                tensors[k] = v.cpu()
-        out["tensors"] = tensors
-        out["stacked_over_dp"] = bool(stacked)
+        """Every state buffer as full per-parameter ("logical") host tensors: the shards are gathered over the data-parallel
+        group and the tensor-parallel slices re-assembled, so the saved state does not depend on the parallel layout and a
+        run may resume at another data- or tensor-parallel size. Collective: every rank must call."""
+        out: Dict[str, object] = {"step": self.step_count, "lr": self.lr, "format": "logical"}
+        out["tensors"] = {k: self.flat.logical_state(v, self.lo, self.hi, self.pc) for k, v in self.state_tensors().items()}
         return out
 
     def load_state_dict(self, sd) -> None:
         self.step_count = int(sd["step"])
+        if sd.get("format") != "logical":
+            # files written before the layout-independent form: flat shards, valid for the layout that wrote them only
+            for k, v in self.state_tensors().items():
+                t = sd["tensors"][k]
+                if sd.get("stacked_over_dp"):
+                    t = t[self.pc.dp_rank]
+                v.copy_(t.to(v.device))
+            return
         for k, v in self.state_tensors().items():
-            t = sd["tensors"][k]
-            if sd.get("stacked_over_dp"):
-                t = t[self.pc.dp_rank]
-            v.copy_(t.to(v.device))
+            self.flat.load_logical_state(sd["tensors"][k], v, self.lo, self.hi, self.pc)
 
 
 class AdamW(_Base):

@@ -27,7 +27,8 @@ import torch.distributed as dist
 
 from .. import ops
 from ..ops.gemm import gemm
-from ..quant.qat import QuantSpec, cached_weight_operand, cached_weight_quant, fake_quant, use_block_scaled_gemm
+from ..quant.qat import (QuantSpec, cached_weight_operand, cached_weight_operand_bwd, cached_weight_quant, cached_weight_quant_bwd, fake_quant,
+                         quantize_grad, use_block_scaled_bwd, use_block_scaled_gemm)
 from .mesh import ParallelContext
 
 
@@ -186,6 +187,11 @@ def _overlap_wgrad(pc: ParallelContext, t: torch.Tensor) -> bool:
     return os.environ.get("ELFA_OVERLAP_WGRAD", "0") not in ("0", "")
 
 
+def _quantised_gather_enabled() -> bool:
+    import os
+    return os.environ.get("ELFA_AG_MXFP8", "1") not in ("0", "")
+
+
 def _quantised_gather(x2: torch.Tensor, w: torch.Tensor, pc: ParallelContext, quant) -> bool:
     """Whether a column-parallel MXFP8 layer all-gathers quantised payloads (``fused.ag_gemm_mxfp8``) instead of
     fake-quantised bf16 rows. ``ELFA_AG_MXFP8=0`` switches it off."""
@@ -215,7 +221,7 @@ class _ColumnParallelSP(torch.autograd.Function):
             xq = fake_quant(x2, quant) if quant is not None else x2
             y, x_full, pre = ag_gemm(xq, wq, pc, b_mn=True, act=act, preact=True, defer_copy=True)   # backward waits for the copy
         ctx.save_for_backward(x_full, wq, pre)
-        ctx.pc, ctx.w_ref, ctx.shape = pc, w, (Sl, B, D)
+        ctx.pc, ctx.w_ref, ctx.shape, ctx.quant = pc, w, (Sl, B, D), quant
         return y.view(Sl * pc.tp_size, B, -1)
 
     @staticmethod
@@ -237,6 +243,11 @@ class _ColumnParallelSP(torch.autograd.Function):
                 dy2 = dpre
             else:
                 dy2 = (dy2.float() * ops.dgelu_tanh_ref(pre.float())).to(dy2.dtype)
+        if ctx.quant is not None and ctx.quant.quant_backward:
+            # quantised backward: dy in MXFP8 blocks along its last dimension, the weight along the same (contraction)
+            # dimension; the reduce-scatter kernel multiplies the dequantised values (the same product)
+            _, dy2 = quantize_grad(dy2)
+            wq = cached_weight_quant_bwd(ctx.w_ref, ctx.quant)
         if _overlap_wgrad(pc, dy2) and getattr(ctx.w_ref, "main_grad", None) is not None:
             # the two products are independent: the weight gradient runs on a second stream on the SMs that the
             # (NVLink-bound) reduce-scatter kernel leaves free
@@ -269,7 +280,7 @@ class _RowParallelSP(torch.autograd.Function):
         wq = cached_weight_quant(w, quant) if quant is not None else w
         y = gemm_rs(xq, wq, pc, b_mn=True)
         ctx.save_for_backward(xq, wq)
-        ctx.pc, ctx.w_ref, ctx.shape = pc, w, (S, B, K)
+        ctx.pc, ctx.w_ref, ctx.shape, ctx.quant = pc, w, (S, B, K), quant
         return y.view(S // pc.tp_size, B, -1)
 
     @staticmethod
@@ -280,7 +291,20 @@ class _RowParallelSP(torch.autograd.Function):
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        dx, dy_full, _ = ag_gemm(dy2, wq, pc, b_mn=False, keep=False)   # all_gather(dy) @ w^T; dy_full is consumed right below
+        q = ctx.quant
+        if q is not None and q.quant_backward:
+            from . import fused
+            if (pc.comm_backend == "fused" and use_block_scaled_bwd(dy2, ctx.w_ref, q)
+                    and fused.supported_mxfp8(dy2.shape[0], dy2.shape[1], ctx.w_ref.shape[0]) and _quantised_gather_enabled()):
+                # e4m3 payloads and scales of dy cross NVLink, the input gradient is a block-scaled product; dy_full is the
+                # bf16 form of the gathered quantised rows
+                dx, dy_full, _ = fused.ag_gemm_mxfp8(dy2, cached_weight_operand_bwd(ctx.w_ref, q), pc)
+                fused.wait_pending_copies(pc)
+            else:
+                _, dyq = quantize_grad(dy2)
+                dx, dy_full, _ = ag_gemm(dyq, cached_weight_quant_bwd(ctx.w_ref, q), pc, b_mn=False, keep=False)
+        else:
+            dx, dy_full, _ = ag_gemm(dy2, wq, pc, b_mn=False, keep=False)   # all_gather(dy) @ w^T; dy_full is consumed right below
         dw = _wgrad(ctx.w_ref, xq, dy_full, wq.dtype)
         return dx.view(S, B, K), dw, None, None
 
@@ -312,7 +336,7 @@ class _QuantLinear(torch.autograd.Function):
             else:
                 y = gemm(xq, wq, b_mn=True, out_dtype=x2.dtype)
         ctx.save_for_backward(xq, wq, pre)
-        ctx.w_ref, ctx.shape = w, x.shape
+        ctx.w_ref, ctx.shape, ctx.quant = w, x.shape, quant
         return y.view(*x.shape[:-1], w.shape[1])
 
     @staticmethod
@@ -329,7 +353,16 @@ class _QuantLinear(torch.autograd.Function):
                 dy2 = dpre
             else:
                 dy2 = (dy2.float() * ops.dgelu_tanh_ref(pre.float())).to(dy2.dtype)
-        dx = gemm(dy2, wq, out_dtype=dy2.dtype).view(ctx.shape)
+        q = ctx.quant
+        if q is not None and q.quant_backward:
+            dy_op, dy2 = quantize_grad(dy2)           # from here on dy2 holds the dequantised values
+            if dy_op is not None and use_block_scaled_bwd(dy2, ctx.w_ref, q):
+                from ..ops.gemm_mxfp8 import gemm_mxfp8
+                dx = gemm_mxfp8(dy_op, cached_weight_operand_bwd(ctx.w_ref, q)).view(ctx.shape)
+            else:
+                dx = gemm(dy2, cached_weight_quant_bwd(ctx.w_ref, q), out_dtype=dy2.dtype).view(ctx.shape)
+        else:
+            dx = gemm(dy2, wq, out_dtype=dy2.dtype).view(ctx.shape)
         dw = _wgrad(ctx.w_ref, xq, dy2, wq.dtype)
         return dx, dw, None, None
 

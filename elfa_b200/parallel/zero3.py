@@ -300,6 +300,10 @@ class Zero3Shards:
             b.ready = None
         if self.side is not None:
             torch.cuda.current_stream(self.device).wait_stream(self.side)
+        if self.arena is not None and self.dp > 1:
+            # the last reduce-scatter of this micro-batch read the peers' gradient slots: nobody may zero or refill a slot
+            # for the next micro-batch before every rank has finished that read
+            self._barrier()
 
     def fold_autograd_grads(self) -> None:
         """Called by the optimizer before the update: the ``rest`` gradient (accumulated over all
@@ -377,6 +381,35 @@ class Zero3Shards:
                 tmp[o:o + p.numel()].copy_(t.reshape(-1).to(self.device, self.dtype))
             self.flat[b.base:b.base + b.shard].copy_(tmp[self.rank * b.shard:(self.rank + 1) * b.shard])
         self._rest_valid = False
+
+    def logical_state(self, v: torch.Tensor, lo: int, hi: int, pc) -> Dict[str, torch.Tensor]:
+        """One optimizer-state buffer (laid out like the local shards) as full per-parameter host tensors (collective)."""
+        out: Dict[str, torch.Tensor] = {}
+        v = v.detach()
+        for b in self.buckets:
+            local = v[b.base:b.base + b.shard].contiguous()
+            if self.dp == 1:
+                full = local
+            elif self.cuda:
+                full = torch.empty(b.numel, dtype=v.dtype, device=v.device)
+                dist.all_gather_into_tensor(full, local, group=self.group)
+            else:
+                parts = [torch.empty_like(local) for _ in range(self.dp)]
+                dist.all_gather(parts, local, group=self.group)
+                full = torch.cat(parts)
+            for n, p, o in zip(b.names, b.params, b.offsets):
+                out[n] = full[o:o + p.numel()].view(p.shape).cpu().clone()
+        return out
+
+    @torch.no_grad()
+    def load_logical_state(self, tensors: Dict[str, torch.Tensor], v: torch.Tensor, lo: int, hi: int, pc) -> None:
+        for b in self.buckets:
+            tmp = torch.zeros(b.numel, dtype=v.dtype, device=v.device)
+            for n, p, o in zip(b.names, b.params, b.offsets):
+                if n not in tensors:
+                    raise KeyError(f"optimizer state is missing tensor '{n}'")
+                tmp[o:o + p.numel()].copy_(tensors[n].reshape(-1).to(v.device, v.dtype))
+            v[b.base:b.base + b.shard].copy_(tmp[self.rank * b.shard:(self.rank + 1) * b.shard])
 
     def memory_report(self) -> Dict[str, int]:
         esz = self.flat.element_size()

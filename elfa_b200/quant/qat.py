@@ -35,6 +35,11 @@ class QuantSpec:
     threshold: float = 1.0
     outside_slope: float = 0.1
     block_scaled_gemm: bool = True
+    backward: str = "none"        # "mxfp8": output gradients and the weights' other axis are quantised for the input-gradient GEMMs
+
+    @property
+    def quant_backward(self) -> bool:
+        return self.fmt != "none" and self.backward == "mxfp8"
 
     @property
     def enabled(self) -> bool:
@@ -43,7 +48,7 @@ class QuantSpec:
     @classmethod
     def from_config(cls, fmt: str, qcfg) -> "QuantSpec":
         return cls(fmt=fmt, bits=qcfg.weight_bits, surrogate=qcfg.surrogate,
-                   block_scaled_gemm=bool(getattr(qcfg, "block_scaled_gemm", True)))
+                   block_scaled_gemm=bool(getattr(qcfg, "block_scaled_gemm", True)), backward=getattr(qcfg, "backward", "none"))
 
 
 _amax_buf = {}
@@ -87,6 +92,46 @@ def cached_weight_operand(w: torch.Tensor, spec: "QuantSpec"):
         op, _ = quantize_mxfp8(wt, right=True)
     _weight_cache[key] = (w, op)
     return op
+
+
+def cached_weight_quant_bwd(w: torch.Tensor, spec: "QuantSpec") -> torch.Tensor:
+    """``[K, N]`` weight fake-quantised (MXFP8) with blocks along N, the contraction dimension of ``dx = dy @ w^T``."""
+    key = (id(w), "mxfp8_bwd")
+    hit = _weight_cache.get(key)
+    if hit is not None and hit[0] is w:
+        return hit[1]
+    wq = fake_quant(w.detach(), QuantSpec(fmt="mxfp8"), weight=False)
+    _weight_cache[key] = (w, wq)
+    return wq
+
+
+def cached_weight_operand_bwd(w: torch.Tensor, spec: "QuantSpec"):
+    """Right-hand MXFP8 operand of the input-gradient GEMM: the ``[K, N]`` weight as it lies in memory (rows of N
+    contiguous elements), scales along N. Same blocks as :func:`cached_weight_quant_bwd`."""
+    key = (id(w), "mxfp8_bwd_operand")
+    hit = _weight_cache.get(key)
+    if hit is not None and hit[0] is w:
+        return hit[1]
+    from ..ops.gemm_mxfp8 import quantize_mxfp8
+    wd = w.detach()
+    op, _ = quantize_mxfp8(wd if wd.is_contiguous() else wd.contiguous(), right=True)
+    _weight_cache[key] = (w, op)
+    return op
+
+
+def use_block_scaled_bwd(dy2: torch.Tensor, w: torch.Tensor, spec: Optional["QuantSpec"]) -> bool:
+    """True when ``dx = dy2 [T, N] @ w[K, N]^T`` runs on the block-scaled tensor-core path."""
+    return (spec is not None and spec.quant_backward and spec.block_scaled_gemm and dy2.is_cuda and dy2.dtype == torch.bfloat16
+            and w.dtype == torch.bfloat16 and dy2.shape[1] % 32 == 0 and w.shape[0] % 8 == 0)
+
+
+def quantize_grad(dy2: torch.Tensor):
+    """MXFP8 quantisation of an output gradient ``[T, N]`` (blocks along N). Returns ``(operand or None, dyq)``:
+    the tensor-core operand (CUDA bf16 only) and the tensor of dequantised values in ``dy2``'s dtype."""
+    if dy2.is_cuda and dy2.dtype == torch.bfloat16 and dy2.shape[1] % 32 == 0:
+        from ..ops.gemm_mxfp8 import quantize_mxfp8
+        return quantize_mxfp8(dy2 if dy2.is_contiguous() else dy2.contiguous(), dequantized=True)
+    return None, fake_quant(dy2, QuantSpec(fmt="mxfp8"), weight=False)
 
 
 def use_block_scaled_gemm(x2: torch.Tensor, w: torch.Tensor, spec: Optional["QuantSpec"]) -> bool:

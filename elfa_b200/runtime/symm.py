@@ -44,6 +44,12 @@ class SymmetricArena:
     _instances: Dict[Tuple[int, int], "SymmetricArena"] = {}
 
     def __init__(self, group, device: torch.device, nbytes: int):
+        import os
+        # Only plain peer pointers are used unless ELFA_NVLS=1 asks for the multimem kernels: without it the arena is not bound
+        # to an NVLink multicast object, so a rank that leaves (fault plan, heartbeat failure, restart loop) cannot raise
+        # NVLink faults on its peers' GPUs.
+        if os.environ.get("ELFA_NVLS", "0") != "1":
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
         self.group = group if group is not None else dist.group.WORLD
         self.device = device

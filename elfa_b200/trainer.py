@@ -224,6 +224,12 @@ class Trainer:
     def finish_step(self, loss_dev: torch.Tensor) -> float:
         """Host side of a step: reads the loss, updates the loss scale and health state."""
         loss = float(loss_dev)
+        if self.device.type == "cuda":
+            # the loss read above has synchronised the stream, so the device status word is current: a bounded wait
+            # that ran out (partly gathered / reduced data) or an id outside the vocabulary ends the run here, before the
+            # loss scale, the history or a checkpoint see this step
+            from .native import check_status
+            check_status()
         if self.pc.dp_size > 1:
             import torch.distributed as dist
             t = torch.tensor([loss], device=self.device)
@@ -373,13 +379,17 @@ class Trainer:
                     raise ValueError(f"tensor '{name}': checkpoint shape {tuple(full.shape)} != model shape {tuple(p.shape)}")
                 p.copy_(full.to(p.device, p.dtype))
         self.step, self.epoch, self.tokens_seen = meta.step, meta.epoch, meta.tokens_seen
-        same_world = opt is not None and tuple(opt.get("world", (1, 1))) == (pc.dp_size, pc.tp_size)
-        if same_world:
+        def _logical(o) -> bool:
+            inner = o.get("optimizer", {})
+            return inner.get("format") == "logical" or ("muon" in inner and inner["muon"].get("format") == "logical")
+        loadable = opt is not None and (_logical(opt) or (tuple(opt.get("world", (1, 1))) == (pc.dp_size, pc.tp_size) and pc.tp_size == 1))
+        if loadable:
+            # logical (per-parameter) state re-shards itself for this run's data- and tensor-parallel sizes
             self.optimizer.load_state_dict(opt["optimizer"])
             self.scheduler.load_state_dict(opt["scheduler"])
             self.scaler.load_state_dict(opt["scaler"])
         else:
-            # different world size or no optimizer state: moments restart from zero, master weights
+            # no optimizer state (or flat shards of another layout): moments restart from zero, master weights
             # are rebuilt from the loaded parameters, the schedule is reconstructed from the step
             self.scheduler.step_count = meta.step
             opt_obj = getattr(self.optimizer, "muon", self.optimizer)

@@ -22,7 +22,7 @@ from elfa_b200.parallel import tp as tpl  # noqa: E402
 from elfa_b200.parallel.mesh import build_context, init_distributed  # noqa: E402
 
 
-def small_cfg(dtype, tp, backend, quant="none"):
+def small_cfg(dtype, tp, backend, quant="none", quant_backward=None):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     cfg = Config.from_file(os.path.join(root, "configs", "bench", "smoke_cpu.yaml"))
     cfg.model.dtype = dtype
@@ -34,6 +34,7 @@ def small_cfg(dtype, tp, backend, quant="none"):
     cfg.runtime.tensor_parallel_size = tp
     cfg.runtime.comm_backend = backend
     cfg.quant.attention = cfg.quant.mlp = quant
+    cfg.quant.backward = quant_backward if quant_backward is not None else os.environ.get("ELFA_TEST_QUANT_BACKWARD", "none")
     cfg.checkpoint.dir = ""
     cfg.checkpoint.save_interval = 0
     cfg.telemetry.log_file = ""
@@ -256,33 +257,47 @@ def mode_hybrid(dev, backend, dtype, tp):
     dist.barrier()
 
 
-def mode_ckpt(dev, stage, ckpt_dir):
-    """Sharded optimizer state survives a checkpoint: train 2 + save + 2 more == resume + 2."""
+def mode_ckpt(dev, stage, ckpt_dir, tp=1, dtype="fp32", resume_tp=None):
+    """Sharded optimizer state survives a checkpoint: train 2 + save + 2 more == resume + 2, for data-parallel shards,
+    tensor-parallel slices, and a resume under another (tp, dp) split of the same ranks."""
     from elfa_b200.trainer import Trainer
-    pc = build_context(1, False, "nccl")
-    def make():
-        cfg = small_cfg("fp32", 1, "nccl")
-        cfg.runtime.zero_stage = stage
-        cfg.training.micro_batch_size = 2
-        cfg.training.global_batch_size = 2 * pc.dp_size
+    world = dist.get_world_size()
+    resume_tp = tp if resume_tp is None else resume_tp
+
+    def make(tp_):
+        pc = build_context(tp_, tp_ > 1, "nccl")
+        cfg = small_cfg(dtype, tp_, "nccl")
+        cfg.runtime.world_size = world
+        cfg.runtime.zero_stage = stage if pc.dp_size > 1 else 0
+        cfg.training.micro_batch_size = 2 if tp_ == tp else 2 * (world // tp) // pc.dp_size
+        cfg.training.global_batch_size = 2 * (world // tp)
         cfg.checkpoint.dir = ckpt_dir
         cfg.checkpoint.save_optimizer = True
         cfg.checkpoint.async_save = False
-        return Trainer(cfg, device=dev, pc=pc, telemetry=False)
-    tr = make()
+        return Trainer(cfg, device=dev, pc=pc, telemetry=False), pc
+    tr, pc = make(tp)
     tr.run(max_steps=2)
     path = tr.save_checkpoint()
     dist.barrier()
     paths = [path]
     dist.broadcast_object_list(paths, src=0)
     cont = tr.run(max_steps=2)
-    tr2 = make()
+    tr2, pc2 = make(resume_tp)
     tr2.resume(paths[0])
     again = tr2.run(max_steps=2)
+    tol = (1e-5 if resume_tp == tp else 2e-4) if dtype == "fp32" else 2e-2
     for a, b in zip(cont, again):
-        assert abs(a - b) < 1e-5 * max(1.0, abs(a)), f"resume diverges: {cont} vs {again}"
-    if pc.rank == 0:
-        print(f"CKPT_OK stage={stage} cont={[round(x, 5) for x in cont]} again={[round(x, 5) for x in again]}")
+        assert abs(a - b) < tol * max(1.0, abs(a)), f"resume diverges: {cont} vs {again}"
+    if resume_tp == tp:
+        # the restored state itself: moments and master weights equal the saved ones on every rank
+        sd1 = tr.optimizer.state_dict()
+        sd2 = tr2.optimizer.state_dict()
+        for k in sd1["tensors"]:
+            for n in sd1["tensors"][k]:
+                d = (sd1["tensors"][k][n].float() - sd2["tensors"][k][n].float()).abs().max().item()
+                assert d < (1e-5 if dtype == "fp32" else 2e-2), f"optimizer state {k}/{n} differs by {d} after resume"
+    if dist.get_rank() == 0:
+        print(f"CKPT_OK stage={stage} tp={tp}->{resume_tp} {dtype} cont={[round(x, 5) for x in cont]} again={[round(x, 5) for x in again]}")
     dist.barrier()
 
 
@@ -366,7 +381,8 @@ def main():
         mode_killrank(dev)
         return
     if mode == "ckpt_cpu":
-        mode_ckpt(dev, int(sys.argv[2]), sys.argv[3])
+        mode_ckpt(dev, int(sys.argv[2]), sys.argv[3], int(sys.argv[4]) if len(sys.argv) > 4 else 1,
+                  sys.argv[5] if len(sys.argv) > 5 else "fp32", int(sys.argv[6]) if len(sys.argv) > 6 else None)
         dist.destroy_process_group()
         return
     if mode in ("hybrid", "hybrid_cpu"):

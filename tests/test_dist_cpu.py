@@ -23,6 +23,14 @@ def test_tp_sp_matches_single_rank_on_cpu(world):
     assert "TP_OK" in r.stdout
 
 
+def test_tp_sp_with_quantised_backward_matches_single_rank_on_cpu():
+    """MXFP8 forward and backward quantisation (dy blocks along its last dimension, weights along the same one): the
+    tensor-parallel result equals the single-rank one because the shard boundaries are block boundaries."""
+    r = _run(2, ["tp_cpu", "nccl", "fp32"], 29618, extra_env={"ELFA_TEST_QUANT": "mxfp8", "ELFA_TEST_QUANT_BACKWARD": "mxfp8"})
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "TP_OK" in r.stdout
+
+
 @pytest.mark.parametrize("world,tp,mode", [(2, 1, "ring"), (4, 2, "ring"), (2, 1, "ulysses"), (2, 1, "zigzag")])
 def test_context_parallel_attention_and_training_on_cpu(world, tp, mode):
     r = _run(world, ["cp_cpu", "nccl", "fp32", str(tp), mode], 29660 + world + {"ring": 0, "ulysses": 10, "zigzag": 20}[mode])
@@ -47,6 +55,16 @@ def test_zero_data_parallel_matches_single_rank_on_cpu(stage):
 @pytest.mark.parametrize("stage", [1, 3])
 def test_sharded_optimizer_state_survives_checkpoint(stage, tmp_path):
     r = _run(2, ["ckpt_cpu", str(stage), str(tmp_path / "ck")], 29641 + stage)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "CKPT_OK" in r.stdout
+
+
+@pytest.mark.parametrize("world,stage,tp,dtype,resume_tp", [(2, 0, 2, "fp32", 2), (2, 0, 2, "bf16", 2), (4, 1, 2, "bf16", 2),
+                                                            (2, 1, 2, "fp32", 1), (2, 1, 1, "fp32", 2)])
+def test_optimizer_state_is_layout_independent(world, stage, tp, dtype, resume_tp, tmp_path):
+    """Tensor-parallel ranks get their own moments / master weights back, and a checkpoint written under one
+    (tp, dp) split resumes under another with its moments intact."""
+    r = _run(world, ["ckpt_cpu", str(stage), str(tmp_path / "ck"), str(tp), dtype, str(resume_tp)], 29700 + world + 3 * tp + resume_tp)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "CKPT_OK" in r.stdout
 

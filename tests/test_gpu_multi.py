@@ -56,6 +56,14 @@ def test_tp_mxfp8_quantised_all_gather_matches_single_gpu(cuda_device):
     assert "TP_OK" in r.stdout
 
 
+def test_tp_mxfp8_quantised_backward_matches_single_gpu(cuda_device):
+    """quant.backward = mxfp8 under tensor parallelism: row-parallel layers all-gather e4m3 payloads of dy, the
+    reduce-scatter kernel multiplies the dequantised dy; the losses follow the single-GPU run with the same setting."""
+    r = _run(["tp", "fused", "bf16"], 29713, extra_env={"ELFA_TEST_QUANT": "mxfp8", "ELFA_TEST_QUANT_BACKWARD": "mxfp8"})
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "TP_OK" in r.stdout
+
+
 def test_missing_peer_signal_times_out_cleanly(cuda_device):
     r = _run(["timeout"], 29704)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]

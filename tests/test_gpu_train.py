@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(device, dtype, quant="none", steps=8):
+def _run(device, dtype, quant="none", steps=8, backward="none"):
     warnings.simplefilter("ignore")
     from elfa_b200.config import Config
     from elfa_b200.trainer import Trainer
@@ -20,6 +20,7 @@ def _run(device, dtype, quant="none", steps=8):
     cfg.checkpoint.dir = ""
     cfg.telemetry.log_file = ""
     cfg.quant.attention = cfg.quant.mlp = quant
+    cfg.quant.backward = backward
     cfg.training.learning_rate = 3e-3          # large enough for the loss to move in a few steps
     tr = Trainer(cfg, device=device, telemetry=False)
     return tr, tr.run(max_steps=steps)
@@ -39,6 +40,18 @@ def test_qat_loss_curve_close_to_cpu_oracle(cuda_device, quant):
     _, cpu = _run(torch.device("cpu"), "fp32", quant, steps=4)
     _, gpu = _run(cuda_device, "bf16", quant, steps=4)
     assert native.status() == 0
+    for a, b in zip(gpu, cpu):
+        assert abs(a - b) < 0.05 * abs(b), (gpu, cpu)
+
+
+def test_mxfp8_quantised_backward_close_to_cpu_oracle(cuda_device):
+    """quant.backward = mxfp8: dy and the weights' output axis are quantised, the input-gradient GEMMs run block-scaled;
+    the CPU oracle applies the same quantisation to fp32 operands."""
+    _, cpu = _run(torch.device("cpu"), "fp32", "mxfp8", steps=4, backward="mxfp8")
+    _, plain = _run(torch.device("cpu"), "fp32", "mxfp8", steps=4)
+    _, gpu = _run(cuda_device, "bf16", "mxfp8", steps=4, backward="mxfp8")
+    assert native.status() == 0
+    assert cpu != plain                       # the backward quantisation changes the updates
     for a, b in zip(gpu, cpu):
         assert abs(a - b) < 0.05 * abs(b), (gpu, cpu)
 
