@@ -85,6 +85,45 @@ def main():
         wire = (world - 1) / world * M * (K if kind == "ag" else N) * 2
         floor_ms = max(flops / peak, wire / link) * 1e3
         rows.append((name, M, N, K, res["nccl"], res["fused"], floor_ms, coll, mm))
+        if kind == "rs" and N % 256 == 0:
+            # the same kernel with row-major receive slots (TMA tensor stores of 128-byte row segments)
+            os.environ["ELFA_RS_CHUNK_MAJOR"] = "0"
+            pc.comm_backend = "fused"
+            t_row = timed(lambda: tpl.gemm_rs(x, w, pc, b_mn=True))
+            os.environ["ELFA_RS_CHUNK_MAJOR"] = "1"
+            rows.append((name + " row-major slots", M, N, K, res["nccl"], t_row, floor_ms, coll, mm))
+        if kind == "ag" and K % 128 == 0:
+            # MXFP8 form: e4m3 payloads + scale atoms on the wire, block-scaled product. Library arm: NCCL all-gather of the
+            # quantised payload and of the scale atoms, then the block-scaled GEMM.
+            from elfa_b200.ops.gemm_mxfp8 import Mxfp8Operand, gemm_mxfp8, quantize_mxfp8, sf_numel
+            from elfa_b200.parallel import fused
+            w_op, _ = quantize_mxfp8(w.t().contiguous(), right=True)
+            Ml = M // world
+            pay = torch.empty(M, K, device=dev, dtype=torch.uint8)
+            sf = torch.empty(sf_numel(M, K), device=dev, dtype=torch.uint8)
+
+            def lib_arm():
+                op, _ = quantize_mxfp8(x)
+                dist.all_gather_into_tensor(pay, op.payload, group=pc.tp_group)
+                dist.all_gather_into_tensor(sf, op.scales, group=pc.tp_group)
+                return gemm_mxfp8(Mxfp8Operand(pay, sf, M, K, False), w_op)
+            pc.comm_backend = "fused"
+            t_lib = timed(lib_arm)
+            xa, _ = quantize_mxfp8(torch.randn(M, K, device=dev).to(torch.bfloat16))
+            mm8 = timed(lambda: gemm_mxfp8(xa, w_op))
+            coll8 = timed(lambda: dist.all_gather_into_tensor(pay, xa.payload[:Ml], group=pc.tp_group))
+            for one in (True, False):
+                fused._ONE_KERNEL = one
+
+                def fused_arm():
+                    y, _, _ = fused.ag_gemm_mxfp8(x, w_op, pc)
+                    fused.wait_pending_copies(pc)
+                    return y
+                t = timed(fused_arm)
+                wire8 = (world - 1) / world * M * K * (1 + 1 / 32)
+                fl8 = max(flops / (2 * peak), wire8 / link) * 1e3        # nominal fp8 rate = 2 x bf16
+                rows.append((name.replace("(AG->GEMM)", "mxfp8 " + ("one kernel" if one else "4 launches")), M, N, K, t_lib, t, fl8, coll8, mm8))
+            fused._ONE_KERNEL = True
     if pc.rank == 0:
         print(f"world={world} tokens={M}")
         print(f"{'op':24s} {'M':>6s} {'N':>6s} {'K':>6s} {'nccl ms':>9s} {'fused ms':>9s} {'speedup':>8s} {'floor ms':>9s} {'floor/fused':>11s} "

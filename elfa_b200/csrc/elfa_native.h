@@ -17,6 +17,7 @@ extern "C" {
 #define ELFA_EPI_ACCUM 16u        // C += result
 #define ELFA_EPI_OUT_F32 32u      // C is fp32 (default bf16)
 #define ELFA_EPI_STORE_PREACT 64u // also store the value before GELU to `preact`
+#define ELFA_EPI_STAGED 128u      // bf16 output through shared memory and TMA stores (the epilogue of the fused reduce-scatter form)
 
 const char* elfa_last_error(void);
 int elfa_version(void);
@@ -111,6 +112,9 @@ int elfa_gemm_ag(const void* x_local, long long ldx, const unsigned long long* p
                  const void* my_flags, unsigned int* arrivals_io, const void* B, void* C, int M, int N, int K, long long ldb,
                  long long ldc, int b_mn_major, void* preact, long long ldpre, unsigned flags, int rank, int world, int wait_ms,
                  void* stream);
+int elfa_gemm_ag_mxfp8(const unsigned long long* peer_buf, const unsigned long long* peer_flags, const void* my_flags,
+                       unsigned int* arrivals_io, const void* B, const void* sfb, void* C, int M, int N, int K, long long ldc,
+                       void* preact, long long ldpre, unsigned flags, int rank, int world, int wait_ms, void* stream);
 int elfa_gemm_rs(const void* A, long long lda, const void* B, long long ldb, int b_mn_major, int M, int N, int K,
                  const unsigned long long* peer_recv, const unsigned long long* peer_flags, const void* my_flags,
                  unsigned int* arrivals_io, void* out, long long ld_out, int rank, int world, int wait_ms, int max_ctas, void* stream);

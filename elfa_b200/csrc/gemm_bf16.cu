@@ -33,9 +33,11 @@
 //            bumps the owner's counter. After its tiles every CTA helps to sum the slots of the
 //            rows this rank owns, in fixed rank order (deterministic), once all counters arrived.
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
+#include "comm.cuh"
 #include "common.cuh"
 #include "elfa_native.h"
 
@@ -66,7 +68,6 @@ struct GemmParams {
 };
 
 enum { COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2 };
-constexpr int MAX_RANKS = 8;
 
 struct CommParams {
   int rank, world;
@@ -85,25 +86,13 @@ struct CommParams {
   const __nv_bfloat16* my_recv;
   __nv_bfloat16* rs_out;                   // [rows_per_rank, N]
   long long ld_out;
+  // chunk-major receive slots: every staged 128-row x 64-column chunk (16 KB, 128-byte swizzled as it lies in shared
+  // memory) travels as ONE contiguous bulk copy and lands at chunk index ((row block * tiles_n + nb) * chunks per tile + cc)
+  // of the source's slot; the reduce phase undoes the permutation. Row-major slots (TMA tensor stores, 128-byte row
+  // segments) when 0.
+  int chunk_major;
+  long long slot_chunks;                   // chunks per source slot
 };
-
-// Bounded wait until *flag >= target (wrap-safe). The counter is written by other GPUs.
-__device__ __forceinline__ bool flag_wait(const unsigned int* flag, unsigned int target, long long limit, volatile int* abort_flag,
-                                          unsigned int* status) {
-  const long long t0 = clock64();
-  for (;;) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-    if ((int)(v - target) >= 0) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > limit) {
-      *abort_flag = 1;
-      atomicOr(status, (unsigned)ELFA_ST_FLAG_TIMEOUT);
-      return false;
-    }
-    __nanosleep(100);
-  }
-}
 
 template <int BN, int STAGES>
 struct SmemLayout {
@@ -558,8 +547,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (lane == 0) {
           const uint32_t src = out0 + (g & 1) * (BM * 128);
           if (n0 + cc * ccols < p.N && !*abort_flag) {
-            if (reduce_add) tma_reduce_add_2d(&om.m[dst_map], src, n0 + cc * ccols, dst_row);
-            else tma_store_2d(&om.m[dst_map], src, n0 + cc * ccols, dst_row);
+            if (COMM == COMM_RS && cm.chunk_major) {
+              const long long chunk = ((long long)((m0 - shard * cm.rows_per_rank) / BM) * p.tiles_n + nb) * CPT + cc;
+              char* dst = reinterpret_cast<char*>(cm.peer_recv[shard]) + ((long long)cm.rank * cm.slot_chunks + chunk) * (BM * 128);
+              asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(BM * 128) : "memory");
+            } else if (reduce_add) {
+              tma_reduce_add_2d(&om.m[dst_map], src, n0 + cc * ccols, dst_row);
+            } else {
+              tma_store_2d(&om.m[dst_map], src, n0 + cc * ccols, dst_row);
+            }
           }
           tma_store_commit();
           tma_store_wait_read<0>();                     // chunk g has left shared memory
@@ -666,7 +662,35 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     __syncthreads();
     const bool ok = rs_ok != 0;
-    if (ok) {
+    if (ok && cm.chunk_major) {
+      // slots hold 16 KB chunks in shared-memory order: vector v of a slot = chunk v / 1024, row (v % 1024) / 8 of the
+      // chunk, 16-byte unit (v % 8) ^ (row % 8) of that row's 128 bytes
+      constexpr int CPT = BN / 64;
+      const long long nvec = cm.slot_chunks * 1024;
+      const long long slot = cm.slot_chunks * (BM * 64);
+      for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
+        const long long chunk = v >> 10;
+        const int within = (int)(v & 1023), rr = within >> 3, unit = (within & 7) ^ (rr & 7);
+        const int cc = (int)(chunk % CPT);
+        const long long t = chunk / CPT;
+        const int nb = (int)(t % p.tiles_n);
+        const long long row = (t / p.tiles_n) * BM + rr;
+        const int col = nb * BN + cc * 64 + unit * 8;
+        if (col >= p.N) continue;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int src = 0; src < cm.world; ++src) {
+          const uint4 q = *reinterpret_cast<const uint4*>(cm.my_recv + src * slot + v * 8);
+          const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[2 * j] += bf16_lo(qw[j]);
+            acc[2 * j + 1] += bf16_hi(qw[j]);
+          }
+        }
+        uint4 o = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+        *reinterpret_cast<uint4*>(cm.rs_out + row * cm.ld_out + col) = o;
+      }
+    } else if (ok) {
       const long long vec_per_row = p.N / 8;
       const long long nvec = (long long)cm.rows_per_rank * vec_per_row;
       const long long slot = (long long)cm.rows_per_rank * p.N;
@@ -910,6 +934,10 @@ ELFA_API int elfa_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
     rc = cached_tmap(&om.m[0], C, 4, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, BM, 32);
     if (rc != ELFA_OK) return rc;
     p.staged = 2;
+  } else if ((flags & ELFA_EPI_STAGED) && !(flags & ~(ELFA_EPI_STAGED | ELFA_EPI_BIAS | ELFA_EPI_GELU)) && N % 64 == 0) {
+    rc = cached_tmap(&om.m[0], C, 2, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, BM, 64);
+    if (rc != ELFA_OK) return rc;
+    p.staged = 1;
   }
   if (pair) return dispatch_pair(a_mn_major, b_mn_major, tmA, tmB, p, ctas, s, &om);
   switch (BN) {
@@ -953,8 +981,6 @@ int comm_grid(int M, int N, int BN, bool pair = false) {
 bool comm_pair(int M, int N, int rows_per_rank) {
   return N >= 256 && rows_per_rank % (2 * BM) == 0 && (long long)(M / (2 * BM)) * ((N + 255) / 256) >= sm_count() / 2;
 }
-
-long long wait_cycles_of(int wait_ms) { return (long long)(wait_ms > 0 ? wait_ms : 10000) * 1900000LL; }
 
 }  // namespace
 }  // namespace elfa
@@ -1057,6 +1083,13 @@ ELFA_API int elfa_gemm_rs(const void* A, long long lda, const void* B, long long
   c.my_recv = reinterpret_cast<const __nv_bfloat16*>(peer_recv[rank]);
   c.rs_out = static_cast<__nv_bfloat16*>(out);
   c.ld_out = ld_out;
+  {
+    // chunk-major slots need whole tiles along N (the slot is then exactly rows x N); ELFA_RS_CHUNK_MAJOR=0 keeps row-major slots
+    const char* e = getenv("ELFA_RS_CHUNK_MAJOR");
+    const bool want = !(e && e[0] == '0');
+    c.chunk_major = (want && N % BN == 0) ? 1 : 0;
+    c.slot_chunks = (long long)(rows / BM) * (N / BN) * (BN / 64);
+  }
   // per source rank: one bump per tile of the shard
   *arrivals_io += (unsigned)((rows / BM) * ((N + BN - 1) / BN));
   c.flag_target = *arrivals_io;

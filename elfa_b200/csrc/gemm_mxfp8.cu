@@ -34,6 +34,7 @@
 #include <mutex>
 #include <unordered_map>
 
+#include "comm.cuh"
 #include "common.cuh"
 #include "elfa_native.h"
 
@@ -44,7 +45,23 @@ constexpr int QBM = 128;       // tile rows
 constexpr int QBK = 128;       // K elements (= bytes) per stage: one 128-byte swizzle row
 constexpr int QUMMA_K = 32;    // K per instruction for 8-bit operands
 constexpr int Q_THREADS = 192;
+constexpr int Q_THREADS_AG = 256;   // + two push warps (all-gather variant)
 constexpr int SF_ATOM = 512;   // bytes of one scale atom (128 rows x 4 K-blocks)
+
+// All-gather variant (AG = true): A = all_gather_rows of the ranks' quantised rows. Every rank has quantised its rows into
+// its own gathered buffer (payload [M, K] followed by the scale atoms [M / 128][K tiles]); two extra warps per CTA push
+// those two byte ranges into the same offsets of every peer's buffer (comm.cuh: push_ranges) while the tensor cores start
+// on the own rows; tiles are visited own shard first, then in the order the pushes arrive, and the producer waits for a
+// shard's arrival counter before its first tile of that shard. All TMA loads read this GPU's own memory.
+struct QComm {
+  int rank, world, rows_per_rank;
+  long long wait_cycles;
+  unsigned long long peer_buf[MAX_RANKS];     // peers' gathered buffers (entry `rank` = this rank's own)
+  unsigned long long peer_flags[MAX_RANKS];   // peers' arrival counters, one u32 per source rank
+  const unsigned int* my_flags;
+  unsigned int flag_target;
+  PushPlan plan;
+};
 
 struct QParams {
   int M, N, K;
@@ -75,9 +92,11 @@ struct QSmem {
   static constexpr int SF_BYTES = KSF * (1 + NATOM) * SF_ATOM;
   static constexpr int SF_OFF = STAGES * (A_BYTES + B_BYTES);
   static constexpr int BAR_OFF = SF_OFF + STAGES * SF_BYTES;
-  static constexpr int NUM_BARS = 2 * STAGES + 4;
+  static constexpr int NUM_BARS = 2 * STAGES + 4 + 4;   // ring full / empty, accumulator full / empty, push buffers (all-gather variant)
   static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16;
   static constexpr int DYN = TOTAL + 1024;
+  static constexpr int PUSH_OFF = (TOTAL + 127) / 128 * 128;      // all-gather variant: 2 warps x 2 buffers of PUSH_PIECE bytes
+  static constexpr int DYN_AG = PUSH_OFF + 4 * PUSH_PIECE + 1024;
   static constexpr uint32_t STAGE_TX = A_BYTES + B_BYTES + SF_BYTES;
 };
 
@@ -91,12 +110,32 @@ __device__ __forceinline__ void q_tile_coords(const QParams& p, int tile, int& m
   nb = r / gsz;
 }
 
-template <int BN, int STAGES, bool TWO, bool FP4 = false>
-__global__ void __launch_bounds__(Q_THREADS, 1)
+// Tile order of the all-gather variant: tiles grouped by the rank whose rows they read, own rows first, then rank - 1,
+// rank - 2, ... (the order in which the pushes arrive).
+template <bool AG>
+__device__ __forceinline__ void q_tile_coords_ag(const QParams& p, const QComm& c, int tile, int tile_m, int& mb, int& nb, int& shard) {
+  if (!AG) {
+    q_tile_coords(p, tile, mb, nb);
+    shard = 0;
+    return;
+  }
+  const int tm_shard = c.rows_per_rank / tile_m;
+  const int per_shard = tm_shard * p.tiles_n;
+  const int i = tile / per_shard;
+  const int lt = tile - i * per_shard;
+  shard = (c.rank - i + c.world) % c.world;
+  mb = shard * tm_shard + lt % tm_shard;
+  nb = lt / tm_shard;
+}
+
+template <int BN, int STAGES, bool TWO, bool FP4 = false, bool AG = false>
+__global__ void __launch_bounds__(AG ? Q_THREADS_AG : Q_THREADS, 1)
 gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB, const QParams p) {
+                  const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB, const QParams p,
+                  const QComm cm) {
   using L = QSmem<BN, STAGES, TWO, FP4>;
   static_assert(!(FP4 && TWO), "the NVFP4 variant is single-CTA");
+  static_assert(!(FP4 && AG), "the all-gather variant is MXFP8 only");
   constexpr int KSF = L::KSF;
   constexpr int TILE_M = TWO ? 2 * QBM : QBM;
   extern __shared__ uint8_t smem_raw[];
@@ -141,6 +180,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       mbar_init(tfull_bar(b), 1);
       mbar_init(tempty_bar(b), TWO ? 8 : 4);
     }
+    for (int b = 0; b < 4; ++b) mbar_init(bar0 + 8u * (2 * STAGES + 4 + b), 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -167,9 +207,17 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      int ready_shard = AG ? cm.rank : -1;
       for (int tile = wid; tile < num_tiles && ok; tile += wstride) {
-        int mb, nb;
-        q_tile_coords(p, tile, mb, nb);
+        int mb, nb, shard;
+        q_tile_coords_ag<AG>(p, cm, tile, TILE_M, mb, nb, shard);
+        if (AG && shard != ready_shard) {
+          // the shard's payload and scales were written by a peer GPU: acquire its counter, then order those writes
+          // before this thread's TMA (async proxy) reads
+          if (!flag_wait(cm.my_flags + shard, cm.flag_target, cm.wait_cycles, abort_flag, p.status)) { ok = false; break; }
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          ready_shard = shard;
+        }
         const int m0 = mb * TILE_M + (int)cta_rank * QBM, n0 = nb * BN;
         const int mblk = m0 / QBM;               // row block of the A scales
         const int atom0 = n0 / 128;              // first row block of the B scales (the tensor is padded by one atom)
@@ -213,8 +261,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t it = 0, tile_iter = 0;
       bool ok = true;
       for (int tile = wid; tile < num_tiles && ok; tile += wstride, ++tile_iter) {
-        int mb, nb;
-        q_tile_coords(p, tile, mb, nb);
+        int mb, nb, shard;
+        q_tile_coords_ag<AG>(p, cm, tile, TILE_M, mb, nb, shard);
         const uint32_t sfb_shift = (uint32_t)((nb * BN) % 128) / 32;   // tile starts inside an atom: skip its first columns
         const uint32_t buf = tile_iter & 1, bph = (tile_iter >> 1) & 1;
         ok = __all_sync(0xffffffffu, mbar_wait(tempty_bar(buf), bph ^ 1, abort_flag, p.status));
@@ -264,7 +312,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;
     uint32_t tile_iter = 0;
@@ -275,8 +323,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       alpha = (aa > 0.f ? aa / (448.f * 6.f) : 1.f) * (ab > 0.f ? ab / (448.f * 6.f) : 1.f);
     }
     for (int tile = wid; tile < num_tiles; tile += wstride, ++tile_iter) {
-      int mb, nb;
-      q_tile_coords(p, tile, mb, nb);
+      int mb, nb, shard;
+      q_tile_coords_ag<AG>(p, cm, tile, TILE_M, mb, nb, shard);
       const int m0 = mb * TILE_M + (int)cta_rank * QBM, n0 = nb * BN;
       const uint32_t buf = tile_iter & 1, bph = (tile_iter >> 1) & 1;
       bool ok = mbar_wait(tfull_bar(buf), bph, abort_flag, p.status);
@@ -330,6 +378,12 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (TWO) mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0)); else mbar_arrive(tempty_bar(buf));
       }
     }
+  } else if (AG) {
+    // ------------------------------------------------------------------ push warps (6, 7)
+    const int w = warp - 6;
+    push_ranges(reinterpret_cast<const char*>(cm.peer_buf[cm.rank]), cm.peer_buf, cm.peer_flags, cm.rank, cm.world, cm.plan,
+                smem_u32(smem + L::PUSH_OFF) + w * 2 * PUSH_PIECE, bar0 + 8u * (2 * STAGES + 4 + w * 2),
+                bar0 + 8u * (2 * STAGES + 4 + w * 2 + 1), 1, w, lane, abort_flag, p.status);
   }
 
   tc_fence_before();
@@ -341,17 +395,31 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
 }
 
-template <int BN, int STAGES, bool TWO, bool FP4 = false>
+// CTAs a launch of the given shape uses (the all-gather variant's arrival counters count them)
+template <int BN, bool TWO>
+int q_grid_ctas(int M, int N) {
+  constexpr int TILE_M = TWO ? 2 * QBM : QBM;
+  const int tiles = ((M + TILE_M - 1) / TILE_M) * ((N + BN - 1) / BN);
+  const int slots = TWO ? device_sm_count() / 2 : device_sm_count();
+  return (TWO ? 2 : 1) * (tiles < slots ? tiles : slots);
+}
+
+template <int BN, int STAGES, bool TWO, bool FP4 = false, bool AG = false>
 int launch_q(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmSFA, const CUtensorMap& tmSFB, QParams p,
-             cudaStream_t stream) {
+             cudaStream_t stream, const QComm* comm = nullptr) {
   using L = QSmem<BN, STAGES, TWO, FP4>;
   constexpr int TILE_M = TWO ? 2 * QBM : QBM;
-  auto kern = gemm_mxfp8_kernel<BN, STAGES, TWO, FP4>;
+  constexpr int DYN = AG ? L::DYN_AG : L::DYN;
+  constexpr int NT = AG ? Q_THREADS_AG : Q_THREADS;
+  static_assert(DYN <= 227 * 1024, "shared memory plan exceeds the per-CTA limit");
+  auto kern = gemm_mxfp8_kernel<BN, STAGES, TWO, FP4, AG>;
   static bool configured = false;
   if (!configured) {
-    ELFA_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
+    ELFA_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN));
     configured = true;
   }
+  QComm cm{};
+  if (comm) cm = *comm;
   p.tiles_m = (p.M + TILE_M - 1) / TILE_M;
   p.tiles_n = (p.N + BN - 1) / BN;
   // rows of A that stay in L2 while the tile order sweeps over N: about 32 MB worth
@@ -363,8 +431,8 @@ int launch_q(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& 
   if (TWO) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2 * grid, 1, 1);
-    cfg.blockDim = dim3(Q_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = L::DYN;
+    cfg.blockDim = dim3(NT, 1, 1);
+    cfg.dynamicSmemBytes = DYN;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -373,9 +441,9 @@ int launch_q(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    ELFA_CUDA(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmSFA, tmSFB, p));
+    ELFA_CUDA(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmSFA, tmSFB, p, cm));
   } else {
-    kern<<<grid, Q_THREADS, L::DYN, stream>>>(tmA, tmB, tmSFA, tmSFB, p);
+    kern<<<grid, NT, DYN, stream>>>(tmA, tmB, tmSFA, tmSFB, p, cm);
   }
   ELFA_CUDA(cudaGetLastError());
   ::elfa::count_launches(1);
@@ -611,6 +679,72 @@ ELFA_API int elfa_gemm_mxfp8(const void* A, const void* sfa, const void* B, cons
   if (pair) return launch_q<192, 7, true>(tmA, tmB, tmSFA, tmSFB, p, s);
   if (BN == 192) return launch_q<192, 5, false>(tmA, tmB, tmSFA, tmSFB, p, s);
   return launch_q<128, 6, false>(tmA, tmB, tmSFA, tmSFB, p, s);
+}
+
+// C[M,N] bf16 = epilogue(all_gather_rows(A)[M,K] * B[N,K]^T) with MXFP8 operands, one kernel. M = world * rows.
+//   peer_buf   : host array of `world` device addresses of the ranks' gathered buffers (entry `rank` = this rank's own):
+//                payload [M, K] e4m3 followed by the scale atoms of a left operand ([M / 128][K / 128] x 512 bytes).
+//                This rank's rows and atoms must already be in ITS buffer (elfa_mxfp8_quantize_gemm into the slice);
+//                the kernel sends them to the same offsets of every peer's buffer while it multiplies.
+//   peer_flags / my_flags / arrivals_io : arrival counters as in elfa_gemm_ag.
+// After the call this rank's buffer holds the whole gathered operand.
+ELFA_API int elfa_gemm_ag_mxfp8(const unsigned long long* peer_buf, const unsigned long long* peer_flags, const void* my_flags,
+                                unsigned int* arrivals_io, const void* B, const void* sfb, void* C, int M, int N, int K, long long ldc,
+                                void* preact, long long ldpre, unsigned flags, int rank, int world, int wait_ms, void* stream) {
+  ELFA_REQUIRE(peer_buf && peer_flags && my_flags && arrivals_io && B && sfb && C, "gemm_ag_mxfp8: null argument");
+  ELFA_REQUIRE(world >= 2 && world <= MAX_RANKS && rank >= 0 && rank < world, "gemm_ag_mxfp8: bad rank/world");
+  ELFA_REQUIRE(M % world == 0 && (M / world) % QBM == 0, "gemm_ag_mxfp8: rows per rank must be a multiple of 128");
+  ELFA_REQUIRE(K % QBK == 0 && N % 8 == 0 && ldc % 8 == 0, "gemm_ag_mxfp8: K must be a multiple of 128, N and ldc of 8");
+  ELFA_REQUIRE(!(flags & ~(ELFA_EPI_GELU | ELFA_EPI_STORE_PREACT)), "gemm_ag_mxfp8: unsupported epilogue flag");
+  ELFA_REQUIRE(!(flags & ELFA_EPI_STORE_PREACT) || (preact && ldpre % 8 == 0), "gemm_ag_mxfp8: preact flag without pointer");
+  ELFA_REQUIRE((reinterpret_cast<uintptr_t>(sfb) & 15) == 0, "gemm_ag_mxfp8: scale tensor must be 16-byte aligned");
+  for (int i = 0; i < world; ++i) ELFA_REQUIRE((peer_buf[i] & 1023) == 0, "gemm_ag_mxfp8: gathered buffers must be 1024-byte aligned");
+  unsigned int* st = status_word();
+  ELFA_REQUIRE(st != nullptr, "gemm_ag_mxfp8: no status word");
+  const int rows = M / world;
+  const int kt = K / QBK;
+  const bool pair = N > 128 && rows % (2 * QBM) == 0 && (long long)(M / 256) * ((N + 191) / 192) >= device_sm_count() / 2;
+  const int BN = (pair || N > 128) ? 192 : 128;
+  const uint8_t* mine = reinterpret_cast<const uint8_t*>(peer_buf[rank]);
+  const uint8_t* sfa = mine + (long long)M * K;
+  CUtensorMap tmA, tmB, tmSFA, tmSFB;
+  int rc = shared_tmap(&tmA, mine, 1, (uint64_t)M, (uint64_t)K, (uint64_t)K, QBM, QBK);
+  if (rc != ELFA_OK) return rc;
+  rc = shared_tmap(&tmB, B, 1, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)(pair ? BN / 2 : BN), QBK);
+  if (rc != ELFA_OK) return rc;
+  rc = sf_tmap(&tmSFA, sfa, (uint64_t)(M / 128) * kt, 1);
+  if (rc != ELFA_OK) return rc;
+  rc = sf_tmap(&tmSFB, sfb, (uint64_t)((N + 127) / 128 + 1) * kt, (uint32_t)(BN <= 128 ? 1 : 2));
+  if (rc != ELFA_OK) return rc;
+  QParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.C = static_cast<__nv_bfloat16*>(C);
+  p.ldc = ldc;
+  p.sfa = sfa;
+  p.sfb = static_cast<const uint8_t*>(sfb);
+  p.kt = kt;
+  p.sfb_atoms = (N + 127) / 128;
+  p.preact = static_cast<__nv_bfloat16*>(preact);
+  p.ldpre = ldpre;
+  p.flags = flags;
+  p.status = st;
+  QComm c{};
+  c.rank = rank; c.world = world; c.rows_per_rank = rows;
+  c.wait_cycles = wait_cycles_of(wait_ms);
+  for (int i = 0; i < world; ++i) { c.peer_buf[i] = peer_buf[i]; c.peer_flags[i] = peer_flags[i]; }
+  c.my_flags = static_cast<const unsigned int*>(my_flags);
+  const long long pay_l = (long long)rows * K, sf_l = (long long)(rows / 128) * kt * SF_ATOM;
+  c.plan.off[0] = (long long)rank * pay_l;
+  c.plan.bytes[0] = pay_l;
+  c.plan.off[1] = (long long)M * K + (long long)rank * sf_l;
+  c.plan.bytes[1] = sf_l;
+  const int ctas = pair ? q_grid_ctas<192, true>(M, N) : (BN == 192 ? q_grid_ctas<192, false>(M, N) : q_grid_ctas<128, false>(M, N));
+  *arrivals_io += (unsigned)ctas;                  // every CTA of a source bumps the counter once
+  c.flag_target = *arrivals_io;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (pair) return launch_q<192, 6, true, false, true>(tmA, tmB, tmSFA, tmSFB, p, s, &c);
+  if (BN == 192) return launch_q<192, 4, false, false, true>(tmA, tmB, tmSFA, tmSFB, p, s, &c);
+  return launch_q<128, 5, false, false, true>(tmA, tmB, tmSFA, tmSFB, p, s, &c);
 }
 
 // ---- NVFP4 ------------------------------------------------------------------------------------------

@@ -40,7 +40,7 @@ def dgelu_tanh_ref(x: torch.Tensor) -> torch.Tensor:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: Optional[torch.Tensor] = None,
          bias: Optional[torch.Tensor] = None, aux: Optional[torch.Tensor] = None, preact: Optional[torch.Tensor] = None,
          gelu: bool = False, dgelu_aux: bool = False, add_aux: bool = False, accumulate: bool = False,
-         out_dtype: torch.dtype = torch.bfloat16, alpha: float = 1.0, force_bn: int = 0, max_ctas: int = 0) -> torch.Tensor:
+         out_dtype: torch.dtype = torch.bfloat16, alpha: float = 1.0, force_bn: int = 0, max_ctas: int = 0, staged: bool = False) -> torch.Tensor:
     """``out[M,N] = epilogue(alpha * op(a) @ op(b))`` on the tcgen05 kernel (bf16 operands).
 
     ``a`` is ``[M,K]`` (or ``[K,M]`` when ``a_mn``), ``b`` is ``[N,K]`` (or ``[K,N]`` when ``b_mn``);
@@ -93,6 +93,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         assert out.dtype == torch.bfloat16
     if preact is not None:
         flags |= EPI_STORE_PREACT
+    if staged:
+        flags |= 128            # ELFA_EPI_STAGED: shared-memory + TMA-store epilogue (what the fused reduce-scatter kernel uses)
     if aux is not None:
         assert aux.dtype == torch.bfloat16 and aux.shape == (M, N) and aux.stride(1) == 1
     lib.call("elfa_gemm_bf16", a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn), bias, aux,

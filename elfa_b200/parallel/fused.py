@@ -4,10 +4,10 @@
   ``src/distributed/tensor_parallel.zig:77-129``, ``src/distributed/sequence_parallel.zig:79-128``);
 * ``gemm_rs``  - GEMM → reduce-scatter in one kernel (``tensor_parallel.zig:154-170``,
   ``sequence_parallel.zig:184-200``);
-* ``ag_gemm_mxfp8`` - the quantise-before-send form of the all-gather for MXFP8 layers: every rank
-  quantises its rows into its ring slot (e4m3 payload + scale atoms, 1.03 bytes per element instead
-  of 2), a signal barrier, a peer-load gather of the other ranks' payloads and scales, then the
-  block-scaled tensor-core GEMM on the gathered operand.
+* ``ag_gemm_mxfp8`` - the all-gather → GEMM of MXFP8 layers: every rank quantises its rows into its
+  ring slot (e4m3 payload + scale atoms, 1.03 bytes per element instead of 2); one kernel then pushes
+  that slice into every peer's slot while its tensor cores multiply block-scaled tiles, own rows
+  first, a peer's rows as soon as that peer's arrival counter says they are there.
 
 Buffers live in the group's :class:`~elfa_b200.runtime.symm.SymmetricArena`. Each primitive owns a
 ring of two slots (gathered-A buffers / receive buffers) with one set of arrival counters per
@@ -31,6 +31,9 @@ from .mesh import ParallelContext
 
 RING = 2
 _WAIT_MS = int(os.environ.get("ELFA_FLAG_TIMEOUT_MS", "10000"))
+# MXFP8 all-gather -> GEMM as one kernel (in-kernel push of payload rows and scale atoms); "0" selects the
+# quantise / barrier / peer-load gather / GEMM sequence of separate launches
+_ONE_KERNEL = os.environ.get("ELFA_AG_MXFP8_ONE_KERNEL", "1") not in ("0", "")
 
 
 class _Slot:
@@ -189,18 +192,29 @@ def ag_gemm_mxfp8(x_local: torch.Tensor, w_op, pc: ParallelContext, *, act: Opti
     scales = buf[world * pay_l: world * (pay_l + sf_l)]
     # 1. quantise the local rows into this rank's own slot, at the place they have in the gathered operand
     lib.call("elfa_mxfp8_quantize_gemm", xl, xl.stride(0), payload[rank * Ml:], scales[rank * sf_l:], None, Ml, K, 0, stream)
-    # 2. every rank's rows are in its slot
-    st.stream_barrier(stream)
-    # 3. pull the other ranks' payloads and scale atoms (peer loads)
-    base = [int(slot.peer_data[r]) for r in range(world)]
-    src_pay = (ctypes.c_uint64 * world)(*[base[r] + r * pay_l for r in range(world)])
-    src_sf = (ctypes.c_uint64 * world)(*[base[r] + world * pay_l + r * sf_l for r in range(world)])
-    lib.call("elfa_zero3_gather", ctypes.addressof(src_pay), world, 0, pay_l, payload, stream)
-    lib.call("elfa_zero3_gather", ctypes.addressof(src_sf), world, 0, sf_l, scales, stream)
-    # 4. block-scaled GEMM on the gathered operand
-    a_op = Mxfp8Operand(payload, scales, M, K, False)
     pre = torch.empty((M, N), dtype=torch.bfloat16, device=x_local.device) if (act == "gelu" and preact) else None
-    y = gemm_mxfp8(a_op, w_op, gelu=act == "gelu", preact=pre)
+    if _ONE_KERNEL:
+        # 2. one kernel: push warps send this rank's payload rows and scale atoms to every peer's slot while the tensor
+        #    cores start on the own rows; tiles of a peer's rows wait for that peer's arrival counter
+        y = torch.empty((M, N), dtype=torch.bfloat16, device=x_local.device)
+        flags = 0
+        if act == "gelu":
+            flags |= EPI_GELU | (EPI_STORE_PREACT if pre is not None else 0)
+        lib.call("elfa_gemm_ag_mxfp8", ctypes.addressof(slot.peer_data), ctypes.addressof(slot.peer_flags), slot.flags.tensor,
+                 ctypes.addressof(slot.arrivals), w_op.payload, w_op.scales, y, M, N, K, y.stride(0), pre,
+                 pre.stride(0) if pre is not None else 0, flags, rank, world, _WAIT_MS, stream)
+    else:
+        # 2. every rank's rows are in its slot
+        st.stream_barrier(stream)
+        # 3. pull the other ranks' payloads and scale atoms (peer loads)
+        base = [int(slot.peer_data[r]) for r in range(world)]
+        src_pay = (ctypes.c_uint64 * world)(*[base[r] + r * pay_l for r in range(world)])
+        src_sf = (ctypes.c_uint64 * world)(*[base[r] + world * pay_l + r * sf_l for r in range(world)])
+        lib.call("elfa_zero3_gather", ctypes.addressof(src_pay), world, 0, pay_l, payload, stream)
+        lib.call("elfa_zero3_gather", ctypes.addressof(src_sf), world, 0, sf_l, scales, stream)
+        # 4. block-scaled GEMM on the gathered operand
+        a_op = Mxfp8Operand(payload, scales, M, K, False)
+        y = gemm_mxfp8(a_op, w_op, gelu=act == "gelu", preact=pre)
     # 5. bf16 copy of the gathered rows for the weight gradient, out of the ring on the side stream
     if st.side is None:
         st.side = torch.cuda.Stream(x_local.device)

@@ -83,7 +83,7 @@ def mode_fused(pc, dev):
     from elfa_b200.parallel import fused
     pc.comm_backend = "fused"
     for it, (Ml, K, N) in enumerate([(128, 256, 512), (256, 512, 1376), (512, 4096, 1536), (128, 256, 512), (1024, 1024, 2048),
-                                     (256, 512, 1376)]):
+                                     (256, 512, 1376), (2048, 4096, 1536), (128, 128, 64)]):   # CTA pairs with several tiles each; one narrow tile
         g = torch.Generator(device="cpu").manual_seed(300 + it)
         x_all = torch.randn(Ml * world, K, generator=g).to(torch.bfloat16).to(dev)
         w = (torch.randn(K, N, generator=g) * 0.05).to(torch.bfloat16).to(dev)
