@@ -99,6 +99,77 @@ def reference_arm(args) -> int:
     return 0
 
 
+# Loss of the very first step (random-init weights, seeded data, no update yet) measured on one GPU; a run at any N must
+# reproduce it: the initial weights and the data do not depend on the parallel layout.
+FIRST_STEP_LOSS = {}
+
+
+def self_check(pc, cfg, mb: int, dev) -> dict:
+    """Correctness of the fused compute + collective kernels on this job's own ranks and per-rank shapes, outside the timed
+    region: each kernel against the library path (NCCL collective + the plain GEMM kernels) on the same inputs. The bound is
+    relative: 2^-8 of the largest reference magnitude (one bf16 rounding of the output plus summation-order effects)."""
+    import torch
+    import torch.distributed as dist
+    from elfa_b200.ops.gemm import gemm
+    from elfa_b200.ops.gemm_mxfp8 import Mxfp8Operand, gemm_mxfp8, quantize_mxfp8, sf_numel
+    from elfa_b200.parallel import fused
+    from elfa_b200.parallel import tp as tpl
+    world, rank = pc.tp_size, pc.tp_rank
+    D, F = cfg.model.hidden_dim, cfg.model.intermediate_dim
+    M = mb * cfg.data.seq_len
+    Ml = M // world
+    g = torch.Generator(device="cpu").manual_seed(4242 + rank)
+    res = {}
+
+    def rel(a, b):
+        return float((a.float() - b.float()).abs().max()), float(b.float().abs().max()) * 2.0 ** -8
+
+    # all-gather -> GEMM (bf16), MLP-up shape
+    x = torch.randn(Ml, D, generator=g).to(torch.bfloat16).to(dev)
+    w = (torch.randn(D, F // world, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+    saved = pc.comm_backend
+    pc.comm_backend = "fused"
+    y, xf, _ = tpl.ag_gemm(x, w, pc, b_mn=True)
+    pc.comm_backend = "nccl"
+    y0, xf0, _ = tpl.ag_gemm(x, w, pc, b_mn=True)
+    e, b = rel(y, y0)
+    res["ag_gemm"] = {"max_err": e, "bound": b, "gathered_equal": bool(torch.equal(xf, xf0)), "ok": e <= b and bool(torch.equal(xf, xf0))}
+    # all-gather -> GEMM (MXFP8, one kernel) against quantise + NCCL all-gather + block-scaled GEMM
+    if fused.supported_mxfp8(Ml, D, F // world):
+        w_op, _ = quantize_mxfp8(w.t().contiguous(), right=True)
+        pc.comm_backend = "fused"
+        y, xq_full, _ = fused.ag_gemm_mxfp8(x, w_op, pc)
+        fused.wait_pending_copies(pc)
+        op, xq = quantize_mxfp8(x, dequantized=True)
+        pay = torch.empty(M, D, device=dev, dtype=torch.uint8)
+        sf = torch.empty(sf_numel(M, D), device=dev, dtype=torch.uint8)
+        dist.all_gather_into_tensor(pay, op.payload, group=pc.tp_group)
+        dist.all_gather_into_tensor(sf, op.scales, group=pc.tp_group)
+        y0 = gemm_mxfp8(Mxfp8Operand(pay, sf, M, D, False), w_op)
+        e, b = rel(y, y0)
+        own = bool(torch.equal(xq_full[rank * Ml:(rank + 1) * Ml], xq))
+        res["ag_gemm_mxfp8"] = {"max_err": e, "bound": b, "own_rows_equal": own, "ok": e <= b and own}
+    # GEMM -> reduce-scatter, MLP-down shape, against an fp32 sum of the ranks' bf16-input products
+    a = torch.randn(M, F // world, generator=g).to(torch.bfloat16).to(dev)
+    w2 = (torch.randn(F // world, D, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+    pc.comm_backend = "fused"
+    o = tpl.gemm_rs(a, w2, pc, b_mn=True)
+    part = torch.empty(M, D, device=dev, dtype=torch.float32)
+    gemm(a, w2, b_mn=True, out=part)
+    dist.all_reduce(part, group=pc.tp_group)
+    ref = part[rank * Ml:(rank + 1) * Ml]
+    e, b = rel(o, ref)
+    b *= 2.0      # the partial products travel as bf16: one more rounding per rank
+    res["gemm_rs"] = {"max_err": e, "bound": b, "ok": e <= b}
+    pc.comm_backend = saved
+    ok = torch.tensor([1.0 if all(v["ok"] for v in res.values()) else 0.0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    res["ok"] = bool(ok.item() > 0)
+    res["what"] = "fused kernels vs library path on this job's per-rank shapes, every rank, bound = 2^-8 * max|reference|"
+    torch.cuda.synchronize()
+    return res
+
+
 def plan_run(cfg, yaml_tp: int, yaml_world: int, world: int, micro_batch: int = 0, keep_global_batch: bool = False):
     """Chooses the parallel layout for ``world`` GPUs from the sizes the configuration FILE names (``yaml_tp``,
     ``yaml_world``: read before any launcher variable touches them) and writes it into ``cfg``.
@@ -130,7 +201,9 @@ def main() -> int:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "baseline"],
+                    help="ours: this framework; reference: the unmodified reference (unavailable: it does not build); baseline: the "
+                         "same model in eager PyTorch with torch.matmul / SDPA / NCCL (baseline/torch_nccl.py), none of this framework's kernels")
     ap.add_argument("--config", default=os.path.join(ROOT, "configs", "bench", "gpt7b_tp8_mxfp8.yaml"))
     ap.add_argument("--micro-batch", type=int, default=0, help="sequences per micro-batch (0 = auto)")
     ap.add_argument("--comm", default=None, choices=[None, "fused", "nccl"])
@@ -161,7 +234,9 @@ def main() -> int:
         return 2
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
-    native.lib.load()
+    baseline = args.impl == "baseline"
+    if not baseline:
+        native.lib.load()
 
     # the file's own world / tensor-parallel sizes choose the branch; the launcher's WORLD_SIZE must not overwrite them first
     cfg = Config.from_file(args.config, env_override=False)
@@ -192,14 +267,23 @@ def main() -> int:
     if args.twin:
         from elfa_b200.parallel.mesh import build_context
         pc = build_context(cfg.runtime.tensor_parallel_size, cfg.runtime.sequence_parallel, "nccl")
-    trainer = Trainer(cfg, telemetry=False, pc=pc)
-    rank = trainer.pc.rank
+    if baseline:
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        from torch_nccl import BaselineTrainer
+        from elfa_b200.parallel.mesh import init_distributed
+        init_distributed()
+        cfg.validate()
+        trainer = BaselineTrainer(cfg, torch.device("cuda", local))
+        rank = trainer.rank
+    else:
+        trainer = Trainer(cfg, telemetry=False, pc=pc)
+        rank = trainer.pc.rank
     S, G = cfg.data.seq_len, cfg.training.global_batch_size
     n_micro = cfg.training.gradient_accumulation_steps
     tokens_per_step = G * S
 
     # synthetic Zipf tokens, one global batch per step, staged in pinned host memory
-    loader = trainer.make_loader("")
+    loader = trainer.make_loader() if baseline else trainer.make_loader("")
     total_steps = args.warmup + 2 * args.steps
     host_steps = []
     for _ in range(min(total_steps, 4)):
@@ -214,10 +298,16 @@ def main() -> int:
             dist.barrier()
         torch.cuda.synchronize()
 
+    first_loss = None
     for i in range(args.warmup):
-        trainer.finish_step(trainer.train_step(host_steps[i % len(host_steps)]))
+        l = trainer.finish_step(trainer.train_step(host_steps[i % len(host_steps)]))
+        if first_loss is None:
+            first_loss = l          # before any update: depends on the initial weights and the data only, not on N
     sync_all()
-    st = native.status()
+    check = None
+    if not baseline and real_world > 1 and not args.twin and cfg.runtime.tensor_parallel_size > 1 and trainer.pc.comm_backend == "fused":
+        check = self_check(trainer.pc, cfg, mb, dev)
+    st = 0 if baseline else native.status()
     if args.twin:
         st &= ~0x8      # the twin's gathered / reduced buffers hold garbage: the optimizer's non-finite flag means nothing there
     if st:
@@ -231,7 +321,8 @@ def main() -> int:
     sampler = ClockSampler(local, uuid)
     sampler.start()
     # ---- device-side timing
-    native.lib.raw("elfa_launch_count")(1)
+    if not baseline:
+        native.lib.raw("elfa_launch_count")(1)
     sync_all()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -240,7 +331,7 @@ def main() -> int:
         last = trainer.train_step(dev_steps[i % len(dev_steps)])
     e1.record()
     sync_all()
-    launches = int(native.lib.raw("elfa_launch_count")(0))
+    launches = 0 if baseline else int(native.lib.raw("elfa_launch_count")(0))
     dev_ms = e0.elapsed_time(e1)
     # ---- end-to-end timing (pinned host inputs, loss read back every step)
     sync_all()
@@ -258,7 +349,7 @@ def main() -> int:
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dev_ms, e2e_ms = float(t[0]), float(t[1])
-    st = native.status()
+    st = 0 if baseline else native.status()
     if rank == 0:
         ms_step = dev_ms / args.steps
         value = tokens_per_step / (ms_step / 1e3)
@@ -301,9 +392,20 @@ def main() -> int:
             # the FLOP model covers the GPT family (dense GEMMs + softmax attention) only
             "mfu_of_measured_sustained_bf16": value * flops / (peak * world) if cfg.mixer() == "attention" else None,
             "model_tflops_per_gpu": value * flops / world / 1e12 if cfg.mixer() == "attention" else None,
-            "loss": loss, "device_status": st,
+            "loss": loss, "loss_first_step": first_loss, "device_status": st,
             "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
         }
+        if baseline:
+            out["impl"] = "baseline"
+            out["gpu_launches"] = 0
+            out["baseline_note"] = ("eager PyTorch restatement (torch.matmul, scaled_dot_product_attention, torch.nn.functional, fused "
+                                    "torch AdamW, NCCL collectives); none of this framework's kernels run")
+            out["config"]["comm_backend"] = "nccl (library)"
+        if check is not None:
+            out["check"] = check
+        if first_loss is not None and cfg.model.name in FIRST_STEP_LOSS:
+            ref, tol = FIRST_STEP_LOSS[cfg.model.name]
+            out["loss_first_step_reference"] = {"n1_value": ref, "tolerance": tol, "ok": abs(first_loss - ref) <= tol}
         if args.layers or args.global_batch:
             out["invalid"] = "layer count or global batch overridden for debugging"
         if args.twin:
@@ -314,6 +416,9 @@ def main() -> int:
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if check is not None and not check["ok"]:
+        print(f"bench.py: the multi-GPU self-check failed: {check}", file=sys.stderr)
+        return 5
     if st & 0x3 and not args.twin:
         print(f"bench.py: device status 0x{st:x}: a bounded device-side wait timed out inside the timed region", file=sys.stderr)
         return 4

@@ -301,6 +301,34 @@ def mode_ckpt(dev, stage, ckpt_dir, tp=1, dtype="fp32", resume_tp=None):
     dist.barrier()
 
 
+def mode_baseline(dev, dtype, tp, stage):
+    """The eager-PyTorch baseline arm under tensor x data parallelism against the product arm on one rank."""
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline"))
+    from torch_nccl import BaselineTrainer
+    from elfa_b200.parallel.mesh import ParallelContext
+    from elfa_b200.trainer import Trainer
+    world = dist.get_world_size()
+    dp = world // tp
+    cfg = small_cfg(dtype, tp, "nccl", "mxfp8", "mxfp8")
+    cfg.runtime.world_size = world
+    cfg.runtime.zero_stage = stage
+    cfg.training.micro_batch_size, cfg.training.global_batch_size = 2, 2 * dp
+    tr = BaselineTrainer(cfg, dev)
+    loader = tr.make_loader()
+    losses = [tr.finish_step(tr.train_step([loader.next_cycling() for _ in range(tr.accum)])) for _ in range(4)]
+    if dist.get_rank() == 0:
+        cfg1 = small_cfg(dtype, 1, "nccl", "mxfp8", "mxfp8")
+        cfg1.runtime.world_size = 1
+        cfg1.runtime.zero_stage = 0
+        cfg1.training.micro_batch_size = cfg1.training.global_batch_size = 2 * dp
+        ref = Trainer(cfg1, device=dev, pc=ParallelContext(), telemetry=False).run(max_steps=4)
+        tol = 2e-3 if dtype == "fp32" else 0.05
+        for a, b in zip(losses, ref):
+            assert abs(a - b) < tol * max(1.0, abs(b)), f"baseline arm {losses} differs from the product arm {ref}"
+        print(f"BASELINE_OK tp={tp} dp={dp} stage={stage} losses={[round(x, 4) for x in losses]} ref={[round(x, 4) for x in ref]}")
+    dist.barrier()
+
+
 def mode_mailbox(pc, dev):
     """Ring hand-off through peer mailboxes: several rounds, payload checked against the sender's rank."""
     from elfa_b200 import native
@@ -374,7 +402,7 @@ def main():
     mode = sys.argv[1]
     backend = sys.argv[2] if len(sys.argv) > 2 else "nccl"
     dtype = sys.argv[3] if len(sys.argv) > 3 else "bf16"
-    use_cuda = torch.cuda.is_available() and mode not in ("tp_cpu", "zero_cpu", "ckpt_cpu", "killrank_cpu", "cp_cpu", "hybrid_cpu")
+    use_cuda = torch.cuda.is_available() and mode not in ("tp_cpu", "zero_cpu", "ckpt_cpu", "killrank_cpu", "cp_cpu", "hybrid_cpu", "baseline_cpu")
     world = init_distributed("nccl" if use_cuda else "gloo")
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if use_cuda else torch.device("cpu")
     if mode == "killrank_cpu":
@@ -383,6 +411,10 @@ def main():
     if mode == "ckpt_cpu":
         mode_ckpt(dev, int(sys.argv[2]), sys.argv[3], int(sys.argv[4]) if len(sys.argv) > 4 else 1,
                   sys.argv[5] if len(sys.argv) > 5 else "fp32", int(sys.argv[6]) if len(sys.argv) > 6 else None)
+        dist.destroy_process_group()
+        return
+    if mode in ("baseline", "baseline_cpu"):
+        mode_baseline(dev, dtype, int(sys.argv[4]) if len(sys.argv) > 4 else 2, int(sys.argv[5]) if len(sys.argv) > 5 else 0)
         dist.destroy_process_group()
         return
     if mode in ("hybrid", "hybrid_cpu"):

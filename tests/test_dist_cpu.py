@@ -69,6 +69,13 @@ def test_optimizer_state_is_layout_independent(world, stage, tp, dtype, resume_t
     assert "CKPT_OK" in r.stdout
 
 
+@pytest.mark.parametrize("world,tp,stage", [(2, 2, 0), (4, 2, 1)])
+def test_baseline_arm_under_tensor_and_data_parallelism_matches_the_product_arm(world, tp, stage):
+    r = _run(world, ["baseline_cpu", "nccl", "fp32", str(tp), str(stage)], 29730 + world + stage)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "BASELINE_OK" in r.stdout
+
+
 def test_rank_that_leaves_between_steps_is_detected_on_the_host(tmp_path):
     """Host-side fault injection (kill_rank) + heartbeat soft barrier: survivors raise RankFailure, nobody hangs."""
     env = {"ELFA_FAULT": "kill_rank:rank=2,step=3,code=0", "ELFA_HEARTBEAT_DIR": str(tmp_path / "hb"), "ELFA_HEARTBEAT_TIMEOUT_S": "3"}
