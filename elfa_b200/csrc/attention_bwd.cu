@@ -35,8 +35,14 @@ namespace {
 constexpr int ATTB_THREADS = 320;
 constexpr int SUBB = 128 * 128;
 
+// Grouped-query attention (Hkv < H): the key-tile pass runs one CTA per key / value head and walks the query tiles of every
+// query head of its group one after the other, so dK / dV are summed in a fixed order; the query-tile pass reads the group's
+// key head. Packed sequences (doc_start, see the forward kernel): masked like the causal diagonal, block pairs without a
+// visible (query, key) pair are skipped.
 struct AttnBwdParams {
   int S, B, H, hd;
+  int Hkv;
+  const int* doc_start;   // [B, S] or null
   const float* lse;    // [B, H, S] natural log
   const float* delta;  // [B, H, S]
   __nv_bfloat16* dqkv;
@@ -56,8 +62,8 @@ struct BwdSmem {
   static constexpr int RES1 = RES0 + NSUB * SUBB;
   static constexpr int IN0 = RES1 + NSUB * SUBB;           // [2 slots][NSUB]
   static constexpr int IN1 = IN0 + 2 * NSUB * SUBB;        // [2 slots][NSUB]
-  static constexpr int VEC_OFF = IN1 + 2 * NSUB * SUBB;    // lse2 / delta of the inner query tile: [2 slots][2][128] floats
-  static constexpr int BAR_OFF = VEC_OFF + 2 * 2 * 128 * 4;
+  static constexpr int VEC_OFF = IN1 + 2 * NSUB * SUBB;    // lse2 / delta / document start of the inner query tile: [2 slots][3][128] words
+  static constexpr int BAR_OFF = VEC_OFF + 2 * 3 * 128 * 4;
   static constexpr int TOTAL = BAR_OFF + BB_COUNT * 8 + 16;
   static constexpr int DYN = TOTAL + 1024;
 };
@@ -103,12 +109,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
   auto bar = [&](int i) { return bar0 + 8u * i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.y, b = blockIdx.z;
+  const int h = blockIdx.y, b = blockIdx.z;     // DKV: key / value head; DQ: query head
+  const int group = p.H / p.Hkv;
+  const int kvh = DKV ? h : h / group;
   // outer tile and the inner range it loops over
   const int outer = DKV ? (int)blockIdx.x : p.n_tiles - 1 - (int)blockIdx.x;   // heaviest first in both modes
-  const int in_begin = DKV ? (p.causal ? outer : 0) : 0;
-  const int in_end = DKV ? p.n_tiles : (p.causal ? outer + 1 : p.n_tiles);
-  const int n_iter = in_end - in_begin;
+  int in_begin = DKV ? (p.causal ? outer : 0) : 0;
+  int in_end = DKV ? p.n_tiles : (p.causal ? outer + 1 : p.n_tiles);
+  const int* dstart = p.doc_start ? p.doc_start + (long long)b * p.S : nullptr;
+  if (dstart) {
+    if (DKV) {      // query tiles whose first row's document starts after this key tile see none of it
+      int e = in_begin + 1;
+      while (e < in_end && dstart[e * 128] <= outer * 128 + 127) ++e;
+      in_end = e;
+    } else {
+      in_begin = dstart[outer * 128] / 128;
+    }
+  }
+  const int n_in = in_end - in_begin;                     // inner tiles per head
+  const int n_iter = DKV ? n_in * group : n_in;           // DKV: every query head of the group in turn
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmQKV);
@@ -135,25 +154,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
 
   if (warp == 0) {
     if (lane == 0) {
-      auto load_qdo = [&](uint32_t dq, uint32_t ddo, int tile, int bar_id) {
+      auto load_qdo = [&](uint32_t dq, uint32_t ddo, int hq, int tile, int bar_id) {
         for (int s = 0; s < NSUB; ++s) {
-          tma_load_4d(dq + s * SUBB, &tmQKV, s * 64, 0 * p.H + h, b, tile * 128, bar(bar_id));
-          tma_load_4d(ddo + s * SUBB, &tmDO, s * 64, h, b, tile * 128, bar(bar_id));
+          tma_load_4d(dq + s * SUBB, &tmQKV, s * 64, hq, b, tile * 128, bar(bar_id));
+          tma_load_4d(ddo + s * SUBB, &tmDO, s * 64, hq, b, tile * 128, bar(bar_id));
         }
       };
       auto load_kv = [&](uint32_t dk, uint32_t dv, int tile, int bar_id) {
         for (int s = 0; s < NSUB; ++s) {
-          tma_load_4d(dk + s * SUBB, &tmQKV, s * 64, 1 * p.H + h, b, tile * 128, bar(bar_id));
-          tma_load_4d(dv + s * SUBB, &tmQKV, s * 64, 2 * p.H + h, b, tile * 128, bar(bar_id));
+          tma_load_4d(dk + s * SUBB, &tmQKV, s * 64, p.H + kvh, b, tile * 128, bar(bar_id));
+          tma_load_4d(dv + s * SUBB, &tmQKV, s * 64, p.H + p.Hkv + kvh, b, tile * 128, bar(bar_id));
         }
       };
       mbar_expect_tx(bar(BB_RES), 2 * NSUB * SUBB);
-      if (DKV) load_kv(sRes0, sRes1, outer, BB_RES); else load_qdo(sRes0, sRes1, outer, BB_RES);
+      if (DKV) load_kv(sRes0, sRes1, outer, BB_RES); else load_qdo(sRes0, sRes1, h, outer, BB_RES);
       for (int it = 0; it < n_iter; ++it) {
         const int slot = it & 1;
         if (it >= 2 && !mbar_wait(bar(BB_INFREE0 + slot), ((it >> 1) - 1) & 1, abort_flag, p.status)) break;
         mbar_expect_tx(bar(BB_INFULL0 + slot), 2 * NSUB * SUBB);
-        if (DKV) load_qdo(sIn0(slot), sIn1(slot), in_begin + it, BB_INFULL0 + slot);
+        if (DKV) load_qdo(sIn0(slot), sIn1(slot), kvh * group + it / n_in, in_begin + it % n_in, BB_INFULL0 + slot);
         else load_kv(sIn0(slot), sIn1(slot), in_begin + it, BB_INFULL0 + slot);
       }
     }
@@ -252,25 +271,33 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
     bool ok = true;
     float lse2 = 0.f, dlt = 0.f;
     bool row_ok = true;
+    int lower = 0;                                // DQ: first key this query row may see (packed sequences)
     if (!DKV) {
       const int row = outer * 128 + row_local;
       row_ok = row < p.S;
       if (row_ok) {   // negated / pre-scaled like the shared-memory vectors of the other mode
         lse2 = -p.lse[((long long)b * p.H + h) * p.S + row] * LOG2E;
         dlt = -p.delta[((long long)b * p.H + h) * p.S + row] * p.scale;
+        if (dstart) lower = dstart[row];
       }
     }
     for (int it = 0; it < n_iter; ++it) {
-      const int q_tile = DKV ? in_begin + it : outer;
+      const int q_tile = DKV ? in_begin + it % n_in : outer;
       const int k_tile = DKV ? outer : in_begin + it;
-      float* vl = svec + (it & 1) * 256;          // [0,128) lse2, [128,256) delta of the inner query tile
+      const int hq = DKV ? kvh * group + it / n_in : h;      // query head of this iteration
+      float* vl = svec + (it & 1) * 384;          // [0,128) lse2, [128,256) delta, [256,384) document start of the inner query tile
+      const int* vdoc = reinterpret_cast<const int*>(vl + 256);
       if (DKV) {
         const int qi = ct & 127;
         const int qrow = q_tile * 128 + qi;
-        const long long idx = ((long long)b * p.H + h) * p.S + qrow;
+        const long long idx = ((long long)b * p.H + hq) * p.S + qrow;
         // stored negated (and delta pre-multiplied by the softmax scale) so that both uses are one fused multiply-add
-        if (ct < 128) vl[qi] = qrow < p.S ? -p.lse[idx] * LOG2E : -INFINITY;   // -inf -> exp2(-inf) = 0 for rows past the end
-        else vl[128 + qi] = qrow < p.S ? -p.delta[idx] * p.scale : 0.f;
+        if (ct < 128) {
+          vl[qi] = qrow < p.S ? -p.lse[idx] * LOG2E : -INFINITY;   // -inf -> exp2(-inf) = 0 for rows past the end
+          if (dstart) reinterpret_cast<int*>(vl + 256)[qi] = dstart[min(qrow, p.S - 1)];
+        } else {
+          vl[128 + qi] = qrow < p.S ? -p.delta[idx] * p.scale : 0.f;
+        }
         named_bar_sync(1, 256);
       }
       // After a timeout the loop keeps running without touching tensor memory so that every warp
@@ -306,7 +333,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
                 const int col = col0 + i + u;
                 float e = fast_exp2(fmaf(__uint_as_float(rs[i + u]), sc2, l4[u]));
                 // DKV: lane = key, column = query -> masked when key > query; DQ: lane = query, column = key
-                const bool masked = DKV ? (diag && row_local > col) : (!row_ok || (diag && col > row_local));
+                bool masked = DKV ? (diag && row_local > col) : (!row_ok || (diag && col > row_local));
+                if (dstart) masked = masked || (DKV ? (k_tile * 128 + row_local < vdoc[col]) : (k_tile * 128 + col < lower));
                 if (masked) e = 0.f;
                 ev[c * 32 + i + u] = e;
               }
@@ -324,7 +352,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
         }
       };
       if (ok) {
-        const bool any_mask = diag || (!DKV && (outer + 1) * 128 > p.S);
+        // a document boundary inside the block pair: the key tile starts before the query tile's last document does
+        const bool doc_mask = dstart && k_tile * 128 < dstart[min(q_tile * 128 + 127, p.S - 1)];
+        const bool any_mask = diag || doc_mask || (!DKV && (outer + 1) * 128 > p.S);
         if (any_mask) phase1(std::true_type{}); else phase1(std::false_type{});
       }
       if (DKV) {
@@ -408,10 +438,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
         uint32_t r[32];
         tmem_ld32((acc == 0 ? TM_ACC0 : TM_ACC1) + lane_addr + c * 32, r);
         tmem_ld_wait();
-        // DKV: acc 0 = dV (plane 2), acc 1 = dK (plane 1); DQ: dQ (plane 0)
-        const int plane = DKV ? (acc == 0 ? 2 : 1) : 0;
+        // DKV: acc 0 = dV, acc 1 = dK of key head `kvh`; DQ: dQ of query head `h`; heads are [H query | Hkv key | Hkv value]
+        const int head = DKV ? (acc == 0 ? p.H + p.Hkv + kvh : p.H + kvh) : h;
         if (row < p.S) {
-          __nv_bfloat16* dst = p.dqkv + (long long)row * p.d_stride_s + (long long)b * p.d_stride_b + ((long long)plane * p.H + h) * p.hd;
+          __nv_bfloat16* dst = p.dqkv + (long long)row * p.d_stride_s + (long long)b * p.d_stride_b + (long long)head * p.hd;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             const int d0 = c * 32 + g * 8;
@@ -445,7 +475,7 @@ int launch_attn_bwd(const CUtensorMap& tmQKV, const CUtensorMap& tmDO, const Att
     ELFA_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
     configured = true;
   }
-  dim3 grid(p.n_tiles, p.H, p.B);
+  dim3 grid(p.n_tiles, DKV ? p.Hkv : p.H, p.B);
   kern<<<grid, ATTB_THREADS, L::DYN, stream>>>(tmQKV, tmDO, p);
   ELFA_CUDA(cudaGetLastError());
   ::elfa::count_launches(1);
@@ -457,13 +487,16 @@ int launch_attn_bwd(const CUtensorMap& tmQKV, const CUtensorMap& tmDO, const Att
 
 using namespace elfa;
 
-// Gradients of attention w.r.t. the fused qkv tensor. `out`/`dout` share strides (o_stride_*),
-// `dqkv` has the layout of qkv with its own strides; `delta` is [B, H, S] fp32 scratch.
-ELFA_API int elfa_attention_bwd(const void* qkv, long long stride_s, long long stride_b, const void* out, const void* dout,
-                                long long o_stride_s, long long o_stride_b, const float* lse, float* delta, void* dqkv,
-                                long long d_stride_s, long long d_stride_b, int S, int B, int H, int hd, float scale, int causal,
-                                void* stream) {
+// Gradients of attention w.r.t. the fused qkv tensor (heads [H query | Hkv key | Hkv value], see elfa_attention_fwd_ex).
+// `out` / `dout` share strides (o_stride_*), `dqkv` has the layout of qkv with its own strides; `delta` is [B, H, S] fp32
+// scratch. doc_start: [B, S] int32 or null.
+ELFA_API int elfa_attention_bwd_ex(const void* qkv, long long stride_s, long long stride_b, const void* out, const void* dout,
+                                   long long o_stride_s, long long o_stride_b, const float* lse, float* delta, void* dqkv,
+                                   long long d_stride_s, long long d_stride_b, int S, int B, int H, int Hkv, int hd, float scale,
+                                   int causal, const int* doc_start, void* stream) {
   ELFA_REQUIRE(qkv && out && dout && lse && delta && dqkv && S > 0 && B > 0 && H > 0, "attention_bwd: bad arguments");
+  ELFA_REQUIRE(Hkv > 0 && H % Hkv == 0, "attention_bwd: the query heads must be a multiple of the key / value heads");
+  ELFA_REQUIRE(!doc_start || causal, "attention_bwd: document masks need causal attention");
   ELFA_REQUIRE(hd % 8 == 0 && hd >= 8 && hd <= 128, "attention_bwd: head_dim must be a multiple of 8 in [8, 128]");
   ELFA_REQUIRE(stride_s % 8 == 0 && stride_b % 8 == 0 && o_stride_s % 8 == 0 && o_stride_b % 8 == 0 && d_stride_s % 8 == 0 &&
                    d_stride_b % 8 == 0,
@@ -478,12 +511,14 @@ ELFA_API int elfa_attention_bwd(const void* qkv, long long stride_s, long long s
   ELFA_CUDA(cudaGetLastError());
   ::elfa::count_launches(1);
   CUtensorMap tmQKV, tmDO;
-  int rc = make_qkv_tmap(&tmQKV, qkv, S, B, H, hd, stride_s, stride_b, 3, 128);
+  int rc = make_qkv_tmap(&tmQKV, qkv, S, B, H + 2 * Hkv, hd, stride_s, stride_b, 1, 128);
   if (rc != ELFA_OK) return rc;
   rc = make_qkv_tmap(&tmDO, dout, S, B, H, hd, o_stride_s, o_stride_b, 1, 128);
   if (rc != ELFA_OK) return rc;
   AttnBwdParams p{};
   p.S = S; p.B = B; p.H = H; p.hd = hd;
+  p.Hkv = Hkv;
+  p.doc_start = doc_start;
   p.lse = lse; p.delta = delta;
   p.dqkv = static_cast<__nv_bfloat16*>(dqkv);
   p.d_stride_s = d_stride_s; p.d_stride_b = d_stride_b;
@@ -500,4 +535,12 @@ ELFA_API int elfa_attention_bwd(const void* qkv, long long stride_s, long long s
   rc = launch_attn_bwd<128, true>(tmQKV, tmDO, p, s);
   if (rc != ELFA_OK) return rc;
   return launch_attn_bwd<128, false>(tmQKV, tmDO, p, s);
+}
+
+ELFA_API int elfa_attention_bwd(const void* qkv, long long stride_s, long long stride_b, const void* out, const void* dout,
+                                long long o_stride_s, long long o_stride_b, const float* lse, float* delta, void* dqkv,
+                                long long d_stride_s, long long d_stride_b, int S, int B, int H, int hd, float scale, int causal,
+                                void* stream) {
+  return elfa_attention_bwd_ex(qkv, stride_s, stride_b, out, dout, o_stride_s, o_stride_b, lse, delta, dqkv, d_stride_s, d_stride_b, S, B,
+                               H, H, hd, scale, causal, nullptr, stream);
 }

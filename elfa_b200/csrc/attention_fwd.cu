@@ -30,8 +30,14 @@ namespace {
 constexpr int ATT_THREADS = 320;
 constexpr int SUB_BYTES = 128 * 128;  // one [128 rows x 64 bf16] swizzled sub-tile
 
+// Grouped-query attention: H query heads share Hkv key / value heads (H / Hkv consecutive query heads per key head); the
+// fused tensor then holds H + 2 * Hkv heads per token: [q heads | k heads | v heads].
+// Packed sequences: `doc_start[b, s]` is the position of the first token of the document that token s belongs to; a query
+// sees keys in [doc_start, s] only, and key blocks that lie wholly before a query tile's first document are skipped.
 struct AttnFwdParams {
   int S, B, H, hd;
+  int Hkv;
+  const int* doc_start;              // [B, S] or null
   __nv_bfloat16* O;
   long long o_stride_s, o_stride_b;  // elements; head stride = hd
   float* lse;                        // [B, H, S]
@@ -78,6 +84,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
   const int n_kv = (p.S + 127) / 128;
   const int n_a = has_a ? (p.causal ? tile_a + 1 : n_kv) : 0;
   const int n_b = p.causal ? tile_b + 1 : n_kv;
+  const int kvh = h / (p.H / p.Hkv);                      // key / value head of this query head
+  // first key block any row of the pair can see (documents start at non-decreasing positions along the sequence)
+  const int j0 = p.doc_start ? p.doc_start[(long long)b * p.S + (has_a ? tile_a : tile_b) * 128] / 128 : 0;
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmQKV);
@@ -106,15 +115,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
         for (int s = 0; s < NSUB; ++s)
           tma_load_4d(sbase + L::Q_OFF + (t * NSUB + s) * SUB_BYTES, &tmQKV, s * 64, 0 * p.H + h, b, q0, bar(BAR_Q));
       }
-      for (int j = 0; j < n_b; ++j) {
-        if (j > 0 && !mbar_wait(bar(BAR_KFREE), (j - 1) & 1, abort_flag, p.status)) break;
+      for (int j = j0; j < n_b; ++j) {
+        if (j > j0 && !mbar_wait(bar(BAR_KFREE), (j - j0 - 1) & 1, abort_flag, p.status)) break;
         mbar_expect_tx(bar(BAR_KFULL), NSUB * SUB_BYTES);
         for (int s = 0; s < NSUB; ++s)
-          tma_load_4d(sbase + L::K_OFF + s * SUB_BYTES, &tmQKV, s * 64, 1 * p.H + h, b, j * 128, bar(BAR_KFULL));
-        if (j > 0 && !mbar_wait(bar(BAR_VFREE), (j - 1) & 1, abort_flag, p.status)) break;
+          tma_load_4d(sbase + L::K_OFF + s * SUB_BYTES, &tmQKV, s * 64, p.H + kvh, b, j * 128, bar(BAR_KFULL));
+        if (j > j0 && !mbar_wait(bar(BAR_VFREE), (j - j0 - 1) & 1, abort_flag, p.status)) break;
         mbar_expect_tx(bar(BAR_VFULL), NSUB * SUB_BYTES);
         for (int s = 0; s < NSUB; ++s)
-          tma_load_4d(sbase + L::V_OFF + s * SUB_BYTES, &tmQKV, s * 64, 2 * p.H + h, b, j * 128, bar(BAR_VFULL));
+          tma_load_4d(sbase + L::V_OFF + s * SUB_BYTES, &tmQKV, s * 64, p.H + p.Hkv + kvh, b, j * 128, bar(BAR_VFULL));
       }
     }
   } else if (warp == 1) {
@@ -147,7 +156,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
           for (int kk = 0; kk < 8; ++kk) {
             const uint32_t poff = (kk / 4) * SUB_BYTES + (kk % 4) * 32;
             tc_mma_f16(TM_O[t], make_smem_desc(pb + poff, 16, 1024, 2), make_smem_desc(vb + kk * 2048, SUB_BYTES, 1024, 2), idesc_o,
-                       (j | kk) != 0);
+                       (j != j0 || kk != 0) ? 1u : 0u);
           }
           tc_commit(bar(BAR_OFULL0 + t));
         }
@@ -160,8 +169,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
         issue_s(1);
         commit(BAR_KFREE);
       }
-      for (int j = 0; j < n_b && ok; ++j) {
-        const uint32_t ph = j & 1;
+      for (int j = j0; j < n_b && ok; ++j) {
+        const uint32_t ph = (j - j0) & 1;
         if (!wait(BAR_VFULL, ph)) break;
         if (j < n_a) {
           if (!wait(BAR_PREADY0, ph)) break;
@@ -197,15 +206,18 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
     const uint32_t p_row = sbase + L::P_OFF + t * 2 * SUB_BYTES + row_local * 128;
     float m = -INFINITY, l = 0.f;   // m: the maximum used in the exponent (may lag the true maximum)
     bool ok = true;
-    for (int j = 0; j < n_t; ++j) {
-      const uint32_t ph = j & 1;
+    // packed sequences: first key this row may see, and the largest such position in the tile (its last row's)
+    const int lower = p.doc_start ? p.doc_start[(long long)b * p.S + min(row, p.S - 1)] : 0;
+    const int lower_max = p.doc_start ? p.doc_start[(long long)b * p.S + min(tile * 128 + 127, p.S - 1)] : 0;
+    for (int j = j0; j < n_t; ++j) {
+      const uint32_t ph = (j - j0) & 1;
       ok = mbar_wait(bar(BAR_SFULL0 + t), ph, abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       const int key0 = j * 128;
       const int limit = p.causal ? row : (p.S - 1);       // last key this row may see
-      const bool need_mask = key0 + 127 > (p.causal ? tile * 128 : p.S - 1);
+      const bool need_mask = key0 + 127 > (p.causal ? tile * 128 : p.S - 1) || key0 < lower_max;
       // Two passes over the S row in 32-column chunks (row maximum, then exponentials), each chunk loaded
       // from tensor memory while the previous one is processed: about 64 live registers instead of 128.
       uint32_t cb[2][32];
@@ -224,7 +236,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               float sv = __uint_as_float(cb[c & 1][i]);
-              if (key0 + c * 32 + i > limit) sv = -INFINITY;
+              if (key0 + c * 32 + i > limit || key0 + c * 32 + i < lower) sv = -INFINITY;
               mx4[i & 3] = fmaxf(mx4[i & 3], sv);
             }
           } else {
@@ -236,13 +248,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       };
       if (need_mask) row_max(std::true_type{}); else row_max(std::false_type{});
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
-      if (j == 0) {
+      if (j == j0) {
         m = mx;
       } else {
         const bool grow = mx - m > 8.f;
         if (__any_sync(0xffffffffu, grow)) {
           // rescale this warp's O rows in tensor memory; the previous P V must have landed
-          ok = mbar_wait(bar(BAR_OFULL0 + t), (j - 1) & 1, abort_flag, p.status);
+          ok = mbar_wait(bar(BAR_OFULL0 + t), (j - j0 - 1) & 1, abort_flag, p.status);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
@@ -279,7 +291,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               float sv = __uint_as_float(r[i]);
-              if (key0 + c * 32 + i > limit) sv = -INFINITY;
+              if (key0 + c * 32 + i > limit || key0 + c * 32 + i < lower) sv = -INFINITY;
               const float e = fast_exp2(fmaf(sv, sc2, neg_m));
               ls4[i & 3] += e;
               r[i] = __float_as_uint(e);
@@ -320,7 +332,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       mbar_arrive(bar(BAR_PREADY0 + t));
     }
     if (ok && n_t > 0) {
-      ok = mbar_wait(bar(BAR_OFULL0 + t), (n_t - 1) & 1, abort_flag, p.status);
+      ok = mbar_wait(bar(BAR_OFULL0 + t), (n_t - 1 - j0) & 1, abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok && n_t > 0) {
@@ -376,7 +388,7 @@ int launch_attn_fwd(const CUtensorMap& tm, const AttnFwdParams& p, cudaStream_t 
 
 }  // namespace
 
-// 4-D map over a fused qkv tensor: dims {hd, 3*H, B, S}, box {64, 1, 1, box_rows}.
+// 4-D map over a fused tensor of `planes * H` heads per token: dims {hd, planes * H, B, S}, box {64, 1, 1, box_rows}.
 int make_qkv_tmap(CUtensorMap* tm, const void* qkv, int S, int B, int H, int hd, long long stride_s, long long stride_b,
                   int planes, uint32_t box_rows) {
   const uint64_t dims[4] = {(uint64_t)hd, (uint64_t)planes * H, (uint64_t)B, (uint64_t)S};
@@ -389,20 +401,26 @@ int make_qkv_tmap(CUtensorMap* tm, const void* qkv, int S, int B, int H, int hd,
 
 using namespace elfa;
 
-// qkv: element (s, b, which, h, d) at s*stride_s + b*stride_b + (which*H + h)*hd + d (bf16).
-// out: element (s, b, h, d) at s*o_stride_s + b*o_stride_b + h*hd + d. lse: [B, H, S] fp32 or null.
-ELFA_API int elfa_attention_fwd(const void* qkv, long long stride_s, long long stride_b, void* out, long long o_stride_s,
-                                long long o_stride_b, float* lse, int S, int B, int H, int hd, float scale, int causal, void* stream) {
+// qkv: element (s, b, head, d) at s*stride_s + b*stride_b + head*hd + d (bf16); heads are [H query | Hkv key | Hkv value]
+// (Hkv == H: the classic [3][H] layout). out: element (s, b, h, d) at s*o_stride_s + b*o_stride_b + h*hd + d.
+// lse: [B, H, S] fp32 or null. doc_start: [B, S] int32 (first position of each token's document) or null.
+ELFA_API int elfa_attention_fwd_ex(const void* qkv, long long stride_s, long long stride_b, void* out, long long o_stride_s,
+                                   long long o_stride_b, float* lse, int S, int B, int H, int Hkv, int hd, float scale, int causal,
+                                   const int* doc_start, void* stream) {
   ELFA_REQUIRE(qkv && out && S > 0 && B > 0 && H > 0, "attention_fwd: bad arguments");
+  ELFA_REQUIRE(Hkv > 0 && H % Hkv == 0, "attention_fwd: the query heads must be a multiple of the key / value heads");
+  ELFA_REQUIRE(!doc_start || causal, "attention_fwd: document masks need causal attention");
   ELFA_REQUIRE(hd % 8 == 0 && hd >= 8 && hd <= 128, "attention_fwd: head_dim must be a multiple of 8 in [8, 128]");
   ELFA_REQUIRE(stride_s % 8 == 0 && stride_b % 8 == 0 && o_stride_s % 8 == 0 && o_stride_b % 8 == 0, "attention_fwd: strides must be multiples of 8");
   unsigned int* st = status_word();
   ELFA_REQUIRE(st != nullptr, "attention_fwd: no status word");
   CUtensorMap tm;
-  int rc = make_qkv_tmap(&tm, qkv, S, B, H, hd, stride_s, stride_b, 3, 128);
+  int rc = make_qkv_tmap(&tm, qkv, S, B, H + 2 * Hkv, hd, stride_s, stride_b, 1, 128);
   if (rc != ELFA_OK) return rc;
   AttnFwdParams p{};
   p.S = S; p.B = B; p.H = H; p.hd = hd;
+  p.Hkv = Hkv;
+  p.doc_start = doc_start;
   p.O = static_cast<__nv_bfloat16*>(out);
   p.o_stride_s = o_stride_s; p.o_stride_b = o_stride_b;
   p.lse = lse;
@@ -412,4 +430,9 @@ ELFA_API int elfa_attention_fwd(const void* qkv, long long stride_s, long long s
   p.status = st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return hd <= 64 ? launch_attn_fwd<64>(tm, p, s) : launch_attn_fwd<128>(tm, p, s);
+}
+
+ELFA_API int elfa_attention_fwd(const void* qkv, long long stride_s, long long stride_b, void* out, long long o_stride_s,
+                                long long o_stride_b, float* lse, int S, int B, int H, int hd, float scale, int causal, void* stream) {
+  return elfa_attention_fwd_ex(qkv, stride_s, stride_b, out, o_stride_s, o_stride_b, lse, S, B, H, H, hd, scale, causal, nullptr, stream);
 }

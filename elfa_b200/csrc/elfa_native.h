@@ -75,12 +75,19 @@ int elfa_muon_apply(void* param, int param_type, float* master, const void* y, l
 int elfa_attention_fwd(const void* qkv, long long stride_s, long long stride_b, void* out, long long o_stride_s,
                        long long o_stride_b, float* lse, int S, int B, int H, int hd, float scale, int causal, void* stream);
 
+int elfa_attention_fwd_ex(const void* qkv, long long stride_s, long long stride_b, void* out, long long o_stride_s,
+                          long long o_stride_b, float* lse, int S, int B, int H, int Hkv, int hd, float scale, int causal,
+                          const int* doc_start, void* stream);
 // ---- attention_bwd.cu --------------------------------------------------------------------------
 int elfa_attention_bwd(const void* qkv, long long stride_s, long long stride_b, const void* out, const void* dout,
                        long long o_stride_s, long long o_stride_b, const float* lse, float* delta, void* dqkv,
                        long long d_stride_s, long long d_stride_b, int S, int B, int H, int hd, float scale, int causal,
                        void* stream);
 
+int elfa_attention_bwd_ex(const void* qkv, long long stride_s, long long stride_b, const void* out, const void* dout,
+                          long long o_stride_s, long long o_stride_b, const float* lse, float* delta, void* dqkv,
+                          long long d_stride_s, long long d_stride_b, int S, int B, int H, int Hkv, int hd, float scale, int causal,
+                          const int* doc_start, void* stream);
 // ---- gemm_mxfp8.cu ------------------------------------------------------------------------------
 // Block-scaled MXFP8 tensor-core GEMM (e4m3 payloads, ue8m0 scales per 32 K-elements in 512-byte atoms)
 long long elfa_mxfp8_sf_bytes(int rows, int cols, int b_operand);

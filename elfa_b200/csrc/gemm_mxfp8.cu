@@ -334,6 +334,41 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t tcol0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * ACC_STRIDE;
+      if (fl == 0) {
+        // plain bf16 output: two register buffers alternating, no per-element branches
+        __nv_bfloat16* crow = p.C + (long long)row * p.ldc;
+        auto store_chunk = [&](const uint32_t (&r)[32], int c) {
+          const int col0 = n0 + c * 32;
+          if (!row_ok || col0 >= p.N) return;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = col0 + g * 8;
+            if (col + 8 > p.N) continue;
+            const uint4 o = make_uint4(pack_bf16(__uint_as_float(r[g * 8 + 0]) * alpha, __uint_as_float(r[g * 8 + 1]) * alpha),
+                                       pack_bf16(__uint_as_float(r[g * 8 + 2]) * alpha, __uint_as_float(r[g * 8 + 3]) * alpha),
+                                       pack_bf16(__uint_as_float(r[g * 8 + 4]) * alpha, __uint_as_float(r[g * 8 + 5]) * alpha),
+                                       pack_bf16(__uint_as_float(r[g * 8 + 6]) * alpha, __uint_as_float(r[g * 8 + 7]) * alpha));
+            *reinterpret_cast<uint4*>(crow + col) = o;
+          }
+        };
+        uint32_t ra[32], rb[32];
+        tmem_ld32(tcol0, ra);
+#pragma unroll
+        for (int c = 0; c < BN / 32; c += 2) {
+          tmem_ld_wait();
+          tmem_ld32(tcol0 + (c + 1) * 32, rb);
+          store_chunk(ra, c);
+          tmem_ld_wait();
+          if (c + 2 < BN / 32) tmem_ld32(tcol0 + (c + 2) * 32, ra);
+          store_chunk(rb, c + 1);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (TWO) mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0)); else mbar_arrive(tempty_bar(buf));
+        }
+        continue;
+      }
       uint32_t rnext[32];
       tmem_ld32(tcol0, rnext);
 #pragma unroll 1

@@ -34,7 +34,8 @@ VERSION = 1
 @dataclass
 class Batch:
     input: torch.Tensor     # [B, S] int64
-    target: torch.Tensor    # [B, S] int64
+    target: torch.Tensor    # [B, S] int64 (-100: no loss at this position)
+    doc_start: Optional[torch.Tensor] = None    # [B, S] int32, packed rows only: first position of each token's document
 
     @property
     def num_tokens(self) -> int:
@@ -194,7 +195,12 @@ class DataLoader:
     """Yields :class:`Batch` es of ``[batch, seq_len]`` int64 tensors (pinned when CUDA exists)."""
 
     def __init__(self, dataset, batch_size: int, seq_len: int, shuffle: bool = True, seed: int = 0, dp_rank: int = 0,
-                 dp_size: int = 1, pin_memory: Optional[bool] = None):
+                 dp_size: int = 1, pin_memory: Optional[bool] = None, pack_eos: Optional[int] = None):
+        """``pack_eos``: rows are documents packed back to back, each ended by this token id (``data.pack_sequences``;
+        reference: ``src/data/dataset.zig:421-465`` positions / sequence ids / cumulative lengths of packed rows,
+        ``src/data_packer.zig:5-112``). Batches then carry ``doc_start`` (attention and positions restart at every document)
+        and the target that would cross into the next document is masked out."""
+        self.pack_eos = pack_eos
         self.ds, self.batch_size, self.seq_len = dataset, batch_size, seq_len
         self.shuffle, self.seed = shuffle, seed
         self.dp_rank, self.dp_size = dp_rank, dp_size
@@ -229,9 +235,16 @@ class DataLoader:
         self._pos += self.batch_size
         t = torch.from_numpy(buf)
         inp, tgt = t[:, :S].contiguous(), t[:, 1:].contiguous()
+        doc = None
+        if self.pack_eos is not None:
+            from .packing import document_starts
+            ends = buf[:, :S] == self.pack_eos                # the end-of-sequence token closes its document
+            doc = torch.from_numpy(document_starts(ends))
+            tgt[torch.from_numpy(ends)] = -100                # no prediction across a document boundary
         if self.pin:
             inp, tgt = inp.pin_memory(), tgt.pin_memory()
-        return Batch(inp, tgt)
+            doc = doc.pin_memory() if doc is not None else None
+        return Batch(inp, tgt, doc)
 
     def skip(self, n_batches: int) -> None:
         """Advances the read position by ``n_batches`` batches (rolling over epochs) without

@@ -55,3 +55,14 @@ class StreamingPacker:
         if self.shuffle:
             np.random.default_rng(self.seed).shuffle(out)
         return out
+
+
+def document_starts(ends: np.ndarray) -> np.ndarray:
+    """``ends [B, S]`` bool (True where a token closes its document) → ``[B, S]`` int32: for every position the index of
+    the first token of its document. Row starts open a document; the token after an end opens the next one."""
+    B, S = ends.shape
+    opens = np.zeros((B, S), dtype=bool)
+    opens[:, 0] = True
+    opens[:, 1:] = ends[:, :-1]
+    idx = np.where(opens, np.arange(S, dtype=np.int64)[None, :], 0)
+    return np.maximum.accumulate(idx, axis=1).astype(np.int32)

@@ -72,37 +72,49 @@ class Attention(nn.Module):
         m = cfg.model
         self.pc = pc
         self.n_heads = m.num_heads // pc.tp_size
+        self.n_kv_heads = m.num_kv_heads // pc.tp_size          # grouped-query attention when smaller than n_heads
+        self.gqa = m.num_kv_heads != m.num_heads
         self.head_dim = m.head_dim
         D = m.hidden_dim
         local = self.n_heads * self.head_dim
-        self.w_qkv = nn.Parameter(torch.empty(D, 3 * local, dtype=dtype, device=device))
+        self.w_qkv = nn.Parameter(torch.empty(D, (self.n_heads + 2 * self.n_kv_heads) * self.head_dim, dtype=dtype, device=device))
         self.w_o = nn.Parameter(torch.empty(local, D, dtype=dtype, device=device))
-        self.w_qkv.tp_shard = ("col_qkv", pc.tp_size)
+        self.w_qkv.tp_shard = (f"col_gqa:{m.num_heads}:{m.num_kv_heads}:{m.head_dim}" if self.gqa else "col_qkv", pc.tp_size)
         self.w_o.tp_shard = ("row", pc.tp_size)
         self.init_std, self.out_std = init_std, out_std
         self.quant = QuantSpec.from_config(cfg.quant.attention, cfg.quant)
 
-    def forward(self, x, cache: Optional[dict] = None):            # x: [S(/tp), B, D]
-        h = tpl.column_parallel_linear(x, self.w_qkv, self.pc, quant=self.quant)      # [S, B, 3*local]
+    def forward(self, x, cache: Optional[dict] = None, doc_start: Optional[torch.Tensor] = None):   # x: [S(/tp), B, D]
+        h = tpl.column_parallel_linear(x, self.w_qkv, self.pc, quant=self.quant)      # [S, B, (H + 2 Hkv) * hd]
         S, B = h.shape[0], h.shape[1]
-        qkv = h.view(S, B, 3, self.n_heads, self.head_dim)
+        H, Hkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
+        if self.gqa:
+            qkv = h.view(S, B, H + 2 * Hkv, hd)                   # heads [query | key | value]
+            q, k, v = qkv[:, :, :H], qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:]
+        else:
+            qkv = h.view(S, B, 3, H, hd)
+            q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
         if cache is not None and cache.get("k") is not None:
             # incremental decoding: the new rows attend to the cached keys / values and, causally, to each other
-            k_all = torch.cat((cache["k"], qkv[:, :, 1]), 0)
-            v_all = torch.cat((cache["v"], qkv[:, :, 2]), 0)
+            k_all = torch.cat((cache["k"], k), 0)
+            v_all = torch.cat((cache["v"], v), 0)
             cache["k"], cache["v"] = k_all, v_all
-            o = _attend_cached(qkv[:, :, 0], k_all, v_all)
+            rep = H // Hkv
+            o = _attend_cached(q, k_all.repeat_interleave(rep, 2) if rep > 1 else k_all, v_all.repeat_interleave(rep, 2) if rep > 1 else v_all)
             return tpl.row_parallel_linear(o, self.w_o, self.pc, quant=self.quant)
         if cache is not None:        # prefill: the ordinary kernel, and keep what decoding will need
-            cache["k"], cache["v"] = qkv[:, :, 1].contiguous(), qkv[:, :, 2].contiguous()
-        if self.pc.cp_size > 1 and self.pc.cp_mode == "ulysses":     # all-to-all to whole sequences of H / cp heads and back
-            from ..parallel.ulysses import ulysses_attention
-            o = ulysses_attention(qkv, self.pc.cp_group, causal=True)
-        elif self.pc.cp_size > 1:    # the sequence is split over the context-parallel group: keys / values travel the ring
-            from ..parallel.ring_attention import ring_attention
-            o = ring_attention(qkv, self.pc.cp_group, causal=True, seq_first=True, zigzag=self.pc.cp_mode == "zigzag")
+            cache["k"], cache["v"] = k.contiguous(), v.contiguous()
+        if self.pc.cp_size > 1:
+            if self.gqa or doc_start is not None:
+                raise ValueError("context parallelism is implemented for num_kv_heads == num_heads and unpacked sequences")
+            if self.pc.cp_mode == "ulysses":     # all-to-all to whole sequences of H / cp heads and back
+                from ..parallel.ulysses import ulysses_attention
+                o = ulysses_attention(qkv, self.pc.cp_group, causal=True)
+            else:                                # the sequence is split over the context-parallel group: keys / values travel the ring
+                from ..parallel.ring_attention import ring_attention
+                o = ring_attention(qkv, self.pc.cp_group, causal=True, seq_first=True, zigzag=self.pc.cp_mode == "zigzag")
         else:
-            o = ops.attention(qkv, causal=True, seq_first=True)                      # [S, B, local]
+            o = ops.attention(qkv, causal=True, seq_first=True, num_heads=H if self.gqa else None, doc_start=doc_start)   # [S, B, local]
         return tpl.row_parallel_linear(o, self.w_o, self.pc, quant=self.quant)        # [S(/tp), B, D]
 
 
@@ -142,12 +154,12 @@ class Block(nn.Module):
         self.mlp = MLP(cfg, pc, dtype, device)
         self.dropout = m.dropout
 
-    def forward(self, x, pending, cache: Optional[dict] = None):
+    def forward(self, x, pending, cache: Optional[dict] = None, doc_start: Optional[torch.Tensor] = None):
         """``pending`` is the previous sub-layer's output that has not been added to the residual
         stream yet; the add is fused into the next norm kernel. ``cache``: this layer's key / value cache
-        when decoding incrementally."""
+        when decoding incrementally. ``doc_start``: packed sequences (see ``ops.attention``)."""
         n, x = self.ln1(x, pending)
-        a = self.attn(n, cache)
+        a = self.attn(n, cache, doc_start)
         if self.dropout > 0 and self.training:
             a = torch.nn.functional.dropout(a, self.dropout)
         n, x = self.ln2(x, a)
@@ -168,9 +180,9 @@ class GPTModel(nn.Module):
         tp = self.pc.tp_size
         if m.vocab_size % tp or m.num_heads % tp or m.intermediate_dim % tp:
             raise ValueError("vocab_size, num_heads and intermediate_dim must be divisible by the tensor-parallel size")
-        if m.num_kv_heads != m.num_heads:
-            raise ValueError(f"model.num_kv_heads ({m.num_kv_heads}) must equal model.num_heads ({m.num_heads}): the attention "
-                             "kernels have no grouped-query form")
+        if m.num_kv_heads <= 0 or m.num_heads % m.num_kv_heads or m.num_kv_heads % tp:
+            raise ValueError(f"model.num_kv_heads ({m.num_kv_heads}) must divide model.num_heads ({m.num_heads}) and be divisible by the "
+                             f"tensor-parallel size ({tp})")
         self.vocab_local = m.vocab_size // tp
         self.vocab_lo = self.pc.tp_rank * self.vocab_local
         D = m.hidden_dim
@@ -216,9 +228,9 @@ class GPTModel(nn.Module):
         F = m.intermediate_dim
         for blk in self.blocks:
             s_in = std if std > 0 else math.sqrt(2.0 / D)
-            wqkv = draw((D, 3 * D), s_in)
-            put(blk.attn.w_qkv, tpl.shard_param(wqkv, "col_qkv", tp, r))
-            put(blk.attn.w_o, tpl.shard_param(draw((D, D), s_in), "row", tp, r))
+            wqkv = draw((D, (m.num_heads + 2 * m.num_kv_heads) * m.head_dim), s_in)
+            put(blk.attn.w_qkv, tpl.shard_param(wqkv, blk.attn.w_qkv.tp_shard[0], tp, r))
+            put(blk.attn.w_o, tpl.shard_param(draw((m.num_heads * m.head_dim, D), s_in), "row", tp, r))
             gated = 2 if blk.mlp.gated else 1
             up = draw((D, F * gated), s_in)
             put(blk.mlp.up, tpl.shard_param(up, "col_gated" if blk.mlp.gated else "col", tp, r))
@@ -261,11 +273,19 @@ class GPTModel(nn.Module):
         return n
 
     # ---------------------------------------------------------------- forward
-    def hidden_states(self, ids: torch.Tensor, pos0: int = 0, caches: Optional[list] = None) -> torch.Tensor:
-        """ids ``[B, S]`` → final-norm output ``[S(/tp), B, D]``."""
+    def hidden_states(self, ids: torch.Tensor, pos0: int = 0, caches: Optional[list] = None,
+                      doc_start: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """ids ``[B, S]`` → final-norm output ``[S(/tp), B, D]``. ``doc_start [B, S]`` int32 (packed sequences): positions
+        restart at every document and attention stays inside a document."""
         pc = self.pc
         ids_sb = ids.t().contiguous()                        # [S, B]
-        if isinstance(pos0, (tuple, list)):
+        if doc_start is not None:
+            x = ops.embedding(ids_sb, self.embed_tokens, None, 0, self.vocab_lo, seq_first=True, vocab_total=self.cfg.model.vocab_size)
+            if self.pos_embed is not None and self.vocab_lo == 0:      # the vocabulary-parallel sum adds the positions once
+                S = ids_sb.shape[0]
+                pos = (torch.arange(S, device=ids.device)[None, :] - doc_start.long()).t().clamp_(0, self.pos_embed.shape[0] - 1)
+                x = x + self.pos_embed[pos]
+        elif isinstance(pos0, (tuple, list)):
             # the local sequence is several equal segments of the whole one (zig-zag context parallelism): one offset each
             n = ids_sb.shape[0] // len(pos0)
             x = torch.cat([ops.embedding(ids_sb[i * n:(i + 1) * n].contiguous(), self.embed_tokens, self.pos_embed, int(p0), self.vocab_lo,
@@ -279,9 +299,9 @@ class GPTModel(nn.Module):
             if caches is not None:
                 x, pending = blk(x, pending, caches[i])
             elif self.cfg.bench.activation_checkpointing and self.training:
-                x, pending = torch.utils.checkpoint.checkpoint(blk, x, pending, use_reentrant=False)
+                x, pending = torch.utils.checkpoint.checkpoint(blk, x, pending, None, doc_start, use_reentrant=False)
             else:
-                x, pending = blk(x, pending)
+                x, pending = blk(x, pending, None, doc_start)
         n, _ = self.final_norm(x, pending)
         return n
 
@@ -306,10 +326,10 @@ class GPTModel(nn.Module):
         return tpl.vocab_parallel_logits(n, head, self.pc, gather=True).transpose(0, 1), states
 
     def forward(self, ids: torch.Tensor, targets: Optional[torch.Tensor] = None, pos0: int = 0,
-                loss_denominator: Optional[float] = None, grad_scale: float = 1.0):
+                loss_denominator: Optional[float] = None, grad_scale: float = 1.0, doc_start: Optional[torch.Tensor] = None):
         """Returns logits ``[B, S, V]`` when ``targets`` is None (single-rank only), else the mean
-        cross-entropy over ``targets`` ``[B, S]`` (label smoothing from the config)."""
-        n = self.hidden_states(ids, pos0)
+        cross-entropy over ``targets`` ``[B, S]`` (label smoothing from the config). ``doc_start``: packed sequences."""
+        n = self.hidden_states(ids, pos0, None, doc_start)
         head = self.lm_head if self.lm_head is not None else self.embed_tokens
         if targets is None:
             logits = tpl.vocab_parallel_logits(n, head, self.pc, gather=True)    # [S, B, V]

@@ -70,6 +70,7 @@ class _Lib:
     def load(self) -> ctypes.CDLL:
         if self._dll is not None:
             return self._dll
+        self._check_fresh()
         if not _LIB_PATH.exists():
             raise NativeError(f"native library {_LIB_PATH} is missing: run `python -m elfa_b200.build`")
         dll = ctypes.CDLL(str(_LIB_PATH), mode=os.RTLD_GLOBAL if hasattr(os, "RTLD_GLOBAL") else ctypes.DEFAULT_MODE)
@@ -80,15 +81,45 @@ class _Lib:
                 raise NativeError(f"symbol {name} declared in elfa_native.h is missing from the library")
             fn.argtypes = argt
             fn.restype = ctypes.c_char_p if ret != "int" else ctypes.c_int
-        # the binary must come from the sources next to it: a stale library (sources edited, not rebuilt) is an error
-        if os.environ.get("ELFA_SKIP_HASH_CHECK", "0") != "1":
-            from .build import source_hash
-            built, here = (dll.elfa_source_hash() or b"").decode(), source_hash()
-            if built != here:
-                raise NativeError(f"native library {_LIB_PATH} was built from other sources (library {built[:12]}, sources {here[:12]}): "
-                                  "run `python -m elfa_b200.build`")
         self._dll = dll
         return dll
+
+    def _check_fresh(self) -> None:
+        """The binary must come from the sources next to it. A stale library (sources edited, not rebuilt) is rebuilt when
+        a compiler is at hand - one process at a time, the others wait on a file lock - and is an error otherwise."""
+        if os.environ.get("ELFA_SKIP_HASH_CHECK", "0") == "1":
+            return
+        from . import build as b
+        here = b.source_hash()
+
+        def built() -> str:
+            if not _LIB_PATH.exists():
+                return ""
+            try:
+                probe = ctypes.CDLL(str(_LIB_PATH))
+                probe.elfa_source_hash.restype = ctypes.c_char_p
+                return (probe.elfa_source_hash() or b"").decode()
+            except (OSError, AttributeError):
+                return ""
+        stamp = b.OBJ_DIR / "source_hash.txt"
+        if _LIB_PATH.exists() and stamp.exists() and stamp.read_text().strip() == here:
+            return              # the build step's own record says the library is current (no need to open it twice)
+        if built() == here:
+            return
+        import fcntl
+        b.OUT_DIR.mkdir(parents=True, exist_ok=True)
+        with open(b.OUT_DIR / ".build.lock", "w") as lock:
+            fcntl.flock(lock, fcntl.LOCK_EX)
+            try:
+                if not (stamp.exists() and stamp.read_text().strip() == here and _LIB_PATH.exists()):
+                    try:
+                        b.build()
+                    except RuntimeError as e:
+                        raise NativeError(f"native library {_LIB_PATH} is missing or was built from other sources and could not be "
+                                          f"rebuilt: {e}") from e
+            finally:
+                fcntl.flock(lock, fcntl.LOCK_UN)
+
 
     def last_error(self) -> str:
         return (self.load().elfa_last_error() or b"").decode()

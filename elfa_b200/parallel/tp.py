@@ -50,6 +50,15 @@ def shard_param(full: torch.Tensor, kind: str, tp: int, rank: int) -> torch.Tens
         w = full.shape[1] // parts
         n = w // tp
         return torch.cat([full[:, i * w + rank * n:i * w + (rank + 1) * n] for i in range(parts)], dim=1)
+    if kind.startswith("col_gqa:"):
+        # grouped-query projection [D, (H + 2 Hkv) hd] laid out [Q | K | V]: this rank's query heads and its key / value heads
+        H, Hkv, hd = (int(v) for v in kind.split(":")[1:])
+        bounds = [(0, H * hd), (H * hd, (H + Hkv) * hd), ((H + Hkv) * hd, (H + 2 * Hkv) * hd)]
+        out = []
+        for a, b in bounds:
+            n = (b - a) // tp
+            out.append(full[:, a + rank * n:a + (rank + 1) * n])
+        return torch.cat(out, dim=1)
     raise ValueError(kind)
 
 
@@ -66,6 +75,11 @@ def unshard_param(shards: List[torch.Tensor], kind: str) -> torch.Tensor:
         parts = 3 if kind == "col_qkv" else 2
         n = shards[0].shape[1] // parts
         return torch.cat([torch.cat([s[:, i * n:(i + 1) * n] for s in shards], dim=1) for i in range(parts)], dim=1)
+    if kind.startswith("col_gqa:"):
+        H, Hkv, hd = (int(v) for v in kind.split(":")[1:])
+        nq, nk = H * hd // tp, Hkv * hd // tp
+        cuts = [(0, nq), (nq, nq + nk), (nq + nk, nq + 2 * nk)]
+        return torch.cat([torch.cat([s[:, a:b] for s in shards], dim=1) for a, b in cuts], dim=1)
     raise ValueError(kind)
 
 

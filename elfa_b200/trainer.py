@@ -152,8 +152,15 @@ class Trainer:
             ds = BinaryDataset.open(path)
             shuffle = True
         # the ranks of a context-parallel group read the same batch and keep their slice of the sequence
+        # data.pack_sequences: rows hold documents back to back, each closed by the tokenizer's <eos>; attention and positions
+        # then restart at every document (softmax-attention family without context parallelism; the EFLA family's state
+        # runs through the row as in the reference)
+        pack_eos = None
+        if cfg.data.pack_sequences and cfg.mixer() == "attention" and pc.cp_size == 1:
+            from .data.tokenizer import EOS as EOS_ID
+            pack_eos = EOS_ID if EOS_ID < cfg.model.vocab_size else None
         loader = DataLoader(ds, mb, S, shuffle=shuffle, seed=cfg.runtime.seed, dp_rank=pc.dp_rank // pc.cp_size,
-                            dp_size=pc.dp_size // pc.cp_size)
+                            dp_size=pc.dp_size // pc.cp_size, pack_eos=pack_eos)
         depth = cfg.data.prefetch_factor * cfg.data.num_workers
         if depth > 0:       # data.prefetch_factor x data.num_workers batches are assembled ahead on a worker thread
             from .data.dataset import PrefetchLoader
@@ -184,6 +191,7 @@ class Trainer:
         for b in batches:
             ids = b.input.to(self.device, non_blocking=True)
             tgt = b.target.to(self.device, non_blocking=True)
+            doc = b.doc_start.to(self.device, non_blocking=True) if getattr(b, "doc_start", None) is not None else None
             pos0 = 0
             if self.pc.cp_size > 1 and self.pc.cp_mode == "zigzag":
                 from .parallel.ring_attention import zigzag_slices
@@ -195,11 +203,17 @@ class Trainer:
                 sl = ids.shape[1] // self.pc.cp_size
                 pos0 = self.pc.cp_rank * sl
                 ids, tgt = ids[:, pos0:pos0 + sl].contiguous(), tgt[:, pos0:pos0 + sl].contiguous()
-            denom = float(tgt.numel() * n_micro)
+            # packed rows mask the targets that would cross a document boundary: average over the tokens that count
+            denom = float((int((b.target >= 0).sum()) if doc is not None else tgt.numel()) * n_micro)
+            if self.pc.cp_size > 1:
+                denom = float(tgt.numel() * n_micro)
             if self.zero3:
                 self.flat.before_forward()
             with self.tracer.phase("forward"):
-                loss = self.model(ids, tgt, pos0=pos0, loss_denominator=denom, grad_scale=scale)
+                if doc is not None:
+                    loss = self.model(ids, tgt, pos0=pos0, loss_denominator=denom, grad_scale=scale, doc_start=doc)
+                else:
+                    loss = self.model(ids, tgt, pos0=pos0, loss_denominator=denom, grad_scale=scale)
             with self.tracer.phase("backward"):
                 loss.backward()          # grad_scale is applied inside the loss op's backward
             if self.zero3:

@@ -33,6 +33,8 @@ def small_cfg(dtype, tp, backend, quant="none", quant_backward=None):
     cfg.training.micro_batch_size, cfg.training.global_batch_size = 2, 2
     cfg.runtime.tensor_parallel_size = tp
     cfg.runtime.comm_backend = backend
+    cfg.model.num_kv_heads = int(os.environ.get("ELFA_TEST_KV_HEADS", "4"))
+    cfg.data.pack_sequences = os.environ.get("ELFA_TEST_PACK", "0") == "1"
     cfg.quant.attention = cfg.quant.mlp = quant
     cfg.quant.backward = quant_backward if quant_backward is not None else os.environ.get("ELFA_TEST_QUANT_BACKWARD", "none")
     cfg.checkpoint.dir = ""

@@ -337,3 +337,31 @@ def test_efla_chunk_parallel_form_equals_the_sequential_recurrence(B, T, H, d, C
     assert o2.shape == o.shape and (o - o2).abs().max() < 1e-4 and (s - s2).abs().max() < 1e-4
     for a, b in zip(g_ref, g_chk):
         assert (a - b).abs().max() < 1e-4 * max(1.0, a.abs().max().item())
+
+
+def test_packed_rows_equal_separate_documents_and_gqa_shapes():
+    """A row of two packed documents (doc_start) gives each document the logits it gets on its own; grouped-query
+    attention trains and checkpoints with its [query | key | value] projection."""
+    import os
+    from elfa_b200.config import Config
+    from elfa_b200.models.gpt import GPTModel
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = Config.from_file(os.path.join(root, "configs", "bench", "smoke_cpu.yaml"), env_override=False)
+    cfg.model.dtype = "fp32"
+    cfg.model.num_kv_heads = 2
+    m = GPTModel(cfg, device=torch.device("cpu"))
+    assert m.blocks[0].attn.w_qkv.shape[1] == (cfg.model.num_heads + 2 * 2) * cfg.model.head_dim
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg.model.vocab_size, (1, 48), generator=g)
+    doc = torch.zeros(1, 48, dtype=torch.int32)
+    doc[:, 20:] = 20
+    with torch.no_grad():
+        packed = m.hidden_states(ids, doc_start=doc)
+        first = m.hidden_states(ids[:, :20])
+        second = m.hidden_states(ids[:, 20:])
+    assert torch.allclose(packed[:20], first, atol=1e-5) and torch.allclose(packed[20:], second, atol=1e-5)
+    from elfa_b200.data.packing import document_starts
+    import numpy as np
+    ends = np.zeros((1, 8), dtype=bool)
+    ends[0, 2] = ends[0, 5] = True
+    assert document_starts(ends).tolist() == [[0, 0, 0, 3, 3, 3, 6, 6]]

@@ -31,6 +31,13 @@ def test_tp_sp_with_quantised_backward_matches_single_rank_on_cpu():
     assert "TP_OK" in r.stdout
 
 
+def test_tp_sp_with_grouped_query_attention_and_packed_rows_matches_single_rank_on_cpu():
+    """model.num_kv_heads = 2 under 4 query heads, tensor parallel over 2 ranks (one key head each), data.pack_sequences on."""
+    r = _run(2, ["tp_cpu", "nccl", "fp32"], 29619, extra_env={"ELFA_TEST_KV_HEADS": "2", "ELFA_TEST_PACK": "1"})
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "TP_OK" in r.stdout
+
+
 @pytest.mark.parametrize("world,tp,mode", [(2, 1, "ring"), (4, 2, "ring"), (2, 1, "ulysses"), (2, 1, "zigzag")])
 def test_context_parallel_attention_and_training_on_cpu(world, tp, mode):
     r = _run(world, ["cp_cpu", "nccl", "fp32", str(tp), mode], 29660 + world + {"ring": 0, "ulysses": 10, "zigzag": 20}[mode])

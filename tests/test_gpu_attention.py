@@ -73,3 +73,36 @@ def test_ring_attention_blocks_on_one_gpu(cuda_device, S, B, H, hd, world):
     scale = ref_in.grad.abs().max().item()
     e = (dqkv.float() - ref_in.grad).abs().max().item()
     assert e < 0.03 * max(scale, 1.0) + 0.03, f"max gradient err {e} (grad scale {scale})"
+
+
+def _doc_starts(B, S, dev, seed):
+    """Random document boundaries: ``doc_start[b, s]`` = first position of the document that holds token s."""
+    g = torch.Generator().manual_seed(seed)
+    ds = torch.zeros(B, S, dtype=torch.int32)
+    for b in range(B):
+        cuts = sorted(set(torch.randint(1, S, (max(1, S // 150),), generator=g).tolist()))
+        for c in cuts:
+            ds[b, c:] = c
+    return ds.to(dev)
+
+
+@pytest.mark.parametrize("S,B,H,Hkv,hd", [(256, 2, 4, 2, 64), (384, 1, 8, 2, 128), (200, 1, 4, 1, 32), (1024, 1, 4, 4, 128)])
+@pytest.mark.parametrize("packed", [False, True])
+def test_grouped_query_and_packed_attention(cuda_device, S, B, H, Hkv, hd, packed):
+    """Grouped-query attention (H query heads on Hkv key / value heads) and packed sequences (per-document causal mask
+    with block skipping), forward and backward, against the fp32 formula with repeated key heads / an explicit mask."""
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn((S, B, H + 2 * Hkv, hd), generator=g).to(torch.bfloat16).to(cuda_device).requires_grad_(True)
+    ds = _doc_starts(B, S, cuda_device, 9) if packed else None
+    out = ops.attention(qkv, causal=True, num_heads=H, doc_start=ds)
+    go = torch.randn_like(out)
+    out.backward(go)
+    torch.cuda.synchronize()
+    assert native.status() == 0
+    ref_in = qkv.detach().float().requires_grad_(True)
+    ref = ops.attention_ref(ref_in, causal=True, num_heads=H, doc_start=ds)
+    ref.backward(go.float())
+    assert (out.float() - ref).abs().max().item() < 0.03
+    scale = ref_in.grad.abs().max().item()
+    e = (qkv.grad.float() - ref_in.grad).abs().max().item()
+    assert e < 0.02 * max(scale, 1.0) + 0.02, f"max gradient err {e} (grad scale {scale})"
