@@ -259,7 +259,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
           if (!ok) break;
           tc_fence_after();
           const float m_new = grow ? mx : m;
-          const float alpha = fast_exp2(m - m_new);
+          // a row that has seen no key yet (packed sequences: -inf so far) keeps factor 1: exp2(-inf + inf) would be NaN
+          const float alpha = m_new == m ? 1.f : fast_exp2(m - m_new);
           tmem_ld_wait();                                  // the chunk prefetched for the second pass
 #pragma unroll 1
           for (int c = 0; c < HDP / 32; ++c) {

@@ -200,6 +200,14 @@ class GPTModel(nn.Module):
         if not m.tie_embeddings:
             self.lm_head = nn.Parameter(torch.empty(self.vocab_local, D, dtype=dtype, device=device))
             self.lm_head.tp_shard = ("vocab", tp)
+        if tp > 1 and not self.pc.sequence_parallel:
+            # without sequence parallelism every rank normalises all tokens: the norm parameters get the same full gradient
+            # everywhere (no reduction), unlike the position table, which only the first vocabulary shard adds
+            for mod in self.modules():
+                if isinstance(mod, Norm):
+                    for p in (mod.weight, mod.bias):
+                        if p is not None:
+                            p.tp_replicated, p.tp_identical = False, True
         self.reset_parameters(cfg.runtime.seed)
 
     # ------------------------------------------------------------------ init

@@ -6,10 +6,12 @@ the backward kernels accumulate into it directly (weight-gradient GEMM epilogue,
 embedding scatter-add). One contiguous layout is what lets the optimizer be a handful of kernel
 launches and lets ZeRO shard optimizer state by plain index ranges:
 
-    [ TP-replicated params | TP-sharded params ]  each part ordered (decay, no-decay)
+    [ TP-replicated, partial grads | TP-replicated, identical grads | TP-sharded ]  each part ordered (decay, no-decay)
 
-* the TP-replicated prefix is the only region whose gradients need an all-reduce over the tensor
-  parallel group (norm weights, position embeddings);
+* the first part (``[0, reduce_end)``) is the only region whose gradients need an all-reduce over the tensor
+  parallel group (norm weights and position embeddings under sequence parallelism); the second part holds
+  replicated parameters that every rank differentiates on the same full activations (no reduction); both count
+  once in the gradient norm (``[0, replicated_end)``);
 * ZeRO-1/2 give data-parallel rank ``r`` the slice ``[r * shard, (r+1) * shard)`` of the whole
   buffer (the buffer is padded to a multiple of ``dp * 1024`` elements).
 
@@ -32,7 +34,8 @@ class Segment:
     start: int
     end: int
     weight_decay: bool
-    replicated: bool
+    replicated: bool          # every tensor-parallel rank holds these parameters: their gradient counts once in the norm
+    reduce: bool = False      # ... and each rank holds only a partial gradient: summed over the tensor-parallel group
 
 
 class FlatParams:
@@ -48,9 +51,12 @@ class FlatParams:
         if not items:
             raise ValueError("no trainable parameters")
         # stable sort: replicated first, then decay before no-decay
+        # tensor-parallel classes: 0 = replicated with partial gradients (`tp_replicated`: summed over the group),
+        # 1 = replicated with identical gradients on every rank (`tp_identical`: no reduction), 2 = sharded
         def key(it):
             p = it[1]
-            return (0 if getattr(p, "tp_replicated", False) else 1, 1 if getattr(p, "no_decay", False) or p.dim() < 2 else 0)
+            cls = 0 if getattr(p, "tp_replicated", False) else (1 if getattr(p, "tp_identical", False) else 2)
+            return (cls, 1 if getattr(p, "no_decay", False) or p.dim() < 2 else 0)
         items.sort(key=key)
         self.names = [n for n, _ in items]
         self.params = [p for _, p in items]
@@ -90,12 +96,14 @@ class FlatParams:
             p._grad_fresh = False
             k = key(("", p))
             seg_end = o + (n + ALIGN - 1) // ALIGN * ALIGN
-            if self.segments and self.segments[-1].replicated == (k[0] == 0) and self.segments[-1].weight_decay == (k[1] == 0):
-                self.segments[-1].end = seg_end
+            last = self.segments[-1] if self.segments else None
+            if last is not None and last.replicated == (k[0] < 2) and last.reduce == (k[0] == 0) and last.weight_decay == (k[1] == 0):
+                last.end = seg_end
             else:
-                self.segments.append(Segment(o, seg_end, k[1] == 0, k[0] == 0))
+                self.segments.append(Segment(o, seg_end, k[1] == 0, k[0] < 2, k[0] == 0))
         self.segments[-1].end = self.numel
         self.replicated_end = max((s.end for s in self.segments if s.replicated), default=0)
+        self.reduce_end = max((s.end for s in self.segments if s.reduce), default=0)
         self.shard_size = self.numel // dp_size
         self.shard_lo = dp_rank * self.shard_size
         self.shard_hi = self.shard_lo + self.shard_size

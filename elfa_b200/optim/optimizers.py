@@ -93,8 +93,9 @@ class _Base:
         pc, f = self.pc, self.flat
         if self.presharded:
             return
-        if pc.tp_size > 1 and f.replicated_end > 0:
-            dist.all_reduce(f.grads[:f.replicated_end], group=pc.tp_group)
+        red = getattr(f, "reduce_end", f.replicated_end)
+        if pc.tp_size > 1 and red > 0:
+            dist.all_reduce(f.grads[:red], group=pc.tp_group)
         if self.zero_fused is not None:
             import ctypes
             z = self.zero_fused

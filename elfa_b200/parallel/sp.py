@@ -63,32 +63,81 @@ def ring_exchange(x: torch.Tensor, step: int = 1, group=None) -> torch.Tensor:
     return out
 
 
+class _HaloFromLeft(torch.autograd.Function):
+    """Forward: every rank sends the tail of its block to the right neighbour. Backward: the gradient of what a rank
+    received travels back to the left neighbour and is added to the gradient of that neighbour's tail."""
+
+    @staticmethod
+    def forward(ctx, x_local, width, group, dim):
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        ctx.cfg = (width, group, dim, rank, world, x_local.shape[dim])
+        tail = x_local.narrow(dim, x_local.shape[dim] - width, width).contiguous()
+        if world == 1:
+            return torch.zeros_like(tail)
+        recv = ring_exchange(tail, 1, group)
+        if rank == 0:
+            recv.zero_()
+        return recv
+
+    @staticmethod
+    def backward(ctx, g):
+        width, group, dim, rank, world, n = ctx.cfg
+        g = g.contiguous()
+        dx_tail = torch.zeros_like(g)
+        if world > 1:
+            if rank == 0:
+                g = torch.zeros_like(g)           # rank 0 received nothing it used
+            dx_tail = ring_exchange(g, -1, group)  # what the right neighbour's halo contributed, sent back
+            if rank == world - 1:
+                dx_tail.zero_()                    # nobody read the last rank's tail
+        shape = list(g.shape)
+        shape[dim] = n
+        dx = torch.zeros(shape, dtype=g.dtype, device=g.device)
+        dx.narrow(dim, n - width, width).copy_(dx_tail)
+        return dx, None, None, None
+
+
 def halo_from_left(x_local: torch.Tensor, width: int, group=None, dim: int = 1) -> torch.Tensor:
     """The last ``width`` positions of the left neighbour's block (zeros on rank 0): what a causal
-    convolution of window ``width + 1`` needs in front of the local block."""
-    rank, world = dist.get_rank(group), dist.get_world_size(group)
-    tail = x_local.narrow(dim, x_local.shape[dim] - width, width).contiguous()
-    if world == 1:
-        return torch.zeros_like(tail)
-    recv = ring_exchange(tail, 1, group)
-    if rank == 0:
-        recv.zero_()
-    return recv
+    convolution of window ``width + 1`` needs in front of the local block. Differentiable: in backward the halo's
+    gradient returns to the neighbour it came from (reference: ``src/distributed/sequence_parallel.zig:202-240``
+    ``syncCrossBoundary``, forward only there)."""
+    return _HaloFromLeft.apply(x_local, width, group, dim)
+
+
+class _GatherStack(torch.autograd.Function):
+    """``x`` (same shape on every rank) → ``[world, *x.shape]``; backward sums the ranks' gradients of slice r on rank r."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        world = dist.get_world_size(group)
+        ctx.group = group
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x.contiguous(), group=group)
+        return torch.stack(parts, 0)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous().clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g[dist.get_rank(ctx.group)], None
 
 
 def efla_cross_rank_state(k_local: torch.Tensor, v_local: torch.Tensor, beta: torch.Tensor, group=None) -> torch.Tensor:
     """The true EFLA state at the start of this rank's token block when the sequence is split over
     the group: every rank reduces its block to the affine map ``(A_r, B_r)``, the maps are gathered
-    (``2 * H * d * d`` numbers per rank) and composed in rank order. Returns ``S_in [B, H, d, d]``."""
+    (``2 * H * d * d`` numbers per rank) and composed in rank order. Returns ``S_in [B, H, d, d]``.
+    Differentiable end to end (the maps come out of the scan, whose backward accepts a final-state gradient; the gather's
+    backward returns every map's gradient to the rank that owns it), so a sequence-parallel run trains exactly like a
+    single rank on the whole sequence (reference: ``src/distributed/sequence_parallel.zig:130-159`` ring exchange of
+    activations; the reference has no state hand-off and no backward through it)."""
     from ..ops.efla import chunk_affine_map
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     A, Bm = chunk_affine_map(k_local, v_local, beta)
     if world == 1:
         return torch.zeros_like(Bm)
-    allA = [torch.empty_like(A) for _ in range(world)]
-    allB = [torch.empty_like(Bm) for _ in range(world)]
-    dist.all_gather(allA, A.contiguous(), group=group)
-    dist.all_gather(allB, Bm.contiguous(), group=group)
+    allA = _GatherStack.apply(A, group)
+    allB = _GatherStack.apply(Bm, group)
     S = torch.zeros_like(Bm)
     for r in range(rank):
         S = allA[r] @ S + allB[r]

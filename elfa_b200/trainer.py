@@ -74,9 +74,9 @@ class Trainer:
             pc = (build_context(tp, cfg.runtime.sequence_parallel, cfg.runtime.comm_backend, cp, cfg.runtime.context_parallel_mode)
                   if world > 1 else ParallelContext())
         self.pc = pc
-        if pc.cp_size > 1 and cfg.mixer() != "attention":
-            raise ValueError("runtime.context_parallel_size > 1 splits softmax attention; the EFLA family splits long sequences with "
-                             "EflaModel.forward_sequence_parallel (state hand-off between ranks) instead")
+        if pc.cp_size > 1 and cfg.mixer() != "attention" and pc.cp_mode == "zigzag":
+            raise ValueError("the EFLA family splits a sequence into contiguous blocks (state hand-off from rank to rank): "
+                             "use runtime.context_parallel_mode ring")
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
         self.device = device
@@ -210,7 +210,10 @@ class Trainer:
             if self.zero3:
                 self.flat.before_forward()
             with self.tracer.phase("forward"):
-                if doc is not None:
+                if self.pc.cp_size > 1 and cfg.mixer() == "efla":
+                    # sequence-parallel EFLA: the state and the ShortConv halo cross the ranks inside the model
+                    loss = self.model(ids, tgt, pos0=pos0, loss_denominator=denom, grad_scale=scale, sp_group=self.pc.cp_group)
+                elif doc is not None:
                     loss = self.model(ids, tgt, pos0=pos0, loss_denominator=denom, grad_scale=scale, doc_start=doc)
                 else:
                     loss = self.model(ids, tgt, pos0=pos0, loss_denominator=denom, grad_scale=scale)

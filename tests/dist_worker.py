@@ -331,6 +331,41 @@ def mode_baseline(dev, dtype, tp, stage):
     dist.barrier()
 
 
+def mode_efla_tp(dev, dtype, tp):
+    """The EFLA + PRISM family under tensor parallelism (heads, MLP columns and vocabulary sharded; norms, PRISM and the
+    ShortConv replicated) x data parallelism against one rank on the global batch."""
+    from elfa_b200.parallel.mesh import ParallelContext
+    from elfa_b200.trainer import Trainer
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    world = dist.get_world_size()
+    pc = build_context(tp, True, "nccl")
+
+    def cfg_for(tp_, world_, opt):
+        cfg = Config.from_file(os.path.join(root, "configs", "smoke.yaml"))
+        cfg.model.dtype = dtype
+        cfg.model.num_layers = 2
+        cfg.runtime.tensor_parallel_size, cfg.runtime.world_size = tp_, world_
+        cfg.training.optimizer = opt
+        cfg.training.learning_rate = 1e-3
+        cfg.training.micro_batch_size = 2 if world_ > 1 else 2 * (world // tp)
+        cfg.training.global_batch_size = 2 * (world // tp)
+        cfg.data.path = ""
+        cfg.checkpoint.dir = ""
+        cfg.checkpoint.save_interval = 0
+        cfg.telemetry.log_file = ""
+        return cfg
+    losses = Trainer(cfg_for(tp, world, "lion"), device=dev, pc=pc, telemetry=False).run(max_steps=4)
+    muon = Trainer(cfg_for(tp, world, "lion_muon"), device=dev, pc=pc, telemetry=False).run(max_steps=2)   # shard-wise Newton-Schulz: runs, not compared
+    assert all(x == x for x in muon)
+    if dist.get_rank() == 0:
+        ref = Trainer(cfg_for(1, 1, "lion"), device=dev, pc=ParallelContext(), telemetry=False).run(max_steps=4)
+        tol = 2e-3 if dtype == "fp32" else 0.05
+        for a, b in zip(losses, ref):
+            assert abs(a - b) < tol * max(1.0, abs(b)), f"EFLA TP losses {losses} differ from single-rank {ref}"
+        print(f"EFLA_TP_OK tp={tp} dp={world // tp} losses={[round(x, 4) for x in losses]} ref={[round(x, 4) for x in ref]}")
+    dist.barrier()
+
+
 def mode_mailbox(pc, dev):
     """Ring hand-off through peer mailboxes: several rounds, payload checked against the sender's rank."""
     from elfa_b200 import native
@@ -404,7 +439,7 @@ def main():
     mode = sys.argv[1]
     backend = sys.argv[2] if len(sys.argv) > 2 else "nccl"
     dtype = sys.argv[3] if len(sys.argv) > 3 else "bf16"
-    use_cuda = torch.cuda.is_available() and mode not in ("tp_cpu", "zero_cpu", "ckpt_cpu", "killrank_cpu", "cp_cpu", "hybrid_cpu", "baseline_cpu")
+    use_cuda = torch.cuda.is_available() and mode not in ("tp_cpu", "zero_cpu", "ckpt_cpu", "killrank_cpu", "cp_cpu", "hybrid_cpu", "baseline_cpu", "efla_tp_cpu")
     world = init_distributed("nccl" if use_cuda else "gloo")
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if use_cuda else torch.device("cpu")
     if mode == "killrank_cpu":
@@ -413,6 +448,10 @@ def main():
     if mode == "ckpt_cpu":
         mode_ckpt(dev, int(sys.argv[2]), sys.argv[3], int(sys.argv[4]) if len(sys.argv) > 4 else 1,
                   sys.argv[5] if len(sys.argv) > 5 else "fp32", int(sys.argv[6]) if len(sys.argv) > 6 else None)
+        dist.destroy_process_group()
+        return
+    if mode in ("efla_tp", "efla_tp_cpu"):
+        mode_efla_tp(dev, dtype, int(sys.argv[4]) if len(sys.argv) > 4 else 2)
         dist.destroy_process_group()
         return
     if mode in ("baseline", "baseline_cpu"):

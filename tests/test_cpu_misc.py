@@ -241,6 +241,55 @@ if r == 0: print("SP_MODEL_OK")
     assert r.returncode == 0 and "SP_MODEL_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
 
 
+def test_efla_model_sequence_parallel_training_matches_single_rank(tmp_path):
+    """Sequence-parallel training of the EFLA family: the loss and every parameter gradient (summed over the ranks) equal
+    the single-rank run on the whole sequence - the state hand-off and the ShortConv halo are differentiated through."""
+    code = r'''
+import sys, torch, torch.distributed as dist
+sys.path.insert(0, %r)
+from elfa_b200.config import Config
+from elfa_b200.models.efla_model import EflaModel
+from elfa_b200.parallel import sp
+dist.init_process_group("gloo")
+r, w = dist.get_rank(), dist.get_world_size()
+cfg = Config.from_file(%r, env_override=False)
+cfg.model.dtype = "fp32"
+cfg.model.num_layers = 2
+m = EflaModel(cfg, device=torch.device("cpu"))
+torch.manual_seed(1)
+ids = torch.randint(0, cfg.model.vocab_size, (2, 97))
+inp, tgt = ids[:, :96], ids[:, 1:]
+denom = float(tgt.numel())
+loss_full = m(inp, tgt, loss_denominator=denom)
+loss_full.backward()
+ref = {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None}
+m.zero_grad()
+loss_loc = m(sp.split_sequence(inp, r, w), sp.split_sequence(tgt, r, w), loss_denominator=denom, sp_group=dist.group.WORLD)
+loss_loc.backward()
+tot = loss_loc.detach().clone()
+dist.all_reduce(tot)
+assert abs(float(tot) - float(loss_full)) < 1e-4 * abs(float(loss_full)), (float(tot), float(loss_full))
+worst = 0.0
+for n, p in m.named_parameters():
+    if n not in ref:
+        continue
+    g = p.grad.clone() if p.grad is not None else torch.zeros_like(p)
+    dist.all_reduce(g)
+    e = (g - ref[n]).abs().max().item() / (ref[n].abs().max().item() + 1e-8)
+    worst = max(worst, e)
+    assert e < 2e-3, (n, e)
+dist.barrier()
+if r == 0: print("SP_TRAIN_OK", worst)
+''' % (ROOT, os.path.join(ROOT, "configs", "smoke.yaml"))
+    path = str(tmp_path / "sp_train_worker.py")
+    with open(path, "w") as f:
+        f.write(code)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
+           "--master-port", "29673", path]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES=""))
+    assert r.returncode == 0 and "SP_TRAIN_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
 def test_launcher_runs_a_command_and_resolves_latest_checkpoint(tmp_path):
     from elfa_b200 import launch
     r = subprocess.run([sys.executable, "-m", "elfa_b200.launch", "--gpus", "1", "version"], capture_output=True, text=True, timeout=300,

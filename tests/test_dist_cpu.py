@@ -83,6 +83,13 @@ def test_baseline_arm_under_tensor_and_data_parallelism_matches_the_product_arm(
     assert "BASELINE_OK" in r.stdout
 
 
+@pytest.mark.parametrize("world,tp", [(2, 2), (4, 2)])
+def test_efla_family_tensor_parallel_matches_single_rank_on_cpu(world, tp):
+    r = _run(world, ["efla_tp_cpu", "nccl", "fp32", str(tp)], 29740 + world)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "EFLA_TP_OK" in r.stdout
+
+
 def test_rank_that_leaves_between_steps_is_detected_on_the_host(tmp_path):
     """Host-side fault injection (kill_rank) + heartbeat soft barrier: survivors raise RankFailure, nobody hangs."""
     env = {"ELFA_FAULT": "kill_rank:rank=2,step=3,code=0", "ELFA_HEARTBEAT_DIR": str(tmp_path / "hb"), "ELFA_HEARTBEAT_TIMEOUT_S": "3"}
