@@ -138,7 +138,9 @@ def efla_cross_rank_state(k_local: torch.Tensor, v_local: torch.Tensor, beta: to
         return torch.zeros_like(Bm)
     allA = _GatherStack.apply(A, group)
     allB = _GatherStack.apply(Bm, group)
-    S = torch.zeros_like(Bm)
+    # every rank's result depends (with weight zero where nothing else does) on the gathered maps, so that every rank runs
+    # the gather's backward collective: rank 0 composes nothing and would otherwise skip it
+    S = torch.zeros_like(Bm) + 0.0 * (allA.sum() + allB.sum())
     for r in range(rank):
         S = allA[r] @ S + allB[r]
     return S

@@ -331,24 +331,26 @@ def mode_baseline(dev, dtype, tp, stage):
     dist.barrier()
 
 
-def mode_efla_tp(dev, dtype, tp):
+def mode_efla_tp(dev, dtype, tp, cp=1):
     """The EFLA + PRISM family under tensor parallelism (heads, MLP columns and vocabulary sharded; norms, PRISM and the
     ShortConv replicated) x data parallelism against one rank on the global batch."""
     from elfa_b200.parallel.mesh import ParallelContext
     from elfa_b200.trainer import Trainer
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     world = dist.get_world_size()
-    pc = build_context(tp, True, "nccl")
+    pc = build_context(tp, True, "nccl", cp)
+    replicas = world // tp // cp          # ranks of a context-parallel group share a batch and split its sequences
 
     def cfg_for(tp_, world_, opt):
         cfg = Config.from_file(os.path.join(root, "configs", "smoke.yaml"))
         cfg.model.dtype = dtype
         cfg.model.num_layers = 2
         cfg.runtime.tensor_parallel_size, cfg.runtime.world_size = tp_, world_
+        cfg.runtime.context_parallel_size = cp if world_ > 1 else 1
         cfg.training.optimizer = opt
         cfg.training.learning_rate = 1e-3
-        cfg.training.micro_batch_size = 2 if world_ > 1 else 2 * (world // tp)
-        cfg.training.global_batch_size = 2 * (world // tp)
+        cfg.training.micro_batch_size = 2 if world_ > 1 else 2 * replicas
+        cfg.training.global_batch_size = 2 * replicas
         cfg.data.path = ""
         cfg.checkpoint.dir = ""
         cfg.checkpoint.save_interval = 0
@@ -362,7 +364,7 @@ def mode_efla_tp(dev, dtype, tp):
         tol = 2e-3 if dtype == "fp32" else 0.05
         for a, b in zip(losses, ref):
             assert abs(a - b) < tol * max(1.0, abs(b)), f"EFLA TP losses {losses} differ from single-rank {ref}"
-        print(f"EFLA_TP_OK tp={tp} dp={world // tp} losses={[round(x, 4) for x in losses]} ref={[round(x, 4) for x in ref]}")
+        print(f"EFLA_TP_OK tp={tp} cp={cp} dp={world // tp} losses={[round(x, 4) for x in losses]} ref={[round(x, 4) for x in ref]}")
     dist.barrier()
 
 
@@ -451,7 +453,7 @@ def main():
         dist.destroy_process_group()
         return
     if mode in ("efla_tp", "efla_tp_cpu"):
-        mode_efla_tp(dev, dtype, int(sys.argv[4]) if len(sys.argv) > 4 else 2)
+        mode_efla_tp(dev, dtype, int(sys.argv[4]) if len(sys.argv) > 4 else 2, int(sys.argv[5]) if len(sys.argv) > 5 else 1)
         dist.destroy_process_group()
         return
     if mode in ("baseline", "baseline_cpu"):

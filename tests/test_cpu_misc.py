@@ -255,6 +255,7 @@ r, w = dist.get_rank(), dist.get_world_size()
 cfg = Config.from_file(%r, env_override=False)
 cfg.model.dtype = "fp32"
 cfg.model.num_layers = 2
+cfg.bench.init_std = 0.005      # small keys: with the default init |k|^2 saturates the delta rule (o_t = v_t) and dL/dk is noise
 m = EflaModel(cfg, device=torch.device("cpu"))
 torch.manual_seed(1)
 ids = torch.randint(0, cfg.model.vocab_size, (2, 97))
@@ -270,12 +271,13 @@ tot = loss_loc.detach().clone()
 dist.all_reduce(tot)
 assert abs(float(tot) - float(loss_full)) < 1e-4 * abs(float(loss_full)), (float(tot), float(loss_full))
 worst = 0.0
+scale = max(v.abs().max().item() for v in ref.values())
 for n, p in m.named_parameters():
     if n not in ref:
         continue
     g = p.grad.clone() if p.grad is not None else torch.zeros_like(p)
     dist.all_reduce(g)
-    e = (g - ref[n]).abs().max().item() / (ref[n].abs().max().item() + 1e-8)
+    e = (g - ref[n]).abs().max().item() / (ref[n].abs().max().item() + 1e-6 * scale)
     worst = max(worst, e)
     assert e < 2e-3, (n, e)
 dist.barrier()

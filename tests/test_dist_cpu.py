@@ -83,9 +83,11 @@ def test_baseline_arm_under_tensor_and_data_parallelism_matches_the_product_arm(
     assert "BASELINE_OK" in r.stdout
 
 
-@pytest.mark.parametrize("world,tp", [(2, 2), (4, 2)])
-def test_efla_family_tensor_parallel_matches_single_rank_on_cpu(world, tp):
-    r = _run(world, ["efla_tp_cpu", "nccl", "fp32", str(tp)], 29740 + world)
+@pytest.mark.parametrize("world,tp,cp", [(2, 2, 1), (4, 2, 1), (2, 1, 2), (4, 2, 2)])
+def test_efla_family_tensor_and_sequence_parallel_training_matches_single_rank_on_cpu(world, tp, cp):
+    """Heads sharded over tensor-parallel ranks; with cp > 1 the sequences are split over ranks too (state hand-off and
+    ShortConv halo differentiated through), through the trainer."""
+    r = _run(world, ["efla_tp_cpu", "nccl", "fp32", str(tp), str(cp)], 29740 + world + 10 * cp)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "EFLA_TP_OK" in r.stdout
 
