@@ -135,6 +135,9 @@ int elfa_zero_adamw_allgather(const unsigned long long* peer_params, int rank, i
                               float* m, float* v, const float* reduced, float lr, float beta1, float beta2, float eps, float wd,
                               int step, const void* scalars, long long wd_lo, long long wd_hi, void* stream);
 
+int elfa_zero_pack_bf16(const float* src, void* dst, long long n, void* stream);
+int elfa_zero3_reduce_acc_bf16(const unsigned long long* peer_staged, int world, long long lo, long long n, float* acc, float scale,
+                               void* stream);
 int elfa_zero3_gather(const unsigned long long* peer_shards, int world, long long src_off_bytes, long long shard_bytes, void* dst,
                       void* stream);
 int elfa_zero3_reduce_acc(const unsigned long long* peer_grads, int world, long long lo, long long n, float* acc, float scale,

@@ -118,6 +118,41 @@ __global__ void __launch_bounds__(256) zero3_reduce_acc_kernel(PeerPtrs grads, i
   }
 }
 
+// bf16 on the wire: every rank first rounds its fp32 gradient bucket to bf16 into a peer-addressable staging region
+// (fp32 -> bf16, 8 elements per thread); the owners then sum the peers' bf16 values in fp32, in fixed rank order.
+// NVLink carries 2 bytes per element instead of 4.
+__global__ void __launch_bounds__(256) zero_pack_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n) {
+  const long long nvec = n / 8;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += stride) {
+    const float4 a = reinterpret_cast<const float4*>(src)[2 * v], b = reinterpret_cast<const float4*>(src)[2 * v + 1];
+    reinterpret_cast<uint4*>(dst)[v] = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
+  }
+}
+
+__global__ void __launch_bounds__(256) zero3_reduce_acc_bf16_kernel(PeerPtrs staged, int world, long long lo, long long n,
+                                                                    float* __restrict__ acc, float scale) {
+  const long long nvec = n / 8;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += stride) {
+    float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < world; ++r) {
+      const uint4 q = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(staged.p[r]) + lo + v * 8);
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        s[2 * j] += bf16_lo(w[j]);
+        s[2 * j + 1] += bf16_hi(w[j]);
+      }
+    }
+    float4 a0 = reinterpret_cast<float4*>(acc)[2 * v], a1 = reinterpret_cast<float4*>(acc)[2 * v + 1];
+    a0.x += s[0] * scale; a0.y += s[1] * scale; a0.z += s[2] * scale; a0.w += s[3] * scale;
+    a1.x += s[4] * scale; a1.y += s[5] * scale; a1.z += s[6] * scale; a1.w += s[7] * scale;
+    reinterpret_cast<float4*>(acc)[2 * v] = a0;
+    reinterpret_cast<float4*>(acc)[2 * v + 1] = a1;
+  }
+}
+
 __global__ void zero_sumsq_finish_kernel(const float* __restrict__ part, int P, StepScalarsZ* scal) {
   __shared__ float sm[256];
   float a = 0.f;
@@ -273,6 +308,28 @@ ELFA_API int elfa_zero3_reduce_acc(const unsigned long long* peer_grads, int wor
   PeerPtrs pp{};
   for (int i = 0; i < world; ++i) pp.p[i] = peer_grads[i];
   zero3_reduce_acc_kernel<<<zgrid(n / 4), 256, 0, static_cast<cudaStream_t>(stream)>>>(pp, world, lo, n, acc, scale);
+  ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
+  return ELFA_OK;
+}
+
+// fp32 gradients -> bf16 staging region (what the peers read in elfa_zero3_reduce_acc_bf16). n: multiple of 8.
+ELFA_API int elfa_zero_pack_bf16(const float* src, void* dst, long long n, void* stream) {
+  ELFA_REQUIRE(src && dst && n > 0 && n % 8 == 0, "zero_pack_bf16: bad arguments");
+  ELFA_REQUIRE((reinterpret_cast<uintptr_t>(src) & 15) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0, "zero_pack_bf16: alignment");
+  zero_pack_bf16_kernel<<<zgrid(n / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(src, static_cast<__nv_bfloat16*>(dst), n);
+  ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
+  return ELFA_OK;
+}
+
+// acc[0..n) += scale * sum over ranks of staged_r[lo .. lo+n), staged = the ranks' bf16 staging regions; fp32 sums in rank order.
+ELFA_API int elfa_zero3_reduce_acc_bf16(const unsigned long long* peer_staged, int world, long long lo, long long n, float* acc,
+                                        float scale, void* stream) {
+  ELFA_REQUIRE(peer_staged && acc && world >= 1 && world <= ZMAX && n > 0 && n % 8 == 0 && lo % 8 == 0, "zero3_reduce_acc_bf16: bad arguments");
+  PeerPtrs pp{};
+  for (int i = 0; i < world; ++i) pp.p[i] = peer_staged[i];
+  zero3_reduce_acc_bf16_kernel<<<zgrid(n / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(pp, world, lo, n, acc, scale);
   ELFA_CUDA(cudaGetLastError());
   ::elfa::count_launches(1);
   return ELFA_OK;

@@ -1,4 +1,4 @@
-"""ZeRO stage 3: parameters, gradients and optimizer state sharded over the data-parallel group.
+"""ZeRO stages 2 and 3: gradients and optimizer state (stage 3: parameters too) sharded over the data-parallel group.
 
 At rest every rank holds ``1/dp`` of each bucket of parameters (model dtype), of its fp32 gradient
 and of the optimizer state. A bucket is one transformer block; everything outside the blocks
@@ -12,6 +12,10 @@ and of the optimizer state. A bucket is one transformer block; everything outsid
   current block computes. The block's fp32 gradient is accumulated by the backward kernels in a
   slot of the same shape and reduce-scattered (averaged) into the rank's gradient shard when the
   next block's backward starts.
+* Stage 2 (``shard_params=False``) keeps every block's parameters whole and resident; it shares the gradient path: per-block
+  fp32 gradient slots that are reused once their reduce-scatter has run (the full-size gradient buffer of stages 0 / 1 does
+  not exist), the reduce-scatter of a block issued on a side stream while the next block's backward runs, bf16 on the wire
+  with fp32 sums, and after the update an all-gather of the parameter shards into the resident copies.
 * The optimizer sees only the local shards: :class:`Zero3Shards` has the interface of
   ``optim.flat.FlatParams`` with ``presharded = True`` (no gradient reduction or parameter gather
   in the optimizer; the gradient norm is summed over the group).
@@ -60,14 +64,17 @@ class Zero3Shards:
     symm = None
 
     def __init__(self, model: torch.nn.Module, pc: ParallelContext, blocks: Optional[Iterable[torch.nn.Module]] = None,
-                 grad_dtype: torch.dtype = torch.float32, prefetch: bool = True, arena=None):
+                 grad_dtype: torch.dtype = torch.float32, prefetch: bool = True, arena=None, shard_params: bool = True,
+                 wire_bf16: bool = True):
         """``arena``: a symmetric arena of the data-parallel group. With it the shards and the gradient
         slots live in peer-addressable memory and both collectives are this library's peer-load kernels
         (gather: every rank reads the peers' shards; reduce-scatter: every rank sums its slice of the
         peers' gradient slots in fixed rank order), ordered by signal-word barriers."""
         if pc.tp_size != 1:
-            raise ValueError("ZeRO stage 3 is implemented for pure data parallelism (tensor_parallel_size 1)")
+            raise ValueError("per-block gradient / parameter sharding is implemented for pure data parallelism (tensor_parallel_size 1)")
         self.pc, self.model = pc, model
+        self.shard_params = shard_params
+        self.wire_bf16 = wire_bf16
         self.dp, self.rank = pc.dp_size, pc.dp_rank
         self.group = pc.dp_group
         named = list(model.named_checkpoint_parameters()) if hasattr(model, "named_checkpoint_parameters") else list(model.named_parameters())
@@ -118,7 +125,10 @@ class Zero3Shards:
         self.names = [n for b in self.buckets for n in b.names]
         # full-size slots: two for the blocks, one for the rest
         nslot = max((b.numel for b in self.block_buckets), default=0)
-        self._pslots = [torch.zeros(nslot, dtype=self.dtype, device=self.device) for _ in range(2)] if nslot else []
+        if shard_params:
+            self._pslots = [torch.zeros(nslot, dtype=self.dtype, device=self.device) for _ in range(2)] if nslot else []
+        else:       # stage 2: every block keeps its own whole parameters
+            self._pslots = [torch.zeros(b.numel, dtype=self.dtype, device=self.device) for b in self.block_buckets]
         self._g_regions = []
         if self.arena is not None:
             import ctypes
@@ -131,6 +141,12 @@ class Zero3Shards:
             mk = lambda region: (ctypes.c_uint64 * w)(*[self.arena.peer_address(r, region) for r in range(w)])
             self._peer = {"flat": mk(self._r_flat), "gslot": [mk(r) for r in self._g_regions], "rest_grad": mk(self._r_rest_grad),
                           "flags": mk(flags), "my_flags": flags, "epoch": 0}
+            if wire_bf16:
+                # bf16 staging regions the peers read instead of the fp32 slots (half the NVLink bytes)
+                self._stage = [self.arena.alloc(max(nslot, 8) * 2, f"zero3.stage{j}") for j in range(2)]
+                self._stage_rest = self.arena.alloc(self.rest.numel * 2, "zero3.stage_rest")
+                self._peer["stage"] = [mk(r) for r in self._stage]
+                self._peer["stage_rest"] = mk(self._stage_rest)
             for g in self._gslots:
                 g.zero_()
             rest_grad.zero_()
@@ -138,7 +154,7 @@ class Zero3Shards:
             self._gslots = [torch.zeros(nslot, dtype=grad_dtype, device=self.device) for _ in range(2)] if nslot else []
             rest_grad = torch.zeros(self.rest.numel, dtype=grad_dtype, device=self.device)
         for i, b in enumerate(self.block_buckets):
-            b.full = self._pslots[i % 2][:b.numel]
+            b.full = self._pslots[i % 2][:b.numel] if shard_params else self._pslots[i]
             b.full_grad = self._gslots[i % 2][:b.numel]
             b.slot = i % 2
         self.rest.full = torch.zeros(self.rest.numel, dtype=self.dtype, device=self.device)
@@ -151,13 +167,16 @@ class Zero3Shards:
                 for p, o in zip(b.params, b.offsets):
                     tmp[o:o + p.numel()].copy_(p.data.reshape(-1))
                 self.flat[b.base:b.base + b.shard].copy_(tmp[self.rank * b.shard:(self.rank + 1) * b.shard])
+                if not shard_params:
+                    b.full.copy_(tmp)
                 for p, o in zip(b.params, b.offsets):
                     p.data = b.full[o:o + p.numel()].view(p.shape)
                     p.main_grad = b.full_grad[o:o + p.numel()].view(p.shape)
                     p._grad_fresh = False
         self.side = torch.cuda.Stream(self.device) if (self.cuda and prefetch) else None
         self._pending_rs: List[_Bucket] = []
-        self._rest_valid = False
+        self._slot_free = {}          # gradient slot -> event of the reduce-scatter that last read it (side stream)
+        self._rest_valid = not shard_params
         self.gathers = 0          # statistics (tests)
         self.reduce_scatters = 0
         for i, b in enumerate(self.block_buckets):
@@ -227,10 +246,18 @@ class Zero3Shards:
         elif self.arena is not None:
             import ctypes
             from ..native import lib, stream_ptr
-            self._barrier()               # every rank's gradient of this bucket is complete and visible
-            peers = self._peer["rest_grad"] if b.slot < 0 else self._peer["gslot"][b.slot]
-            lib.call("elfa_zero3_reduce_acc", ctypes.addressof(peers), self.dp, self.rank * b.shard, b.shard, dst, 1.0 / self.dp,
-                     stream_ptr(dst))
+            if self.wire_bf16:
+                stage = self._stage_rest if b.slot < 0 else self._stage[b.slot]
+                lib.call("elfa_zero_pack_bf16", b.full_grad, stage.tensor, b.numel, stream_ptr(dst))
+                self._barrier()           # every rank's staged gradient of this bucket is complete and visible
+                peers = self._peer["stage_rest"] if b.slot < 0 else self._peer["stage"][b.slot]
+                lib.call("elfa_zero3_reduce_acc_bf16", ctypes.addressof(peers), self.dp, self.rank * b.shard, b.shard, dst,
+                         1.0 / self.dp, stream_ptr(dst))
+            else:
+                self._barrier()           # every rank's gradient of this bucket is complete and visible
+                peers = self._peer["rest_grad"] if b.slot < 0 else self._peer["gslot"][b.slot]
+                lib.call("elfa_zero3_reduce_acc", ctypes.addressof(peers), self.dp, self.rank * b.shard, b.shard, dst, 1.0 / self.dp,
+                         stream_ptr(dst))
         elif self.cuda:
             out = torch.empty_like(dst)
             dist.reduce_scatter_tensor(out, b.full_grad, op=dist.ReduceOp.AVG, group=self.group)
@@ -241,16 +268,33 @@ class Zero3Shards:
             dst.add_(g[self.rank * b.shard:(self.rank + 1) * b.shard] / self.dp)
 
     def _flush_pending(self) -> None:
+        """Reduce-scatters the blocks whose backward has finished. On a GPU the collective runs on the side stream, next to
+        the following block's backward; the slot's next user waits for the event recorded here."""
         for b in self._pending_rs:
-            self._reduce_scatter(b)
+            if self.side is not None and self.dp > 1:
+                self.side.wait_stream(torch.cuda.current_stream(self.device))      # the block's gradient is complete
+                with torch.cuda.stream(self.side):
+                    self._reduce_scatter(b)
+                    ev = torch.cuda.Event()
+                    ev.record(self.side)
+                self._slot_free[b.slot] = ev
+            else:
+                self._reduce_scatter(b)
             b.state = "sharded"
         self._pending_rs = []
+
+    def _wait_slot(self, slot: int) -> None:
+        ev = self._slot_free.pop(slot, None)
+        if ev is not None:
+            torch.cuda.current_stream(self.device).wait_event(ev)
 
     # ------------------------------------------------------------------ hooks on the blocks
     def _hook(self, i: int, b: _Bucket) -> None:
         blocks = self.block_buckets
 
         def pre_forward(module, args):
+            if not self.shard_params:
+                return                      # stage 2: the parameters are resident
             if b.state == "sharded":
                 self._gather(b, "fwd")
             self._wait(b)
@@ -259,16 +303,21 @@ class Zero3Shards:
                 self._gather(blocks[i + 1], "fwd", asynchronous=True)
 
         def post_forward(module, args, out):
+            if not self.shard_params:
+                return
             if b.state == "fwd":
                 b.state = "sharded"         # the slot may be overwritten; backward gathers again
 
         def pre_backward(module, grad_out):
             self._flush_pending()
             if b.state != "bwd":
-                if b.state == "sharded":
+                if b.state == "sharded" and self.shard_params:
                     self._gather(b, "bwd")
                 b.state = "bwd"
+                self._wait_slot(b.slot)     # the reduce-scatter that last read this gradient slot has finished
                 b.full_grad.zero_()
+            if not self.shard_params:
+                return
             self._wait(b)
             if i - 1 >= 0 and blocks[i - 1].state == "sharded":
                 self._gather(blocks[i - 1], "bwd_prefetched", asynchronous=True)
@@ -285,7 +334,7 @@ class Zero3Shards:
     # ------------------------------------------------------------------ step protocol (called by the trainer / optimizer)
     def before_forward(self) -> None:
         """Makes the ``rest`` bucket valid (once per optimizer step) and resets block states."""
-        if not self._rest_valid:
+        if not self._rest_valid and self.shard_params:
             self._gather_into(self.rest)
             self._rest_valid = True
         for b in self.block_buckets:
@@ -300,6 +349,7 @@ class Zero3Shards:
             b.ready = None
         if self.side is not None:
             torch.cuda.current_stream(self.device).wait_stream(self.side)
+            self._slot_free.clear()
         if self.arena is not None and self.dp > 1:
             # the last reduce-scatter of this micro-batch read the peers' gradient slots: nobody may zero or refill a slot
             # for the next micro-batch before every rank has finished that read
@@ -309,6 +359,10 @@ class Zero3Shards:
         """Called by the optimizer before the update: the ``rest`` gradient (accumulated over all
         micro-batches in its full-size buffer) is reduce-scattered now."""
         self._flush_pending()
+        if self.side is not None:
+            # barriers are counted: the ones issued on the side stream must run before the next one on this stream
+            torch.cuda.current_stream(self.device).wait_stream(self.side)
+            self._slot_free.clear()
         self._reduce_scatter(self.rest)
         self.rest.full_grad.zero_()
 
@@ -316,6 +370,13 @@ class Zero3Shards:
         self._rest_valid = False
         if self.arena is not None and self.dp > 1:
             self._barrier()               # all shards updated before anyone gathers them again
+        if not self.shard_params:
+            # stage 2: the updated shards go back into every rank's resident parameters
+            for b in self.buckets:
+                self._gather_into(b)
+            self._rest_valid = True
+            if self.arena is not None and self.dp > 1:
+                self._barrier()           # nobody updates its shards again while a peer still reads them
 
     def zero_grad(self) -> None:
         self.grads.zero_()
@@ -365,7 +426,7 @@ class Zero3Shards:
             if b is not self.rest:
                 b.state = "sharded"
         self._rest_valid = True
-        return out
+        return out if self.shard_params else [(n, t) for n, t in out]
 
     @torch.no_grad()
     def load_full(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -380,7 +441,9 @@ class Zero3Shards:
                     raise ValueError(f"tensor '{n}': checkpoint shape {tuple(t.shape)} != model shape {tuple(p.shape)}")
                 tmp[o:o + p.numel()].copy_(t.reshape(-1).to(self.device, self.dtype))
             self.flat[b.base:b.base + b.shard].copy_(tmp[self.rank * b.shard:(self.rank + 1) * b.shard])
-        self._rest_valid = False
+            if not self.shard_params:
+                b.full.copy_(tmp)
+        self._rest_valid = not self.shard_params
 
     def logical_state(self, v: torch.Tensor, lo: int, hi: int, pc) -> Dict[str, torch.Tensor]:
         """One optimizer-state buffer (laid out like the local shards) as full per-parameter host tensors (collective)."""
@@ -414,5 +477,8 @@ class Zero3Shards:
     def memory_report(self) -> Dict[str, int]:
         esz = self.flat.element_size()
         full = sum(b.numel for b in self.buckets)
-        return {"param_bytes_at_rest": self.numel * esz, "param_bytes_unsharded": full * esz,
-                "transient_bytes": (sum(s.numel() for s in self._pslots) + self.rest.numel) * esz}
+        gslots = sum(g.numel() for g in self._gslots) + self.rest.numel
+        return {"param_bytes_at_rest": (self.numel if self.shard_params else full + self.numel) * esz, "param_bytes_unsharded": full * esz,
+                "transient_bytes": ((sum(s.numel() for s in self._pslots) if self.shard_params else 0) + self.rest.numel) * esz,
+                # fp32 gradient memory: this rank's shard plus the reusable block slots, against one full-size buffer
+                "grad_bytes": (self.numel + gslots) * 4, "grad_bytes_unsharded": full * 4}

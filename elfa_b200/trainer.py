@@ -87,12 +87,18 @@ class Trainer:
         self.model = build_model(cfg, pc, device)
         self.model.train()
         dp_arena = None
-        if (pc.dp_size > 1 and cfg.runtime.zero_stage in (1, 2) and pc.comm_backend == "fused" and device.type == "cuda"
+        blockwise2 = (cfg.runtime.zero_stage == 2 and pc.tp_size == 1 and pc.cp_size == 1 and cfg.training.optimizer in ("adamw", "lion"))
+        if (pc.dp_size > 1 and cfg.runtime.zero_stage in (1, 2) and not blockwise2 and pc.comm_backend == "fused" and device.type == "cuda"
                 and cfg.model.dtype != "fp32"):
             from .runtime.symm import SymmetricArena
             n_est = sum(p.numel() + 64 for p in self.model.parameters()) + pc.dp_size * 1024
             dp_arena = SymmetricArena.for_group(pc.dp_group, device, n_est * 6 + (16 << 20))
-        if cfg.runtime.zero_stage == 3 and pc.dp_size > 1:
+        # stage 3 shards parameters, gradients and optimizer state per block; stage 2 shares its gradient path (reusable
+        # per-block gradient slots, reduce-scatter per block next to backward) with resident parameters. Both need pure data
+        # parallelism and an element-wise optimizer; otherwise stage 2 keeps the stage-1 mechanism (full gradient buffer)
+        blockwise = cfg.runtime.zero_stage == 3 or (cfg.runtime.zero_stage == 2 and pc.tp_size == 1 and pc.cp_size == 1
+                                                   and cfg.training.optimizer in ("adamw", "lion"))
+        if blockwise and pc.dp_size > 1:
             from .parallel.zero3 import Zero3Shards
             arena3 = None
             if pc.comm_backend == "fused" and device.type == "cuda" and pc.tp_size == 1:
@@ -100,8 +106,9 @@ class Trainer:
                 n_est = sum(p.numel() + 64 for p in self.model.parameters())
                 esz = 2 if cfg.model.dtype != "fp32" else 4
                 per_block = n_est // max(cfg.model.num_layers, 1) + (1 << 20)
-                arena3 = SymmetricArena.for_group(pc.dp_group, device, n_est * esz // pc.dp_size + 3 * per_block * 4 + n_est * 4 // 4 + (64 << 20))
-            self.flat = Zero3Shards(self.model, pc, arena=arena3)
+                arena3 = SymmetricArena.for_group(pc.dp_group, device, n_est * esz // pc.dp_size + 3 * per_block * 4 + n_est * 4 // 4 +
+                                                     2 * per_block * 2 + n_est * 2 // 4 + (64 << 20))
+            self.flat = Zero3Shards(self.model, pc, arena=arena3, shard_params=cfg.runtime.zero_stage == 3)
         else:
             self.flat = FlatParams(self.model.named_checkpoint_parameters(), dp_size=pc.dp_size, dp_rank=pc.dp_rank, allocator=dp_arena)
         self.zero3 = bool(getattr(self.flat, "presharded", False))

@@ -198,13 +198,21 @@ def mode_zero(dev, backend, dtype, stage):
     world = pc.dp_size
     cfg = small_cfg(dtype, 1, backend)
     cfg.runtime.zero_stage = stage
-    accum = 2 if stage == 3 else 1            # stage 3 also covers gradient accumulation over micro-batches
+    accum = 2 if stage >= 2 else 1            # stages 2 and 3 also cover gradient accumulation over micro-batches
     cfg.training.micro_batch_size = 2
     cfg.training.global_batch_size = 2 * world * accum
     tr = Trainer(cfg, device=dev, pc=pc, telemetry=False)
     losses = tr.run(max_steps=4)
     if dev.type == "cuda":
         assert native.status() == 0
+    if stage == 2:
+        # real gradient sharding: no full-size fp32 gradient buffer, two reusable block slots + the shard instead; parameters whole
+        rep = tr.flat.memory_report()
+        nb = len(tr.flat.block_buckets)
+        assert tr.zero3 and not tr.flat.shard_params and rep["param_bytes_at_rest"] >= rep["param_bytes_unsharded"], rep
+        if nb >= 4:
+            assert rep["grad_bytes"] < rep["grad_bytes_unsharded"], rep
+        assert tr.flat.reduce_scatters == 4 * (accum * nb + 1), tr.flat.reduce_scatters
     if stage == 3:
         rep = tr.flat.memory_report()
         assert tr.zero3 and rep["param_bytes_at_rest"] * world <= rep["param_bytes_unsharded"] + 4096 * world, rep

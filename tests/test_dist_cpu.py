@@ -52,14 +52,14 @@ def test_tensor_parallel_times_data_parallel_zero2_mixed_quant_on_cpu():
     assert "HYBRID_OK tp=2 dp=2" in r.stdout
 
 
-@pytest.mark.parametrize("stage", [0, 1, 3])
+@pytest.mark.parametrize("stage", [0, 1, 2, 3])
 def test_zero_data_parallel_matches_single_rank_on_cpu(stage):
     r = _run(2, ["zero_cpu", "nccl", "fp32", str(stage)], 29621 + stage)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "ZERO_OK" in r.stdout
 
 
-@pytest.mark.parametrize("stage", [1, 3])
+@pytest.mark.parametrize("stage", [1, 2, 3])
 def test_sharded_optimizer_state_survives_checkpoint(stage, tmp_path):
     r = _run(2, ["ckpt_cpu", str(stage), str(tmp_path / "ck")], 29641 + stage)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]

@@ -90,6 +90,17 @@ def test_zero3_parameter_sharding_matches_single_gpu(cuda_device, backend):
         assert "peer_kernels=True" in r.stdout
 
 
+@pytest.mark.parametrize("backend", ["nccl", "fused"])
+def test_zero2_gradient_sharding_matches_single_gpu(cuda_device, backend):
+    """Stage 2: whole parameters, per-block gradient slots reduce-scattered (bf16 on the wire, side stream) into fp32 shards,
+    parameter shards all-gathered after the update; two micro-batches per step."""
+    r = _run(["zero", backend, "bf16", "2"], 29714 if backend == "nccl" else 29715)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "ZERO_OK stage=2" in r.stdout
+    if backend == "fused":
+        assert "peer_kernels=True" in r.stdout
+
+
 def test_ring_handoff_through_peer_mailboxes(cuda_device):
     r = _run(["mailbox"], 29709)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
