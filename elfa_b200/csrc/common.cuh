@@ -33,6 +33,7 @@ void set_last_error(const char* msg);
 int cuda_fail(cudaError_t e, const char* what);
 unsigned int* status_word();   // device pointer to this device's status word (lazily created)
 void count_launches(int n);    // bookkeeping: kernels launched by this library (read by elfa_launch_count)
+bool deterministic_mode();     // runtime.deterministic: fixed summation orders only (set by elfa_set_deterministic)
 
 #define ELFA_CUDA(call)                                   \
   do {                                                    \

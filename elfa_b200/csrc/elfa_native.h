@@ -21,6 +21,7 @@ extern "C" {
 
 const char* elfa_last_error(void);
 int elfa_version(void);
+int elfa_set_deterministic(int on);
 // SHA-256 (hex) over the sources this library was built from; the Python side compares it with the sources it finds
 const char* elfa_source_hash(void);
 long long elfa_launch_count(int reset);
@@ -125,6 +126,10 @@ int elfa_gemm_ag_mxfp8(const unsigned long long* peer_buf, const unsigned long l
 int elfa_gemm_rs(const void* A, long long lda, const void* B, long long ldb, int b_mn_major, int M, int N, int K,
                  const unsigned long long* peer_recv, const unsigned long long* peer_flags, const void* my_flags,
                  unsigned int* arrivals_io, void* out, long long ld_out, int rank, int world, int wait_ms, int max_ctas, void* stream);
+
+// ---- multimem.cu (NVLS: reductions inside the NVSwitch through the arena's multicast mapping) ------------------
+int elfa_multimem_collective(unsigned long long mc, const void* local, void* out, long long off_bytes, long long n, int dtype,
+                             int rank, int world, float scale, int mode, void* stream);
 
 // ---- zero.cu -----------------------------------------------------------------------------------
 int elfa_symm_barrier(const unsigned long long* peer_flags, const void* my_flags, int rank, int world, unsigned int epoch,

@@ -841,7 +841,7 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, in
   if (TWO) max_ctas /= 2;    // work slots are CTA pairs
   const int num_kb_host = (p.K + BK - 1) / BK;
   p.splits = 1;
-  if (COMM == COMM_NONE && (p.flags & (ELFA_EPI_ACCUM | ELFA_EPI_OUT_F32)) == (ELFA_EPI_ACCUM | ELFA_EPI_OUT_F32)) {
+  if (COMM == COMM_NONE && !deterministic_mode() && (p.flags & (ELFA_EPI_ACCUM | ELFA_EPI_OUT_F32)) == (ELFA_EPI_ACCUM | ELFA_EPI_OUT_F32)) {
     // fp32 accumulate outputs (weight gradients): split K when the tile count fills the SMs badly
     const int t = p.tiles_m * p.tiles_n;
     auto eff = [&](int sp) { const int u = t * sp; return (double)u / (double)(((u + max_ctas - 1) / max_ctas) * max_ctas); };

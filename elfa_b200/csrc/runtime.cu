@@ -22,6 +22,9 @@ int cuda_fail(cudaError_t e, const char* what) {
 static std::atomic<long long> g_launches{0};
 void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+static std::atomic<int> g_deterministic{0};
+bool deterministic_mode() { return g_deterministic.load(std::memory_order_relaxed) != 0; }
+
 static std::mutex g_mu;
 static unsigned int* g_status[64] = {nullptr};
 
@@ -126,6 +129,12 @@ using namespace elfa;
 ELFA_API const char* elfa_last_error() { return g_last_error.c_str(); }
 
 ELFA_API int elfa_version() { return 100; }
+
+// runtime.deterministic: kernels choose a fixed summation order (the GEMM does not split the contraction across CTAs)
+ELFA_API int elfa_set_deterministic(int on) {
+  elfa::g_deterministic.store(on ? 1 : 0, std::memory_order_relaxed);
+  return ELFA_OK;
+}
 
 #ifndef ELFA_SOURCE_HASH
 #define ELFA_SOURCE_HASH "unknown"

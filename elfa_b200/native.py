@@ -158,6 +158,22 @@ def status() -> int:
     return int(out.value)
 
 
+_deterministic = False
+
+
+def set_deterministic(on: bool) -> None:
+    """``runtime.deterministic``: fixed summation orders only - the GEMM stops splitting contractions across CTAs (fp32
+    atomics) and the embedding gradient is reduced over sorted token ids instead of scattered with atomics."""
+    global _deterministic
+    _deterministic = bool(on)
+    if lib.available():
+        lib.call("elfa_set_deterministic", int(bool(on)))
+
+
+def deterministic() -> bool:
+    return _deterministic
+
+
 def check_status() -> None:
     st = status()
     if st & (ST_MBAR_TIMEOUT | ST_FLAG_TIMEOUT):

@@ -273,8 +273,26 @@ class _Embedding(torch.autograd.Function):
                     dpos_buf.zero_()
             else:
                 dpos_buf = dpos_ret = torch.zeros(pos.shape, dtype=torch.float32, device=dy.device)
-        lib.call("elfa_embedding_bwd", idc, dyc, dtok_buf, dpos_buf, B * T, D, T, B if seq_first else 1, pos0, vocab_lo,
-                 vocab_lo + vloc, 1, stream_ptr(dyc))
+        from .. import native
+        if native.deterministic():
+            # runtime.deterministic: no atomics. Rows of dy are grouped by token id (stable sort) and summed per group in a
+            # fixed order; positions likewise (every position gets one row per batch entry).
+            local = idc - vocab_lo
+            keep = (local >= 0) & (local < vloc)
+            dy2 = dyc.view(B * T, D)
+            order = torch.argsort(torch.where(keep, local, torch.full_like(local, vloc)), stable=True)
+            srt = local[order]
+            nkeep = int(keep.sum())
+            if nkeep:
+                uniq, counts = torch.unique_consecutive(srt[:nkeep], return_counts=True)
+                sums = torch.segment_reduce(dy2[order[:nkeep]].float(), "sum", lengths=counts)
+                dtok_buf.index_put_((uniq,), dtok_buf[uniq] + sums)
+            if dpos_buf is not None and vocab_lo == 0:
+                per_pos = dy2.view(T, B, D).float().sum(1) if seq_first else dy2.view(B, T, D).float().sum(0)
+                dpos_buf[pos0:pos0 + T] += per_pos
+        else:
+            lib.call("elfa_embedding_bwd", idc, dyc, dtok_buf, dpos_buf, B * T, D, T, B if seq_first else 1, pos0, vocab_lo,
+                     vocab_lo + vloc, 1, stream_ptr(dyc))
         if dtok_ret is not None:
             dtok_ret = dtok_ret.to(tok.dtype)
         if dpos_ret is not None:

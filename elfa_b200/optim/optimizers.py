@@ -72,6 +72,13 @@ class _Base:
             }
             self.gshard = torch.zeros(n, dtype=torch.float32, device=dev)
             arena.barrier()
+        # unsharded data parallel with the gradient buffer in an arena that has a multicast mapping (ELFA_NVLS=1): the gradient
+        # all-reduce is one in-switch reduction pass (parallel/nvls.py) instead of the library call
+        self.nvls = None
+        if (not self.sharded and not self.presharded and zf is not None and self.pc.dp_size > 1 and flat.flat.is_cuda
+                and self.pc.comm_backend == "fused" and getattr(zf[0], "multicast_ptr", 0)):
+            from ..parallel.nvls import MultimemGroup
+            self.nvls = MultimemGroup(zf[0])
 
     # --------------------------------------------------------------- gradient synchronisation
     def _symm_barrier(self) -> None:
@@ -102,6 +109,9 @@ class _Base:
             self._symm_barrier()          # every rank's gradients are complete and visible
             lib.call("elfa_zero_reduce", ctypes.addressof(z["peer_grads"]), pc.dp_rank, pc.dp_size, self.lo, self.hi - self.lo,
                      self.gshard, 1.0 / pc.dp_size, self.part, self.scalars, stream_ptr(f.grads))
+            return
+        if pc.dp_size > 1 and self.nvls is not None:
+            self.nvls.all_reduce_(f.symm[2], f.numel, torch.float32, 1.0 / pc.dp_size)
             return
         if pc.dp_size > 1:
             if self.sharded and f.grads.is_cuda:

@@ -21,6 +21,8 @@ import torch
 import torch.distributed as dist
 
 ALIGN = 1024     # bytes
+CANARY = 0xE1FAB200E1FAB200 - (1 << 64)     # guard word (as int64) written behind every region
+GUARD = 1024     # bytes of guard words behind every region (the arena's allocation quantum)
 
 
 @dataclass
@@ -59,9 +61,12 @@ class SymmetricArena:
         self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
         self.handle = symm_mem.rendezvous(self.buf, self.group)
         self.peer_ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
+        # multicast address of the arena (0 when the fabric has no NVLS or ELFA_NVLS is not 1): the multimem kernels' operand
+        self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0) if os.environ.get("ELFA_NVLS", "0") == "1" else 0
         assert self.peer_ptrs[self.rank] == self.buf.data_ptr()
         self.buf.zero_()
         self._cursor = 0
+        self._guards: List[Tuple[int, str]] = []
         self._named: Dict[str, Region] = {}
         self.epochs: Dict[str, int] = {}
         # device copy of the peer base addresses (kernels index it by rank)
@@ -91,13 +96,29 @@ class SymmetricArena:
                 raise RuntimeError(f"symmetric region '{name}' was created with {r.nbytes} bytes, {nbytes} requested")
             return r
         size = (nbytes + ALIGN - 1) // ALIGN * ALIGN
-        if self._cursor + size > self.nbytes:
+        if self._cursor + size + GUARD > self.nbytes:
             raise MemoryError(f"symmetric arena exhausted ({self._cursor} + {size} > {self.nbytes}); set ELFA_SYMM_BYTES")
         r = Region(self._cursor, size, self.buf[self._cursor:self._cursor + size])
         self._cursor += size
+        # guard words behind the region: a kernel (this rank's or a peer's) that writes past a region's end lands here first
+        g = self.buf[self._cursor:self._cursor + GUARD].view(torch.int64)
+        g.fill_(CANARY)
+        self._guards.append((self._cursor, name or f"region@{r.offset}"))
+        self._cursor += GUARD
         if name is not None:
             self._named[name] = r
         return r
+
+    def check_canaries(self) -> List[str]:
+        """Names of the regions whose guard words were overwritten (synchronises the device). The stand-in for a memory
+        checker on the peer-addressable memory, where an out-of-range store from another GPU would otherwise go unnoticed
+        (reference: ``scripts/profile.sh:43-57`` runs compute-sanitizer memcheck / racecheck instead)."""
+        torch.cuda.synchronize(self.device)
+        bad = []
+        for off, name in self._guards:
+            if not bool((self.buf[off:off + GUARD].view(torch.int64) == CANARY).all()):
+                bad.append(name)
+        return bad
 
     def peer_address(self, rank: int, region: Region) -> int:
         return self.peer_ptrs[rank] + region.offset

@@ -81,6 +81,9 @@ class Trainer:
             device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
         self.device = device
         torch.manual_seed(cfg.runtime.seed)
+        if device.type == "cuda":
+            from . import native
+            native.set_deterministic(cfg.runtime.deterministic)
         if pc.comm_backend == "fused" and device.type == "cuda" and pc.tp_size > 1 and pc.symm is None:
             from .runtime.symm import SymmetricArena
             pc.symm = SymmetricArena.for_group(pc.tp_group, device)
@@ -88,8 +91,9 @@ class Trainer:
         self.model.train()
         dp_arena = None
         blockwise2 = (cfg.runtime.zero_stage == 2 and pc.tp_size == 1 and pc.cp_size == 1 and cfg.training.optimizer in ("adamw", "lion"))
-        if (pc.dp_size > 1 and cfg.runtime.zero_stage in (1, 2) and not blockwise2 and pc.comm_backend == "fused" and device.type == "cuda"
-                and cfg.model.dtype != "fp32"):
+        nvls0 = cfg.runtime.zero_stage == 0 and os.environ.get("ELFA_NVLS", "0") == "1"     # in-switch gradient all-reduce
+        if (pc.dp_size > 1 and ((cfg.runtime.zero_stage in (1, 2) and not blockwise2) or nvls0) and pc.comm_backend == "fused"
+                and device.type == "cuda" and cfg.model.dtype != "fp32"):
             from .runtime.symm import SymmetricArena
             n_est = sum(p.numel() + 64 for p in self.model.parameters()) + pc.dp_size * 1024
             dp_arena = SymmetricArena.for_group(pc.dp_group, device, n_est * 6 + (16 << 20))

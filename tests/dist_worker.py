@@ -103,6 +103,9 @@ def mode_fused(pc, dev):
     st = native.status()
     assert st == 0, f"device status 0x{st:x}"
     dist.barrier()
+    bad = pc.symm.check_canaries()          # nobody (this rank or a peer) wrote past the end of a ring slot or a flag region
+    assert not bad, f"guard words overwritten behind {bad}"
+    dist.barrier()
     if rank == 0:
         print(f"FUSED_OK worst_rs_err={worst:.4f}")
 
@@ -232,7 +235,7 @@ def mode_zero(dev, backend, dtype, stage):
         for a, b in zip(losses, ref):
             assert abs(a - b) < tol * max(1.0, abs(b)), f"ZeRO losses {losses} differ from single-rank {ref}"
         print(f"ZERO_OK stage={stage} backend={backend} fused={tr.optimizer.zero_fused is not None} "
-              f"peer_kernels={getattr(tr.flat, 'arena', None) is not None} "
+              f"peer_kernels={getattr(tr.flat, 'arena', None) is not None} nvls={getattr(tr.optimizer, 'nvls', None) is not None} "
               f"losses={[round(x, 4) for x in losses]} ref={[round(x, 4) for x in ref]}")
     dist.barrier()
 
@@ -376,6 +379,56 @@ def mode_efla_tp(dev, dtype, tp, cp=1):
     dist.barrier()
 
 
+def mode_multimem(pc, dev):
+    """In-switch collectives (multimem.ld_reduce / multimem.st) against the library's, fp32 and bf16."""
+    from elfa_b200 import native
+    from elfa_b200.parallel.nvls import MultimemGroup
+    from elfa_b200.runtime.symm import SymmetricArena
+    arena = SymmetricArena.for_group(pc.tp_group, dev, 256 << 20)
+    world, rank = arena.world, arena.rank
+    if not arena.multicast_ptr:
+        if rank == 0:
+            print("MULTIMEM_SKIPPED no multicast mapping on this machine")
+        dist.barrier()
+        return
+    mm = MultimemGroup(arena)
+    n = world * 1024 * 257
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+        esz = 4 if dtype == torch.float32 else 2
+        reg = arena.alloc(n * esz, f"mm.test.{esz}")
+        x = reg.view(dtype, (n,))
+        g = torch.Generator(device="cpu").manual_seed(7 + rank)
+        mine = torch.randn(n, generator=g).to(dtype).to(dev)
+        ref = mine.float().clone()
+        dist.all_reduce(ref, group=pc.tp_group)
+        for _ in range(2):      # twice: the barrier words are counted, not reset
+            x.copy_(mine)
+            mm.all_reduce_(reg, n, dtype, 0.5)
+            torch.cuda.synchronize()
+            e = (x.float() - 0.5 * ref).abs().max().item()
+            assert e <= tol * ref.abs().max().item(), f"multimem all-reduce {dtype}: {e}"
+        x.copy_(mine)
+        out = torch.empty(n // world, dtype=dtype, device=dev)
+        mm.reduce_scatter(reg, n, out, dtype)
+        torch.cuda.synchronize()
+        per = n // world
+        e = (out.float() - ref[rank * per:(rank + 1) * per]).abs().max().item()
+        assert e <= tol * ref.abs().max().item(), f"multimem reduce-scatter {dtype}: {e}"
+        x.copy_(mine)
+        mm.all_gather_(reg, n, dtype)
+        torch.cuda.synchronize()
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine, group=pc.tp_group)
+        want = torch.cat([parts[r][r * per:(r + 1) * per] for r in range(world)])
+        assert torch.equal(x, want), f"multimem all-gather {dtype}"
+    assert native.status() == 0
+    dist.barrier()
+    assert not arena.check_canaries()
+    dist.barrier()
+    if rank == 0:
+        print("MULTIMEM_OK")
+
+
 def mode_mailbox(pc, dev):
     """Ring hand-off through peer mailboxes: several rounds, payload checked against the sender's rank."""
     from elfa_b200 import native
@@ -489,6 +542,8 @@ def main():
         mode_timeout(pc, dev)
     elif mode == "mailbox":
         mode_mailbox(pc, dev)
+    elif mode == "multimem":
+        mode_multimem(pc, dev)
     dist.destroy_process_group()
 
 

@@ -101,6 +101,18 @@ def test_zero2_gradient_sharding_matches_single_gpu(cuda_device, backend):
         assert "peer_kernels=True" in r.stdout
 
 
+def test_multimem_collectives_through_the_switch(cuda_device):
+    """ELFA_NVLS=1: all-reduce / reduce-scatter / all-gather with multimem instructions against the library's results; then a
+    data-parallel run whose gradient all-reduce goes through the switch. Every rank exits normally."""
+    r = _run(["multimem"], 29716, extra_env={"ELFA_NVLS": "1"})
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "MULTIMEM_OK" in r.stdout or "MULTIMEM_SKIPPED" in r.stdout
+    if "MULTIMEM_OK" in r.stdout:
+        r = _run(["zero", "fused", "bf16", "0"], 29717, extra_env={"ELFA_NVLS": "1"})
+        assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+        assert "ZERO_OK stage=0" in r.stdout and "nvls=True" in r.stdout
+
+
 def test_ring_handoff_through_peer_mailboxes(cuda_device):
     r = _run(["mailbox"], 29709)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]

@@ -75,3 +75,25 @@ def test_checkpoint_resume_continues_identically(cuda_device, tmp_path):
     lb = b.run(max_steps=3)
     for x, y in zip(la[3:], lb):
         assert abs(x - y) < 2e-3 * abs(x), (la, lb)
+
+
+def test_deterministic_mode_repeats_bit_for_bit(cuda_device):
+    """runtime.deterministic: no split-K atomics, embedding gradient reduced over sorted ids - two runs give identical bits."""
+    warnings.simplefilter("ignore")
+    from elfa_b200.config import Config
+    from elfa_b200.trainer import Trainer
+
+    def run():
+        cfg = Config.from_file(os.path.join(ROOT, "configs", "bench", "smoke_cpu.yaml"), env_override=False)
+        cfg.model.dtype = "bf16"
+        cfg.checkpoint.dir = ""
+        cfg.telemetry.log_file = ""
+        cfg.runtime.deterministic = True
+        cfg.training.learning_rate = 3e-3
+        tr = Trainer(cfg, device=cuda_device, telemetry=False)
+        losses = tr.run(max_steps=3)
+        return losses, tr.flat.flat.clone()
+    la, wa = run()
+    lb, wb = run()
+    assert la == lb and torch.equal(wa, wb)
+    assert native.deterministic()
