@@ -49,11 +49,24 @@ def gather_sequence(x_local: torch.Tensor, group=None, dim: int = 1) -> torch.Te
     return torch.cat(parts, dim=dim)
 
 
+_MAILBOXES = {}      # (id(group), step) -> PeerMailbox: neighbour hand-offs that go over NVLink peer memory
+
+
+def register_mailboxes(group, arena, nbytes: int) -> None:
+    """Routes the neighbour exchanges of ``group`` (``ring_exchange`` with step +1 / -1 on CUDA tensors of at most ``nbytes``)
+    through peer-memory mailboxes in ``arena`` (write-then-flag over NVLink) instead of library send / receive. Collective."""
+    _MAILBOXES[(id(group), 1)] = PeerMailbox(arena, nbytes, "sp.mailbox.right", direction=1)
+    _MAILBOXES[(id(group), -1)] = PeerMailbox(arena, nbytes, "sp.mailbox.left", direction=-1)
+
+
 def ring_exchange(x: torch.Tensor, step: int = 1, group=None) -> torch.Tensor:
     """Sends ``x`` to rank ``(r + step) % N`` and returns the tensor received from ``(r - step) % N``."""
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     if world == 1:
         return x.clone()
+    box = _MAILBOXES.get((id(group), step)) if x.is_cuda else None
+    if box is not None and x.numel() * x.element_size() <= box.nbytes and (x.numel() * x.element_size()) % 16 == 0:
+        return ring_exchange_peer(x, box)
     ranks = dist.get_process_group_ranks(group) if group is not None else list(range(world))
     dst, src = ranks[(rank + step) % world], ranks[(rank - step) % world]
     out = torch.empty_like(x)
@@ -173,14 +186,15 @@ class PeerMailbox:
     (``syncCrossBoundary``) - grouped NCCL send / receive there.
     """
 
-    def __init__(self, arena, nbytes: int, name: str = "sp.mailbox"):
+    def __init__(self, arena, nbytes: int, name: str = "sp.mailbox", direction: int = 1):
+        """``direction`` +1: messages travel to the right neighbour (rank + 1); -1: to the left one."""
         import ctypes
         self.arena = arena
         self.nbytes = (nbytes + 15) // 16 * 16
         self.rank, self.world = arena.rank, arena.world
         self.data = arena.alloc(2 * self.nbytes, name + ".data")
         self.flags = arena.alloc(1024, name + ".flags")          # u32[0] arrivals, u32[64] acks (separate cache lines)
-        self.right, self.left = (self.rank + 1) % self.world, (self.rank - 1) % self.world
+        self.right, self.left = (self.rank + direction) % self.world, (self.rank - direction) % self.world
         self._scratch = torch.zeros(4, dtype=torch.int32, device=arena.device)   # 16-byte payload of an acknowledgement
         self._ack_sink = arena.alloc(1024, name + ".acksink")
         self._blocks = ctypes.c_int(0)

@@ -89,6 +89,14 @@ class Trainer:
             pc.symm = SymmetricArena.for_group(pc.tp_group, device)
         self.model = build_model(cfg, pc, device)
         self.model.train()
+        if pc.cp_size > 1 and cfg.mixer() == "efla" and pc.comm_backend == "fused" and device.type == "cuda":
+            # sequence-parallel EFLA: the ShortConv halo (and its gradient) goes from neighbour to neighbour through
+            # peer-memory mailboxes (write-then-flag over NVLink)
+            from .parallel import sp
+            from .runtime.symm import SymmetricArena
+            halo = cfg.training.micro_batch_size * max(cfg.model.prism.shortconv_window - 1, 1) * cfg.model.hidden_dim * 4
+            arena_cp = SymmetricArena.for_group(pc.cp_group, device, 4 * halo + (8 << 20))
+            sp.register_mailboxes(pc.cp_group, arena_cp, halo)
         dp_arena = None
         blockwise2 = (cfg.runtime.zero_stage == 2 and pc.tp_size == 1 and pc.cp_size == 1 and cfg.training.optimizer in ("adamw", "lion"))
         nvls0 = cfg.runtime.zero_stage == 0 and os.environ.get("ELFA_NVLS", "0") == "1"     # in-switch gradient all-reduce

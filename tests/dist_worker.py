@@ -444,6 +444,16 @@ def mode_mailbox(pc, dev):
         assert native.status() == 0
         want = float(((r - 1) % w) * 100 + rnd)
         assert bool((got == want).all()), (r, rnd, float(got[0]), want)
+    # the registered route: ring_exchange in both directions (what the differentiable halo exchange uses)
+    from elfa_b200.parallel import sp
+    sp.register_mailboxes(pc.tp_group, arena, 1 << 20)
+    for rnd in range(3):
+        for step in (1, -1):
+            x = torch.full((2, 15, 64), float(r * 10 + rnd), device=dev, dtype=torch.bfloat16)
+            got = sp.ring_exchange(x, step, pc.tp_group)
+            torch.cuda.synchronize()
+            assert bool((got == float(((r - step) % w) * 10 + rnd)).all()), (r, rnd, step)
+    assert native.status() == 0 and not arena.check_canaries()
     dist.barrier()
     if r == 0:
         print("MAILBOX_OK")
