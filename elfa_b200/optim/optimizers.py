@@ -390,9 +390,15 @@ class Muon(_Base):
                 st = stream_ptr(g)
                 y = torch.empty(n, dtype=torch.bfloat16, device=g.device)
                 lib.call("elfa_muon_momentum", m, g, _ptype(g), y, n, float(self.momentum), self.scalars, self.part, None, st)
-                ok = rows % 8 == 0 and cols % 8 == 0
-                y2 = newton_schulz(y.view(rows, cols), self.iterations) if ok else \
-                    newton_schulz(y.view(rows, cols).float().cpu(), self.iterations).to(g.device, torch.bfloat16)
+                if rows % 8 == 0 and cols % 8 == 0:
+                    y2 = newton_schulz(y.view(rows, cols), self.iterations)
+                else:
+                    # the tensor-core GEMM wants multiples of 8: zero rows / columns change nothing (they stay zero through
+                    # every Y <- 0.5 Y (3I - Y^T Y) step and add nothing to Y^T Y)
+                    pr, pc_ = (rows + 7) // 8 * 8, (cols + 7) // 8 * 8
+                    yp = torch.zeros((pr, pc_), dtype=torch.bfloat16, device=g.device)
+                    yp[:rows, :cols] = y.view(rows, cols)
+                    y2 = newton_schulz(yp, self.iterations)[:rows, :cols]
                 pout = None if self.master_is_param else p.data.view(-1)
                 lib.call("elfa_muon_apply", pout, 0 if pout is None else 1, master, y2.contiguous(), n, float(self.lr), self.scalars, st)
             else:

@@ -8,7 +8,8 @@ from elfa_b200.ops import efla as eops
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("B,T,H,d,chunk", [(1, 16, 1, 32, 16), (2, 50, 2, 64, 16), (1, 40, 2, 128, 8), (1, 70, 1, 96, 16), (2, 100, 2, 64, 32)])
+@pytest.mark.parametrize("B,T,H,d,chunk", [(1, 16, 1, 32, 16), (2, 50, 2, 64, 16), (1, 40, 2, 128, 8), (1, 70, 1, 96, 16), (2, 100, 2, 64, 32),
+                                           (1, 2048, 2, 64, 16), (1, 4096, 1, 128, 16)])     # long sequences: fp32 state drift would show
 @pytest.mark.parametrize("with_state", [False, True])
 def test_efla_scan_forward_backward(cuda_device, B, T, H, d, chunk, with_state):
     torch.manual_seed(d + T)
@@ -27,7 +28,7 @@ def test_efla_scan_forward_backward(cuda_device, B, T, H, d, chunk, with_state):
     vr = v.detach().float().requires_grad_(True)
     br = beta.detach().clone().requires_grad_(True)
     sr = s0.detach().clone().requires_grad_(True) if with_state else None
-    o_ref, s_ref = eops.efla_scan_ref(kr, vr, br, sr)
+    o_ref, s_ref = (eops.efla_scan_ref if T <= 256 else eops.efla_scan_chunked_ref)(kr, vr, br, sr)
     torch.autograd.backward([o_ref, s_ref], [go.float(), gs])
     assert (o.float() - o_ref).abs().max() < 0.05
     assert (s - s_ref).abs().max() < 0.02

@@ -174,3 +174,22 @@ def test_newton_schulz_on_the_gemm_matches_fp32(cuda_device):
         assert (got - ref).abs().max().item() < 0.02 * ref.abs().max().item() + 1e-3
     torch.cuda.synchronize()
     assert native.status() == 0
+
+
+def test_muon_handles_dimensions_that_are_not_multiples_of_eight(cuda_device):
+    """A 2-D parameter whose sides are not multiples of 8 is orthogonalised on the GPU too (zero padding, exact), not on the host."""
+    from elfa_b200.optim import FlatParams
+    from elfa_b200.optim.optimizers import Muon, newton_schulz
+    g = torch.Generator().manual_seed(5)
+    w = torch.nn.Parameter((torch.randn(100, 36, generator=g) * 0.1).to(torch.bfloat16).to(cuda_device))
+    flat = FlatParams([("w", w)])
+    opt = Muon(flat, lr=0.1, momentum=0.0, iterations=3, max_grad_norm=0.0)
+    grad = torch.randn(100, 36, generator=g).to(cuda_device)
+    w.main_grad.copy_(grad)
+    before = w.detach().float().clone()
+    opt.step(0.1)
+    torch.cuda.synchronize()
+    assert native.status() == 0
+    ref = newton_schulz((grad / grad.norm()).float().cpu(), 3)
+    step = (before - w.detach().float()).cpu() / 0.1
+    assert (step - ref).abs().max().item() < 0.03 * ref.abs().max().item() + 2e-3
