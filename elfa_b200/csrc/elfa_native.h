@@ -55,6 +55,8 @@ int elfa_cast(const void* src, int src_type, void* dst, int dst_type, long long 
 // ---- xent.cu -----------------------------------------------------------------------------------
 int elfa_xent_stats(const void* logits, long long ld, const long long* targets, float* stats, int rows, int V, int vocab_lo,
                     int vocab_total, void* stream);
+int elfa_xent_stats_push(const void* logits, long long ld, const long long* targets, const unsigned long long* peer_tables,
+                         int slice, int world, int rows, int V, int vocab_lo, int vocab_total, void* stream);
 int elfa_xent_grad(void* logits, long long ld, void* dlogits, long long ldd, const long long* targets, const float* stats,
                    int nslices, float* loss_out, int rows, int V, int vocab_lo, int vocab_total, float smoothing,
                    const float* grad_scale_ptr, float grad_scale, void* stream);

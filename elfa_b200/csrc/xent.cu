@@ -26,10 +26,19 @@ __device__ __forceinline__ void online_combine(float& m, float& s, float m2, flo
   m = nm;
 }
 
-// stats[row] = (max, sum exp(x - max), x[target] if the target is in this slice else 0, sum x)
+struct StatPeers {      // vocabulary-parallel exchange: every rank's [slices][rows] statistics table (peer-addressable)
+  unsigned long long p[8];
+  int world, slice, rows;
+};
+
+// stats[row] = (max, sum exp(x - max), x[target] if the target is in this slice else 0, sum x).
+// With `peers.world > 0` the four numbers are also stored into slot [slice][row] of every rank's table (16-byte peer
+// stores over NVLink): the exchange of the vocabulary-parallel loss happens inside this kernel instead of a library
+// all-gather (reference call site: src/distributed/tensor_parallel.zig:77-129 gather, then consume).
 __global__ void __launch_bounds__(XENT_THREADS) xent_stats_kernel(const __nv_bfloat16* __restrict__ logits, long long ld,
                                                                   const long long* __restrict__ targets, RowStat* __restrict__ stats,
-                                                                  int V, int vocab_lo, int vocab_total, unsigned int* status) {
+                                                                  int V, int vocab_lo, int vocab_total, unsigned int* status,
+                                                                  const StatPeers peers) {
   __shared__ float sm[3][XENT_THREADS / 32];
   const int row = blockIdx.x;
   const __nv_bfloat16* x = logits + (long long)row * ld;
@@ -72,7 +81,12 @@ __global__ void __launch_bounds__(XENT_THREADS) xent_stats_kernel(const __nv_bfl
     float tl = 0.f;
     if (t >= vocab_lo && t < vocab_lo + V) tl = __bfloat162float(x[t - vocab_lo]);
     else if (t != -100 && (t < 0 || t >= vocab_total)) atomicOr(status, (unsigned)ELFA_ST_BAD_TARGET);
-    stats[row] = RowStat{M, S, tl, SX};
+    const RowStat rs{M, S, tl, SX};
+    if (stats) stats[row] = rs;
+    for (int i = 0; i < peers.world; ++i) {
+      const int r = (peers.slice + i) % peers.world;      // own table first, then the peers, staggered by rank
+      reinterpret_cast<RowStat*>(peers.p[r])[(long long)peers.slice * peers.rows + row] = rs;
+    }
   }
 }
 
@@ -142,7 +156,30 @@ ELFA_API int elfa_xent_stats(const void* logits, long long ld, const long long* 
   unsigned int* st = status_word();
   ELFA_REQUIRE(st != nullptr, "xent: no status word");
   xent_stats_kernel<<<rows, XENT_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(logits), ld, targets, reinterpret_cast<RowStat*>(stats), V, vocab_lo, vocab_total, st);
+      static_cast<const __nv_bfloat16*>(logits), ld, targets, reinterpret_cast<RowStat*>(stats), V, vocab_lo, vocab_total, st, StatPeers{});
+  ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
+  return ELFA_OK;
+}
+
+// Pass 1 of the vocabulary-parallel loss with the exchange inside the kernel: this rank's statistics go to slot [slice] of
+// every rank's table (peer_tables: `world` device addresses of [world][rows][4] fp32 tables in peer-addressable memory).
+// A barrier over the group (elfa_symm_barrier) must follow before any rank runs pass 2 on its table.
+ELFA_API int elfa_xent_stats_push(const void* logits, long long ld, const long long* targets, const unsigned long long* peer_tables,
+                                  int slice, int world, int rows, int V, int vocab_lo, int vocab_total, void* stream) {
+  ELFA_REQUIRE(logits && targets && peer_tables && rows > 0 && V > 0, "xent_stats_push: bad arguments");
+  ELFA_REQUIRE(world >= 1 && world <= 8 && slice >= 0 && slice < world, "xent_stats_push: bad slice / world");
+  ELFA_REQUIRE(ld % 8 == 0, "xent_stats_push: row pitch must be a multiple of 8");
+  unsigned int* st = status_word();
+  ELFA_REQUIRE(st != nullptr, "xent: no status word");
+  StatPeers sp{};
+  for (int i = 0; i < world; ++i) {
+    ELFA_REQUIRE((peer_tables[i] & 15) == 0, "xent_stats_push: tables must be 16-byte aligned");
+    sp.p[i] = peer_tables[i];
+  }
+  sp.world = world; sp.slice = slice; sp.rows = rows;
+  xent_stats_kernel<<<rows, XENT_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(logits), ld, targets, nullptr, V, vocab_lo, vocab_total, st, sp);
   ELFA_CUDA(cudaGetLastError());
   ::elfa::count_launches(1);
   return ELFA_OK;

@@ -50,7 +50,7 @@ class _State:
     def __init__(self, arena):
         self.arena = arena
         self.slots: Dict[Tuple[str, int, int], _Slot] = {}
-        self.counter = {"ag": 0, "rs": 0, "agq": 0}
+        self.counter = {"ag": 0, "rs": 0, "agq": 0, "xent": 0}
         self.bar = None                                     # signal words of the stream-ordered barrier
         self.bar_peers = None
         self.bar_epoch = 0
@@ -251,3 +251,19 @@ def gemm_rs(a: torch.Tensor, w: torch.Tensor, pc: ParallelContext, *, b_mn: bool
              ctypes.addressof(slot.peer_flags), slot.flags.tensor, ctypes.addressof(slot.arrivals), out, out.stride(0), rank, world,
              _WAIT_MS, max_ctas, stream_ptr(ac))
     return out
+
+
+def xent_stats_exchange(logits2: torch.Tensor, targets1: torch.Tensor, pc: ParallelContext, rows: int, v_local: int, vocab_lo: int,
+                        vocab_total: int) -> torch.Tensor:
+    """Pass 1 of the vocabulary-parallel cross-entropy with the exchange inside the kernel: every rank's per-token statistics
+    (max, sum-exp, target logit, sum of logits) are stored into its slot of every rank's ``[world, rows, 4]`` table with peer
+    stores, then a signal barrier. Two tables alternate: a rank that is one loss ahead writes into the other one.
+    Returns this rank's table (valid until the second call after this one)."""
+    st = _state(pc)
+    world, rank = pc.tp_size, pc.tp_rank
+    slot = st.next_slot("xent", _round_class(world * rows * 16))
+    stream = stream_ptr(logits2)
+    lib.call("elfa_xent_stats_push", logits2, logits2.stride(0), targets1, ctypes.addressof(slot.peer_data), rank, world, rows, v_local,
+             vocab_lo, vocab_total, stream)
+    st.stream_barrier(stream)          # all ranks' stores have landed (the barrier's signal is a release after a system fence)
+    return slot.data.view(torch.float32, (world, rows, 4))

@@ -439,10 +439,15 @@ class _VocabParallelCE(torch.autograd.Function):
         if l2.is_cuda:
             from ..native import lib, stream_ptr
             st = stream_ptr(l2)
-            mine = torch.empty((rows, 4), dtype=torch.float32, device=l2.device)
-            lib.call("elfa_xent_stats", l2, l2.stride(0), t1, mine, rows, Vl, vocab_lo, vocab_total, st)
-            allst = torch.empty((pc.tp_size, rows, 4), dtype=torch.float32, device=l2.device)
-            dist.all_gather_into_tensor(allst, mine, group=pc.tp_group)
+            if pc.comm_backend == "fused" and pc.symm is not None:
+                # the statistics kernel stores its four numbers per token straight into every rank's table (peer stores)
+                from . import fused
+                allst = fused.xent_stats_exchange(l2, t1, pc, rows, Vl, vocab_lo, vocab_total)
+            else:
+                mine = torch.empty((rows, 4), dtype=torch.float32, device=l2.device)
+                lib.call("elfa_xent_stats", l2, l2.stride(0), t1, mine, rows, Vl, vocab_lo, vocab_total, st)
+                allst = torch.empty((pc.tp_size, rows, 4), dtype=torch.float32, device=l2.device)
+                dist.all_gather_into_tensor(allst, mine, group=pc.tp_group)
             per = torch.empty(rows, dtype=torch.float32, device=l2.device)
             lib.call("elfa_xent_grad", l2, l2.stride(0), l2, l2.stride(0), t1, allst, pc.tp_size, per, rows, Vl, vocab_lo,
                      vocab_total, float(smoothing), None, grad_scale / denom, st)
