@@ -129,6 +129,11 @@ int elfa_gemm_rs(const void* A, long long lda, const void* B, long long ldb, int
                  const unsigned long long* peer_recv, const unsigned long long* peer_flags, const void* my_flags,
                  unsigned int* arrivals_io, void* out, long long ld_out, int rank, int world, int wait_ms, int max_ctas, void* stream);
 
+int elfa_gemm_rs_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, int M, int N, int K,
+                       const unsigned long long* peer_recv, const unsigned long long* peer_flags, const void* my_flags,
+                       unsigned int* arrivals_io, void* out, long long ld_out, int rank, int world, int wait_ms, void* stream);
+int elfa_gemm_rs_slot_cols(int N);
+
 // ---- multimem.cu (NVLS: reductions inside the NVSwitch through the arena's multicast mapping) ------------------
 int elfa_multimem_collective(unsigned long long mc, const void* local, void* out, long long off_bytes, long long n, int dtype,
                              int rank, int world, float scale, int mode, void* stream);

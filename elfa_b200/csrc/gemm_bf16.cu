@@ -65,6 +65,7 @@ struct GemmParams {
   int staged;        // epilogue goes through shared memory + TMA store (plain bf16 output)
   int splits;        // split-K factor (fp32 accumulate outputs only; partial tiles are added atomically)
   int kb_per_split;  // K blocks per split
+  int sfb_atoms;     // MXFP8: row blocks of the B scale tensor
 };
 
 enum { COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2 };
@@ -94,11 +95,14 @@ struct CommParams {
   long long slot_chunks;                   // chunks per source slot
 };
 
-template <int BN, int STAGES>
+// SF: bytes of scale atoms per stage (block-scaled MXFP8 operands: one atom of A scales + the atoms of B scales; 0 for bf16)
+template <int BN, int STAGES, int SF = 0>
 struct SmemLayout {
-  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int A_BYTES = BM * BK * 2;      // bf16: 128 rows x 64 elements; MXFP8: 128 rows x 128 one-byte elements
   static constexpr int B_BYTES = BN * BK * 2;
-  static constexpr int BAR_OFF = STAGES * (A_BYTES + B_BYTES);
+  static constexpr int SF_BYTES = SF;
+  static constexpr int SF_OFF = STAGES * (A_BYTES + B_BYTES);
+  static constexpr int BAR_OFF = SF_OFF + STAGES * SF_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 4 + 4;   // ring full/empty, accumulator full/empty, push buffers (all-gather variant)
   static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16;
   static constexpr int DYN = TOTAL + 1024;  // slack for manual 1024-byte alignment
@@ -110,6 +114,7 @@ struct SmemLayout {
 
 struct OutMaps {   // tensor maps over every rank's receive buffer, viewed as [world * rows_per_rank, N] bf16
   CUtensorMap m[MAX_RANKS];
+  CUtensorMap sfa, sfb;   // MXFP8 operands: scale atoms of A / B as rows of 128 32-bit words (see gemm_mxfp8.cu)
 };
 
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& mb, int& nb) {
@@ -147,14 +152,23 @@ __device__ __forceinline__ void tile_coords_comm(const GemmParams& p, const Comm
 // each CTA ends up with its 128 rows of the accumulator in its own tensor memory. Per CTA this
 // needs a third less shared-memory fill per FLOP than a 128 x BN tile. In the fused variants a pair's 256 rows lie
 // inside one rank's shard (rows per rank a multiple of 256); flags, pushes and the reduce phase work per CTA as before.
-template <int BN, bool A_MN, bool B_MN, int STAGES, int COMM, bool TWO = false>
+// MX = true: block-scaled MXFP8 operands (e4m3 payloads, both K-major, one ue8m0 scale per 32 K-elements in 512-byte atoms,
+// tcgen05.mma.kind::mxf8f6f4.block_scale with the scales in tensor memory) through the same roles: used by the fused
+// GEMM -> reduce-scatter kernel of the MXFP8 layers. A stage then holds 128 K-elements (= bytes) per row plus the scale
+// atoms; accumulator b sits at tensor-memory column 256 * b with the scale columns behind it (BN <= 192).
+template <int BN, bool A_MN, bool B_MN, int STAGES, int COMM, bool TWO = false, bool MX = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmA2, const GemmParams p, const CommParams cm,
                  const __grid_constant__ OutMaps om) {
   constexpr int BN_CTA = TWO ? BN / 2 : BN;   // rows of B this CTA keeps in shared memory
   constexpr int TILE_M = TWO ? 2 * BM : BM;   // rows of one work unit
-  using L = SmemLayout<BN_CTA, STAGES>;
+  constexpr int NATOM = BN <= 128 ? 1 : 2;                 // B scale atoms a tile touches (tiles start 0 or 64 rows into an atom)
+  constexpr int SF_ATOM = 512;
+  using L = SmemLayout<BN_CTA, STAGES, MX ? (1 + NATOM) * SF_ATOM : 0>;
+  static_assert(!MX || (!A_MN && !B_MN && BN <= 192), "block-scaled operands are K-major and leave room for the scale columns");
+  constexpr int KSTEP = MX ? 128 : BK;                     // contraction elements per stage
+  constexpr uint32_t ACC_STRIDE = MX ? 256 : BN;           // tensor-memory columns between the two accumulators
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -171,7 +185,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  constexpr uint32_t TMEM_COLS = 2 * BN;  // 128 / 256 / 512: a power of two >= 32
+  constexpr uint32_t TMEM_COLS = MX ? 512 : 2 * BN;  // 128 / 256 / 512: a power of two >= 32
   const uint32_t cta_rank = TWO ? cluster_ctarank() : 0u;                       // position in the pair; 0 issues the MMAs
   const int wid = TWO ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;               // work slot: one per CTA, or one per pair
   const int wstride = TWO ? (int)(gridDim.x >> 1) : (int)gridDim.x;
@@ -207,7 +221,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t tmem_base = *tmem_holder;
 
   const int num_tiles = p.tiles_m * p.tiles_n;
-  const int num_kb = (p.K + BK - 1) / BK;
+  const int num_kb = (p.K + KSTEP - 1) / KSTEP;
   const bool staged = COMM == COMM_RS || p.staged != 0;
   const int splits = COMM == COMM_NONE ? p.splits : 1;
   const int num_units = num_tiles * splits;   // work unit = (tile, K split)
@@ -238,6 +252,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status)) { ok = false; break; }
           const uint32_t a_dst = smem_u32(sA + s * L::A_BYTES);
           const uint32_t b_dst = smem_u32(sB + s * L::B_BYTES);
+          if (MX) {
+            // payload tiles (128 bytes of K per row) and the scale atoms of this tile and K tile
+            const uint32_t sf_dst = smem_u32(smem + L::SF_OFF + s * L::SF_BYTES);
+            const int sfa_row = (m0 / BM) * num_kb + kb, sfb_row = kb * (p.sfb_atoms + 1) + n0 / 128;
+            constexpr uint32_t TX = L::A_BYTES + L::B_BYTES + L::SF_BYTES;
+            if (TWO) {
+              const uint32_t fb = map_to_cta(full_bar(s), 0);
+              if (cta_rank == 0) mbar_expect_tx(full_bar(s), 2 * TX);
+              tma_load_2d_pair(a_dst, &tmA, kb * KSTEP, m0, fb);
+              tma_load_2d_pair(b_dst, &tmB, kb * KSTEP, n0 + (int)cta_rank * BN_CTA, fb);
+              tma_load_2d_pair(sf_dst, &om.sfa, 0, sfa_row, fb);
+              tma_load_2d_pair(sf_dst + SF_ATOM, &om.sfb, 0, sfb_row, fb);
+            } else {
+              mbar_expect_tx(full_bar(s), TX);
+              tma_load_2d(a_dst, &tmA, kb * KSTEP, m0, full_bar(s));
+              tma_load_2d(b_dst, &tmB, kb * KSTEP, n0, full_bar(s));
+              tma_load_2d(sf_dst, &om.sfa, 0, sfa_row, full_bar(s));
+              tma_load_2d(sf_dst + SF_ATOM, &om.sfb, 0, sfb_row, full_bar(s));
+            }
+            continue;
+          }
           if (TWO) {
             // both CTAs' copies complete on the even CTA's barrier, which expects the bytes of both
             const uint32_t fb = map_to_cta(full_bar(s), 0);
@@ -297,7 +332,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         ok = __all_sync(0xffffffffu, mbar_wait(tempty_bar(buf), bph ^ 1, abort_flag, p.status));
         if (!ok) break;
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + buf * BN;
+        const uint32_t tmem_d = tmem_base + buf * ACC_STRIDE;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -306,6 +341,36 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tc_fence_after();
           const uint32_t a_base = smem_u32(sA + s * L::A_BYTES);
           const uint32_t b_base = smem_u32(sB + s * L::B_BYTES);
+          if (MX) {
+            // scale atoms -> tensor memory (two column sets alternate between K tiles), then four block-scaled MMAs of
+            // 32 K-elements each; byte k of the scale columns belongs to MMA k (selected through the descriptor)
+            const uint32_t sf_base = smem_u32(smem + L::SF_OFF + s * L::SF_BYTES);
+            const uint32_t sf_tmem = tmem_base + (it & 1u) * ACC_STRIDE;
+            constexpr uint32_t SFA_COL = BN, SFB_COL = BN + 4;
+            int mb_, nb_, sh_;
+            tile_coords_comm<COMM>(p, cm, unit / splits, mb_, nb_, sh_, TILE_M);
+            const uint32_t sfb_shift = (uint32_t)((nb_ * BN) % 128) / 32;
+            if (elect_one()) {
+              if (TWO) tc_cp_32x128b_warpx4_pair(sf_tmem + SFA_COL, make_smem_desc(sf_base, 0, 128, 0));
+              else tc_cp_32x128b_warpx4(sf_tmem + SFA_COL, make_smem_desc(sf_base, 0, 128, 0));
+#pragma unroll
+              for (int j = 0; j < NATOM; ++j) {
+                if (TWO) tc_cp_32x128b_warpx4_pair(sf_tmem + SFB_COL + 4 * j, make_smem_desc(sf_base + (1 + j) * SF_ATOM, 0, 128, 0));
+                else tc_cp_32x128b_warpx4(sf_tmem + SFB_COL + 4 * j, make_smem_desc(sf_base + (1 + j) * SF_ATOM, 0, 128, 0));
+              }
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const uint64_t da = make_smem_desc(a_base + k * 32, 16, 1024, 2);
+                const uint64_t db = make_smem_desc(b_base + k * 32, 16, 1024, 2);
+                const uint32_t acc = ((kb - kb0) | k) != 0 ? 1u : 0u;
+                if (TWO) tc_mma_mxf8_pair(tmem_d, da, db, make_idesc_mxf8(TILE_M, BN, k, k), acc, sf_tmem + SFA_COL, sf_tmem + SFB_COL + sfb_shift);
+                else tc_mma_mxf8(tmem_d, da, db, make_idesc_mxf8(TILE_M, BN, k, k), acc, sf_tmem + SFA_COL, sf_tmem + SFB_COL + sfb_shift);
+              }
+              if (TWO) tc_commit_pair(empty_bar(s)); else tc_commit(empty_bar(s));
+            }
+            __syncwarp();
+            continue;
+          }
           if (elect_one()) {
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
@@ -357,7 +422,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int rloc = q * 32 + lane;
         const bool f32 = p.staged == 2;
         const int nchunk = f32 ? BN / 32 : BN / 64;
-        const uint32_t tcol0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+        const uint32_t tcol0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * ACC_STRIDE;
         uint32_t ra[32], rb[32];
         if (!dead) tmem_ld32(tcol0, ra);                           // first 32 accumulator columns in flight
 #pragma unroll 1
@@ -437,7 +502,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (fl == 0) {
         // plain bf16 output: convert and store, two register buffers alternating so that the next 32 accumulator columns
         // are in flight while these are stored; no per-element branches (narrow-K products are bound by this loop)
-        const uint32_t tcol0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+        const uint32_t tcol0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * ACC_STRIDE;
         __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc;
         const float alpha = p.alpha;
         auto store_chunk = [&](const uint32_t (&r)[32], int c) {
@@ -473,14 +538,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         continue;
       }
       uint32_t rnext[32];
-      tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN, rnext);
+      tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * ACC_STRIDE, rnext);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) r[j] = rnext[j];
-        if (c + 1 < BN / 32) tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + (c + 1) * 32, rnext);   // next chunk in flight
+        if (c + 1 < BN / 32) tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * ACC_STRIDE + (c + 1) * 32, rnext);   // next chunk in flight
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) continue;  // uniform across the warp
         float v[32];
@@ -604,7 +669,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       if (lane == 0 && COMM == COMM_RS) {
         if (pend[1] >= 0) {
-          if (CPT == 4) tma_store_wait<8>(); else if (CPT == 2) tma_store_wait<4>(); else tma_store_wait<2>();   // all but the last two tiles' groups
+          if (CPT == 4) tma_store_wait<8>(); else if (CPT == 3) tma_store_wait<6>(); else if (CPT == 2) tma_store_wait<4>(); else tma_store_wait<2>();   // all but the last two tiles' groups
           __threadfence_system();
           unsigned int* cnt = reinterpret_cast<unsigned int*>(cm.peer_flags[pend[1]]) + cm.rank;
           asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
@@ -818,13 +883,14 @@ int sm_count() {
   return g_sm_count;
 }
 
-template <int BN, bool A_MN, bool B_MN, int COMM = COMM_NONE, bool TWO = false>
+template <int BN, bool A_MN, bool B_MN, int COMM = COMM_NONE, bool TWO = false, bool MX = false>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int max_ctas, cudaStream_t stream,
                 const CUtensorMap* tmA2 = nullptr, const CommParams* comm = nullptr, const OutMaps* om = nullptr) {
-  constexpr int STAGES = TWO ? 6 : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
+  constexpr int STAGES = MX ? (TWO ? 6 : (BN == 192 ? 4 : 5)) : (TWO ? 6 : (BN == 256 ? 4 : (BN == 128 ? 6 : 8)));
   constexpr int TILE_M = TWO ? 2 * BM : BM;
-  using L = SmemLayout<TWO ? BN / 2 : BN, STAGES>;
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, STAGES, COMM, TWO>;
+  using L = SmemLayout<TWO ? BN / 2 : BN, STAGES, MX ? (1 + (BN <= 128 ? 1 : 2)) * 512 : 0>;
+  static_assert(L::DYN_RS <= 227 * 1024, "shared-memory plan exceeds the per-CTA limit");
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, STAGES, COMM, TWO, MX>;
   constexpr int DYN = L::DYN_RS;   // every variant carries the two staging tiles of the TMA-store epilogue
   static bool configured = false;
   if (!configured) {
@@ -839,7 +905,7 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, in
     p.group_m = (int)std::max(1LL, rows / TILE_M);
   }
   if (TWO) max_ctas /= 2;    // work slots are CTA pairs
-  const int num_kb_host = (p.K + BK - 1) / BK;
+  const int num_kb_host = MX ? (p.K + 127) / 128 : (p.K + BK - 1) / BK;
   p.splits = 1;
   if (COMM == COMM_NONE && !deterministic_mode() && (p.flags & (ELFA_EPI_ACCUM | ELFA_EPI_OUT_F32)) == (ELFA_EPI_ACCUM | ELFA_EPI_OUT_F32)) {
     // fp32 accumulate outputs (weight gradients): split K when the tile count fills the SMs badly
@@ -1126,7 +1192,7 @@ ELFA_API int elfa_gemm_rs(const void* A, long long lda, const void* B, long long
     const char* e = getenv("ELFA_RS_CHUNK_MAJOR");
     const bool want = !(e && e[0] == '0');
     c.chunk_major = (want && N % BN == 0) ? 1 : 0;
-    c.slot_chunks = (long long)(rows / BM) * (N / BN) * (BN / 64);
+    c.slot_chunks = (long long)(rows / BM) * ((N + BN - 1) / BN) * (BN / 64);
   }
   // per source rank: one bump per tile of the shard
   *arrivals_io += (unsigned)((rows / BM) * ((N + BN - 1) / BN));
@@ -1138,4 +1204,66 @@ ELFA_API int elfa_gemm_rs(const void* A, long long lda, const void* B, long long
   }
   // max_ctas < SM count leaves SMs to a kernel on another stream (a weight-gradient GEMM next to this comm-bound kernel)
   return dispatch_comm<COMM_RS>(BN, b_mn_major, tmA, tmB, tmA, p, c, static_cast<cudaStream_t>(stream), &om, max_ctas, pair);
+}
+
+// out[M/world, N] = reduce_scatter_rows(A[M,K] * B[N,K]^T) with MXFP8 operands (e4m3 payloads, scale atoms as produced by
+// elfa_mxfp8_quantize_gemm: A a left operand, B a right operand): the block-scaled product of the row-parallel MXFP8 layers
+// inside the fused GEMM -> reduce-scatter kernel. Receive slots are chunk-major and hold N rounded up to whole 192- (or
+// 128-) wide tiles: `peer_recv` buffers need world * (M / world) * elfa_gemm_rs_slot_cols(N) * 2 bytes.
+ELFA_API int elfa_gemm_rs_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, int M, int N, int K,
+                                const unsigned long long* peer_recv, const unsigned long long* peer_flags, const void* my_flags,
+                                unsigned int* arrivals_io, void* out, long long ld_out, int rank, int world, int wait_ms, void* stream) {
+  ELFA_REQUIRE(A && sfa && B && sfb && peer_recv && peer_flags && my_flags && arrivals_io && out, "gemm_rs_mxfp8: null argument");
+  ELFA_REQUIRE(world >= 2 && world <= MAX_RANKS && rank >= 0 && rank < world, "gemm_rs_mxfp8: bad rank/world");
+  ELFA_REQUIRE(M % world == 0 && (M / world) % BM == 0, "gemm_rs_mxfp8: rows per rank must be a multiple of 128");
+  ELFA_REQUIRE(N % 64 == 0 && K % 32 == 0 && ld_out % 8 == 0, "gemm_rs_mxfp8: N must be a multiple of 64, K of 32");
+  ELFA_REQUIRE((reinterpret_cast<uintptr_t>(sfa) & 15) == 0 && (reinterpret_cast<uintptr_t>(sfb) & 15) == 0,
+               "gemm_rs_mxfp8: scale tensors must be 16-byte aligned");
+  unsigned int* st = status_word();
+  ELFA_REQUIRE(st != nullptr, "gemm_rs_mxfp8: no status word");
+  const int rows = M / world;
+  const bool wide = N > 128;
+  const int BN = wide ? 192 : 128;
+  const bool pair = wide && rows % (2 * BM) == 0 && (long long)(M / (2 * BM)) * ((N + 191) / 192) >= sm_count() / 2;
+  const int kt = (K + 127) / 128;
+  CUtensorMap tmA, tmB;
+  int rc = cached_tmap(&tmA, A, 1, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, 128);
+  if (rc != ELFA_OK) return rc;
+  rc = cached_tmap(&tmB, B, 1, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)(pair ? BN / 2 : BN), 128);
+  if (rc != ELFA_OK) return rc;
+  OutMaps om{};
+  rc = make_tmap_2d(&om.sfa, sfa, 4, (uint64_t)((M + 127) / 128) * kt, 128, 512, 1, 128, false);
+  if (rc != ELFA_OK) return rc;
+  rc = make_tmap_2d(&om.sfb, sfb, 4, (uint64_t)((N + 127) / 128 + 1) * kt, 128, 512, (uint32_t)(wide ? 2 : 1), 128, false);
+  if (rc != ELFA_OK) return rc;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.C = out; p.ldc = ld_out;
+  p.alpha = 1.f;
+  p.status = st;
+  p.sfb_atoms = (N + 127) / 128;
+  CommParams c{};
+  c.rank = rank; c.world = world; c.rows_per_rank = rows;
+  c.wait_cycles = wait_cycles_of(wait_ms);
+  for (int i = 0; i < world; ++i) { c.peer_recv[i] = peer_recv[i]; c.peer_flags[i] = peer_flags[i]; }
+  c.my_flags = static_cast<const unsigned int*>(my_flags);
+  c.my_recv = reinterpret_cast<const __nv_bfloat16*>(peer_recv[rank]);
+  c.rs_out = static_cast<__nv_bfloat16*>(out);
+  c.ld_out = ld_out;
+  c.chunk_major = 1;
+  c.slot_chunks = (long long)(rows / BM) * ((N + BN - 1) / BN) * (BN / 64);
+  *arrivals_io += (unsigned)((rows / BM) * ((N + BN - 1) / BN));
+  c.flag_target = *arrivals_io;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int ctas = sm_count();
+  if (pair) return launch_gemm<192, false, false, COMM_RS, true, true>(tmA, tmB, p, ctas, s, &tmA, &c, &om);
+  if (wide) return launch_gemm<192, false, false, COMM_RS, false, true>(tmA, tmB, p, ctas, s, &tmA, &c, &om);
+  return launch_gemm<128, false, false, COMM_RS, false, true>(tmA, tmB, p, ctas, s, &tmA, &c, &om);
+}
+
+// Columns a receive slot of the fused reduce-scatter kernels must hold for an N-column output: N rounded up to whole tiles
+// of every tile width the kernels may choose.
+ELFA_API int elfa_gemm_rs_slot_cols(int N) {
+  const int a = (N + 127) / 128 * 128, b = (N + 191) / 192 * 192, c = (N + 255) / 256 * 256;
+  return std::max(a, std::max(b, c));
 }

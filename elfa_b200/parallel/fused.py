@@ -253,6 +253,25 @@ def gemm_rs(a: torch.Tensor, w: torch.Tensor, pc: ParallelContext, *, b_mn: bool
     return out
 
 
+def supported_rs_mxfp8(M: int, K: int, N: int, world: int) -> bool:
+    return M % world == 0 and (M // world) % 128 == 0 and K % 32 == 0 and N % 64 == 0
+
+
+def gemm_rs_mxfp8(a_op, w_op, pc: ParallelContext) -> torch.Tensor:
+    """``reduce_scatter_rows(a @ w^T)`` with MXFP8 operands (``a_op`` left operand ``[M, K]``, ``w_op`` right operand ``[N, K]``):
+    the block-scaled product inside the fused GEMM → reduce-scatter kernel. Returns ``[M / world, N]`` bf16."""
+    world, rank = pc.tp_size, pc.tp_rank
+    M, K, N = a_op.rows, a_op.cols, w_op.rows
+    st = _state(pc)
+    cols = int(lib.raw("elfa_gemm_rs_slot_cols")(N))
+    slot = st.next_slot("rs", _round_class(M * cols * 2))
+    out = torch.empty((M // world, N), dtype=torch.bfloat16, device=a_op.payload.device)
+    lib.call("elfa_gemm_rs_mxfp8", a_op.payload, a_op.scales, w_op.payload, w_op.scales, M, N, K, ctypes.addressof(slot.peer_data),
+             ctypes.addressof(slot.peer_flags), slot.flags.tensor, ctypes.addressof(slot.arrivals), out, out.stride(0), rank, world,
+             _WAIT_MS, stream_ptr(a_op.payload))
+    return out
+
+
 def xent_stats_exchange(logits2: torch.Tensor, targets1: torch.Tensor, pc: ParallelContext, rows: int, v_local: int, vocab_lo: int,
                         vocab_total: int) -> torch.Tensor:
     """Pass 1 of the vocabulary-parallel cross-entropy with the exchange inside the kernel: every rank's per-token statistics

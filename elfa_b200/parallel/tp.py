@@ -201,6 +201,16 @@ def _overlap_wgrad(pc: ParallelContext, t: torch.Tensor) -> bool:
     return os.environ.get("ELFA_OVERLAP_WGRAD", "0") not in ("0", "")
 
 
+def _block_scaled_rs(pc: ParallelContext, M: int, K: int, N: int) -> bool:
+    """Whether a GEMM → reduce-scatter of MXFP8 operands runs block-scaled inside the fused kernel (``ELFA_RS_MXFP8=0``: the
+    same kernel on the dequantised bf16 values)."""
+    import os
+    if pc.comm_backend != "fused" or pc.tp_size == 1 or os.environ.get("ELFA_RS_MXFP8", "1") in ("0", ""):
+        return False
+    from . import fused
+    return fused.supported_rs_mxfp8(M, K, N, pc.tp_size)
+
+
 def _quantised_gather_enabled() -> bool:
     import os
     return os.environ.get("ELFA_AG_MXFP8", "1") not in ("0", "")
@@ -260,7 +270,12 @@ class _ColumnParallelSP(torch.autograd.Function):
         if ctx.quant is not None and ctx.quant.quant_backward:
             # quantised backward: dy in MXFP8 blocks along its last dimension, the weight along the same (contraction)
             # dimension; the reduce-scatter kernel multiplies the dequantised values (the same product)
-            _, dy2 = quantize_grad(dy2)
+            dy_op, dy2 = quantize_grad(dy2)
+            if dy_op is not None and use_block_scaled_bwd(dy2, ctx.w_ref, ctx.quant) and _block_scaled_rs(pc, dy2.shape[0], dy2.shape[1], ctx.w_ref.shape[0]):
+                from . import fused
+                dx = fused.gemm_rs_mxfp8(dy_op, cached_weight_operand_bwd(ctx.w_ref, ctx.quant), pc)     # block-scaled dy @ w^T
+                dw = _wgrad(ctx.w_ref, x_full, dy2, wq.dtype)
+                return dx.view(Sl, B, D), dw, None, None, None
             wq = cached_weight_quant_bwd(ctx.w_ref, ctx.quant)
         if _overlap_wgrad(pc, dy2) and getattr(ctx.w_ref, "main_grad", None) is not None:
             # the two products are independent: the weight gradient runs on a second stream on the SMs that the
@@ -290,9 +305,18 @@ class _RowParallelSP(torch.autograd.Function):
     def forward(ctx, x, w, pc, quant):
         S, B, K = x.shape
         x2 = x.reshape(S * B, K)
-        xq = fake_quant(x2, quant) if quant is not None else x2
         wq = cached_weight_quant(w, quant) if quant is not None else w
-        y = gemm_rs(xq, wq, pc, b_mn=True)
+        if (quant is not None and quant.fmt == "mxfp8" and use_block_scaled_gemm(x2, w, quant)
+                and _block_scaled_rs(pc, x2.shape[0], x2.shape[1], w.shape[1])):
+            # e4m3 payloads and scales straight into the block-scaled MMAs of the fused kernel; the bf16 copy of the quantised
+            # activations (same values) is kept for the weight gradient
+            from ..ops.gemm_mxfp8 import quantize_mxfp8
+            from . import fused
+            x_op, xq = quantize_mxfp8(x2 if x2.is_contiguous() else x2.contiguous(), dequantized=True)
+            y = fused.gemm_rs_mxfp8(x_op, cached_weight_operand(w, quant), pc)
+        else:
+            xq = fake_quant(x2, quant) if quant is not None else x2
+            y = gemm_rs(xq, wq, pc, b_mn=True)
         ctx.save_for_backward(xq, wq)
         ctx.pc, ctx.w_ref, ctx.shape, ctx.quant = pc, w, (S, B, K), quant
         return y.view(S // pc.tp_size, B, -1)

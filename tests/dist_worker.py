@@ -102,6 +102,22 @@ def mode_fused(pc, dev):
         torch.cuda.synchronize()
         assert torch.equal(x_full, xq_all), f"gathered quantised rows differ ({Ml}, {K}, {N})"
         assert torch.equal(y, y_ref) and torch.equal(pre, pre_ref), f"quantised all-gather GEMM differs ({Ml}, {K}, {N})"
+    # block-scaled GEMM -> reduce-scatter: every rank holds a K-slice of both operands, quantised along K
+    from elfa_b200.ops.gemm_mxfp8 import dequantize_mxfp8
+    for it, (Ml, Kl, N) in enumerate([(128, 128, 256), (256, 512, 4096), (1024, 1376, 4096), (128, 96, 192), (2048, 512, 4096)]):
+        g = torch.Generator(device="cpu").manual_seed(500 + it * 8 + rank)
+        a = torch.randn(Ml * world, Kl, generator=g).to(torch.bfloat16).to(dev)
+        w = (torch.randn(N, Kl, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+        a_op, _ = quantize_mxfp8(a)
+        w_op, _ = quantize_mxfp8(w, right=True)
+        assert fused.supported_rs_mxfp8(Ml * world, Kl, N, world)
+        o = fused.gemm_rs_mxfp8(a_op, w_op, pc)
+        part = dequantize_mxfp8(a_op).double() @ dequantize_mxfp8(w_op).double().t()
+        dist.all_reduce(part, group=pc.tp_group)
+        ref = part[rank * Ml:(rank + 1) * Ml].float()
+        torch.cuda.synchronize()
+        e = (o.float() - ref).abs().max().item()
+        assert e <= 2.0 ** -7 * ref.abs().max().item(), f"block-scaled gemm_rs ({Ml}, {Kl}, {N}): {e} vs {ref.abs().max().item()}"
     st = native.status()
     assert st == 0, f"device status 0x{st:x}"
     dist.barrier()
