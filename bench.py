@@ -170,6 +170,27 @@ def self_check(pc, cfg, mb: int, dev) -> dict:
     return res
 
 
+def roofline(cfg, tokens_per_s: float, world: int, bf16_peak: float, baseline: bool) -> dict:
+    """Per-class roofline of the GPT family: the FLOPs of one token split by the precision they run at, each class against its
+    own peak - bf16 against the measured sustained cuBLAS rate, block-scaled e4m3 against twice that (the nominal fp8 : bf16
+    ratio; no fp8 peak is measured on the machine). ``fraction`` = time at peak / measured time."""
+    m = cfg.model
+    D, F, L, V, S = m.hidden_dim, m.intermediate_dim, m.num_layers, m.vocab_size, cfg.data.seq_len
+    up = 2 if m.activation == "swiglu" else 1
+    lin = 2.0 * L * ((1 + 2 * m.num_kv_heads / m.num_heads) * D * D + D * D + (up + 1) * D * F)   # one pass over the layers' weights
+    head = 2.0 * D * V
+    attn = 3.0 * L * 2 * S * D                                                      # causal attention, forward + backward
+    q_fwd = not baseline and cfg.quant.attention in ("mxfp8", "nvfp4") and cfg.quant.mlp in ("mxfp8", "nvfp4")
+    q_bwd = q_fwd and cfg.quant.backward == "mxfp8"
+    fp8 = lin * ((1 if q_fwd else 0) + (1 if q_bwd else 0))                          # forward and input-gradient products
+    bf16 = 3.0 * lin - fp8 + 3.0 * head + attn                                       # weight gradients, head, attention, the rest
+    t_peak = fp8 / (2.0 * bf16_peak) + bf16 / bf16_peak          # seconds per token on one GPU with every class at its peak
+    per_gpu = tokens_per_s / world
+    return {"flops_per_token": {"block_scaled_e4m3": fp8, "bf16": bf16},
+            "peaks_tflops": {"bf16_measured_sustained": bf16_peak / 1e12, "e4m3_nominal_2x": 2.0 * bf16_peak / 1e12},
+            "fraction": t_peak * per_gpu}
+
+
 def plan_run(cfg, yaml_tp: int, yaml_world: int, world: int, micro_batch: int = 0, keep_global_batch: bool = False):
     """Chooses the parallel layout for ``world`` GPUs from the sizes the configuration FILE names (``yaml_tp``,
     ``yaml_world``: read before any launcher variable touches them) and writes it into ``cfg``.
@@ -392,6 +413,7 @@ def main() -> int:
             # the FLOP model covers the GPT family (dense GEMMs + softmax attention) only
             "mfu_of_measured_sustained_bf16": value * flops / (peak * world) if cfg.mixer() == "attention" else None,
             "model_tflops_per_gpu": value * flops / world / 1e12 if cfg.mixer() == "attention" else None,
+            "roofline": roofline(cfg, value, world, peak, baseline) if cfg.mixer() == "attention" else None,
             "loss": loss, "loss_first_step": first_loss, "device_status": st,
             "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
         }
