@@ -19,6 +19,7 @@
 // tensor memory (tcgen05.ld / multiply / tcgen05.st), which is rare after the first blocks. Each
 // S row is read from tensor memory once.
 // Every wait is bounded (status word + abort flag), as in the GEMM.
+#include <cstdlib>
 #include <type_traits>
 
 #include "common.cuh"
@@ -61,7 +62,10 @@ struct AttnSmem {
   static constexpr int DYN = TOTAL + 1024;
 };
 
-template <int HDP>
+// PT = true: the probabilities stay in tensor memory - each softmax thread writes its row's bf16 P over the first 64 columns
+// of the S tile it came from (two values per 32-bit column) and the P V product reads its A operand from there - instead of
+// going through a 128-byte-swizzled shared-memory tile and an async-proxy fence.
+template <int HDP, bool PT>
 __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnFwdParams p) {
   using L = AttnSmem<HDP>;
   constexpr int NSUB = L::NSUB;
@@ -155,8 +159,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
             const uint32_t poff = (kk / 4) * SUB_BYTES + (kk % 4) * 32;
-            tc_mma_f16(TM_O[t], make_smem_desc(pb + poff, 16, 1024, 2), make_smem_desc(vb + kk * 2048, SUB_BYTES, 1024, 2), idesc_o,
-                       (j != j0 || kk != 0) ? 1u : 0u);
+            if (PT)   // A = P from tensor memory: 16 keys of this K step = 8 columns
+              tc_mma_f16_ts(TM_O[t], TM_S[t] + kk * 8, make_smem_desc(vb + kk * 2048, SUB_BYTES, 1024, 2), idesc_o,
+                            (j != j0 || kk != 0) ? 1u : 0u);
+            else
+              tc_mma_f16(TM_O[t], make_smem_desc(pb + poff, 16, 1024, 2), make_smem_desc(vb + kk * 2048, SUB_BYTES, 1024, 2), idesc_o,
+                         (j != j0 || kk != 0) ? 1u : 0u);
           }
           tc_commit(bar(BAR_OFULL0 + t));
         }
@@ -309,15 +317,24 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
               r[i + 1] = __float_as_uint(e1);
             }
           }
+          if (PT) {
+            // this chunk's 32 probabilities as 16 packed words over columns [16 c, 16 c + 16) of the row's own S tile: those
+            // columns held S values of chunks this thread has already consumed (chunk c sits at columns [32 c, 32 c + 32))
+            uint32_t w[16];
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int q8 = c * 4 + g;  // 16-byte chunk index along the 128 keys
-            const uint32_t addr = p_row + (q8 >> 3) * SUB_BYTES + (((q8 & 7) ^ (row_local & 7)) << 4);
-            const uint32_t w0 = pack_bf16(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
-            const uint32_t w1 = pack_bf16(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
-            const uint32_t w2 = pack_bf16(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
-            const uint32_t w3 = pack_bf16(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+            for (int i = 0; i < 16; ++i) w[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+            tmem_st16(TM_S[t] + lane_addr + 16 * c, w);
+          } else {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int q8 = c * 4 + g;  // 16-byte chunk index along the 128 keys
+              const uint32_t addr = p_row + (q8 >> 3) * SUB_BYTES + (((q8 & 7) ^ (row_local & 7)) << 4);
+              const uint32_t w0 = pack_bf16(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
+              const uint32_t w1 = pack_bf16(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
+              const uint32_t w2 = pack_bf16(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
+              const uint32_t w3 = pack_bf16(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+            }
           }
         }
       };
@@ -328,7 +345,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
         unpack_f32x2(lsp[1], a2, a3);
         l += ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3])) + ((a0 + a1) + (a2 + a3));
       }
-      fence_proxy_async();
+      if (PT) tmem_st_wait(); else fence_proxy_async();
       tc_fence_before();
       mbar_arrive(bar(BAR_PREADY0 + t));
     }
@@ -371,10 +388,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
   }
 }
 
-template <int HDP>
+template <int HDP, bool PT>
 int launch_attn_fwd(const CUtensorMap& tm, const AttnFwdParams& p, cudaStream_t stream) {
   using L = AttnSmem<HDP>;
-  auto kern = attn_fwd_kernel<HDP>;
+  auto kern = attn_fwd_kernel<HDP, PT>;
   static bool configured = false;
   if (!configured) {
     ELFA_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
@@ -430,7 +447,10 @@ ELFA_API int elfa_attention_fwd_ex(const void* qkv, long long stride_s, long lon
   p.n_qtiles = (S + 127) / 128;
   p.status = st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return hd <= 64 ? launch_attn_fwd<64>(tm, p, s) : launch_attn_fwd<128>(tm, p, s);
+  // ELFA_ATTN_P_TMEM=1: probabilities through tensor memory instead of shared memory (see the kernel's PT parameter)
+  const char* e = getenv("ELFA_ATTN_P_TMEM");
+  if (e && e[0] == '1') return hd <= 64 ? launch_attn_fwd<64, true>(tm, p, s) : launch_attn_fwd<128, true>(tm, p, s);
+  return hd <= 64 ? launch_attn_fwd<64, false>(tm, p, s) : launch_attn_fwd<128, false>(tm, p, s);
 }
 
 ELFA_API int elfa_attention_fwd(const void* qkv, long long stride_s, long long stride_b, void* out, long long o_stride_s,

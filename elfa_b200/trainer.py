@@ -120,7 +120,9 @@ class Trainer:
                 per_block = n_est // max(cfg.model.num_layers, 1) + (1 << 20)
                 arena3 = SymmetricArena.for_group(pc.dp_group, device, n_est * esz // pc.dp_size + 3 * per_block * 4 + n_est * 4 // 4 +
                                                      2 * per_block * 2 + n_est * 2 // 4 + (64 << 20))
-            self.flat = Zero3Shards(self.model, pc, arena=arena3, shard_params=cfg.runtime.zero_stage == 3)
+            # ELFA_ZERO3_PREFETCH=0 (measurement aid): gathers and reduce-scatters run on the compute stream, nothing overlaps
+            self.flat = Zero3Shards(self.model, pc, arena=arena3, shard_params=cfg.runtime.zero_stage == 3,
+                                    prefetch=os.environ.get("ELFA_ZERO3_PREFETCH", "1") not in ("0", ""))
         else:
             self.flat = FlatParams(self.model.named_checkpoint_parameters(), dp_size=pc.dp_size, dp_rank=pc.dp_rank, allocator=dp_arena)
         self.zero3 = bool(getattr(self.flat, "presharded", False))
