@@ -18,6 +18,8 @@ struct StepScalars {   // device-resident scalars shared by the kernels of one o
   float clip_coef;     // min(1, max_norm / norm) * inv_loss_scale
   float grad_norm;     // unscaled global gradient norm (for telemetry)
   int skip;            // 1 if the norm is not finite -> every update kernel leaves state untouched
+  float lr;            // learning rate of this step, read by the Lion / Muon kernels when their `lr` argument is negative:
+                       // a captured CUDA graph of the update then follows the schedule without being captured again
 };
 
 __device__ __forceinline__ float sumsq16(const uint4& v, float) {
@@ -168,6 +170,7 @@ __global__ void __launch_bounds__(256) lion_kernel(ParamT* __restrict__ param, f
   if (scal) {
     if (scal->skip) return;
     gscale = scal->clip_coef;
+    if (lr < 0.f) lr = scal->lr;
   }
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
@@ -247,6 +250,7 @@ __global__ void __launch_bounds__(256) muon_apply_kernel(ParamT* __restrict__ pa
                                                          const __nv_bfloat16* __restrict__ y, long long n, float lr,
                                                          const StepScalars* __restrict__ scal) {
   if (scal && scal->skip) return;
+  if (scal && lr < 0.f) lr = scal->lr;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
     const float p = master[i] - lr * __bfloat162float(y[i]);

@@ -26,6 +26,7 @@ struct PeerPtrs {
 struct StepScalarsZ {   // same layout as the optimizer's scalars
   float sumsq, clip_coef, grad_norm;
   int skip;
+  float lr;
 };
 
 // One thread per peer: announce arrival to the peer, then wait for the peer's announcement.

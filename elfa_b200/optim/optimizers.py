@@ -45,13 +45,14 @@ class _Base:
         self.lr, self.weight_decay, self.max_grad_norm = lr, weight_decay, max_grad_norm
         self.step_count = 0
         self.loss_scale = 1.0
+        self.lr_on_device = False      # Lion / Muon kernels read the learning rate from scalars[4] (CUDA-graph replay)
         dev = flat.device
         self.sharded = self.zero_stage >= 1
         self.lo, self.hi = (flat.shard_lo, flat.shard_hi) if self.sharded else (0, flat.numel)
         n = self.hi - self.lo
         self.master_is_param = flat.dtype == torch.float32
         self.master = flat.flat[self.lo:self.hi] if self.master_is_param else flat.flat[self.lo:self.hi].float()
-        self.scalars = torch.zeros(4, dtype=torch.float32, device=dev)     # sumsq, clip_coef, grad_norm, skip
+        self.scalars = torch.zeros(8, dtype=torch.float32, device=dev)     # sumsq, clip_coef, grad_norm, skip, lr (graph replay)
         self.part = torch.zeros(4096, dtype=torch.float32, device=dev)
         self.n_local = n
         self.last_grad_norm = 0.0
@@ -309,7 +310,8 @@ class Lion(_Base):
             wdv = self.weight_decay if wd else 0.0
             if g.is_cuda:
                 lib.call("elfa_lion", pout[s:e] if pout is not None else None, ptype, self.master[s:e], self.m[s:e], g, _ptype(g),
-                         e - s, float(self.lr), float(b1), float(b2), float(wdv), self.scalars, stream_ptr(g))
+                         e - s, -1.0 if self.lr_on_device else float(self.lr), float(b1), float(b2), float(wdv), self.scalars,
+                         stream_ptr(g))
             else:
                 if self.skipped():
                     continue
@@ -400,7 +402,8 @@ class Muon(_Base):
                     yp[:rows, :cols] = y.view(rows, cols)
                     y2 = newton_schulz(yp, self.iterations)[:rows, :cols]
                 pout = None if self.master_is_param else p.data.view(-1)
-                lib.call("elfa_muon_apply", pout, 0 if pout is None else 1, master, y2.contiguous(), n, float(self.lr), self.scalars, st)
+                lib.call("elfa_muon_apply", pout, 0 if pout is None else 1, master, y2.contiguous(), n,
+                         -1.0 if self.lr_on_device else float(self.lr), self.scalars, st)
             else:
                 if self.skipped():
                     continue
@@ -439,6 +442,7 @@ class LionMuon:
         self.flat, self.pc = flat, self.muon.pc
         self.step_count = 0
         self.lr = lr
+        self._graph = None
 
     @property
     def loss_scale(self):
@@ -453,7 +457,15 @@ class LionMuon:
     def scalars(self):
         return self.muon.scalars
 
+    def _updates(self) -> None:
+        self.muon._update()
+        self.lion._update()
+
     def step(self, lr: Optional[float] = None) -> None:
+        """The update itself is hundreds to thousands of small launches (momentum, 2 x iterations Newton-Schulz products and
+        an apply per matrix). On a GPU it is captured once into a CUDA graph - after one eager step that has loaded every
+        kernel and filled the caches - and replayed afterwards; the learning rate travels through the device scalars.
+        ``ELFA_OPT_GRAPH=0`` keeps it eager."""
         if lr is not None:
             self.lr = lr
         self.muon.lr = self.lion.lr = self.lr
@@ -462,8 +474,20 @@ class LionMuon:
         self.muon._norm_and_clip()
         self.step_count += 1
         self.muon.step_count = self.lion.step_count = self.step_count
-        self.muon._update()
-        self.lion._update()
+        import os
+        use_graph = self.flat.flat.is_cuda and os.environ.get("ELFA_OPT_GRAPH", "1") not in ("0", "")
+        if not use_graph or self.step_count == 1:
+            self._updates()
+        else:
+            self.muon.scalars[4] = float(self.lr)
+            if self._graph is None:
+                self.muon.lr_on_device = self.lion.lr_on_device = True
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._updates()
+                self._graph = g
+            self._graph.replay()
         from ..quant.qat import new_weight_epoch
         new_weight_epoch()
 

@@ -98,6 +98,38 @@ def test_efla_model_trains_on_gpu(cuda_device):
         assert abs(a - b) < 0.08 * abs(b), losses
 
 
+def test_lion_muon_update_replayed_from_a_cuda_graph_equals_eager(cuda_device, monkeypatch):
+    """The Lion + Muon update is captured into a CUDA graph at the second step and replayed afterwards (learning rate through the
+    device scalars, so the schedule is followed): same losses and weights as launching every kernel eagerly."""
+    import os
+    import warnings
+    warnings.simplefilter("ignore")
+    from elfa_b200.config import Config
+    from elfa_b200.trainer import Trainer
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def run(graph):
+        monkeypatch.setenv("ELFA_OPT_GRAPH", "1" if graph else "0")
+        cfg = Config.from_file(os.path.join(root, "configs", "smoke.yaml"), env_override=False)
+        cfg.model.dtype = "bf16"
+        cfg.checkpoint.dir = ""
+        cfg.telemetry.log_file = ""
+        cfg.bench.synthetic = "uniform"
+        cfg.data.seq_len = 32
+        cfg.training.lr_schedule = "linear_warmup_cosine"       # the learning rate changes every step
+        cfg.training.warmup_steps = 2
+        cfg.training.total_steps = 6
+        tr = Trainer(cfg, device=cuda_device, telemetry=False)
+        losses = tr.run(max_steps=5)
+        assert (tr.optimizer._graph is not None) == graph
+        return losses, tr.flat.flat.float().clone()
+    la, wa = run(True)
+    lb, wb = run(False)
+    assert native.status() == 0
+    assert la == lb, (la, lb)
+    assert torch.equal(wa, wb)
+
+
 def test_prism_refine_kernel_matches_reference(cuda_device):
     from elfa_b200.ops import efla as eops
     torch.manual_seed(0)
