@@ -403,9 +403,9 @@ class BaselineTrainer:
                 g.div_(self.dp)
         gs = g[self.lo:self.hi]
         rep_hi = min(max(self.rep_numel, self.lo), self.hi)
-        sq = gs[rep_hi - self.lo:].double().pow(2).sum()
+        sq = torch.linalg.vector_norm(gs[rep_hi - self.lo:]).double() ** 2          # no full-size temporaries
         if self.tp_rank == 0 and rep_hi > self.lo:
-            sq = sq + gs[:rep_hi - self.lo].double().pow(2).sum()
+            sq = sq + torch.linalg.vector_norm(gs[:rep_hi - self.lo]).double() ** 2
         if self.world > 1 and (self.tp > 1 or self.stage >= 1):
             dist.all_reduce(sq, group=None if self.stage >= 1 else self.tp_group)
         norm = sq.sqrt().float()

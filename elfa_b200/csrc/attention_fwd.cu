@@ -447,9 +447,10 @@ ELFA_API int elfa_attention_fwd_ex(const void* qkv, long long stride_s, long lon
   p.n_qtiles = (S + 127) / 128;
   p.status = st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // ELFA_ATTN_P_TMEM=1: probabilities through tensor memory instead of shared memory (see the kernel's PT parameter)
+  // probabilities through tensor memory (the kernel's PT parameter; measured 3.5 % faster at S 4096, 32 heads, hd 128);
+  // ELFA_ATTN_P_TMEM=0 selects the shared-memory form
   const char* e = getenv("ELFA_ATTN_P_TMEM");
-  if (e && e[0] == '1') return hd <= 64 ? launch_attn_fwd<64, true>(tm, p, s) : launch_attn_fwd<128, true>(tm, p, s);
+  if (!(e && e[0] == '0')) return hd <= 64 ? launch_attn_fwd<64, true>(tm, p, s) : launch_attn_fwd<128, true>(tm, p, s);
   return hd <= 64 ? launch_attn_fwd<64, false>(tm, p, s) : launch_attn_fwd<128, false>(tm, p, s);
 }
 

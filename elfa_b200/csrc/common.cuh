@@ -420,6 +420,37 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 // ---- misc -------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b);
+
+// Epilogue helper of the GEMM kernels. A warp holds 32 rows x 64 accumulator columns (lane = row, two 32-column chunks) and
+// has to write them as bf16 into a row-major matrix. Stored straight from registers, every instruction would touch 32
+// different rows with 16 bytes each; through the warp's private 4 KB of shared memory (128-byte swizzle, no bank conflicts,
+// only __syncwarp) every store instruction writes four whole 128-byte lines instead: an eighth of the memory requests.
+//   stage: shared address of this warp's 4 KB; dst: element (row 0 of the warp's 32 rows, first of the 64 columns);
+//   rows_valid / cols_valid: how many of the 32 rows / 64 columns lie inside the matrix (cols_valid a multiple of 8).
+__device__ __forceinline__ void warp_stage_64cols(uint32_t stage, const uint32_t (&ra)[32], const uint32_t (&rb)[32], float alpha, int lane) {
+  const uint32_t row = stage + lane * 128;
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const uint32_t* r = u < 4 ? ra + u * 8 : rb + (u - 4) * 8;
+    const uint32_t w0 = pack_bf16(__uint_as_float(r[0]) * alpha, __uint_as_float(r[1]) * alpha);
+    const uint32_t w1 = pack_bf16(__uint_as_float(r[2]) * alpha, __uint_as_float(r[3]) * alpha);
+    const uint32_t w2 = pack_bf16(__uint_as_float(r[4]) * alpha, __uint_as_float(r[5]) * alpha);
+    const uint32_t w3 = pack_bf16(__uint_as_float(r[6]) * alpha, __uint_as_float(r[7]) * alpha);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row + ((u ^ (lane & 7)) << 4)), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+  }
+}
+__device__ __forceinline__ void warp_flush_64cols(uint32_t stage, __nv_bfloat16* dst, long long ld, int rows_valid, int cols_valid, int lane) {
+  const int u = lane & 7;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int r = it * 4 + (lane >> 3);
+    uint32_t w0, w1, w2, w3;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(stage + r * 128 + ((u ^ (r & 7)) << 4)) : "memory");
+    if (r < rows_valid && u * 8 + 8 <= cols_valid) *reinterpret_cast<uint4*>(dst + (long long)r * ld + u * 8) = make_uint4(w0, w1, w2, w3);
+  }
+}
+
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {

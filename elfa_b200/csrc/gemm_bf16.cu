@@ -499,36 +499,30 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
-      if (fl == 0) {
-        // plain bf16 output: convert and store, two register buffers alternating so that the next 32 accumulator columns
-        // are in flight while these are stored; no per-element branches (narrow-K products are bound by this loop)
+      if (fl == 0 && COMM != COMM_AG) {
+        // plain bf16 output (narrow-K products are bound by this loop): 64 accumulator columns at a time go through the warp's
+        // private 4 KB of the staging area and leave as whole 128-byte lines; the next 64 columns are requested from tensor
+        // memory before the lines are written. (The all-gather variant's push warps own the staging area: it keeps the
+        // register path below.)
         const uint32_t tcol0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * ACC_STRIDE;
-        __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc;
-        const float alpha = p.alpha;
-        auto store_chunk = [&](const uint32_t (&r)[32], int c) {
-          const int col0 = n0 + c * 32;
-          if (!row_ok || col0 >= p.N) return;
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int col = col0 + g * 8;
-            if (col + 8 > p.N) continue;
-            const uint4 o = make_uint4(pack_bf16(__uint_as_float(r[g * 8 + 0]) * alpha, __uint_as_float(r[g * 8 + 1]) * alpha),
-                                       pack_bf16(__uint_as_float(r[g * 8 + 2]) * alpha, __uint_as_float(r[g * 8 + 3]) * alpha),
-                                       pack_bf16(__uint_as_float(r[g * 8 + 4]) * alpha, __uint_as_float(r[g * 8 + 5]) * alpha),
-                                       pack_bf16(__uint_as_float(r[g * 8 + 6]) * alpha, __uint_as_float(r[g * 8 + 7]) * alpha));
-            *reinterpret_cast<uint4*>(crow + col) = o;
-          }
-        };
+        const uint32_t stage = smem_u32(smem + L::OUT_OFF) + q * 4096;
+        const int row0 = m0 + q * 32;
+        __nv_bfloat16* cbase = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row0 * p.ldc + n0;
+        const int rows_valid = p.M - row0;
         uint32_t ra[32], rb[32];
         tmem_ld32(tcol0, ra);
+        tmem_ld32(tcol0 + 32, rb);
 #pragma unroll
         for (int c = 0; c < BN / 32; c += 2) {
           tmem_ld_wait();
-          tmem_ld32(tcol0 + (c + 1) * 32, rb);
-          store_chunk(ra, c);
-          tmem_ld_wait();
-          if (c + 2 < BN / 32) tmem_ld32(tcol0 + (c + 2) * 32, ra);
-          store_chunk(rb, c + 1);
+          warp_stage_64cols(stage, ra, rb, p.alpha, lane);
+          if (c + 2 < BN / 32) {
+            tmem_ld32(tcol0 + (c + 2) * 32, ra);
+            tmem_ld32(tcol0 + (c + 3) * 32, rb);
+          }
+          __syncwarp();
+          warp_flush_64cols(stage, cbase + c * 32, p.ldc, rows_valid, p.N - n0 - c * 32, lane);
+          __syncwarp();
         }
         tc_fence_before();
         __syncwarp();

@@ -93,7 +93,9 @@ struct QSmem {
   static constexpr int SF_OFF = STAGES * (A_BYTES + B_BYTES);
   static constexpr int BAR_OFF = SF_OFF + STAGES * SF_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 4 + 4;   // ring full / empty, accumulator full / empty, push buffers (all-gather variant)
-  static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16;
+  static constexpr int TOTAL0 = BAR_OFF + NUM_BARS * 8 + 16;
+  static constexpr int EPI_OFF = (TOTAL0 + 127) / 128 * 128;      // epilogue staging: 4 warps x 4 KB (whole-line stores)
+  static constexpr int TOTAL = EPI_OFF + 4 * 4096;
   static constexpr int DYN = TOTAL + 1024;
   static constexpr int PUSH_OFF = (TOTAL + 127) / 128 * 128;      // all-gather variant: 2 warps x 2 buffers of PUSH_PIECE bytes
   static constexpr int DYN_AG = PUSH_OFF + 4 * PUSH_PIECE + 1024;
@@ -335,32 +337,26 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const bool row_ok = row < p.M;
       const uint32_t tcol0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * ACC_STRIDE;
       if (fl == 0) {
-        // plain bf16 output: two register buffers alternating, no per-element branches
-        __nv_bfloat16* crow = p.C + (long long)row * p.ldc;
-        auto store_chunk = [&](const uint32_t (&r)[32], int c) {
-          const int col0 = n0 + c * 32;
-          if (!row_ok || col0 >= p.N) return;
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int col = col0 + g * 8;
-            if (col + 8 > p.N) continue;
-            const uint4 o = make_uint4(pack_bf16(__uint_as_float(r[g * 8 + 0]) * alpha, __uint_as_float(r[g * 8 + 1]) * alpha),
-                                       pack_bf16(__uint_as_float(r[g * 8 + 2]) * alpha, __uint_as_float(r[g * 8 + 3]) * alpha),
-                                       pack_bf16(__uint_as_float(r[g * 8 + 4]) * alpha, __uint_as_float(r[g * 8 + 5]) * alpha),
-                                       pack_bf16(__uint_as_float(r[g * 8 + 6]) * alpha, __uint_as_float(r[g * 8 + 7]) * alpha));
-            *reinterpret_cast<uint4*>(crow + col) = o;
-          }
-        };
+        // plain bf16 output: 64 accumulator columns at a time through the warp's private 4 KB of shared memory, written as
+        // whole 128-byte lines (common.cuh: warp_stage_64cols / warp_flush_64cols)
+        const uint32_t stage = smem_u32(smem + L::EPI_OFF) + q * 4096;
+        const int row0 = m0 + q * 32;
+        __nv_bfloat16* cbase = p.C + (long long)row0 * p.ldc + n0;
+        const int rows_valid = p.M - row0;
         uint32_t ra[32], rb[32];
         tmem_ld32(tcol0, ra);
+        tmem_ld32(tcol0 + 32, rb);
 #pragma unroll
         for (int c = 0; c < BN / 32; c += 2) {
           tmem_ld_wait();
-          tmem_ld32(tcol0 + (c + 1) * 32, rb);
-          store_chunk(ra, c);
-          tmem_ld_wait();
-          if (c + 2 < BN / 32) tmem_ld32(tcol0 + (c + 2) * 32, ra);
-          store_chunk(rb, c + 1);
+          warp_stage_64cols(stage, ra, rb, alpha, lane);
+          if (c + 2 < BN / 32) {
+            tmem_ld32(tcol0 + (c + 2) * 32, ra);
+            tmem_ld32(tcol0 + (c + 3) * 32, rb);
+          }
+          __syncwarp();
+          warp_flush_64cols(stage, cbase + c * 32, p.ldc, rows_valid, p.N - n0 - c * 32, lane);
+          __syncwarp();
         }
         tc_fence_before();
         __syncwarp();
