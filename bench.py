@@ -101,7 +101,7 @@ def reference_arm(args) -> int:
 
 # Loss of the very first step (random-init weights, seeded data, no update yet) measured on one GPU; a run at any N must
 # reproduce it: the initial weights and the data do not depend on the parallel layout.
-FIRST_STEP_LOSS = {}
+FIRST_STEP_LOSS = {"gpt-7b-tp8-mxfp8": (10.8394, 0.02)}
 
 
 def self_check(pc, cfg, mb: int, dev) -> dict:
@@ -161,6 +161,17 @@ def self_check(pc, cfg, mb: int, dev) -> dict:
     e, b = rel(o, ref)
     b *= 2.0      # the partial products travel as bf16: one more rounding per rank
     res["gemm_rs"] = {"max_err": e, "bound": b, "ok": e <= b}
+    # the same with block-scaled MXFP8 operands, against the fp32 sum of the products of the dequantised operands
+    if fused.supported_rs_mxfp8(M, F // world, D, world):
+        from elfa_b200.ops.gemm_mxfp8 import dequantize_mxfp8
+        a_op, _ = quantize_mxfp8(a)
+        w_op, _ = quantize_mxfp8(w2.t().contiguous(), right=True)
+        o = fused.gemm_rs_mxfp8(a_op, w_op, pc)
+        gemm(dequantize_mxfp8(a_op), dequantize_mxfp8(w_op), out=part)
+        dist.all_reduce(part, group=pc.tp_group)
+        e, b = rel(o, part[rank * Ml:(rank + 1) * Ml])
+        b *= 2.0
+        res["gemm_rs_mxfp8"] = {"max_err": e, "bound": b, "ok": e <= b}
     pc.comm_backend = saved
     ok = torch.tensor([1.0 if all(v["ok"] for v in res.values()) else 0.0], device=dev)
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
