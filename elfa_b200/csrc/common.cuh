@@ -428,18 +428,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b);
 // only __syncwarp) every store instruction writes four whole 128-byte lines instead: an eighth of the memory requests.
 //   stage: shared address of this warp's 4 KB; dst: element (row 0 of the warp's 32 rows, first of the 64 columns);
 //   rows_valid / cols_valid: how many of the 32 rows / 64 columns lie inside the matrix (cols_valid a multiple of 8).
-__device__ __forceinline__ void warp_stage_64cols(uint32_t stage, const uint32_t (&ra)[32], const uint32_t (&rb)[32], float alpha, int lane) {
-  const uint32_t row = stage + lane * 128;
-#pragma unroll
-  for (int u = 0; u < 8; ++u) {
-    const uint32_t* r = u < 4 ? ra + u * 8 : rb + (u - 4) * 8;
-    const uint32_t w0 = pack_bf16(__uint_as_float(r[0]) * alpha, __uint_as_float(r[1]) * alpha);
-    const uint32_t w1 = pack_bf16(__uint_as_float(r[2]) * alpha, __uint_as_float(r[3]) * alpha);
-    const uint32_t w2 = pack_bf16(__uint_as_float(r[4]) * alpha, __uint_as_float(r[5]) * alpha);
-    const uint32_t w3 = pack_bf16(__uint_as_float(r[6]) * alpha, __uint_as_float(r[7]) * alpha);
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row + ((u ^ (lane & 7)) << 4)), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
-  }
-}
 __device__ __forceinline__ void warp_flush_64cols(uint32_t stage, __nv_bfloat16* dst, long long ld, int rows_valid, int cols_valid, int lane) {
   const int u = lane & 7;
 #pragma unroll
@@ -475,6 +463,23 @@ __device__ __forceinline__ float dgelu_tanh(float x) {
   const float u = k * (x + 0.044715f * x * x2);
   const float t = tanh_fast(u);
   return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * k * (1.0f + 3.0f * 0.044715f * x2);
+}
+// GELU = true: tanh-GELU after the scale (the activation output of an MLP-up product)
+template <bool GELU = false>
+__device__ __forceinline__ void warp_stage_64cols(uint32_t stage, const uint32_t (&ra)[32], const uint32_t (&rb)[32], float alpha, int lane) {
+  const uint32_t row = stage + lane * 128;
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const uint32_t* r = u < 4 ? ra + u * 8 : rb + (u - 4) * 8;
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      f[j] = __uint_as_float(r[j]) * alpha;
+      if (GELU) f[j] = gelu_tanh(f[j]);
+    }
+    const uint32_t w0 = pack_bf16(f[0], f[1]), w1 = pack_bf16(f[2], f[3]), w2 = pack_bf16(f[4], f[5]), w3 = pack_bf16(f[6], f[7]);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row + ((u ^ (lane & 7)) << 4)), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+  }
 }
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

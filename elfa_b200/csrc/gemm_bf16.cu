@@ -499,7 +499,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
-      if (fl == 0 && COMM != COMM_AG) {
+      if (!(fl & ~(ELFA_EPI_GELU | ELFA_EPI_STORE_PREACT)) && COMM != COMM_AG) {
         // plain bf16 output (narrow-K products are bound by this loop): 64 accumulator columns at a time go through the warp's
         // private 4 KB of the staging area and leave as whole 128-byte lines; the next 64 columns are requested from tensor
         // memory before the lines are written. (The all-gather variant's push warps own the staging area: it keeps the
@@ -515,7 +515,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
         for (int c = 0; c < BN / 32; c += 2) {
           tmem_ld_wait();
-          warp_stage_64cols(stage, ra, rb, p.alpha, lane);
+          if (fl & ELFA_EPI_STORE_PREACT) {      // the value before the activation goes out first, through the same staging
+            warp_stage_64cols(stage, ra, rb, p.alpha, lane);
+            __syncwarp();
+            warp_flush_64cols(stage, p.preact + (long long)row0 * p.ldpre + n0 + c * 32, p.ldpre, rows_valid, p.N - n0 - c * 32, lane);
+            __syncwarp();
+          }
+          if (fl & ELFA_EPI_GELU) warp_stage_64cols<true>(stage, ra, rb, p.alpha, lane);
+          else warp_stage_64cols(stage, ra, rb, p.alpha, lane);
           if (c + 2 < BN / 32) {
             tmem_ld32(tcol0 + (c + 2) * 32, ra);
             tmem_ld32(tcol0 + (c + 3) * 32, rb);

@@ -336,8 +336,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t tcol0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * ACC_STRIDE;
-      if (fl == 0) {
-        // plain bf16 output: 64 accumulator columns at a time through the warp's private 4 KB of shared memory, written as
+      if (!(fl & ELFA_EPI_BIAS)) {
+        // bf16 output (optionally the pre-activation too): 64 accumulator columns at a time through the warp's private 4 KB of shared memory, written as
         // whole 128-byte lines (common.cuh: warp_stage_64cols / warp_flush_64cols)
         const uint32_t stage = smem_u32(smem + L::EPI_OFF) + q * 4096;
         const int row0 = m0 + q * 32;
@@ -349,7 +349,14 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
         for (int c = 0; c < BN / 32; c += 2) {
           tmem_ld_wait();
-          warp_stage_64cols(stage, ra, rb, alpha, lane);
+          if (fl & ELFA_EPI_STORE_PREACT) {
+            warp_stage_64cols(stage, ra, rb, alpha, lane);
+            __syncwarp();
+            warp_flush_64cols(stage, p.preact + (long long)row0 * p.ldpre + n0 + c * 32, p.ldpre, rows_valid, p.N - n0 - c * 32, lane);
+            __syncwarp();
+          }
+          if (fl & ELFA_EPI_GELU) warp_stage_64cols<true>(stage, ra, rb, alpha, lane);
+          else warp_stage_64cols(stage, ra, rb, alpha, lane);
           if (c + 2 < BN / 32) {
             tmem_ld32(tcol0 + (c + 2) * 32, ra);
             tmem_ld32(tcol0 + (c + 3) * 32, rb);
