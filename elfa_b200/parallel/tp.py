@@ -235,7 +235,6 @@ class _ColumnParallelSP(torch.autograd.Function):
     def forward(ctx, x, w, pc, act, quant):
         Sl, B, D = x.shape
         x2 = x.reshape(Sl * B, D)
-        wq = cached_weight_quant(w, quant) if quant is not None else w
         if _quantised_gather(x2, w, pc, quant):
             # quantise before sending: e4m3 payloads and scales cross NVLink (half the bytes), the product runs on
             # the block-scaled tensor-core path; x_full is the bf16 form of the gathered quantised rows
@@ -243,15 +242,19 @@ class _ColumnParallelSP(torch.autograd.Function):
             y, x_full, pre = fused.ag_gemm_mxfp8(x2, cached_weight_operand(w, quant), pc, act=act, preact=True)
         else:
             xq = fake_quant(x2, quant) if quant is not None else x2
+            wq = cached_weight_quant(w, quant) if quant is not None else w
             y, x_full, pre = ag_gemm(xq, wq, pc, b_mn=True, act=act, preact=True, defer_copy=True)   # backward waits for the copy
-        ctx.save_for_backward(x_full, wq, pre)
+        # the bf16 fake-quantised copy of the weight is not kept: paths that need it ask the per-step cache again
+        ctx.save_for_backward(x_full, pre)
         ctx.pc, ctx.w_ref, ctx.shape, ctx.quant = pc, w, (Sl, B, D), quant
         return y.view(Sl * pc.tp_size, B, -1)
 
     @staticmethod
     def backward(ctx, dy):
-        x_full, wq, pre = ctx.saved_tensors
+        x_full, pre = ctx.saved_tensors
         pc = ctx.pc
+        wdt = ctx.w_ref.dtype
+        wq = None
         if pc.comm_backend == "fused" and x_full.is_cuda:
             from . import fused
             fused.wait_pending_copies(pc)        # x_full may have been copied on a side stream
@@ -274,9 +277,11 @@ class _ColumnParallelSP(torch.autograd.Function):
             if dy_op is not None and use_block_scaled_bwd(dy2, ctx.w_ref, ctx.quant) and _block_scaled_rs(pc, dy2.shape[0], dy2.shape[1], ctx.w_ref.shape[0]):
                 from . import fused
                 dx = fused.gemm_rs_mxfp8(dy_op, cached_weight_operand_bwd(ctx.w_ref, ctx.quant), pc)     # block-scaled dy @ w^T
-                dw = _wgrad(ctx.w_ref, x_full, dy2, wq.dtype)
+                dw = _wgrad(ctx.w_ref, x_full, dy2, wdt)
                 return dx.view(Sl, B, D), dw, None, None, None
             wq = cached_weight_quant_bwd(ctx.w_ref, ctx.quant)
+        if wq is None:
+            wq = cached_weight_quant(ctx.w_ref, ctx.quant) if ctx.quant is not None else ctx.w_ref
         if _overlap_wgrad(pc, dy2) and getattr(ctx.w_ref, "main_grad", None) is not None:
             # the two products are independent: the weight gradient runs on a second stream on the SMs that the
             # (NVLink-bound) reduce-scatter kernel leaves free
@@ -289,12 +294,12 @@ class _ColumnParallelSP(torch.autograd.Function):
             rs_ctas = max(16, (sms * 7 // 16) // 2 * 2)
             side.wait_stream(cur)
             with torch.cuda.stream(side):
-                dw = _wgrad(ctx.w_ref, x_full, dy2, wq.dtype, max_ctas=sms - rs_ctas)
+                dw = _wgrad(ctx.w_ref, x_full, dy2, wdt, max_ctas=sms - rs_ctas)
             dx = gemm_rs(dy2, wq, pc, b_mn=False, max_ctas=rs_ctas)
             cur.wait_stream(side)
         else:
             dx = gemm_rs(dy2, wq, pc, b_mn=False)              # dy @ w^T, summed over ranks, rows scattered
-            dw = _wgrad(ctx.w_ref, x_full, dy2, wq.dtype)
+            dw = _wgrad(ctx.w_ref, x_full, dy2, wdt)
         return dx.view(Sl, B, D), dw, None, None, None
 
 
@@ -305,7 +310,6 @@ class _RowParallelSP(torch.autograd.Function):
     def forward(ctx, x, w, pc, quant):
         S, B, K = x.shape
         x2 = x.reshape(S * B, K)
-        wq = cached_weight_quant(w, quant) if quant is not None else w
         if (quant is not None and quant.fmt == "mxfp8" and use_block_scaled_gemm(x2, w, quant)
                 and _block_scaled_rs(pc, x2.shape[0], x2.shape[1], w.shape[1])):
             # e4m3 payloads and scales straight into the block-scaled MMAs of the fused kernel; the bf16 copy of the quantised
@@ -316,14 +320,15 @@ class _RowParallelSP(torch.autograd.Function):
             y = fused.gemm_rs_mxfp8(x_op, cached_weight_operand(w, quant), pc)
         else:
             xq = fake_quant(x2, quant) if quant is not None else x2
+            wq = cached_weight_quant(w, quant) if quant is not None else w
             y = gemm_rs(xq, wq, pc, b_mn=True)
-        ctx.save_for_backward(xq, wq)
+        ctx.save_for_backward(xq)
         ctx.pc, ctx.w_ref, ctx.shape, ctx.quant = pc, w, (S, B, K), quant
         return y.view(S // pc.tp_size, B, -1)
 
     @staticmethod
     def backward(ctx, dy):
-        xq, wq = ctx.saved_tensors
+        (xq,) = ctx.saved_tensors
         pc = ctx.pc
         S, B, K = ctx.shape
         dy2 = dy.reshape(-1, dy.shape[-1])
@@ -342,8 +347,9 @@ class _RowParallelSP(torch.autograd.Function):
                 _, dyq = quantize_grad(dy2)
                 dx, dy_full, _ = ag_gemm(dyq, cached_weight_quant_bwd(ctx.w_ref, q), pc, b_mn=False, keep=False)
         else:
+            wq = cached_weight_quant(ctx.w_ref, q) if q is not None else ctx.w_ref
             dx, dy_full, _ = ag_gemm(dy2, wq, pc, b_mn=False, keep=False)   # all_gather(dy) @ w^T; dy_full is consumed right below
-        dw = _wgrad(ctx.w_ref, xq, dy_full, wq.dtype)
+        dw = _wgrad(ctx.w_ref, xq, dy_full, ctx.w_ref.dtype)
         return dx.view(S, B, K), dw, None, None
 
 
@@ -353,7 +359,6 @@ class _QuantLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, act, quant):
         x2 = x.reshape(-1, x.shape[-1])
-        wq = cached_weight_quant(w, quant)
         pre = torch.empty((x2.shape[0], w.shape[1]), dtype=x2.dtype, device=x2.device) if act == "gelu" else None
         if use_block_scaled_gemm(x2, w, quant):
             # e4m3 payloads + ue8m0 scales straight into the block-scaled MMA; the bf16 copy of the
@@ -369,17 +374,20 @@ class _QuantLinear(torch.autograd.Function):
                 y = gemm_mxfp8(x_op, cached_weight_operand(w, quant), gelu=act == "gelu", preact=pre)
         else:
             xq = fake_quant(x2, quant)
+            wq = cached_weight_quant(w, quant)
             if act == "gelu":
                 y = gemm(xq, wq, b_mn=True, gelu=True, preact=pre, out_dtype=x2.dtype)
             else:
                 y = gemm(xq, wq, b_mn=True, out_dtype=x2.dtype)
-        ctx.save_for_backward(xq, wq, pre)
+        # the bf16 fake-quantised weight is not kept (2 bytes per parameter on the block-scaled paths for nothing): backward
+        # asks the per-step cache again where it multiplies bf16 operands
+        ctx.save_for_backward(xq, pre)
         ctx.w_ref, ctx.shape, ctx.quant = w, x.shape, quant
         return y.view(*x.shape[:-1], w.shape[1])
 
     @staticmethod
     def backward(ctx, dy):
-        xq, wq, pre = ctx.saved_tensors
+        xq, pre = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
@@ -400,8 +408,8 @@ class _QuantLinear(torch.autograd.Function):
             else:
                 dx = gemm(dy2, cached_weight_quant_bwd(ctx.w_ref, q), out_dtype=dy2.dtype).view(ctx.shape)
         else:
-            dx = gemm(dy2, wq, out_dtype=dy2.dtype).view(ctx.shape)
-        dw = _wgrad(ctx.w_ref, xq, dy2, wq.dtype)
+            dx = gemm(dy2, cached_weight_quant(ctx.w_ref, q), out_dtype=dy2.dtype).view(ctx.shape)
+        dw = _wgrad(ctx.w_ref, xq, dy2, ctx.w_ref.dtype)
         return dx, dw, None, None
 
 
