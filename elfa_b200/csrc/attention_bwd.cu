@@ -109,11 +109,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
   auto bar = [&](int i) { return bar0 + 8u * i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.y, b = blockIdx.z;     // DKV: key / value head; DQ: query head
+  // one-dimensional grid, heaviest outer tile first over the whole grid: every (batch, head) runs its longest tile before any
+  // runs its second longest, so the short CTAs fill the tail of the launch
+  const int n_heads = DKV ? p.Hkv : p.H;
+  const int hb = (int)(blockIdx.x % (unsigned)(n_heads * p.B));
+  const int rank = (int)(blockIdx.x / (unsigned)(n_heads * p.B));
+  const int h = hb % n_heads, b = hb / n_heads;     // DKV: key / value head; DQ: query head
   const int group = p.H / p.Hkv;
   const int kvh = DKV ? h : h / group;
   // outer tile and the inner range it loops over
-  const int outer = DKV ? (int)blockIdx.x : p.n_tiles - 1 - (int)blockIdx.x;   // heaviest first in both modes
+  const int outer = DKV ? rank : p.n_tiles - 1 - rank;   // heaviest first in both modes
   int in_begin = DKV ? (p.causal ? outer : 0) : 0;
   int in_end = DKV ? p.n_tiles : (p.causal ? outer + 1 : p.n_tiles);
   const int* dstart = p.doc_start ? p.doc_start + (long long)b * p.S : nullptr;
@@ -132,7 +137,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmQKV);
     prefetch_tmap(&tmDO);
-    for (int i = 0; i < BB_COUNT; ++i) mbar_init(bar(i), (i == BB_P || i == BB_DS) ? 256 : 1);
+    for (int i = 0; i < BB_COUNT; ++i) mbar_init(bar(i), (i == BB_P || i == BB_DS) ? 8 : 1);   // one arrival per compute warp
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -375,10 +380,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
           tmem_st_wait();
         }
         tc_fence_before();
-        mbar_arrive(bar(BB_P));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BB_P));
       } else {
         tc_fence_before();
-        mbar_arrive(bar(BB_P));            // the S columns have been read: the next S product may overwrite them
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BB_P));            // the S columns have been read: the next S product may overwrite them
       }
       // ---- phase 2: dS = P * (dP - delta) * scale
       if (ok) ok = mbar_wait(bar(BB_DP), it & 1, abort_flag, p.status);
@@ -420,7 +427,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
         tmem_st_wait();
       }
       tc_fence_before();
-      mbar_arrive(bar(BB_DS));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BB_DS));
     }
     // ---------------------------------------------------------------- epilogue
     if (ok) {
@@ -475,7 +483,7 @@ int launch_attn_bwd(const CUtensorMap& tmQKV, const CUtensorMap& tmDO, const Att
     ELFA_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
     configured = true;
   }
-  dim3 grid(p.n_tiles, DKV ? p.Hkv : p.H, p.B);
+  dim3 grid((unsigned)p.n_tiles * (DKV ? p.Hkv : p.H) * p.B);
   kern<<<grid, ATTB_THREADS, L::DYN, stream>>>(tmQKV, tmDO, p);
   ELFA_CUDA(cudaGetLastError());
   ::elfa::count_launches(1);

@@ -52,7 +52,7 @@ constexpr int PUSH_PIECE = 8192;   // bytes per bulk copy
 
 // Push role, run by two warps (`w` = 0 / 1) of every CTA of the grid. Peer rank+1 first, then rank+2, ...
 // so that at any time every GPU receives from one sender. Lane 0 of each warp drives a two-buffer
-// pipeline of bulk copies; after a peer's last piece has landed (store group complete, system fence)
+// pipeline of bulk copies; after a peer's last piece has landed (store groups complete, system fence)
 // warp 0 increments that peer's arrival counter [rank] once: the counter reaches `gridDim.x` more
 // than before when the whole range is there.
 //   buf0        : shared memory of this warp, 2 x PUSH_PIECE bytes, 16-byte aligned
@@ -86,10 +86,28 @@ __device__ __forceinline__ void push_ranges(const char* local_base, const unsign
                  ::"r"(buf0 + b * PUSH_PIECE), "l"(local_base + off), "r"(nb), "r"(bar) : "memory");
     ++n_issued;
   };
+  // Peers are served one after the other without draining the pipeline in between: a peer's counter is raised once the
+  // NEXT peer's stores have been issued and this peer's (older) bulk groups are known to be complete, so the NVLink round
+  // trip of one peer's last pieces overlaps the next peer's transfers.
+  auto wait_all_but = [](uint32_t n) {     // completion of every bulk group except the `n` most recent ones
+    switch (n) {
+      case 0: tma_store_wait<0>(); break;
+      case 1: tma_store_wait<1>(); break;
+      case 2: tma_store_wait<2>(); break;
+      case 3: tma_store_wait<3>(); break;
+      case 4: tma_store_wait<4>(); break;
+      case 5: tma_store_wait<5>(); break;
+      case 6: tma_store_wait<6>(); break;
+      case 7: tma_store_wait<7>(); break;
+      default: tma_store_wait<8>(); break;   // more than asked for: still correct
+    }
+  };
+  int prev_peer = -1;
   for (int i = 1; i < world; ++i) {
     const int peer = (rank + i) % world;
     if (lane == 0) {
       char* dst = reinterpret_cast<char*>(peer_base[peer]);
+      uint32_t stores = 0;
       if (ok && c_first < npieces) issue_load(c_first);
       for (long long c = c_first; c < npieces && ok; c += c_step) {
         if (c + c_step < npieces) issue_load(c + c_step);
@@ -102,13 +120,28 @@ __device__ __forceinline__ void push_ranges(const char* local_base, const unsign
                      ::"l"(dst + off), "r"(buf0 + b * PUSH_PIECE), "r"(nb) : "memory");
         tma_store_commit();
         ++n_done;
+        ++stores;
       }
-      tma_store_wait<0>();                            // every store to this peer has completed
+      if (prev_peer >= 0) {
+        wait_all_but(ok ? stores : 0u);                 // every store to the previous peer has completed
+        __threadfence_system();
+      }
+    }
+    __syncwarp();
+    if (prev_peer >= 0) {
+      named_bar_sync(sync_id, 64);                      // both push warps are done with the previous peer
+      if (w == 0 && lane == 0) flag_bump(peer_flags[prev_peer], rank);
+    }
+    prev_peer = peer;
+  }
+  if (prev_peer >= 0) {
+    if (lane == 0) {
+      tma_store_wait<0>();
       __threadfence_system();
     }
     __syncwarp();
-    named_bar_sync(sync_id, 64);                      // both push warps are done with this peer
-    if (w == 0 && lane == 0) flag_bump(peer_flags[peer], rank);
+    named_bar_sync(sync_id, 64);
+    if (w == 0 && lane == 0) flag_bump(peer_flags[prev_peer], rank);
   }
   if (lane == 0 && !ok) {   // give a load that is still in flight a bounded chance to land before the CTA exits
     for (uint32_t j = n_done; j < n_issued; ++j) {

@@ -161,6 +161,10 @@ int elfa_softmax_rows(const void* x, void* out, long long rows, int cols, long l
 int elfa_p2p_send(const void* src, unsigned long long peer_dst, long long bytes, unsigned long long peer_counter, int* blocks_out,
                   void* stream);
 int elfa_p2p_wait(const void* counter, unsigned int target, int wait_ms, void* stream);
+// Link probe: copy `bytes` to `dst` (a peer address) with per-thread 16-byte stores (mode 0) or a bulk-copy pipeline through
+// shared memory (mode 1: `warps` lanes per CTA, `depth` buffers of `piece` bytes each).
+int elfa_p2p_probe(const void* src, unsigned long long dst, long long bytes, int mode, int ctas, int warps, int piece, int depth,
+                   void* stream);
 
 // ---- prism.cu ----------------------------------------------------------------------------------
 int elfa_prism_fwd(const void* u, const void* v, const unsigned long long* p, void* y, long long tokens, int G, int d, int L,

@@ -782,13 +782,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int col = nb * BN + cc * 64 + unit * 8;
         if (col >= p.N) continue;
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int src = 0; src < cm.world; ++src) {
-          const uint4 q = *reinterpret_cast<const uint4*>(cm.my_recv + src * slot + v * 8);
-          const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+        uint4 q[MAX_RANKS];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            acc[2 * j] += bf16_lo(qw[j]);
-            acc[2 * j + 1] += bf16_hi(qw[j]);
+        for (int src = 0; src < MAX_RANKS; ++src)      // every slot's load in flight before the first add
+          if (src < cm.world) q[src] = *reinterpret_cast<const uint4*>(cm.my_recv + src * slot + v * 8);
+#pragma unroll
+        for (int src = 0; src < MAX_RANKS; ++src) {    // fixed order
+          if (src < cm.world) {
+            const uint32_t qw[4] = {q[src].x, q[src].y, q[src].z, q[src].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              acc[2 * j] += bf16_lo(qw[j]);
+              acc[2 * j + 1] += bf16_hi(qw[j]);
+            }
           }
         }
         uint4 o = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
@@ -801,13 +807,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
         const long long r = v / vec_per_row, cv = v - r * vec_per_row;
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int src = 0; src < cm.world; ++src) {
-          const uint4 q = *reinterpret_cast<const uint4*>(cm.my_recv + src * slot + r * p.N + cv * 8);
-          const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+        uint4 q[MAX_RANKS];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            acc[2 * j] += bf16_lo(qw[j]);
-            acc[2 * j + 1] += bf16_hi(qw[j]);
+        for (int src = 0; src < MAX_RANKS; ++src)      // every slot's load in flight before the first add
+          if (src < cm.world) q[src] = *reinterpret_cast<const uint4*>(cm.my_recv + src * slot + r * p.N + cv * 8);
+#pragma unroll
+        for (int src = 0; src < MAX_RANKS; ++src) {    // fixed order
+          if (src < cm.world) {
+            const uint32_t qw[4] = {q[src].x, q[src].y, q[src].z, q[src].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              acc[2 * j] += bf16_lo(qw[j]);
+              acc[2 * j + 1] += bf16_hi(qw[j]);
+            }
           }
         }
         uint4 o = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));

@@ -59,10 +59,13 @@ __global__ void __launch_bounds__(256) zero_reduce_kernel(PeerPtrs grads, int ra
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += stride) {
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int r = 0; r < world; ++r) {   // fixed order: deterministic sum
-      const float4 g = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + lo + v * 4);
-      s.x += g.x; s.y += g.y; s.z += g.z; s.w += g.w;
-    }
+    float4 g[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r)          // every peer's load in flight before the first add
+      if (r < world) g[r] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + lo + v * 4);
+#pragma unroll
+    for (int r = 0; r < 8; ++r)          // fixed order: deterministic sum
+      if (r < world) { s.x += g[r].x; s.y += g[r].y; s.z += g[r].z; s.w += g[r].w; }
     s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
     reinterpret_cast<float4*>(out)[v] = s;
     acc2 += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
@@ -109,10 +112,13 @@ __global__ void __launch_bounds__(256) zero3_reduce_acc_kernel(PeerPtrs grads, i
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += stride) {
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int r = 0; r < world; ++r) {
-      const float4 g = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + lo + v * 4);
-      s.x += g.x; s.y += g.y; s.z += g.z; s.w += g.w;
-    }
+    float4 g[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r)          // every peer's load in flight before the first add
+      if (r < world) g[r] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + lo + v * 4);
+#pragma unroll
+    for (int r = 0; r < 8; ++r)          // fixed order
+      if (r < world) { s.x += g[r].x; s.y += g[r].y; s.z += g[r].z; s.w += g[r].w; }
     float4 a = reinterpret_cast<float4*>(acc)[v];
     a.x += s.x * scale; a.y += s.y * scale; a.z += s.z * scale; a.w += s.w * scale;
     reinterpret_cast<float4*>(acc)[v] = a;
@@ -137,13 +143,19 @@ __global__ void __launch_bounds__(256) zero3_reduce_acc_bf16_kernel(PeerPtrs sta
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += stride) {
     float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int r = 0; r < world; ++r) {
-      const uint4 q = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(staged.p[r]) + lo + v * 8);
-      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    uint4 q[8];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        s[2 * j] += bf16_lo(w[j]);
-        s[2 * j + 1] += bf16_hi(w[j]);
+    for (int r = 0; r < 8; ++r)          // every peer's load in flight before the first add
+      if (r < world) q[r] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(staged.p[r]) + lo + v * 8);
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {        // fixed rank order
+      if (r < world) {
+        const uint32_t w[4] = {q[r].x, q[r].y, q[r].z, q[r].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          s[2 * j] += bf16_lo(w[j]);
+          s[2 * j + 1] += bf16_hi(w[j]);
+        }
       }
     }
     float4 a0 = reinterpret_cast<float4*>(acc)[2 * v], a1 = reinterpret_cast<float4*>(acc)[2 * v + 1];

@@ -26,14 +26,16 @@ def small_cfg(dtype, tp, backend, quant="none", quant_backward=None):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     cfg = Config.from_file(os.path.join(root, "configs", "bench", "smoke_cpu.yaml"))
     cfg.model.dtype = dtype
-    cfg.model.hidden_dim, cfg.model.num_heads, cfg.model.head_dim = 256, 4, 64
-    cfg.model.intermediate_dim = 1024
+    # the model grows with the tensor-parallel size beyond 4 so that every rank keeps at least one head and 64 hidden columns
+    heads = max(4, tp)
+    cfg.model.hidden_dim, cfg.model.num_heads, cfg.model.head_dim = 64 * heads, heads, 64
+    cfg.model.intermediate_dim = 256 * heads
     cfg.data.seq_len = 256
     cfg.model.max_seq_len = 256
     cfg.training.micro_batch_size, cfg.training.global_batch_size = 2, 2
     cfg.runtime.tensor_parallel_size = tp
     cfg.runtime.comm_backend = backend
-    cfg.model.num_kv_heads = int(os.environ.get("ELFA_TEST_KV_HEADS", "4"))
+    cfg.model.num_kv_heads = int(os.environ.get("ELFA_TEST_KV_HEADS", str(heads)))
     cfg.data.pack_sequences = os.environ.get("ELFA_TEST_PACK", "0") == "1"
     cfg.quant.attention = cfg.quant.mlp = quant
     cfg.quant.backward = quant_backward if quant_backward is not None else os.environ.get("ELFA_TEST_QUANT_BACKWARD", "none")
@@ -46,7 +48,8 @@ def small_cfg(dtype, tp, backend, quant="none", quant_backward=None):
 def mode_fused(pc, dev):
     from elfa_b200 import native
     from elfa_b200.runtime.symm import SymmetricArena
-    pc.symm = SymmetricArena.for_group(pc.tp_group, dev, 1 << 30)
+    # every shape below keeps its own ring slots, and the gathered / received buffers grow with the number of ranks
+    pc.symm = SymmetricArena.for_group(pc.tp_group, dev, (1 << 30) * max(1, pc.tp_size // 2))
     world, rank = pc.tp_size, pc.tp_rank
     torch.manual_seed(1234)
     worst = 0.0
