@@ -720,10 +720,34 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                    ::"r"(buf0 + b * 8192), "l"(src_of(c)), "r"(pb), "r"(pbar(b)) : "memory");
       ++n_issued;
     };
+    // Peers are served one after the other without draining the pipeline in between: a peer's counter is raised once the
+    // NEXT peer's stores have been issued and this peer's (older) bulk groups are known to be complete.
+    auto wait_all_but = [](uint32_t n) {     // completion of every bulk group except the `n` most recent ones
+      switch (n) {
+        case 0: tma_store_wait<0>(); break;
+        case 1: tma_store_wait<1>(); break;
+        case 2: tma_store_wait<2>(); break;
+        case 3: tma_store_wait<3>(); break;
+        case 4: tma_store_wait<4>(); break;
+        case 5: tma_store_wait<5>(); break;
+        case 6: tma_store_wait<6>(); break;
+        case 7: tma_store_wait<7>(); break;
+        default: tma_store_wait<8>(); break;   // more than asked for: still correct
+      }
+    };
+    auto signal = [&](int peer) {              // both push warps have finished `peer`: one counter increment per CTA
+      named_bar_sync(1, 64);
+      if (w == 0 && lane == 0 && peer != cm.rank) {
+        unsigned int* cnt = reinterpret_cast<unsigned int*>(cm.peer_flags[peer]) + cm.rank;
+        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
+      }
+    };
+    int prev_peer = -1;
     for (int i = 1; i <= cm.world; ++i) {
       const int peer = (cm.rank + i) % cm.world;
       if (lane == 0) {
         char* dst = reinterpret_cast<char*>(cm.peer_xfull[peer]);
+        uint32_t stores = 0;
         if (okp && c_first < nchunks) issue_load(c_first);
         for (long long c = c_first; c < nchunks && okp; c += c_step) {
           if (c + c_step < nchunks) issue_load(c + c_step);
@@ -733,17 +757,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                        ::"l"(dst + dst_off(c)), "r"(buf0 + b * 8192), "r"(pb) : "memory");
           tma_store_commit();
           ++n_done;
+          ++stores;
         }
-        tma_store_wait<0>();                            // every store to this peer has completed
-        __threadfence_system();
+        if (prev_peer >= 0) {
+          wait_all_but(okp ? stores : 0u);              // every store to the previous peer has completed
+          __threadfence_system();
+        }
       }
       __syncwarp();
-      named_bar_sync(1, 64);                            // both push warps are done with this peer
-      if (w == 0 && lane == 0 && peer != cm.rank) {     // one counter increment per CTA
-        unsigned int* cnt = reinterpret_cast<unsigned int*>(cm.peer_flags[peer]) + cm.rank;
-        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
-      }
+      if (prev_peer >= 0) signal(prev_peer);
+      prev_peer = peer;
     }
+    if (lane == 0) {
+      tma_store_wait<0>();
+      __threadfence_system();
+    }
+    __syncwarp();
+    signal(prev_peer);
     if (lane == 0 && !okp) {   // give a load that is still in flight a bounded chance to land before the CTA exits
       for (uint32_t j = n_done; j < n_issued; ++j) {
         const long long t0 = clock64();
