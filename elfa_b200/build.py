@@ -67,7 +67,25 @@ def _compile(nvcc: str, src: Path, obj: Path, verbose: bool, extra=()) -> str:
     return r.stderr
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+def lib_path(bounds: bool = False) -> Path:
+    return OUT_DIR / "libelfa_b200_bounds.so" if bounds else LIB
+
+
+def obj_dir(bounds: bool = False) -> Path:
+    return OUT_DIR / "obj_bounds" if bounds else OBJ_DIR
+
+
+def build(force: bool = False, verbose: bool = False, bounds: bool = False) -> Path:
+    """Compile and link the native library. ``bounds``: the checked variant (``-DELFA_BOUNDS``): kernels test the tile
+    coordinates, ring-slot offsets and push ranges they compute against the extents they were given, record a violation in
+    the device status word (``ELFA_ST_BOUNDS``) and skip the access instead of making it. It is a separate library beside
+    the normal one, loaded when ``ELFA_BOUNDS=1``."""
+    if bounds:
+        return _build_variant(force, verbose, lib_path(True), obj_dir(True), ("-DELFA_BOUNDS",))
+    return _build_variant(force, verbose, LIB, OBJ_DIR, ())
+
+
+def _build_variant(force: bool, verbose: bool, LIB: Path, OBJ_DIR: Path, extra_flags) -> Path:
     nvcc = find_nvcc()
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
     sources = sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cpp"))
@@ -87,7 +105,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             jobs.append((src, obj))
     if jobs:
         def flags(src):
-            return (f'-DELFA_SOURCE_HASH="{digest}"',) if src.name == "runtime.cu" else ()
+            return tuple(extra_flags) + ((f'-DELFA_SOURCE_HASH="{digest}"',) if src.name == "runtime.cu" else ())
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             for log in ex.map(lambda j: _compile(nvcc, j[0], j[1], verbose, flags(j[0])), jobs):
                 if verbose and log:
@@ -106,8 +124,9 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--bounds", action="store_true", help="build the checked variant (-DELFA_BOUNDS) beside the normal library")
     a = ap.parse_args(argv)
-    print(build(force=a.force, verbose=a.verbose))
+    print(build(force=a.force, verbose=a.verbose, bounds=a.bounds))
     return 0
 
 

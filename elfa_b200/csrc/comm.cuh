@@ -46,6 +46,7 @@ __device__ __forceinline__ void flag_bump(unsigned long long peer_flags_base, in
 struct PushPlan {
   long long off[2];      // byte offsets inside the buffer, 16-byte aligned
   long long bytes[2];    // sizes, multiples of 16 bytes (0 = unused)
+  long long limit;       // size of the buffer the ranges lie in (checked build: a piece past it is recorded and not sent)
 };
 
 constexpr int PUSH_PIECE = 8192;   // bytes per bulk copy
@@ -116,8 +117,9 @@ __device__ __forceinline__ void push_ranges(const char* local_base, const unsign
         long long off;
         uint32_t nb;
         piece(c, off, nb);
-        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
-                     ::"l"(dst + off), "r"(buf0 + b * PUSH_PIECE), "r"(nb) : "memory");
+        if (bounds_ok(off + nb - 1, plan.limit, status))
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                       ::"l"(dst + off), "r"(buf0 + b * PUSH_PIECE), "r"(nb) : "memory");
         tma_store_commit();
         ++n_done;
         ++stores;

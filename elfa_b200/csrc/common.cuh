@@ -25,6 +25,7 @@ enum {
   ELFA_ST_FLAG_TIMEOUT = 1u << 1,    // a wait on a peer / signal flag gave up
   ELFA_ST_BAD_TARGET = 1u << 2,      // cross-entropy saw a target outside [0, vocab)
   ELFA_ST_NONFINITE = 1u << 3,       // optimizer saw a non-finite gradient norm
+  ELFA_ST_BOUNDS = 1u << 4,          // checked build (-DELFA_BOUNDS): a computed index lay outside its extent; the access was skipped
 };
 
 namespace elfa {
@@ -72,6 +73,18 @@ int device_sm_count();
 // ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// Checked build (-DELFA_BOUNDS): true when 0 <= i < n; otherwise the violation is recorded in the status word and the caller
+// skips the access (nothing traps). In the normal build the test is compiled out.
+__device__ __forceinline__ bool bounds_ok(long long i, long long n, unsigned int* status) {
+#ifdef ELFA_BOUNDS
+  if (i >= 0 && i < n) return true;
+  if (status) atomicOr(status, (unsigned)ELFA_ST_BOUNDS);
+  return false;
+#else
+  return true;
+#endif
 }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

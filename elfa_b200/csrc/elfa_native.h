@@ -26,6 +26,10 @@ int elfa_set_deterministic(int on);
 const char* elfa_source_hash(void);
 long long elfa_launch_count(int reset);
 int elfa_status(unsigned int* out);
+// Checked variant of the library (built with -DELFA_BOUNDS): kernels test the tile coordinates, ring-slot offsets and push
+// ranges they compute, record a violation in the status word (bit 4) and skip the access.
+int elfa_bounds_enabled();
+int elfa_bounds_selftest(void* stream);
 int elfa_device_info(int device, long long* out6);
 int elfa_is_blackwell(int device);
 int elfa_enable_peer_access(int* n_enabled);

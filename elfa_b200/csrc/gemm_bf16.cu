@@ -237,6 +237,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int kb0 = (unit - tile * splits) * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
         int mb, nb, shard;
         tile_coords_comm<COMM>(p, cm, tile, mb, nb, shard, TILE_M);
+        if (!bounds_ok(mb, p.tiles_m, p.status) || !bounds_ok(nb, p.tiles_n, p.status) || !bounds_ok(shard, COMM == COMM_NONE ? 1 : cm.world, p.status)) {
+          *abort_flag = 1;     // checked build: a tile outside the grid ends the CTA (every role sees the flag)
+          break;
+        }
         const int m0 = mb * TILE_M + (int)cta_rank * BM, n0 = nb * BN;
         const bool own = COMM == COMM_AG && shard == cm.rank;
         if (COMM == COMM_AG && !own && shard != ready_shard) {
@@ -654,7 +658,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (COMM == COMM_RS && cm.chunk_major) {
               const long long chunk = ((long long)((m0 - shard * cm.rows_per_rank) / BM) * p.tiles_n + nb) * CPT + cc;
               char* dst = reinterpret_cast<char*>(cm.peer_recv[shard]) + ((long long)cm.rank * cm.slot_chunks + chunk) * (BM * 128);
-              asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(BM * 128) : "memory");
+              if (bounds_ok(chunk, cm.slot_chunks, p.status))      // checked build: the chunk lies inside this rank's slot
+                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(BM * 128) : "memory");
             } else if (reduce_add) {
               tma_reduce_add_2d(&om.m[dst_map], src, n0 + cc * ccols, dst_row);
             } else {
@@ -753,8 +758,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (c + c_step < nchunks) issue_load(c + c_step);
           const int b = n_done & 1;
           if (!mbar_wait(pbar(b), (n_done >> 1) & 1, abort_flag, p.status)) { okp = false; break; }
-          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
-                       ::"l"(dst + dst_off(c)), "r"(buf0 + b * 8192), "r"(pb) : "memory");
+          if (bounds_ok(dst_off(c) + pb - 1, (long long)cm.world * cm.rows_per_rank * p.K * 2, p.status))
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                         ::"l"(dst + dst_off(c)), "r"(buf0 + b * 8192), "r"(pb) : "memory");
           tma_store_commit();
           ++n_done;
           ++stores;
@@ -811,6 +817,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const long long row = (t / p.tiles_n) * BM + rr;
         const int col = nb * BN + cc * 64 + unit * 8;
         if (col >= p.N) continue;
+        if (!bounds_ok(row, cm.rows_per_rank, p.status)) continue;
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         uint4 q[MAX_RANKS];
 #pragma unroll

@@ -776,6 +776,7 @@ ELFA_API int elfa_gemm_ag_mxfp8(const unsigned long long* peer_buf, const unsign
   c.plan.bytes[0] = pay_l;
   c.plan.off[1] = (long long)M * K + (long long)rank * sf_l;
   c.plan.bytes[1] = sf_l;
+  c.plan.limit = (long long)M * K + (long long)world * sf_l;
   const int ctas = pair ? q_grid_ctas<192, true>(M, N) : (BN == 192 ? q_grid_ctas<192, false>(M, N) : q_grid_ctas<128, false>(M, N));
   *arrivals_io += (unsigned)ctas;                  // every CTA of a source bumps the counter once
   c.flag_target = *arrivals_io;

@@ -149,6 +149,32 @@ ELFA_API long long elfa_launch_count(int reset) {
 }
 
 // Reads and clears the status word of the current device (synchronises the device).
+namespace {
+__global__ void bounds_selftest_kernel(unsigned int* status) {
+  // no memory is touched: an index one past a four-element extent goes through the same test the kernels use
+  if (threadIdx.x == 0 && !elfa::bounds_ok(4, 4, status)) return;
+}
+}  // namespace
+
+// 1 when this library is the checked variant (-DELFA_BOUNDS), else 0.
+ELFA_API int elfa_bounds_enabled() {
+#ifdef ELFA_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+// Runs the index test of the checked build on an out-of-range index (no access follows): afterwards the status word carries
+// ELFA_ST_BOUNDS in the checked variant and stays clear in the normal one.
+ELFA_API int elfa_bounds_selftest(void* stream) {
+  unsigned int* st = elfa::status_word();
+  ELFA_REQUIRE(st != nullptr, "bounds_selftest: no status word");
+  bounds_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(st);
+  ELFA_CUDA(cudaGetLastError());
+  return ELFA_OK;
+}
+
 ELFA_API int elfa_status(unsigned int* out) {
   unsigned int* p = status_word();
   ELFA_REQUIRE(p != nullptr, "no status word (no device?)");

@@ -16,13 +16,17 @@ from typing import Any, Dict, Optional
 import torch
 
 _PKG = Path(__file__).resolve().parent
-_LIB_PATH = _PKG / "_native" / "libelfa_b200.so"
+# ELFA_BOUNDS=1 selects the checked variant of the library (see build.build(bounds=True)): in-kernel index checks that record
+# a violation in the status word and skip the access
+_BOUNDS = os.environ.get("ELFA_BOUNDS", "0") == "1"
+_LIB_PATH = _PKG / "_native" / ("libelfa_b200_bounds.so" if _BOUNDS else "libelfa_b200.so")
 _HEADER = _PKG / "csrc" / "elfa_native.h"
 
 ST_MBAR_TIMEOUT = 1
 ST_FLAG_TIMEOUT = 2
 ST_BAD_TARGET = 4
 ST_NONFINITE = 8
+ST_BOUNDS = 16
 
 EPI_BIAS, EPI_GELU, EPI_DGELU_AUX, EPI_ADD_AUX, EPI_ACCUM, EPI_OUT_F32, EPI_STORE_PREACT = 1, 2, 4, 8, 16, 32, 64
 
@@ -101,7 +105,7 @@ class _Lib:
                 return (probe.elfa_source_hash() or b"").decode()
             except (OSError, AttributeError):
                 return ""
-        stamp = b.OBJ_DIR / "source_hash.txt"
+        stamp = b.obj_dir(_BOUNDS) / "source_hash.txt"
         if _LIB_PATH.exists() and stamp.exists() and stamp.read_text().strip() == here:
             return              # the build step's own record says the library is current (no need to open it twice)
         if built() == here:
@@ -113,7 +117,7 @@ class _Lib:
             try:
                 if not (stamp.exists() and stamp.read_text().strip() == here and _LIB_PATH.exists()):
                     try:
-                        b.build()
+                        b.build(bounds=_BOUNDS)
                     except RuntimeError as e:
                         raise NativeError(f"native library {_LIB_PATH} is missing or was built from other sources and could not be "
                                           f"rebuilt: {e}") from e
@@ -180,6 +184,8 @@ def check_status() -> None:
         raise CommTimeout(f"a device-side wait timed out (status 0x{st:x})")
     if st & ST_BAD_TARGET:
         raise NativeError("token or target id outside the vocabulary")
+    if st & ST_BOUNDS:
+        raise NativeError("a kernel of the checked build computed an index outside the extents it was given (the access was skipped)")
 
 
 def require_native(t: torch.Tensor) -> bool:
