@@ -91,17 +91,25 @@ def _build_variant(force: bool, verbose: bool, LIB: Path, OBJ_DIR: Path, extra_f
     sources = sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cpp"))
     if not sources:
         raise RuntimeError("no native sources found")
-    hdr_m = _newest_header_mtime()
     digest = source_hash()
     stamp = OBJ_DIR / "source_hash.txt"
-    hash_changed = not stamp.exists() or stamp.read_text().strip() != digest
+    # an object is current when the hash of its source and of every header it may include matches the one recorded beside it
+    # (file times do not survive a copy of the tree to another machine)
+    import hashlib
+    hdr = hashlib.sha256()
+    for h in sorted(q for pat in ("*.h", "*.hpp", "*.cuh") for q in CSRC.glob(pat)):
+        hdr.update(h.name.encode() + b"\0" + h.read_bytes() + b"\0")
+    hdr.update(" ".join(extra_flags).encode())
     jobs = []
+    want = {}
     for src in sources:
         obj = OBJ_DIR / (src.stem + ".o")
-        stale = force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_m)
-        if src.name == "runtime.cu" and hash_changed:
-            stale = True            # carries the hash of all sources
-        if stale:
+        key = hashlib.sha256(hdr.digest() + src.read_bytes()).hexdigest()
+        if src.name == "runtime.cu":
+            key = hashlib.sha256((key + digest).encode()).hexdigest()     # carries the hash of all sources
+        want[src.stem] = key
+        rec = OBJ_DIR / (src.stem + ".hash")
+        if force or not obj.exists() or not rec.exists() or rec.read_text().strip() != key:
             jobs.append((src, obj))
     if jobs:
         def flags(src):
@@ -110,6 +118,8 @@ def _build_variant(force: bool, verbose: bool, LIB: Path, OBJ_DIR: Path, extra_f
             for log in ex.map(lambda j: _compile(nvcc, j[0], j[1], verbose, flags(j[0])), jobs):
                 if verbose and log:
                     print(log, file=sys.stderr)
+        for src, _ in jobs:
+            (OBJ_DIR / (src.stem + ".hash")).write_text(want[src.stem] + "\n")
     objs = [OBJ_DIR / (s.stem + ".o") for s in sources]
     if jobs or not LIB.exists():
         cmd = [nvcc, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart", "-Xcompiler", "-fPIC"]

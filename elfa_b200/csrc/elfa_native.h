@@ -129,13 +129,19 @@ int elfa_gemm_ag(const void* x_local, long long ldx, const unsigned long long* p
 int elfa_gemm_ag_mxfp8(const unsigned long long* peer_buf, const unsigned long long* peer_flags, const void* my_flags,
                        unsigned int* arrivals_io, const void* B, const void* sfb, void* C, int M, int N, int K, long long ldc,
                        void* preact, long long ldpre, unsigned flags, int rank, int world, int wait_ms, void* stream);
+// ZeRO stage 3: the parameter all-gather inside the consuming GEMM. B [K, N] row-major is bytes [w_off, w_off + K*N*2) of a
+// bucket sharded over `world` ranks (`shard_bytes` each, rank r's shard at shard_src[r], peer addressable); the kernel copies it
+// into the local bucket `bucket_dst` (B = bucket_dst + w_off) while it multiplies. `flags_dev`: `world` zeroed u32 counters.
+int elfa_gemm_gb(const void* A, long long lda, void* C, long long ldc, int M, int N, int K, void* preact, long long ldpre,
+                 unsigned flags, const unsigned long long* shard_src, void* bucket_dst, long long w_off, long long shard_bytes,
+                 void* flags_dev, int rank, int world, int wait_ms, void* stream);
 int elfa_gemm_rs(const void* A, long long lda, const void* B, long long ldb, int b_mn_major, int M, int N, int K,
                  const unsigned long long* peer_recv, const unsigned long long* peer_flags, const void* my_flags,
                  unsigned int* arrivals_io, void* out, long long ld_out, int rank, int world, int wait_ms, int max_ctas, void* stream);
 
 int elfa_gemm_rs_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, int M, int N, int K,
                        const unsigned long long* peer_recv, const unsigned long long* peer_flags, const void* my_flags,
-                       unsigned int* arrivals_io, void* out, long long ld_out, int rank, int world, int wait_ms, void* stream);
+                       unsigned int* arrivals_io, void* out, long long ld_out, int rank, int world, int wait_ms, int max_ctas, void* stream);
 int elfa_gemm_rs_slot_cols(int N);
 
 // ---- multimem.cu (NVLS: reductions inside the NVSwitch through the arena's multicast mapping) ------------------
@@ -154,6 +160,8 @@ int elfa_zero_adamw_allgather(const unsigned long long* peer_params, int rank, i
 int elfa_zero_pack_bf16(const float* src, void* dst, long long n, void* stream);
 int elfa_zero3_reduce_acc_bf16(const unsigned long long* peer_staged, int world, long long lo, long long n, float* acc, float scale,
                                void* stream);
+int elfa_zero3_gather_window(const unsigned long long* peer_shards, int world, long long src_off_bytes, long long shard_bytes,
+                             long long lo_bytes, long long hi_bytes, void* dst, void* stream);
 int elfa_zero3_gather(const unsigned long long* peer_shards, int world, long long src_off_bytes, long long shard_bytes, void* dst,
                       void* stream);
 int elfa_zero3_reduce_acc(const unsigned long long* peer_grads, int world, long long lo, long long n, float* acc, float scale,

@@ -68,7 +68,7 @@ struct GemmParams {
   int sfb_atoms;     // MXFP8: row blocks of the B scale tensor
 };
 
-enum { COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2 };
+enum { COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2, COMM_GB = 3 };
 
 struct CommParams {
   int rank, world;
@@ -93,6 +93,17 @@ struct CommParams {
   // segments) when 0.
   int chunk_major;
   long long slot_chunks;                   // chunks per source slot
+  // gather of B (COMM_GB): B is a parameter that lies sharded over the ranks - bytes [gb_w_off, gb_w_off + gb_w_bytes) of a
+  // bucket whose rank r holds bytes [r * gb_shard_bytes, (r + 1) * gb_shard_bytes) at gb_src[r] (peer addressable). Two warps
+  // per CTA copy the parameter's pieces into the local full-size bucket at gb_dst (bulk loads from the owners, bulk stores to
+  // local memory) and raise the LOCAL counter gb_flags[r] once per CTA and owner; the TMA producer waits for the owners of
+  // the B rows of a K block before it loads them.
+  unsigned long long gb_src[MAX_RANKS];
+  char* gb_dst;
+  long long gb_w_off, gb_w_bytes, gb_shard_bytes, gb_row_bytes;
+  unsigned int* gb_flags;
+  unsigned int gb_target;
+  int gb_kb_rot;                           // the K loop starts at this K block (the first one inside this rank's own part) and wraps
 };
 
 // SF: bytes of scale atoms per stage (block-scaled MXFP8 operands: one atom of A scales + the atoms of B scales; 0 for bf16)
@@ -133,7 +144,7 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
 template <int COMM>
 __device__ __forceinline__ void tile_coords_comm(const GemmParams& p, const CommParams& c, int tile, int& mb, int& nb, int& shard,
                                                  int tile_m = BM) {
-  if (COMM == COMM_NONE) {
+  if (COMM == COMM_NONE || COMM == COMM_GB) {
     tile_coords(p, tile, mb, nb);
     shard = 0;
     return;
@@ -232,6 +243,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t it = 0;
       bool ok = true;
       int ready_shard = -1;
+      uint32_t gb_ready = 0;            // COMM_GB: owners whose part of B is known to be in place
       for (int unit = wid; unit < num_units && ok; unit += wstride) {
         const int tile = unit / splits;
         const int kb0 = (unit - tile * splits) * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
@@ -250,9 +262,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           asm volatile("fence.proxy.async.global;" ::: "memory");
           ready_shard = shard;
         }
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        for (int kb_seq = kb0; kb_seq < kb1; ++kb_seq, ++it) {
+          int kb = kb_seq;
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
+          if (COMM == COMM_GB) {
+            // the K blocks are visited own part first, then in the order in which the copy warps fetch the other owners'
+            // parts (a sum over K may start anywhere); the MMA warp only counts blocks
+            kb = (kb_seq + cm.gb_kb_rot) % num_kb;
+            // rows [kb * BK, kb * BK + BK) of B: the ranks that own those bytes of the bucket must have been copied in
+            const long long lo = cm.gb_w_off + (long long)kb * BK * cm.gb_row_bytes;
+            long long hi = lo + (long long)BK * cm.gb_row_bytes;
+            if (hi > cm.gb_w_off + cm.gb_w_bytes) hi = cm.gb_w_off + cm.gb_w_bytes;
+            const int r_lo = (int)(lo / cm.gb_shard_bytes), r_hi = (int)((hi - 1) / cm.gb_shard_bytes);
+            for (int r = r_lo; r <= r_hi && ok; ++r) {
+              if (gb_ready & (1u << r)) continue;
+              if (!bounds_ok(r, cm.world, p.status) || !flag_wait(cm.gb_flags + r, cm.gb_target, cm.wait_cycles, abort_flag, p.status)) { ok = false; break; }
+              asm volatile("fence.proxy.async.global;" ::: "memory");   // the copies were bulk stores of other warps / CTAs
+              gb_ready |= 1u << r;
+            }
+            if (!ok) break;
+          }
           if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status)) { ok = false; break; }
           const uint32_t a_dst = smem_u32(sA + s * L::A_BYTES);
           const uint32_t b_dst = smem_u32(sB + s * L::B_BYTES);
@@ -503,7 +533,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
-      if (!(fl & ~(ELFA_EPI_GELU | ELFA_EPI_STORE_PREACT)) && COMM != COMM_AG) {
+      if (!(fl & ~(ELFA_EPI_GELU | ELFA_EPI_STORE_PREACT)) && COMM != COMM_AG && COMM != COMM_GB) {
         // plain bf16 output (narrow-K products are bound by this loop): 64 accumulator columns at a time go through the warp's
         // private 4 KB of the staging area and leave as whole 128-byte lines; the next 64 columns are requested from tensor
         // memory before the lines are written. (The all-gather variant's push warps own the staging area: it keeps the
@@ -780,6 +810,62 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     __syncwarp();
     signal(prev_peer);
+    if (lane == 0 && !okp) {   // give a load that is still in flight a bounded chance to land before the CTA exits
+      for (uint32_t j = n_done; j < n_issued; ++j) {
+        const long long t0 = clock64();
+        while (!mbar_try(pbar(j & 1), (j >> 1) & 1) && clock64() - t0 < 4000000) {}
+      }
+    }
+  }
+
+  if (COMM == COMM_GB && warp >= 7) {
+    // ------------------------------------------------------------------ gather warps (7, 8)
+    // The parameter's bytes are fetched owner by owner, this rank's own part first (a local copy), then rank + 1, ...:
+    // bulk load from the owner's shard (peer memory, no multicast) into shared memory, bulk store into the local bucket.
+    // After an owner's pieces of this CTA have landed, warp 7 raises the local counter of that owner once.
+    const int w = warp - 7;
+    const uint32_t buf0 = smem_u32(smem + L::OUT_OFF) + w * 16384;
+    auto pbar = [&](int b) { return bar0 + 8u * (2 * STAGES + 4 + w * 2 + b); };
+    uint32_t n_issued = 0, n_done = 0;
+    bool okp = true;
+    const long long w_end = cm.gb_w_off + cm.gb_w_bytes;
+    for (int i = 0; i < cm.world; ++i) {
+      const int r = (cm.rank + i) % cm.world;
+      long long lo = (long long)r * cm.gb_shard_bytes, hi = lo + cm.gb_shard_bytes;
+      if (lo < cm.gb_w_off) lo = cm.gb_w_off;
+      if (hi > w_end) hi = w_end;
+      const long long npieces = hi > lo ? (hi - lo + 8191) / 8192 : 0;
+      const long long c_first = (long long)blockIdx.x * 2 + w, c_step = (long long)gridDim.x * 2;
+      if (lane == 0) {
+        const char* src = reinterpret_cast<const char*>(cm.gb_src[r]) + (lo - (long long)r * cm.gb_shard_bytes);
+        char* dst = cm.gb_dst + lo;
+        auto nbytes_of = [&](long long c) { const long long rem = hi - lo - c * 8192; return (uint32_t)(rem < 8192 ? rem : 8192); };
+        auto issue_load = [&](long long c) {
+          const int b = n_issued & 1;
+          tma_store_wait_read<0>();                       // the store that last used this buffer has read it
+          mbar_expect_tx(pbar(b), nbytes_of(c));
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                       ::"r"(buf0 + b * 8192), "l"(src + c * 8192), "r"(nbytes_of(c)), "r"(pbar(b)) : "memory");
+          ++n_issued;
+        };
+        if (okp && c_first < npieces) issue_load(c_first);
+        for (long long c = c_first; c < npieces && okp; c += c_step) {
+          if (c + c_step < npieces) issue_load(c + c_step);
+          const int b = n_done & 1;
+          if (!mbar_wait(pbar(b), (n_done >> 1) & 1, abort_flag, p.status)) { okp = false; break; }
+          if (bounds_ok(lo + c * 8192 + nbytes_of(c) - 1, w_end, p.status))
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                         ::"l"(dst + c * 8192), "r"(buf0 + b * 8192), "r"(nbytes_of(c)) : "memory");
+          tma_store_commit();
+          ++n_done;
+        }
+        tma_store_wait<0>();                              // this owner's pieces are in local memory
+        __threadfence();
+      }
+      __syncwarp();
+      named_bar_sync(1, 64);                              // both gather warps are done with this owner
+      if (w == 0 && lane == 0 && okp) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(cm.gb_flags + r) : "memory");
+    }
     if (lane == 0 && !okp) {   // give a load that is still in flight a bounded chance to land before the CTA exits
       for (uint32_t j = n_done; j < n_issued; ++j) {
         const long long t0 = clock64();
@@ -1203,6 +1289,69 @@ ELFA_API int elfa_gemm_ag(const void* x_local, long long ldx, const unsigned lon
   return dispatch_comm<COMM_AG>(BN, b_mn_major, tmA, tmB, tmA2, p, c, static_cast<cudaStream_t>(stream), &om, 0, pair);
 }
 
+// C[M,N] = epilogue(A[M,K] * B[K,N]) where B (row-major, ld = N) is a parameter sharded over `world` ranks: bytes
+// [w_off, w_off + K * N * 2) of a bucket whose rank r keeps bytes [r * shard_bytes, (r + 1) * shard_bytes) at shard_src[r]
+// (peer addressable, stable during the call). The kernel copies the parameter into the local full-size bucket
+// (`bucket_dst`, the bucket's base; B = bucket_dst + w_off) while the tensor cores start on the K blocks that have arrived:
+// the parameter all-gather of ZeRO stage 3 inside the consuming GEMM. `flags_dev`: `world` zeroed u32 counters in local
+// memory. Nothing is signalled to another GPU; the owners' shards only have to stay unchanged.
+ELFA_API int elfa_gemm_gb(const void* A, long long lda, void* C, long long ldc, int M, int N, int K, void* preact, long long ldpre,
+                          unsigned flags, const unsigned long long* shard_src, void* bucket_dst, long long w_off, long long shard_bytes,
+                          void* flags_dev, int rank, int world, int wait_ms, void* stream) {
+  ELFA_REQUIRE(A && C && shard_src && bucket_dst && flags_dev, "gemm_gb: null argument");
+  ELFA_REQUIRE(world >= 2 && world <= MAX_RANKS && rank >= 0 && rank < world, "gemm_gb: bad rank/world");
+  ELFA_REQUIRE(M > 0 && N % 8 == 0 && K % 8 == 0 && lda % 8 == 0 && ldc % 8 == 0, "gemm_gb: alignment");
+  ELFA_REQUIRE(w_off >= 0 && w_off % 16 == 0 && shard_bytes > 0 && shard_bytes % 16 == 0, "gemm_gb: byte ranges must be 16-byte aligned");
+  ELFA_REQUIRE(w_off + (long long)K * N * 2 <= shard_bytes * world, "gemm_gb: the parameter must lie inside the bucket");
+  ELFA_REQUIRE(!(flags & ~(ELFA_EPI_GELU | ELFA_EPI_STORE_PREACT)), "gemm_gb: unsupported epilogue flag");
+  ELFA_REQUIRE(!(flags & ELFA_EPI_STORE_PREACT) || (preact && ldpre % 8 == 0), "gemm_gb: preact flag without pointer");
+  ELFA_REQUIRE((reinterpret_cast<uintptr_t>(bucket_dst) & 15) == 0, "gemm_gb: bucket must be 16-byte aligned");
+  unsigned int* st = status_word();
+  ELFA_REQUIRE(st != nullptr, "gemm_gb: no status word");
+  const void* B = static_cast<const char*>(bucket_dst) + w_off;
+  const bool pair = N >= 256 && (long long)((M + 255) / 256) * ((N + 255) / 256) >= sm_count() / 2;
+  const int BN = (pair || (N >= 256 && (long long)((M + BM - 1) / BM) * ((N + 255) / 256) >= sm_count())) ? 256 : 128;
+  CUtensorMap tmA, tmB;
+  int rc = cached_tmap_bf16(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, BK);
+  if (rc != ELFA_OK) return rc;
+  rc = cached_tmap_bf16(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)N, BK, 64);
+  if (rc != ELFA_OK) return rc;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc;
+  p.preact = static_cast<__nv_bfloat16*>(preact);
+  p.ldpre = ldpre;
+  p.alpha = 1.f;
+  p.flags = flags;
+  p.status = st;
+  CommParams c{};
+  c.rank = rank; c.world = world;
+  c.wait_cycles = wait_cycles_of(wait_ms);
+  for (int i = 0; i < world; ++i) {
+    ELFA_REQUIRE(shard_src[i] && (shard_src[i] & 15) == 0, "gemm_gb: shard addresses must be 16-byte aligned");
+    c.gb_src[i] = shard_src[i];
+  }
+  c.gb_dst = static_cast<char*>(bucket_dst);
+  c.gb_w_off = w_off;
+  c.gb_w_bytes = (long long)K * N * 2;
+  c.gb_shard_bytes = shard_bytes;
+  c.gb_row_bytes = (long long)N * 2;
+  c.gb_flags = static_cast<unsigned int*>(flags_dev);
+  c.gb_target = (unsigned)comm_grid(M, N, BN, pair);       // every CTA raises every owner's counter once
+  {
+    const long long own_lo = std::max(w_off, (long long)rank * shard_bytes), blk = (long long)BK * c.gb_row_bytes;
+    const int num_kb = (K + BK - 1) / BK;
+    const long long rot = own_lo < w_off + c.gb_w_bytes ? (own_lo - w_off + blk - 1) / blk : 0;
+    c.gb_kb_rot = rot < num_kb ? (int)rot : 0;
+  }
+  OutMaps om{};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int ctas = sm_count();
+  if (pair) return launch_gemm<256, false, true, COMM_GB, true>(tmA, tmB, p, ctas, s, &tmA, &c, &om);
+  if (BN == 256) return launch_gemm<256, false, true, COMM_GB>(tmA, tmB, p, ctas, s, &tmA, &c, &om);
+  return launch_gemm<128, false, true, COMM_GB>(tmA, tmB, p, ctas, s, &tmA, &c, &om);
+}
+
 // out[M/world, N] = reduce_scatter_rows(A[M,K] * op(B)): partial tiles travel to the owner's receive
 // buffer ([world][M/world][N] bf16, symmetric) and are summed there in rank order.
 ELFA_API int elfa_gemm_rs(const void* A, long long lda, const void* B, long long ldb, int b_mn_major, int M, int N, int K,
@@ -1262,7 +1411,8 @@ ELFA_API int elfa_gemm_rs(const void* A, long long lda, const void* B, long long
 // 128-) wide tiles: `peer_recv` buffers need world * (M / world) * elfa_gemm_rs_slot_cols(N) * 2 bytes.
 ELFA_API int elfa_gemm_rs_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, int M, int N, int K,
                                 const unsigned long long* peer_recv, const unsigned long long* peer_flags, const void* my_flags,
-                                unsigned int* arrivals_io, void* out, long long ld_out, int rank, int world, int wait_ms, void* stream) {
+                                unsigned int* arrivals_io, void* out, long long ld_out, int rank, int world, int wait_ms, int max_ctas,
+                                void* stream) {
   ELFA_REQUIRE(A && sfa && B && sfb && peer_recv && peer_flags && my_flags && arrivals_io && out, "gemm_rs_mxfp8: null argument");
   ELFA_REQUIRE(world >= 2 && world <= MAX_RANKS && rank >= 0 && rank < world, "gemm_rs_mxfp8: bad rank/world");
   ELFA_REQUIRE(M % world == 0 && (M / world) % BM == 0, "gemm_rs_mxfp8: rows per rank must be a multiple of 128");
@@ -1274,7 +1424,10 @@ ELFA_API int elfa_gemm_rs_mxfp8(const void* A, const void* sfa, const void* B, c
   const int rows = M / world;
   const bool wide = N > 128;
   const int BN = wide ? 192 : 128;
-  const bool pair = wide && rows % (2 * BM) == 0 && (long long)(M / (2 * BM)) * ((N + 191) / 192) >= sm_count() / 2;
+  // max_ctas < SM count leaves SMs to a kernel on another stream (a weight-gradient GEMM next to this NVLink-bound kernel);
+  // arrivals are counted per tile, so the grid size does not enter the protocol
+  const bool whole = max_ctas <= 0 || max_ctas >= sm_count();
+  const bool pair = whole && wide && rows % (2 * BM) == 0 && (long long)(M / (2 * BM)) * ((N + 191) / 192) >= sm_count() / 2;
   const int kt = (K + 127) / 128;
   CUtensorMap tmA, tmB;
   int rc = cached_tmap(&tmA, A, 1, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, 128);
@@ -1305,7 +1458,7 @@ ELFA_API int elfa_gemm_rs_mxfp8(const void* A, const void* sfa, const void* B, c
   *arrivals_io += (unsigned)((rows / BM) * ((N + BN - 1) / BN));
   c.flag_target = *arrivals_io;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int ctas = sm_count();
+  const int ctas = whole ? sm_count() : max_ctas;
   if (pair) return launch_gemm<192, false, false, COMM_RS, true, true>(tmA, tmB, p, ctas, s, &tmA, &c, &om);
   if (wide) return launch_gemm<192, false, false, COMM_RS, false, true>(tmA, tmB, p, ctas, s, &tmA, &c, &om);
   return launch_gemm<128, false, false, COMM_RS, false, true>(tmA, tmB, p, ctas, s, &tmA, &c, &om);

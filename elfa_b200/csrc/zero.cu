@@ -105,6 +105,17 @@ __global__ void __launch_bounds__(256) zero3_gather_kernel(PeerPtrs shards, int 
   }
 }
 
+// The same for a window [v_lo, v_hi) (16-byte vectors) of the concatenation: the part of a bucket that no GEMM fetches itself.
+__global__ void __launch_bounds__(256) zero3_gather_window_kernel(PeerPtrs shards, long long src_off, long long shard_vecs, long long v_lo,
+                                                                  long long v_hi, uint4* __restrict__ dst) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long v = v_lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; v < v_hi; v += stride) {
+    const int r = (int)(v / shard_vecs);
+    const long long i = v - (long long)r * shard_vecs;
+    dst[v] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(shards.p[r]) + src_off + i * 16);
+  }
+}
+
 // Gradient reduce-scatter with peer loads: acc[i] += scale * sum_r grads_r[lo + i] (fixed order).
 __global__ void __launch_bounds__(256) zero3_reduce_acc_kernel(PeerPtrs grads, int world, long long lo, long long n,
                                                                float* __restrict__ acc, float scale) {
@@ -292,6 +303,24 @@ ELFA_API int elfa_zero_adamw_allgather(const unsigned long long* peer_params, in
   zero_adamw_allgather_kernel<<<zgrid(n / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       pp, rank, world, lo, n, master, m, v, reduced, lr, beta1, beta2, eps, wd, bc1, bc2, static_cast<const StepScalarsZ*>(scalars),
       wd_lo, wd_hi);
+  ELFA_CUDA(cudaGetLastError());
+  ::elfa::count_launches(1);
+  return ELFA_OK;
+}
+
+// Stage 3 parameter gather of bytes [lo_bytes, hi_bytes) of the concatenation only (see elfa_zero3_gather for the rest).
+ELFA_API int elfa_zero3_gather_window(const unsigned long long* peer_shards, int world, long long src_off_bytes, long long shard_bytes,
+                                      long long lo_bytes, long long hi_bytes, void* dst, void* stream) {
+  ELFA_REQUIRE(peer_shards && dst && world >= 1 && world <= ZMAX, "zero3_gather_window: bad arguments");
+  ELFA_REQUIRE(shard_bytes > 0 && shard_bytes % 16 == 0 && src_off_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0,
+               "zero3_gather_window: sizes and offsets must be multiples of 16 bytes");
+  ELFA_REQUIRE(lo_bytes >= 0 && lo_bytes % 16 == 0 && hi_bytes % 16 == 0 && lo_bytes <= hi_bytes && hi_bytes <= shard_bytes * world,
+               "zero3_gather_window: the window must be 16-byte aligned and inside the bucket");
+  if (lo_bytes == hi_bytes) return ELFA_OK;
+  PeerPtrs pp{};
+  for (int i = 0; i < world; ++i) pp.p[i] = peer_shards[i];
+  zero3_gather_window_kernel<<<zgrid((hi_bytes - lo_bytes) / 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      pp, src_off_bytes, shard_bytes / 16, lo_bytes / 16, hi_bytes / 16, static_cast<uint4*>(dst));
   ELFA_CUDA(cudaGetLastError());
   ::elfa::count_launches(1);
   return ELFA_OK;

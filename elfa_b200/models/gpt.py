@@ -154,6 +154,13 @@ class Block(nn.Module):
         self.mlp = MLP(cfg, pc, dtype, device)
         self.dropout = m.dropout
 
+    def gemm_weights(self):
+        """The parameters that are read only as the right-hand operand of ``ops.linear`` (no tensor parallelism, no
+        quantiser in front of them): under ZeRO stage 3 their forward product can fetch them itself."""
+        a, m = self.attn, self.mlp
+        plain = a.pc.tp_size == 1 and not (a.quant is not None and a.quant.enabled) and not (m.quant is not None and m.quant.enabled)
+        return [a.w_qkv, a.w_o, m.up, m.down] if plain else []
+
     def forward(self, x, pending, cache: Optional[dict] = None, doc_start: Optional[torch.Tensor] = None):
         """``pending`` is the previous sub-layer's output that has not been added to the residual
         stream yet; the add is fused into the next norm kernel. ``cache``: this layer's key / value cache

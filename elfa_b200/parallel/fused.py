@@ -257,7 +257,7 @@ def supported_rs_mxfp8(M: int, K: int, N: int, world: int) -> bool:
     return M % world == 0 and (M // world) % 128 == 0 and K % 32 == 0 and N % 64 == 0
 
 
-def gemm_rs_mxfp8(a_op, w_op, pc: ParallelContext) -> torch.Tensor:
+def gemm_rs_mxfp8(a_op, w_op, pc: ParallelContext, max_ctas: int = 0) -> torch.Tensor:
     """``reduce_scatter_rows(a @ w^T)`` with MXFP8 operands (``a_op`` left operand ``[M, K]``, ``w_op`` right operand ``[N, K]``):
     the block-scaled product inside the fused GEMM → reduce-scatter kernel. Returns ``[M / world, N]`` bf16."""
     world, rank = pc.tp_size, pc.tp_rank
@@ -268,7 +268,7 @@ def gemm_rs_mxfp8(a_op, w_op, pc: ParallelContext) -> torch.Tensor:
     out = torch.empty((M // world, N), dtype=torch.bfloat16, device=a_op.payload.device)
     lib.call("elfa_gemm_rs_mxfp8", a_op.payload, a_op.scales, w_op.payload, w_op.scales, M, N, K, ctypes.addressof(slot.peer_data),
              ctypes.addressof(slot.peer_flags), slot.flags.tensor, ctypes.addressof(slot.arrivals), out, out.stride(0), rank, world,
-             _WAIT_MS, stream_ptr(a_op.payload))
+             _WAIT_MS, max_ctas, stream_ptr(a_op.payload))
     return out
 
 

@@ -276,7 +276,23 @@ class _ColumnParallelSP(torch.autograd.Function):
             dy_op, dy2 = quantize_grad(dy2)
             if dy_op is not None and use_block_scaled_bwd(dy2, ctx.w_ref, ctx.quant) and _block_scaled_rs(pc, dy2.shape[0], dy2.shape[1], ctx.w_ref.shape[0]):
                 from . import fused
-                dx = fused.gemm_rs_mxfp8(dy_op, cached_weight_operand_bwd(ctx.w_ref, ctx.quant), pc)     # block-scaled dy @ w^T
+                w_op = cached_weight_operand_bwd(ctx.w_ref, ctx.quant)
+                if _overlap_wgrad(pc, dy2) and getattr(ctx.w_ref, "main_grad", None) is not None:
+                    # the NVLink-bound reduce-scatter kernel on part of the SMs, the weight gradient on the rest (second stream)
+                    dev = dy2.device
+                    side = _side_streams.get(dev)
+                    if side is None:
+                        side = _side_streams[dev] = torch.cuda.Stream(dev)
+                    cur = torch.cuda.current_stream(dev)
+                    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+                    rs_ctas = max(16, (sms * 7 // 16) // 2 * 2)
+                    side.wait_stream(cur)
+                    with torch.cuda.stream(side):
+                        dw = _wgrad(ctx.w_ref, x_full, dy2, wdt, max_ctas=sms - rs_ctas)
+                    dx = fused.gemm_rs_mxfp8(dy_op, w_op, pc, max_ctas=rs_ctas)
+                    cur.wait_stream(side)
+                    return dx.view(Sl, B, D), dw, None, None, None
+                dx = fused.gemm_rs_mxfp8(dy_op, w_op, pc)     # block-scaled dy @ w^T
                 dw = _wgrad(ctx.w_ref, x_full, dy2, wdt)
                 return dx.view(Sl, B, D), dw, None, None, None
             wq = cached_weight_quant_bwd(ctx.w_ref, ctx.quant)

@@ -12,6 +12,10 @@ and of the optimizer state. A bucket is one transformer block; everything outsid
   current block computes. The block's fp32 gradient is accumulated by the backward kernels in a
   slot of the same shape and reduce-scattered (averaged) into the rank's gradient shard when the
   next block's backward starts.
+* ``gather_in_gemm`` (``ELFA_ZERO3_GATHER_IN_GEMM=1``; needs the symmetric arena): in forward no kernel gathers a block's
+  matrices. The product that consumes a matrix fetches it itself - ``elfa_gemm_gb``: two warps of every CTA copy the owners'
+  pieces into the local slot while the tensor cores work through the K blocks that have arrived - and only the rest of the
+  bucket (norm weights) is gathered by a small windowed copy. Backward keeps the whole-block gather one block ahead.
 * Stage 2 (``shard_params=False``) keeps every block's parameters whole and resident; it shares the gradient path: per-block
   fp32 gradient slots that are reused once their reduce-scatter has run (the full-size gradient buffer of stages 0 / 1 does
   not exist), the reduce-scatter of a block issued on a side stream while the next block's backward runs, bf16 on the wire
@@ -53,6 +57,36 @@ class _Bucket:
     module: Optional[torch.nn.Module] = None
     state: str = "sharded"                                  # sharded | fwd | bwd
     ready: Optional[object] = None                          # CUDA event: gather finished
+    fetch_end: int = 0                                      # elements [0, fetch_end) are matrices their forward products fetch themselves
+    fused_fwd: bool = False                                 # forward of this block is running with such products
+    fetched: set = field(default_factory=set)               # matrices already fetched in this forward
+    src_addrs: Optional[object] = None                      # ctypes array: address of every rank's shard of this bucket
+
+
+class _GemmGather:
+    """Attached to a matrix (``w._gemm_gather``) whose forward product may fetch it from the owners' shards itself."""
+
+    def __init__(self, shards: "Zero3Shards", bucket: _Bucket, offset: int):
+        self.shards, self.bucket, self.offset = shards, bucket, offset
+
+    def pending(self, w: torch.Tensor) -> bool:
+        return self.bucket.fused_fwd and id(w) not in self.bucket.fetched
+
+    def gemm(self, x2: torch.Tensor, w: torch.Tensor, gelu: bool, pre: Optional[torch.Tensor]) -> torch.Tensor:
+        import ctypes
+        from ..native import EPI_GELU, EPI_STORE_PREACT, lib, stream_ptr
+        z, b = self.shards, self.bucket
+        M, K = x2.shape
+        N = w.shape[1]
+        y = torch.empty((M, N), dtype=x2.dtype, device=x2.device)
+        counters = torch.zeros(z.dp, dtype=torch.int32, device=x2.device)       # one per owner, raised by the kernel's copy warps
+        esz = z.flat.element_size()
+        flags = (EPI_GELU | (EPI_STORE_PREACT if pre is not None else 0)) if gelu else 0
+        lib.call("elfa_gemm_gb", x2, x2.stride(0), y, y.stride(0), M, N, K, pre, pre.stride(0) if pre is not None else 0, flags,
+                 ctypes.addressof(b.src_addrs), b.full, self.offset * esz, b.shard * esz, counters, z.rank, z.dp, 0, stream_ptr(x2))
+        b.fetched.add(id(w))
+        z.gemm_gathers += 1
+        return y
 
 
 def _is_no_decay(p: torch.nn.Parameter) -> bool:
@@ -65,7 +99,7 @@ class Zero3Shards:
 
     def __init__(self, model: torch.nn.Module, pc: ParallelContext, blocks: Optional[Iterable[torch.nn.Module]] = None,
                  grad_dtype: torch.dtype = torch.float32, prefetch: bool = True, arena=None, shard_params: bool = True,
-                 wire_bf16: bool = True):
+                 wire_bf16: bool = True, gather_in_gemm: Optional[bool] = None):
         """``arena``: a symmetric arena of the data-parallel group. With it the shards and the gradient
         slots live in peer-addressable memory and both collectives are this library's peer-load kernels
         (gather: every rank reads the peers' shards; reduce-scatter: every rank sums its slice of the
@@ -179,6 +213,27 @@ class Zero3Shards:
         self._rest_valid = not shard_params
         self.gathers = 0          # statistics (tests)
         self.reduce_scatters = 0
+        self.gemm_gathers = 0
+        # parameter gather inside the consuming GEMM (forward): matrices the block declares, laid out first in the bucket
+        import os
+        if gather_in_gemm is None:
+            gather_in_gemm = os.environ.get("ELFA_ZERO3_GATHER_IN_GEMM", "0") == "1"
+        self.gather_in_gemm = bool(gather_in_gemm and shard_params and self.arena is not None and self.dp > 1
+                                   and self.dtype == torch.bfloat16)
+        if self.gather_in_gemm:
+            import ctypes
+            esz = self.flat.element_size()
+            for b in self.block_buckets:
+                own = {id(p) for p in (b.module.gemm_weights() if hasattr(b.module, "gemm_weights") else [])}
+                end = 0
+                for p, o in zip(b.params, b.offsets):        # the leading run of declared matrices
+                    if id(p) in own and p.dim() == 2 and o == end and p.shape[0] % 8 == 0 and p.shape[1] % 8 == 0:
+                        p._gemm_gather = _GemmGather(self, b, o)
+                        end = o + (p.numel() + ALIGN - 1) // ALIGN * ALIGN
+                    else:
+                        break
+                b.fetch_end = end
+                b.src_addrs = (ctypes.c_uint64 * self.dp)(*[self.arena.peer_address(r, self._r_flat) + b.base * esz for r in range(self.dp)])
         for i, b in enumerate(self.block_buckets):
             self._hook(i, b)
         if self.arena is not None:
@@ -211,6 +266,14 @@ class Zero3Shards:
             parts = [torch.empty_like(shard) for _ in range(self.dp)]
             dist.all_gather(parts, shard.contiguous(), group=self.group)
             b.full.copy_(torch.cat(parts))
+
+    def _gather_rest_of(self, b: _Bucket) -> None:
+        """What no product fetches itself (``[fetch_end, numel)``: norm weights, biases) by a windowed peer-load copy."""
+        import ctypes
+        from ..native import lib, stream_ptr
+        esz = self.flat.element_size()
+        lib.call("elfa_zero3_gather_window", ctypes.addressof(self._peer["flat"]), self.dp, b.base * esz, b.shard * esz,
+                 b.fetch_end * esz, b.numel * esz, b.full, stream_ptr(b.full))
 
     def _gather(self, b: _Bucket, state: str, asynchronous: bool = False) -> None:
         if b.state != "sharded":
@@ -295,6 +358,11 @@ class Zero3Shards:
         def pre_forward(module, args):
             if not self.shard_params:
                 return                      # stage 2: the parameters are resident
+            if self.gather_in_gemm and b.fetch_end > 0 and b.state == "sharded":
+                # the block's products fetch their matrices themselves; only the rest of the bucket is copied here
+                self._gather_rest_of(b)
+                b.state, b.fused_fwd, b.fetched = "fwd", True, set()
+                return
             if b.state == "sharded":
                 self._gather(b, "fwd")
             self._wait(b)
@@ -305,6 +373,7 @@ class Zero3Shards:
         def post_forward(module, args, out):
             if not self.shard_params:
                 return
+            b.fused_fwd = False
             if b.state == "fwd":
                 b.state = "sharded"         # the slot may be overwritten; backward gathers again
 

@@ -29,9 +29,15 @@ def _run(args, port, timeout=600, extra_env=None):
     return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
 
 
+def _why(r):
+    """The workers' own error lines first (the launcher's per-rank summary is long at 8 ranks), then the tails."""
+    own = [ln for ln in r.stderr.splitlines() if ("Error" in ln or "assert" in ln) and "ChildFailedError" not in ln and "elastic" not in ln]
+    return "\n".join(own[:12]) + "\n" + r.stdout[-2000:] + r.stderr[-3000:]
+
+
 def test_fused_ag_gemm_and_gemm_rs(cuda_device):
     r = _run(["fused"], 29701)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, _why(r)
     assert "FUSED_OK" in r.stdout
 
 
@@ -88,6 +94,14 @@ def test_zero3_parameter_sharding_matches_single_gpu(cuda_device, backend):
     assert "ZERO_OK stage=3" in r.stdout
     if backend == "fused":
         assert "peer_kernels=True" in r.stdout
+
+
+def test_zero3_parameter_gather_inside_the_gemm(cuda_device):
+    """Stage 3 with the forward products fetching their matrices from the owners' shards themselves (bulk loads from peer
+    memory into the local slot, K blocks multiplied as they arrive); same losses as one GPU on the global batch."""
+    r = _run(["zero", "fused", "bf16", "3"], 29718, extra_env={"ELFA_ZERO3_GATHER_IN_GEMM": "1"})
+    assert r.returncode == 0, _why(r)
+    assert "ZERO_OK stage=3" in r.stdout and "gather_in_gemm=True" in r.stdout
 
 
 @pytest.mark.parametrize("backend", ["nccl", "fused"])
