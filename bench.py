@@ -402,7 +402,7 @@ def main() -> int:
                    if cfg.quant.backward == "mxfp8" else "backward GEMMs bf16")
             dtype_note = (f"bf16 ({cfg.quant.attention.upper()} / {cfg.quant.mlp.upper()} QAT on the attention / MLP GEMMs: forward GEMMs multiply block-scaled "
                           "payloads on the tensor cores at N = 1; at N > 1 the column-parallel layers all-gather quantised payloads and multiply them block-scaled, "
-                          f"the row-parallel GEMM->reduce-scatter kernel multiplies fake-quantised bf16 operands (the same product); {bwd}; "
+                          f"the row-parallel GEMM->reduce-scatter kernel multiplies block-scaled MXFP8 payloads too (NVFP4 layers: fake-quantised bf16 operands, the same product); {bwd}; "
                           "fp32 master weights / moments / grad accumulation)")
         parallelism = "single" if world == 1 else "+".join(
             ([f"tp{tpn}+sp"] if tpn > 1 else []) + ([f"dp{dp_size}-zero{cfg.runtime.zero_stage}"] if dp_size > 1 else []))

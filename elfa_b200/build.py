@@ -38,11 +38,6 @@ def find_nvcc() -> str:
     return cand
 
 
-def _newest_header_mtime() -> float:
-    headers = [p for pat in ("*.h", "*.hpp", "*.cuh") for p in CSRC.glob(pat)]
-    return max((p.stat().st_mtime for p in headers), default=0.0)
-
-
 def source_hash() -> str:
     """SHA-256 over the names and contents of every native source and header: the identity of the sources a library was
     built from. It is compiled into the library (``elfa_source_hash``) and checked when the library is loaded."""
@@ -85,6 +80,24 @@ def build(force: bool = False, verbose: bool = False, bounds: bool = False) -> P
     return _build_variant(force, verbose, LIB, OBJ_DIR, ())
 
 
+def object_keys(csrc: Path, extra_flags=(), digest: str = "") -> dict:
+    """``{source stem: key}``: an object file is current when the key recorded beside it equals the hash of its source, of
+    every header it may include and of the extra compiler flags (file times do not survive a copy of the tree to another
+    machine). ``runtime.cu`` also carries ``digest``, the hash of all sources, which is compiled into it."""
+    import hashlib
+    hdr = hashlib.sha256()
+    for h in sorted(q for pat in ("*.h", "*.hpp", "*.cuh") for q in csrc.glob(pat)):
+        hdr.update(h.name.encode() + b"\0" + h.read_bytes() + b"\0")
+    hdr.update(" ".join(extra_flags).encode())
+    keys = {}
+    for src in sorted(csrc.glob("*.cu")) + sorted(csrc.glob("*.cpp")):
+        key = hashlib.sha256(hdr.digest() + src.read_bytes()).hexdigest()
+        if src.name == "runtime.cu":
+            key = hashlib.sha256((key + digest).encode()).hexdigest()
+        keys[src.stem] = key
+    return keys
+
+
 def _build_variant(force: bool, verbose: bool, LIB: Path, OBJ_DIR: Path, extra_flags) -> Path:
     nvcc = find_nvcc()
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
@@ -93,23 +106,12 @@ def _build_variant(force: bool, verbose: bool, LIB: Path, OBJ_DIR: Path, extra_f
         raise RuntimeError("no native sources found")
     digest = source_hash()
     stamp = OBJ_DIR / "source_hash.txt"
-    # an object is current when the hash of its source and of every header it may include matches the one recorded beside it
-    # (file times do not survive a copy of the tree to another machine)
-    import hashlib
-    hdr = hashlib.sha256()
-    for h in sorted(q for pat in ("*.h", "*.hpp", "*.cuh") for q in CSRC.glob(pat)):
-        hdr.update(h.name.encode() + b"\0" + h.read_bytes() + b"\0")
-    hdr.update(" ".join(extra_flags).encode())
     jobs = []
-    want = {}
+    want = object_keys(CSRC, extra_flags, digest)
     for src in sources:
         obj = OBJ_DIR / (src.stem + ".o")
-        key = hashlib.sha256(hdr.digest() + src.read_bytes()).hexdigest()
-        if src.name == "runtime.cu":
-            key = hashlib.sha256((key + digest).encode()).hexdigest()     # carries the hash of all sources
-        want[src.stem] = key
         rec = OBJ_DIR / (src.stem + ".hash")
-        if force or not obj.exists() or not rec.exists() or rec.read_text().strip() != key:
+        if force or not obj.exists() or not rec.exists() or rec.read_text().strip() != want[src.stem]:
             jobs.append((src, obj))
     if jobs:
         def flags(src):

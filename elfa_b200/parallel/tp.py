@@ -192,9 +192,9 @@ _side_streams = {}
 
 def _overlap_wgrad(pc: ParallelContext, t: torch.Tensor) -> bool:
     """Whether the weight-gradient GEMM runs on a second stream next to the fused GEMM→reduce-scatter kernel
-    (which then gets 7/16 of the SMs). Off unless ``ELFA_OVERLAP_WGRAD=1``: measured on the 7B configuration it
-    costs 6 % at 2 ranks (the GEMM dominates there) and 5 % at 8 ranks (1061 vs 1011 ms per step), because the
-    reduce-scatter kernel's own GEMM slows down more than the overlap saves."""
+    (which then gets 7/16 of the SMs). Off unless ``ELFA_OVERLAP_WGRAD=1``: on the 7B configuration at 2 ranks, where the
+    products dominate, it costs 5 % (60.0 against 62.9 K tokens/s): the reduce-scatter kernel's own GEMM slows down more
+    than the overlap saves."""
     import os
     if not (t.is_cuda and pc.comm_backend == "fused" and pc.tp_size > 1):
         return False

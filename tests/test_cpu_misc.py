@@ -571,3 +571,22 @@ def test_bench_takes_the_headline_branch_at_every_world_size(world, monkeypatch)
     cfg.runtime.world_size = world
     mb, scaling, _ = bench.plan_run(cfg, ytp, yw, world)
     assert scaling == "weak" and cfg.training.global_batch_size == mb * world and cfg.runtime.tensor_parallel_size == 1
+
+
+def test_build_object_keys_follow_contents(tmp_path):
+    """An object is rebuilt when its source, a header or the flags change - and only then (contents, not file times)."""
+    from elfa_b200.build import object_keys
+    (tmp_path / "a.cu").write_text("// a\n")
+    (tmp_path / "runtime.cu").write_text("// r\n")
+    (tmp_path / "c.cuh").write_text("// h\n")
+    k0 = object_keys(tmp_path, (), "d0")
+    assert set(k0) == {"a", "runtime"} and k0 == object_keys(tmp_path, (), "d0")
+    (tmp_path / "a.cu").write_text("// a2\n")
+    k1 = object_keys(tmp_path, (), "d0")
+    assert k1["a"] != k0["a"] and k1["runtime"] == k0["runtime"]
+    assert object_keys(tmp_path, (), "d1")["runtime"] != k1["runtime"] and object_keys(tmp_path, (), "d1")["a"] == k1["a"]
+    (tmp_path / "c.cuh").write_text("// h2\n")
+    k2 = object_keys(tmp_path, (), "d0")
+    assert k2["a"] != k1["a"] and k2["runtime"] != k1["runtime"]
+    k3 = object_keys(tmp_path, ("-DELFA_BOUNDS",), "d0")
+    assert k3["a"] != k2["a"] and k3["runtime"] != k2["runtime"]
