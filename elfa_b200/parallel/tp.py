@@ -193,8 +193,8 @@ _side_streams = {}
 def _overlap_wgrad(pc: ParallelContext, t: torch.Tensor) -> bool:
     """Whether the weight-gradient GEMM runs on a second stream next to the fused GEMM→reduce-scatter kernel
     (which then gets 7/16 of the SMs). Off unless ``ELFA_OVERLAP_WGRAD=1``: on the 7B configuration at 2 ranks, where the
-    products dominate, it costs 5 % (60.0 against 62.9 K tokens/s): the reduce-scatter kernel's own GEMM slows down more
-    than the overlap saves."""
+    products dominate, it costs 5 % (60.0 against 62.9 K tokens/s), and at 8 ranks 4.5 % (139.6 against 146.2 K): the
+    reduce-scatter kernel's own GEMM and store pipeline slow down more than the overlap saves."""
     import os
     if not (t.is_cuda and pc.comm_backend == "fused" and pc.tp_size > 1):
         return False
