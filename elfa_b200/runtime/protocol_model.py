@@ -12,6 +12,11 @@ Modelled (same rules as the kernels and their host bookkeeping):
   every peer and then raises that peer's arrival counter; counters only grow, the wait target of the
   ``n``-th use of a slot is ``(n + 1) * world``. With ``ring=2`` the protocol is safe; ``ring=1`` is the
   negative control (a fast rank overwrites data a slow one has not read yet).
+* :class:`DeferredSignalPushModel` - the push role of the fused all-gather kernels as it runs now (``csrc/comm.cuh``
+  ``push_ranges``): stores are asynchronous (bulk copies that complete some time after they were issued, in any order), the
+  peers are served one after the other without draining the pipeline, and a peer's counter is raised only after the NEXT
+  peer's stores have been issued and every store older than those is known to be complete (``cp.async.bulk.wait_group n``
+  with ``n`` = the stores issued since). Raising the counter without that wait is the negative control.
 * :class:`MailboxModel` - the two-slot neighbour mailbox of ``parallel/sp.py`` (``csrc/p2p.cu``):
   arrival counter on the receiver, acknowledgement counter on the sender, a send waits for the
   acknowledgement of the message that used the same slot two sends ago.
@@ -91,6 +96,102 @@ class PushGatherModel:
         for t in ts:
             t.start()
         for t in ts:
+            t.join()
+        return self.ranks
+
+
+class DeferredSignalPushModel:
+    """``world`` ranks, each pushes ``pieces`` pieces of its shard to every peer per operation. A store is issued into the
+    rank's queue and lands when the rank's link thread gets to it (random order among the queued ones, random delays);
+    ``wait_all_but(n)`` returns once every store except the ``n`` most recently issued has landed."""
+
+    def __init__(self, world: int, pieces: int = 3, ring: int = 2, seed: int = 0, max_delay_s: float = 2e-4, wait_limit_s: float = 5.0,
+                 wait_for_completion: bool = True):
+        self.world, self.pieces, self.ring = world, pieces, ring
+        self.rng = random.Random(seed)
+        self.max_delay, self.limit = max_delay_s, wait_limit_s
+        self.wait_for_completion = wait_for_completion
+        # data[rank][slot][source][piece] = stamp (op, source, piece); arrivals[rank][slot][source] = uses signalled so far
+        self.data = [[[[None] * pieces for _ in range(world)] for _ in range(ring)] for _ in range(world)]
+        self.arrivals = [[[0] * world for _ in range(ring)] for _ in range(world)]
+        self.queue = [[] for _ in range(world)]           # per sender: [issue index, landed?, (peer, slot, piece, stamp)]
+        self.issued = [0] * world
+        self.lock = threading.Lock()
+        self.stop = False
+        self.ranks = [_Rank() for _ in range(world)]
+
+    def _link(self, r: int):
+        """The sender's link: lands queued stores one at a time, any of the queued ones next."""
+        rng = random.Random(self.rng.random() + 100 + r)
+        while not self.stop:
+            with self.lock:
+                waiting = [e for e in self.queue[r] if not e[1]]
+                e = rng.choice(waiting) if waiting else None
+            if e is None:
+                time.sleep(0)
+                continue
+            time.sleep(rng.random() * self.max_delay)
+            peer, slot, piece, stamp = e[2]
+            self.data[peer][slot][r][piece] = stamp
+            with self.lock:
+                e[1] = True
+
+    def _wait_all_but(self, r: int, n: int) -> bool:
+        def done():
+            with self.lock:
+                limit = self.issued[r] - n
+                ok = all(e[1] for e in self.queue[r] if e[0] < limit)
+                if ok:
+                    self.queue[r] = [e for e in self.queue[r] if not (e[1] and e[0] < limit)]
+                return ok
+        return _wait(done, self.limit)
+
+    def _run_rank(self, r: int, ops: int):
+        rng = random.Random(self.rng.random() + r)
+        me = self.ranks[r]
+        for n in range(ops):
+            slot, use = n % self.ring, n // self.ring + 1
+            for p in range(self.pieces):                 # the own shard is a local copy
+                self.data[r][slot][r][p] = (n, r, p)
+            self.arrivals[r][slot][r] = use
+            prev = None
+            for i in range(1, self.world):
+                peer = (r + i) % self.world
+                for p in range(self.pieces):
+                    time.sleep(rng.random() * self.max_delay)
+                    with self.lock:
+                        self.queue[r].append([self.issued[r], False, (peer, slot, p, (n, r, p))])
+                        self.issued[r] += 1
+                if prev is not None:
+                    if self.wait_for_completion and not self._wait_all_but(r, self.pieces):
+                        me.status = TIMEOUT
+                        return
+                    self.arrivals[prev][slot][r] = use   # release: everything older has landed
+                prev = peer
+            if prev is not None:
+                if self.wait_for_completion and not self._wait_all_but(r, 0):
+                    me.status = TIMEOUT
+                    return
+                self.arrivals[prev][slot][r] = use
+            for i in range(self.world):                  # consume in arrival order: own shard, then rank - 1, rank - 2, ...
+                src = (r - i) % self.world
+                if not _wait(lambda: self.arrivals[r][slot][src] >= use, self.limit):
+                    me.status = TIMEOUT
+                    return
+                for p in range(self.pieces):
+                    got = self.data[r][slot][src][p]
+                    if got != (n, src, p):
+                        me.errors.append(f"rank {r} op {n}: slot {slot} source {src} piece {p} holds {got}")
+
+    def run(self, ops: int) -> List[_Rank]:
+        links = [threading.Thread(target=self._link, args=(r,)) for r in range(self.world)]
+        ts = [threading.Thread(target=self._run_rank, args=(r, ops)) for r in range(self.world)]
+        for t in links + ts:
+            t.start()
+        for t in ts:
+            t.join()
+        self.stop = True
+        for t in links:
             t.join()
         return self.ranks
 

@@ -590,3 +590,20 @@ def test_build_object_keys_follow_contents(tmp_path):
     assert k2["a"] != k1["a"] and k2["runtime"] != k1["runtime"]
     k3 = object_keys(tmp_path, ("-DELFA_BOUNDS",), "d0")
     assert k3["a"] != k2["a"] and k3["runtime"] != k2["runtime"]
+
+
+def test_deferred_signal_push_protocol_model():
+    """The push role as it runs now: asynchronous stores that land in any order, peers served without draining the pipeline, a
+    peer's counter raised one peer late after the older stores are known to have landed. Safe with the wait; the negative
+    control (counter raised without it) lets a consumer read pieces that have not landed."""
+    from elfa_b200.runtime.protocol_model import DeferredSignalPushModel
+    for seed in range(2):
+        ranks = DeferredSignalPushModel(4, pieces=3, seed=seed).run(16)
+        assert all(r.status == 0 and not r.errors for r in ranks), [r.errors[:2] for r in ranks]
+    broken = 0
+    for seed in range(20):
+        ranks = DeferredSignalPushModel(4, pieces=3, seed=seed, wait_for_completion=False).run(16)
+        broken += any(r.errors for r in ranks)
+        if broken:
+            break
+    assert broken > 0
