@@ -123,7 +123,7 @@ class _Linear(torch.autograd.Function):
             x2 = x2.contiguous()
         pre = None
         fetch = getattr(w, "_gemm_gather", None)     # ZeRO stage 3: this product fetches the parameter itself (parallel/zero3.py)
-        if fetch is not None and bias is None and x2.is_cuda and act in (None, "gelu") and fetch.pending(w):
+        if fetch is not None and bias is None and act in (None, "gelu") and fetch.pending(w):
             if act == "gelu":
                 pre = torch.empty((x2.shape[0], w.shape[1]), dtype=x2.dtype, device=x2.device)
             y = fetch.gemm(x2, w, act == "gelu", pre)

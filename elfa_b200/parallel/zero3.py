@@ -73,9 +73,18 @@ class _GemmGather:
         return self.bucket.fused_fwd and id(w) not in self.bucket.fetched
 
     def gemm(self, x2: torch.Tensor, w: torch.Tensor, gelu: bool, pre: Optional[torch.Tensor]) -> torch.Tensor:
+        z, b = self.shards, self.bucket
+        if not x2.is_cuda:
+            # CPU ranks (gloo): the same bookkeeping with a library all-gather in place of the kernel's copy warps
+            from ..ops.gemm import gemm
+            full = z._all_gather_shards(b)
+            n = w.numel()
+            b.full[self.offset:self.offset + n].copy_(full[self.offset:self.offset + n])
+            b.fetched.add(id(w))
+            z.gemm_gathers += 1
+            return gemm(x2, w, b_mn=True, gelu=gelu, preact=pre, out_dtype=x2.dtype)
         import ctypes
         from ..native import EPI_GELU, EPI_STORE_PREACT, lib, stream_ptr
-        z, b = self.shards, self.bucket
         M, K = x2.shape
         N = w.shape[1]
         y = torch.empty((M, N), dtype=x2.dtype, device=x2.device)
@@ -218,8 +227,8 @@ class Zero3Shards:
         import os
         if gather_in_gemm is None:
             gather_in_gemm = os.environ.get("ELFA_ZERO3_GATHER_IN_GEMM", "0") == "1"
-        self.gather_in_gemm = bool(gather_in_gemm and shard_params and self.arena is not None and self.dp > 1
-                                   and self.dtype == torch.bfloat16)
+        kernel_form = self.arena is not None and self.dtype == torch.bfloat16        # GPUs with a symmetric arena
+        self.gather_in_gemm = bool(gather_in_gemm and shard_params and self.dp > 1 and (kernel_form or not self.cuda))
         if self.gather_in_gemm:
             import ctypes
             esz = self.flat.element_size()
@@ -233,7 +242,8 @@ class Zero3Shards:
                     else:
                         break
                 b.fetch_end = end
-                b.src_addrs = (ctypes.c_uint64 * self.dp)(*[self.arena.peer_address(r, self._r_flat) + b.base * esz for r in range(self.dp)])
+                if kernel_form:
+                    b.src_addrs = (ctypes.c_uint64 * self.dp)(*[self.arena.peer_address(r, self._r_flat) + b.base * esz for r in range(self.dp)])
         for i, b in enumerate(self.block_buckets):
             self._hook(i, b)
         if self.arena is not None:
@@ -267,8 +277,18 @@ class Zero3Shards:
             dist.all_gather(parts, shard.contiguous(), group=self.group)
             b.full.copy_(torch.cat(parts))
 
+    def _all_gather_shards(self, b: _Bucket) -> torch.Tensor:
+        """The bucket's concatenated shards through the library (CPU ranks)."""
+        shard = self.flat[b.base:b.base + b.shard]
+        parts = [torch.empty_like(shard) for _ in range(self.dp)]
+        dist.all_gather(parts, shard.contiguous(), group=self.group)
+        return torch.cat(parts)
+
     def _gather_rest_of(self, b: _Bucket) -> None:
         """What no product fetches itself (``[fetch_end, numel)``: norm weights, biases) by a windowed peer-load copy."""
+        if self.arena is None:
+            b.full[b.fetch_end:b.numel].copy_(self._all_gather_shards(b)[b.fetch_end:b.numel])
+            return
         import ctypes
         from ..native import lib, stream_ptr
         esz = self.flat.element_size()

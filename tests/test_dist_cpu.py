@@ -59,6 +59,15 @@ def test_zero_data_parallel_matches_single_rank_on_cpu(stage):
     assert "ZERO_OK" in r.stdout
 
 
+def test_zero3_gather_in_gemm_bookkeeping_on_cpu():
+    """Stage 3 with the forward products fetching their matrices themselves (on CPU ranks a library all-gather stands in for
+    the kernel's copy warps): same losses as one rank, four fetches per block and micro-batch, whole-block gathers only in
+    backward."""
+    r = _run(2, ["zero_cpu", "nccl", "fp32", "3"], 29628, extra_env={"ELFA_ZERO3_GATHER_IN_GEMM": "1"})
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "ZERO_OK stage=3" in r.stdout and "gather_in_gemm=True" in r.stdout
+
+
 @pytest.mark.parametrize("stage", [1, 2, 3])
 def test_sharded_optimizer_state_survives_checkpoint(stage, tmp_path):
     r = _run(2, ["ckpt_cpu", str(stage), str(tmp_path / "ck")], 29641 + stage)
