@@ -19,10 +19,14 @@ def _ngpus():
     return min(n, want)
 
 
-def _run(args, port, timeout=600, extra_env=None):
+def _run(args, port, timeout=600, extra_env=None, nproc=None):
     n = _ngpus()
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
+    if nproc is not None:
+        if n < nproc:
+            pytest.skip(f"needs at least {nproc} GPUs (ELFA_TEST_GPUS={nproc})")
+        n = nproc
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), os.path.join(ROOT, "tests", "dist_worker.py"), *args]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", **(extra_env or {}))
@@ -125,6 +129,15 @@ def test_multimem_collectives_through_the_switch(cuda_device):
         r = _run(["zero", "fused", "bf16", "0"], 29717, extra_env={"ELFA_NVLS": "1"})
         assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
         assert "ZERO_OK stage=0" in r.stdout and "nvls=True" in r.stdout
+
+
+def test_tensor_parallel_times_data_parallel_zero2_mixed_quant(cuda_device):
+    """The layout of the 13B benchmark configuration in small (TP 2 x DP 2, ZeRO-2, NVFP4 MLP + MXFP8 attention QAT, fused
+    backend) against one GPU on the global batch. Needs four GPUs (``ELFA_TEST_GPUS=4``); the same worker runs as four gloo
+    ranks in the CPU suite."""
+    r = _run(["hybrid", "fused", "bf16", "2"], 29719, nproc=4)
+    assert r.returncode == 0, _why(r)
+    assert "HYBRID_OK tp=2 dp=2" in r.stdout
 
 
 def test_ring_handoff_through_peer_mailboxes(cuda_device):
