@@ -245,7 +245,10 @@ def cmd_profile(a) -> int:
           "  python -m elfa_b200.utils.microbench gemm|attn_fwd|efla|...   # one kernel, device-timed, for a small capture\n"
           "  ELFA_TRACE=1 adds NVTX ranges and per-phase device times (trainer.tracer.summary())\n"
           "  python bench.py --twin 8    # per-rank compute time of an 8-rank job without communication, on one GPU\n"
-          "  ELFA_FLAG_TIMEOUT_MS=500 shortens every device-side wait; the status word reports a timeout")
+          "  ELFA_FLAG_TIMEOUT_MS=500 shortens every device-side wait; the status word reports a timeout\n"
+          "  python -m elfa_b200.build --bounds; ELFA_BOUNDS=1 ...   # checked build: index tests inside the pipelined kernels (status bit 4)\n"
+          "  torchrun --nproc-per-node N baseline/link_probe.py      # peer-memory copy mechanisms apart from any GEMM\n"
+          "  torchrun --nproc-per-node N baseline/fused_vs_nccl.py   # fused kernels against NCCL collective + GEMM, per op")
     return 0
 
 
