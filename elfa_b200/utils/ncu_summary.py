@@ -22,6 +22,7 @@ WANTED = [
     ("dram__bytes_write.sum", "DRAM written"),
     ("gpu__dram_throughput.avg.pct_of_peak_sustained_elapsed", "DRAM throughput, % of peak"),
     ("sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_active", "tensor pipe active, %"),
+    ("sm__inst_executed_pipe_xu.avg.pct_of_peak_sustained_active", "MUFU pipe (exp, rsqrt), % of peak"),
     ("sm__throughput.avg.pct_of_peak_sustained_elapsed", "SM throughput, % of peak"),
     ("smsp__issue_active.avg.pct_of_peak_sustained_active", "issue slots used, %"),
     ("sm__warps_active.avg.pct_of_peak_sustained_active", "warps active, % of slots"),
@@ -55,6 +56,17 @@ def summarise(launch: Dict[str, str], top_stalls: int = 4) -> str:
     for key, label in WANTED:
         if key in launch:
             lines.append(f"| {label} | {launch[key]} |")
+    # load balance over the SMs: a tail shows as a busiest SM far above the average
+    cyc = {}
+    for key in ("sm__cycles_active.avg", "sm__cycles_active.max", "sm__cycles_active.min", "sm__cycles_elapsed.max"):
+        try:
+            cyc[key] = float(launch[key].split()[0].replace(",", ""))
+        except (KeyError, ValueError, IndexError):
+            pass
+    if len(cyc) == 4:
+        lines.append(f"| SM active cycles avg / max / min (elapsed max) | {cyc['sm__cycles_active.avg'] / 1e3:.0f} K / "
+                     f"{cyc['sm__cycles_active.max'] / 1e3:.0f} K / {cyc['sm__cycles_active.min'] / 1e3:.0f} K "
+                     f"({cyc['sm__cycles_elapsed.max'] / 1e3:.0f} K) |")
     stalls = []
     for k, v in launch.items():
         if k.startswith(STALL_PREFIX) and k.endswith(STALL_SUFFIX):
