@@ -1,6 +1,6 @@
 """Peer-memory copy rates of the mechanisms the fused kernels can use, apart from any GEMM:
 per-thread 16-byte stores against a bulk-copy pipeline through shared memory, for several grid sizes, piece sizes and
-pipeline depths; plus the copy engine (``Tensor.copy_`` between the two GPUs' arenas) and NCCL's all-gather for reference.
+pipeline depths; plus NCCL's all-gather (on local tensors) for reference.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29570 \
         baseline/link_probe.py [--mb 256]
