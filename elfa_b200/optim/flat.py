@@ -60,7 +60,9 @@ class FlatParams:
         items.sort(key=key)
         self.names = [n for n, _ in items]
         self.params = [p for _, p in items]
-        self.dtype = self.params[0].dtype
+        # the buffer has the dtype of the model's weights (the largest parameter's), not of whichever parameter sorts first: a small
+        # fp32 parameter (a learned scalar) may lead the order and is then stored in the model dtype like everything else
+        self.dtype = max(self.params, key=lambda p: p.numel()).dtype
         self.device = self.params[0].device
         self.dp_size, self.dp_rank = dp_size, dp_rank
         offsets, off = [], 0

@@ -122,7 +122,7 @@ class Zero3Shards:
         self.group = pc.dp_group
         named = list(model.named_checkpoint_parameters()) if hasattr(model, "named_checkpoint_parameters") else list(model.named_parameters())
         named = [(n, p) for n, p in named if p.requires_grad]
-        self.dtype = named[0][1].dtype
+        self.dtype = max((p for _, p in named), key=lambda p: p.numel()).dtype      # the weights' dtype, not a leading scalar's
         self.device = named[0][1].device
         self.cuda = self.device.type == "cuda"
         blocks = list(blocks if blocks is not None else getattr(model, "blocks", []))

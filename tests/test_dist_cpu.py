@@ -101,6 +101,14 @@ def test_efla_family_tensor_and_sequence_parallel_training_matches_single_rank_o
     assert "EFLA_TP_OK" in r.stdout
 
 
+def test_efla_family_tensor_parallel_in_bf16_on_cpu():
+    """The same with a bf16 model: every weight stays bf16 although the fp32 learned scalar leads the flat buffer's order
+    (tensor-parallel replicated class), and the losses follow the single-rank run."""
+    r = _run(2, ["efla_tp_cpu", "nccl", "bf16", "2", "1"], 29759)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "EFLA_TP_OK tp=2" in r.stdout
+
+
 def test_rank_that_leaves_between_steps_is_detected_on_the_host(tmp_path):
     """Host-side fault injection (kill_rank) + heartbeat soft barrier: survivors raise RankFailure, nobody hangs."""
     env = {"ELFA_FAULT": "kill_rank:rank=2,step=3,code=0", "ELFA_HEARTBEAT_DIR": str(tmp_path / "hb"), "ELFA_HEARTBEAT_TIMEOUT_S": "3"}

@@ -140,6 +140,14 @@ def test_tensor_parallel_times_data_parallel_zero2_mixed_quant(cuda_device):
     assert "HYBRID_OK tp=2 dp=2" in r.stdout
 
 
+def test_efla_family_tensor_parallel_training(cuda_device):
+    """The EFLA + PRISM family with heads, MLP columns and vocabulary sharded over two GPUs (bf16, Lion; Lion + Muon runs too)
+    against one GPU on the global batch."""
+    r = _run(["efla_tp", "nccl", "bf16", "2"], 29720, nproc=2)
+    assert r.returncode == 0, _why(r)
+    assert "EFLA_TP_OK tp=2" in r.stdout
+
+
 def test_ring_handoff_through_peer_mailboxes(cuda_device):
     r = _run(["mailbox"], 29709)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
