@@ -14,4 +14,4 @@ def test_flat_buffer_takes_the_weights_dtype_not_the_first_parameters():
     assert flat.names[0] == "beta"                       # the replicated class leads the order
     assert flat.dtype == torch.bfloat16 and flat.flat.dtype == torch.bfloat16
     assert w1.dtype == torch.bfloat16 and w2.dtype == torch.bfloat16 and beta.dtype == torch.bfloat16
-    assert float(beta) == 1.0
+    assert float(beta.detach()) == 1.0
